@@ -1,0 +1,345 @@
+"""Pins the CPU checker against every known answer the reference's own tests hold for the path."""
+import math
+
+import numpy as np
+import pytest
+
+from oracle import dpstep as orc
+from oracle import host_logic as hl
+
+NAN = float("nan")
+
+
+def one_tensor_state(values, work_dtype=orc.F32):
+    p = np.array(values, dtype=np.float32)
+    return orc.StepState([p], [np.zeros_like(p)], [np.zeros_like(p)], None, work_dtype)
+
+
+def clip_only(grads, max_value, max_norm):
+    """clip_gradients alone (src/grad_clip.rs:36-56): returns (norm, clipped grads)."""
+    flat = [np.array(g, dtype=np.float32) for g in grads]
+    if max_value == max_value:
+        raw = math.sqrt(sum(orc.sumsq(g) for g in flat))
+        if not math.isfinite(raw):
+            return raw, flat
+        for g in flat:
+            orc.lib().orc_clamp(g.ctypes.data, g.size, max_value)
+    norm = math.sqrt(sum(orc.sumsq(g) for g in flat))
+    if math.isfinite(norm) and norm > max_norm:
+        c = np.float32(max_norm / (norm + 1e-6))
+        for g in flat:
+            orc.lib().orc_scale(g.ctypes.data, g.size, c)
+    return norm, flat
+
+
+F64_MAX = 1.7976931348623157e308
+
+
+def test_norm_of_3_4_is_5_and_grads_unchanged():
+    # src/grad_clip.rs:118-128
+    norm, g = clip_only([[3.0, 4.0]], NAN, F64_MAX)
+    assert abs(norm - 5.0) < 1e-6
+    assert g[0].tolist() == [3.0, 4.0]
+
+
+def test_value_clip_bounds_huge_gradients():
+    # src/grad_clip.rs:82-96
+    norm, g = clip_only([[1e15, -1e15, 0.25], [-7e14, 3.0]], 0.5, F64_MAX)
+    vals = np.concatenate(g)
+    assert np.all(np.abs(vals) <= 0.5)
+    assert vals[2] == 0.25
+    assert abs(norm - math.sqrt(4.0 * 0.25 + 0.0625)) < 1e-6
+
+
+def test_norm_clip_runs_after_value_clip():
+    # src/grad_clip.rs:98-116: clamp to 3 gives norm 6, the norm clip scales to 1.5 -> elements 0.75
+    norm, g = clip_only([[100.0, -100.0, 100.0, -100.0]], 3.0, 1.5)
+    assert abs(norm - 6.0) < 1e-5
+    assert np.all(np.abs(np.abs(g[0]) - 0.75) < 1e-5)
+
+
+@pytest.mark.parametrize("bad", [float("nan"), float("inf"), float("-inf")])
+def test_non_finite_gradient_reports_non_finite_norm(bad):
+    # src/grad_clip.rs:130-143
+    norm, _ = clip_only([[1.0, bad]], 0.5, 1.0)
+    assert not math.isfinite(norm)
+
+
+def test_sum_over_ranks_is_a_sum_not_a_mean():
+    # src/dp/reduce.rs:88-121: [1,0] + [2,-1] = [3,-1]
+    r0 = np.array([1.0, -0.0], dtype=np.float32)
+    r1 = np.array([2.0, -1.0], dtype=np.float32)
+    assert orc.sum_ranks([r0, r1], orc.F32).tolist() == [3.0, -1.0]
+
+
+def test_unscale_widens_f16_so_tiny_gradients_survive():
+    # src/loss_scale/scaler.rs:249-271
+    tiny = np.float32(1e-8)
+    assert orc.widen(orc.to_f16(np.array([tiny])), orc.F16)[0] == 0.0
+    scaled = orc.to_f16(np.array([tiny * np.float32(65536.0)], dtype=np.float32))
+    got = orc.unscale(scaled, orc.F16, 65536.0)
+    assert got.dtype == np.float32
+    assert abs(got[0] - tiny) < tiny * 2e-3
+
+
+def test_f16_and_bf16_conversions_match_numpy():
+    rng = np.random.default_rng(0)
+    x = np.concatenate([
+        rng.standard_normal(20000).astype(np.float32) * np.float32(10.0) ** rng.integers(-9, 6, 20000).astype(np.float32),
+        np.array([0.0, -0.0, 65504.0, 65520.0, 65519.99, 1e-8, 5.96e-8, 2.98e-8, 2.9802322e-8, 6.1e-5, np.inf, -np.inf], np.float32),
+    ])
+    want = x.astype(np.float16).view(np.uint16)
+    got = orc.to_f16(x)
+    assert np.array_equal(got, want)
+    assert np.array_equal(orc.widen(got, orc.F16), want.view(np.float16).astype(np.float32))
+    # bf16: round to nearest even on the top 16 bits
+    u = x.view(np.uint32).astype(np.uint64)
+    want_bf = ((u + 0x7FFF + ((u >> 16) & 1)) >> 16).astype(np.uint16)
+    assert np.array_equal(orc.to_bf16(x), want_bf)
+    assert np.isnan(orc.widen(orc.to_bf16(np.array([np.nan], np.float32)), orc.BF16)[0])
+
+
+def test_scaler_halves_on_overflow_and_grows_after_interval():
+    # src/loss_scale/scaler.rs:273-289
+    s = hl.LossScaler(hl.LossScaleConfig(initial=64.0, growth_interval=2))
+    s.record_step(True)
+    assert s.scale() == 32.0
+    s.record_step(False)
+    assert s.scale() == 32.0
+    s.record_step(False)
+    assert s.scale() == 64.0
+
+
+def test_scaler_growth_table():
+    # tests/loss_scale.rs:180-214
+    s = hl.LossScaler(hl.LossScaleConfig(initial=64.0, growth_interval=2))
+    for scale, ok in [(64.0, 1), (128.0, 0), (128.0, 1), (256.0, 0)]:
+        s.record_step(False)
+        assert (s.state().scale, s.state().consecutive_ok) == (scale, ok)
+
+
+def test_scaler_defaults_and_checks():
+    # src/loss_scale/config.rs:134-235
+    c = hl.LossScaleConfig()
+    assert (c.initial, c.growth_factor, c.backoff_factor, c.growth_interval) == (65536.0, 2.0, 0.5, 2000)
+    for bad in [dict(initial=0.0), dict(growth_factor=1.0), dict(backoff_factor=1.0), dict(growth_interval=0)]:
+        with pytest.raises(ValueError):
+            hl.LossScaleConfig(**bad).check()
+    s = hl.LossScaler()
+    with pytest.raises(ValueError):
+        s.restore(hl.GradScalerState(NAN, 0))
+    s.restore(hl.GradScalerState(512.0, 7))
+    assert (s.state().scale, s.state().consecutive_ok) == (512.0, 7)
+
+
+def test_overflow_step_changes_nothing_and_backs_off():
+    # tests/loss_scale.rs:118-176: params bit-unchanged, timestep 0, scale 2^20 -> 2^19
+    st = one_tensor_state([0.5, -0.25, 1.0])
+    before = [a.copy() for a in (st.master[0], st.exp_avg[0], st.exp_avg_sq[0])]
+    g = orc.to_f16(np.array([1.0, np.inf, 2.0], dtype=np.float32))
+    scaler = hl.LossScaler(hl.LossScaleConfig(initial=1048576.0))
+    res = orc.step(st, [[g]], orc.F16, orc.StepConfig(loss_scale=scaler.scale()))
+    assert res.overflow == 1 and res.applied == 0 and st.timestep == 0
+    assert not math.isfinite(res.reported_norm)
+    hl.record_after_step(scaler, bool(res.overflow), False)
+    assert (scaler.state().scale, scaler.state().consecutive_ok) == (524288.0, 0)
+    for a, b in zip(before, (st.master[0], st.exp_avg[0], st.exp_avg_sq[0])):
+        assert np.array_equal(a.view(np.uint32), b.view(np.uint32))
+
+
+NAMES = [
+    ("model.embed_tokens.weight", 2), ("model.layers.0.input_layernorm.weight", 1),
+    ("model.layers.0.self_attn.q_proj.weight", 2), ("model.layers.0.self_attn.q_proj.bias", 1),
+    ("model.layers.0.self_attn.q_proj.lora_a", 2), ("model.layers.1.mamba.a_log", 2),
+    ("model.layers.1.mamba.d_param", 1), ("model.layers.1.mamba.dt_bias", 1),
+    ("model.layers.1.mamba.b_bias", 2), ("lm_head.weight", 2),
+]
+
+
+def test_skip_1d_golden_names():
+    # src/weight_decay/rule.rs:142-176
+    spec = hl.WeightDecaySpec("skip_1d")
+    assert [n for n, r in NAMES if spec.excludes(n, r)] == [
+        "model.layers.0.input_layernorm.weight", "model.layers.0.self_attn.q_proj.bias",
+        "model.layers.1.mamba.a_log", "model.layers.1.mamba.d_param", "model.layers.1.mamba.dt_bias",
+        "model.layers.1.mamba.b_bias"]
+    assert not any(hl.WeightDecaySpec("decay_all").excludes(n, r) for n, r in NAMES)
+    assert all(hl.WeightDecaySpec("skip_all").excludes(n, r) for n, r in NAMES)
+    # src/weight_decay/rule.rs:178-185
+    with_p = [n for n, r in NAMES if hl.WeightDecaySpec("skip_1d", ["embed_tokens", "lora_"]).excludes(n, r)]
+    assert "model.embed_tokens.weight" in with_p and "model.layers.0.self_attn.q_proj.lora_a" in with_p
+    assert "lm_head.weight" not in with_p and "model.layers.0.self_attn.q_proj.weight" not in with_p
+    # src/weight_decay/rule.rs:187-196
+    with pytest.raises(ValueError, match="skip_1d"):
+        hl.WeightDecaySpec("decay_all", ["embed"]).check()
+    with pytest.raises(ValueError, match=r"no_decay_patterns\[0\]"):
+        hl.WeightDecaySpec("skip_1d", [""]).check()
+
+
+def test_tied_id_counts_once():
+    # src/weight_decay/plan.rs:153-175
+    no_decay, dt, de, nde = hl.decay_plan(hl.WeightDecaySpec("skip_1d"), [
+        (7, "model.embed_tokens.weight", 2, 6), (7, "lm_head.weight", 2, 6), (9, "model.norm.weight", 1, 3)])
+    assert no_decay == {9} and (dt, de, nde) == (1, 6, 3)
+    assert hl.decay_plan(hl.WeightDecaySpec("decay_all"), [(1, "model.norm.weight", 1, 3)])[0] == set()
+
+
+def test_zero_gradient_step_moves_only_the_decay_group():
+    # tests/weight_decay.rs:102-147: g = 0, m = v = 0: decay tensors shrink in magnitude, no-decay ones keep their bits
+    rng = np.random.default_rng(1)
+    mats = rng.standard_normal(64).astype(np.float32)
+    norm = rng.standard_normal(8).astype(np.float32)
+    st = orc.StepState([mats.copy(), norm.copy()], [np.zeros(64, np.float32), np.zeros(8, np.float32)],
+                       [np.zeros(64, np.float32), np.zeros(8, np.float32)], None, orc.F32,
+                       lr_scale=[1.0, 1.0], group_wd=[NAN, 0.0])
+    res = orc.step(st, [[np.zeros(64, np.float32), np.zeros(8, np.float32)]], orc.F32, orc.StepConfig(lr=3e-3))
+    assert res.applied == 1
+    assert np.array_equal(st.master[1].view(np.uint32), norm.view(np.uint32))
+    assert np.all(np.abs(st.master[0]) < np.abs(mats))
+    assert np.all(np.sign(st.master[0]) == np.sign(mats))
+
+
+def test_skip_all_equals_weight_decay_zero():
+    # tests/weight_decay.rs:165-187: bit-exact
+    rng = np.random.default_rng(2)
+    p = rng.standard_normal(100).astype(np.float32)
+    g = (rng.standard_normal(100) * 1e-2).astype(np.float32)
+    a = orc.StepState([p.copy()], [np.zeros(100, np.float32)], [np.zeros(100, np.float32)], None, group_wd=[0.0])
+    b = orc.StepState([p.copy()], [np.zeros(100, np.float32)], [np.zeros(100, np.float32)], None)
+    orc.step(a, [[g]], orc.F32, orc.StepConfig(weight_decay=0.1))
+    orc.step(b, [[g]], orc.F32, orc.StepConfig(weight_decay=0.0))
+    assert np.array_equal(a.master[0].view(np.uint32), b.master[0].view(np.uint32))
+
+
+def test_two_ranks_overflow_on_one_skips_for_all():
+    # tests/data_parallel.rs:353-392
+    st = one_tensor_state([1.0, 2.0])
+    res = orc.step(st, [[np.array([1.0, 1.0], np.float32)], [np.array([np.inf, 1.0], np.float32)]], orc.F32,
+                   orc.StepConfig())
+    assert res.overflow == 1 and res.applied == 0
+    assert st.master[0].tolist() == [1.0, 2.0]
+
+
+def test_reported_norm_and_target_clip():
+    # src/trainer.rs:635-661
+    st = one_tensor_state([0.0, 0.0])
+    res = orc.step(st, [[np.array([3.0, 4.0], np.float32)]], orc.F32, orc.StepConfig(max_grad_norm=1.0))
+    assert abs(res.grad_norm - 5.0) < 1e-6 and res.reported_norm == 1.0
+    st = one_tensor_state([0.0, 0.0])
+    res = orc.step(st, [[np.array([3.0, 4.0], np.float32)]], orc.F32,
+                   orc.StepConfig(max_grad_norm=10.0, target_grad_norm=2.0))
+    assert res.reported_norm == 2.0 and abs(res.clip_coef - 2.0 / (5.0 + 1e-6)) < 1e-7
+    st = one_tensor_state([0.0, 0.0])
+    res = orc.step(st, [[np.array([3.0, 4.0], np.float32)]], orc.F32, orc.StepConfig(spike_skip=True))
+    assert res.applied == 0 and res.overflow == 0 and abs(res.reported_norm - 5.0) < 1e-6
+
+
+def test_absent_gradient_leaves_the_tensor_untouched():
+    # src/dp/reduce.rs:20, src/loss_scale/scaler.rs:75-77: an expert no rank routed to has no gradient
+    p0, p1 = np.ones(4, np.float32), np.ones(4, np.float32)
+    st = orc.StepState([p0, p1], [np.zeros(4, np.float32) for _ in range(2)], [np.zeros(4, np.float32) for _ in range(2)], None)
+    res = orc.step(st, [[np.full(4, 0.1, np.float32), None], [None, None]], orc.F32, orc.StepConfig())
+    assert res.applied == 1
+    assert np.array_equal(st.master[1], np.ones(4, np.float32)) and not np.array_equal(st.master[0], np.ones(4, np.float32))
+
+
+def test_spike_guard_known_answers():
+    # src/metrics/spike.rs:204-217
+    g = hl.SpikeGuard(hl.SpikeGuardConfig(window=4, z_threshold=6.0, min_steps=50))
+    for i, loss in enumerate([1.0, 2.0, 0.5]):
+        assert g.observe(i + 1, loss) is None
+    assert g.state.observed == 3 and abs(g.state.mean - 1.04) < 1e-12 and abs(g.state.variance - 0.3384) < 1e-12
+    # src/metrics/state.rs:122-152
+    g = hl.SpikeGuard(hl.SpikeGuardConfig(window=4, z_threshold=6.0, min_steps=2))
+    losses = [1e3 if i == 3 else 1.0 + 0.1 * (i % 2) for i in range(5)]
+    assert [g.judge(i, l) for i, l in enumerate(losses)] == [False, False, False, True, False]
+    assert (g.state.observed, g.state.detected, g.state.skipped) == (4, 1, 1)
+    # src/metrics/spike.rs:219-229, 254-264, 266-277
+    g = hl.SpikeGuard(hl.SpikeGuardConfig(window=4, z_threshold=1.0, min_steps=3))
+    assert g.observe(1, 1.0) is None and g.observe(2, 1.1) is None and g.observe(3, 50.0) is None
+    g = hl.SpikeGuard(hl.SpikeGuardConfig(window=4, z_threshold=6.0, min_steps=2, action="warn"))
+    g.observe(1, 1.0); g.observe(2, 1.1)
+    assert g.observe(3, 1000.0) is not None and not g.judge(3, 1000.0)
+    assert hl.SpikeGuardConfig(window=4).alpha() == 0.4 and hl.SpikeGuardConfig(min_steps=0).warmup_losses() == 2
+    g = hl.SpikeGuard(hl.SpikeGuardConfig(window=4, z_threshold=6.0, min_steps=2))
+    g.observe(1, 1.0); g.observe(2, 1.1)
+    before = (g.state.mean, g.state.variance, g.state.observed)
+    for loss in [NAN, float("inf"), float("-inf")]:
+        assert g.observe(3, loss) is None
+    assert before == (g.state.mean, g.state.variance, g.state.observed)
+
+
+def test_lr_plan_known_answers():
+    # src/schedule.rs:373-416: wsd phase boundaries and midpoints
+    base, total = 3e-4, 110
+    for shape in ["linear", "cosine", "sqrt"]:
+        f = lambda s: hl.lr_at(s, base, "wsd", 10, total, 0.1, decay_steps=20, decay_shape=shape)
+        assert f(0) == base * (1.0 / 10.0) and f(9) == base and f(10) == base and f(89) == base and f(90) == base
+        assert f(91) < base and f(109) > base * 0.1 and f(total) == base * 0.1 and f(total + 50) == base * 0.1
+    mid = lambda shape: hl.lr_at(100, base, "wsd", 10, total, 0.1, decay_steps=20, decay_shape=shape) / base
+    assert abs(mid("linear") - 0.55) < 1e-12 and abs(mid("cosine") - 0.55) < 1e-12
+    assert abs(mid("sqrt") - (0.1 + 0.9 * (1.0 - math.sqrt(0.5)))) < 1e-12
+    # src/schedule.rs:418-428: ceil(110 * 0.1) = 11 decay steps
+    d = hl.wsd_decay_steps(total, None, None)
+    assert d == 11
+    assert hl.lr_at(99, base, "wsd", 10, total, 0.1, decay_steps=d) == base
+    assert hl.lr_at(100, base, "wsd", 10, total, 0.1, decay_steps=d) < base
+    # src/schedule.rs:284-351: warmup floor and the post-warmup multiplier
+    assert hl.lr_at(0, 1e-9, "constant", 10, total, 0.0) == 1e-7
+    assert hl.lr_at(120, base, "cosine", 120, total, 0.1) == base
+    assert hl.lr_at(121, base, "cosine", 120, total, 0.1) == base * 0.1
+
+
+def test_row_layout_advance_matches_step_by_step():
+    # src/data/rows.rs:293-311
+    for rows, bs in [(10, 3), (9, 3), (7, 1), (5, 5), (11, 4)]:
+        l = hl.RowLayout(rows, bs)
+        for start_row in range(rows + 1):
+            for n in range(4 * l.batches_per_epoch() + 3):
+                pos = hl.DataPosition(2, start_row)
+                for _ in range(n):
+                    s = l.batch_start(pos)
+                    pos = hl.DataPosition(s.epoch, s.row + l.batch_size())
+                assert l.advance(hl.DataPosition(2, start_row), n) == pos
+
+
+def test_row_layout_world_known_answers():
+    # src/data/rows.rs:313-360
+    l = hl.RowLayout(10, 3)
+    assert l.batches_per_epoch() == 3 and l.total_steps(1, 2) == 6
+    assert l.batch_start(hl.DataPosition(0, 9)) == hl.DataPosition(1, 0)
+    assert hl.RowLayout(12, 2).total_steps(2, 3) == 9 and hl.RowLayout(12, 2).total_steps(4, 1) == 1
+    w = hl.RowLayout(22, 3, 2)
+    assert (w.batch_size(), w.batches_per_epoch(), w.total_steps(1, 2)) == (6, 3, 6)
+    assert w.advance(hl.DataPosition(), 4) == hl.DataPosition(1, 6)
+    with pytest.raises(ValueError, match="one global batch of 6 rows"):
+        hl.RowLayout(5, 3, 2)
+    with pytest.raises(ValueError, match="fewer than batch_size 4"):
+        hl.RowLayout(3, 4)
+
+
+def test_rank_windows_concatenate_to_the_global_window():
+    # tests/data_ranks.rs:94-122 / src/data/ranks.rs:85-103 in stream order: 23 rows, 2 ranks x 3
+    seq = 3
+    glob = hl.RowLayout(23, 6, 1)
+    ranks = hl.RowLayout(23, 3, 2)
+    gpos = hl.DataPosition()
+    rpos = [hl.DataPosition(), hl.DataPosition()]
+    for _ in range(10):
+        grows, gin, gtg, gpos = hl.rank_window(glob, gpos, 0, seq)
+        rows, ins = [], []
+        for k in range(2):
+            r, i, t, rpos[k] = hl.rank_window(ranks, rpos[k], k, seq)
+            rows += r
+            ins += i
+            assert all(tt[j] == ii[j] + 1 for ii, tt in zip(i, t) for j in range(seq))
+        assert rows == grows and ins == gin and rpos[0] == rpos[1] == gpos
+
+
+def test_step_weighting():
+    # src/dp/weighting.rs:109-201
+    assert hl.reduce_step_weighting([(2, None), (2, None)]) == [(4, None), (4, None)]
+    assert hl.reduce_step_weighting([(1, 5), (1, 7)]) == [(2, 12), (2, 12)]
+    with pytest.raises(ValueError, match="1 of 2"):
+        hl.reduce_step_weighting([(1, 5), (1, None)])
+    assert hl.reduce_step_weighting([(3, None)]) == [(3, None)]
