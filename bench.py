@@ -1,0 +1,355 @@
+#!/usr/bin/env python
+"""Benchmark of the data-parallel optimizer step (gradient sync + unscale/inf check + global-norm clip + fused AdamW
++ weight write-back) on the Llama-3.2-1B parameter set.
+
+    python bench.py --gpus 1 --steps 20 --warmup 5
+    python -m torch.distributed.run --nnodes=1 --nproc-per-node N --master-addr 127.0.0.1 --master-port P \
+        bench.py --gpus N --steps K --warmup W
+    python bench.py --impl reference ...      # the CPU restatement of the reference's path on the host cores
+
+One JSON line on stdout (rank 0). A step is one pass of the whole path over one set of synthetic gradients:
+bf16 gradients ~N(0,1e-3) from seed+rank, f32 master ~N(0,0.02), m ~N(0,1e-4), v = |N(0,1e-6)|.
+`value` is params/s with the gradients already resident in HBM; `e2e` is the same call fed from pinned host memory.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import threading
+import time
+
+import numpy as np
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+METRIC = "dp_sync_clip_adamw_step_params_per_s"
+UNIT = "params/s"
+WORKLOAD = "llama-3.2-1b"
+SEED = 1234
+HYPER = dict(lr=3e-4, beta1=0.9, beta2=0.95, eps=1e-8, weight_decay=0.1, max_grad_norm=1.0)
+# Algorithmic HBM bytes per parameter: the norm pass reads the bf16 gradient (2); the update reads gradient 2 +
+# master 4 + m 4 + v 4 and writes master 4 + m 4 + v 4 + bf16 weight 2 (28).
+BYTES_NORM, BYTES_UPDATE = 2, 28
+
+
+def measured_peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        with open(path) as f:
+            return float(json.load(f)["hbm_gbs"]), "measured"
+    return 6650.0, "fallback"
+
+
+class ClockSampler:
+    """Samples SM clocks and throttle reasons of one GPU with nvidia-smi while the timed region runs."""
+
+    FIELDS = ("clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.hw_slowdown,"
+              "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
+              "clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index: int):
+        self.index, self.proc, self.lines = index, None, []
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(["nvidia-smi", "-i", str(self.index), f"--query-gpu={self.FIELDS}",
+                                          "--format=csv,noheader,nounits", "-lms", "100"],
+                                         stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            self.thread = threading.Thread(target=self._read, daemon=True)
+            self.thread.start()
+        except OSError:
+            self.proc = None
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.lines.append(line.strip())
+
+    def stop(self) -> dict:
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=5)
+        except subprocess.TimeoutExpired:
+            self.proc.kill()
+        sm, mx, reasons = [], [], set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for line in self.lines:
+            parts = [p.strip() for p in line.split(",")]
+            if len(parts) < 7:
+                continue
+            try:
+                sm.append(float(parts[0]))
+                mx.append(float(parts[1]))
+            except ValueError:
+                continue
+            for name, val in zip(names, parts[3:7]):
+                if val.lower().startswith("active"):
+                    reasons.add(name)
+        return {"sm_mhz": statistics.median(sm) if sm else None, "sm_max_mhz": max(mx) if mx else None,
+                "samples": len(sm), "reasons": sorted(reasons)}
+
+
+def device_view(ptr: int, nbytes: int, dtype):
+    """A torch tensor over library-owned device memory (no copy)."""
+    import torch
+
+    class _Mem:
+        pass
+
+    m = _Mem()
+    m.__cuda_array_interface__ = {"shape": (nbytes,), "typestr": "|u1", "data": (ptr, False), "version": 3}
+    return torch.as_tensor(m, device="cuda").view(dtype)
+
+
+def tiled_normal(n: int, std: float, seed: int, absolute: bool = False) -> np.ndarray:
+    """n seeded N(0, std) values; a 4M-value block repeated, which keeps host generation short."""
+    block = np.random.default_rng(seed).standard_normal(min(n, 1 << 22)).astype(np.float32) * np.float32(std)
+    if absolute:
+        block = np.abs(block)
+    return np.resize(block, n)
+
+
+# ------------------------------------------------------------------ the CPU arm
+def cpu_arm(steps: int, warmup: int, threads: int | None = None):
+    """The reference's CPU optimizer path, restated (the reference is Rust over un-vendored crates and cannot be
+    built here), on a bounded sample of the workload: the first 4 of 16 decoder layers."""
+    from oracle import dpstep as orc
+    from oxidizr_b200 import DecayPlan, WeightDecaySpec, inventory
+
+    tensors = inventory.llama_3_2_1b()
+    plan = DecayPlan(WeightDecaySpec("skip_1d"), tensors)
+    pick = list(range(1, 1 + 9 * 4))  # 4 layers x (2 norms + 4 attention + 3 MLP tensors); the embedding is skipped
+    numel = [tensors[i].elements for i in pick]
+    P = sum(numel)
+    if threads:
+        orc.lib().orc_set_num_threads(threads)
+    cores = orc.lib().orc_num_threads()
+    master = [tiled_normal(n, 0.02, SEED + i) for i, n in enumerate(numel)]
+    state = orc.StepState(master, [tiled_normal(n, 1e-4, SEED + 100 + i) for i, n in enumerate(numel)],
+                          [tiled_normal(n, 1e-6, SEED + 200 + i, True) for i, n in enumerate(numel)],
+                          [orc.to_bf16(p) for p in master], orc.BF16, lr_scale=[1.0] * len(numel),
+                          group_wd=[0.0 if plan.no_decay[i] else float("nan") for i in pick], timestep=1)
+    grads = [orc.to_bf16(tiled_normal(n, 1e-3, SEED + 300 + i)) for i, n in enumerate(numel)]
+    cfg = orc.StepConfig(**HYPER)
+    for _ in range(warmup):
+        orc.step(state, [grads], orc.BF16, cfg)
+    t0 = time.perf_counter()
+    for _ in range(steps):
+        orc.step(state, [grads], orc.BF16, cfg)
+    dt = (time.perf_counter() - t0) / max(steps, 1)
+    sample = f"{len(pick)} tensors = 4 of 16 decoder layers, {P} of 1235814400 params, {steps} steps"
+    return P / dt, dt * 1e3, cores, sample
+
+
+def run_reference(args):
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    value, ms, cores, sample = cpu_arm(args.steps, args.warmup)
+    line = {
+        "impl": "reference", "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": args.gpus, "steps": args.steps,
+        "warmup": args.warmup, "ms_per_step": ms, "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
+        "dtype": "f32", "data": "synthetic",
+        "config": {"workload": WORKLOAD, "params": 1235814400, "grad_dtype": "bf16", "param_dtype": "bf16",
+                   "world": args.gpus, "note": "CPU restatement of the reference's unfused per-tensor path; "
+                                               "ms_per_step is for the sample, value is sample params / time"},
+        "cpu_baseline": {"value": value, "unit": UNIT, "cores": cores, "kind": "port", "sample": sample},
+        "e2e": {"value": value, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "gpu_launches": 0,
+    }
+    print(json.dumps(line), flush=True)
+
+
+# ------------------------------------------------------------------ the GPU arm
+def run_gpu(args):
+    import torch
+    import oxidizr_b200 as ox
+    from oxidizr_b200 import inventory
+
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    if world != args.gpus:
+        raise SystemExit(f"--gpus {args.gpus} but WORLD_SIZE is {world}: launch with torch.distributed.run --nproc-per-node {args.gpus}")
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device: the optimizer step has no CPU fallback (use --impl reference for the CPU arm)")
+    torch.cuda.set_device(local_rank)
+    dist = None
+    comm = None
+    if world > 1:
+        import torch.distributed as dist
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
+        uid = [ox.Communicator.unique_id() if rank == 0 else None]
+        dist.broadcast_object_list(uid, src=0)
+        comm = ox.Communicator.init_rank(local_rank, rank, world, uid[0])
+
+    tensors = inventory.llama_3_2_1b()
+    plan = ox.DecayPlan(ox.WeightDecaySpec("skip_1d"), tensors)
+    numel = [t.elements for t in tensors]
+    P = sum(numel)
+    mode = {"p2p": ox.SYNC_P2P, "nccl": ox.SYNC_NCCL}[args.sync] if world > 1 else ox.SYNC_SINGLE
+    opt = ox.DpOptimizer(numel, plan.no_decay, ox.BF16, ox.BF16, world=world, rank=rank, sync_mode=mode,
+                         device=local_rank, comm=comm)
+    ptr, info = opt.pointers(), opt.info
+    stream = torch.cuda.Stream()
+    opt.set_stream(stream.cuda_stream)
+    opt.set_profile(True)
+
+    # seeded synthetic state, generated on the device straight into the library's buffers
+    gen = torch.Generator(device="cuda")
+    grads = device_view(ptr["grads"], info.padded_total * 2, torch.bfloat16)
+    work = device_view(ptr["work"], info.padded_total * 2, torch.bfloat16)
+    master = device_view(ptr["master"], info.local_elems * 4, torch.float32)
+    m = device_view(ptr["exp_avg"], info.local_elems * 4, torch.float32)
+    v = device_view(ptr["exp_avg_sq"], info.local_elems * 4, torch.float32)
+    gen.manual_seed(SEED)
+    chunk = 1 << 26
+    for lo in range(0, info.local_elems, chunk):
+        hi = min(info.local_elems, lo + chunk)
+        master[lo:hi].normal_(0.0, 0.02, generator=gen)
+        m[lo:hi].normal_(0.0, 1e-4, generator=gen)
+        v[lo:hi].normal_(0.0, 1e-6, generator=gen).abs_()
+    gen.manual_seed(SEED + 1 + rank)
+    for off, n in zip(opt.offsets, numel):
+        grads[off:off + n] = torch.empty(n, device="cuda", dtype=torch.float32).normal_(0.0, 1e-3, generator=gen).to(torch.bfloat16)
+    if world == 1:
+        work.copy_(master.to(torch.bfloat16))
+    opt.timestep = 1
+    torch.cuda.synchronize()
+
+    cfg = ox.StepConfig(**HYPER)
+
+    def barrier():
+        torch.cuda.synchronize()
+        if comm is not None:
+            comm.barrier()
+
+    def timed(n_steps: int, before_step=None):
+        """n_steps steps bracketed by barrier + synchronize; device time by CUDA events; returns seconds."""
+        barrier()
+        t0 = torch.cuda.Event(enable_timing=True)
+        t1 = torch.cuda.Event(enable_timing=True)
+        profs = []
+        with torch.cuda.stream(stream):
+            t0.record(stream)
+            for _ in range(n_steps):
+                if before_step is not None:
+                    before_step()
+                res = opt.step(cfg)
+                profs.append(opt.profile())
+            t1.record(stream)
+        barrier()
+        sec = t0.elapsed_time(t1) / 1e3
+        if dist is not None:
+            t = torch.tensor([sec], device="cuda", dtype=torch.float64)
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+            sec = float(t.item())
+        return sec, profs, res
+
+    for _ in range(max(args.warmup, 3)):
+        opt.step(cfg)
+    sampler = ClockSampler(local_rank)
+    sampler.start()
+    sec, profs, res = timed(args.steps)
+    clocks = sampler.stop()
+    ms_per_step = sec * 1e3 / args.steps
+    value = P * args.steps / sec
+
+    # end to end: every step copies that step's gradients from pinned host memory, then reads the result back
+    host = torch.empty(P, dtype=torch.bfloat16).pin_memory()
+    pos = 0
+    host_off = []
+    for off, n in zip(opt.offsets, numel):
+        host[pos:pos + n].copy_(grads[off:off + n])
+        host_off.append(pos)
+        pos += n
+    torch.cuda.synchronize()
+    base = host.data_ptr()
+
+    def upload():
+        for i, n in enumerate(numel):
+            opt.upload_grads(i, base + host_off[i] * 2)
+
+    e2e_steps = max(2, min(args.steps, 5))
+    timed(1, upload)
+    e2e_sec, _, _ = timed(e2e_steps, upload)
+    e2e_value = P * e2e_steps / e2e_sec
+
+    peak, peak_kind = measured_peaks()
+    upd = statistics.mean(p.update_ms for p in profs)
+    nrm = statistics.mean(p.norm_ms for p in profs)
+    local_params = P / world
+    achieved = BYTES_UPDATE * local_params / (upd * 1e-3) / 1e9
+    line = {
+        "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps, "warmup": max(args.warmup, 3),
+        "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
+        "dtype": "f32", "data": "synthetic",
+        "config": {"workload": WORKLOAD, "params": P, "tensors": len(numel), "grad_dtype": "bf16", "param_dtype": "bf16",
+                   "world": world, "sync": args.sync if world > 1 else "single",
+                   "l2": "inputs larger than L2: 30 B/param x %d params per rank per step" % int(local_params),
+                   "hyper": HYPER},
+        "roofline": {"bound": "hbm", "kernel": "k_adamw", "achieved": achieved, "peak": peak, "unit": "GB/s",
+                     "frac": achieved / peak, "peak_kind": peak_kind, "traffic": None,
+                     "algorithmic_bytes_per_launch": BYTES_UPDATE * local_params, "kernel_ms": upd,
+                     "norm_kernel": {"kernel": "k_pull_sumsq" if mode == ox.SYNC_P2P else "k_sumsq", "kernel_ms": nrm}},
+        "phases_ms": {k: statistics.mean(getattr(p, k) for p in profs) for k in
+                      ("collect_ms", "norm_ms", "decide_ms", "update_ms", "publish_ms", "total_ms")},
+        "step_roofline": step_roofline(P, world, ms_per_step, peak),
+        "e2e": {"value": e2e_value, "unit": UNIT, "h2d_bytes_per_step": P * 2 * world, "d2h_bytes_per_step": 32 * world,
+                "ms_per_step": e2e_sec * 1e3 / e2e_steps, "steps": e2e_steps},
+        "gpu_launches": 4 * args.steps * world,
+        "clocks": clocks,
+        "result": {"grad_norm": res.grad_norm, "applied": res.applied, "timestep": res.timestep},
+    }
+    if rank == 0:
+        if not args.no_cpu_baseline and world == 1:
+            v, ms, cores, sample = cpu_arm(3, 1)
+            line["cpu_baseline"] = {"value": v, "unit": UNIT, "cores": cores, "kind": "port", "sample": sample}
+        else:
+            line["cpu_baseline"] = None
+        print(json.dumps(line), flush=True)
+    opt.destroy()
+    if comm is not None:
+        comm.barrier()
+        comm.destroy()
+    if dist is not None:
+        dist.destroy_process_group()
+
+
+def step_roofline(P: int, world: int, ms: float, hbm_gbs: float) -> dict:
+    """Whole-step roofline: the slower of the HBM term (30 B/param on each rank's 1/world) and, with more ranks,
+    the NVLink term (bf16 reduce-scatter in + bf16 all-gather out, (world-1)/world * 2 B/param each)."""
+    hbm_ms_nominal = (BYTES_NORM + BYTES_UPDATE) * P / world / 8.0e12 * 1e3
+    hbm_ms_measured = (BYTES_NORM + BYTES_UPDATE) * P / world / (hbm_gbs * 1e9) * 1e3
+    wire = 2 * (world - 1) / world * 2 * P
+    wire_ms_nominal = wire / 900e9 * 1e3
+    wire_ms_measured = wire / 770e9 * 1e3
+    nominal = max(hbm_ms_nominal, wire_ms_nominal)
+    measured = max(hbm_ms_measured, wire_ms_measured)
+    return {"roofline_ms_nominal": nominal, "frac_of_nominal": nominal / ms, "roofline_ms_measured_peaks": measured,
+            "frac_of_measured_peaks": measured / ms, "bound": "nvlink" if wire_ms_nominal > hbm_ms_nominal else "hbm"}
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--impl", choices=["ours", "reference"], default="ours")
+    ap.add_argument("--sync", choices=["p2p", "nccl"], default="p2p", help="how ranks meet at --gpus > 1")
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    args = ap.parse_args()
+    if args.impl == "reference":
+        run_reference(args)
+    else:
+        run_gpu(args)
+
+
+if __name__ == "__main__":
+    main()

@@ -1,0 +1,275 @@
+/*
+ * oxz_dpstep — C ABI of a B200-native data-parallel optimizer step for oxidizr.
+ *
+ * The library replaces, behind oxidizr's LitTrainer::training_step, the work between
+ * "AFTER ACCUMULATION LOOP" (src/trainer.rs:515) and the end of step_once (src/trainer.rs:695):
+ * the gradient sum over ranks, the loss-scale unscale, the inf/NaN decision, the value and
+ * global-norm clips, the fused AdamW update with the weight-decay groups, and the write-back of
+ * f32 master and narrow working weights.
+ *
+ * Conventions
+ *   - Every function returns an oxz_status (0 = OK) and never throws or aborts the process.
+ *     oxz_last_error() returns the calling thread's last error text.
+ *   - One oxz_plan (and one oxz_comm) per rank. A plan is used by one thread at a time; different
+ *     ranks' plans may be driven from different threads of one process (the reference runs one OS
+ *     thread per rank, src/dp/launch.rs:207-240) or from one process per rank.
+ *   - Device work is enqueued on the plan's stream. Calls named *_async return before it ends.
+ *   - There is no CPU fallback: a call that needs the GPU fails with OXZ_ERR_CUDA without one.
+ */
+#ifndef OXZ_DPSTEP_H
+#define OXZ_DPSTEP_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define OXZ_ABI_VERSION 1u
+
+typedef enum oxz_status {
+    OXZ_OK = 0,
+    OXZ_ERR_INVALID = 1,     /* bad argument; mirrors boostr Error::InvalidArgument / TrainingError */
+    OXZ_ERR_CUDA = 2,        /* a CUDA runtime call failed */
+    OXZ_ERR_NCCL = 3,        /* a collective failed; mirrors Error::DistributedError. Peers may be waiting:
+                                the caller must abort the group (src/dp/reduce.rs:27-29) */
+    OXZ_ERR_STATE = 4,       /* call order: state not allocated, a step still in flight, ... */
+    OXZ_ERR_ABORTED = 5,     /* the communicator was aborted (src/dp/launch.rs:97-103) */
+    OXZ_ERR_UNSUPPORTED = 6, /* NCCL library or peer access unavailable */
+    OXZ_ERR_DATA = 7         /* mirrors Error::DataError of the row arithmetic */
+} oxz_status;
+
+typedef enum oxz_dtype { OXZ_F32 = 0, OXZ_BF16 = 1, OXZ_F16 = 2 } oxz_dtype;
+
+/* How the gradients of different ranks meet. */
+typedef enum oxz_sync_mode {
+    OXZ_SYNC_SINGLE = 0, /* world 1: no collective (NoOpCommunicator, src/trainer.rs:234) */
+    OXZ_SYNC_P2P = 1,    /* fused kernels over NVLink peer memory: pull-reduce in f32 in rank order,
+                            push of the narrow weights; NCCL only for the 3-double norm all-reduce */
+    OXZ_SYNC_NCCL = 2    /* ncclReduceScatter / ncclAllGather in the gradient's own dtype */
+} oxz_sync_mode;
+
+typedef struct oxz_comm oxz_comm;
+typedef struct oxz_plan oxz_plan;
+
+uint32_t oxz_abi_version(void);
+const char* oxz_last_error(void);
+const char* oxz_status_name(int32_t status);
+
+/* ------------------------------------------------------------------ communicator
+ * Replaces boostr's NcclCommunicator as oxidizr creates and ends it:
+ * NcclCommunicator::from_streams (src/dp/launch.rs:82-95) and abort (src/dp/launch.rs:97-103). */
+
+/* 128-byte rendezvous token for oxz_comm_init_rank; make it on one rank and hand it to the others. */
+int32_t oxz_comm_unique_id(uint8_t id[128]);
+/* One communicator for this rank, on `device`. Collective over all ranks. One process per rank or one thread per rank. */
+int32_t oxz_comm_init_rank(int32_t device, int32_t rank, int32_t world, const uint8_t id[128], oxz_comm** out);
+/* All communicators of a single-process group at once, as from_streams does (src/dp/launch.rs:82-95). */
+int32_t oxz_comm_init_all(int32_t n, const int32_t* devices, oxz_comm** out);
+int32_t oxz_comm_world_size(const oxz_comm* comm, int32_t* world);
+int32_t oxz_comm_rank(const oxz_comm* comm, int32_t* rank);
+/* Ends every pending and future collective of this rank with an error; callable from any thread. */
+int32_t oxz_comm_abort(oxz_comm* comm);
+int32_t oxz_comm_destroy(oxz_comm* comm);
+/* Sum of two host counts over every rank: the step-weighting collective (src/dp/weighting.rs:63-101). Blocking. */
+int32_t oxz_allreduce_i64x2(oxz_comm* comm, int64_t inout[2]);
+/* Sum of up to 16 host doubles over every rank: the logged loss when it must be known before the update is
+ * enqueued (the `extras` of boostr all_reduce_flat_sum, src/dp/reduce.rs:57-59). Blocking. */
+int32_t oxz_allreduce_f64(oxz_comm* comm, double* inout, uint32_t n);
+/* Broadcast of device memory from `root`: initial replica sync and the stop flag (src/dp/broadcast.rs:54,77). */
+int32_t oxz_broadcast(oxz_comm* comm, void* device_ptr, uint64_t bytes, int32_t root);
+/* Barrier over every rank (src/dp/trainer_hooks.rs:104). Blocking. */
+int32_t oxz_barrier(oxz_comm* comm);
+
+/* ------------------------------------------------------------------ plan
+ * The flat layout of the trainable parameters and their AdamW groups. Replaces the `declared`
+ * (id, shape) list of reduce_step_gradients (src/dp/reduce.rs:45-56) and DecayPlan::param_groups
+ * (src/weight_decay/plan.rs:113-122). Tensors keep parameter_ids order (src/trainer.rs:208). */
+
+typedef struct oxz_plan_desc {
+    uint64_t n_tensors;
+    const uint64_t* numel;       /* [n_tensors] elements per tensor */
+    const uint8_t* no_decay;     /* [n_tensors] 1 = member of the zero-decay group; NULL = none */
+    const float* lr_scale;       /* [n_tensors] ParamGroup::lr_scale; NULL = 1.0 */
+    int32_t grad_dtype;          /* oxz_dtype of the gradients a rank produces */
+    int32_t param_dtype;         /* oxz_dtype of the working weights; OXZ_F32 keeps no separate master */
+    int32_t world, rank;
+    int32_t sync_mode;           /* oxz_sync_mode; OXZ_SYNC_SINGLE requires world 1 */
+    int32_t device;              /* CUDA device ordinal */
+    uint64_t bucket_bytes;       /* gradient bytes per bucket; 0 = 64 MiB */
+} oxz_plan_desc;
+
+typedef struct oxz_plan_info {
+    uint64_t n_tensors;
+    uint64_t numel_total;     /* trainable elements */
+    uint64_t padded_total;    /* elements of the flat space (tensor starts are tile-aligned) */
+    uint64_t tile_elems;      /* alignment of every tensor start, bucket and shard, in elements */
+    uint64_t n_buckets;
+    uint64_t bucket_elems;    /* elements per bucket, the last bucket may be shorter */
+    uint64_t local_elems;     /* elements of optimizer state this rank owns (1/world of every bucket) */
+    uint64_t n_groups;        /* distinct (lr_scale, decay) groups */
+} oxz_plan_info;
+
+int32_t oxz_plan_create(const oxz_plan_desc* desc, oxz_plan** out); /* host only: runs without a GPU */
+int32_t oxz_plan_destroy(oxz_plan* plan);
+int32_t oxz_plan_query(const oxz_plan* plan, oxz_plan_info* info);
+/* offsets[i]: first flat element of tensor i */
+int32_t oxz_plan_tensor_offsets(const oxz_plan* plan, uint64_t* offsets);
+/* For bucket b: its flat start, its length, and the start and length of the part rank `rank` owns. */
+int32_t oxz_plan_bucket(const oxz_plan* plan, uint64_t b, int32_t rank, uint64_t* start, uint64_t* len,
+                        uint64_t* shard_start, uint64_t* shard_len);
+/* Flat element -> element of `rank`'s local state arrays, or UINT64_MAX when another rank owns it. */
+int32_t oxz_plan_local_index(const oxz_plan* plan, int32_t rank, uint64_t flat_index, uint64_t* local_index);
+/* The CUDA stream (cudaStream_t) the plan enqueues on; NULL restores the plan's own stream. */
+int32_t oxz_plan_set_stream(oxz_plan* plan, void* stream);
+
+/* ------------------------------------------------------------------ state
+ * Replaces the state boostr's AdamW owns: exp_avg, exp_avg_sq, the f32 master and the applied-step
+ * count (src/checkpoint_set/optimizer_io.rs:1-5), plus the flat gradient and working-weight buffers. */
+
+/* Allocates the device buffers (zero-filled). `comm` may be NULL at world 1. With OXZ_SYNC_P2P this is
+ * collective: ranks exchange peer mappings of their gradient and weight buffers. */
+int32_t oxz_state_alloc(oxz_plan* plan, oxz_comm* comm);
+/* Device pointers of the flat buffers. grads: padded_total x grad_dtype. work: padded_total x param_dtype
+ * (for param_dtype F32 it is the master itself and only valid at world 1). master/exp_avg/exp_avg_sq:
+ * local_elems x f32. A backward pass may write its gradients straight into grads + offsets[i]. */
+int32_t oxz_state_pointers(const oxz_plan* plan, void** grads, void** work, void** master, void** exp_avg,
+                           void** exp_avg_sq);
+typedef enum oxz_state_kind { OXZ_STATE_MASTER = 0, OXZ_STATE_EXP_AVG = 1, OXZ_STATE_EXP_AVG_SQ = 2,
+                              OXZ_STATE_WORK = 3, OXZ_STATE_GRADS = 4 } oxz_state_kind;
+/* Copies one whole tensor from host memory (f32 for master/moments; the buffer's dtype for work and grads).
+ * A rank keeps the elements it owns and ignores the rest (work and grads are whole on every rank). Blocking. */
+int32_t oxz_state_import(oxz_plan* plan, int32_t kind, uint64_t tensor, const void* host);
+/* Copies the elements this rank owns of one tensor into host memory and leaves the others untouched. Blocking.
+ * Mirrors optimizer.state_dict / load_state_dict (src/checkpoint_set/optimizer_io.rs:41-63,116-136). */
+int32_t oxz_state_export(oxz_plan* plan, int32_t kind, uint64_t tensor, void* host);
+int32_t oxz_state_set_timestep(oxz_plan* plan, uint64_t applied_steps);
+int32_t oxz_state_timestep(const oxz_plan* plan, uint64_t* applied_steps); /* optimizer_timestep, src/trainer.rs:906-908 */
+
+/* ------------------------------------------------------------------ gradients in
+ * Replaces the flatten half of boostr all_reduce_flat_sum (called at src/dp/reduce.rs:58). */
+
+/* Packs per-tensor device gradients (grad_dtype, 16-byte aligned) into the flat buffer. grad_ptrs[i] NULL = this
+ * rank has no gradient for tensor i: its span is zero-filled. accumulate != 0 adds instead of storing, in f32,
+ * which is the micro-batch accumulation of src/trainer.rs:1087-1107. Asynchronous. */
+int32_t oxz_grads_flatten_async(oxz_plan* plan, const void* const* grad_ptrs, int32_t accumulate);
+/* Host gradients of one tensor (grad_dtype; pinned memory copies asynchronously) into the flat buffer. */
+int32_t oxz_grads_upload_async(oxz_plan* plan, uint64_t tensor, const void* host);
+
+/* ------------------------------------------------------------------ the step */
+
+typedef struct oxz_hyper {
+    double lr;               /* this step's learning rate, LrPlan::lr_at (src/trainer.rs:254) */
+    double beta1, beta2, eps, weight_decay; /* AdamWConfig, src/trainer.rs:184-191 */
+    double max_grad_norm;    /* src/trainer.rs:581-587 */
+    double max_grad_value;   /* NaN = off (src/grad_clip.rs:47) */
+    double target_grad_norm; /* NaN = off (src/trainer.rs:635-645) */
+    double loss_scale;       /* LossScaler::scale; NaN or 0 = no scaler (src/trainer.rs:573-575) */
+    double clip_eps;         /* epsilon of the clip coefficient max/(norm+eps); 1e-6 conventional */
+    int32_t decay_after;     /* 0 = weight decay before the Adam term (default) */
+    int32_t eps_mode;        /* 0 = sqrt(v)/sqrt(1-beta2^t) + eps (default), 1 = sqrt(v) + eps */
+    int32_t spike_skip;      /* the spike guard vetoed this step (src/trainer.rs:612) */
+    int32_t reserved;
+} oxz_hyper;
+
+typedef struct oxz_step_result {
+    double grad_norm;     /* the norm clip_gradients measured (src/grad_clip.rs:28-35) */
+    double reported_norm; /* what training_step returns (src/trainer.rs:629-632, 657-661) */
+    double clip_coef;     /* product of the applied clip coefficients */
+    int32_t overflow;     /* !grad_norm.is_finite() (src/trainer.rs:619) */
+    int32_t applied;      /* optimizer.step ran */
+    uint64_t timestep;    /* applied steps after this one */
+} oxz_step_result;
+
+/* One optimizer step on the gradients now in the flat buffer: src/trainer.rs:520-661 in one call.
+ * present: [n_tensors] 0 = no rank produced a gradient for this tensor this step (it is left untouched,
+ *          src/dp/reduce.rs:20); NULL = all present. Must be equal on every rank.
+ * extras:  n_extras host doubles summed over ranks in place (the logged loss, src/dp/reduce.rs:57-59).
+ * The decision to skip is taken on the device; nothing is read back between the norm and the update. */
+int32_t oxz_step_async(oxz_plan* plan, oxz_comm* comm, const oxz_hyper* hyper, const uint8_t* present,
+                       double* extras, uint32_t n_extras);
+/* Waits for the step in flight, fills `result` and the extras, and advances the applied-step count. */
+int32_t oxz_step_wait(oxz_plan* plan, oxz_step_result* result);
+/* oxz_step_async followed by oxz_step_wait. */
+int32_t oxz_step(oxz_plan* plan, oxz_comm* comm, const oxz_hyper* hyper, const uint8_t* present, double* extras,
+                 uint32_t n_extras, oxz_step_result* result);
+
+/* Per-phase device times of the last finished step, measured with CUDA events on the plan's stream: the
+ * counterpart of the reference's PROFILE_TRAIN wall-clock lines (src/trainer.rs:579-593, 648-655). */
+typedef struct oxz_step_profile {
+    float collect_ms; /* waiting for / reducing the ranks' gradients before the norm kernel (0 at world 1) */
+    float norm_ms;    /* the unscale + inf check + sum-of-squares kernel (with the peer pull in P2P mode) */
+    float decide_ms;  /* partials -> norm all-reduce -> decision and clip coefficients */
+    float update_ms;  /* the fused AdamW kernel (with the peer push in P2P mode) */
+    float publish_ms; /* all-gather or closing barrier (0 at world 1) */
+    float total_ms;
+} oxz_step_profile;
+/* on != 0: record the events every step (a few microseconds); off by default. */
+int32_t oxz_plan_set_profile(oxz_plan* plan, int32_t on);
+int32_t oxz_step_profile_read(oxz_plan* plan, oxz_step_profile* out);
+
+/* Global L2 norm of n device gradients after the unscale (and after the clamp when max_grad_value is not NaN),
+ * as a pure measurement: compute_grad_norm(.., f64::MAX) of src/grad_clip.rs:49. A non-finite element gives a
+ * non-finite norm (src/grad_clip.rs:130-143). Blocking; allocates its partial-sum scratch on first use per device. */
+int32_t oxz_grad_norm(const void* device_grads, int32_t dtype, uint64_t n, double loss_scale, double max_grad_value,
+                      void* stream, double* norm);
+
+/* ------------------------------------------------------------------ host decisions (pure, no GPU) */
+
+typedef struct oxz_scaler_config { double initial, growth_factor, backoff_factor; uint64_t growth_interval; } oxz_scaler_config;
+typedef struct oxz_scaler_state { double scale; uint64_t consecutive_ok; } oxz_scaler_state;
+/* LossScaleConfig::check (src/loss_scale/config.rs:66-100). */
+int32_t oxz_scaler_check(const oxz_scaler_config* cfg);
+/* LossScaler::new / restore (src/loss_scale/scaler.rs:19-37). */
+int32_t oxz_scaler_init(const oxz_scaler_config* cfg, oxz_scaler_state* state);
+int32_t oxz_scaler_restore(const oxz_scaler_state* saved, oxz_scaler_state* state);
+/* The scaler update at the end of a step (src/trainer.rs:666-681): untouched on a finite-gradient spike skip. */
+int32_t oxz_scaler_record_step(const oxz_scaler_config* cfg, oxz_scaler_state* state, int32_t overflow,
+                               int32_t spike_skip);
+
+typedef enum oxz_decay_rule { OXZ_DECAY_ALL = 0, OXZ_SKIP_1D = 1, OXZ_SKIP_ALL = 2 } oxz_decay_rule;
+/* WeightDecaySpec::check and ::excludes (src/weight_decay/rule.rs:78-118). *excluded = 1: no weight decay. */
+int32_t oxz_decay_check(int32_t rule, const char* const* patterns, uint32_t n_patterns);
+int32_t oxz_decay_excludes(int32_t rule, const char* const* patterns, uint32_t n_patterns, const char* name,
+                           uint32_t rank, int32_t* excluded);
+
+typedef struct oxz_spike_config { uint64_t window; double z_threshold; uint64_t min_steps; int32_t action_warn; int32_t reserved; } oxz_spike_config;
+typedef struct oxz_spike_state { double mean, variance; uint64_t observed, detected, skipped; } oxz_spike_state;
+/* TrainMetrics::judge over SpikeGuard::observe (src/metrics/state.rs:79-86, src/metrics/spike.rs:124-168).
+ * index is the 0-based step; *skip = 1 when the step must skip the optimizer; *flagged = 1 for any spike. */
+int32_t oxz_spike_judge(const oxz_spike_config* cfg, oxz_spike_state* state, uint64_t index, double loss,
+                        int32_t* skip, int32_t* flagged);
+
+typedef enum oxz_lr_schedule { OXZ_LR_CONSTANT = 0, OXZ_LR_COSINE = 1, OXZ_LR_LINEAR = 2, OXZ_LR_WSD = 3 } oxz_lr_schedule;
+typedef enum oxz_decay_shape { OXZ_SHAPE_LINEAR = 0, OXZ_SHAPE_COSINE = 1, OXZ_SHAPE_SQRT = 2 } oxz_decay_shape;
+typedef struct oxz_lr_plan {
+    double base_lr, min_lr_ratio;
+    uint64_t warmup_steps, total_steps;
+    uint64_t decay_steps;  /* wsd only: resolved span (src/schedule.rs:124-132) */
+    int32_t schedule, decay_shape;
+} oxz_lr_plan;
+/* LrPlan::lr_at (src/schedule.rs:177-183). */
+int32_t oxz_lr_at(const oxz_lr_plan* plan, uint64_t step, double* lr);
+
+typedef struct oxz_row_layout { uint64_t num_rows, rank_batch_size, world_size; } oxz_row_layout;
+typedef struct oxz_data_position { uint64_t epoch, row; } oxz_data_position;
+/* RowLayout::for_world checks (src/data/rows.rs:66-123). */
+int32_t oxz_rows_check(const oxz_row_layout* layout);
+/* RowLayout::advance (src/data/rows.rs:167-191). */
+int32_t oxz_rows_advance(const oxz_row_layout* layout, oxz_data_position pos, uint64_t batches, oxz_data_position* out);
+/* One rank's draw of the next global batch in stream order (src/data/positioning.rs:44-68, src/data/batch.rs:51-71):
+ * rows[rank_batch_size] are the global row indices, and when `tokens` (u32 LE stream) is given, inputs/targets
+ * [rank_batch_size * seq_len] receive the i64 token ids. *next is the position after the global batch. */
+int32_t oxz_rows_next_window(const oxz_row_layout* layout, oxz_data_position pos, uint64_t rank, uint64_t seq_len,
+                             uint64_t first_row, const uint32_t* tokens, uint64_t n_tokens, uint64_t* rows,
+                             int64_t* inputs, int64_t* targets, oxz_data_position* next);
+/* StepWeighting::over_ranks applied to the summed counts (src/dp/weighting.rs:46-61): counts = {scored, masked ranks}
+ * after oxz_allreduce_i64x2. *global_scored = -1 for an unmasked step. Mixed masks are OXZ_ERR_INVALID on every rank. */
+int32_t oxz_step_weighting(uint64_t local_micro_batches, int32_t world, const int64_t counts[2],
+                           uint64_t* micro_batches, int64_t* global_scored);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* OXZ_DPSTEP_H */

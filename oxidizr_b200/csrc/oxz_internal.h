@@ -1,0 +1,176 @@
+// Internal declarations shared by the translation units of liboxz_dpstep.so.
+#pragma once
+
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include <atomic>
+#include <string>
+#include <vector>
+
+#include "../../include/oxz_dpstep.h"
+
+namespace oxz {
+
+// ---- errors: thread-local text behind oxz_last_error() ----
+int32_t fail(int32_t status, const char* fmt, ...) __attribute__((format(printf, 2, 3)));
+void clear_error();
+
+#define OXZ_CUDA(expr)                                                                              \
+    do {                                                                                            \
+        cudaError_t e__ = (expr);                                                                   \
+        if (e__ != cudaSuccess)                                                                     \
+            return ::oxz::fail(OXZ_ERR_CUDA, "%s failed: %s (%s:%d)", #expr, cudaGetErrorString(e__), \
+                               __FILE__, __LINE__);                                                 \
+    } while (0)
+
+#define OXZ_TRY(expr)                  \
+    do {                               \
+        int32_t s__ = (expr);          \
+        if (s__ != OXZ_OK) return s__; \
+    } while (0)
+
+constexpr uint32_t TILE = 256;           // elements per tile: one 8-element vector per lane of a warp
+constexpr uint32_t MAX_GROUPS = 8;       // distinct (lr_scale, decay) groups a plan may hold
+constexpr uint32_t PAD_TILE = 0xFFFFFFFFu;  // tile_meta of a tile past the last tensor
+constexpr uint32_t MAX_PEERS = 16;
+constexpr uint32_t MAX_EXTRAS = 13;      // doubles that ride on the norm all-reduce
+
+inline size_t dtype_size(int32_t dt) { return dt == OXZ_F32 ? 4 : 2; }
+
+// Maps a tile of this rank's local state arrays to a tile of the flat parameter space.
+// Bucket b holds tiles [b*tpb, ...); rank r owns the r-th 1/world of every bucket.
+struct TileMap {
+    uint32_t tiles_per_shard;       // tiles a rank owns of a full bucket
+    uint32_t tiles_per_bucket;      // tiles of a full bucket = world * tiles_per_shard
+    uint32_t n_buckets;
+    uint32_t last_shard_tiles;      // tiles a rank owns of the last bucket
+    uint32_t rank;
+    uint32_t n_local_tiles;
+};
+
+// Per-step scalars of the update, rounded to f32 on the host from f64.
+struct AdamParams {
+    float beta1, one_minus_beta1, beta2, one_minus_beta2;
+    float eps, bias2_sqrt;
+    float inv_scale;   // 1/loss_scale, 1.0f without a scaler
+    float clamp_hi;    // max_grad_value
+    int32_t clamp_on;
+    int32_t decay_after, eps_mode;
+    float step_size[MAX_GROUPS];
+    float decay_mul[MAX_GROUPS];
+};
+
+// Device-resident outcome of the norm pass; the update kernel reads it, no host round trip.
+struct DevScalars {
+    double norm;        // measured global norm (inf or NaN on overflow)
+    double sumsq;
+    float c1, c2;       // clip coefficients applied in this order
+    int32_t overflow;
+    int32_t skip;       // overflow or spike veto: the update kernel returns at once
+};
+
+struct PeerTable {
+    const void* grads[MAX_PEERS];
+    void* work[MAX_PEERS];
+};
+
+struct FinalizeParams {
+    double max_grad_norm, target_grad_norm, clip_eps;
+    int32_t has_target, spike_skip;
+};
+
+// ---- kernel launchers (oxz_kernels.cu) ----
+struct LaunchGeom {
+    int sm_count;
+    int norm_blocks;   // multiple of the cluster size
+    int adam_blocks;
+};
+int32_t query_geom(int device, LaunchGeom* g);
+uint32_t norm_partial_slots(const LaunchGeom& g);
+
+// Sum of squares of unscaled (and optionally clamped) gradients held in one local array of dtype `dt`.
+int32_t launch_sumsq(cudaStream_t s, const LaunchGeom& g, const void* grads, int32_t dt, const TileMap& map,
+                     const uint32_t* tile_meta, const uint8_t* present, float inv_scale, float clamp_hi,
+                     int32_t clamp_on, double* partials);
+// Same over a plain array of n elements (no plan): the standalone norm entry point.
+int32_t launch_sumsq_plain(cudaStream_t s, int blocks, const void* grads, int32_t dt, uint64_t n, float inv_scale,
+                           float clamp_hi, int32_t clamp_on, double* partials);
+// Pull-reduce: sums this rank's tiles of every peer's gradient buffer in f32 in rank order, stores the sum
+// in `reduced` (local, f32) and accumulates the squares as launch_sumsq does.
+int32_t launch_pull_sumsq(cudaStream_t s, const LaunchGeom& g, const PeerTable& peers, int32_t world, int32_t dt,
+                          const TileMap& map, const uint32_t* tile_meta, const uint8_t* present, float inv_scale,
+                          float clamp_hi, int32_t clamp_on, float* reduced, double* partials);
+// partials[slots][3] -> acc[3] = {sum, inf count, nan count}
+int32_t launch_reduce_partials(cudaStream_t s, const double* partials, uint32_t slots, double* acc);
+// acc[3] -> scalars (norm, clip coefficients, decisions)
+int32_t launch_finalize(cudaStream_t s, const double* acc, const FinalizeParams& fp, DevScalars* scalars);
+// The fused update. gsrc is indexed in local space (dtype gdt); master/m/v local f32; work is written in flat space
+// to every pointer of `peers.work[0..n_work)` (n_work 0: no working copy).
+int32_t launch_adamw(cudaStream_t s, const LaunchGeom& g, const void* gsrc, int32_t gdt, float* master, float* m,
+                     float* v, const PeerTable& peers, int32_t n_work, int32_t pdt, const TileMap& map,
+                     const uint32_t* tile_meta, const uint8_t* present, const DevScalars* scalars,
+                     const AdamParams& ap);
+// Packs per-tensor gradients into the flat buffer.
+int32_t launch_flatten(cudaStream_t s, const LaunchGeom& g, void* flat, int32_t dt, uint32_t n_tiles,
+                       const uint32_t* tile_meta, const uint64_t* d_offsets, const uint64_t* d_numel,
+                       const void* const* d_src, int32_t accumulate);
+
+}  // namespace oxz
+
+// ---- opaque handles ----
+struct oxz_comm {
+    void* nccl = nullptr;  // ncclComm_t
+    int32_t rank = 0, world = 1, device = 0;
+    cudaStream_t stream = nullptr;  // for the small blocking collectives
+    void* d_small = nullptr;        // 512 bytes of device scratch for them
+    std::atomic<int> aborted{0};
+};
+
+struct oxz_plan {
+    // layout (host)
+    uint64_t T = 0;
+    std::vector<uint64_t> numel, offset;
+    std::vector<uint8_t> group_of;
+    std::vector<float> group_lr_scale;
+    std::vector<uint8_t> group_no_decay;
+    int32_t gdt = 0, pdt = 0, world = 1, rank = 0, mode = 0, device = 0;
+    uint64_t numel_total = 0, total_tiles = 0;
+    uint64_t bucket_tiles = 0, n_buckets = 0, last_bucket_tiles = 0, local_tiles = 0;
+    std::vector<uint32_t> tile_meta;  // per flat tile: tensor | group << 24
+
+    // device state
+    bool allocated = false;
+    cudaStream_t own_stream = nullptr, stream = nullptr;
+    oxz::LaunchGeom geom{};
+    void* grads = nullptr;
+    void* work = nullptr;
+    float *master = nullptr, *exp_avg = nullptr, *exp_avg_sq = nullptr;
+    void* reduced = nullptr;  // W>1: the summed gradients of this rank's tiles (f32 for P2P, grad dtype for NCCL)
+    uint32_t* d_tile_meta = nullptr;
+    uint8_t* d_present = nullptr;
+    uint64_t *d_offsets = nullptr, *d_numel = nullptr;
+    const void** d_src = nullptr;
+    double* d_partials = nullptr;
+    double* d_acc = nullptr;  // 3 + MAX_EXTRAS doubles
+    oxz::DevScalars* d_scalars = nullptr;
+    // pinned host mirrors
+    oxz::DevScalars* h_scalars = nullptr;
+    double* h_acc = nullptr;
+    uint8_t* h_present = nullptr;
+    const void** h_src = nullptr;
+    cudaEvent_t done = nullptr;
+    bool profile = false;
+    cudaEvent_t ev[6] = {nullptr, nullptr, nullptr, nullptr, nullptr, nullptr};
+    oxz::PeerTable peers{};
+    std::vector<void*> ipc_opened;
+    oxz_comm* comm = nullptr;
+
+    // step bookkeeping
+    uint64_t timestep = 0;
+    bool inflight = false;
+    bool present_all = true;
+    oxz_hyper inflight_hyper{};
+    double* inflight_extras = nullptr;
+    uint32_t inflight_n_extras = 0;
+};

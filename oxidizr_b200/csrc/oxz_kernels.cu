@@ -1,0 +1,560 @@
+// Hand-written sm_100a kernels of the data-parallel optimizer step.
+//
+// All of them are HBM-bound streaming kernels: no tensor cores, 128-bit coalesced accesses, grids sized in
+// multiples of the SM count, one 8-element vector per lane and one 256-element tile per warp. A tile never
+// straddles two tensors (tensor starts are tile-aligned), so the group scalars are warp-uniform.
+//
+//   k_sumsq        unscale + non-finite detection + sum of squares; warp shuffle, then a thread-block-cluster
+//                  reduction through distributed shared memory, one partial per cluster.
+//   k_pull_sumsq   the same fused with the gradient sum over ranks: every rank pulls its tiles from all peers'
+//                  buffers over NVLink with plain 128-bit loads and adds them in f32 in rank order.
+//   k_reduce_partials / k_finalize   partials -> norm, overflow, clip coefficients, all on the device.
+//   k_adamw        clip-scale + bias-corrected AdamW + decoupled decay by group + f32 master and narrow working
+//                  weights; with peers it stores the working weights into every rank's buffer (the all-gather).
+//   k_flatten      per-tensor gradients -> flat buffer.
+//
+// The update uses explicit round-to-nearest intrinsics so that no multiply-add is contracted: every f32
+// operation rounds once, and the result is bit-identical to a plain C restatement compiled without contraction.
+#include <cooperative_groups.h>
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
+
+#include "oxz_internal.h"
+
+namespace cg = cooperative_groups;
+
+namespace oxz {
+
+constexpr int THREADS = 256;
+constexpr int WARPS = THREADS / 32;
+constexpr int CLUSTER = 4;
+constexpr uint32_t FLAG_INF = 1u, FLAG_NAN = 2u;
+
+// ---------------------------------------------------------------- vector access
+
+__device__ __forceinline__ uint4 ld_stream(const uint4* p) { return __ldcs(p); }
+__device__ __forceinline__ float4 ld_stream(const float4* p) { return __ldcs(p); }
+__device__ __forceinline__ void st_stream(float4* p, float4 v) { __stcs(p, v); }
+__device__ __forceinline__ void st_stream(uint4* p, uint4 v) { __stcs(p, v); }
+
+// 8 consecutive elements of dtype DT starting at element index `e` (a multiple of 8) as f32.
+template <int DT>
+__device__ __forceinline__ void load8(const void* base, uint64_t e, float (&x)[8]) {
+    if constexpr (DT == OXZ_F32) {
+        const float4* p = reinterpret_cast<const float4*>(static_cast<const float*>(base) + e);
+        float4 a = ld_stream(p), b = ld_stream(p + 1);
+        x[0] = a.x; x[1] = a.y; x[2] = a.z; x[3] = a.w;
+        x[4] = b.x; x[5] = b.y; x[6] = b.z; x[7] = b.w;
+    } else {
+        uint4 r = ld_stream(reinterpret_cast<const uint4*>(static_cast<const uint16_t*>(base) + e));
+        const uint32_t w[4] = {r.x, r.y, r.z, r.w};
+#pragma unroll
+        for (int i = 0; i < 4; i++) {
+            if constexpr (DT == OXZ_BF16) {
+                x[2 * i] = __uint_as_float(w[i] << 16);
+                x[2 * i + 1] = __uint_as_float(w[i] & 0xffff0000u);
+            } else {
+                __half2 h = *reinterpret_cast<const __half2*>(&w[i]);
+                float2 f = __half22float2(h);
+                x[2 * i] = f.x;
+                x[2 * i + 1] = f.y;
+            }
+        }
+    }
+}
+
+template <int DT>
+__device__ __forceinline__ void store8(void* base, uint64_t e, const float (&x)[8]) {
+    if constexpr (DT == OXZ_F32) {
+        float4* p = reinterpret_cast<float4*>(static_cast<float*>(base) + e);
+        st_stream(p, make_float4(x[0], x[1], x[2], x[3]));
+        st_stream(p + 1, make_float4(x[4], x[5], x[6], x[7]));
+    } else {
+        uint32_t w[4];
+#pragma unroll
+        for (int i = 0; i < 4; i++) {
+            if constexpr (DT == OXZ_BF16) {
+                __nv_bfloat162 h = __floats2bfloat162_rn(x[2 * i], x[2 * i + 1]);
+                w[i] = *reinterpret_cast<uint32_t*>(&h);
+            } else {
+                __half2 h = __floats2half2_rn(x[2 * i], x[2 * i + 1]);
+                w[i] = *reinterpret_cast<uint32_t*>(&h);
+            }
+        }
+        st_stream(reinterpret_cast<uint4*>(static_cast<uint16_t*>(base) + e), make_uint4(w[0], w[1], w[2], w[3]));
+    }
+}
+
+__device__ __forceinline__ uint32_t flat_tile(const TileMap& m, uint32_t lt) {
+    uint32_t b = lt / m.tiles_per_shard;
+    uint32_t within = lt - b * m.tiles_per_shard;
+    uint32_t shard = (b == m.n_buckets - 1) ? m.last_shard_tiles : m.tiles_per_shard;
+    return b * m.tiles_per_bucket + m.rank * shard + within;
+}
+
+__device__ __forceinline__ bool finite_f32(float x) { return (__float_as_uint(x) & 0x7f800000u) != 0x7f800000u; }
+
+// ---------------------------------------------------------------- sum of squares
+
+struct NormAcc {
+    double sum = 0.0;
+    uint32_t flags = 0;
+};
+
+// Adds the squares of 8 gradients (already widened to f32) to `a`.
+// The overflow decision must not depend on the summation order: a step overflows exactly when some element's
+// f32 square is not finite. The fast path sums the 8 squares in f32; only when that sum is not finite does the
+// slow path look at each square, so a partial sum that overflows by itself is never mistaken for an overflow.
+__device__ __forceinline__ void acc8(const float (&g)[8], float inv_scale, float clamp_hi, bool clamp_on, NormAcc& a) {
+    float x[8];
+    float s = 0.f;
+#pragma unroll
+    for (int i = 0; i < 8; i++) {
+        x[i] = __fmul_rn(g[i], inv_scale);
+        s = fmaf(x[i], x[i], s);
+    }
+    if (finite_f32(s)) {
+        if (clamp_on) {
+            float sc = 0.f;
+#pragma unroll
+            for (int i = 0; i < 8; i++) {
+                float c = fminf(fmaxf(x[i], -clamp_hi), clamp_hi);
+                sc = fmaf(c, c, sc);
+            }
+            a.sum += static_cast<double>(sc);
+        } else {
+            a.sum += static_cast<double>(s);
+        }
+        return;
+    }
+#pragma unroll
+    for (int i = 0; i < 8; i++) {
+        float q = __fmul_rn(x[i], x[i]);
+        if (!finite_f32(q)) {
+            a.flags |= (q != q) ? FLAG_NAN : FLAG_INF;
+        } else {
+            float c = clamp_on ? fminf(fmaxf(x[i], -clamp_hi), clamp_hi) : x[i];
+            a.sum += static_cast<double>(__fmul_rn(c, c));
+        }
+    }
+}
+
+// Warp shuffle -> shared memory -> distributed shared memory of the cluster's first block -> one partial per cluster.
+// partials[cluster][0] = sum, [1] = 1 if an infinity was seen, [2] = 1 if a NaN was seen. No atomics: the order
+// of every addition is fixed, so the norm is reproducible from run to run.
+__device__ __forceinline__ void cluster_reduce_store(NormAcc a, double* partials) {
+    __shared__ double s_sum[WARPS];
+    __shared__ uint32_t s_flag[WARPS];
+    __shared__ double c_sum[CLUSTER];
+    __shared__ uint32_t c_flag[CLUSTER];
+    cg::cluster_group cluster = cg::this_cluster();
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+        a.sum += __shfl_down_sync(0xffffffffu, a.sum, o);
+        a.flags |= __shfl_down_sync(0xffffffffu, a.flags, o);
+    }
+    if (lane == 0) {
+        s_sum[warp] = a.sum;
+        s_flag[warp] = a.flags;
+    }
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        double t = 0.0;
+        uint32_t f = 0;
+#pragma unroll
+        for (int w = 0; w < WARPS; w++) {
+            t += s_sum[w];
+            f |= s_flag[w];
+        }
+        const unsigned r = cluster.block_rank();
+        double* dst_sum = cluster.map_shared_rank(c_sum, 0);
+        uint32_t* dst_flag = cluster.map_shared_rank(c_flag, 0);
+        dst_sum[r] = t;
+        dst_flag[r] = f;
+    }
+    cluster.sync();
+    if (cluster.block_rank() == 0 && threadIdx.x == 0) {
+        double t = 0.0;
+        uint32_t f = 0;
+#pragma unroll
+        for (int r = 0; r < CLUSTER; r++) {
+            t += c_sum[r];
+            f |= c_flag[r];
+        }
+        const uint32_t cid = blockIdx.x / CLUSTER;
+        partials[3 * cid + 0] = t;
+        partials[3 * cid + 1] = (f & FLAG_INF) ? 1.0 : 0.0;
+        partials[3 * cid + 2] = (f & FLAG_NAN) ? 1.0 : 0.0;
+    }
+}
+
+template <int DT, int ILP>
+__global__ void __cluster_dims__(CLUSTER, 1, 1) __launch_bounds__(THREADS)
+    k_sumsq(const void* __restrict__ grads, TileMap map, const uint32_t* __restrict__ tile_meta,
+            const uint8_t* __restrict__ present, float inv_scale, float clamp_hi, int clamp_on,
+            double* __restrict__ partials) {
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    NormAcc a;
+    const uint32_t per_iter = gridDim.x * WARPS * ILP;
+    for (uint32_t base = (blockIdx.x * WARPS + warp) * ILP; base < map.n_local_tiles; base += per_iter) {
+        float g[ILP][8];
+        bool on[ILP];
+#pragma unroll
+        for (int j = 0; j < ILP; j++) {
+            const uint32_t lt = base + j;
+            on[j] = false;
+            if (lt < map.n_local_tiles) {
+                const uint32_t meta = tile_meta[flat_tile(map, lt)];
+                on[j] = meta != PAD_TILE && present[meta & 0xffffffu];
+                if (on[j]) load8<DT>(grads, static_cast<uint64_t>(lt) * TILE + lane * 8, g[j]);
+            }
+        }
+#pragma unroll
+        for (int j = 0; j < ILP; j++)
+            if (on[j]) acc8(g[j], inv_scale, clamp_hi, clamp_on != 0, a);
+    }
+    cluster_reduce_store(a, partials);
+}
+
+// The standalone measurement over a plain array: n elements, any n; the tail is read element by element.
+template <int DT>
+__global__ void __cluster_dims__(CLUSTER, 1, 1) __launch_bounds__(THREADS)
+    k_sumsq_plain(const void* __restrict__ grads, uint64_t n, float inv_scale, float clamp_hi, int clamp_on,
+                  double* __restrict__ partials) {
+    NormAcc a;
+    const uint64_t nvec = n / 8;
+    const uint64_t stride = static_cast<uint64_t>(gridDim.x) * THREADS;
+    for (uint64_t i = static_cast<uint64_t>(blockIdx.x) * THREADS + threadIdx.x; i < nvec; i += stride) {
+        float g[8];
+        load8<DT>(grads, i * 8, g);
+        acc8(g, inv_scale, clamp_hi, clamp_on != 0, a);
+    }
+    if (blockIdx.x == 0 && threadIdx.x == 0 && (n & 7)) {
+        float g[8];
+#pragma unroll
+        for (int k = 0; k < 8; k++) {
+            const uint64_t e = nvec * 8 + k;
+            float v = 0.f;
+            if (e < n) {
+                if constexpr (DT == OXZ_F32) v = static_cast<const float*>(grads)[e];
+                else if constexpr (DT == OXZ_BF16) v = __uint_as_float(static_cast<uint32_t>(static_cast<const uint16_t*>(grads)[e]) << 16);
+                else v = __half2float(static_cast<const __half*>(grads)[e]);
+            }
+            g[k] = v;
+        }
+        acc8(g, inv_scale, clamp_hi, clamp_on != 0, a);
+    }
+    cluster_reduce_store(a, partials);
+}
+
+template <int DT>
+__global__ void __cluster_dims__(CLUSTER, 1, 1) __launch_bounds__(THREADS)
+    k_pull_sumsq(PeerTable peers, int world, TileMap map, const uint32_t* __restrict__ tile_meta,
+                 const uint8_t* __restrict__ present, float inv_scale, float clamp_hi, int clamp_on,
+                 float* __restrict__ reduced, double* __restrict__ partials) {
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    NormAcc a;
+    const uint32_t per_iter = gridDim.x * WARPS;
+    for (uint32_t lt = blockIdx.x * WARPS + warp; lt < map.n_local_tiles; lt += per_iter) {
+        const uint32_t ft = flat_tile(map, lt);
+        const uint32_t meta = tile_meta[ft];
+        if (meta == PAD_TILE || !present[meta & 0xffffffu]) continue;
+        const uint64_t fe = static_cast<uint64_t>(ft) * TILE + lane * 8;
+        float s[8];
+        load8<DT>(peers.grads[0], fe, s);
+        // Two peers in flight at a time keeps NVLink busy without a register array indexed by rank.
+        int r = 1;
+        for (; r + 1 < world; r += 2) {
+            float p0[8], p1[8];
+            load8<DT>(peers.grads[r], fe, p0);
+            load8<DT>(peers.grads[r + 1], fe, p1);
+#pragma unroll
+            for (int i = 0; i < 8; i++) s[i] = __fadd_rn(__fadd_rn(s[i], p0[i]), p1[i]);
+        }
+        if (r < world) {
+            float p0[8];
+            load8<DT>(peers.grads[r], fe, p0);
+#pragma unroll
+            for (int i = 0; i < 8; i++) s[i] = __fadd_rn(s[i], p0[i]);
+        }
+        store8<OXZ_F32>(reduced, static_cast<uint64_t>(lt) * TILE + lane * 8, s);
+        acc8(s, inv_scale, clamp_hi, clamp_on != 0, a);
+    }
+    cluster_reduce_store(a, partials);
+}
+
+// One block: adds the per-cluster partials in index order.
+__global__ void __launch_bounds__(THREADS) k_reduce_partials(const double* __restrict__ partials, uint32_t slots,
+                                                             double* __restrict__ acc) {
+    __shared__ double sh[3][THREADS];
+    double t[3] = {0.0, 0.0, 0.0};
+    // contiguous chunks per thread keep the order fixed
+    const uint32_t per = (slots + THREADS - 1) / THREADS;
+    const uint32_t lo = threadIdx.x * per, hi = min(slots, lo + per);
+    for (uint32_t i = lo; i < hi; i++)
+        for (int k = 0; k < 3; k++) t[k] += partials[3 * i + k];
+    for (int k = 0; k < 3; k++) sh[k][threadIdx.x] = t[k];
+    __syncthreads();
+    if (threadIdx.x < 3) {
+        double r = 0.0;
+        for (int i = 0; i < THREADS; i++) r += sh[threadIdx.x][i];
+        acc[threadIdx.x] = r;
+    }
+}
+
+// acc = {sum of squares, infinities seen, NaNs seen} summed over every rank.
+// norm, the overflow decision and the clip coefficients follow src/grad_clip.rs:36-56 and src/trainer.rs:619-645.
+__global__ void k_finalize(const double* __restrict__ acc, FinalizeParams fp, DevScalars* __restrict__ out) {
+    if (threadIdx.x != 0 || blockIdx.x != 0) return;
+    const double sum = acc[0];
+    double norm;
+    if (acc[2] > 0.0) norm = __longlong_as_double(0x7ff8000000000000ll);
+    else if (acc[1] > 0.0) norm = __longlong_as_double(0x7ff0000000000000ll);
+    else norm = sqrt(sum);
+    const bool overflow = !isfinite(norm);
+    float c1 = 1.f, c2 = 1.f;
+    if (!overflow && norm > fp.max_grad_norm) c1 = static_cast<float>(fp.max_grad_norm / (norm + fp.clip_eps));
+    if (!overflow && !fp.spike_skip && fp.has_target) {
+        const double eff = norm < fp.max_grad_norm ? norm : fp.max_grad_norm;
+        if (eff > fp.target_grad_norm && eff > 1e-8) c2 = static_cast<float>(fp.target_grad_norm / (eff + fp.clip_eps));
+    }
+    out->norm = norm;
+    out->sumsq = sum;
+    out->c1 = c1;
+    out->c2 = c2;
+    out->overflow = overflow ? 1 : 0;
+    out->skip = (overflow || fp.spike_skip) ? 1 : 0;
+}
+
+// ---------------------------------------------------------------- AdamW
+
+__device__ __forceinline__ void adam1(float& p, float& m, float& v, float g, const AdamParams& k, float step,
+                                      float decay) {
+    if (!k.decay_after) p = __fmul_rn(p, decay);
+    m = __fadd_rn(__fmul_rn(k.beta1, m), __fmul_rn(k.one_minus_beta1, g));
+    const float gg = __fmul_rn(g, g);
+    v = __fadd_rn(__fmul_rn(k.beta2, v), __fmul_rn(k.one_minus_beta2, gg));
+    const float root = __fsqrt_rn(v);
+    const float denom = k.eps_mode == 0 ? __fadd_rn(__fdiv_rn(root, k.bias2_sqrt), k.eps) : __fadd_rn(root, k.eps);
+    const float q = __fdiv_rn(m, denom);
+    p = __fsub_rn(p, __fmul_rn(step, q));
+    if (k.decay_after) p = __fmul_rn(p, decay);
+}
+
+template <int GDT, int PDT, int ILP>
+__global__ void __launch_bounds__(THREADS)
+    k_adamw(const void* __restrict__ gsrc, float* __restrict__ master, float* __restrict__ exp_avg,
+            float* __restrict__ exp_avg_sq, PeerTable peers, int n_work, TileMap map,
+            const uint32_t* __restrict__ tile_meta, const uint8_t* __restrict__ present,
+            const DevScalars* __restrict__ scalars, AdamParams k) {
+    // The skip decision was taken on the device by the norm pass: an overflow or a spike veto changes nothing.
+    if (scalars->skip) return;
+    const float c1 = scalars->c1, c2 = scalars->c2;
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const uint32_t per_iter = gridDim.x * WARPS * ILP;
+    for (uint32_t base = (blockIdx.x * WARPS + warp) * ILP; base < map.n_local_tiles; base += per_iter) {
+        float g[ILP][8], p[ILP][8], m[ILP][8], v[ILP][8];
+        bool on[ILP];
+        uint32_t ftile[ILP], grp[ILP];
+#pragma unroll
+        for (int j = 0; j < ILP; j++) {
+            const uint32_t lt = base + j;
+            on[j] = false;
+            if (lt < map.n_local_tiles) {
+                ftile[j] = flat_tile(map, lt);
+                const uint32_t meta = tile_meta[ftile[j]];
+                grp[j] = meta >> 24;
+                on[j] = meta != PAD_TILE && present[meta & 0xffffffu];
+                if (on[j]) {
+                    const uint64_t le = static_cast<uint64_t>(lt) * TILE + lane * 8;
+                    load8<GDT>(gsrc, le, g[j]);
+                    load8<OXZ_F32>(master, le, p[j]);
+                    load8<OXZ_F32>(exp_avg, le, m[j]);
+                    load8<OXZ_F32>(exp_avg_sq, le, v[j]);
+                }
+            }
+        }
+#pragma unroll
+        for (int j = 0; j < ILP; j++) {
+            if (!on[j]) continue;
+            const float step = k.step_size[grp[j]], decay = k.decay_mul[grp[j]];
+#pragma unroll
+            for (int i = 0; i < 8; i++) {
+                float x = __fmul_rn(g[j][i], k.inv_scale);
+                if (k.clamp_on) {
+                    x = x > k.clamp_hi ? k.clamp_hi : x;
+                    x = x < -k.clamp_hi ? -k.clamp_hi : x;
+                }
+                x = __fmul_rn(__fmul_rn(x, c1), c2);
+                adam1(p[j][i], m[j][i], v[j][i], x, k, step, decay);
+            }
+            const uint64_t le = static_cast<uint64_t>(base + j) * TILE + lane * 8;
+            store8<OXZ_F32>(master, le, p[j]);
+            store8<OXZ_F32>(exp_avg, le, m[j]);
+            store8<OXZ_F32>(exp_avg_sq, le, v[j]);
+            const uint64_t fe = static_cast<uint64_t>(ftile[j]) * TILE + lane * 8;
+            for (int r = 0; r < n_work; r++) store8<PDT>(peers.work[r], fe, p[j]);
+        }
+    }
+}
+
+// ---------------------------------------------------------------- flatten
+
+template <int DT>
+__global__ void __launch_bounds__(THREADS)
+    k_flatten(void* __restrict__ flat, uint32_t n_tiles, const uint32_t* __restrict__ tile_meta,
+              const uint64_t* __restrict__ offsets, const uint64_t* __restrict__ numel,
+              const void* const* __restrict__ src, int accumulate) {
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const uint32_t per_iter = gridDim.x * WARPS;
+    for (uint32_t ft = blockIdx.x * WARPS + warp; ft < n_tiles; ft += per_iter) {
+        const uint32_t meta = tile_meta[ft];
+        const uint64_t fe = static_cast<uint64_t>(ft) * TILE + lane * 8;
+        float x[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+        if (meta != PAD_TILE) {
+            const uint32_t t = meta & 0xffffffu;
+            const void* s = src[t];
+            if (s != nullptr) {
+                const uint64_t te = fe - offsets[t];  // element within the tensor
+                const uint64_t n = numel[t];
+                if (te + 8 <= n) {
+                    load8<DT>(s, te, x);
+                } else {
+#pragma unroll
+                    for (int i = 0; i < 8; i++) {
+                        if (te + i < n) {
+                            if constexpr (DT == OXZ_F32) x[i] = static_cast<const float*>(s)[te + i];
+                            else if constexpr (DT == OXZ_BF16)
+                                x[i] = __uint_as_float(static_cast<uint32_t>(static_cast<const uint16_t*>(s)[te + i]) << 16);
+                            else x[i] = __half2float(static_cast<const __half*>(s)[te + i]);
+                        }
+                    }
+                }
+                if (accumulate) {
+                    float old[8];
+                    load8<DT>(flat, fe, old);
+#pragma unroll
+                    for (int i = 0; i < 8; i++) x[i] = __fadd_rn(old[i], x[i]);
+                }
+            } else if (accumulate) {
+                continue;  // nothing to add
+            }
+        }
+        store8<DT>(flat, fe, x);
+    }
+}
+
+// ---------------------------------------------------------------- launchers
+
+int32_t query_geom(int device, LaunchGeom* g) {
+    cudaDeviceProp prop;
+    OXZ_CUDA(cudaGetDeviceProperties(&prop, device));
+    g->sm_count = prop.multiProcessorCount;
+    // 4 resident blocks of 256 threads per SM for the read-only pass, 2 for the update (register bound).
+    int nb = g->sm_count * 4;
+    nb -= nb % CLUSTER;
+    g->norm_blocks = nb > 0 ? nb : CLUSTER;
+    g->adam_blocks = g->sm_count * 2;
+    return OXZ_OK;
+}
+
+uint32_t norm_partial_slots(const LaunchGeom& g) { return static_cast<uint32_t>(g.norm_blocks / CLUSTER); }
+
+static int32_t check_launch(const char* what) {
+    cudaError_t e = cudaGetLastError();
+    if (e != cudaSuccess) return fail(OXZ_ERR_CUDA, "launch of %s failed: %s", what, cudaGetErrorString(e));
+    return OXZ_OK;
+}
+
+int32_t launch_sumsq(cudaStream_t s, const LaunchGeom& g, const void* grads, int32_t dt, const TileMap& map,
+                     const uint32_t* tile_meta, const uint8_t* present, float inv_scale, float clamp_hi,
+                     int32_t clamp_on, double* partials) {
+    constexpr int ILP = 4;
+    dim3 grid(g.norm_blocks), block(THREADS);
+    switch (dt) {
+        case OXZ_F32: k_sumsq<OXZ_F32, ILP><<<grid, block, 0, s>>>(grads, map, tile_meta, present, inv_scale, clamp_hi, clamp_on, partials); break;
+        case OXZ_BF16: k_sumsq<OXZ_BF16, ILP><<<grid, block, 0, s>>>(grads, map, tile_meta, present, inv_scale, clamp_hi, clamp_on, partials); break;
+        case OXZ_F16: k_sumsq<OXZ_F16, ILP><<<grid, block, 0, s>>>(grads, map, tile_meta, present, inv_scale, clamp_hi, clamp_on, partials); break;
+        default: return fail(OXZ_ERR_INVALID, "unknown gradient dtype %d", dt);
+    }
+    return check_launch("k_sumsq");
+}
+
+int32_t launch_sumsq_plain(cudaStream_t s, int blocks, const void* grads, int32_t dt, uint64_t n, float inv_scale,
+                           float clamp_hi, int32_t clamp_on, double* partials) {
+    dim3 grid(blocks), block(THREADS);
+    switch (dt) {
+        case OXZ_F32: k_sumsq_plain<OXZ_F32><<<grid, block, 0, s>>>(grads, n, inv_scale, clamp_hi, clamp_on, partials); break;
+        case OXZ_BF16: k_sumsq_plain<OXZ_BF16><<<grid, block, 0, s>>>(grads, n, inv_scale, clamp_hi, clamp_on, partials); break;
+        case OXZ_F16: k_sumsq_plain<OXZ_F16><<<grid, block, 0, s>>>(grads, n, inv_scale, clamp_hi, clamp_on, partials); break;
+        default: return fail(OXZ_ERR_INVALID, "unknown gradient dtype %d", dt);
+    }
+    return check_launch("k_sumsq_plain");
+}
+
+int32_t launch_pull_sumsq(cudaStream_t s, const LaunchGeom& g, const PeerTable& peers, int32_t world, int32_t dt,
+                          const TileMap& map, const uint32_t* tile_meta, const uint8_t* present, float inv_scale,
+                          float clamp_hi, int32_t clamp_on, float* reduced, double* partials) {
+    dim3 grid(g.norm_blocks), block(THREADS);
+    switch (dt) {
+        case OXZ_F32: k_pull_sumsq<OXZ_F32><<<grid, block, 0, s>>>(peers, world, map, tile_meta, present, inv_scale, clamp_hi, clamp_on, reduced, partials); break;
+        case OXZ_BF16: k_pull_sumsq<OXZ_BF16><<<grid, block, 0, s>>>(peers, world, map, tile_meta, present, inv_scale, clamp_hi, clamp_on, reduced, partials); break;
+        case OXZ_F16: k_pull_sumsq<OXZ_F16><<<grid, block, 0, s>>>(peers, world, map, tile_meta, present, inv_scale, clamp_hi, clamp_on, reduced, partials); break;
+        default: return fail(OXZ_ERR_INVALID, "unknown gradient dtype %d", dt);
+    }
+    return check_launch("k_pull_sumsq");
+}
+
+int32_t launch_reduce_partials(cudaStream_t s, const double* partials, uint32_t slots, double* acc) {
+    k_reduce_partials<<<1, THREADS, 0, s>>>(partials, slots, acc);
+    return check_launch("k_reduce_partials");
+}
+
+int32_t launch_finalize(cudaStream_t s, const double* acc, const FinalizeParams& fp, DevScalars* scalars) {
+    k_finalize<<<1, 32, 0, s>>>(acc, fp, scalars);
+    return check_launch("k_finalize");
+}
+
+template <int GDT>
+static int32_t launch_adamw_g(cudaStream_t s, const LaunchGeom& g, const void* gsrc, float* master, float* m, float* v,
+                              const PeerTable& peers, int32_t n_work, int32_t pdt, const TileMap& map,
+                              const uint32_t* tile_meta, const uint8_t* present, const DevScalars* scalars,
+                              const AdamParams& ap) {
+    constexpr int ILP = 2;
+    dim3 grid(g.adam_blocks), block(THREADS);
+    switch (pdt) {
+        case OXZ_F32: k_adamw<GDT, OXZ_F32, ILP><<<grid, block, 0, s>>>(gsrc, master, m, v, peers, n_work, map, tile_meta, present, scalars, ap); break;
+        case OXZ_BF16: k_adamw<GDT, OXZ_BF16, ILP><<<grid, block, 0, s>>>(gsrc, master, m, v, peers, n_work, map, tile_meta, present, scalars, ap); break;
+        case OXZ_F16: k_adamw<GDT, OXZ_F16, ILP><<<grid, block, 0, s>>>(gsrc, master, m, v, peers, n_work, map, tile_meta, present, scalars, ap); break;
+        default: return fail(OXZ_ERR_INVALID, "unknown parameter dtype %d", pdt);
+    }
+    return check_launch("k_adamw");
+}
+
+int32_t launch_adamw(cudaStream_t s, const LaunchGeom& g, const void* gsrc, int32_t gdt, float* master, float* m,
+                     float* v, const PeerTable& peers, int32_t n_work, int32_t pdt, const TileMap& map,
+                     const uint32_t* tile_meta, const uint8_t* present, const DevScalars* scalars,
+                     const AdamParams& ap) {
+    switch (gdt) {
+        case OXZ_F32: return launch_adamw_g<OXZ_F32>(s, g, gsrc, master, m, v, peers, n_work, pdt, map, tile_meta, present, scalars, ap);
+        case OXZ_BF16: return launch_adamw_g<OXZ_BF16>(s, g, gsrc, master, m, v, peers, n_work, pdt, map, tile_meta, present, scalars, ap);
+        case OXZ_F16: return launch_adamw_g<OXZ_F16>(s, g, gsrc, master, m, v, peers, n_work, pdt, map, tile_meta, present, scalars, ap);
+        default: return fail(OXZ_ERR_INVALID, "unknown gradient dtype %d", gdt);
+    }
+}
+
+int32_t launch_flatten(cudaStream_t s, const LaunchGeom& g, void* flat, int32_t dt, uint32_t n_tiles,
+                       const uint32_t* tile_meta, const uint64_t* d_offsets, const uint64_t* d_numel,
+                       const void* const* d_src, int32_t accumulate) {
+    dim3 grid(g.sm_count * 4), block(THREADS);
+    switch (dt) {
+        case OXZ_F32: k_flatten<OXZ_F32><<<grid, block, 0, s>>>(flat, n_tiles, tile_meta, d_offsets, d_numel, d_src, accumulate); break;
+        case OXZ_BF16: k_flatten<OXZ_BF16><<<grid, block, 0, s>>>(flat, n_tiles, tile_meta, d_offsets, d_numel, d_src, accumulate); break;
+        case OXZ_F16: k_flatten<OXZ_F16><<<grid, block, 0, s>>>(flat, n_tiles, tile_meta, d_offsets, d_numel, d_src, accumulate); break;
+        default: return fail(OXZ_ERR_INVALID, "unknown gradient dtype %d", dt);
+    }
+    return check_launch("k_flatten");
+}
+
+}  // namespace oxz

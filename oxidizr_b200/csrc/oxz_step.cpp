@@ -1,0 +1,593 @@
+// Device state of a plan and the optimizer step itself: the order of src/trainer.rs:515-695 as one stream of
+// kernel launches with the skip decision taken on the device.
+#include <unistd.h>
+
+#include <cmath>
+#include <cstring>
+#include <map>
+#include <mutex>
+
+#include "oxz_internal.h"
+#include "oxz_nccl.h"
+
+using namespace oxz;
+
+namespace {
+
+TileMap tile_map(const oxz_plan* p) {
+    TileMap m;
+    m.tiles_per_shard = (uint32_t)(p->bucket_tiles / (uint64_t)p->world);
+    m.tiles_per_bucket = (uint32_t)p->bucket_tiles;
+    m.n_buckets = (uint32_t)p->n_buckets;
+    m.last_shard_tiles = (uint32_t)(p->last_bucket_tiles / (uint64_t)p->world);
+    m.rank = (uint32_t)p->rank;
+    m.n_local_tiles = (uint32_t)p->local_tiles;
+    return m;
+}
+
+ncclDataType_t nccl_dtype(int32_t dt) { return dt == OXZ_F32 ? ncclFloat32 : dt == OXZ_BF16 ? ncclBfloat16 : ncclFloat16; }
+
+struct PeerBlob {
+    uint64_t pid;
+    uint64_t grads_ptr, work_ptr;
+    int32_t device, pad;
+    cudaIpcMemHandle_t grads_handle, work_handle;
+};
+
+// Exchanges the gradient and weight buffers of every rank and maps the peers' copies into this process.
+// Ranks of one process (one thread per rank) use each other's pointers directly after enabling peer access;
+// ranks of other processes are opened through CUDA IPC handles.
+int32_t exchange_peers(oxz_plan* p, oxz_comm* c) {
+    const NcclApi* api = nccl_api();
+    if (!api) return fail(OXZ_ERR_UNSUPPORTED, "OXZ_SYNC_P2P needs NCCL for its rendezvous and it is not loaded");
+    PeerBlob mine{};
+    mine.pid = (uint64_t)getpid();
+    mine.grads_ptr = (uint64_t)p->grads;
+    mine.work_ptr = (uint64_t)p->work;
+    mine.device = p->device;
+    OXZ_CUDA(cudaIpcGetMemHandle(&mine.grads_handle, p->grads));
+    OXZ_CUDA(cudaIpcGetMemHandle(&mine.work_handle, p->work));
+    const int W = p->world;
+    PeerBlob* d_all = nullptr;
+    OXZ_CUDA(cudaMalloc(&d_all, sizeof(PeerBlob) * W));
+    OXZ_CUDA(cudaMemcpyAsync(d_all + p->rank, &mine, sizeof mine, cudaMemcpyHostToDevice, p->stream));
+    ncclResult_t rc = api->AllGather(d_all + p->rank, d_all, sizeof(PeerBlob), ncclInt8, (ncclComm_t)c->nccl, p->stream);
+    if (rc != ncclSuccess) return nccl_fail("peer rendezvous", rc);
+    std::vector<PeerBlob> all(W);
+    OXZ_CUDA(cudaMemcpyAsync(all.data(), d_all, sizeof(PeerBlob) * W, cudaMemcpyDeviceToHost, p->stream));
+    OXZ_CUDA(cudaStreamSynchronize(p->stream));
+    OXZ_CUDA(cudaFree(d_all));
+    for (int r = 0; r < W; r++) {
+        if (r == p->rank) {
+            p->peers.grads[r] = p->grads;
+            p->peers.work[r] = p->work;
+            continue;
+        }
+        const PeerBlob& b = all[r];
+        if (b.pid == mine.pid) {
+            if (b.device != p->device) {
+                int can = 0;
+                OXZ_CUDA(cudaDeviceCanAccessPeer(&can, p->device, b.device));
+                if (!can) return fail(OXZ_ERR_UNSUPPORTED, "device %d cannot access device %d as a peer", p->device, b.device);
+                cudaError_t e = cudaDeviceEnablePeerAccess(b.device, 0);
+                if (e == cudaErrorPeerAccessAlreadyEnabled) cudaGetLastError();
+                else if (e != cudaSuccess) return fail(OXZ_ERR_CUDA, "cudaDeviceEnablePeerAccess(%d): %s", b.device, cudaGetErrorString(e));
+            }
+            p->peers.grads[r] = (const void*)b.grads_ptr;
+            p->peers.work[r] = (void*)b.work_ptr;
+        } else {
+            void *g = nullptr, *w = nullptr;
+            OXZ_CUDA(cudaIpcOpenMemHandle(&g, b.grads_handle, cudaIpcMemLazyEnablePeerAccess));
+            OXZ_CUDA(cudaIpcOpenMemHandle(&w, b.work_handle, cudaIpcMemLazyEnablePeerAccess));
+            p->ipc_opened.push_back(g);
+            p->ipc_opened.push_back(w);
+            p->peers.grads[r] = g;
+            p->peers.work[r] = w;
+        }
+    }
+    return OXZ_OK;
+}
+
+// Runs of one tensor's flat span that a rank owns: calls fn(flat_start, local_start, len) per run.
+template <class F>
+void for_owned_runs(const oxz_plan* p, uint64_t tensor, F fn) {
+    const uint64_t lo = p->offset[tensor], hi = lo + p->numel[tensor];
+    if (hi == lo) return;
+    const uint64_t bucket_elems = p->bucket_tiles * TILE;
+    const uint64_t full_shard = bucket_elems / (uint64_t)p->world;
+    for (uint64_t b = lo / bucket_elems; b < p->n_buckets && b * bucket_elems < hi; b++) {
+        const uint64_t tiles = (b == p->n_buckets - 1) ? p->last_bucket_tiles : p->bucket_tiles;
+        const uint64_t shard = tiles * TILE / (uint64_t)p->world;
+        const uint64_t s0 = b * bucket_elems + (uint64_t)p->rank * shard, s1 = s0 + shard;
+        const uint64_t a = lo > s0 ? lo : s0, z = hi < s1 ? hi : s1;
+        if (a < z) fn(a, b * full_shard + (a - s0), z - a);
+    }
+}
+
+float* state_array(oxz_plan* p, int32_t kind) {
+    switch (kind) {
+        case OXZ_STATE_MASTER: return p->master;
+        case OXZ_STATE_EXP_AVG: return p->exp_avg;
+        case OXZ_STATE_EXP_AVG_SQ: return p->exp_avg_sq;
+        default: return nullptr;
+    }
+}
+
+int32_t check_state_call(oxz_plan* p, int32_t kind, uint64_t tensor, const void* host, const char* who) {
+    if (!p || !host) return fail(OXZ_ERR_INVALID, "%s: null argument", who);
+    if (!p->allocated) return fail(OXZ_ERR_STATE, "%s: the plan has no device state. Call oxz_state_alloc first", who);
+    if (p->inflight) return fail(OXZ_ERR_STATE, "%s: a step is in flight. Call oxz_step_wait first", who);
+    if (tensor >= p->T) return fail(OXZ_ERR_INVALID, "%s: tensor %llu of %llu", who, (unsigned long long)tensor, (unsigned long long)p->T);
+    if (kind < OXZ_STATE_MASTER || kind > OXZ_STATE_GRADS) return fail(OXZ_ERR_INVALID, "%s: unknown state kind %d", who, kind);
+    return OXZ_OK;
+}
+
+}  // namespace
+
+extern "C" {
+
+int32_t oxz_plan_destroy(oxz_plan* p) {
+    if (!p) return OXZ_OK;
+    if (p->allocated) {
+        cudaSetDevice(p->device);
+        cudaStreamSynchronize(p->stream);
+        for (void* q : p->ipc_opened) cudaIpcCloseMemHandle(q);
+        if (p->work && p->work != (void*)p->master) cudaFree(p->work);
+        for (void* q : {(void*)p->grads, (void*)p->master, (void*)p->exp_avg, (void*)p->exp_avg_sq, p->reduced,
+                        (void*)p->d_tile_meta, (void*)p->d_present, (void*)p->d_offsets, (void*)p->d_numel,
+                        (void*)p->d_src, (void*)p->d_partials, (void*)p->d_acc, (void*)p->d_scalars})
+            if (q) cudaFree(q);
+        for (void* q : {(void*)p->h_scalars, (void*)p->h_acc, (void*)p->h_present, (void*)p->h_src})
+            if (q) cudaFreeHost(q);
+        if (p->done) cudaEventDestroy(p->done);
+        for (auto e : p->ev) if (e) cudaEventDestroy(e);
+        if (p->own_stream) cudaStreamDestroy(p->own_stream);
+    }
+    delete p;
+    return OXZ_OK;
+}
+
+int32_t oxz_plan_set_stream(oxz_plan* p, void* stream) {
+    if (!p) return fail(OXZ_ERR_INVALID, "oxz_plan_set_stream: null plan");
+    if (!p->allocated) return fail(OXZ_ERR_STATE, "oxz_plan_set_stream: call oxz_state_alloc first");
+    if (p->inflight) return fail(OXZ_ERR_STATE, "oxz_plan_set_stream: a step is in flight");
+    p->stream = stream ? (cudaStream_t)stream : p->own_stream;
+    return OXZ_OK;
+}
+
+int32_t oxz_state_alloc(oxz_plan* p, oxz_comm* comm) {
+    if (!p) return fail(OXZ_ERR_INVALID, "oxz_state_alloc: null plan");
+    if (p->allocated) return fail(OXZ_ERR_STATE, "oxz_state_alloc: the plan already has device state");
+    if (p->world > 1) {
+        OXZ_TRY(comm_check(comm, "oxz_state_alloc"));
+        if (comm->world != p->world || comm->rank != p->rank)
+            return fail(OXZ_ERR_INVALID, "oxz_state_alloc: the plan is rank %d of %d but the communicator is rank %d of %d",
+                        p->rank, p->world, comm->rank, comm->world);
+    }
+    OXZ_CUDA(cudaSetDevice(p->device));
+    OXZ_TRY(query_geom(p->device, &p->geom));
+    OXZ_CUDA(cudaStreamCreateWithFlags(&p->own_stream, cudaStreamNonBlocking));
+    p->stream = p->own_stream;
+    p->comm = comm;
+    const uint64_t padded = p->total_tiles * TILE, local = p->local_tiles * TILE;
+    const size_t gs = dtype_size(p->gdt), ps = dtype_size(p->pdt);
+    auto zalloc = [](void** q, size_t bytes) -> cudaError_t {
+        cudaError_t e = cudaMalloc(q, bytes ? bytes : 16);
+        if (e != cudaSuccess) return e;
+        return cudaMemset(*q, 0, bytes ? bytes : 16);
+    };
+    OXZ_CUDA(zalloc(&p->grads, padded * gs));
+    OXZ_CUDA(zalloc((void**)&p->master, local * 4));
+    OXZ_CUDA(zalloc((void**)&p->exp_avg, local * 4));
+    OXZ_CUDA(zalloc((void**)&p->exp_avg_sq, local * 4));
+    const bool separate_work = !(p->pdt == OXZ_F32 && p->world == 1);
+    if (separate_work) OXZ_CUDA(zalloc(&p->work, padded * ps));
+    else p->work = p->master;
+    if (p->world > 1) OXZ_CUDA(zalloc(&p->reduced, local * (p->mode == OXZ_SYNC_P2P ? 4 : gs)));
+    OXZ_CUDA(zalloc((void**)&p->d_tile_meta, p->total_tiles * 4));
+    OXZ_CUDA(cudaMemcpy(p->d_tile_meta, p->tile_meta.data(), p->total_tiles * 4, cudaMemcpyHostToDevice));
+    OXZ_CUDA(zalloc((void**)&p->d_present, p->T));
+    if (p->T) OXZ_CUDA(cudaMemset(p->d_present, 1, p->T));
+    OXZ_CUDA(zalloc((void**)&p->d_offsets, p->T * 8));
+    OXZ_CUDA(zalloc((void**)&p->d_numel, p->T * 8));
+    if (p->T) {
+        OXZ_CUDA(cudaMemcpy(p->d_offsets, p->offset.data(), p->T * 8, cudaMemcpyHostToDevice));
+        OXZ_CUDA(cudaMemcpy(p->d_numel, p->numel.data(), p->T * 8, cudaMemcpyHostToDevice));
+    }
+    OXZ_CUDA(zalloc((void**)&p->d_src, p->T * 8));
+    OXZ_CUDA(zalloc((void**)&p->d_partials, (size_t)norm_partial_slots(p->geom) * 3 * 8));
+    OXZ_CUDA(zalloc((void**)&p->d_acc, (3 + MAX_EXTRAS) * 8));
+    OXZ_CUDA(zalloc((void**)&p->d_scalars, sizeof(DevScalars)));
+    OXZ_CUDA(cudaMallocHost((void**)&p->h_scalars, sizeof(DevScalars)));
+    OXZ_CUDA(cudaMallocHost((void**)&p->h_acc, (3 + MAX_EXTRAS) * 8));
+    OXZ_CUDA(cudaMallocHost((void**)&p->h_present, p->T ? p->T : 1));
+    OXZ_CUDA(cudaMallocHost((void**)&p->h_src, (p->T ? p->T : 1) * 8));
+    memset(p->h_present, 1, p->T ? p->T : 1);
+    OXZ_CUDA(cudaEventCreateWithFlags(&p->done, cudaEventDisableTiming));
+    OXZ_CUDA(cudaDeviceSynchronize());
+    p->peers.grads[0] = p->grads;
+    p->peers.work[0] = p->work;
+    if (p->mode == OXZ_SYNC_P2P) OXZ_TRY(exchange_peers(p, comm));
+    p->allocated = true;
+    return OXZ_OK;
+}
+
+int32_t oxz_state_pointers(const oxz_plan* p, void** grads, void** work, void** master, void** exp_avg,
+                           void** exp_avg_sq) {
+    if (!p) return fail(OXZ_ERR_INVALID, "oxz_state_pointers: null plan");
+    if (!p->allocated) return fail(OXZ_ERR_STATE, "oxz_state_pointers: call oxz_state_alloc first");
+    if (grads) *grads = p->grads;
+    if (work) *work = p->work;
+    if (master) *master = p->master;
+    if (exp_avg) *exp_avg = p->exp_avg;
+    if (exp_avg_sq) *exp_avg_sq = p->exp_avg_sq;
+    return OXZ_OK;
+}
+
+int32_t oxz_state_import(oxz_plan* p, int32_t kind, uint64_t tensor, const void* host) {
+    OXZ_TRY(check_state_call(p, kind, tensor, host, "oxz_state_import"));
+    OXZ_CUDA(cudaSetDevice(p->device));
+    OXZ_CUDA(cudaStreamSynchronize(p->stream));
+    const uint64_t n = p->numel[tensor];
+    if (kind == OXZ_STATE_GRADS || kind == OXZ_STATE_WORK) {
+        const size_t es = dtype_size(kind == OXZ_STATE_GRADS ? p->gdt : p->pdt);
+        char* base = static_cast<char*>(kind == OXZ_STATE_GRADS ? p->grads : p->work);
+        if (kind == OXZ_STATE_WORK && p->work == (void*)p->master) kind = OXZ_STATE_MASTER;
+        else {
+            OXZ_CUDA(cudaMemcpy(base + p->offset[tensor] * es, host, n * es, cudaMemcpyHostToDevice));
+            return OXZ_OK;
+        }
+    }
+    float* arr = state_array(p, kind);
+    cudaError_t err = cudaSuccess;
+    for_owned_runs(p, tensor, [&](uint64_t flat, uint64_t local, uint64_t len) {
+        if (err != cudaSuccess) return;
+        err = cudaMemcpy(arr + local, static_cast<const float*>(host) + (flat - p->offset[tensor]), len * 4, cudaMemcpyHostToDevice);
+    });
+    if (err != cudaSuccess) return fail(OXZ_ERR_CUDA, "oxz_state_import: %s", cudaGetErrorString(err));
+    return OXZ_OK;
+}
+
+int32_t oxz_state_export(oxz_plan* p, int32_t kind, uint64_t tensor, void* host) {
+    OXZ_TRY(check_state_call(p, kind, tensor, host, "oxz_state_export"));
+    OXZ_CUDA(cudaSetDevice(p->device));
+    OXZ_CUDA(cudaStreamSynchronize(p->stream));
+    const uint64_t n = p->numel[tensor];
+    if (kind == OXZ_STATE_GRADS || kind == OXZ_STATE_WORK) {
+        const size_t es = dtype_size(kind == OXZ_STATE_GRADS ? p->gdt : p->pdt);
+        const char* base = static_cast<const char*>(kind == OXZ_STATE_GRADS ? p->grads : p->work);
+        if (kind == OXZ_STATE_WORK && p->work == (void*)p->master) kind = OXZ_STATE_MASTER;
+        else {
+            OXZ_CUDA(cudaMemcpy(host, base + p->offset[tensor] * es, n * es, cudaMemcpyDeviceToHost));
+            return OXZ_OK;
+        }
+    }
+    const float* arr = state_array(p, kind);
+    cudaError_t err = cudaSuccess;
+    for_owned_runs(p, tensor, [&](uint64_t flat, uint64_t local, uint64_t len) {
+        if (err != cudaSuccess) return;
+        err = cudaMemcpy(static_cast<float*>(host) + (flat - p->offset[tensor]), arr + local, len * 4, cudaMemcpyDeviceToHost);
+    });
+    if (err != cudaSuccess) return fail(OXZ_ERR_CUDA, "oxz_state_export: %s", cudaGetErrorString(err));
+    return OXZ_OK;
+}
+
+int32_t oxz_state_set_timestep(oxz_plan* p, uint64_t t) {
+    if (!p) return fail(OXZ_ERR_INVALID, "oxz_state_set_timestep: null plan");
+    if (p->inflight) return fail(OXZ_ERR_STATE, "oxz_state_set_timestep: a step is in flight");
+    p->timestep = t;
+    return OXZ_OK;
+}
+
+int32_t oxz_state_timestep(const oxz_plan* p, uint64_t* t) {
+    if (!p || !t) return fail(OXZ_ERR_INVALID, "oxz_state_timestep: null argument");
+    *t = p->timestep;
+    return OXZ_OK;
+}
+
+int32_t oxz_grads_flatten_async(oxz_plan* p, const void* const* grad_ptrs, int32_t accumulate) {
+    if (!p || !grad_ptrs) return fail(OXZ_ERR_INVALID, "oxz_grads_flatten_async: null argument");
+    if (!p->allocated) return fail(OXZ_ERR_STATE, "oxz_grads_flatten_async: call oxz_state_alloc first");
+    if (p->inflight) return fail(OXZ_ERR_STATE, "oxz_grads_flatten_async: a step is in flight. Call oxz_step_wait first");
+    OXZ_CUDA(cudaSetDevice(p->device));
+    for (uint64_t i = 0; i < p->T; i++) {
+        if (grad_ptrs[i] && ((uintptr_t)grad_ptrs[i] & 15))
+            return fail(OXZ_ERR_INVALID, "oxz_grads_flatten_async: the gradient of tensor %llu is not 16-byte aligned", (unsigned long long)i);
+    }
+    // The pointer table is staged in pinned memory; the previous use must have left the stream.
+    OXZ_CUDA(cudaStreamSynchronize(p->stream));
+    for (uint64_t i = 0; i < p->T; i++) p->h_src[i] = grad_ptrs[i];
+    if (p->T) OXZ_CUDA(cudaMemcpyAsync(p->d_src, p->h_src, p->T * 8, cudaMemcpyHostToDevice, p->stream));
+    return launch_flatten(p->stream, p->geom, p->grads, p->gdt, (uint32_t)p->total_tiles, p->d_tile_meta, p->d_offsets,
+                          p->d_numel, p->d_src, accumulate);
+}
+
+int32_t oxz_grads_upload_async(oxz_plan* p, uint64_t tensor, const void* host) {
+    if (!p || !host) return fail(OXZ_ERR_INVALID, "oxz_grads_upload_async: null argument");
+    if (!p->allocated) return fail(OXZ_ERR_STATE, "oxz_grads_upload_async: call oxz_state_alloc first");
+    if (p->inflight) return fail(OXZ_ERR_STATE, "oxz_grads_upload_async: a step is in flight. Call oxz_step_wait first");
+    if (tensor >= p->T) return fail(OXZ_ERR_INVALID, "oxz_grads_upload_async: tensor %llu of %llu", (unsigned long long)tensor, (unsigned long long)p->T);
+    OXZ_CUDA(cudaSetDevice(p->device));
+    const size_t es = dtype_size(p->gdt);
+    OXZ_CUDA(cudaMemcpyAsync(static_cast<char*>(p->grads) + p->offset[tensor] * es, host, p->numel[tensor] * es,
+                             cudaMemcpyHostToDevice, p->stream));
+    return OXZ_OK;
+}
+
+static int32_t check_hyper(const oxz_hyper* h) {
+    auto pos = [](double x) { return std::isfinite(x) && x > 0.0; };
+    if (!std::isfinite(h->lr) || h->lr < 0.0) return fail(OXZ_ERR_INVALID, "learning rate %g must be finite and not negative", h->lr);
+    if (!(h->beta1 >= 0.0 && h->beta1 < 1.0) || !(h->beta2 >= 0.0 && h->beta2 < 1.0))
+        return fail(OXZ_ERR_INVALID, "adamw betas (%g, %g) must lie in [0, 1)", h->beta1, h->beta2);
+    if (!std::isfinite(h->eps) || h->eps < 0.0) return fail(OXZ_ERR_INVALID, "adamw_eps %g must be finite and not negative", h->eps);
+    if (!std::isfinite(h->weight_decay)) return fail(OXZ_ERR_INVALID, "weight_decay %g must be finite", h->weight_decay);
+    if (std::isnan(h->max_grad_norm) || h->max_grad_norm <= 0.0) return fail(OXZ_ERR_INVALID, "max_grad_norm %g must be positive", h->max_grad_norm);
+    // check_max_grad_value, src/grad_clip.rs:18-26
+    if (!std::isnan(h->max_grad_value) && !pos(h->max_grad_value))
+        return fail(OXZ_ERR_INVALID, "trainer.max_grad_value is %g: it must be a finite positive number. Set a positive value, or remove the key to disable per-element clipping.", h->max_grad_value);
+    if (!std::isnan(h->target_grad_norm) && !pos(h->target_grad_norm))
+        return fail(OXZ_ERR_INVALID, "target_grad_norm %g must be finite and positive", h->target_grad_norm);
+    if (!std::isnan(h->loss_scale) && h->loss_scale != 0.0 && !pos(h->loss_scale))
+        return fail(OXZ_ERR_INVALID, "loss scale %g must be finite and positive", h->loss_scale);
+    if (!std::isfinite(h->clip_eps) || h->clip_eps < 0.0) return fail(OXZ_ERR_INVALID, "clip_eps %g must be finite and not negative", h->clip_eps);
+    return OXZ_OK;
+}
+
+int32_t oxz_step_async(oxz_plan* p, oxz_comm* comm, const oxz_hyper* h, const uint8_t* present, double* extras,
+                       uint32_t n_extras) {
+    if (!p || !h) return fail(OXZ_ERR_INVALID, "oxz_step_async: null argument");
+    if (!p->allocated) return fail(OXZ_ERR_STATE, "oxz_step_async: the plan has no device state. Call oxz_state_alloc first");
+    if (p->inflight) return fail(OXZ_ERR_STATE, "oxz_step_async: the previous step is still in flight. Call oxz_step_wait first");
+    if (n_extras > MAX_EXTRAS || (n_extras && !extras)) return fail(OXZ_ERR_INVALID, "oxz_step_async: at most %u extras", MAX_EXTRAS);
+    OXZ_TRY(check_hyper(h));
+    if (p->world > 1) {
+        OXZ_TRY(comm_check(comm, "oxz_step_async"));
+        if (comm != p->comm) return fail(OXZ_ERR_INVALID, "oxz_step_async: this is not the communicator the state was allocated with");
+    }
+    OXZ_CUDA(cudaSetDevice(p->device));
+    cudaStream_t s = p->stream;
+    const NcclApi* api = p->world > 1 ? nccl_api() : nullptr;
+    ncclComm_t nc = p->world > 1 ? (ncclComm_t)comm->nccl : nullptr;
+
+    // which tensors have a gradient this step
+    bool changed = false;
+    for (uint64_t i = 0; i < p->T; i++) {
+        const uint8_t v = present ? (present[i] ? 1 : 0) : 1;
+        if (p->h_present[i] != v) {
+            p->h_present[i] = v;
+            changed = true;
+        }
+    }
+    if (changed) OXZ_CUDA(cudaMemcpyAsync(p->d_present, p->h_present, p->T, cudaMemcpyHostToDevice, s));
+
+    // per-step scalars, f64 on the host, rounded to f32 once
+    const uint64_t t = p->timestep + 1;
+    const bool scaled = !std::isnan(h->loss_scale) && h->loss_scale != 0.0;
+    AdamParams ap{};
+    const double bc1 = 1.0 - std::pow(h->beta1, (double)t), bc2 = 1.0 - std::pow(h->beta2, (double)t);
+    ap.beta1 = (float)h->beta1;
+    ap.one_minus_beta1 = (float)(1.0 - h->beta1);
+    ap.beta2 = (float)h->beta2;
+    ap.one_minus_beta2 = (float)(1.0 - h->beta2);
+    ap.eps = (float)h->eps;
+    ap.bias2_sqrt = (float)std::sqrt(bc2);
+    ap.inv_scale = scaled ? (float)(1.0 / h->loss_scale) : 1.0f;
+    ap.clamp_on = std::isnan(h->max_grad_value) ? 0 : 1;
+    ap.clamp_hi = ap.clamp_on ? (float)h->max_grad_value : 0.f;
+    ap.decay_after = h->decay_after ? 1 : 0;
+    ap.eps_mode = h->eps_mode ? 1 : 0;
+    for (size_t g = 0; g < p->group_lr_scale.size(); g++) {
+        const double lr_t = h->lr * (double)p->group_lr_scale[g];
+        const double wd = p->group_no_decay[g] ? 0.0 : h->weight_decay;
+        ap.step_size[g] = ap.eps_mode == 0 ? (float)(lr_t / bc1) : (float)(lr_t * std::sqrt(bc2) / bc1);
+        ap.decay_mul[g] = (float)(1.0 - lr_t * wd);
+    }
+    FinalizeParams fp{};
+    fp.max_grad_norm = h->max_grad_norm;
+    fp.has_target = std::isnan(h->target_grad_norm) ? 0 : 1;
+    fp.target_grad_norm = fp.has_target ? h->target_grad_norm : 0.0;
+    fp.clip_eps = h->clip_eps;
+    fp.spike_skip = h->spike_skip ? 1 : 0;
+
+    const TileMap map = tile_map(p);
+    const uint32_t slots = norm_partial_slots(p->geom);
+    const void* gsrc = p->grads;
+    int32_t gsrc_dt = p->gdt;
+    int32_t* bar = p->world > 1 ? reinterpret_cast<int32_t*>(static_cast<char*>(comm->d_small) + 384) : nullptr;
+
+    auto mark = [&](int i) -> cudaError_t { return p->profile ? cudaEventRecord(p->ev[i], s) : cudaSuccess; };
+    OXZ_CUDA(mark(0));
+    if (p->mode == OXZ_SYNC_SINGLE) {
+        OXZ_CUDA(mark(1));
+        OXZ_TRY(launch_sumsq(s, p->geom, p->grads, p->gdt, map, p->d_tile_meta, p->d_present, ap.inv_scale, ap.clamp_hi,
+                             ap.clamp_on, p->d_partials));
+    } else if (p->mode == OXZ_SYNC_P2P) {
+        // every rank's gradients must be complete before anyone pulls them
+        ncclResult_t rc = api->AllReduce(bar, bar, 1, ncclInt32, ncclSum, nc, s);
+        if (rc != ncclSuccess) return nccl_fail("the pre-pull barrier", rc);
+        OXZ_CUDA(mark(1));
+        OXZ_TRY(launch_pull_sumsq(s, p->geom, p->peers, p->world, p->gdt, map, p->d_tile_meta, p->d_present, ap.inv_scale,
+                                  ap.clamp_hi, ap.clamp_on, static_cast<float*>(p->reduced), p->d_partials));
+        gsrc = p->reduced;
+        gsrc_dt = OXZ_F32;
+    } else {
+        const size_t gs = dtype_size(p->gdt);
+        ncclResult_t rc = api->GroupStart();
+        if (rc != ncclSuccess) return nccl_fail("ncclGroupStart", rc);
+        for (uint64_t b = 0; b < p->n_buckets; b++) {
+            uint64_t start, len, ss, sl;
+            oxz_plan_bucket(p, b, p->rank, &start, &len, &ss, &sl);
+            const uint64_t local = b * (p->bucket_tiles / (uint64_t)p->world) * TILE;
+            rc = api->ReduceScatter(static_cast<const char*>(p->grads) + start * gs, static_cast<char*>(p->reduced) + local * gs,
+                                    sl, nccl_dtype(p->gdt), ncclSum, nc, s);
+            if (rc != ncclSuccess) return nccl_fail("the gradient reduce-scatter", rc);
+        }
+        rc = api->GroupEnd();
+        if (rc != ncclSuccess) return nccl_fail("the gradient reduce-scatter", rc);
+        OXZ_CUDA(mark(1));
+        OXZ_TRY(launch_sumsq(s, p->geom, p->reduced, p->gdt, map, p->d_tile_meta, p->d_present, ap.inv_scale, ap.clamp_hi,
+                             ap.clamp_on, p->d_partials));
+        gsrc = p->reduced;
+    }
+    OXZ_CUDA(mark(2));
+    OXZ_TRY(launch_reduce_partials(s, p->d_partials, slots, p->d_acc));
+    if (p->world > 1) {
+        for (uint32_t i = 0; i < n_extras; i++) p->h_acc[3 + i] = extras[i];
+        if (n_extras) OXZ_CUDA(cudaMemcpyAsync(p->d_acc + 3, p->h_acc + 3, n_extras * 8, cudaMemcpyHostToDevice, s));
+        // The one all-reduce of the step: {sum of squares, inf count, NaN count, extras...}. In P2P mode its end
+        // also tells every rank that all peers have finished reading its gradient buffer.
+        ncclResult_t rc = api->AllReduce(p->d_acc, p->d_acc, 3 + n_extras, ncclFloat64, ncclSum, nc, s);
+        if (rc != ncclSuccess) return nccl_fail("the norm all-reduce", rc);
+    }
+    OXZ_TRY(launch_finalize(s, p->d_acc, fp, p->d_scalars));
+    OXZ_CUDA(cudaMemcpyAsync(p->h_scalars, p->d_scalars, sizeof(DevScalars), cudaMemcpyDeviceToHost, s));
+    if (p->world > 1 && n_extras)
+        OXZ_CUDA(cudaMemcpyAsync(p->h_acc, p->d_acc, (3 + n_extras) * 8, cudaMemcpyDeviceToHost, s));
+
+    OXZ_CUDA(mark(3));
+    const bool separate_work = p->work != (void*)p->master;
+    const int32_t n_work = !separate_work ? 0 : (p->mode == OXZ_SYNC_P2P ? p->world : 1);
+    OXZ_TRY(launch_adamw(s, p->geom, gsrc, gsrc_dt, p->master, p->exp_avg, p->exp_avg_sq, p->peers, n_work, p->pdt, map,
+                         p->d_tile_meta, p->d_present, p->d_scalars, ap));
+    OXZ_CUDA(mark(4));
+    if (p->mode == OXZ_SYNC_NCCL) {
+        const size_t ps = dtype_size(p->pdt);
+        ncclResult_t rc = api->GroupStart();
+        if (rc != ncclSuccess) return nccl_fail("ncclGroupStart", rc);
+        for (uint64_t b = 0; b < p->n_buckets; b++) {
+            uint64_t start, len, ss, sl;
+            oxz_plan_bucket(p, b, p->rank, &start, &len, &ss, &sl);
+            rc = api->AllGather(static_cast<const char*>(p->work) + ss * ps, static_cast<char*>(p->work) + start * ps, sl * ps,
+                                ncclInt8, nc, s);
+            if (rc != ncclSuccess) return nccl_fail("the weight all-gather", rc);
+        }
+        rc = api->GroupEnd();
+        if (rc != ncclSuccess) return nccl_fail("the weight all-gather", rc);
+    } else if (p->mode == OXZ_SYNC_P2P) {
+        // every rank's stores into this rank's weight buffer must have landed before the step is reported done
+        ncclResult_t rc = api->AllReduce(bar, bar, 1, ncclInt32, ncclSum, nc, s);
+        if (rc != ncclSuccess) return nccl_fail("the post-push barrier", rc);
+    }
+    OXZ_CUDA(mark(5));
+    OXZ_CUDA(cudaEventRecord(p->done, s));
+    p->inflight = true;
+    p->inflight_hyper = *h;
+    p->inflight_extras = extras;
+    p->inflight_n_extras = n_extras;
+    return OXZ_OK;
+}
+
+int32_t oxz_step_wait(oxz_plan* p, oxz_step_result* res) {
+    if (!p) return fail(OXZ_ERR_INVALID, "oxz_step_wait: null plan");
+    if (!p->inflight) return fail(OXZ_ERR_STATE, "oxz_step_wait: no step is in flight");
+    OXZ_CUDA(cudaSetDevice(p->device));
+    cudaError_t e = cudaEventSynchronize(p->done);
+    p->inflight = false;
+    if (p->comm && p->comm->aborted.load()) return fail(OXZ_ERR_ABORTED, "oxz_step_wait: the communicator was aborted during the step");
+    if (e != cudaSuccess) return fail(OXZ_ERR_CUDA, "oxz_step_wait: %s", cudaGetErrorString(e));
+    const DevScalars& d = *p->h_scalars;
+    const oxz_hyper& h = p->inflight_hyper;
+    const bool applied = !d.skip;
+    if (applied) p->timestep += 1;
+    if (p->world > 1)
+        for (uint32_t i = 0; i < p->inflight_n_extras; i++) p->inflight_extras[i] = p->h_acc[3 + i];
+    if (res) {
+        res->grad_norm = d.norm;
+        res->overflow = d.overflow;
+        res->applied = applied ? 1 : 0;
+        res->timestep = p->timestep;
+        res->clip_coef = (double)d.c1 * (double)d.c2;
+        double rep = d.norm;
+        if (applied) {
+            rep = d.norm < h.max_grad_norm ? d.norm : h.max_grad_norm;
+            if (!std::isnan(h.target_grad_norm) && h.target_grad_norm < rep) rep = h.target_grad_norm;
+        }
+        res->reported_norm = rep;
+    }
+    return OXZ_OK;
+}
+
+int32_t oxz_plan_set_profile(oxz_plan* p, int32_t on) {
+    if (!p) return fail(OXZ_ERR_INVALID, "oxz_plan_set_profile: null plan");
+    if (!p->allocated) return fail(OXZ_ERR_STATE, "oxz_plan_set_profile: call oxz_state_alloc first");
+    if (p->inflight) return fail(OXZ_ERR_STATE, "oxz_plan_set_profile: a step is in flight");
+    OXZ_CUDA(cudaSetDevice(p->device));
+    if (on && !p->ev[0])
+        for (auto& e : p->ev) OXZ_CUDA(cudaEventCreate(&e));
+    p->profile = on != 0;
+    return OXZ_OK;
+}
+
+int32_t oxz_step_profile_read(oxz_plan* p, oxz_step_profile* out) {
+    if (!p || !out) return fail(OXZ_ERR_INVALID, "oxz_step_profile_read: null argument");
+    if (!p->profile) return fail(OXZ_ERR_STATE, "oxz_step_profile_read: profiling is off. Call oxz_plan_set_profile first");
+    if (p->inflight) return fail(OXZ_ERR_STATE, "oxz_step_profile_read: a step is in flight. Call oxz_step_wait first");
+    OXZ_CUDA(cudaSetDevice(p->device));
+    float d[5];
+    for (int i = 0; i < 5; i++) OXZ_CUDA(cudaEventElapsedTime(&d[i], p->ev[i], p->ev[i + 1]));
+    out->collect_ms = d[0];
+    out->norm_ms = d[1];
+    out->decide_ms = d[2];
+    out->update_ms = d[3];
+    out->publish_ms = d[4];
+    OXZ_CUDA(cudaEventElapsedTime(&out->total_ms, p->ev[0], p->ev[5]));
+    return OXZ_OK;
+}
+
+int32_t oxz_step(oxz_plan* p, oxz_comm* comm, const oxz_hyper* h, const uint8_t* present, double* extras,
+                 uint32_t n_extras, oxz_step_result* res) {
+    OXZ_TRY(oxz_step_async(p, comm, h, present, extras, n_extras));
+    return oxz_step_wait(p, res);
+}
+
+// ---- standalone norm ----
+namespace {
+struct NormScratch {
+    int blocks = 0;
+    uint32_t slots = 0;
+    double* d_partials = nullptr;
+    double* d_acc = nullptr;
+    DevScalars* d_scalars = nullptr;
+    DevScalars* h_scalars = nullptr;
+};
+std::mutex g_norm_mu;
+std::map<int, NormScratch> g_norm_scratch;
+}  // namespace
+
+int32_t oxz_grad_norm(const void* device_grads, int32_t dtype, uint64_t n, double loss_scale, double max_grad_value,
+                      void* stream, double* norm) {
+    if (!norm || (!device_grads && n)) return fail(OXZ_ERR_INVALID, "oxz_grad_norm: null argument");
+    if (dtype != OXZ_F32 && dtype != OXZ_BF16 && dtype != OXZ_F16) return fail(OXZ_ERR_INVALID, "oxz_grad_norm: dtype %d is none of f32, bf16, f16", dtype);
+    if ((uintptr_t)device_grads & 15) return fail(OXZ_ERR_INVALID, "oxz_grad_norm: the gradients are not 16-byte aligned");
+    if (!std::isnan(max_grad_value) && !(std::isfinite(max_grad_value) && max_grad_value > 0.0))
+        return fail(OXZ_ERR_INVALID, "trainer.max_grad_value is %g: it must be a finite positive number. Set a positive value, or remove the key to disable per-element clipping.", max_grad_value);
+    int dev = 0;
+    OXZ_CUDA(cudaGetDevice(&dev));
+    std::lock_guard<std::mutex> lock(g_norm_mu);
+    NormScratch& sc = g_norm_scratch[dev];
+    if (!sc.d_partials) {
+        LaunchGeom g;
+        OXZ_TRY(query_geom(dev, &g));
+        sc.blocks = g.norm_blocks;
+        sc.slots = norm_partial_slots(g);
+        OXZ_CUDA(cudaMalloc((void**)&sc.d_partials, (size_t)norm_partial_slots(g) * 3 * 8));
+        OXZ_CUDA(cudaMalloc((void**)&sc.d_acc, 3 * 8));
+        OXZ_CUDA(cudaMalloc((void**)&sc.d_scalars, sizeof(DevScalars)));
+        OXZ_CUDA(cudaMallocHost((void**)&sc.h_scalars, sizeof(DevScalars)));
+    }
+    cudaStream_t s = (cudaStream_t)stream;
+    const bool scaled = !std::isnan(loss_scale) && loss_scale != 0.0;
+    const int clamp_on = std::isnan(max_grad_value) ? 0 : 1;
+    OXZ_TRY(launch_sumsq_plain(s, sc.blocks, device_grads, dtype, n, scaled ? (float)(1.0 / loss_scale) : 1.0f,
+                               clamp_on ? (float)max_grad_value : 0.f, clamp_on, sc.d_partials));
+    OXZ_TRY(launch_reduce_partials(s, sc.d_partials, sc.slots, sc.d_acc));
+    FinalizeParams fp{};
+    fp.max_grad_norm = 1.7976931348623157e308;  // a pure measurement: nothing is rescaled
+    OXZ_TRY(launch_finalize(s, sc.d_acc, fp, sc.d_scalars));
+    OXZ_CUDA(cudaMemcpyAsync(sc.h_scalars, sc.d_scalars, sizeof(DevScalars), cudaMemcpyDeviceToHost, s));
+    OXZ_CUDA(cudaStreamSynchronize(s));
+    *norm = sc.h_scalars->norm;
+    return OXZ_OK;
+}
+
+}  // extern "C"

@@ -1,0 +1,574 @@
+"""Host-side mirror of the reference interface for the data-parallel optimizer step.
+
+Thin Python classes over the C ABI of liboxz_dpstep.so, named after what they replace in oxidizr
+(``LossScaler``, ``WeightDecaySpec``/``DecayPlan``, ``SpikeGuard``, ``LrPlan``, ``RowLayout``, the communicator,
+and the post-accumulation half of ``LitTrainer::step_once``). All arithmetic and every decision is made by the
+library; nothing here computes on the CPU in its place.
+"""
+from __future__ import annotations
+
+import ctypes as C
+import math
+from dataclasses import dataclass, field
+
+import numpy as np
+
+from . import _ffi as ffi
+from ._ffi import BF16, F16, F32, OxzError, check, lib
+
+NAN = float("nan")
+_NP = {F32: np.float32, BF16: np.uint16, F16: np.uint16}
+DTYPE_NAMES = {"f32": F32, "bf16": BF16, "f16": F16}
+
+
+# ------------------------------------------------------------------ communicator
+class Communicator:
+    """One rank's communicator (boostr ``Communicator`` as oxidizr uses it, src/dp/launch.rs:82-109)."""
+
+    def __init__(self, handle: int, owns: bool = True):
+        self._h = C.c_void_p(handle)
+        self._owns = owns
+
+    @staticmethod
+    def unique_id() -> bytes:
+        buf = (C.c_uint8 * 128)()
+        check(lib().oxz_comm_unique_id(buf))
+        return bytes(buf)
+
+    @classmethod
+    def init_rank(cls, device: int, rank: int, world: int, unique_id: bytes) -> "Communicator":
+        buf = (C.c_uint8 * 128).from_buffer_copy(unique_id)
+        out = C.c_void_p()
+        check(lib().oxz_comm_init_rank(device, rank, world, buf, C.byref(out)))
+        return cls(out.value)
+
+    @classmethod
+    def init_all(cls, devices: list[int]) -> list["Communicator"]:
+        n = len(devices)
+        out = (C.c_void_p * n)()
+        check(lib().oxz_comm_init_all(n, (C.c_int32 * n)(*devices), out))
+        return [cls(out[i]) for i in range(n)]
+
+    @property
+    def handle(self) -> C.c_void_p:
+        return self._h
+
+    def world_size(self) -> int:
+        v = C.c_int32()
+        check(lib().oxz_comm_world_size(self._h, C.byref(v)))
+        return v.value
+
+    def rank(self) -> int:
+        v = C.c_int32()
+        check(lib().oxz_comm_rank(self._h, C.byref(v)))
+        return v.value
+
+    def abort(self) -> None:
+        check(lib().oxz_comm_abort(self._h))
+
+    def barrier(self) -> None:
+        check(lib().oxz_barrier(self._h))
+
+    def sum_counts(self, scored: int, masks: int) -> tuple[int, int]:
+        """The I64[2] sum of reduce_step_weighting (src/dp/weighting.rs:63-101)."""
+        buf = (C.c_int64 * 2)(scored, masks)
+        check(lib().oxz_allreduce_i64x2(self._h, buf))
+        return buf[0], buf[1]
+
+    def sum_f64(self, values: list[float]) -> list[float]:
+        """Sum of a few host doubles over every rank (the logged loss, src/dp/reduce.rs:57-59). Blocking."""
+        n = len(values)
+        buf = (C.c_double * n)(*values)
+        check(lib().oxz_allreduce_f64(self._h, buf, n))
+        return [buf[i] for i in range(n)]
+
+    def broadcast(self, device_ptr: int, nbytes: int, root: int = 0) -> None:
+        check(lib().oxz_broadcast(self._h, C.c_void_p(device_ptr), nbytes, root))
+
+    def destroy(self) -> None:
+        if self._h and self._owns:
+            lib().oxz_comm_destroy(self._h)
+        self._h = C.c_void_p()
+
+
+# ------------------------------------------------------------------ loss scale
+@dataclass
+class LossScaleConfig:
+    """``trainer.loss_scale`` (src/loss_scale/config.rs:28-41)."""
+    initial: float = 65536.0
+    growth_factor: float = 2.0
+    backoff_factor: float = 0.5
+    growth_interval: int = 2000
+
+    def _c(self) -> ffi.ScalerConfig:
+        return ffi.ScalerConfig(self.initial, self.growth_factor, self.backoff_factor, self.growth_interval)
+
+    def check(self) -> None:
+        check(lib().oxz_scaler_check(C.byref(self._c())))
+
+
+@dataclass
+class GradScalerState:
+    scale: float
+    consecutive_ok: int = 0
+
+
+class LossScaler:
+    """The loss scaler of one run (src/loss_scale/scaler.rs:13-51)."""
+
+    def __init__(self, config: LossScaleConfig | None = None):
+        self.config = config or LossScaleConfig()
+        self._cfg = self.config._c()
+        self._st = ffi.ScalerState()
+        check(lib().oxz_scaler_init(C.byref(self._cfg), C.byref(self._st)))
+
+    def scale(self) -> float:
+        return self._st.scale
+
+    def state(self) -> GradScalerState:
+        return GradScalerState(self._st.scale, self._st.consecutive_ok)
+
+    def restore(self, state: GradScalerState) -> None:
+        saved = ffi.ScalerState(state.scale, state.consecutive_ok)
+        check(lib().oxz_scaler_restore(C.byref(saved), C.byref(self._st)))
+
+    def record_step(self, overflow: bool, spike_skip: bool = False) -> None:
+        check(lib().oxz_scaler_record_step(C.byref(self._cfg), C.byref(self._st), int(overflow), int(spike_skip)))
+
+
+# ------------------------------------------------------------------ weight decay
+_RULES = {"decay_all": ffi.DECAY_ALL, "skip_1d": ffi.SKIP_1D, "skip_all": ffi.SKIP_ALL}
+
+
+@dataclass
+class WeightDecaySpec:
+    """The resolved weight decay rule of one run (src/weight_decay/rule.rs:49-118)."""
+    rule: str = "skip_1d"
+    no_decay_patterns: list[str] = field(default_factory=list)
+
+    def _patterns(self):
+        n = len(self.no_decay_patterns)
+        return (C.c_char_p * max(n, 1))(*[p.encode() for p in self.no_decay_patterns]), n
+
+    def check(self) -> None:
+        arr, n = self._patterns()
+        check(lib().oxz_decay_check(_RULES[self.rule], arr, n))
+
+    def excludes(self, name: str, rank: int) -> bool:
+        arr, n = self._patterns()
+        out = C.c_int32()
+        check(lib().oxz_decay_excludes(_RULES[self.rule], arr, n, name.encode(), rank, C.byref(out)))
+        return bool(out.value)
+
+
+@dataclass
+class TensorInfo:
+    """One trainable tensor as the decay rule sees it (src/weight_decay/plan.rs:10-19)."""
+    name: str       # checkpoint name, ``model.``-prefixed
+    shape: tuple
+    id: int | None = None
+
+    @property
+    def elements(self) -> int:
+        return int(math.prod(self.shape))
+
+
+class DecayPlan:
+    """The no-decay set of one run (src/weight_decay/plan.rs:22-122). A repeated id counts once."""
+
+    def __init__(self, spec: WeightDecaySpec, tensors: list[TensorInfo]):
+        spec.check()
+        self.spec = spec
+        self.no_decay: list[bool] = []
+        self.decay_tensors = self.decay_elements = self.no_decay_elements = 0
+        self.tensors: list[TensorInfo] = []
+        seen = set()
+        for i, t in enumerate(tensors):
+            tid = t.id if t.id is not None else ("#", i)
+            if tid in seen:
+                continue
+            seen.add(tid)
+            self.tensors.append(t)
+            ex = spec.excludes(t.name, len(t.shape))
+            self.no_decay.append(ex)
+            if ex:
+                self.no_decay_elements += t.elements
+            else:
+                self.decay_tensors += 1
+                self.decay_elements += t.elements
+
+    def summary(self, weight_decay: float) -> str:
+        return (f"Weight decay {weight_decay} with rule {self.spec.rule}: {self.decay_tensors} tensors "
+                f"({self.decay_elements} params) decay, {sum(self.no_decay)} tensors "
+                f"({self.no_decay_elements} params) do not")
+
+
+# ------------------------------------------------------------------ spike guard
+@dataclass
+class SpikeGuardConfig:
+    """``trainer.spike_guard`` (src/metrics/config.rs:69-115)."""
+    window: int = 100
+    z_threshold: float = 6.0
+    min_steps: int = 50
+    action: str = "skip"
+
+
+class SpikeGuard:
+    """EMA loss-spike guard (src/metrics/spike.rs:72-168)."""
+
+    def __init__(self, config: SpikeGuardConfig):
+        self.config = config
+        self._cfg = ffi.SpikeConfig(config.window, config.z_threshold, config.min_steps, int(config.action == "warn"), 0)
+        self._st = ffi.SpikeState()
+        self.last_flagged = False
+        skip, flagged = C.c_int32(), C.c_int32()
+        probe = ffi.SpikeState()
+        check(lib().oxz_spike_judge(C.byref(self._cfg), C.byref(probe), 0, NAN, C.byref(skip), C.byref(flagged)))
+
+    def judge(self, index: int, loss: float) -> bool:
+        """True when the 0-based step ``index`` must skip the optimizer (src/metrics/state.rs:79-86)."""
+        skip, flagged = C.c_int32(), C.c_int32()
+        check(lib().oxz_spike_judge(C.byref(self._cfg), C.byref(self._st), index, loss, C.byref(skip), C.byref(flagged)))
+        self.last_flagged = bool(flagged.value)
+        return bool(skip.value)
+
+    @property
+    def state(self):
+        s = self._st
+        return dict(mean=s.mean, variance=s.variance, observed=s.observed, detected=s.detected, skipped=s.skipped)
+
+
+# ------------------------------------------------------------------ learning rate
+_SCHED = {"constant": ffi.LR_CONSTANT, "cosine": ffi.LR_COSINE, "linear": ffi.LR_LINEAR, "wsd": ffi.LR_WSD}
+_SHAPE = {"linear": ffi.SHAPE_LINEAR, "cosine": ffi.SHAPE_COSINE, "sqrt": ffi.SHAPE_SQRT}
+
+
+class LrPlan:
+    """Learning rate of every step of one run (src/schedule.rs:135-202)."""
+
+    def __init__(self, base_lr: float, schedule: str = "constant", warmup_steps: int = 0, total_steps: int = 0,
+                 min_lr_ratio: float = 0.0, decay_steps: int | None = None, decay_ratio: float | None = None,
+                 decay_shape: str = "linear"):
+        if schedule == "wsd" and decay_steps is None:
+            decay_steps = int(math.ceil(float(total_steps) * (0.1 if decay_ratio is None else decay_ratio)))
+        self._c = ffi.LrPlanC(base_lr, min_lr_ratio, warmup_steps, total_steps, decay_steps or 0, _SCHED[schedule],
+                              _SHAPE[decay_shape])
+        self.lr_at(0)
+
+    def lr_at(self, step: int) -> float:
+        out = C.c_double()
+        check(lib().oxz_lr_at(C.byref(self._c), step, C.byref(out)))
+        return out.value
+
+
+# ------------------------------------------------------------------ rows
+@dataclass(frozen=True)
+class DataPosition:
+    epoch: int = 0
+    row: int = 0
+
+
+class RowLayout:
+    """Row and batch counts of one loader's row range (src/data/rows.rs:53-208)."""
+
+    def __init__(self, num_rows: int, rank_batch_size: int, world_size: int = 1):
+        self._c = ffi.RowLayoutC(num_rows, rank_batch_size, world_size)
+        check(lib().oxz_rows_check(C.byref(self._c)))
+        self.num_rows, self.rank_batch_size, self.world_size = num_rows, rank_batch_size, world_size
+
+    def batch_size(self) -> int:
+        return self.rank_batch_size * self.world_size
+
+    def batches_per_epoch(self) -> int:
+        return self.num_rows // self.batch_size()
+
+    def total_steps(self, grad_accum: int, num_epochs: int) -> int:
+        return self.batches_per_epoch() * num_epochs // max(grad_accum, 1)
+
+    def advance(self, pos: DataPosition, batches: int) -> DataPosition:
+        out = ffi.DataPositionC()
+        check(lib().oxz_rows_advance(C.byref(self._c), ffi.DataPositionC(pos.epoch, pos.row), batches, C.byref(out)))
+        return DataPosition(out.epoch, out.row)
+
+    def position_after_steps(self, steps: int, grad_accum: int) -> DataPosition:
+        return self.advance(DataPosition(), steps * grad_accum)
+
+    def next_window(self, pos: DataPosition, rank: int, seq_len: int, tokens: np.ndarray | None = None,
+                    first_row: int = 0):
+        """One rank's rows of the next global batch in stream order: (rows, inputs, targets, next position)."""
+        B = self.rank_batch_size
+        rows = np.empty(B, dtype=np.uint64)
+        nxt = ffi.DataPositionC()
+        inputs = targets = None
+        tok_p, n_tok, in_p, tg_p = None, 0, None, None
+        if tokens is not None:
+            tokens = np.ascontiguousarray(tokens, dtype=np.uint32)
+            inputs = np.empty((B, seq_len), dtype=np.int64)
+            targets = np.empty((B, seq_len), dtype=np.int64)
+            tok_p = tokens.ctypes.data_as(C.POINTER(C.c_uint32))
+            n_tok = tokens.size
+            in_p, tg_p = inputs.ctypes.data_as(ffi.i64p), targets.ctypes.data_as(ffi.i64p)
+        check(lib().oxz_rows_next_window(C.byref(self._c), ffi.DataPositionC(pos.epoch, pos.row), rank, seq_len,
+                                         first_row, tok_p, n_tok, rows.ctypes.data_as(ffi.u64p), in_p, tg_p,
+                                         C.byref(nxt)))
+        return rows, inputs, targets, DataPosition(nxt.epoch, nxt.row)
+
+
+def step_weighting(local_micro_batches: int, world: int, scored: int, masked_ranks: int):
+    """StepWeighting::over_ranks on the summed counts (src/dp/weighting.rs:46-61): (micro_batches, scored or None)."""
+    mb, gs = C.c_uint64(), C.c_int64()
+    check(lib().oxz_step_weighting(local_micro_batches, world, (C.c_int64 * 2)(scored, masked_ranks), C.byref(mb),
+                                   C.byref(gs)))
+    return mb.value, (None if gs.value < 0 else gs.value)
+
+
+# ------------------------------------------------------------------ the optimizer step
+@dataclass
+class StepConfig:
+    """The trainer keys the step reads, with the reference's defaults (src/config.rs:40-62)."""
+    lr: float = 3e-4
+    beta1: float = 0.9
+    beta2: float = 0.95
+    eps: float = 1e-6
+    weight_decay: float = 0.1
+    max_grad_norm: float = 1.0
+    max_grad_value: float = NAN
+    target_grad_norm: float = NAN
+    loss_scale: float = NAN
+    clip_eps: float = 1e-6
+    decay_after: int = 0
+    eps_mode: int = 0
+    spike_skip: bool = False
+
+    def hyper(self) -> ffi.Hyper:
+        return ffi.Hyper(self.lr, self.beta1, self.beta2, self.eps, self.weight_decay, self.max_grad_norm,
+                         self.max_grad_value, self.target_grad_norm, self.loss_scale, self.clip_eps,
+                         self.decay_after, self.eps_mode, int(self.spike_skip), 0)
+
+
+class DpOptimizer:
+    """Flat-buffer AdamW state of one rank plus the fused step (replaces boostr FusedAdamW + the collectives).
+
+    ``numel`` keeps ``parameter_ids`` order. ``no_decay`` comes from :class:`DecayPlan`.
+    """
+
+    def __init__(self, numel: list[int], no_decay: list[bool] | None = None, grad_dtype: int = BF16,
+                 param_dtype: int = BF16, world: int = 1, rank: int = 0, sync_mode: int | None = None,
+                 device: int = 0, bucket_bytes: int = 0, lr_scale: list[float] | None = None,
+                 comm: Communicator | None = None, allocate: bool = True):
+        T = len(numel)
+        self.numel = [int(n) for n in numel]
+        self.grad_dtype, self.param_dtype, self.world, self.rank, self.device = grad_dtype, param_dtype, world, rank, device
+        if sync_mode is None:
+            sync_mode = ffi.SYNC_SINGLE if world == 1 else ffi.SYNC_P2P
+        self.sync_mode = sync_mode
+        self._numel = (C.c_uint64 * max(T, 1))(*self.numel)
+        self._nd = (C.c_uint8 * max(T, 1))(*[int(bool(x)) for x in (no_decay or [False] * T)])
+        self._ls = (C.c_float * max(T, 1))(*(lr_scale or [1.0] * T))
+        desc = ffi.PlanDesc(T, self._numel, self._nd, self._ls, grad_dtype, param_dtype, world, rank, sync_mode, device,
+                            bucket_bytes)
+        self._h = C.c_void_p()
+        check(lib().oxz_plan_create(C.byref(desc), C.byref(self._h)))
+        self.comm = comm
+        self.info = ffi.PlanInfo()
+        check(lib().oxz_plan_query(self._h, C.byref(self.info)))
+        off = (C.c_uint64 * max(T, 1))()
+        check(lib().oxz_plan_tensor_offsets(self._h, off))
+        self.offsets = [off[i] for i in range(T)]
+        self.allocated = False
+        if allocate:
+            self.alloc()
+
+    # -- layout
+    def bucket(self, b: int, rank: int | None = None):
+        vals = [C.c_uint64() for _ in range(4)]
+        check(lib().oxz_plan_bucket(self._h, b, self.rank if rank is None else rank, *[C.byref(v) for v in vals]))
+        return tuple(v.value for v in vals)
+
+    def local_index(self, flat_index: int, rank: int | None = None) -> int | None:
+        out = C.c_uint64()
+        check(lib().oxz_plan_local_index(self._h, self.rank if rank is None else rank, flat_index, C.byref(out)))
+        return None if out.value == 0xFFFFFFFFFFFFFFFF else out.value
+
+    # -- state
+    def alloc(self) -> None:
+        check(lib().oxz_state_alloc(self._h, self.comm.handle if self.comm else None))
+        self.allocated = True
+
+    def set_stream(self, stream: int | None) -> None:
+        check(lib().oxz_plan_set_stream(self._h, C.c_void_p(stream) if stream else None))
+
+    def pointers(self) -> dict:
+        """Device addresses of the flat buffers: grads, work, master, exp_avg, exp_avg_sq."""
+        ps = [C.c_void_p() for _ in range(5)]
+        check(lib().oxz_state_pointers(self._h, *[C.byref(p) for p in ps]))
+        return dict(zip(("grads", "work", "master", "exp_avg", "exp_avg_sq"), [p.value for p in ps]))
+
+    def _dtype_of(self, kind: int):
+        return _NP[self.grad_dtype] if kind == ffi.STATE_GRADS else _NP[self.param_dtype] if kind == ffi.STATE_WORK else np.float32
+
+    def import_tensor(self, kind: int, tensor: int, host: np.ndarray) -> None:
+        host = np.ascontiguousarray(host, dtype=self._dtype_of(kind)).reshape(-1)
+        if host.size != self.numel[tensor]:
+            raise ValueError(f"tensor {tensor} has {self.numel[tensor]} elements, got {host.size}")
+        if host.size:
+            check(lib().oxz_state_import(self._h, kind, tensor, host.ctypes.data))
+
+    def export_tensor(self, kind: int, tensor: int, out: np.ndarray | None = None) -> np.ndarray:
+        if out is None:
+            out = np.zeros(self.numel[tensor], dtype=self._dtype_of(kind))
+        if out.size:
+            check(lib().oxz_state_export(self._h, kind, tensor, out.ctypes.data))
+        return out
+
+    @property
+    def timestep(self) -> int:
+        """Applied optimizer steps (LitTrainer::optimizer_timestep, src/trainer.rs:906-908)."""
+        v = C.c_uint64()
+        check(lib().oxz_state_timestep(self._h, C.byref(v)))
+        return v.value
+
+    @timestep.setter
+    def timestep(self, t: int) -> None:
+        check(lib().oxz_state_set_timestep(self._h, t))
+
+    # -- gradients in
+    def flatten_grads(self, device_ptrs: list[int | None], accumulate: bool = False) -> None:
+        arr = (C.c_void_p * max(len(device_ptrs), 1))(*[C.c_void_p(p) if p else None for p in device_ptrs])
+        check(lib().oxz_grads_flatten_async(self._h, arr, int(accumulate)))
+
+    def upload_grads(self, tensor: int, host_ptr: int) -> None:
+        check(lib().oxz_grads_upload_async(self._h, tensor, C.c_void_p(host_ptr)))
+
+    # -- the step
+    def step_async(self, cfg: StepConfig, present: list[bool] | None = None, extras: list[float] | None = None) -> None:
+        h = cfg.hyper()
+        pres = (C.c_uint8 * max(len(present), 1))(*[int(bool(x)) for x in present]) if present is not None else None
+        n = len(extras) if extras else 0
+        self._extras = (C.c_double * max(n, 1))(*(extras or [0.0]))
+        self._n_extras = n
+        check(lib().oxz_step_async(self._h, self.comm.handle if self.comm else None, C.byref(h), pres, self._extras, n))
+
+    def step_wait(self) -> ffi.StepResult:
+        res = ffi.StepResult()
+        check(lib().oxz_step_wait(self._h, C.byref(res)))
+        self.last_extras = [self._extras[i] for i in range(self._n_extras)]
+        return res
+
+    def step(self, cfg: StepConfig, present: list[bool] | None = None, extras: list[float] | None = None) -> ffi.StepResult:
+        self.step_async(cfg, present, extras)
+        return self.step_wait()
+
+    def set_profile(self, on: bool) -> None:
+        """Per-phase CUDA-event timing of each step (the PROFILE_TRAIN switch, src/trainer.rs:262-263)."""
+        check(lib().oxz_plan_set_profile(self._h, int(on)))
+
+    def profile(self) -> ffi.StepProfile:
+        out = ffi.StepProfile()
+        check(lib().oxz_step_profile_read(self._h, C.byref(out)))
+        return out
+
+    def destroy(self) -> None:
+        if self._h:
+            lib().oxz_plan_destroy(self._h)
+            self._h = C.c_void_p()
+
+    def __del__(self):
+        try:
+            self.destroy()
+        except Exception:
+            pass
+
+
+def compute_grad_norm(device_ptr: int, dtype: int, n: int, loss_scale: float = NAN, max_grad_value: float = NAN,
+                      stream: int | None = None) -> float:
+    """Global L2 norm of device gradients as a pure measurement (compute_grad_norm(.., f64::MAX), src/grad_clip.rs:49)."""
+    out = C.c_double()
+    check(lib().oxz_grad_norm(C.c_void_p(device_ptr), dtype, n, loss_scale, max_grad_value,
+                              C.c_void_p(stream) if stream else None, C.byref(out)))
+    return out.value
+
+
+# ------------------------------------------------------------------ the trainer's half of the step
+@dataclass
+class TrainerConfig:
+    """The optimizer keys of oxidizr's TrainerConfig (src/config.rs:40-62, 641-727)."""
+    learning_rate: float = 3e-4
+    adamw_beta1: float = 0.9
+    adamw_beta2: float = 0.95
+    adamw_eps: float = 1e-6
+    weight_decay: float = 0.1
+    max_grad_norm: float = 1.0
+    target_grad_norm: float | None = None
+    max_grad_value: float | None = None
+    loss_scale: LossScaleConfig | None = None   # f16 runs only (src/loss_scale/config.rs:103-128)
+    spike_guard: SpikeGuardConfig | None = None
+    lr_schedule: str = "constant"
+    warmup_steps: int = 0
+    total_steps: int = 0
+    min_lr_ratio: float = 0.0
+
+
+class LitTrainerStep:
+    """The post-accumulation half of LitTrainer::step_once (src/trainer.rs:515-695) over a :class:`DpOptimizer`.
+
+    ``training_step(local_loss)`` expects this rank's summed micro-batch gradients in the optimizer's flat gradient
+    buffer and returns ``(loss, grad_norm)`` exactly as the reference does.
+    """
+
+    def __init__(self, config: TrainerConfig, optimizer: DpOptimizer, start_step: int = 0):
+        self.config = config
+        self.optimizer = optimizer
+        self.global_step = start_step
+        self.lr_plan = LrPlan(config.learning_rate, config.lr_schedule, config.warmup_steps, config.total_steps,
+                              config.min_lr_ratio)
+        self.loss_scaler = LossScaler(config.loss_scale) if config.loss_scale is not None else None
+        self.spike_guard = SpikeGuard(config.spike_guard) if config.spike_guard is not None else None
+        self.loss_probe = None  # (index, loss) -> loss, the fault-injection hook of src/metrics/state.rs:10-14
+        self.last_loss = None
+        self.prev_grad_norm = None
+
+    def optimizer_timestep(self) -> int:
+        return self.optimizer.timestep
+
+    def loss_scale_state(self) -> GradScalerState | None:
+        return self.loss_scaler.state() if self.loss_scaler else None
+
+    def training_step(self, local_loss: float, present: list[bool] | None = None) -> tuple[float, float]:
+        opt = self.optimizer
+        judged = self.spike_guard is not None or self.loss_probe is not None
+        if opt.world > 1 and judged:
+            # The guard judges the loss summed over ranks, so every rank decides alike (src/trainer.rs:611-612).
+            # Its verdict must be known before the update is enqueued: one blocking 8-byte sum, as the reference's
+            # step-weighting collective is (src/dp/weighting.rs:63-101).
+            loss = opt.comm.sum_f64([local_loss])[0]
+            extras = None
+        elif opt.world > 1:
+            loss, extras = None, [local_loss]  # the loss rides on the norm all-reduce
+        else:
+            loss, extras = local_loss, None
+        spike_skip = False
+        if judged:
+            if self.loss_probe is not None:
+                loss = self.loss_probe(self.global_step, loss)
+            if self.spike_guard is not None:
+                spike_skip = self.spike_guard.judge(self.global_step, loss)
+        res = opt.step(self._cfg(spike_skip), present, extras)
+        if loss is None:
+            loss = opt.last_extras[0]
+        overflow = bool(res.overflow)
+        if self.loss_scaler is not None:
+            self.loss_scaler.record_step(overflow, spike_skip)
+        self.prev_grad_norm = res.reported_norm
+        self.global_step += 1
+        self.last_loss = loss
+        return loss, res.reported_norm
+
+    def _cfg(self, spike_skip: bool) -> StepConfig:
+        c = self.config
+        return StepConfig(
+            lr=self.lr_plan.lr_at(self.global_step), beta1=c.adamw_beta1, beta2=c.adamw_beta2, eps=c.adamw_eps,
+            weight_decay=c.weight_decay, max_grad_norm=c.max_grad_norm,
+            max_grad_value=NAN if c.max_grad_value is None else c.max_grad_value,
+            target_grad_norm=NAN if c.target_grad_norm is None else c.target_grad_norm,
+            loss_scale=self.loss_scaler.scale() if self.loss_scaler else NAN, spike_skip=spike_skip)
