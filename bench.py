@@ -46,53 +46,45 @@ def measured_peaks():
 
 
 class ClockSampler:
-    """Samples SM clocks and throttle reasons of one GPU with nvidia-smi while the timed region runs."""
+    """Samples the SM clock and the throttle reasons of one GPU through NVML while the timed region runs.
+    Read-only: it queries, it never sets anything."""
 
-    FIELDS = ("clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.hw_slowdown,"
-              "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
-              "clocks_event_reasons.sw_power_cap")
+    REASONS = {"hw_slowdown": 0x8, "hw_thermal_slowdown": 0x40, "sw_thermal_slowdown": 0x20, "sw_power_cap": 0x4}
 
     def __init__(self, index: int):
-        self.index, self.proc, self.lines = index, None, []
+        self.index, self.sm, self.bits, self.stop_flag, self.thread, self.max_mhz = index, [], 0, False, None, None
+        try:
+            import pynvml
+            pynvml.nvmlInit()
+            self.nv = pynvml
+            self.h = pynvml.nvmlDeviceGetHandleByIndex(index)
+            self.max_mhz = float(pynvml.nvmlDeviceGetMaxClockInfo(self.h, pynvml.NVML_CLOCK_SM))
+        except Exception:  # noqa: BLE001
+            self.nv = None
+
+    def _loop(self):
+        nv = self.nv
+        while not self.stop_flag:
+            try:
+                self.sm.append(float(nv.nvmlDeviceGetClockInfo(self.h, nv.NVML_CLOCK_SM)))
+                self.bits |= int(nv.nvmlDeviceGetCurrentClocksEventReasons(self.h))
+            except Exception:  # noqa: BLE001
+                pass
+            time.sleep(0.002)
 
     def start(self):
-        try:
-            self.proc = subprocess.Popen(["nvidia-smi", "-i", str(self.index), f"--query-gpu={self.FIELDS}",
-                                          "--format=csv,noheader,nounits", "-lms", "100"],
-                                         stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
-            self.thread = threading.Thread(target=self._read, daemon=True)
+        if self.nv is not None:
+            self.thread = threading.Thread(target=self._loop, daemon=True)
             self.thread.start()
-        except OSError:
-            self.proc = None
-
-    def _read(self):
-        for line in self.proc.stdout:
-            self.lines.append(line.strip())
 
     def stop(self) -> dict:
-        if self.proc is None:
-            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
-        self.proc.terminate()
-        try:
-            self.proc.wait(timeout=5)
-        except subprocess.TimeoutExpired:
-            self.proc.kill()
-        sm, mx, reasons = [], [], set()
-        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
-        for line in self.lines:
-            parts = [p.strip() for p in line.split(",")]
-            if len(parts) < 7:
-                continue
-            try:
-                sm.append(float(parts[0]))
-                mx.append(float(parts[1]))
-            except ValueError:
-                continue
-            for name, val in zip(names, parts[3:7]):
-                if val.lower().startswith("active"):
-                    reasons.add(name)
-        return {"sm_mhz": statistics.median(sm) if sm else None, "sm_max_mhz": max(mx) if mx else None,
-                "samples": len(sm), "reasons": sorted(reasons)}
+        if self.nv is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "samples": 0, "reasons": ["nvml unavailable"]}
+        self.stop_flag = True
+        self.thread.join(2.0)
+        reasons = sorted(k for k, b in self.REASONS.items() if self.bits & b)
+        return {"sm_mhz": statistics.median(self.sm) if self.sm else None, "sm_max_mhz": self.max_mhz,
+                "samples": len(self.sm), "reasons": reasons}
 
 
 def device_view(ptr: int, nbytes: int, dtype):
@@ -189,7 +181,7 @@ def run_gpu(args):
         dist.broadcast_object_list(uid, src=0)
         comm = ox.Communicator.init_rank(local_rank, rank, world, uid[0])
 
-    tensors = inventory.llama_3_2_1b()
+    tensors = inventory.PARAM_SETS[args.workload]()
     plan = ox.DecayPlan(ox.WeightDecaySpec("skip_1d"), tensors)
     numel = [t.elements for t in tensors]
     P = sum(numel)
@@ -262,24 +254,28 @@ def run_gpu(args):
     value = P * args.steps / sec
 
     # end to end: every step copies that step's gradients from pinned host memory, then reads the result back
-    host = torch.empty(P, dtype=torch.bfloat16).pin_memory()
-    pos = 0
-    host_off = []
-    for off, n in zip(opt.offsets, numel):
-        host[pos:pos + n].copy_(grads[off:off + n])
-        host_off.append(pos)
-        pos += n
-    torch.cuda.synchronize()
-    base = host.data_ptr()
+    host_off, base = [], 0
+    if not args.skip_e2e:
+        host = torch.empty(P, dtype=torch.bfloat16).pin_memory()
+        pos = 0
+        for off, n in zip(opt.offsets, numel):
+            host[pos:pos + n].copy_(grads[off:off + n])
+            host_off.append(pos)
+            pos += n
+        torch.cuda.synchronize()
+        base = host.data_ptr()
 
     def upload():
         for i, n in enumerate(numel):
             opt.upload_grads(i, base + host_off[i] * 2)
 
     e2e_steps = max(2, min(args.steps, 5))
-    timed(1, upload)
-    e2e_sec, _, _ = timed(e2e_steps, upload)
-    e2e_value = P * e2e_steps / e2e_sec
+    if args.skip_e2e:
+        e2e_sec, e2e_value = float("nan"), None
+    else:
+        timed(1, upload)
+        e2e_sec, _, _ = timed(e2e_steps, upload)
+        e2e_value = P * e2e_steps / e2e_sec
 
     peak, peak_kind = measured_peaks()
     upd = statistics.mean(p.update_ms for p in profs)
@@ -290,7 +286,7 @@ def run_gpu(args):
         "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps, "warmup": max(args.warmup, 3),
         "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
         "dtype": "f32", "data": "synthetic",
-        "config": {"workload": WORKLOAD, "params": P, "tensors": len(numel), "grad_dtype": "bf16", "param_dtype": "bf16",
+        "config": {"workload": args.workload, "params": P, "tensors": len(numel), "grad_dtype": "bf16", "param_dtype": "bf16",
                    "world": world, "sync": args.sync if world > 1 else "single",
                    "l2": "inputs larger than L2: 30 B/param x %d params per rank per step" % int(local_params),
                    "hyper": HYPER},
@@ -344,6 +340,8 @@ def main():
     ap.add_argument("--impl", choices=["ours", "reference"], default="ours")
     ap.add_argument("--sync", choices=["p2p", "nccl"], default="p2p", help="how ranks meet at --gpus > 1")
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--skip-e2e", action="store_true", help="profiling runs: leave the host-fed leg out")
+    ap.add_argument("--workload", default=WORKLOAD, help="parameter set; the headline is llama-3.2-1b, smaller sets serve profiler captures")
     args = ap.parse_args()
     if args.impl == "reference":
         run_reference(args)

@@ -37,7 +37,8 @@ typedef enum oxz_status {
     OXZ_ERR_STATE = 4,       /* call order: state not allocated, a step still in flight, ... */
     OXZ_ERR_ABORTED = 5,     /* the communicator was aborted (src/dp/launch.rs:97-103) */
     OXZ_ERR_UNSUPPORTED = 6, /* NCCL library or peer access unavailable */
-    OXZ_ERR_DATA = 7         /* mirrors Error::DataError of the row arithmetic */
+    OXZ_ERR_DATA = 7,        /* mirrors Error::DataError of the row arithmetic */
+    OXZ_ERR_TIMEOUT = 8      /* a rank never joined a collective of a local group within its timeout */
 } oxz_status;
 
 typedef enum oxz_dtype { OXZ_F32 = 0, OXZ_BF16 = 1, OXZ_F16 = 2 } oxz_dtype;
@@ -67,6 +68,11 @@ int32_t oxz_comm_unique_id(uint8_t id[128]);
 int32_t oxz_comm_init_rank(int32_t device, int32_t rank, int32_t world, const uint8_t id[128], oxz_comm** out);
 /* All communicators of a single-process group at once, as from_streams does (src/dp/launch.rs:82-95). */
 int32_t oxz_comm_init_all(int32_t n, const int32_t* devices, oxz_comm** out);
+/* An in-process group of n rank threads that meet on the host, with a collective timeout and abort: the counterpart
+ * of boostr's LocalCommunicator::with_timeout (src/dp/launch.rs:52-71, tests/data_parallel.rs:158-185). Ranks may
+ * share one GPU (devices[i] equal) or use none (devices NULL or -1: host collectives only). Device collectives
+ * drain the stream and go through host memory; it serves OXZ_SYNC_P2P plans, not OXZ_SYNC_NCCL ones. */
+int32_t oxz_comm_init_local(int32_t n, const int32_t* devices, double timeout_seconds, oxz_comm** out);
 int32_t oxz_comm_world_size(const oxz_comm* comm, int32_t* world);
 int32_t oxz_comm_rank(const oxz_comm* comm, int32_t* rank);
 /* Ends every pending and future collective of this rank with an error; callable from any thread. */

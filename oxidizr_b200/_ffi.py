@@ -11,7 +11,7 @@ import os
 _HERE = os.path.dirname(os.path.abspath(__file__))
 LIB_PATH = os.path.join(_HERE, "liboxz_dpstep.so")
 
-OK, ERR_INVALID, ERR_CUDA, ERR_NCCL, ERR_STATE, ERR_ABORTED, ERR_UNSUPPORTED, ERR_DATA = range(8)
+OK, ERR_INVALID, ERR_CUDA, ERR_NCCL, ERR_STATE, ERR_ABORTED, ERR_UNSUPPORTED, ERR_DATA, ERR_TIMEOUT = range(9)
 F32, BF16, F16 = 0, 1, 2
 SYNC_SINGLE, SYNC_P2P, SYNC_NCCL = 0, 1, 2
 STATE_MASTER, STATE_EXP_AVG, STATE_EXP_AVG_SQ, STATE_WORK, STATE_GRADS = range(5)
@@ -90,6 +90,7 @@ SIGNATURES = {
     "oxz_comm_unique_id": (C.c_int32, [u8p]),
     "oxz_comm_init_rank": (C.c_int32, [C.c_int32, C.c_int32, C.c_int32, u8p, C.POINTER(vp)]),
     "oxz_comm_init_all": (C.c_int32, [C.c_int32, C.POINTER(C.c_int32), C.POINTER(vp)]),
+    "oxz_comm_init_local": (C.c_int32, [C.c_int32, C.POINTER(C.c_int32), C.c_double, C.POINTER(vp)]),
     "oxz_comm_world_size": (C.c_int32, [vp, C.POINTER(C.c_int32)]),
     "oxz_comm_rank": (C.c_int32, [vp, C.POINTER(C.c_int32)]),
     "oxz_comm_abort": (C.c_int32, [vp]),

@@ -5,6 +5,7 @@
 #include <stdint.h>
 
 #include <atomic>
+#include <memory>
 #include <string>
 #include <vector>
 
@@ -91,16 +92,16 @@ uint32_t norm_partial_slots(const LaunchGeom& g);
 
 // Sum of squares of unscaled (and optionally clamped) gradients held in one local array of dtype `dt`.
 int32_t launch_sumsq(cudaStream_t s, const LaunchGeom& g, const void* grads, int32_t dt, const TileMap& map,
-                     const uint32_t* tile_meta, const uint8_t* present, float inv_scale, float clamp_hi,
-                     int32_t clamp_on, double* partials);
+                     const uint32_t* tile_meta, const uint8_t* present, bool check_present, float inv_scale,
+                     float clamp_hi, int32_t clamp_on, double* partials);
 // Same over a plain array of n elements (no plan): the standalone norm entry point.
 int32_t launch_sumsq_plain(cudaStream_t s, int blocks, const void* grads, int32_t dt, uint64_t n, float inv_scale,
                            float clamp_hi, int32_t clamp_on, double* partials);
 // Pull-reduce: sums this rank's tiles of every peer's gradient buffer in f32 in rank order, stores the sum
 // in `reduced` (local, f32) and accumulates the squares as launch_sumsq does.
 int32_t launch_pull_sumsq(cudaStream_t s, const LaunchGeom& g, const PeerTable& peers, int32_t world, int32_t dt,
-                          const TileMap& map, const uint32_t* tile_meta, const uint8_t* present, float inv_scale,
-                          float clamp_hi, int32_t clamp_on, float* reduced, double* partials);
+                          const TileMap& map, const uint32_t* tile_meta, const uint8_t* present, bool check_present,
+                          float inv_scale, float clamp_hi, int32_t clamp_on, float* reduced, double* partials);
 // partials[slots][3] -> acc[3] = {sum, inf count, nan count}
 int32_t launch_reduce_partials(cudaStream_t s, const double* partials, uint32_t slots, double* acc);
 // acc[3] -> scalars (norm, clip coefficients, decisions)
@@ -109,7 +110,7 @@ int32_t launch_finalize(cudaStream_t s, const double* acc, const FinalizeParams&
 // to every pointer of `peers.work[0..n_work)` (n_work 0: no working copy).
 int32_t launch_adamw(cudaStream_t s, const LaunchGeom& g, const void* gsrc, int32_t gdt, float* master, float* m,
                      float* v, const PeerTable& peers, int32_t n_work, int32_t pdt, const TileMap& map,
-                     const uint32_t* tile_meta, const uint8_t* present, const DevScalars* scalars,
+                     const uint32_t* tile_meta, const uint8_t* present, bool check_present, const DevScalars* scalars,
                      const AdamParams& ap);
 // Packs per-tensor gradients into the flat buffer.
 int32_t launch_flatten(cudaStream_t s, const LaunchGeom& g, void* flat, int32_t dt, uint32_t n_tiles,
@@ -118,8 +119,15 @@ int32_t launch_flatten(cudaStream_t s, const LaunchGeom& g, void* flat, int32_t 
 
 }  // namespace oxz
 
+namespace oxz {
+// In-process rendezvous of a local group: the counterpart of boostr's LocalCommunicator (src/dp/launch.rs:52-71).
+struct LocalGroup;
+}  // namespace oxz
+
 // ---- opaque handles ----
 struct oxz_comm {
+    int32_t kind = 0;      // 0 = NCCL, 1 = local (in-process threads, host rendezvous with timeout and abort)
+    std::shared_ptr<oxz::LocalGroup> local;
     void* nccl = nullptr;  // ncclComm_t
     int32_t rank = 0, world = 1, device = 0;
     cudaStream_t stream = nullptr;  // for the small blocking collectives
@@ -157,6 +165,7 @@ struct oxz_plan {
     // pinned host mirrors
     oxz::DevScalars* h_scalars = nullptr;
     double* h_acc = nullptr;
+    double* h_extras = nullptr;
     uint8_t* h_present = nullptr;
     const void** h_src = nullptr;
     cudaEvent_t done = nullptr;

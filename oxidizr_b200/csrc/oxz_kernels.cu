@@ -189,7 +189,10 @@ __device__ __forceinline__ void cluster_reduce_store(NormAcc a, double* partials
     }
 }
 
-template <int DT, int ILP>
+// CHECK = false is the common step: every tensor has a gradient. Padding holds zeros, so no tile needs its
+// metadata and the pass is a pure stream. CHECK = true looks up each tile's tensor to leave absent ones out.
+// All loads of an iteration are issued before anything depends on them.
+template <int DT, int ILP, bool CHECK>
 __global__ void __cluster_dims__(CLUSTER, 1, 1) __launch_bounds__(THREADS)
     k_sumsq(const void* __restrict__ grads, TileMap map, const uint32_t* __restrict__ tile_meta,
             const uint8_t* __restrict__ present, float inv_scale, float clamp_hi, int clamp_on,
@@ -200,15 +203,20 @@ __global__ void __cluster_dims__(CLUSTER, 1, 1) __launch_bounds__(THREADS)
     for (uint32_t base = (blockIdx.x * WARPS + warp) * ILP; base < map.n_local_tiles; base += per_iter) {
         float g[ILP][8];
         bool on[ILP];
+        uint32_t meta[ILP];
 #pragma unroll
         for (int j = 0; j < ILP; j++) {
             const uint32_t lt = base + j;
-            on[j] = false;
-            if (lt < map.n_local_tiles) {
-                const uint32_t meta = tile_meta[flat_tile(map, lt)];
-                on[j] = meta != PAD_TILE && present[meta & 0xffffffu];
-                if (on[j]) load8<DT>(grads, static_cast<uint64_t>(lt) * TILE + lane * 8, g[j]);
+            on[j] = lt < map.n_local_tiles;
+            if (on[j]) {
+                load8<DT>(grads, static_cast<uint64_t>(lt) * TILE + lane * 8, g[j]);
+                if constexpr (CHECK) meta[j] = tile_meta[flat_tile(map, lt)];
             }
+        }
+        if constexpr (CHECK) {
+#pragma unroll
+            for (int j = 0; j < ILP; j++)
+                if (on[j]) on[j] = meta[j] != PAD_TILE && present[meta[j] & 0xffffffu];
         }
 #pragma unroll
         for (int j = 0; j < ILP; j++)
@@ -248,7 +256,7 @@ __global__ void __cluster_dims__(CLUSTER, 1, 1) __launch_bounds__(THREADS)
     cluster_reduce_store(a, partials);
 }
 
-template <int DT>
+template <int DT, bool CHECK>
 __global__ void __cluster_dims__(CLUSTER, 1, 1) __launch_bounds__(THREADS)
     k_pull_sumsq(PeerTable peers, int world, TileMap map, const uint32_t* __restrict__ tile_meta,
                  const uint8_t* __restrict__ present, float inv_scale, float clamp_hi, int clamp_on,
@@ -258,25 +266,31 @@ __global__ void __cluster_dims__(CLUSTER, 1, 1) __launch_bounds__(THREADS)
     const uint32_t per_iter = gridDim.x * WARPS;
     for (uint32_t lt = blockIdx.x * WARPS + warp; lt < map.n_local_tiles; lt += per_iter) {
         const uint32_t ft = flat_tile(map, lt);
-        const uint32_t meta = tile_meta[ft];
-        if (meta == PAD_TILE || !present[meta & 0xffffffu]) continue;
+        uint32_t meta = 0;
+        if constexpr (CHECK) meta = tile_meta[ft];
         const uint64_t fe = static_cast<uint64_t>(ft) * TILE + lane * 8;
         float s[8];
         load8<DT>(peers.grads[0], fe, s);
-        // Two peers in flight at a time keeps NVLink busy without a register array indexed by rank.
+        // Up to four peers in flight at a time keeps NVLink busy; the additions stay in rank order.
         int r = 1;
-        for (; r + 1 < world; r += 2) {
-            float p0[8], p1[8];
+        for (; r + 3 < world; r += 4) {
+            float p0[8], p1[8], p2[8], p3[8];
             load8<DT>(peers.grads[r], fe, p0);
             load8<DT>(peers.grads[r + 1], fe, p1);
+            load8<DT>(peers.grads[r + 2], fe, p2);
+            load8<DT>(peers.grads[r + 3], fe, p3);
 #pragma unroll
-            for (int i = 0; i < 8; i++) s[i] = __fadd_rn(__fadd_rn(s[i], p0[i]), p1[i]);
+            for (int i = 0; i < 8; i++)
+                s[i] = __fadd_rn(__fadd_rn(__fadd_rn(__fadd_rn(s[i], p0[i]), p1[i]), p2[i]), p3[i]);
         }
-        if (r < world) {
+        for (; r < world; r++) {
             float p0[8];
             load8<DT>(peers.grads[r], fe, p0);
 #pragma unroll
             for (int i = 0; i < 8; i++) s[i] = __fadd_rn(s[i], p0[i]);
+        }
+        if constexpr (CHECK) {
+            if (meta == PAD_TILE || !present[meta & 0xffffffu]) continue;
         }
         store8<OXZ_F32>(reduced, static_cast<uint64_t>(lt) * TILE + lane * 8, s);
         acc8(s, inv_scale, clamp_hi, clamp_on != 0, a);
@@ -342,7 +356,7 @@ __device__ __forceinline__ void adam1(float& p, float& m, float& v, float g, con
     if (k.decay_after) p = __fmul_rn(p, decay);
 }
 
-template <int GDT, int PDT, int ILP>
+template <int GDT, int PDT, int ILP, bool CHECK>
 __global__ void __launch_bounds__(THREADS)
     k_adamw(const void* __restrict__ gsrc, float* __restrict__ master, float* __restrict__ exp_avg,
             float* __restrict__ exp_avg_sq, PeerTable peers, int n_work, TileMap map,
@@ -356,29 +370,30 @@ __global__ void __launch_bounds__(THREADS)
     for (uint32_t base = (blockIdx.x * WARPS + warp) * ILP; base < map.n_local_tiles; base += per_iter) {
         float g[ILP][8], p[ILP][8], m[ILP][8], v[ILP][8];
         bool on[ILP];
-        uint32_t ftile[ILP], grp[ILP];
+        uint32_t ftile[ILP], meta[ILP];
+        // every load of the iteration is issued here, none depends on another
 #pragma unroll
         for (int j = 0; j < ILP; j++) {
             const uint32_t lt = base + j;
-            on[j] = false;
-            if (lt < map.n_local_tiles) {
+            on[j] = lt < map.n_local_tiles;
+            if (on[j]) {
+                const uint64_t le = static_cast<uint64_t>(lt) * TILE + lane * 8;
+                load8<GDT>(gsrc, le, g[j]);
+                load8<OXZ_F32>(master, le, p[j]);
+                load8<OXZ_F32>(exp_avg, le, m[j]);
+                load8<OXZ_F32>(exp_avg_sq, le, v[j]);
                 ftile[j] = flat_tile(map, lt);
-                const uint32_t meta = tile_meta[ftile[j]];
-                grp[j] = meta >> 24;
-                on[j] = meta != PAD_TILE && present[meta & 0xffffffu];
-                if (on[j]) {
-                    const uint64_t le = static_cast<uint64_t>(lt) * TILE + lane * 8;
-                    load8<GDT>(gsrc, le, g[j]);
-                    load8<OXZ_F32>(master, le, p[j]);
-                    load8<OXZ_F32>(exp_avg, le, m[j]);
-                    load8<OXZ_F32>(exp_avg_sq, le, v[j]);
-                }
+                meta[j] = tile_meta[ftile[j]];
             }
         }
 #pragma unroll
         for (int j = 0; j < ILP; j++) {
-            if (!on[j]) continue;
-            const float step = k.step_size[grp[j]], decay = k.decay_mul[grp[j]];
+            if (!on[j] || meta[j] == PAD_TILE) continue;
+            if constexpr (CHECK) {
+                if (!present[meta[j] & 0xffffffu]) continue;
+            }
+            const uint32_t grp = meta[j] >> 24;
+            const float step = k.step_size[grp], decay = k.decay_mul[grp];
 #pragma unroll
             for (int i = 0; i < 8; i++) {
                 float x = __fmul_rn(g[j][i], k.inv_scale);
@@ -467,18 +482,26 @@ static int32_t check_launch(const char* what) {
     return OXZ_OK;
 }
 
-int32_t launch_sumsq(cudaStream_t s, const LaunchGeom& g, const void* grads, int32_t dt, const TileMap& map,
-                     const uint32_t* tile_meta, const uint8_t* present, float inv_scale, float clamp_hi,
-                     int32_t clamp_on, double* partials) {
+template <bool CHECK>
+static int32_t launch_sumsq_c(cudaStream_t s, const LaunchGeom& g, const void* grads, int32_t dt, const TileMap& map,
+                              const uint32_t* tile_meta, const uint8_t* present, float inv_scale, float clamp_hi,
+                              int32_t clamp_on, double* partials) {
     constexpr int ILP = 4;
     dim3 grid(g.norm_blocks), block(THREADS);
     switch (dt) {
-        case OXZ_F32: k_sumsq<OXZ_F32, ILP><<<grid, block, 0, s>>>(grads, map, tile_meta, present, inv_scale, clamp_hi, clamp_on, partials); break;
-        case OXZ_BF16: k_sumsq<OXZ_BF16, ILP><<<grid, block, 0, s>>>(grads, map, tile_meta, present, inv_scale, clamp_hi, clamp_on, partials); break;
-        case OXZ_F16: k_sumsq<OXZ_F16, ILP><<<grid, block, 0, s>>>(grads, map, tile_meta, present, inv_scale, clamp_hi, clamp_on, partials); break;
+        case OXZ_F32: k_sumsq<OXZ_F32, ILP, CHECK><<<grid, block, 0, s>>>(grads, map, tile_meta, present, inv_scale, clamp_hi, clamp_on, partials); break;
+        case OXZ_BF16: k_sumsq<OXZ_BF16, ILP, CHECK><<<grid, block, 0, s>>>(grads, map, tile_meta, present, inv_scale, clamp_hi, clamp_on, partials); break;
+        case OXZ_F16: k_sumsq<OXZ_F16, ILP, CHECK><<<grid, block, 0, s>>>(grads, map, tile_meta, present, inv_scale, clamp_hi, clamp_on, partials); break;
         default: return fail(OXZ_ERR_INVALID, "unknown gradient dtype %d", dt);
     }
     return check_launch("k_sumsq");
+}
+
+int32_t launch_sumsq(cudaStream_t s, const LaunchGeom& g, const void* grads, int32_t dt, const TileMap& map,
+                     const uint32_t* tile_meta, const uint8_t* present, bool check_present, float inv_scale,
+                     float clamp_hi, int32_t clamp_on, double* partials) {
+    return check_present ? launch_sumsq_c<true>(s, g, grads, dt, map, tile_meta, present, inv_scale, clamp_hi, clamp_on, partials)
+                         : launch_sumsq_c<false>(s, g, grads, dt, map, tile_meta, present, inv_scale, clamp_hi, clamp_on, partials);
 }
 
 int32_t launch_sumsq_plain(cudaStream_t s, int blocks, const void* grads, int32_t dt, uint64_t n, float inv_scale,
@@ -493,17 +516,25 @@ int32_t launch_sumsq_plain(cudaStream_t s, int blocks, const void* grads, int32_
     return check_launch("k_sumsq_plain");
 }
 
-int32_t launch_pull_sumsq(cudaStream_t s, const LaunchGeom& g, const PeerTable& peers, int32_t world, int32_t dt,
-                          const TileMap& map, const uint32_t* tile_meta, const uint8_t* present, float inv_scale,
-                          float clamp_hi, int32_t clamp_on, float* reduced, double* partials) {
+template <bool CHECK>
+static int32_t launch_pull_c(cudaStream_t s, const LaunchGeom& g, const PeerTable& peers, int32_t world, int32_t dt,
+                             const TileMap& map, const uint32_t* tile_meta, const uint8_t* present, float inv_scale,
+                             float clamp_hi, int32_t clamp_on, float* reduced, double* partials) {
     dim3 grid(g.norm_blocks), block(THREADS);
     switch (dt) {
-        case OXZ_F32: k_pull_sumsq<OXZ_F32><<<grid, block, 0, s>>>(peers, world, map, tile_meta, present, inv_scale, clamp_hi, clamp_on, reduced, partials); break;
-        case OXZ_BF16: k_pull_sumsq<OXZ_BF16><<<grid, block, 0, s>>>(peers, world, map, tile_meta, present, inv_scale, clamp_hi, clamp_on, reduced, partials); break;
-        case OXZ_F16: k_pull_sumsq<OXZ_F16><<<grid, block, 0, s>>>(peers, world, map, tile_meta, present, inv_scale, clamp_hi, clamp_on, reduced, partials); break;
+        case OXZ_F32: k_pull_sumsq<OXZ_F32, CHECK><<<grid, block, 0, s>>>(peers, world, map, tile_meta, present, inv_scale, clamp_hi, clamp_on, reduced, partials); break;
+        case OXZ_BF16: k_pull_sumsq<OXZ_BF16, CHECK><<<grid, block, 0, s>>>(peers, world, map, tile_meta, present, inv_scale, clamp_hi, clamp_on, reduced, partials); break;
+        case OXZ_F16: k_pull_sumsq<OXZ_F16, CHECK><<<grid, block, 0, s>>>(peers, world, map, tile_meta, present, inv_scale, clamp_hi, clamp_on, reduced, partials); break;
         default: return fail(OXZ_ERR_INVALID, "unknown gradient dtype %d", dt);
     }
     return check_launch("k_pull_sumsq");
+}
+
+int32_t launch_pull_sumsq(cudaStream_t s, const LaunchGeom& g, const PeerTable& peers, int32_t world, int32_t dt,
+                          const TileMap& map, const uint32_t* tile_meta, const uint8_t* present, bool check_present,
+                          float inv_scale, float clamp_hi, int32_t clamp_on, float* reduced, double* partials) {
+    return check_present ? launch_pull_c<true>(s, g, peers, world, dt, map, tile_meta, present, inv_scale, clamp_hi, clamp_on, reduced, partials)
+                         : launch_pull_c<false>(s, g, peers, world, dt, map, tile_meta, present, inv_scale, clamp_hi, clamp_on, reduced, partials);
 }
 
 int32_t launch_reduce_partials(cudaStream_t s, const double* partials, uint32_t slots, double* acc) {
@@ -516,7 +547,7 @@ int32_t launch_finalize(cudaStream_t s, const double* acc, const FinalizeParams&
     return check_launch("k_finalize");
 }
 
-template <int GDT>
+template <int GDT, bool CHECK>
 static int32_t launch_adamw_g(cudaStream_t s, const LaunchGeom& g, const void* gsrc, float* master, float* m, float* v,
                               const PeerTable& peers, int32_t n_work, int32_t pdt, const TileMap& map,
                               const uint32_t* tile_meta, const uint8_t* present, const DevScalars* scalars,
@@ -524,24 +555,33 @@ static int32_t launch_adamw_g(cudaStream_t s, const LaunchGeom& g, const void* g
     constexpr int ILP = 2;
     dim3 grid(g.adam_blocks), block(THREADS);
     switch (pdt) {
-        case OXZ_F32: k_adamw<GDT, OXZ_F32, ILP><<<grid, block, 0, s>>>(gsrc, master, m, v, peers, n_work, map, tile_meta, present, scalars, ap); break;
-        case OXZ_BF16: k_adamw<GDT, OXZ_BF16, ILP><<<grid, block, 0, s>>>(gsrc, master, m, v, peers, n_work, map, tile_meta, present, scalars, ap); break;
-        case OXZ_F16: k_adamw<GDT, OXZ_F16, ILP><<<grid, block, 0, s>>>(gsrc, master, m, v, peers, n_work, map, tile_meta, present, scalars, ap); break;
+        case OXZ_F32: k_adamw<GDT, OXZ_F32, ILP, CHECK><<<grid, block, 0, s>>>(gsrc, master, m, v, peers, n_work, map, tile_meta, present, scalars, ap); break;
+        case OXZ_BF16: k_adamw<GDT, OXZ_BF16, ILP, CHECK><<<grid, block, 0, s>>>(gsrc, master, m, v, peers, n_work, map, tile_meta, present, scalars, ap); break;
+        case OXZ_F16: k_adamw<GDT, OXZ_F16, ILP, CHECK><<<grid, block, 0, s>>>(gsrc, master, m, v, peers, n_work, map, tile_meta, present, scalars, ap); break;
         default: return fail(OXZ_ERR_INVALID, "unknown parameter dtype %d", pdt);
     }
     return check_launch("k_adamw");
 }
 
-int32_t launch_adamw(cudaStream_t s, const LaunchGeom& g, const void* gsrc, int32_t gdt, float* master, float* m,
-                     float* v, const PeerTable& peers, int32_t n_work, int32_t pdt, const TileMap& map,
-                     const uint32_t* tile_meta, const uint8_t* present, const DevScalars* scalars,
-                     const AdamParams& ap) {
+template <bool CHECK>
+static int32_t launch_adamw_c(cudaStream_t s, const LaunchGeom& g, const void* gsrc, int32_t gdt, float* master, float* m,
+                              float* v, const PeerTable& peers, int32_t n_work, int32_t pdt, const TileMap& map,
+                              const uint32_t* tile_meta, const uint8_t* present, const DevScalars* scalars,
+                              const AdamParams& ap) {
     switch (gdt) {
-        case OXZ_F32: return launch_adamw_g<OXZ_F32>(s, g, gsrc, master, m, v, peers, n_work, pdt, map, tile_meta, present, scalars, ap);
-        case OXZ_BF16: return launch_adamw_g<OXZ_BF16>(s, g, gsrc, master, m, v, peers, n_work, pdt, map, tile_meta, present, scalars, ap);
-        case OXZ_F16: return launch_adamw_g<OXZ_F16>(s, g, gsrc, master, m, v, peers, n_work, pdt, map, tile_meta, present, scalars, ap);
+        case OXZ_F32: return launch_adamw_g<OXZ_F32, CHECK>(s, g, gsrc, master, m, v, peers, n_work, pdt, map, tile_meta, present, scalars, ap);
+        case OXZ_BF16: return launch_adamw_g<OXZ_BF16, CHECK>(s, g, gsrc, master, m, v, peers, n_work, pdt, map, tile_meta, present, scalars, ap);
+        case OXZ_F16: return launch_adamw_g<OXZ_F16, CHECK>(s, g, gsrc, master, m, v, peers, n_work, pdt, map, tile_meta, present, scalars, ap);
         default: return fail(OXZ_ERR_INVALID, "unknown gradient dtype %d", gdt);
     }
+}
+
+int32_t launch_adamw(cudaStream_t s, const LaunchGeom& g, const void* gsrc, int32_t gdt, float* master, float* m,
+                     float* v, const PeerTable& peers, int32_t n_work, int32_t pdt, const TileMap& map,
+                     const uint32_t* tile_meta, const uint8_t* present, bool check_present, const DevScalars* scalars,
+                     const AdamParams& ap) {
+    return check_present ? launch_adamw_c<true>(s, g, gsrc, gdt, master, m, v, peers, n_work, pdt, map, tile_meta, present, scalars, ap)
+                         : launch_adamw_c<false>(s, g, gsrc, gdt, master, m, v, peers, n_work, pdt, map, tile_meta, present, scalars, ap);
 }
 
 int32_t launch_flatten(cudaStream_t s, const LaunchGeom& g, void* flat, int32_t dt, uint32_t n_tiles,

@@ -31,4 +31,13 @@ int32_t nccl_fail(const char* what, int rc);
 struct oxz_comm;
 namespace oxz {
 int32_t comm_check(oxz_comm* c, const char* who);
+
+// Collectives the step enqueues, for either kind of communicator. With NCCL they are asynchronous on `s`; a local
+// group drains `s`, meets the other rank threads on the host and resumes.
+// Barrier: every rank's work enqueued before it on its own stream has finished when it ends.
+int32_t comm_stream_barrier(oxz_comm* c, int32_t* d_flag, cudaStream_t s);
+// Sum of n device doubles over ranks, in place. h_tmp: n pinned doubles of staging for the local kind.
+int32_t comm_stream_allreduce_f64(oxz_comm* c, double* d_buf, uint32_t n, double* h_tmp, cudaStream_t s);
+// All-gather of `bytes` host bytes per rank into out_all (world * bytes), blocking.
+int32_t comm_allgather_host(oxz_comm* c, const void* in, void* out_all, size_t bytes, cudaStream_t s);
 }

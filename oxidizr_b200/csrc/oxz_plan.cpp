@@ -43,6 +43,7 @@ const char* oxz_status_name(int32_t status) {
         case OXZ_ERR_ABORTED: return "OXZ_ERR_ABORTED";
         case OXZ_ERR_UNSUPPORTED: return "OXZ_ERR_UNSUPPORTED";
         case OXZ_ERR_DATA: return "OXZ_ERR_DATA";
+        case OXZ_ERR_TIMEOUT: return "OXZ_ERR_TIMEOUT";
         default: return "OXZ_ERR_UNKNOWN";
     }
 }

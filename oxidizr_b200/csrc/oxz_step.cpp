@@ -38,8 +38,7 @@ struct PeerBlob {
 // Ranks of one process (one thread per rank) use each other's pointers directly after enabling peer access;
 // ranks of other processes are opened through CUDA IPC handles.
 int32_t exchange_peers(oxz_plan* p, oxz_comm* c) {
-    const NcclApi* api = nccl_api();
-    if (!api) return fail(OXZ_ERR_UNSUPPORTED, "OXZ_SYNC_P2P needs NCCL for its rendezvous and it is not loaded");
+    if (c->kind == 0 && !nccl_api()) return fail(OXZ_ERR_UNSUPPORTED, "the NCCL communicator's library is not loaded");
     PeerBlob mine{};
     mine.pid = (uint64_t)getpid();
     mine.grads_ptr = (uint64_t)p->grads;
@@ -48,15 +47,8 @@ int32_t exchange_peers(oxz_plan* p, oxz_comm* c) {
     OXZ_CUDA(cudaIpcGetMemHandle(&mine.grads_handle, p->grads));
     OXZ_CUDA(cudaIpcGetMemHandle(&mine.work_handle, p->work));
     const int W = p->world;
-    PeerBlob* d_all = nullptr;
-    OXZ_CUDA(cudaMalloc(&d_all, sizeof(PeerBlob) * W));
-    OXZ_CUDA(cudaMemcpyAsync(d_all + p->rank, &mine, sizeof mine, cudaMemcpyHostToDevice, p->stream));
-    ncclResult_t rc = api->AllGather(d_all + p->rank, d_all, sizeof(PeerBlob), ncclInt8, (ncclComm_t)c->nccl, p->stream);
-    if (rc != ncclSuccess) return nccl_fail("peer rendezvous", rc);
     std::vector<PeerBlob> all(W);
-    OXZ_CUDA(cudaMemcpyAsync(all.data(), d_all, sizeof(PeerBlob) * W, cudaMemcpyDeviceToHost, p->stream));
-    OXZ_CUDA(cudaStreamSynchronize(p->stream));
-    OXZ_CUDA(cudaFree(d_all));
+    OXZ_TRY(comm_allgather_host(c, &mine, all.data(), sizeof(PeerBlob), p->stream));
     for (int r = 0; r < W; r++) {
         if (r == p->rank) {
             p->peers.grads[r] = p->grads;
@@ -137,7 +129,7 @@ int32_t oxz_plan_destroy(oxz_plan* p) {
                         (void*)p->d_tile_meta, (void*)p->d_present, (void*)p->d_offsets, (void*)p->d_numel,
                         (void*)p->d_src, (void*)p->d_partials, (void*)p->d_acc, (void*)p->d_scalars})
             if (q) cudaFree(q);
-        for (void* q : {(void*)p->h_scalars, (void*)p->h_acc, (void*)p->h_present, (void*)p->h_src})
+        for (void* q : {(void*)p->h_scalars, (void*)p->h_acc, (void*)p->h_extras, (void*)p->h_present, (void*)p->h_src})
             if (q) cudaFreeHost(q);
         if (p->done) cudaEventDestroy(p->done);
         for (auto e : p->ev) if (e) cudaEventDestroy(e);
@@ -200,6 +192,7 @@ int32_t oxz_state_alloc(oxz_plan* p, oxz_comm* comm) {
     OXZ_CUDA(zalloc((void**)&p->d_scalars, sizeof(DevScalars)));
     OXZ_CUDA(cudaMallocHost((void**)&p->h_scalars, sizeof(DevScalars)));
     OXZ_CUDA(cudaMallocHost((void**)&p->h_acc, (3 + MAX_EXTRAS) * 8));
+    OXZ_CUDA(cudaMallocHost((void**)&p->h_extras, MAX_EXTRAS * 8));
     OXZ_CUDA(cudaMallocHost((void**)&p->h_present, p->T ? p->T : 1));
     OXZ_CUDA(cudaMallocHost((void**)&p->h_src, (p->T ? p->T : 1) * 8));
     memset(p->h_present, 1, p->T ? p->T : 1);
@@ -346,8 +339,11 @@ int32_t oxz_step_async(oxz_plan* p, oxz_comm* comm, const oxz_hyper* h, const ui
     }
     OXZ_CUDA(cudaSetDevice(p->device));
     cudaStream_t s = p->stream;
-    const NcclApi* api = p->world > 1 ? nccl_api() : nullptr;
-    ncclComm_t nc = p->world > 1 ? (ncclComm_t)comm->nccl : nullptr;
+    const bool nccl_mode = p->mode == OXZ_SYNC_NCCL;
+    if (nccl_mode && comm->kind != 0)
+        return fail(OXZ_ERR_UNSUPPORTED, "OXZ_SYNC_NCCL needs an NCCL communicator; a local group serves OXZ_SYNC_P2P");
+    const NcclApi* api = nccl_mode ? nccl_api() : nullptr;
+    ncclComm_t nc = nccl_mode ? (ncclComm_t)comm->nccl : nullptr;
 
     // which tensors have a gradient this step
     bool changed = false;
@@ -359,6 +355,8 @@ int32_t oxz_step_async(oxz_plan* p, oxz_comm* comm, const oxz_hyper* h, const ui
         }
     }
     if (changed) OXZ_CUDA(cudaMemcpyAsync(p->d_present, p->h_present, p->T, cudaMemcpyHostToDevice, s));
+    bool some_absent = false;
+    for (uint64_t i = 0; i < p->T; i++) some_absent |= p->h_present[i] == 0;
 
     // per-step scalars, f64 on the host, rounded to f32 once
     const uint64_t t = p->timestep + 1;
@@ -399,15 +397,14 @@ int32_t oxz_step_async(oxz_plan* p, oxz_comm* comm, const oxz_hyper* h, const ui
     OXZ_CUDA(mark(0));
     if (p->mode == OXZ_SYNC_SINGLE) {
         OXZ_CUDA(mark(1));
-        OXZ_TRY(launch_sumsq(s, p->geom, p->grads, p->gdt, map, p->d_tile_meta, p->d_present, ap.inv_scale, ap.clamp_hi,
-                             ap.clamp_on, p->d_partials));
+        OXZ_TRY(launch_sumsq(s, p->geom, p->grads, p->gdt, map, p->d_tile_meta, p->d_present, some_absent, ap.inv_scale,
+                             ap.clamp_hi, ap.clamp_on, p->d_partials));
     } else if (p->mode == OXZ_SYNC_P2P) {
         // every rank's gradients must be complete before anyone pulls them
-        ncclResult_t rc = api->AllReduce(bar, bar, 1, ncclInt32, ncclSum, nc, s);
-        if (rc != ncclSuccess) return nccl_fail("the pre-pull barrier", rc);
+        OXZ_TRY(comm_stream_barrier(comm, bar, s));
         OXZ_CUDA(mark(1));
-        OXZ_TRY(launch_pull_sumsq(s, p->geom, p->peers, p->world, p->gdt, map, p->d_tile_meta, p->d_present, ap.inv_scale,
-                                  ap.clamp_hi, ap.clamp_on, static_cast<float*>(p->reduced), p->d_partials));
+        OXZ_TRY(launch_pull_sumsq(s, p->geom, p->peers, p->world, p->gdt, map, p->d_tile_meta, p->d_present, some_absent,
+                                  ap.inv_scale, ap.clamp_hi, ap.clamp_on, static_cast<float*>(p->reduced), p->d_partials));
         gsrc = p->reduced;
         gsrc_dt = OXZ_F32;
     } else {
@@ -425,19 +422,18 @@ int32_t oxz_step_async(oxz_plan* p, oxz_comm* comm, const oxz_hyper* h, const ui
         rc = api->GroupEnd();
         if (rc != ncclSuccess) return nccl_fail("the gradient reduce-scatter", rc);
         OXZ_CUDA(mark(1));
-        OXZ_TRY(launch_sumsq(s, p->geom, p->reduced, p->gdt, map, p->d_tile_meta, p->d_present, ap.inv_scale, ap.clamp_hi,
-                             ap.clamp_on, p->d_partials));
+        OXZ_TRY(launch_sumsq(s, p->geom, p->reduced, p->gdt, map, p->d_tile_meta, p->d_present, some_absent, ap.inv_scale,
+                             ap.clamp_hi, ap.clamp_on, p->d_partials));
         gsrc = p->reduced;
     }
     OXZ_CUDA(mark(2));
     OXZ_TRY(launch_reduce_partials(s, p->d_partials, slots, p->d_acc));
     if (p->world > 1) {
-        for (uint32_t i = 0; i < n_extras; i++) p->h_acc[3 + i] = extras[i];
-        if (n_extras) OXZ_CUDA(cudaMemcpyAsync(p->d_acc + 3, p->h_acc + 3, n_extras * 8, cudaMemcpyHostToDevice, s));
+        for (uint32_t i = 0; i < n_extras; i++) p->h_extras[i] = extras[i];
+        if (n_extras) OXZ_CUDA(cudaMemcpyAsync(p->d_acc + 3, p->h_extras, n_extras * 8, cudaMemcpyHostToDevice, s));
         // The one all-reduce of the step: {sum of squares, inf count, NaN count, extras...}. In P2P mode its end
         // also tells every rank that all peers have finished reading its gradient buffer.
-        ncclResult_t rc = api->AllReduce(p->d_acc, p->d_acc, 3 + n_extras, ncclFloat64, ncclSum, nc, s);
-        if (rc != ncclSuccess) return nccl_fail("the norm all-reduce", rc);
+        OXZ_TRY(comm_stream_allreduce_f64(comm, p->d_acc, 3 + n_extras, p->h_acc, s));
     }
     OXZ_TRY(launch_finalize(s, p->d_acc, fp, p->d_scalars));
     OXZ_CUDA(cudaMemcpyAsync(p->h_scalars, p->d_scalars, sizeof(DevScalars), cudaMemcpyDeviceToHost, s));
@@ -448,7 +444,7 @@ int32_t oxz_step_async(oxz_plan* p, oxz_comm* comm, const oxz_hyper* h, const ui
     const bool separate_work = p->work != (void*)p->master;
     const int32_t n_work = !separate_work ? 0 : (p->mode == OXZ_SYNC_P2P ? p->world : 1);
     OXZ_TRY(launch_adamw(s, p->geom, gsrc, gsrc_dt, p->master, p->exp_avg, p->exp_avg_sq, p->peers, n_work, p->pdt, map,
-                         p->d_tile_meta, p->d_present, p->d_scalars, ap));
+                         p->d_tile_meta, p->d_present, some_absent, p->d_scalars, ap));
     OXZ_CUDA(mark(4));
     if (p->mode == OXZ_SYNC_NCCL) {
         const size_t ps = dtype_size(p->pdt);
@@ -465,8 +461,7 @@ int32_t oxz_step_async(oxz_plan* p, oxz_comm* comm, const oxz_hyper* h, const ui
         if (rc != ncclSuccess) return nccl_fail("the weight all-gather", rc);
     } else if (p->mode == OXZ_SYNC_P2P) {
         // every rank's stores into this rank's weight buffer must have landed before the step is reported done
-        ncclResult_t rc = api->AllReduce(bar, bar, 1, ncclInt32, ncclSum, nc, s);
-        if (rc != ncclSuccess) return nccl_fail("the post-push barrier", rc);
+        OXZ_TRY(comm_stream_barrier(comm, bar, s));
     }
     OXZ_CUDA(mark(5));
     OXZ_CUDA(cudaEventRecord(p->done, s));

@@ -49,6 +49,14 @@ class Communicator:
         check(lib().oxz_comm_init_all(n, (C.c_int32 * n)(*devices), out))
         return [cls(out[i]) for i in range(n)]
 
+    @classmethod
+    def local_group(cls, n: int, devices: list[int] | None = None, timeout: float = 30.0) -> list["Communicator"]:
+        """In-process rank threads with a collective timeout (LocalCommunicator::with_timeout, src/dp/launch.rs:58)."""
+        out = (C.c_void_p * n)()
+        dev = (C.c_int32 * n)(*devices) if devices is not None else None
+        check(lib().oxz_comm_init_local(n, dev, timeout, out))
+        return [cls(out[i]) for i in range(n)]
+
     @property
     def handle(self) -> C.c_void_p:
         return self._h

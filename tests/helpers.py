@@ -85,13 +85,21 @@ class Pair:
                 assert np.array_equal(bits(a), bits(b)), f"{key}[{i}] differs: {np.sum(bits(a) != bits(b))} of {a.size} elements"
 
     def assert_close(self, rel=1e-6):
-        """|gpu - ref| <= rel * |ref| for master and moments (the per-step bound the path is held to)."""
+        """|gpu - ref| <= rel * (|ref| + rms(ref)) for master and moments.
+
+        The rms term keeps the bound meaningful where a moment passes through zero: its relative error is
+        unbounded there although the absolute error is one rounding of a typical element. The reference's own
+        cross-run bound has the same shape (1e-6 + 1e-5*|w|, tests/data_parallel.rs:258-262).
+        """
         g, r = self.gpu_state(), self.ref_state()
         for key in ("master", "exp_avg", "exp_avg_sq"):
             for i, (a, b) in enumerate(zip(g[key], r[key])):
-                err = np.abs(a.astype(np.float64) - b.astype(np.float64))
-                bound = rel * np.abs(b.astype(np.float64)) + 1e-30
-                assert np.all(err <= bound), f"{key}[{i}]: max rel err {np.max(err / (np.abs(b) + 1e-30)):.3e}"
+                if b.size == 0:
+                    continue
+                b64 = b.astype(np.float64)
+                err = np.abs(a.astype(np.float64) - b64)
+                bound = rel * (np.abs(b64) + np.sqrt(np.mean(b64 ** 2))) + 1e-30
+                assert np.all(err <= bound), f"{key}[{i}]: max err/bound {np.max(err / bound):.3e}"
 
     def close(self):
         self.opt.destroy()

@@ -1,0 +1,183 @@
+"""The sharded multi-rank step against the CPU checker's replicated step.
+
+Ranks run as threads of this process, one optimizer each (the reference's one-thread-per-rank model,
+src/dp/launch.rs:207-240). With a local group every rank may share cuda:0, so the pull-reduce and push kernels are
+exercised on a single GPU; with two or more GPUs the same tests also run over NCCL and real peer memory.
+The checker sums the ranks' gradients in rank order in f32 (src/dp/reduce.rs:11-29); the P2P kernels do the same,
+so without clipping the result is bit-identical.
+"""
+import math
+from concurrent.futures import ThreadPoolExecutor
+
+import numpy as np
+import pytest
+
+import oxidizr_b200 as ox
+from oxidizr_b200 import ffi
+from oracle import dpstep as orc
+from tests.helpers import NAN, bits, seeded_state
+
+pytestmark = pytest.mark.gpu
+
+NUMEL = [1, 300, 4096, 70001, 0, 513, 9000]
+NO_DECAY = [True, True, False, False, False, True, False]
+
+
+def gpu_count():
+    import torch
+    return torch.cuda.device_count()
+
+
+class Group:
+    def __init__(self, world, devices, kind, mode=ox.SYNC_P2P, gd=ox.BF16, pd=ox.BF16, seed=0, grad_std=1e-3,
+                 bucket_bytes=16384, numel=NUMEL, no_decay=NO_DECAY):
+        self.world, self.numel, self.gd, self.pd = world, numel, gd, pd
+        self.pool = ThreadPoolExecutor(world)
+        if kind == "local":
+            self.comms = ox.Communicator.local_group(world, devices, timeout=60.0)
+        else:
+            self.comms = ox.Communicator.init_all(devices)
+        master, m, v, grads = seeded_state(numel, seed, grad_std, world, gd)
+        self.grads = grads
+        work = [orc.narrow(p, pd) for p in master]
+        self.ref = orc.StepState([p.copy() for p in master], [x.copy() for x in m], [x.copy() for x in v],
+                                 [w.copy() for w in work], pd, lr_scale=[1.0] * len(numel),
+                                 group_wd=[0.0 if nd else NAN for nd in no_decay])
+
+        def make(r):
+            opt = ox.DpOptimizer(numel, no_decay, gd, pd, world=world, rank=r, sync_mode=mode, device=devices[r],
+                                 bucket_bytes=bucket_bytes, comm=self.comms[r])
+            for i in range(len(numel)):
+                opt.import_tensor(ffi.STATE_MASTER, i, master[i])
+                opt.import_tensor(ffi.STATE_EXP_AVG, i, m[i])
+                opt.import_tensor(ffi.STATE_EXP_AVG_SQ, i, v[i])
+                opt.import_tensor(ffi.STATE_WORK, i, work[i])
+                opt.import_tensor(ffi.STATE_GRADS, i, grads[r][i])
+            return opt
+        self.opts = list(self.pool.map(make, range(world)))
+
+    def set_grads(self, grads):
+        self.grads = grads
+        def put(r):
+            for i, g in enumerate(grads[r]):
+                self.opts[r].import_tensor(ffi.STATE_GRADS, i, g)
+        list(self.pool.map(put, range(self.world)))
+
+    def step(self, cfg, extras=None, present=None):
+        def run(r):
+            res = self.opts[r].step(cfg, present, [extras[r]] if extras else None)
+            return res, (self.opts[r].last_extras if extras else None)
+        out = list(self.pool.map(run, range(self.world)))
+        rg = [[g if (present is None or present[i]) else None for i, g in enumerate(self.grads[r])] for r in range(self.world)]
+        ocfg = orc.StepConfig(**{k: getattr(cfg, k) for k in orc.StepConfig.__dataclass_fields__})
+        ref = orc.step(self.ref, rg, self.gd, ocfg)
+        return out, ref
+
+    def merged(self, kind):
+        """Each rank exports the elements it owns; together they must cover every tensor."""
+        out = []
+        for i, n in enumerate(self.numel):
+            acc = np.full(n, np.nan, np.float32)
+            for opt in self.opts:
+                opt.export_tensor(kind, i, acc)
+            out.append(acc)
+        return out
+
+    def assert_state(self, exact=True, rel=1e-6):
+        for kind, ref in ((ffi.STATE_MASTER, self.ref.master), (ffi.STATE_EXP_AVG, self.ref.exp_avg),
+                          (ffi.STATE_EXP_AVG_SQ, self.ref.exp_avg_sq)):
+            for i, (a, b) in enumerate(zip(self.merged(kind), ref)):
+                assert not np.isnan(a).any(), f"tensor {i}: some element has no owner"
+                if exact:
+                    assert np.array_equal(bits(a), bits(b)), (kind, i, int(np.sum(bits(a) != bits(b))))
+                else:
+                    tol = rel * (np.abs(b.astype(np.float64)) + math.sqrt(float(np.mean(b.astype(np.float64) ** 2)) if b.size else 0.0))
+                    assert np.all(np.abs(a.astype(np.float64) - b) <= tol + 1e-30), (kind, i)
+        # every rank holds the full, identical working weights after the push / all-gather
+        for r, opt in enumerate(self.opts):
+            for i in range(len(self.numel)):
+                w = opt.export_tensor(ffi.STATE_WORK, i)
+                if exact:
+                    assert np.array_equal(bits(w), bits(self.ref.work[i])), (r, i)
+                else:
+                    assert np.array_equal(bits(w), bits(self.opts[0].export_tensor(ffi.STATE_WORK, i))), (r, i)
+
+    def close(self):
+        list(self.pool.map(lambda r: self.opts[r].destroy(), range(self.world)))
+        for c in self.comms:
+            c.destroy()
+        self.pool.shutdown()
+
+
+def layouts():
+    out = [("local", 2, [0, 0]), ("local", 3, [0, 0, 0]), ("local", 4, [0, 0, 0, 0])]
+    n = gpu_count()
+    if n >= 2:
+        out += [("nccl", 2, [0, 1]), ("local", 2, [0, 1])]
+    if n >= 4:
+        out += [("nccl", 4, [0, 1, 2, 3])]
+    if n >= 8:
+        out += [("nccl", 8, list(range(8)))]
+    return out
+
+
+@pytest.mark.parametrize("kind,world,devices", layouts())
+@pytest.mark.parametrize("gd,pd", [(ox.BF16, ox.BF16), (ox.F16, ox.F16), (ox.F32, ox.F32)])
+def test_sharded_p2p_step_is_bit_identical_to_the_replicated_step(kind, world, devices, gd, pd):
+    g = Group(world, devices, kind, gd=gd, pd=pd, seed=21)
+    cfg = ox.StepConfig(max_grad_norm=1e9, eps=1e-8)
+    for s in range(2):
+        out, ref = g.step(cfg, extras=[0.25 * (r + 1) for r in range(world)])
+        for res, extras in out:
+            assert (res.overflow, res.applied, res.timestep) == (ref.overflow, ref.applied, ref.timestep)
+            assert abs(res.grad_norm - ref.grad_norm) <= 1e-5 * ref.grad_norm
+            assert extras == [sum(0.25 * (r + 1) for r in range(world))]  # the loss summed over ranks
+        norms = {res.grad_norm for res, _ in out}
+        assert len(norms) == 1, "every rank must see the same norm bits"
+        g.assert_state(exact=True)
+    g.close()
+
+
+@pytest.mark.parametrize("kind,world,devices", layouts())
+def test_sharded_step_with_clipping_and_absent_tensors(kind, world, devices):
+    g = Group(world, devices, kind, seed=22, grad_std=1.0)
+    present = [True, True, False, True, True, True, True]
+    out, ref = g.step(ox.StepConfig(max_grad_norm=1.0), present=present)
+    for res, _ in out:
+        assert abs(res.grad_norm - ref.grad_norm) <= 1e-5 * ref.grad_norm
+        assert abs(res.clip_coef - ref.clip_coef) <= 1e-6 * ref.clip_coef and res.reported_norm == 1.0
+    g.assert_state(exact=False)
+    g.close()
+
+
+@pytest.mark.parametrize("kind,world,devices", layouts())
+def test_overflow_on_one_rank_skips_on_every_rank(kind, world, devices):
+    # tests/data_parallel.rs:353-392
+    g = Group(world, devices, kind, gd=ox.F16, pd=ox.F16, seed=23)
+    before = [g.merged(k) for k in (ffi.STATE_MASTER, ffi.STATE_EXP_AVG, ffi.STATE_EXP_AVG_SQ)]
+    grads = [[x.copy() for x in rg] for rg in g.grads]
+    grads[world - 1][3][4242] = np.array([np.inf], np.float16).view(np.uint16)[0]
+    g.set_grads(grads)
+    out, ref = g.step(ox.StepConfig(loss_scale=1024.0))
+    for res, _ in out:
+        assert (res.overflow, res.applied, res.timestep) == (1, 0, 0) == (ref.overflow, ref.applied, ref.timestep)
+        assert not math.isfinite(res.grad_norm)
+    after = [g.merged(k) for k in (ffi.STATE_MASTER, ffi.STATE_EXP_AVG, ffi.STATE_EXP_AVG_SQ)]
+    for b, a in zip(before, after):
+        for x, y in zip(b, a):
+            assert np.array_equal(bits(x), bits(y))
+    g.close()
+
+
+@pytest.mark.skipif(gpu_count() < 2, reason="needs two GPUs")
+@pytest.mark.parametrize("gd", [ox.F32, ox.BF16])
+def test_nccl_mode_matches_within_its_wire_precision(gd):
+    # reduce-scatter in the gradient's dtype: f32 sums differ from the rank-order sum only by rounding order;
+    # bf16 sums are rounded to bf16 by the collective, so only the looser bound holds
+    g = Group(2, [0, 1], "nccl", mode=ox.SYNC_NCCL, gd=gd, pd=ox.BF16, seed=24)
+    out, ref = g.step(ox.StepConfig(max_grad_norm=1e9))
+    rel = 1e-6 if gd == ox.F32 else 2e-2
+    for res, _ in out:
+        assert res.applied == 1 and abs(res.grad_norm - ref.grad_norm) <= max(rel, 1e-5) * ref.grad_norm
+    g.assert_state(exact=False, rel=rel)
+    g.close()
