@@ -300,6 +300,7 @@ def run_gpu(args):
         "e2e": {"value": e2e_value, "unit": UNIT, "h2d_bytes_per_step": P * 2 * world, "d2h_bytes_per_step": 32 * world,
                 "ms_per_step": e2e_sec * 1e3 / e2e_steps, "steps": e2e_steps},
         "gpu_launches": 4 * args.steps * world,
+        "launch_geometry": opt.launch_geometry(),
         "clocks": clocks,
         "result": {"grad_norm": res.grad_norm, "applied": res.applied, "timestep": res.timestep},
     }

@@ -211,6 +211,8 @@ typedef struct oxz_step_profile {
     float publish_ms; /* all-gather or closing barrier (0 at world 1) */
     float total_ms;
 } oxz_step_profile;
+/* Grid sizes the plan launches with (blocks of 256 threads) and the device's SM count. */
+int32_t oxz_plan_launch_geometry(const oxz_plan* plan, int32_t* sm_count, int32_t* norm_blocks, int32_t* update_blocks);
 /* on != 0: record the events every step (a few microseconds); off by default. */
 int32_t oxz_plan_set_profile(oxz_plan* plan, int32_t on);
 int32_t oxz_step_profile_read(oxz_plan* plan, oxz_step_profile* out);

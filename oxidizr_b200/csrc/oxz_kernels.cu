@@ -462,15 +462,53 @@ __global__ void __launch_bounds__(THREADS)
 
 // ---------------------------------------------------------------- launchers
 
+// Clusters of CLUSTER blocks of `func` that can be resident on the device at once.
+static int max_cluster_blocks(const void* func, int fallback) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(CLUSTER * 1024);
+    cfg.blockDim = dim3(THREADS);
+    cudaLaunchAttribute attr;
+    attr.id = cudaLaunchAttributeClusterDimension;
+    attr.val.clusterDim.x = CLUSTER;
+    attr.val.clusterDim.y = 1;
+    attr.val.clusterDim.z = 1;
+    cfg.attrs = &attr;
+    cfg.numAttrs = 1;
+    int n = 0;
+    if (cudaOccupancyMaxActiveClusters(&n, func, &cfg) != cudaSuccess || n <= 0) {
+        cudaGetLastError();
+        return fallback;
+    }
+    return n * CLUSTER;
+}
+
 int32_t query_geom(int device, LaunchGeom* g) {
     cudaDeviceProp prop;
     OXZ_CUDA(cudaGetDeviceProperties(&prop, device));
     g->sm_count = prop.multiProcessorCount;
-    // 4 resident blocks of 256 threads per SM for the read-only pass, 2 for the update (register bound).
+    // The reduction kernels are persistent: every block takes an equal share, so the grid must be resident in
+    // one wave. Size it by the clusters the device can hold at once, the smallest over the variants.
     int nb = g->sm_count * 4;
     nb -= nb % CLUSTER;
+    const void* funcs[] = {
+        (const void*)k_sumsq<OXZ_F32, 4, false>,  (const void*)k_sumsq<OXZ_BF16, 4, false>, (const void*)k_sumsq<OXZ_F16, 4, false>,
+        (const void*)k_sumsq<OXZ_F32, 4, true>,   (const void*)k_sumsq<OXZ_BF16, 4, true>,  (const void*)k_sumsq<OXZ_F16, 4, true>,
+        (const void*)k_pull_sumsq<OXZ_F32, false>, (const void*)k_pull_sumsq<OXZ_BF16, false>, (const void*)k_pull_sumsq<OXZ_F16, false>,
+        (const void*)k_pull_sumsq<OXZ_F32, true>,  (const void*)k_pull_sumsq<OXZ_BF16, true>,  (const void*)k_pull_sumsq<OXZ_F16, true>,
+        (const void*)k_sumsq_plain<OXZ_F32>, (const void*)k_sumsq_plain<OXZ_BF16>, (const void*)k_sumsq_plain<OXZ_F16>};
+    for (const void* f : funcs) {
+        const int m = max_cluster_blocks(f, nb);
+        if (m < nb) nb = m;
+    }
     g->norm_blocks = nb > 0 ? nb : CLUSTER;
-    g->adam_blocks = g->sm_count * 2;
+    // The update kernel is register bound: as many blocks as fit, never more than one wave.
+    int per_sm = 0;
+    if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, k_adamw<OXZ_BF16, OXZ_BF16, 2, false>, THREADS, 0) != cudaSuccess || per_sm <= 0) {
+        cudaGetLastError();
+        per_sm = 2;
+    }
+    if (per_sm > 4) per_sm = 4;
+    g->adam_blocks = g->sm_count * per_sm;
     return OXZ_OK;
 }
 

@@ -502,6 +502,15 @@ int32_t oxz_step_wait(oxz_plan* p, oxz_step_result* res) {
     return OXZ_OK;
 }
 
+int32_t oxz_plan_launch_geometry(const oxz_plan* p, int32_t* sm_count, int32_t* norm_blocks, int32_t* update_blocks) {
+    if (!p) return fail(OXZ_ERR_INVALID, "oxz_plan_launch_geometry: null plan");
+    if (!p->allocated) return fail(OXZ_ERR_STATE, "oxz_plan_launch_geometry: call oxz_state_alloc first");
+    if (sm_count) *sm_count = p->geom.sm_count;
+    if (norm_blocks) *norm_blocks = p->geom.norm_blocks;
+    if (update_blocks) *update_blocks = p->geom.adam_blocks;
+    return OXZ_OK;
+}
+
 int32_t oxz_plan_set_profile(oxz_plan* p, int32_t on) {
     if (!p) return fail(OXZ_ERR_INVALID, "oxz_plan_set_profile: null plan");
     if (!p->allocated) return fail(OXZ_ERR_STATE, "oxz_plan_set_profile: call oxz_state_alloc first");

@@ -467,6 +467,11 @@ class DpOptimizer:
         self.step_async(cfg, present, extras)
         return self.step_wait()
 
+    def launch_geometry(self) -> dict:
+        v = [C.c_int32() for _ in range(3)]
+        check(lib().oxz_plan_launch_geometry(self._h, *[C.byref(x) for x in v]))
+        return dict(sm_count=v[0].value, norm_blocks=v[1].value, update_blocks=v[2].value)
+
     def set_profile(self, on: bool) -> None:
         """Per-phase CUDA-event timing of each step (the PROFILE_TRAIN switch, src/trainer.rs:262-263)."""
         check(lib().oxz_plan_set_profile(self._h, int(on)))
