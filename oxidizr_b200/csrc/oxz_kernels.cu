@@ -19,6 +19,8 @@
 #include <cuda_bf16.h>
 #include <cuda_fp16.h>
 
+#include <cstdlib>
+
 #include "oxz_internal.h"
 
 namespace cg = cooperative_groups;
@@ -41,10 +43,11 @@ __device__ __forceinline__ void st_stream(uint4* p, uint4 v) { __stcs(p, v); }
 template <int DT>
 __device__ __forceinline__ void load8(const void* base, uint64_t e, float (&x)[8]) {
     if constexpr (DT == OXZ_F32) {
-        const float4* p = reinterpret_cast<const float4*>(static_cast<const float*>(base) + e);
-        float4 a = ld_stream(p), b = ld_stream(p + 1);
-        x[0] = a.x; x[1] = a.y; x[2] = a.z; x[3] = a.w;
-        x[4] = b.x; x[5] = b.y; x[6] = b.z; x[7] = b.w;
+        // one 256-bit access per lane (sm_100): a warp covers 1 KiB contiguously with a single instruction
+        const float* p = static_cast<const float*>(base) + e;
+        asm volatile("ld.global.cs.v8.f32 {%0,%1,%2,%3,%4,%5,%6,%7}, [%8];"
+                     : "=f"(x[0]), "=f"(x[1]), "=f"(x[2]), "=f"(x[3]), "=f"(x[4]), "=f"(x[5]), "=f"(x[6]), "=f"(x[7])
+                     : "l"(p));
     } else {
         uint4 r = ld_stream(reinterpret_cast<const uint4*>(static_cast<const uint16_t*>(base) + e));
         const uint32_t w[4] = {r.x, r.y, r.z, r.w};
@@ -66,9 +69,10 @@ __device__ __forceinline__ void load8(const void* base, uint64_t e, float (&x)[8
 template <int DT>
 __device__ __forceinline__ void store8(void* base, uint64_t e, const float (&x)[8]) {
     if constexpr (DT == OXZ_F32) {
-        float4* p = reinterpret_cast<float4*>(static_cast<float*>(base) + e);
-        st_stream(p, make_float4(x[0], x[1], x[2], x[3]));
-        st_stream(p + 1, make_float4(x[4], x[5], x[6], x[7]));
+        float* p = static_cast<float*>(base) + e;
+        asm volatile("st.global.cs.v8.f32 [%0], {%1,%2,%3,%4,%5,%6,%7,%8};" ::"l"(p), "f"(x[0]), "f"(x[1]), "f"(x[2]),
+                     "f"(x[3]), "f"(x[4]), "f"(x[5]), "f"(x[6]), "f"(x[7])
+                     : "memory");
     } else {
         uint32_t w[4];
 #pragma unroll
@@ -356,8 +360,8 @@ __device__ __forceinline__ void adam1(float& p, float& m, float& v, float g, con
     if (k.decay_after) p = __fmul_rn(p, decay);
 }
 
-template <int GDT, int PDT, int ILP, bool CHECK>
-__global__ void __launch_bounds__(THREADS)
+template <int GDT, int PDT, int ILP, int MINB, bool CHECK>
+__global__ void __launch_bounds__(THREADS, MINB)
     k_adamw(const void* __restrict__ gsrc, float* __restrict__ master, float* __restrict__ exp_avg,
             float* __restrict__ exp_avg_sq, PeerTable peers, int n_work, TileMap map,
             const uint32_t* __restrict__ tile_meta, const uint8_t* __restrict__ present,
@@ -462,6 +466,16 @@ __global__ void __launch_bounds__(THREADS)
 
 // ---------------------------------------------------------------- launchers
 
+static int adam_variant() {
+    static int v = [] {
+        const char* e = getenv("OXZ_ADAM_VARIANT");
+        return e ? atoi(e) : 0;
+    }();
+    return v;
+}
+
+static int adam_blocks_per_sm(int variant) { return variant == 1 ? 4 : variant == 2 ? 2 : 3; }
+
 // Clusters of CLUSTER blocks of `func` that can be resident on the device at once.
 static int max_cluster_blocks(const void* func, int fallback) {
     cudaLaunchConfig_t cfg = {};
@@ -501,14 +515,7 @@ int32_t query_geom(int device, LaunchGeom* g) {
         if (m < nb) nb = m;
     }
     g->norm_blocks = nb > 0 ? nb : CLUSTER;
-    // The update kernel is register bound: as many blocks as fit, never more than one wave.
-    int per_sm = 0;
-    if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, k_adamw<OXZ_BF16, OXZ_BF16, 2, false>, THREADS, 0) != cudaSuccess || per_sm <= 0) {
-        cudaGetLastError();
-        per_sm = 2;
-    }
-    if (per_sm > 4) per_sm = 4;
-    g->adam_blocks = g->sm_count * per_sm;
+    g->adam_blocks = g->sm_count * adam_blocks_per_sm(adam_variant());
     return OXZ_OK;
 }
 
@@ -585,17 +592,34 @@ int32_t launch_finalize(cudaStream_t s, const double* acc, const FinalizeParams&
     return check_launch("k_finalize");
 }
 
+// The update kernel's shape: tiles per warp per iteration (ILP) and the resident blocks per SM its register budget
+// is held to. Measured on B200 on the 1.24 B-parameter set (28 B/param): ILP 1 x 3 blocks/SM streams 6.4 TB/s,
+// ILP 2 x 2 blocks/SM 5.4 TB/s, ILP 1 x 4 blocks/SM 5.7 TB/s. OXZ_ADAM_VARIANT=1|2 selects the other two for tuning.
+template <int GDT, int PDT, bool CHECK>
+static void launch_adamw_v(int variant, dim3 grid, cudaStream_t s, const void* gsrc, float* master, float* m, float* v,
+                           const PeerTable& peers, int32_t n_work, const TileMap& map, const uint32_t* tile_meta,
+                           const uint8_t* present, const DevScalars* scalars, const AdamParams& ap) {
+    dim3 block(THREADS);
+#define OXZ_ADAM(ILP, MINB) k_adamw<GDT, PDT, ILP, MINB, CHECK><<<grid, block, 0, s>>>(gsrc, master, m, v, peers, n_work, map, tile_meta, present, scalars, ap)
+    switch (variant) {
+        case 1: OXZ_ADAM(1, 4); break;
+        case 2: OXZ_ADAM(2, 2); break;
+        default: OXZ_ADAM(1, 3); break;
+    }
+#undef OXZ_ADAM
+}
+
 template <int GDT, bool CHECK>
 static int32_t launch_adamw_g(cudaStream_t s, const LaunchGeom& g, const void* gsrc, float* master, float* m, float* v,
                               const PeerTable& peers, int32_t n_work, int32_t pdt, const TileMap& map,
                               const uint32_t* tile_meta, const uint8_t* present, const DevScalars* scalars,
                               const AdamParams& ap) {
-    constexpr int ILP = 2;
-    dim3 grid(g.adam_blocks), block(THREADS);
+    const int variant = adam_variant();
+    dim3 grid(g.adam_blocks);
     switch (pdt) {
-        case OXZ_F32: k_adamw<GDT, OXZ_F32, ILP, CHECK><<<grid, block, 0, s>>>(gsrc, master, m, v, peers, n_work, map, tile_meta, present, scalars, ap); break;
-        case OXZ_BF16: k_adamw<GDT, OXZ_BF16, ILP, CHECK><<<grid, block, 0, s>>>(gsrc, master, m, v, peers, n_work, map, tile_meta, present, scalars, ap); break;
-        case OXZ_F16: k_adamw<GDT, OXZ_F16, ILP, CHECK><<<grid, block, 0, s>>>(gsrc, master, m, v, peers, n_work, map, tile_meta, present, scalars, ap); break;
+        case OXZ_F32: launch_adamw_v<GDT, OXZ_F32, CHECK>(variant, grid, s, gsrc, master, m, v, peers, n_work, map, tile_meta, present, scalars, ap); break;
+        case OXZ_BF16: launch_adamw_v<GDT, OXZ_BF16, CHECK>(variant, grid, s, gsrc, master, m, v, peers, n_work, map, tile_meta, present, scalars, ap); break;
+        case OXZ_F16: launch_adamw_v<GDT, OXZ_F16, CHECK>(variant, grid, s, gsrc, master, m, v, peers, n_work, map, tile_meta, present, scalars, ap); break;
         default: return fail(OXZ_ERR_INVALID, "unknown parameter dtype %d", pdt);
     }
     return check_launch("k_adamw");
