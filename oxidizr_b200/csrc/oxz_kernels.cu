@@ -39,7 +39,8 @@ __device__ __forceinline__ float4 ld_stream(const float4* p) { return __ldcs(p);
 __device__ __forceinline__ void st_stream(float4* p, float4 v) { __stcs(p, v); }
 __device__ __forceinline__ void st_stream(uint4* p, uint4 v) { __stcs(p, v); }
 
-// 8 consecutive elements of dtype DT starting at element index `e` (a multiple of 8) as f32.
+// 8 consecutive elements of dtype DT starting at element index `e` (a multiple of 8) as f32, from a buffer the
+// library allocated (256-byte aligned base, so an f32 vector is 32-byte aligned).
 template <int DT>
 __device__ __forceinline__ void load8(const void* base, uint64_t e, float (&x)[8]) {
     if constexpr (DT == OXZ_F32) {
@@ -63,6 +64,19 @@ __device__ __forceinline__ void load8(const void* base, uint64_t e, float (&x)[8
                 x[2 * i + 1] = f.y;
             }
         }
+    }
+}
+
+// The same for memory the caller owns, which is only promised to be 16-byte aligned: f32 goes as two 128-bit loads.
+template <int DT>
+__device__ __forceinline__ void load8_user(const void* base, uint64_t e, float (&x)[8]) {
+    if constexpr (DT == OXZ_F32) {
+        const float4* p = reinterpret_cast<const float4*>(static_cast<const float*>(base) + e);
+        float4 a = ld_stream(p), b = ld_stream(p + 1);
+        x[0] = a.x; x[1] = a.y; x[2] = a.z; x[3] = a.w;
+        x[4] = b.x; x[5] = b.y; x[6] = b.z; x[7] = b.w;
+    } else {
+        load8<DT>(base, e, x);
     }
 }
 
@@ -239,7 +253,7 @@ __global__ void __cluster_dims__(CLUSTER, 1, 1) __launch_bounds__(THREADS)
     const uint64_t stride = static_cast<uint64_t>(gridDim.x) * THREADS;
     for (uint64_t i = static_cast<uint64_t>(blockIdx.x) * THREADS + threadIdx.x; i < nvec; i += stride) {
         float g[8];
-        load8<DT>(grads, i * 8, g);
+        load8_user<DT>(grads, i * 8, g);
         acc8(g, inv_scale, clamp_hi, clamp_on != 0, a);
     }
     if (blockIdx.x == 0 && threadIdx.x == 0 && (n & 7)) {
@@ -438,7 +452,7 @@ __global__ void __launch_bounds__(THREADS)
                 const uint64_t te = fe - offsets[t];  // element within the tensor
                 const uint64_t n = numel[t];
                 if (te + 8 <= n) {
-                    load8<DT>(s, te, x);
+                    load8_user<DT>(s, te, x);
                 } else {
 #pragma unroll
                     for (int i = 0; i < 8; i++) {

@@ -261,6 +261,24 @@ def test_flatten_packs_per_tensor_gradients():
     opt.destroy()
 
 
+def test_f32_gradients_need_only_16_byte_alignment():
+    # caller-owned f32 memory is promised 16-byte aligned, not 32: the norm and the flatten must accept it
+    import torch
+    rng = np.random.default_rng(15)
+    host = rng.standard_normal(4 + 5000).astype(np.float32)
+    dev = torch.from_numpy(host).cuda()
+    ptr = dev.data_ptr() + 16  # 16-byte aligned, not 32
+    assert ptr % 32 == 16
+    want = math.sqrt(orc.sumsq(host[4:]))
+    assert abs(ox.compute_grad_norm(ptr, ox.F32, 5000) - want) <= NORM_RTOL * want
+    opt = ox.DpOptimizer([5000], None, ox.F32, ox.F32)
+    opt.flatten_grads([ptr])
+    assert np.array_equal(opt.export_tensor(ffi.STATE_GRADS, 0), host[4:])
+    with pytest.raises(ox.OxzError, match="16-byte aligned"):
+        opt.flatten_grads([ptr + 4])
+    opt.destroy()
+
+
 def test_call_order_errors_are_reported_not_fatal():
     opt = ox.DpOptimizer([100], None, ox.BF16, ox.BF16)
     with pytest.raises(ox.OxzError, match="no step is in flight"):
