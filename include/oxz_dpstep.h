@@ -223,6 +223,22 @@ int32_t oxz_step_profile_read(oxz_plan* plan, oxz_step_profile* out);
 int32_t oxz_grad_norm(const void* device_grads, int32_t dtype, uint64_t n, double loss_scale, double max_grad_value,
                       void* stream, double* norm);
 
+/* The same measurement as oxz_grad_norm for hosts that must not allocate. It has no counterpart in the reference:
+ * it exists for callers of this library whose device memory is already spoken for (a trainer whose caching
+ * allocator owns the whole GPU, a process with a fixed memory budget) or whose step loop must not meet the
+ * device-wide synchronisation of cudaMalloc/cudaFree. The partial sums live in a static device array inside the
+ * library image (about 7 KiB, held by every GPU that loads the library until the process exits); the call makes
+ * no cudaMalloc, cudaMallocHost or cudaFree, and the result is copied straight into *norm.
+ *   clusters: how many 4-block clusters to launch; 0 = as many as the device holds at once. The array holds the
+ *             partial sums of at most OXZ_STATIC_NORM_MAX_CLUSTERS clusters: a larger request is OXZ_ERR_INVALID.
+ * The first call on each device looks up the array's device address and the launch geometry (with that device
+ * current) and keeps them; make that first call outside any stream capture. All calls on one device share the one
+ * array, and it keeps the last call's contents (no stage depends on them): two calls whose kernels overlap on the
+ * GPU, from different streams or threads, race on it and must be serialised by the caller. Blocking. */
+#define OXZ_STATIC_NORM_MAX_CLUSTERS 256u
+int32_t oxz_grad_norm_static(const void* device_grads, int32_t dtype, uint64_t n, double loss_scale,
+                             double max_grad_value, uint32_t clusters, void* stream, double* norm);
+
 /* ------------------------------------------------------------------ host decisions (pure, no GPU) */
 
 typedef struct oxz_scaler_config { double initial, growth_factor, backoff_factor; uint64_t growth_interval; } oxz_scaler_config;

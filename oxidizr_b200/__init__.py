@@ -7,4 +7,5 @@ from ._ffi import BF16, F16, F32, SYNC_NCCL, SYNC_P2P, SYNC_SINGLE, OxzError, li
 from . import _ffi as ffi  # noqa: F401
 from .dpstep import (Communicator, DataPosition, DecayPlan, DpOptimizer, GradScalerState, LitTrainerStep,  # noqa: F401
                      LossScaleConfig, LossScaler, LrPlan, RowLayout, SpikeGuard, SpikeGuardConfig, StepConfig,
-                     TensorInfo, TrainerConfig, WeightDecaySpec, compute_grad_norm, step_weighting)
+                     TensorInfo, TrainerConfig, WeightDecaySpec, compute_grad_norm, compute_grad_norm_static,
+                     step_weighting)

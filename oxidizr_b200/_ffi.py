@@ -121,6 +121,7 @@ SIGNATURES = {
     "oxz_plan_set_profile": (C.c_int32, [vp, C.c_int32]),
     "oxz_step_profile_read": (C.c_int32, [vp, C.POINTER(StepProfile)]),
     "oxz_grad_norm": (C.c_int32, [vp, C.c_int32, C.c_uint64, C.c_double, C.c_double, vp, f64p]),
+    "oxz_grad_norm_static": (C.c_int32, [vp, C.c_int32, C.c_uint64, C.c_double, C.c_double, C.c_uint32, vp, f64p]),
     "oxz_scaler_check": (C.c_int32, [C.POINTER(ScalerConfig)]),
     "oxz_scaler_init": (C.c_int32, [C.POINTER(ScalerConfig), C.POINTER(ScalerState)]),
     "oxz_scaler_restore": (C.c_int32, [C.POINTER(ScalerState), C.POINTER(ScalerState)]),

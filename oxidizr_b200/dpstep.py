@@ -502,6 +502,20 @@ def compute_grad_norm(device_ptr: int, dtype: int, n: int, loss_scale: float = N
     return out.value
 
 
+STATIC_NORM_MAX_CLUSTERS = 256
+
+
+def compute_grad_norm_static(device_ptr: int, dtype: int, n: int, loss_scale: float = NAN,
+                             max_grad_value: float = NAN, clusters: int = 0, stream: int | None = None) -> float:
+    """compute_grad_norm for a host that must not allocate: same kernels, scratch in a static device array of the
+    library (partial sums of at most STATIC_NORM_MAX_CLUSTERS clusters). Calls on one device share that array and
+    must not overlap on the GPU; the first call on a device does the one-time set-up."""
+    out = C.c_double()
+    check(lib().oxz_grad_norm_static(C.c_void_p(device_ptr), dtype, n, loss_scale, max_grad_value, clusters,
+                                     C.c_void_p(stream) if stream else None, C.byref(out)))
+    return out.value
+
+
 # ------------------------------------------------------------------ the trainer's half of the step
 @dataclass
 class TrainerConfig:
