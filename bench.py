@@ -175,6 +175,7 @@ def run_gpu(args):
     dist = None
     comm = None
     if world > 1:
+        os.environ.setdefault("NCCL_DEBUG_FILE", "/dev/stderr")  # keep stdout for the one JSON line
         import torch.distributed as dist
         dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
         uid = [ox.Communicator.unique_id() if rank == 0 else None]

@@ -85,10 +85,12 @@ struct FinalizeParams {
 struct LaunchGeom {
     int sm_count;
     int norm_blocks;   // multiple of the cluster size
+    int pull_blocks[3];  // per gradient dtype (f32, bf16, f16), never more than norm_blocks
     int adam_blocks;
 };
 int32_t query_geom(int device, LaunchGeom* g);
 uint32_t norm_partial_slots(const LaunchGeom& g);
+uint32_t pull_partial_slots(const LaunchGeom& g, int32_t dt);
 
 // Sum of squares of unscaled (and optionally clamped) gradients held in one local array of dtype `dt`.
 int32_t launch_sumsq(cudaStream_t s, const LaunchGeom& g, const void* grads, int32_t dt, const TileMap& map,

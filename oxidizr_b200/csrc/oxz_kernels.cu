@@ -274,44 +274,121 @@ __global__ void __cluster_dims__(CLUSTER, 1, 1) __launch_bounds__(THREADS)
     cluster_reduce_store(a, partials);
 }
 
-template <int DT, bool CHECK>
+// A vector of 8 elements as it sits in memory: 16-bit types stay packed (4 registers) until they are needed, so a
+// lane can keep eight remote loads in flight without eight times the registers.
+template <int DT>
+struct RawVec {
+    uint4 v;
+};
+template <>
+struct RawVec<OXZ_F32> {
+    float x[8];
+};
+
+template <int DT>
+__device__ __forceinline__ void load_raw(const void* base, uint64_t e, RawVec<DT>& r) {
+    if constexpr (DT == OXZ_F32) load8<OXZ_F32>(base, e, r.x);
+    else r.v = ld_stream(reinterpret_cast<const uint4*>(static_cast<const uint16_t*>(base) + e));
+}
+
+template <int DT>
+__device__ __forceinline__ void widen_raw(const RawVec<DT>& r, float (&x)[8]) {
+    if constexpr (DT == OXZ_F32) {
+#pragma unroll
+        for (int i = 0; i < 8; i++) x[i] = r.x[i];
+    } else {
+        const uint32_t w[4] = {r.v.x, r.v.y, r.v.z, r.v.w};
+#pragma unroll
+        for (int i = 0; i < 4; i++) {
+            if constexpr (DT == OXZ_BF16) {
+                x[2 * i] = __uint_as_float(w[i] << 16);
+                x[2 * i + 1] = __uint_as_float(w[i] & 0xffff0000u);
+            } else {
+                const float2 f = __half22float2(*reinterpret_cast<const __half2*>(&w[i]));
+                x[2 * i] = f.x;
+                x[2 * i + 1] = f.y;
+            }
+        }
+    }
+}
+
+// WORLD > 0: the rank count is known at compile time (2, 4 or 8). Every lane then issues all of an iteration's
+// loads at once - WORLD sources x ILP tiles = 8 vectors of 16 bytes - which is what it takes to cover NVLink's
+// latency at its bandwidth; the additions still run in rank order. WORLD == 0 is the general form.
+template <int DT, bool CHECK, int WORLD>
 __global__ void __cluster_dims__(CLUSTER, 1, 1) __launch_bounds__(THREADS)
     k_pull_sumsq(PeerTable peers, int world, TileMap map, const uint32_t* __restrict__ tile_meta,
                  const uint8_t* __restrict__ present, float inv_scale, float clamp_hi, int clamp_on,
                  float* __restrict__ reduced, double* __restrict__ partials) {
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     NormAcc a;
-    const uint32_t per_iter = gridDim.x * WARPS;
-    for (uint32_t lt = blockIdx.x * WARPS + warp; lt < map.n_local_tiles; lt += per_iter) {
-        const uint32_t ft = flat_tile(map, lt);
-        uint32_t meta = 0;
-        if constexpr (CHECK) meta = tile_meta[ft];
-        const uint64_t fe = static_cast<uint64_t>(ft) * TILE + lane * 8;
-        float s[8];
-        load8<DT>(peers.grads[0], fe, s);
-        // Up to four peers in flight at a time keeps NVLink busy; the additions stay in rank order.
-        int r = 1;
-        for (; r + 3 < world; r += 4) {
-            float p0[8], p1[8], p2[8], p3[8];
-            load8<DT>(peers.grads[r], fe, p0);
-            load8<DT>(peers.grads[r + 1], fe, p1);
-            load8<DT>(peers.grads[r + 2], fe, p2);
-            load8<DT>(peers.grads[r + 3], fe, p3);
+    if constexpr (WORLD > 0) {
+        constexpr int ILP = 8 / WORLD;
+        const uint32_t per_iter = gridDim.x * WARPS * ILP;
+        for (uint32_t base = (blockIdx.x * WARPS + warp) * ILP; base < map.n_local_tiles; base += per_iter) {
+            RawVec<DT> raw[ILP][WORLD];
+            bool on[ILP];
+            uint32_t meta[ILP];
 #pragma unroll
-            for (int i = 0; i < 8; i++)
-                s[i] = __fadd_rn(__fadd_rn(__fadd_rn(__fadd_rn(s[i], p0[i]), p1[i]), p2[i]), p3[i]);
-        }
-        for (; r < world; r++) {
-            float p0[8];
-            load8<DT>(peers.grads[r], fe, p0);
+            for (int j = 0; j < ILP; j++) {
+                const uint32_t lt = base + j;
+                on[j] = lt < map.n_local_tiles;
+                if (on[j]) {
+                    const uint32_t ft = flat_tile(map, lt);
+                    const uint64_t fe = static_cast<uint64_t>(ft) * TILE + lane * 8;
 #pragma unroll
-            for (int i = 0; i < 8; i++) s[i] = __fadd_rn(s[i], p0[i]);
+                    for (int r = 0; r < WORLD; r++) load_raw<DT>(peers.grads[r], fe, raw[j][r]);
+                    if constexpr (CHECK) meta[j] = tile_meta[ft];
+                }
+            }
+#pragma unroll
+            for (int j = 0; j < ILP; j++) {
+                if (!on[j]) continue;
+                if constexpr (CHECK) {
+                    if (meta[j] == PAD_TILE || !present[meta[j] & 0xffffffu]) continue;
+                }
+                float s[8];
+                widen_raw<DT>(raw[j][0], s);
+#pragma unroll
+                for (int r = 1; r < WORLD; r++) {
+                    float p[8];
+                    widen_raw<DT>(raw[j][r], p);
+#pragma unroll
+                    for (int i = 0; i < 8; i++) s[i] = __fadd_rn(s[i], p[i]);
+                }
+                store8<OXZ_F32>(reduced, static_cast<uint64_t>(base + j) * TILE + lane * 8, s);
+                acc8(s, inv_scale, clamp_hi, clamp_on != 0, a);
+            }
         }
-        if constexpr (CHECK) {
-            if (meta == PAD_TILE || !present[meta & 0xffffffu]) continue;
+    } else {
+        const uint32_t per_iter = gridDim.x * WARPS;
+        for (uint32_t lt = blockIdx.x * WARPS + warp; lt < map.n_local_tiles; lt += per_iter) {
+            const uint32_t ft = flat_tile(map, lt);
+            uint32_t meta = 0;
+            if constexpr (CHECK) meta = tile_meta[ft];
+            const uint64_t fe = static_cast<uint64_t>(ft) * TILE + lane * 8;
+            float s[8];
+            load8<DT>(peers.grads[0], fe, s);
+            int r = 1;
+            for (; r + 1 < world; r += 2) {
+                float p0[8], p1[8];
+                load8<DT>(peers.grads[r], fe, p0);
+                load8<DT>(peers.grads[r + 1], fe, p1);
+#pragma unroll
+                for (int i = 0; i < 8; i++) s[i] = __fadd_rn(__fadd_rn(s[i], p0[i]), p1[i]);
+            }
+            for (; r < world; r++) {
+                float p0[8];
+                load8<DT>(peers.grads[r], fe, p0);
+#pragma unroll
+                for (int i = 0; i < 8; i++) s[i] = __fadd_rn(s[i], p0[i]);
+            }
+            if constexpr (CHECK) {
+                if (meta == PAD_TILE || !present[meta & 0xffffffu]) continue;
+            }
+            store8<OXZ_F32>(reduced, static_cast<uint64_t>(lt) * TILE + lane * 8, s);
+            acc8(s, inv_scale, clamp_hi, clamp_on != 0, a);
         }
-        store8<OXZ_F32>(reduced, static_cast<uint64_t>(lt) * TILE + lane * 8, s);
-        acc8(s, inv_scale, clamp_hi, clamp_on != 0, a);
     }
     cluster_reduce_store(a, partials);
 }
@@ -521,12 +598,26 @@ int32_t query_geom(int device, LaunchGeom* g) {
     const void* funcs[] = {
         (const void*)k_sumsq<OXZ_F32, 4, false>,  (const void*)k_sumsq<OXZ_BF16, 4, false>, (const void*)k_sumsq<OXZ_F16, 4, false>,
         (const void*)k_sumsq<OXZ_F32, 4, true>,   (const void*)k_sumsq<OXZ_BF16, 4, true>,  (const void*)k_sumsq<OXZ_F16, 4, true>,
-        (const void*)k_pull_sumsq<OXZ_F32, false>, (const void*)k_pull_sumsq<OXZ_BF16, false>, (const void*)k_pull_sumsq<OXZ_F16, false>,
-        (const void*)k_pull_sumsq<OXZ_F32, true>,  (const void*)k_pull_sumsq<OXZ_BF16, true>,  (const void*)k_pull_sumsq<OXZ_F16, true>,
         (const void*)k_sumsq_plain<OXZ_F32>, (const void*)k_sumsq_plain<OXZ_BF16>, (const void*)k_sumsq_plain<OXZ_F16>};
     for (const void* f : funcs) {
         const int m = max_cluster_blocks(f, nb);
         if (m < nb) nb = m;
+    }
+    // the pull kernels hold up to eight vectors per lane; their register use, and so their grid, depends on the dtype
+    const void* pulls[3][8] = {
+        {(const void*)k_pull_sumsq<OXZ_F32, false, 0>, (const void*)k_pull_sumsq<OXZ_F32, true, 0>, (const void*)k_pull_sumsq<OXZ_F32, false, 2>, (const void*)k_pull_sumsq<OXZ_F32, true, 2>,
+         (const void*)k_pull_sumsq<OXZ_F32, false, 4>, (const void*)k_pull_sumsq<OXZ_F32, true, 4>, (const void*)k_pull_sumsq<OXZ_F32, false, 8>, (const void*)k_pull_sumsq<OXZ_F32, true, 8>},
+        {(const void*)k_pull_sumsq<OXZ_BF16, false, 0>, (const void*)k_pull_sumsq<OXZ_BF16, true, 0>, (const void*)k_pull_sumsq<OXZ_BF16, false, 2>, (const void*)k_pull_sumsq<OXZ_BF16, true, 2>,
+         (const void*)k_pull_sumsq<OXZ_BF16, false, 4>, (const void*)k_pull_sumsq<OXZ_BF16, true, 4>, (const void*)k_pull_sumsq<OXZ_BF16, false, 8>, (const void*)k_pull_sumsq<OXZ_BF16, true, 8>},
+        {(const void*)k_pull_sumsq<OXZ_F16, false, 0>, (const void*)k_pull_sumsq<OXZ_F16, true, 0>, (const void*)k_pull_sumsq<OXZ_F16, false, 2>, (const void*)k_pull_sumsq<OXZ_F16, true, 2>,
+         (const void*)k_pull_sumsq<OXZ_F16, false, 4>, (const void*)k_pull_sumsq<OXZ_F16, true, 4>, (const void*)k_pull_sumsq<OXZ_F16, false, 8>, (const void*)k_pull_sumsq<OXZ_F16, true, 8>}};
+    for (int dt = 0; dt < 3; dt++) {
+        int pb = nb;
+        for (const void* f : pulls[dt]) {
+            const int m = max_cluster_blocks(f, pb);
+            if (m < pb) pb = m;
+        }
+        g->pull_blocks[dt] = pb > 0 ? pb : CLUSTER;
     }
     g->norm_blocks = nb > 0 ? nb : CLUSTER;
     g->adam_blocks = g->sm_count * adam_blocks_per_sm(adam_variant());
@@ -534,6 +625,9 @@ int32_t query_geom(int device, LaunchGeom* g) {
 }
 
 uint32_t norm_partial_slots(const LaunchGeom& g) { return static_cast<uint32_t>(g.norm_blocks / CLUSTER); }
+uint32_t pull_partial_slots(const LaunchGeom& g, int32_t dt) {
+    return static_cast<uint32_t>(g.pull_blocks[dt == OXZ_F32 ? 0 : dt == OXZ_BF16 ? 1 : 2] / CLUSTER);
+}
 
 static int32_t check_launch(const char* what) {
     cudaError_t e = cudaGetLastError();
@@ -575,18 +669,30 @@ int32_t launch_sumsq_plain(cudaStream_t s, int blocks, const void* grads, int32_
     return check_launch("k_sumsq_plain");
 }
 
+template <bool CHECK, int WORLD>
+static int32_t launch_pull_w(cudaStream_t s, const LaunchGeom& g, const PeerTable& peers, int32_t world, int32_t dt,
+                             const TileMap& map, const uint32_t* tile_meta, const uint8_t* present, float inv_scale,
+                             float clamp_hi, int32_t clamp_on, float* reduced, double* partials) {
+    dim3 grid(g.pull_blocks[dt == OXZ_F32 ? 0 : dt == OXZ_BF16 ? 1 : 2]), block(THREADS);
+    switch (dt) {
+        case OXZ_F32: k_pull_sumsq<OXZ_F32, CHECK, WORLD><<<grid, block, 0, s>>>(peers, world, map, tile_meta, present, inv_scale, clamp_hi, clamp_on, reduced, partials); break;
+        case OXZ_BF16: k_pull_sumsq<OXZ_BF16, CHECK, WORLD><<<grid, block, 0, s>>>(peers, world, map, tile_meta, present, inv_scale, clamp_hi, clamp_on, reduced, partials); break;
+        case OXZ_F16: k_pull_sumsq<OXZ_F16, CHECK, WORLD><<<grid, block, 0, s>>>(peers, world, map, tile_meta, present, inv_scale, clamp_hi, clamp_on, reduced, partials); break;
+        default: return fail(OXZ_ERR_INVALID, "unknown gradient dtype %d", dt);
+    }
+    return check_launch("k_pull_sumsq");
+}
+
 template <bool CHECK>
 static int32_t launch_pull_c(cudaStream_t s, const LaunchGeom& g, const PeerTable& peers, int32_t world, int32_t dt,
                              const TileMap& map, const uint32_t* tile_meta, const uint8_t* present, float inv_scale,
                              float clamp_hi, int32_t clamp_on, float* reduced, double* partials) {
-    dim3 grid(g.norm_blocks), block(THREADS);
-    switch (dt) {
-        case OXZ_F32: k_pull_sumsq<OXZ_F32, CHECK><<<grid, block, 0, s>>>(peers, world, map, tile_meta, present, inv_scale, clamp_hi, clamp_on, reduced, partials); break;
-        case OXZ_BF16: k_pull_sumsq<OXZ_BF16, CHECK><<<grid, block, 0, s>>>(peers, world, map, tile_meta, present, inv_scale, clamp_hi, clamp_on, reduced, partials); break;
-        case OXZ_F16: k_pull_sumsq<OXZ_F16, CHECK><<<grid, block, 0, s>>>(peers, world, map, tile_meta, present, inv_scale, clamp_hi, clamp_on, reduced, partials); break;
-        default: return fail(OXZ_ERR_INVALID, "unknown gradient dtype %d", dt);
+    switch (world) {
+        case 2: return launch_pull_w<CHECK, 2>(s, g, peers, world, dt, map, tile_meta, present, inv_scale, clamp_hi, clamp_on, reduced, partials);
+        case 4: return launch_pull_w<CHECK, 4>(s, g, peers, world, dt, map, tile_meta, present, inv_scale, clamp_hi, clamp_on, reduced, partials);
+        case 8: return launch_pull_w<CHECK, 8>(s, g, peers, world, dt, map, tile_meta, present, inv_scale, clamp_hi, clamp_on, reduced, partials);
+        default: return launch_pull_w<CHECK, 0>(s, g, peers, world, dt, map, tile_meta, present, inv_scale, clamp_hi, clamp_on, reduced, partials);
     }
-    return check_launch("k_pull_sumsq");
 }
 
 int32_t launch_pull_sumsq(cudaStream_t s, const LaunchGeom& g, const PeerTable& peers, int32_t world, int32_t dt,

@@ -388,7 +388,7 @@ int32_t oxz_step_async(oxz_plan* p, oxz_comm* comm, const oxz_hyper* h, const ui
     fp.spike_skip = h->spike_skip ? 1 : 0;
 
     const TileMap map = tile_map(p);
-    const uint32_t slots = norm_partial_slots(p->geom);
+    const uint32_t slots = p->mode == OXZ_SYNC_P2P ? pull_partial_slots(p->geom, p->gdt) : norm_partial_slots(p->geom);
     const void* gsrc = p->grads;
     int32_t gsrc_dt = p->gdt;
     int32_t* bar = p->world > 1 ? reinterpret_cast<int32_t*>(static_cast<char*>(comm->d_small) + 384) : nullptr;
