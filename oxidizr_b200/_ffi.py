@@ -112,6 +112,8 @@ SIGNATURES = {
     "oxz_state_export": (C.c_int32, [vp, C.c_int32, C.c_uint64, vp]),
     "oxz_state_set_timestep": (C.c_int32, [vp, C.c_uint64]),
     "oxz_state_timestep": (C.c_int32, [vp, u64p]),
+    "oxz_optimizer_save": (C.c_int32, [vp, vp, C.c_char_p, C.POINTER(C.c_char_p), C.POINTER(C.c_uint32), u64p]),
+    "oxz_optimizer_load": (C.c_int32, [vp, C.c_char_p, C.POINTER(C.c_char_p), C.POINTER(C.c_uint32), u64p]),
     "oxz_grads_flatten_async": (C.c_int32, [vp, C.POINTER(vp), C.c_int32]),
     "oxz_grads_upload_async": (C.c_int32, [vp, C.c_uint64, vp]),
     "oxz_step_async": (C.c_int32, [vp, vp, C.POINTER(Hyper), u8p, f64p, C.c_uint32]),

@@ -172,6 +172,21 @@ int32_t comm_stream_allreduce_f64(oxz_comm* c, double* d_buf, uint32_t n, double
     return OXZ_OK;
 }
 
+int32_t comm_stream_allreduce_u32(oxz_comm* c, uint32_t* d_buf, uint64_t n, cudaStream_t s) {
+    if (c->kind == 1) {
+        std::vector<uint32_t> host(n);
+        OXZ_CUDA(cudaMemcpyAsync(host.data(), d_buf, n * 4, cudaMemcpyDeviceToHost, s));
+        OXZ_CUDA(cudaStreamSynchronize(s));
+        OXZ_TRY(local_sum<uint32_t>(c, host.data(), n, "the state merge"));
+        OXZ_CUDA(cudaMemcpyAsync(d_buf, host.data(), n * 4, cudaMemcpyHostToDevice, s));
+        OXZ_CUDA(cudaStreamSynchronize(s));
+        return OXZ_OK;
+    }
+    ncclResult_t rc = nccl_api()->AllReduce(d_buf, d_buf, n, ncclUint32, ncclSum, (ncclComm_t)c->nccl, s);
+    if (rc != ncclSuccess) return nccl_fail("the state merge", rc);
+    return OXZ_OK;
+}
+
 int32_t comm_allgather_host(oxz_comm* c, const void* in, void* out_all, size_t bytes, cudaStream_t s) {
     if (c->kind == 1) return local_gather(c, in, out_all, bytes, "peer rendezvous");
     char* d_all = nullptr;

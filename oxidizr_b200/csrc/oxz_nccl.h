@@ -38,6 +38,8 @@ int32_t comm_check(oxz_comm* c, const char* who);
 int32_t comm_stream_barrier(oxz_comm* c, int32_t* d_flag, cudaStream_t s);
 // Sum of n device doubles over ranks, in place. h_tmp: n pinned doubles of staging for the local kind.
 int32_t comm_stream_allreduce_f64(oxz_comm* c, double* d_buf, uint32_t n, double* h_tmp, cudaStream_t s);
+// Sum of n device 32-bit words over ranks, in place (merging disjoint slices bit for bit). Blocking for a local group.
+int32_t comm_stream_allreduce_u32(oxz_comm* c, uint32_t* d_buf, uint64_t n, cudaStream_t s);
 // All-gather of `bytes` host bytes per rank into out_all (world * bytes), blocking.
 int32_t comm_allgather_host(oxz_comm* c, const void* in, void* out_all, size_t bytes, cudaStream_t s);
 }

@@ -440,6 +440,28 @@ class DpOptimizer:
     def timestep(self, t: int) -> None:
         check(lib().oxz_state_set_timestep(self._h, t))
 
+    # -- optimizer state file
+    def _names_shapes(self, tensors):
+        T = len(tensors)
+        if T != len(self.numel):
+            raise ValueError(f"{T} tensors named, the optimizer holds {len(self.numel)}")
+        names = (C.c_char_p * max(T, 1))(*[t.name.encode() for t in tensors])
+        ndim = (C.c_uint32 * max(T, 1))(*[len(t.shape) for t in tensors])
+        flat = [d for t in tensors for d in t.shape]
+        dims = (C.c_uint64 * max(len(flat), 1))(*flat)
+        return names, ndim, dims
+
+    def save_optimizer(self, path: str, tensors: list["TensorInfo"]) -> None:
+        """Write `<name>.exp_avg/.exp_avg_sq/.master` and `__step` as the reference's optimizer file does
+        (src/checkpoint_set/optimizer_io.rs:62-74). Collective at world > 1; rank 0 writes."""
+        names, ndim, dims = self._names_shapes(tensors)
+        check(lib().oxz_optimizer_save(self._h, self.comm.handle if self.comm else None, path.encode(), names, ndim, dims))
+
+    def load_optimizer(self, path: str, tensors: list["TensorInfo"]) -> None:
+        """Strict load of an optimizer file (src/checkpoint_set/optimizer_io.rs:113-137)."""
+        names, ndim, dims = self._names_shapes(tensors)
+        check(lib().oxz_optimizer_load(self._h, path.encode(), names, ndim, dims))
+
     # -- gradients in
     def flatten_grads(self, device_ptrs: list[int | None], accumulate: bool = False) -> None:
         arr = (C.c_void_p * max(len(device_ptrs), 1))(*[C.c_void_p(p) if p else None for p in device_ptrs])
