@@ -35,6 +35,9 @@ HYPER = dict(lr=3e-4, beta1=0.9, beta2=0.95, eps=1e-8, weight_decay=0.1, max_gra
 # Algorithmic HBM bytes per parameter: the norm pass reads the bf16 gradient (2); the update reads gradient 2 +
 # master 4 + m 4 + v 4 and writes master 4 + m 4 + v 4 + bf16 weight 2 (28).
 BYTES_NORM, BYTES_UPDATE = 2, 28
+# DRAM bytes over algorithmic bytes of k_adamw from one ncu capture of a smaller case of the same kernel
+# (profiles/k_adamw_k_sumsq_nano_dense_ncu_full.md): 3.7008 GB read+write for 3.7573 GB algorithmic.
+ADAMW_TRAFFIC_RATIO = 3.7008 / 3.7573
 
 
 def measured_peaks():
@@ -292,7 +295,9 @@ def run_gpu(args):
                    "l2": "inputs larger than L2: 30 B/param x %d params per rank per step" % int(local_params),
                    "hyper": HYPER},
         "roofline": {"bound": "hbm", "kernel": "k_adamw", "achieved": achieved, "peak": peak, "unit": "GB/s",
-                     "frac": achieved / peak, "peak_kind": peak_kind, "traffic": None,
+                     "frac": achieved / peak, "peak_kind": peak_kind,
+                     "traffic": ADAMW_TRAFFIC_RATIO * BYTES_UPDATE * local_params,
+                     "traffic_source": "ncu capture of nano_dense scaled by parameters per launch",
                      "algorithmic_bytes_per_launch": BYTES_UPDATE * local_params, "kernel_ms": upd,
                      "norm_kernel": {"kernel": "k_pull_sumsq" if mode == ox.SYNC_P2P else "k_sumsq", "kernel_ms": nrm}},
         "phases_ms": {k: statistics.mean(getattr(p, k) for p in profs) for k in
