@@ -90,18 +90,6 @@ class ClockSampler:
                 "samples": len(self.sm), "reasons": reasons}
 
 
-def device_view(ptr: int, nbytes: int, dtype):
-    """A torch tensor over library-owned device memory (no copy)."""
-    import torch
-
-    class _Mem:
-        pass
-
-    m = _Mem()
-    m.__cuda_array_interface__ = {"shape": (nbytes,), "typestr": "|u1", "data": (ptr, False), "version": 3}
-    return torch.as_tensor(m, device="cuda").view(dtype)
-
-
 def tiled_normal(n: int, std: float, seed: int, absolute: bool = False) -> np.ndarray:
     """n seeded N(0, std) values; a 4M-value block repeated, which keeps host generation short."""
     block = np.random.default_rng(seed).standard_normal(min(n, 1 << 22)).astype(np.float32) * np.float32(std)
@@ -166,6 +154,7 @@ def run_gpu(args):
     import torch
     import oxidizr_b200 as ox
     from oxidizr_b200 import inventory
+    from oxidizr_b200.interop import device_view
 
     rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
@@ -199,11 +188,11 @@ def run_gpu(args):
 
     # seeded synthetic state, generated on the device straight into the library's buffers
     gen = torch.Generator(device="cuda")
-    grads = device_view(ptr["grads"], info.padded_total * 2, torch.bfloat16)
-    work = device_view(ptr["work"], info.padded_total * 2, torch.bfloat16)
-    master = device_view(ptr["master"], info.local_elems * 4, torch.float32)
-    m = device_view(ptr["exp_avg"], info.local_elems * 4, torch.float32)
-    v = device_view(ptr["exp_avg_sq"], info.local_elems * 4, torch.float32)
+    grads = device_view(ptr["grads"], info.padded_total * 2, torch.bfloat16, local_rank)
+    work = device_view(ptr["work"], info.padded_total * 2, torch.bfloat16, local_rank)
+    master = device_view(ptr["master"], info.local_elems * 4, torch.float32, local_rank)
+    m = device_view(ptr["exp_avg"], info.local_elems * 4, torch.float32, local_rank)
+    v = device_view(ptr["exp_avg_sq"], info.local_elems * 4, torch.float32, local_rank)
     gen.manual_seed(SEED)
     chunk = 1 << 26
     for lo in range(0, info.local_elems, chunk):
