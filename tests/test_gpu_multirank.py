@@ -181,3 +181,44 @@ def test_nccl_mode_matches_within_its_wire_precision(gd):
         assert res.applied == 1 and abs(res.grad_norm - ref.grad_norm) <= max(rel, 1e-5) * ref.grad_norm
     g.assert_state(exact=False, rel=rel)
     g.close()
+
+
+def test_f16_loss_scale_run_with_seeded_overflows_over_eight_ranks():
+    """fp16 gradients pre-multiplied by a dynamic loss scale of 65536, eight ranks, and a seeded 1-in-50 step that
+    writes an inf into a random rank's bucket: the skip/backoff decisions must equal the checker's on every step and
+    the state must stay within the 100-step bound (the growth interval is shortened so growth is exercised too)."""
+    world, steps = 8, 100
+    numel = [3000, 64, 5000, 7, 1200]
+    no_decay = [False, True, False, True, False]
+    g = Group(world, [0] * world, "local", gd=ox.F16, pd=ox.F16, seed=50, numel=numel, no_decay=no_decay, bucket_bytes=4096)
+    cfg_scaler = dict(initial=65536.0, growth_interval=20)
+    gpu_scaler = ox.LossScaler(ox.LossScaleConfig(**cfg_scaler))
+    from oracle import host_logic as hl
+    ref_scaler = hl.LossScaler(hl.LossScaleConfig(**cfg_scaler))
+    pick = np.random.default_rng(51)
+    skipped = 0
+    for s in range(steps):
+        scale = gpu_scaler.scale()
+        assert scale == ref_scaler.scale()
+        grads = []
+        for r in range(world):
+            rng = np.random.default_rng(10_000 + 97 * s + r)
+            grads.append([orc.narrow((rng.standard_normal(n) * 1e-3 * scale).astype(np.float32), ox.F16) for n in numel])
+        inject = pick.integers(0, 50) == 0 or s == 7
+        if inject:
+            r, t = int(pick.integers(0, world)), int(pick.choice([0, 2, 4]))
+            grads[r][t][int(pick.integers(0, numel[t]))] = np.array([np.inf], np.float16).view(np.uint16)[0]
+        g.set_grads(grads)
+        out, ref = g.step(ox.StepConfig(lr=1e-3, max_grad_norm=1.0, loss_scale=scale))
+        for res, _ in out:
+            assert (res.overflow, res.applied, res.timestep) == (ref.overflow, ref.applied, ref.timestep), s
+            if not ref.overflow:
+                assert abs(res.grad_norm - ref.grad_norm) <= 1e-5 * ref.grad_norm
+        assert bool(ref.overflow) == bool(inject)
+        skipped += ref.overflow
+        gpu_scaler.record_step(bool(out[0][0].overflow))
+        hl.record_after_step(ref_scaler, bool(ref.overflow), False)
+        assert (gpu_scaler.state().scale, gpu_scaler.state().consecutive_ok) == (ref_scaler.state().scale, ref_scaler.state().consecutive_ok)
+    assert skipped >= 1 and g.opts[0].timestep == steps - skipped
+    g.assert_state(exact=False, rel=1e-4)
+    g.close()
