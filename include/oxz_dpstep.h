@@ -88,6 +88,16 @@ int32_t oxz_broadcast(oxz_comm* comm, void* device_ptr, uint64_t bytes, int32_t 
 /* Barrier over every rank (src/dp/trainer_hooks.rs:104). Blocking. */
 int32_t oxz_barrier(oxz_comm* comm);
 
+/* One thread per rank with a first-failure abort: run_ranks (src/dp/launch.rs:183-272). `body` runs once per rank
+ * (on the calling thread when world is 1). The first rank whose body returns a non-zero status aborts every
+ * communicator in comms (may be NULL) once, so peers blocked in a collective return; all threads are joined; the
+ * status and text of the rank that failed first are returned as "rank r of w failed first: ...", later errors are
+ * dropped. *failed_rank receives that rank, or -1. */
+typedef int32_t (*oxz_rank_body)(int32_t rank, int32_t world, void* user);
+int32_t oxz_run_ranks(int32_t world, oxz_comm* const* comms, oxz_rank_body body, void* user, int32_t* failed_rank);
+/* Sets the calling thread's error text, for a body whose failure did not come from this library. */
+int32_t oxz_set_last_error(const char* message);
+
 /* ------------------------------------------------------------------ plan
  * The flat layout of the trainable parameters and their AdamW groups. Replaces the `declared`
  * (id, shape) list of reduce_step_gradients (src/dp/reduce.rs:45-56) and DecayPlan::param_groups

@@ -8,4 +8,4 @@ from . import _ffi as ffi  # noqa: F401
 from .dpstep import (Communicator, DataPosition, DecayPlan, DpOptimizer, GradScalerState, LitTrainerStep,  # noqa: F401
                      LossScaleConfig, LossScaler, LrPlan, RowLayout, SpikeGuard, SpikeGuardConfig, StepConfig,
                      TensorInfo, TrainerConfig, WeightDecaySpec, compute_grad_norm, compute_grad_norm_static,
-                     step_weighting)
+                     run_ranks, step_weighting)

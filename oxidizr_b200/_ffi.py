@@ -82,6 +82,8 @@ class DataPositionC(C.Structure):
     _fields_ = [("epoch", C.c_uint64), ("row", C.c_uint64)]
 
 
+RankBody = C.CFUNCTYPE(C.c_int32, C.c_int32, C.c_int32, C.c_void_p)
+
 # name -> (restype, argtypes): one row per declaration of include/oxz_dpstep.h
 SIGNATURES = {
     "oxz_abi_version": (C.c_uint32, []),
@@ -99,6 +101,8 @@ SIGNATURES = {
     "oxz_allreduce_f64": (C.c_int32, [vp, f64p, C.c_uint32]),
     "oxz_broadcast": (C.c_int32, [vp, vp, C.c_uint64, C.c_int32]),
     "oxz_barrier": (C.c_int32, [vp]),
+    "oxz_run_ranks": (C.c_int32, [C.c_int32, C.POINTER(vp), RankBody, vp, C.POINTER(C.c_int32)]),
+    "oxz_set_last_error": (C.c_int32, [C.c_char_p]),
     "oxz_plan_create": (C.c_int32, [C.POINTER(PlanDesc), C.POINTER(vp)]),
     "oxz_plan_destroy": (C.c_int32, [vp]),
     "oxz_plan_query": (C.c_int32, [vp, C.POINTER(PlanInfo)]),

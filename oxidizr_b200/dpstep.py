@@ -99,6 +99,37 @@ class Communicator:
         self._h = C.c_void_p()
 
 
+def run_ranks(comms: list["Communicator"], body):
+    """Run ``body(rank, world, comm)`` once per rank, one thread each, and return the values in rank order
+    (run_ranks, src/dp/launch.rs:183-272). The first rank to fail aborts the group, so peers blocked in a collective
+    return; the error raised is the first failure's, with its rank as context."""
+    world = len(comms)
+    values: list = [None] * world
+    errors: list = [None] * world
+
+    def _body(rank, world_, _user):
+        try:
+            values[rank] = body(rank, world_, comms[rank])
+            return ffi.OK
+        except OxzError as e:
+            errors[rank] = e
+            lib().oxz_set_last_error(e.message.encode())
+            return e.status
+        except BaseException as e:  # a panic becomes an error
+            errors[rank] = e
+            lib().oxz_set_last_error(f"panic: {e}".encode())
+            return ffi.ERR_INVALID
+    cb = ffi.RankBody(_body)
+    handles = (C.c_void_p * world)(*[c.handle for c in comms])
+    failed = C.c_int32(-1)
+    status = lib().oxz_run_ranks(world, handles, cb, None, C.byref(failed))
+    if status != ffi.OK:
+        err = OxzError(status, lib().oxz_last_error().decode())
+        err.failed_rank = failed.value
+        raise err from errors[failed.value] if 0 <= failed.value < world else None
+    return values
+
+
 # ------------------------------------------------------------------ loss scale
 @dataclass
 class LossScaleConfig:

@@ -95,3 +95,69 @@ def test_negative_count_is_refused_before_the_collective():
     with pytest.raises(ox.OxzError, match="timeout"):
         ox.Communicator.local_group(2, None, timeout=0.0)
     comms[0].destroy()
+
+
+# ---- the rank launcher (src/dp/launch.rs:296-366: first error wins, panic -> error, no hang)
+
+def test_run_ranks_returns_values_in_rank_order():
+    comms = ox.Communicator.local_group(3, None, timeout=5.0)
+    out = ox.run_ranks(comms, lambda rank, world, comm: (rank, world, comm.sum_counts(rank, 0)[0]))
+    assert out == [(0, 3, 3), (1, 3, 3), (2, 3, 3)]
+    one = ox.Communicator.local_group(1, None)
+    assert ox.run_ranks(one, lambda rank, world, comm: threading.current_thread() is threading.main_thread()) == [True]
+    for c in comms + one:
+        c.destroy()
+
+
+def test_the_first_failure_wins_and_releases_the_blocked_peers():
+    comms = ox.Communicator.local_group(3, None, timeout=30.0)
+
+    def body(rank, world, comm):
+        comm.sum_counts(1, 0)               # step 1: everyone joins
+        if rank == 1:
+            raise ox.OxzError(ffi.ERR_DATA, "the loader of this rank ran out of rows")   # tests/data_parallel.rs:512-542
+        comm.sum_counts(1, 0)               # the peers block here until the abort
+        return rank
+    t0 = time.time()
+    with pytest.raises(ox.OxzError, match="rank 1 of 3 failed first: the loader of this rank ran out of rows") as info:
+        ox.run_ranks(comms, body)
+    assert time.time() - t0 < 10.0, "the peers waited for the timeout instead of the abort"
+    assert info.value.failed_rank == 1 and info.value.status == ffi.ERR_DATA
+    for c in comms:
+        c.destroy()
+
+
+def test_a_panic_becomes_an_error_with_its_rank():
+    comms = ox.Communicator.local_group(2, None, timeout=30.0)
+
+    def body(rank, world, comm):
+        if rank == 0:
+            raise ZeroDivisionError("boom")
+        return comm.sum_counts(1, 0)
+    with pytest.raises(ox.OxzError, match="rank 0 of 2 failed first: panic: boom"):
+        ox.run_ranks(comms, body)
+    for c in comms:
+        c.destroy()
+
+
+def test_a_fault_injected_at_the_nth_collective_surfaces_as_that_ranks_error():
+    # tests/data_parallel_run.rs:283-394: a wrapper communicator that errors at its N-th count all-reduce
+    class FaultyRank:
+        def __init__(self, comm, fail_at):
+            self.comm, self.calls, self.fail_at = comm, 0, fail_at
+
+        def sum_counts(self, a, b):
+            self.calls += 1
+            if self.calls == self.fail_at:
+                raise ox.OxzError(ffi.ERR_NCCL, f"injected failure at collective {self.calls}")
+            return self.comm.sum_counts(a, b)
+    comms = ox.Communicator.local_group(2, None, timeout=30.0)
+
+    def body(rank, world, comm):
+        c = FaultyRank(comm, 3) if rank == 1 else comm
+        return [c.sum_counts(1, 0) for _ in range(5)]
+    with pytest.raises(ox.OxzError, match="rank 1 of 2 failed first: injected failure at collective 3") as info:
+        ox.run_ranks(comms, body)
+    assert info.value.status == ffi.ERR_NCCL
+    for c in comms:
+        c.destroy()
