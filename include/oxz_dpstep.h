@@ -311,6 +311,23 @@ int32_t oxz_rows_advance(const oxz_row_layout* layout, oxz_data_position pos, ui
 int32_t oxz_rows_next_window(const oxz_row_layout* layout, oxz_data_position pos, uint64_t rank, uint64_t seq_len,
                              uint64_t first_row, const uint32_t* tokens, uint64_t n_tokens, uint64_t* rows,
                              int64_t* inputs, int64_t* targets, oxz_data_position* next);
+/* The rank-sliced row loader in stream order (LitDataLoader::with_rank + next_batch, src/data/ranks.rs:25-41,
+ * src/data/positioning.rs:44-68, src/data/batch.rs:51-71) over one little-endian u32 token file mapped read-only
+ * (src/data/source.rs:7-12, 204-230). Rows are seq_len + 1 tokens; rows [first_row, end_row) form the loader's range
+ * (end_row 0 = every whole row; the tail shorter than a row is never read). Opening needs no GPU. */
+typedef struct oxz_loader oxz_loader;
+int32_t oxz_loader_open(const char* path, uint64_t seq_len, uint64_t rank_batch_size, uint64_t rank, uint64_t world,
+                        uint64_t first_row, uint64_t end_row, int32_t device, oxz_loader** out);
+int32_t oxz_loader_close(oxz_loader* loader);
+int32_t oxz_loader_num_rows(const oxz_loader* loader, uint64_t* rows);
+/* LitDataLoader::position / seek (src/data/positioning.rs:14-42): the position is global, every rank seeks the same one. */
+int32_t oxz_loader_position(const oxz_loader* loader, oxz_data_position* pos);
+int32_t oxz_loader_seek(oxz_loader* loader, oxz_data_position pos);
+/* Draws this rank's rows of the next global batch and advances past the whole global batch. *inputs and *targets
+ * are device pointers to [rank_batch_size, seq_len] i64 owned by the loader, valid until the second-next call;
+ * rows (may be NULL) receives the global row indices. Asynchronous on `stream`. */
+int32_t oxz_loader_next_batch_async(oxz_loader* loader, void* stream, int64_t** inputs, int64_t** targets, uint64_t* rows);
+
 /* StepWeighting::over_ranks applied to the summed counts (src/dp/weighting.rs:46-61): counts = {scored, masked ranks}
  * after oxz_allreduce_i64x2. *global_scored = -1 for an unmasked step. Mixed masks are OXZ_ERR_INVALID on every rank. */
 int32_t oxz_step_weighting(uint64_t local_micro_batches, int32_t world, const int64_t counts[2],

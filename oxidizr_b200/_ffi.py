@@ -143,6 +143,13 @@ SIGNATURES = {
     "oxz_rows_next_window": (C.c_int32, [C.POINTER(RowLayoutC), DataPositionC, C.c_uint64, C.c_uint64, C.c_uint64,
                                          C.POINTER(C.c_uint32), C.c_uint64, u64p, i64p, i64p,
                                          C.POINTER(DataPositionC)]),
+    "oxz_loader_open": (C.c_int32, [C.c_char_p, C.c_uint64, C.c_uint64, C.c_uint64, C.c_uint64, C.c_uint64, C.c_uint64,
+                                    C.c_int32, C.POINTER(vp)]),
+    "oxz_loader_close": (C.c_int32, [vp]),
+    "oxz_loader_num_rows": (C.c_int32, [vp, u64p]),
+    "oxz_loader_position": (C.c_int32, [vp, C.POINTER(DataPositionC)]),
+    "oxz_loader_seek": (C.c_int32, [vp, DataPositionC]),
+    "oxz_loader_next_batch_async": (C.c_int32, [vp, vp, C.POINTER(vp), C.POINTER(vp), u64p]),
     "oxz_step_weighting": (C.c_int32, [C.c_uint64, C.c_int32, i64p, u64p, i64p]),
 }
 

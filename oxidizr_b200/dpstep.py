@@ -353,6 +353,42 @@ class RowLayout:
         return rows, inputs, targets, DataPosition(nxt.epoch, nxt.row)
 
 
+class LitDataLoader:
+    """The rank-sliced loader over one u32 token file in stream order (src/data/ranks.rs:25-41, src/data/batch.rs:51-71)."""
+
+    def __init__(self, path: str, batch_size: int, seq_len: int, rank: int = 0, world_size: int = 1, first_row: int = 0,
+                 end_row: int = 0, device: int = 0):
+        self._h = C.c_void_p()
+        check(lib().oxz_loader_open(path.encode(), seq_len, batch_size, rank, world_size, first_row, end_row, device,
+                                    C.byref(self._h)))
+        self.batch_size, self.seq_len, self.rank, self.world_size = batch_size, seq_len, rank, world_size
+
+    def num_rows(self) -> int:
+        v = C.c_uint64()
+        check(lib().oxz_loader_num_rows(self._h, C.byref(v)))
+        return v.value
+
+    def position(self) -> DataPosition:
+        p = ffi.DataPositionC()
+        check(lib().oxz_loader_position(self._h, C.byref(p)))
+        return DataPosition(p.epoch, p.row)
+
+    def seek(self, pos: DataPosition) -> None:
+        check(lib().oxz_loader_seek(self._h, ffi.DataPositionC(pos.epoch, pos.row)))
+
+    def next_batch(self, stream: int | None = None):
+        """(inputs device address, targets device address, global rows): [batch, seq_len] i64 each."""
+        i, t = C.c_void_p(), C.c_void_p()
+        rows = (C.c_uint64 * self.batch_size)()
+        check(lib().oxz_loader_next_batch_async(self._h, C.c_void_p(stream) if stream else None, C.byref(i), C.byref(t), rows))
+        return i.value, t.value, list(rows)
+
+    def close(self) -> None:
+        if self._h:
+            lib().oxz_loader_close(self._h)
+            self._h = C.c_void_p()
+
+
 def step_weighting(local_micro_batches: int, world: int, scored: int, masked_ranks: int):
     """StepWeighting::over_ranks on the summed counts (src/dp/weighting.rs:46-61): (micro_batches, scored or None)."""
     mb, gs = C.c_uint64(), C.c_int64()
