@@ -178,7 +178,7 @@ def run_gpu(args):
     plan = ox.DecayPlan(ox.WeightDecaySpec("skip_1d"), tensors)
     numel = [t.elements for t in tensors]
     P = sum(numel)
-    mode = {"p2p": ox.SYNC_P2P, "nccl": ox.SYNC_NCCL}[args.sync] if world > 1 else ox.SYNC_SINGLE
+    mode = {"p2p": ox.SYNC_P2P, "nccl": ox.SYNC_NCCL, "copy": ox.SYNC_COPY}[args.sync] if world > 1 else ox.SYNC_SINGLE
     opt = ox.DpOptimizer(numel, plan.no_decay, ox.BF16, ox.BF16, world=world, rank=rank, sync_mode=mode,
                          device=local_rank, comm=comm)
     ptr, info = opt.pointers(), opt.info
@@ -288,13 +288,15 @@ def run_gpu(args):
                      "traffic": ADAMW_TRAFFIC_RATIO * BYTES_UPDATE * local_params,
                      "traffic_source": "ncu capture of nano_dense scaled by parameters per launch",
                      "algorithmic_bytes_per_launch": BYTES_UPDATE * local_params, "kernel_ms": upd,
-                     "norm_kernel": {"kernel": "k_pull_sumsq" if mode == ox.SYNC_P2P else "k_sumsq", "kernel_ms": nrm}},
+                     "norm_kernel": {"kernel": "k_pull_sumsq" if mode in (ox.SYNC_P2P, ox.SYNC_COPY) else "k_sumsq", "kernel_ms": nrm}},
         "phases_ms": {k: statistics.mean(getattr(p, k) for p in profs) for k in
                       ("collect_ms", "norm_ms", "decide_ms", "update_ms", "publish_ms", "total_ms")},
         "step_roofline": step_roofline(P, world, ms_per_step, peak),
         "e2e": {"value": e2e_value, "unit": UNIT, "h2d_bytes_per_step": P * 2 * world, "d2h_bytes_per_step": 32 * world,
                 "ms_per_step": e2e_sec * 1e3 / e2e_steps, "steps": e2e_steps},
-        "gpu_launches": 4 * args.steps * world,
+        # kernels of this library per step: norm (or pull) + reduce_partials + finalize + update; the copy mode runs
+        # the pull and the update once per pipeline group (4 groups)
+        "gpu_launches": (10 if mode == ox.SYNC_COPY else 4) * args.steps * world,
         "launch_geometry": opt.launch_geometry(),
         "clocks": clocks,
         "result": {"grad_norm": res.grad_norm, "applied": res.applied, "timestep": res.timestep},
@@ -334,7 +336,7 @@ def main():
     ap.add_argument("--steps", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", choices=["ours", "reference"], default="ours")
-    ap.add_argument("--sync", choices=["p2p", "nccl"], default="p2p", help="how ranks meet at --gpus > 1")
+    ap.add_argument("--sync", choices=["p2p", "copy", "nccl"], default="p2p", help="how ranks meet at --gpus > 1")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--skip-e2e", action="store_true", help="profiling runs: leave the host-fed leg out")
     ap.add_argument("--workload", default=WORKLOAD, help="parameter set; the headline is llama-3.2-1b, smaller sets serve profiler captures")

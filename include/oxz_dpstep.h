@@ -48,7 +48,10 @@ typedef enum oxz_sync_mode {
     OXZ_SYNC_SINGLE = 0, /* world 1: no collective (NoOpCommunicator, src/trainer.rs:234) */
     OXZ_SYNC_P2P = 1,    /* fused kernels over NVLink peer memory: pull-reduce in f32 in rank order,
                             push of the narrow weights; NCCL only for the 3-double norm all-reduce */
-    OXZ_SYNC_NCCL = 2    /* ncclReduceScatter / ncclAllGather in the gradient's own dtype */
+    OXZ_SYNC_NCCL = 2,   /* ncclReduceScatter / ncclAllGather in the gradient's own dtype */
+    OXZ_SYNC_COPY = 3    /* copy engines move the bytes over NVLink (peers' gradient slices into local staging,
+                            the updated weights out to every peer), pipelined by groups of buckets with the
+                            kernels that sum in f32 in rank order, measure the norm and update */
 } oxz_sync_mode;
 
 typedef struct oxz_comm oxz_comm;

@@ -35,7 +35,8 @@ constexpr uint32_t TILE = 256;           // elements per tile: one 8-element vec
 constexpr uint32_t MAX_GROUPS = 8;       // distinct (lr_scale, decay) groups a plan may hold
 constexpr uint32_t PAD_TILE = 0xFFFFFFFFu;  // tile_meta of a tile past the last tensor
 constexpr uint32_t MAX_PEERS = 16;
-constexpr uint32_t MAX_EXTRAS = 13;      // doubles that ride on the norm all-reduce
+constexpr uint32_t MAX_EXTRAS = 13;
+constexpr uint32_t MAX_PIPE = 8;         // groups of buckets a copy-engine step is pipelined in      // doubles that ride on the norm all-reduce
 
 inline size_t dtype_size(int32_t dt) { return dt == OXZ_F32 ? 4 : 2; }
 
@@ -47,7 +48,8 @@ struct TileMap {
     uint32_t n_buckets;
     uint32_t last_shard_tiles;      // tiles a rank owns of the last bucket
     uint32_t rank;
-    uint32_t n_local_tiles;
+    uint32_t n_local_tiles;         // end of the tile range a launch covers
+    uint32_t first_tile;            // start of that range (0 for a whole-shard launch)
 };
 
 // Per-step scalars of the update, rounded to f32 on the host from f64.
@@ -101,7 +103,7 @@ int32_t launch_sumsq_plain(cudaStream_t s, int blocks, const void* grads, int32_
                            float clamp_hi, int32_t clamp_on, double* partials);
 // Pull-reduce: sums this rank's tiles of every peer's gradient buffer in f32 in rank order, stores the sum
 // in `reduced` (local, f32) and accumulates the squares as launch_sumsq does.
-int32_t launch_pull_sumsq(cudaStream_t s, const LaunchGeom& g, const PeerTable& peers, int32_t world, int32_t dt,
+int32_t launch_pull_sumsq(cudaStream_t s, const LaunchGeom& g, const PeerTable& peers, int32_t world, int staged, int32_t dt,
                           const TileMap& map, const uint32_t* tile_meta, const uint8_t* present, bool check_present,
                           float inv_scale, float clamp_hi, int32_t clamp_on, float* reduced, double* partials);
 // partials[slots][3] -> acc[3] = {sum, inf count, nan count}
@@ -175,6 +177,12 @@ struct oxz_plan {
     cudaEvent_t ev[6] = {nullptr, nullptr, nullptr, nullptr, nullptr, nullptr};
     oxz::PeerTable peers{};
     std::vector<void*> ipc_opened;
+    // OXZ_SYNC_COPY: staging for the peers' gradient slices, one copy stream per peer, pipeline events
+    void* stage = nullptr;
+    oxz::PeerTable staged_src{};
+    cudaStream_t copy_stream[oxz::MAX_PEERS] = {};
+    cudaEvent_t ev_go = nullptr, ev_copied[oxz::MAX_PEERS][oxz::MAX_PIPE] = {}, ev_updated[oxz::MAX_PIPE] = {}, ev_pushed[oxz::MAX_PEERS] = {};
+    uint32_t pipe_groups = 1;
     oxz_comm* comm = nullptr;
 
     // step bookkeeping

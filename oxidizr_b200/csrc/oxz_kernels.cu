@@ -218,7 +218,7 @@ __global__ void __cluster_dims__(CLUSTER, 1, 1) __launch_bounds__(THREADS)
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     NormAcc a;
     const uint32_t per_iter = gridDim.x * WARPS * ILP;
-    for (uint32_t base = (blockIdx.x * WARPS + warp) * ILP; base < map.n_local_tiles; base += per_iter) {
+    for (uint32_t base = map.first_tile + (blockIdx.x * WARPS + warp) * ILP; base < map.n_local_tiles; base += per_iter) {
         float g[ILP][8];
         bool on[ILP];
         uint32_t meta[ILP];
@@ -317,15 +317,17 @@ __device__ __forceinline__ void widen_raw(const RawVec<DT>& r, float (&x)[8]) {
 // latency at its bandwidth; the additions still run in rank order. WORLD == 0 is the general form.
 template <int DT, bool CHECK, int WORLD>
 __global__ void __cluster_dims__(CLUSTER, 1, 1) __launch_bounds__(THREADS)
-    k_pull_sumsq(PeerTable peers, int world, TileMap map, const uint32_t* __restrict__ tile_meta,
+    k_pull_sumsq(PeerTable peers, int world, int staged, TileMap map, const uint32_t* __restrict__ tile_meta,
                  const uint8_t* __restrict__ present, float inv_scale, float clamp_hi, int clamp_on,
                  float* __restrict__ reduced, double* __restrict__ partials) {
+    // staged != 0: the other ranks' gradients were copied into local staging buffers laid out like this rank's
+    // state (indexed by local element); this rank's own gradients are read in place (indexed by flat element).
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     NormAcc a;
     if constexpr (WORLD > 0) {
         constexpr int ILP = 8 / WORLD;
         const uint32_t per_iter = gridDim.x * WARPS * ILP;
-        for (uint32_t base = (blockIdx.x * WARPS + warp) * ILP; base < map.n_local_tiles; base += per_iter) {
+        for (uint32_t base = map.first_tile + (blockIdx.x * WARPS + warp) * ILP; base < map.n_local_tiles; base += per_iter) {
             RawVec<DT> raw[ILP][WORLD];
             bool on[ILP];
             uint32_t meta[ILP];
@@ -336,8 +338,10 @@ __global__ void __cluster_dims__(CLUSTER, 1, 1) __launch_bounds__(THREADS)
                 if (on[j]) {
                     const uint32_t ft = flat_tile(map, lt);
                     const uint64_t fe = static_cast<uint64_t>(ft) * TILE + lane * 8;
+                    const uint64_t le = static_cast<uint64_t>(lt) * TILE + lane * 8;
 #pragma unroll
-                    for (int r = 0; r < WORLD; r++) load_raw<DT>(peers.grads[r], fe, raw[j][r]);
+                    for (int r = 0; r < WORLD; r++)
+                        load_raw<DT>(peers.grads[r], (staged && r != static_cast<int>(map.rank)) ? le : fe, raw[j][r]);
                     if constexpr (CHECK) meta[j] = tile_meta[ft];
                 }
             }
@@ -362,24 +366,26 @@ __global__ void __cluster_dims__(CLUSTER, 1, 1) __launch_bounds__(THREADS)
         }
     } else {
         const uint32_t per_iter = gridDim.x * WARPS;
-        for (uint32_t lt = blockIdx.x * WARPS + warp; lt < map.n_local_tiles; lt += per_iter) {
+        for (uint32_t lt = map.first_tile + blockIdx.x * WARPS + warp; lt < map.n_local_tiles; lt += per_iter) {
             const uint32_t ft = flat_tile(map, lt);
             uint32_t meta = 0;
             if constexpr (CHECK) meta = tile_meta[ft];
             const uint64_t fe = static_cast<uint64_t>(ft) * TILE + lane * 8;
+            const uint64_t le = static_cast<uint64_t>(lt) * TILE + lane * 8;
+            const int me = static_cast<int>(map.rank);
             float s[8];
-            load8<DT>(peers.grads[0], fe, s);
+            load8<DT>(peers.grads[0], (staged && me != 0) ? le : fe, s);
             int r = 1;
             for (; r + 1 < world; r += 2) {
                 float p0[8], p1[8];
-                load8<DT>(peers.grads[r], fe, p0);
-                load8<DT>(peers.grads[r + 1], fe, p1);
+                load8<DT>(peers.grads[r], (staged && r != me) ? le : fe, p0);
+                load8<DT>(peers.grads[r + 1], (staged && r + 1 != me) ? le : fe, p1);
 #pragma unroll
                 for (int i = 0; i < 8; i++) s[i] = __fadd_rn(__fadd_rn(s[i], p0[i]), p1[i]);
             }
             for (; r < world; r++) {
                 float p0[8];
-                load8<DT>(peers.grads[r], fe, p0);
+                load8<DT>(peers.grads[r], (staged && r != me) ? le : fe, p0);
 #pragma unroll
                 for (int i = 0; i < 8; i++) s[i] = __fadd_rn(s[i], p0[i]);
             }
@@ -462,7 +468,7 @@ __global__ void __launch_bounds__(THREADS, MINB)
     const float c1 = scalars->c1, c2 = scalars->c2;
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     const uint32_t per_iter = gridDim.x * WARPS * ILP;
-    for (uint32_t base = (blockIdx.x * WARPS + warp) * ILP; base < map.n_local_tiles; base += per_iter) {
+    for (uint32_t base = map.first_tile + (blockIdx.x * WARPS + warp) * ILP; base < map.n_local_tiles; base += per_iter) {
         float g[ILP][8], p[ILP][8], m[ILP][8], v[ILP][8];
         bool on[ILP];
         uint32_t ftile[ILP], meta[ILP];
@@ -670,36 +676,36 @@ int32_t launch_sumsq_plain(cudaStream_t s, int blocks, const void* grads, int32_
 }
 
 template <bool CHECK, int WORLD>
-static int32_t launch_pull_w(cudaStream_t s, const LaunchGeom& g, const PeerTable& peers, int32_t world, int32_t dt,
+static int32_t launch_pull_w(cudaStream_t s, const LaunchGeom& g, const PeerTable& peers, int32_t world, int staged, int32_t dt,
                              const TileMap& map, const uint32_t* tile_meta, const uint8_t* present, float inv_scale,
                              float clamp_hi, int32_t clamp_on, float* reduced, double* partials) {
     dim3 grid(g.pull_blocks[dt == OXZ_F32 ? 0 : dt == OXZ_BF16 ? 1 : 2]), block(THREADS);
     switch (dt) {
-        case OXZ_F32: k_pull_sumsq<OXZ_F32, CHECK, WORLD><<<grid, block, 0, s>>>(peers, world, map, tile_meta, present, inv_scale, clamp_hi, clamp_on, reduced, partials); break;
-        case OXZ_BF16: k_pull_sumsq<OXZ_BF16, CHECK, WORLD><<<grid, block, 0, s>>>(peers, world, map, tile_meta, present, inv_scale, clamp_hi, clamp_on, reduced, partials); break;
-        case OXZ_F16: k_pull_sumsq<OXZ_F16, CHECK, WORLD><<<grid, block, 0, s>>>(peers, world, map, tile_meta, present, inv_scale, clamp_hi, clamp_on, reduced, partials); break;
+        case OXZ_F32: k_pull_sumsq<OXZ_F32, CHECK, WORLD><<<grid, block, 0, s>>>(peers, world, staged, map, tile_meta, present, inv_scale, clamp_hi, clamp_on, reduced, partials); break;
+        case OXZ_BF16: k_pull_sumsq<OXZ_BF16, CHECK, WORLD><<<grid, block, 0, s>>>(peers, world, staged, map, tile_meta, present, inv_scale, clamp_hi, clamp_on, reduced, partials); break;
+        case OXZ_F16: k_pull_sumsq<OXZ_F16, CHECK, WORLD><<<grid, block, 0, s>>>(peers, world, staged, map, tile_meta, present, inv_scale, clamp_hi, clamp_on, reduced, partials); break;
         default: return fail(OXZ_ERR_INVALID, "unknown gradient dtype %d", dt);
     }
     return check_launch("k_pull_sumsq");
 }
 
 template <bool CHECK>
-static int32_t launch_pull_c(cudaStream_t s, const LaunchGeom& g, const PeerTable& peers, int32_t world, int32_t dt,
+static int32_t launch_pull_c(cudaStream_t s, const LaunchGeom& g, const PeerTable& peers, int32_t world, int staged, int32_t dt,
                              const TileMap& map, const uint32_t* tile_meta, const uint8_t* present, float inv_scale,
                              float clamp_hi, int32_t clamp_on, float* reduced, double* partials) {
     switch (world) {
-        case 2: return launch_pull_w<CHECK, 2>(s, g, peers, world, dt, map, tile_meta, present, inv_scale, clamp_hi, clamp_on, reduced, partials);
-        case 4: return launch_pull_w<CHECK, 4>(s, g, peers, world, dt, map, tile_meta, present, inv_scale, clamp_hi, clamp_on, reduced, partials);
-        case 8: return launch_pull_w<CHECK, 8>(s, g, peers, world, dt, map, tile_meta, present, inv_scale, clamp_hi, clamp_on, reduced, partials);
-        default: return launch_pull_w<CHECK, 0>(s, g, peers, world, dt, map, tile_meta, present, inv_scale, clamp_hi, clamp_on, reduced, partials);
+        case 2: return launch_pull_w<CHECK, 2>(s, g, peers, world, staged, dt, map, tile_meta, present, inv_scale, clamp_hi, clamp_on, reduced, partials);
+        case 4: return launch_pull_w<CHECK, 4>(s, g, peers, world, staged, dt, map, tile_meta, present, inv_scale, clamp_hi, clamp_on, reduced, partials);
+        case 8: return launch_pull_w<CHECK, 8>(s, g, peers, world, staged, dt, map, tile_meta, present, inv_scale, clamp_hi, clamp_on, reduced, partials);
+        default: return launch_pull_w<CHECK, 0>(s, g, peers, world, staged, dt, map, tile_meta, present, inv_scale, clamp_hi, clamp_on, reduced, partials);
     }
 }
 
-int32_t launch_pull_sumsq(cudaStream_t s, const LaunchGeom& g, const PeerTable& peers, int32_t world, int32_t dt,
+int32_t launch_pull_sumsq(cudaStream_t s, const LaunchGeom& g, const PeerTable& peers, int32_t world, int staged, int32_t dt,
                           const TileMap& map, const uint32_t* tile_meta, const uint8_t* present, bool check_present,
                           float inv_scale, float clamp_hi, int32_t clamp_on, float* reduced, double* partials) {
-    return check_present ? launch_pull_c<true>(s, g, peers, world, dt, map, tile_meta, present, inv_scale, clamp_hi, clamp_on, reduced, partials)
-                         : launch_pull_c<false>(s, g, peers, world, dt, map, tile_meta, present, inv_scale, clamp_hi, clamp_on, reduced, partials);
+    return check_present ? launch_pull_c<true>(s, g, peers, world, staged, dt, map, tile_meta, present, inv_scale, clamp_hi, clamp_on, reduced, partials)
+                         : launch_pull_c<false>(s, g, peers, world, staged, dt, map, tile_meta, present, inv_scale, clamp_hi, clamp_on, reduced, partials);
 }
 
 int32_t launch_reduce_partials(cudaStream_t s, const double* partials, uint32_t slots, double* acc) {

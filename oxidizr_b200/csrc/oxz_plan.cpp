@@ -63,12 +63,12 @@ int32_t oxz_plan_create(const oxz_plan_desc* d, oxz_plan** out) {
     if (d->rank < 0 || d->rank >= d->world)
         return fail(OXZ_ERR_INVALID, "rank %d is not below world size %d. Pass a rank in [0, %d).", d->rank,
                     d->world, d->world);
-    if (d->sync_mode != OXZ_SYNC_SINGLE && d->sync_mode != OXZ_SYNC_P2P && d->sync_mode != OXZ_SYNC_NCCL)
+    if (d->sync_mode < OXZ_SYNC_SINGLE || d->sync_mode > OXZ_SYNC_COPY)
         return fail(OXZ_ERR_INVALID, "oxz_plan_create: unknown sync mode %d", d->sync_mode);
     if ((d->sync_mode == OXZ_SYNC_SINGLE) != (d->world == 1))
         return fail(OXZ_ERR_INVALID,
                     "oxz_plan_create: sync mode %d with world size %d. World 1 runs no collective and takes "
-                    "OXZ_SYNC_SINGLE; more ranks need OXZ_SYNC_P2P or OXZ_SYNC_NCCL",
+                    "OXZ_SYNC_SINGLE; more ranks need OXZ_SYNC_P2P, OXZ_SYNC_COPY or OXZ_SYNC_NCCL",
                     d->sync_mode, d->world);
 
     oxz_plan* p = new oxz_plan();

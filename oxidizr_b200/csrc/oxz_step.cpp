@@ -3,6 +3,7 @@
 #include <unistd.h>
 
 #include <cmath>
+#include <cstdlib>
 #include <cstring>
 #include <map>
 #include <mutex>
@@ -22,6 +23,7 @@ TileMap tile_map(const oxz_plan* p) {
     m.last_shard_tiles = (uint32_t)(p->last_bucket_tiles / (uint64_t)p->world);
     m.rank = (uint32_t)p->rank;
     m.n_local_tiles = (uint32_t)p->local_tiles;
+    m.first_tile = 0;
     return m;
 }
 
@@ -96,6 +98,45 @@ void for_owned_runs(const oxz_plan* p, uint64_t tensor, F fn) {
     }
 }
 
+// Buckets [b0, b1) of pipeline group g: the buckets are split into pipe_groups nearly equal runs.
+void group_buckets(const oxz_plan* p, uint32_t g, uint64_t* b0, uint64_t* b1) {
+    const uint64_t nb = p->n_buckets, G = p->pipe_groups;
+    *b0 = nb * g / G;
+    *b1 = nb * (g + 1) / G;
+}
+
+// The local tile range of buckets [b0, b1).
+void group_tiles(const oxz_plan* p, uint64_t b0, uint64_t b1, uint32_t* first, uint32_t* end) {
+    const uint64_t tps = p->bucket_tiles / (uint64_t)p->world;
+    *first = (uint32_t)(b0 * tps);
+    *end = (uint32_t)(b1 == p->n_buckets ? p->local_tiles : b1 * tps);
+}
+
+// Copies this rank's shard of buckets [b0, b1) between two buffers with the copy engine. A buffer is either flat
+// (the shard of bucket b sits at b * bucket + rank * shard) or packed (at b * shard, the layout of the local state).
+// The full buckets form one strided 2-D copy; a shorter last bucket is one more 1-D copy.
+int32_t copy_shard_rows(const oxz_plan* p, char* dst, bool dst_packed, const char* src, bool src_packed, size_t es,
+                        uint64_t b0, uint64_t b1, cudaStream_t st) {
+    const uint64_t W = (uint64_t)p->world, bucket = p->bucket_tiles * TILE, shard = bucket / W;
+    const uint64_t last = p->n_buckets - 1;
+    const bool has_last = b1 == p->n_buckets && p->last_bucket_tiles != p->bucket_tiles;
+    const uint64_t full_end = has_last ? last : b1;
+    auto at = [&](bool packed, uint64_t b, uint64_t shard_elems) -> uint64_t {
+        return packed ? b * shard : b * bucket + (uint64_t)p->rank * shard_elems;
+    };
+    if (full_end > b0) {
+        OXZ_CUDA(cudaMemcpy2DAsync(dst + at(dst_packed, b0, shard) * es, (dst_packed ? shard : bucket) * es,
+                                   src + at(src_packed, b0, shard) * es, (src_packed ? shard : bucket) * es, shard * es,
+                                   full_end - b0, cudaMemcpyDeviceToDevice, st));
+    }
+    if (has_last && b1 > b0) {
+        const uint64_t lshard = p->last_bucket_tiles * TILE / W;
+        OXZ_CUDA(cudaMemcpyAsync(dst + at(dst_packed, last, lshard) * es, src + at(src_packed, last, lshard) * es, lshard * es,
+                                 cudaMemcpyDeviceToDevice, st));
+    }
+    return OXZ_OK;
+}
+
 float* state_array(oxz_plan* p, int32_t kind) {
     switch (kind) {
         case OXZ_STATE_MASTER: return p->master;
@@ -131,6 +172,12 @@ int32_t oxz_plan_destroy(oxz_plan* p) {
             if (q) cudaFree(q);
         for (void* q : {(void*)p->h_scalars, (void*)p->h_acc, (void*)p->h_extras, (void*)p->h_present, (void*)p->h_src})
             if (q) cudaFreeHost(q);
+        if (p->stage) cudaFree(p->stage);
+        for (auto st : p->copy_stream) if (st) cudaStreamDestroy(st);
+        if (p->ev_go) cudaEventDestroy(p->ev_go);
+        for (auto& row : p->ev_copied) for (auto e : row) if (e) cudaEventDestroy(e);
+        for (auto e : p->ev_updated) if (e) cudaEventDestroy(e);
+        for (auto e : p->ev_pushed) if (e) cudaEventDestroy(e);
         if (p->done) cudaEventDestroy(p->done);
         for (auto e : p->ev) if (e) cudaEventDestroy(e);
         if (p->own_stream) cudaStreamDestroy(p->own_stream);
@@ -175,7 +222,8 @@ int32_t oxz_state_alloc(oxz_plan* p, oxz_comm* comm) {
     const bool separate_work = !(p->pdt == OXZ_F32 && p->world == 1);
     if (separate_work) OXZ_CUDA(zalloc(&p->work, padded * ps));
     else p->work = p->master;
-    if (p->world > 1) OXZ_CUDA(zalloc(&p->reduced, local * (p->mode == OXZ_SYNC_P2P ? 4 : gs)));
+    const bool peer_mode = p->mode == OXZ_SYNC_P2P || p->mode == OXZ_SYNC_COPY;
+    if (p->world > 1) OXZ_CUDA(zalloc(&p->reduced, local * (peer_mode ? 4 : gs)));
     OXZ_CUDA(zalloc((void**)&p->d_tile_meta, p->total_tiles * 4));
     OXZ_CUDA(cudaMemcpy(p->d_tile_meta, p->tile_meta.data(), p->total_tiles * 4, cudaMemcpyHostToDevice));
     OXZ_CUDA(zalloc((void**)&p->d_present, p->T));
@@ -187,7 +235,7 @@ int32_t oxz_state_alloc(oxz_plan* p, oxz_comm* comm) {
         OXZ_CUDA(cudaMemcpy(p->d_numel, p->numel.data(), p->T * 8, cudaMemcpyHostToDevice));
     }
     OXZ_CUDA(zalloc((void**)&p->d_src, p->T * 8));
-    OXZ_CUDA(zalloc((void**)&p->d_partials, (size_t)norm_partial_slots(p->geom) * 3 * 8));
+    OXZ_CUDA(zalloc((void**)&p->d_partials, (size_t)norm_partial_slots(p->geom) * 3 * 8 * MAX_PIPE));
     OXZ_CUDA(zalloc((void**)&p->d_acc, (3 + MAX_EXTRAS) * 8));
     OXZ_CUDA(zalloc((void**)&p->d_scalars, sizeof(DevScalars)));
     OXZ_CUDA(cudaMallocHost((void**)&p->h_scalars, sizeof(DevScalars)));
@@ -200,7 +248,31 @@ int32_t oxz_state_alloc(oxz_plan* p, oxz_comm* comm) {
     OXZ_CUDA(cudaDeviceSynchronize());
     p->peers.grads[0] = p->grads;
     p->peers.work[0] = p->work;
-    if (p->mode == OXZ_SYNC_P2P) OXZ_TRY(exchange_peers(p, comm));
+    if (peer_mode) OXZ_TRY(exchange_peers(p, comm));
+    if (p->mode == OXZ_SYNC_COPY) {
+        // one staging slot per peer, laid out like this rank's local state; the own slot is the gradient buffer itself
+        OXZ_CUDA(zalloc(&p->stage, (size_t)(p->world - 1) * local * gs));
+        int slot = 0;
+        for (int r = 0; r < p->world; r++) {
+            if (r == p->rank) {
+                p->staged_src.grads[r] = p->grads;
+            } else {
+                p->staged_src.grads[r] = static_cast<char*>(p->stage) + (size_t)slot * local * gs;
+                slot++;
+            }
+            OXZ_CUDA(cudaStreamCreateWithFlags(&p->copy_stream[r], cudaStreamNonBlocking));
+            OXZ_CUDA(cudaEventCreateWithFlags(&p->ev_pushed[r], cudaEventDisableTiming));
+            for (uint32_t g = 0; g < MAX_PIPE; g++) OXZ_CUDA(cudaEventCreateWithFlags(&p->ev_copied[r][g], cudaEventDisableTiming));
+        }
+        OXZ_CUDA(cudaEventCreateWithFlags(&p->ev_go, cudaEventDisableTiming));
+        for (uint32_t g = 0; g < MAX_PIPE; g++) OXZ_CUDA(cudaEventCreateWithFlags(&p->ev_updated[g], cudaEventDisableTiming));
+        const char* e = getenv("OXZ_PIPE_GROUPS");
+        uint32_t want = e ? (uint32_t)atoi(e) : 4;
+        if (want < 1) want = 1;
+        if (want > MAX_PIPE) want = MAX_PIPE;
+        if (want > p->n_buckets) want = (uint32_t)p->n_buckets;
+        p->pipe_groups = want;
+    }
     p->allocated = true;
     return OXZ_OK;
 }
@@ -388,7 +460,8 @@ int32_t oxz_step_async(oxz_plan* p, oxz_comm* comm, const oxz_hyper* h, const ui
     fp.spike_skip = h->spike_skip ? 1 : 0;
 
     const TileMap map = tile_map(p);
-    const uint32_t slots = p->mode == OXZ_SYNC_P2P ? pull_partial_slots(p->geom, p->gdt) : norm_partial_slots(p->geom);
+    const bool peer_mode = p->mode == OXZ_SYNC_P2P || p->mode == OXZ_SYNC_COPY;
+    uint32_t slots = peer_mode ? pull_partial_slots(p->geom, p->gdt) : norm_partial_slots(p->geom);
     const void* gsrc = p->grads;
     int32_t gsrc_dt = p->gdt;
     int32_t* bar = p->world > 1 ? reinterpret_cast<int32_t*>(static_cast<char*>(comm->d_small) + 384) : nullptr;
@@ -403,8 +476,38 @@ int32_t oxz_step_async(oxz_plan* p, oxz_comm* comm, const oxz_hyper* h, const ui
         // every rank's gradients must be complete before anyone pulls them
         OXZ_TRY(comm_stream_barrier(comm, bar, s));
         OXZ_CUDA(mark(1));
-        OXZ_TRY(launch_pull_sumsq(s, p->geom, p->peers, p->world, p->gdt, map, p->d_tile_meta, p->d_present, some_absent,
+        OXZ_TRY(launch_pull_sumsq(s, p->geom, p->peers, p->world, 0, p->gdt, map, p->d_tile_meta, p->d_present, some_absent,
                                   ap.inv_scale, ap.clamp_hi, ap.clamp_on, static_cast<float*>(p->reduced), p->d_partials));
+        gsrc = p->reduced;
+        gsrc_dt = OXZ_F32;
+    } else if (p->mode == OXZ_SYNC_COPY) {
+        // every rank's gradients must be complete before anyone copies them
+        OXZ_TRY(comm_stream_barrier(comm, bar, s));
+        OXZ_CUDA(mark(1));
+        OXZ_CUDA(cudaEventRecord(p->ev_go, s));
+        const size_t gs = dtype_size(p->gdt);
+        const uint32_t G = p->pipe_groups;
+        for (int r = 0; r < p->world; r++)
+            if (r != p->rank) OXZ_CUDA(cudaStreamWaitEvent(p->copy_stream[r], p->ev_go, 0));
+        for (uint32_t g = 0; g < G; g++) {
+            uint64_t b0, b1;
+            group_buckets(p, g, &b0, &b1);
+            for (int r = 0; r < p->world; r++) {
+                if (r == p->rank) continue;
+                // the peer's slices of this rank's shard, buckets [b0, b1): a strided read, packed into the slot
+                OXZ_TRY(copy_shard_rows(p, static_cast<char*>(const_cast<void*>(p->staged_src.grads[r])), true,
+                                        static_cast<const char*>(p->peers.grads[r]), false, gs, b0, b1, p->copy_stream[r]));
+                OXZ_CUDA(cudaEventRecord(p->ev_copied[r][g], p->copy_stream[r]));
+            }
+            for (int r = 0; r < p->world; r++)
+                if (r != p->rank) OXZ_CUDA(cudaStreamWaitEvent(s, p->ev_copied[r][g], 0));
+            TileMap gm = map;
+            group_tiles(p, b0, b1, &gm.first_tile, &gm.n_local_tiles);
+            OXZ_TRY(launch_pull_sumsq(s, p->geom, p->staged_src, p->world, 1, p->gdt, gm, p->d_tile_meta, p->d_present, some_absent,
+                                      ap.inv_scale, ap.clamp_hi, ap.clamp_on, static_cast<float*>(p->reduced),
+                                      p->d_partials + (size_t)g * slots * 3));
+        }
+        slots *= G;
         gsrc = p->reduced;
         gsrc_dt = OXZ_F32;
     } else {
@@ -443,9 +546,40 @@ int32_t oxz_step_async(oxz_plan* p, oxz_comm* comm, const oxz_hyper* h, const ui
     OXZ_CUDA(mark(3));
     const bool separate_work = p->work != (void*)p->master;
     const int32_t n_work = !separate_work ? 0 : (p->mode == OXZ_SYNC_P2P ? p->world : 1);
+    if (p->mode == OXZ_SYNC_COPY) {
+        // the update runs group by group; as soon as a group's weights are written the copy engines push them to
+        // every peer while the next group updates
+        const size_t ps = dtype_size(p->pdt);
+        PeerTable own{};
+        own.work[0] = p->work;
+        for (uint32_t g = 0; g < p->pipe_groups; g++) {
+            uint64_t b0, b1;
+            group_buckets(p, g, &b0, &b1);
+            TileMap gm = map;
+            group_tiles(p, b0, b1, &gm.first_tile, &gm.n_local_tiles);
+            OXZ_TRY(launch_adamw(s, p->geom, gsrc, gsrc_dt, p->master, p->exp_avg, p->exp_avg_sq, own, 1, p->pdt, gm,
+                                 p->d_tile_meta, p->d_present, some_absent, p->d_scalars, ap));
+            OXZ_CUDA(cudaEventRecord(p->ev_updated[g], s));
+            for (int r = 0; r < p->world; r++) {
+                if (r == p->rank) continue;
+                OXZ_CUDA(cudaStreamWaitEvent(p->copy_stream[r], p->ev_updated[g], 0));
+                OXZ_TRY(copy_shard_rows(p, static_cast<char*>(p->peers.work[r]), false, static_cast<const char*>(p->work), false,
+                                        ps, b0, b1, p->copy_stream[r]));
+            }
+        }
+        OXZ_CUDA(mark(4));
+        for (int r = 0; r < p->world; r++) {
+            if (r == p->rank) continue;
+            OXZ_CUDA(cudaEventRecord(p->ev_pushed[r], p->copy_stream[r]));
+            OXZ_CUDA(cudaStreamWaitEvent(s, p->ev_pushed[r], 0));
+        }
+        // every rank's copies into this rank's weight buffer must have landed before the step is reported done
+        OXZ_TRY(comm_stream_barrier(comm, bar, s));
+    } else {
     OXZ_TRY(launch_adamw(s, p->geom, gsrc, gsrc_dt, p->master, p->exp_avg, p->exp_avg_sq, p->peers, n_work, p->pdt, map,
                          p->d_tile_meta, p->d_present, some_absent, p->d_scalars, ap));
     OXZ_CUDA(mark(4));
+    }
     if (p->mode == OXZ_SYNC_NCCL) {
         const size_t ps = dtype_size(p->pdt);
         ncclResult_t rc = api->GroupStart();

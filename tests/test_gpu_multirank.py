@@ -121,10 +121,11 @@ def layouts():
     return out
 
 
+@pytest.mark.parametrize("mode", [ox.SYNC_P2P, ox.SYNC_COPY])
 @pytest.mark.parametrize("kind,world,devices", layouts())
 @pytest.mark.parametrize("gd,pd", [(ox.BF16, ox.BF16), (ox.F16, ox.F16), (ox.F32, ox.F32)])
-def test_sharded_p2p_step_is_bit_identical_to_the_replicated_step(kind, world, devices, gd, pd):
-    g = Group(world, devices, kind, gd=gd, pd=pd, seed=21)
+def test_sharded_p2p_step_is_bit_identical_to_the_replicated_step(kind, world, devices, gd, pd, mode):
+    g = Group(world, devices, kind, mode=mode, gd=gd, pd=pd, seed=21)
     cfg = ox.StepConfig(max_grad_norm=1e9, eps=1e-8)
     for s in range(2):
         out, ref = g.step(cfg, extras=[0.25 * (r + 1) for r in range(world)])
@@ -138,9 +139,10 @@ def test_sharded_p2p_step_is_bit_identical_to_the_replicated_step(kind, world, d
     g.close()
 
 
+@pytest.mark.parametrize("mode", [ox.SYNC_P2P, ox.SYNC_COPY])
 @pytest.mark.parametrize("kind,world,devices", layouts())
-def test_sharded_step_with_clipping_and_absent_tensors(kind, world, devices):
-    g = Group(world, devices, kind, seed=22, grad_std=1.0)
+def test_sharded_step_with_clipping_and_absent_tensors(kind, world, devices, mode):
+    g = Group(world, devices, kind, mode=mode, seed=22, grad_std=1.0)
     present = [True, True, False, True, True, True, True]
     out, ref = g.step(ox.StepConfig(max_grad_norm=1.0), present=present)
     for res, _ in out:
@@ -150,10 +152,11 @@ def test_sharded_step_with_clipping_and_absent_tensors(kind, world, devices):
     g.close()
 
 
+@pytest.mark.parametrize("mode", [ox.SYNC_P2P, ox.SYNC_COPY])
 @pytest.mark.parametrize("kind,world,devices", layouts())
-def test_overflow_on_one_rank_skips_on_every_rank(kind, world, devices):
+def test_overflow_on_one_rank_skips_on_every_rank(kind, world, devices, mode):
     # tests/data_parallel.rs:353-392
-    g = Group(world, devices, kind, gd=ox.F16, pd=ox.F16, seed=23)
+    g = Group(world, devices, kind, mode=mode, gd=ox.F16, pd=ox.F16, seed=23)
     before = [g.merged(k) for k in (ffi.STATE_MASTER, ffi.STATE_EXP_AVG, ffi.STATE_EXP_AVG_SQ)]
     grads = [[x.copy() for x in rg] for rg in g.grads]
     grads[world - 1][3][4242] = np.array([np.inf], np.float16).view(np.uint16)[0]
