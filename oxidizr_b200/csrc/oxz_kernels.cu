@@ -624,6 +624,10 @@ int32_t query_geom(int device, LaunchGeom* g) {
             if (m < pb) pb = m;
         }
         g->pull_blocks[dt] = pb > 0 ? pb : CLUSTER;
+        if (const char* e = getenv("OXZ_PULL_BLOCKS")) {  // tuning aid
+            int want = atoi(e) / CLUSTER * CLUSTER;
+            if (want >= CLUSTER && want < g->pull_blocks[dt]) g->pull_blocks[dt] = want;
+        }
     }
     g->norm_blocks = nb > 0 ? nb : CLUSTER;
     g->adam_blocks = g->sm_count * adam_blocks_per_sm(adam_variant());
