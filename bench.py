@@ -270,6 +270,19 @@ def run_gpu(args):
         e2e_sec, _, _ = timed(e2e_steps, upload)
         e2e_value = P * e2e_steps / e2e_sec
 
+    # Overlap with backward: three quarters of the buckets are handed in while "backward" would still be running
+    # (untimed here); the timed part is what is left exposed after backward ends. A separate figure, not `value`.
+    overlap = None
+    if mode in (ox.SYNC_SINGLE, ox.SYNC_P2P):
+        nb = info.n_buckets
+        early = max(1, (3 * nb) // 4)
+        exposed = []
+        for _ in range(5):
+            opt.grads_ready(cfg, nb - early, early, producer_stream=stream.cuda_stream)
+            sec1, _, _ = timed(1)
+            exposed.append(sec1 * 1e3)
+        overlap = {"buckets": nb, "buckets_reduced_during_backward": early, "exposed_ms_per_step": statistics.median(exposed)}
+
     peak, peak_kind = measured_peaks()
     upd = statistics.mean(p.update_ms for p in profs)
     nrm = statistics.mean(p.norm_ms for p in profs)
@@ -298,6 +311,7 @@ def run_gpu(args):
         # the pull and the update once per pipeline group (4 groups)
         "gpu_launches": (10 if mode == ox.SYNC_COPY else 4) * args.steps * world,
         "launch_geometry": opt.launch_geometry(),
+        "overlap_with_backward": overlap,
         "clocks": clocks,
         "result": {"grad_norm": res.grad_norm, "applied": res.applied, "timestep": res.timestep},
     }

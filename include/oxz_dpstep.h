@@ -221,6 +221,15 @@ typedef struct oxz_step_result {
  * The decision to skip is taken on the device; nothing is read back between the norm and the update. */
 int32_t oxz_step_async(oxz_plan* plan, oxz_comm* comm, const oxz_hyper* hyper, const uint8_t* present,
                        double* extras, uint32_t n_extras);
+/* Overlap with the tail of backward: reduces over ranks (at world 1: measures) the gradient buckets
+ * [first_bucket, first_bucket + n_buckets) now, on a side stream, while backward still produces the others. The
+ * buckets must be complete on every rank once the work enqueued so far on `producer_stream` (the stream backward
+ * writes the gradients on; NULL = the legacy default stream) has finished. Collective: every rank makes the same calls
+ * in the same order. hyper (its loss_scale and max_grad_value) and present must be the ones the step's
+ * oxz_step_async is then given; that call reduces whatever buckets are left and finishes the step. Up to 6 calls per
+ * step. Serves OXZ_SYNC_SINGLE and OXZ_SYNC_P2P. (The reference reduces once, after backward: src/trainer.rs:520-527.) */
+int32_t oxz_grads_ready_async(oxz_plan* plan, oxz_comm* comm, const oxz_hyper* hyper, const uint8_t* present,
+                              uint64_t first_bucket, uint64_t n_buckets, void* producer_stream);
 /* Waits for the step in flight, fills `result` and the extras, and advances the applied-step count. */
 int32_t oxz_step_wait(oxz_plan* plan, oxz_step_result* result);
 /* oxz_step_async followed by oxz_step_wait. */

@@ -121,6 +121,7 @@ SIGNATURES = {
     "oxz_grads_flatten_async": (C.c_int32, [vp, C.POINTER(vp), C.c_int32]),
     "oxz_grads_upload_async": (C.c_int32, [vp, C.c_uint64, vp]),
     "oxz_step_async": (C.c_int32, [vp, vp, C.POINTER(Hyper), u8p, f64p, C.c_uint32]),
+    "oxz_grads_ready_async": (C.c_int32, [vp, vp, C.POINTER(Hyper), u8p, C.c_uint64, C.c_uint64, vp]),
     "oxz_step_wait": (C.c_int32, [vp, C.POINTER(StepResult)]),
     "oxz_step": (C.c_int32, [vp, vp, C.POINTER(Hyper), u8p, f64p, C.c_uint32, C.POINTER(StepResult)]),
     "oxz_plan_launch_geometry": (C.c_int32, [vp] + [C.POINTER(C.c_int32)] * 3),

@@ -185,6 +185,13 @@ struct oxz_plan {
     uint32_t pipe_groups = 1;
     oxz_comm* comm = nullptr;
 
+    // buckets reduced ahead of the step (oxz_grads_ready_async)
+    cudaStream_t early_stream = nullptr;
+    cudaEvent_t ev_produced = nullptr, ev_early = nullptr;
+    std::vector<uint8_t> early_done;   // per bucket
+    uint32_t early_groups = 0;         // partial-sum groups already written this step
+    double early_scale = 0.0, early_clamp = 0.0;
+
     // step bookkeeping
     uint64_t timestep = 0;
     bool inflight = false;

@@ -172,6 +172,9 @@ int32_t oxz_plan_destroy(oxz_plan* p) {
             if (q) cudaFree(q);
         for (void* q : {(void*)p->h_scalars, (void*)p->h_acc, (void*)p->h_extras, (void*)p->h_present, (void*)p->h_src})
             if (q) cudaFreeHost(q);
+        if (p->early_stream) cudaStreamDestroy(p->early_stream);
+        if (p->ev_produced) cudaEventDestroy(p->ev_produced);
+        if (p->ev_early) cudaEventDestroy(p->ev_early);
         if (p->stage) cudaFree(p->stage);
         for (auto st : p->copy_stream) if (st) cudaStreamDestroy(st);
         if (p->ev_go) cudaEventDestroy(p->ev_go);
@@ -379,6 +382,41 @@ int32_t oxz_grads_upload_async(oxz_plan* p, uint64_t tensor, const void* host) {
     return OXZ_OK;
 }
 
+namespace {
+
+bool same_or_both_nan(double a, double b) { return a == b || (std::isnan(a) && std::isnan(b)); }
+
+// Records which tensors have a gradient this step; returns whether any is absent.
+int32_t update_present(oxz_plan* p, const uint8_t* present, cudaStream_t s, bool* some_absent) {
+    bool changed = false;
+    for (uint64_t i = 0; i < p->T; i++) {
+        const uint8_t v = present ? (present[i] ? 1 : 0) : 1;
+        if (p->h_present[i] != v) {
+            p->h_present[i] = v;
+            changed = true;
+        }
+    }
+    if (changed) OXZ_CUDA(cudaMemcpyAsync(p->d_present, p->h_present, p->T, cudaMemcpyHostToDevice, s));
+    *some_absent = false;
+    for (uint64_t i = 0; i < p->T; i++) *some_absent |= p->h_present[i] == 0;
+    return OXZ_OK;
+}
+
+// The norm pass (fused with the pull over ranks in P2P mode) over buckets [b0, b1) into partial-sum group `group`.
+int32_t reduce_buckets(oxz_plan* p, cudaStream_t s, const LaunchGeom& geom, uint64_t b0, uint64_t b1, uint32_t group,
+                       uint32_t slots, bool some_absent, float inv_scale, float clamp_hi, int32_t clamp_on) {
+    TileMap gm = tile_map(p);
+    group_tiles(p, b0, b1, &gm.first_tile, &gm.n_local_tiles);
+    double* partials = p->d_partials + (size_t)group * slots * 3;
+    if (p->mode == OXZ_SYNC_SINGLE)
+        return launch_sumsq(s, geom, p->grads, p->gdt, gm, p->d_tile_meta, p->d_present, some_absent, inv_scale, clamp_hi,
+                            clamp_on, partials);
+    return launch_pull_sumsq(s, geom, p->peers, p->world, 0, p->gdt, gm, p->d_tile_meta, p->d_present, some_absent,
+                             inv_scale, clamp_hi, clamp_on, static_cast<float*>(p->reduced), partials);
+}
+
+}  // namespace
+
 static int32_t check_hyper(const oxz_hyper* h) {
     auto pos = [](double x) { return std::isfinite(x) && x > 0.0; };
     if (!std::isfinite(h->lr) || h->lr < 0.0) return fail(OXZ_ERR_INVALID, "learning rate %g must be finite and not negative", h->lr);
@@ -418,17 +456,18 @@ int32_t oxz_step_async(oxz_plan* p, oxz_comm* comm, const oxz_hyper* h, const ui
     ncclComm_t nc = nccl_mode ? (ncclComm_t)comm->nccl : nullptr;
 
     // which tensors have a gradient this step
-    bool changed = false;
-    for (uint64_t i = 0; i < p->T; i++) {
-        const uint8_t v = present ? (present[i] ? 1 : 0) : 1;
-        if (p->h_present[i] != v) {
-            p->h_present[i] = v;
-            changed = true;
-        }
-    }
-    if (changed) OXZ_CUDA(cudaMemcpyAsync(p->d_present, p->h_present, p->T, cudaMemcpyHostToDevice, s));
     bool some_absent = false;
-    for (uint64_t i = 0; i < p->T; i++) some_absent |= p->h_present[i] == 0;
+    if (p->early_groups == 0) {
+        OXZ_TRY(update_present(p, present, s, &some_absent));
+    } else {
+        for (uint64_t i = 0; i < p->T; i++) {
+            const uint8_t v = present ? (present[i] ? 1 : 0) : 1;
+            if (p->h_present[i] != v) return fail(OXZ_ERR_INVALID, "oxz_step_async: `present` differs from the one oxz_grads_ready_async was given for this step");
+            some_absent |= v == 0;
+        }
+        if (!same_or_both_nan(h->loss_scale, p->early_scale) || !same_or_both_nan(h->max_grad_value, p->early_clamp))
+            return fail(OXZ_ERR_INVALID, "oxz_step_async: loss_scale or max_grad_value differs from the one oxz_grads_ready_async was given for this step");
+    }
 
     // per-step scalars, f64 on the host, rounded to f32 once
     const uint64_t t = p->timestep + 1;
@@ -468,18 +507,30 @@ int32_t oxz_step_async(oxz_plan* p, oxz_comm* comm, const oxz_hyper* h, const ui
 
     auto mark = [&](int i) -> cudaError_t { return p->profile ? cudaEventRecord(p->ev[i], s) : cudaSuccess; };
     OXZ_CUDA(mark(0));
-    if (p->mode == OXZ_SYNC_SINGLE) {
+    if (p->mode == OXZ_SYNC_SINGLE || p->mode == OXZ_SYNC_P2P) {
+        // buckets already reduced during backward are skipped; the rest goes now, one launch per run of buckets
+        uint32_t groups = p->early_groups;
+        if (groups) OXZ_CUDA(cudaStreamWaitEvent(s, p->ev_early, 0));
+        bool any_left = false;
+        for (uint64_t b = 0; b < p->n_buckets; b++) any_left |= !(groups && p->early_done[b]);
+        // every rank's remaining gradients must be complete before anyone pulls them
+        if (p->mode == OXZ_SYNC_P2P && any_left) OXZ_TRY(comm_stream_barrier(comm, bar, s));
         OXZ_CUDA(mark(1));
-        OXZ_TRY(launch_sumsq(s, p->geom, p->grads, p->gdt, map, p->d_tile_meta, p->d_present, some_absent, ap.inv_scale,
-                             ap.clamp_hi, ap.clamp_on, p->d_partials));
-    } else if (p->mode == OXZ_SYNC_P2P) {
-        // every rank's gradients must be complete before anyone pulls them
-        OXZ_TRY(comm_stream_barrier(comm, bar, s));
-        OXZ_CUDA(mark(1));
-        OXZ_TRY(launch_pull_sumsq(s, p->geom, p->peers, p->world, 0, p->gdt, map, p->d_tile_meta, p->d_present, some_absent,
-                                  ap.inv_scale, ap.clamp_hi, ap.clamp_on, static_cast<float*>(p->reduced), p->d_partials));
-        gsrc = p->reduced;
-        gsrc_dt = OXZ_F32;
+        for (uint64_t b = 0; b < p->n_buckets;) {
+            if (groups && p->early_done[b]) { b++; continue; }
+            uint64_t e = b;
+            while (e < p->n_buckets && !(p->early_groups && p->early_done[e])) e++;
+            if (groups >= MAX_PIPE) return fail(OXZ_ERR_STATE, "oxz_step_async: the buckets left after oxz_grads_ready_async form too many separate runs");
+            OXZ_TRY(reduce_buckets(p, s, p->geom, b, e, groups, slots, some_absent, ap.inv_scale, ap.clamp_hi, ap.clamp_on));
+            groups++;
+            b = e;
+        }
+        slots *= groups;
+        p->early_groups = 0;
+        if (p->mode == OXZ_SYNC_P2P) {
+            gsrc = p->reduced;
+            gsrc_dt = OXZ_F32;
+        }
     } else if (p->mode == OXZ_SYNC_COPY) {
         // every rank's gradients must be complete before anyone copies them
         OXZ_TRY(comm_stream_barrier(comm, bar, s));
@@ -603,6 +654,74 @@ int32_t oxz_step_async(oxz_plan* p, oxz_comm* comm, const oxz_hyper* h, const ui
     p->inflight_hyper = *h;
     p->inflight_extras = extras;
     p->inflight_n_extras = n_extras;
+    return OXZ_OK;
+}
+
+int32_t oxz_grads_ready_async(oxz_plan* p, oxz_comm* comm, const oxz_hyper* h, const uint8_t* present, uint64_t first_bucket,
+                              uint64_t n_buckets, void* producer_stream) {
+    if (!p || !h) return fail(OXZ_ERR_INVALID, "oxz_grads_ready_async: null argument");
+    if (!p->allocated) return fail(OXZ_ERR_STATE, "oxz_grads_ready_async: the plan has no device state. Call oxz_state_alloc first");
+    if (p->inflight) return fail(OXZ_ERR_STATE, "oxz_grads_ready_async: the previous step is still in flight. Call oxz_step_wait first");
+    if (p->mode != OXZ_SYNC_SINGLE && p->mode != OXZ_SYNC_P2P)
+        return fail(OXZ_ERR_UNSUPPORTED, "oxz_grads_ready_async serves OXZ_SYNC_SINGLE and OXZ_SYNC_P2P plans");
+    OXZ_TRY(check_hyper(h));
+    if (n_buckets == 0 || first_bucket + n_buckets > p->n_buckets)
+        return fail(OXZ_ERR_INVALID, "oxz_grads_ready_async: buckets [%llu, %llu) of %llu", (unsigned long long)first_bucket,
+                    (unsigned long long)(first_bucket + n_buckets), (unsigned long long)p->n_buckets);
+    if (p->early_groups >= MAX_PIPE - 2) return fail(OXZ_ERR_STATE, "oxz_grads_ready_async: at most %u calls per step", MAX_PIPE - 2);
+    if (p->world > 1) {
+        OXZ_TRY(comm_check(comm, "oxz_grads_ready_async"));
+        if (comm != p->comm) return fail(OXZ_ERR_INVALID, "oxz_grads_ready_async: this is not the communicator the state was allocated with");
+    }
+    OXZ_CUDA(cudaSetDevice(p->device));
+    if (!p->early_stream) {
+        OXZ_CUDA(cudaStreamCreateWithFlags(&p->early_stream, cudaStreamNonBlocking));
+        OXZ_CUDA(cudaEventCreateWithFlags(&p->ev_produced, cudaEventDisableTiming));
+        OXZ_CUDA(cudaEventCreateWithFlags(&p->ev_early, cudaEventDisableTiming));
+    }
+    cudaStream_t es = p->early_stream;
+    bool some_absent = false;
+    if (p->early_groups == 0) {
+        p->early_done.assign(p->n_buckets, 0);
+        p->early_scale = h->loss_scale;
+        p->early_clamp = h->max_grad_value;
+        // the side stream must not run ahead of the previous step's update, which read the same buffers
+        OXZ_CUDA(cudaEventRecord(p->ev_early, p->stream));
+        OXZ_CUDA(cudaStreamWaitEvent(es, p->ev_early, 0));
+        OXZ_TRY(update_present(p, present, es, &some_absent));
+    } else {
+        if (!same_or_both_nan(h->loss_scale, p->early_scale) || !same_or_both_nan(h->max_grad_value, p->early_clamp))
+            return fail(OXZ_ERR_INVALID, "oxz_grads_ready_async: loss_scale or max_grad_value changed within one step");
+        for (uint64_t i = 0; i < p->T; i++) {
+            const uint8_t v = present ? (present[i] ? 1 : 0) : 1;
+            if (p->h_present[i] != v) return fail(OXZ_ERR_INVALID, "oxz_grads_ready_async: `present` changed within one step");
+            some_absent |= v == 0;
+        }
+    }
+    for (uint64_t b = first_bucket; b < first_bucket + n_buckets; b++)
+        if (p->early_done[b]) return fail(OXZ_ERR_INVALID, "oxz_grads_ready_async: bucket %llu was already handed in this step", (unsigned long long)b);
+    // the producer's work so far must have finished before the buckets are read
+    OXZ_CUDA(cudaEventRecord(p->ev_produced, (cudaStream_t)producer_stream));
+    OXZ_CUDA(cudaStreamWaitEvent(es, p->ev_produced, 0));
+    if (p->mode == OXZ_SYNC_P2P) {
+        int32_t* bar = reinterpret_cast<int32_t*>(static_cast<char*>(comm->d_small) + 448);
+        OXZ_TRY(comm_stream_barrier(comm, bar, es));
+    }
+    const bool scaled = !std::isnan(h->loss_scale) && h->loss_scale != 0.0;
+    const int32_t clamp_on = std::isnan(h->max_grad_value) ? 0 : 1;
+    // a quarter of the usual grid: the pull is NVLink-bound and backward still needs the SMs
+    LaunchGeom geom = p->geom;
+    const int cap = (geom.sm_count / 4) * 4;
+    geom.norm_blocks = geom.norm_blocks < cap ? geom.norm_blocks : cap;
+    for (int& b : geom.pull_blocks) b = b < cap ? b : cap;
+    const uint32_t slots = p->mode == OXZ_SYNC_P2P ? pull_partial_slots(p->geom, p->gdt) : norm_partial_slots(p->geom);
+    // the smaller grid fills only the first slots of its group; the rest must read as zero
+    OXZ_CUDA(cudaMemsetAsync(p->d_partials + (size_t)p->early_groups * slots * 3, 0, (size_t)slots * 3 * 8, es));
+    OXZ_TRY(reduce_buckets(p, es, geom, first_bucket, first_bucket + n_buckets, p->early_groups, slots, some_absent,
+                           scaled ? (float)(1.0 / h->loss_scale) : 1.0f, clamp_on ? (float)h->max_grad_value : 0.f, clamp_on));
+    OXZ_CUDA(cudaEventRecord(p->ev_early, es));
+    for (uint64_t b = first_bucket; b < first_bucket + n_buckets; b++) p->early_done[b] = 1;
+    p->early_groups++;
     return OXZ_OK;
 }
 

@@ -546,6 +546,15 @@ class DpOptimizer:
         self._n_extras = n
         check(lib().oxz_step_async(self._h, self.comm.handle if self.comm else None, C.byref(h), pres, self._extras, n))
 
+    def grads_ready(self, cfg: StepConfig, first_bucket: int, n_buckets: int, present: list[bool] | None = None,
+                    producer_stream: int | None = None) -> None:
+        """Reduce buckets [first_bucket, first_bucket + n_buckets) now, on a side stream, while backward still
+        produces the others; the step's step_async/step then handles what is left. Collective at world > 1."""
+        h = cfg.hyper()
+        pres = (C.c_uint8 * max(len(present), 1))(*[int(bool(x)) for x in present]) if present is not None else None
+        check(lib().oxz_grads_ready_async(self._h, self.comm.handle if self.comm else None, C.byref(h), pres, first_bucket,
+                                          n_buckets, C.c_void_p(producer_stream) if producer_stream else None))
+
     def step_wait(self) -> ffi.StepResult:
         res = ffi.StepResult()
         check(lib().oxz_step_wait(self._h, C.byref(res)))

@@ -225,3 +225,48 @@ def test_f16_loss_scale_run_with_seeded_overflows_over_eight_ranks():
     assert skipped >= 1 and g.opts[0].timestep == steps - skipped
     g.assert_state(exact=False, rel=1e-4)
     g.close()
+
+
+@pytest.mark.parametrize("world", [1, 2, 4])
+def test_buckets_reduced_during_backward_give_the_same_step(world):
+    """oxz_grads_ready_async hands finished buckets in early (last buckets first, as backward produces them); the step
+    then reduces the rest. The state must equal the checker's bit for bit, exactly as a plain step's does."""
+    numel = [5000, 300, 70001, 513, 9000, 40000]
+    no_decay = [False, True, False, True, False, False]
+    if world == 1:
+        from tests.helpers import Pair
+        pair = Pair(numel, no_decay, ox.BF16, ox.BF16, seed=61, bucket_bytes=16384)
+        nb = pair.opt.info.n_buckets
+        assert nb >= 6
+        cfg = ox.StepConfig(max_grad_norm=1e9, eps=1e-8)
+        for s in range(2):
+            pair.opt.grads_ready(cfg, nb - 2, 2)
+            pair.opt.grads_ready(cfg, nb - 5, 3)
+            res, ref = pair.step(cfg)
+            assert (res.applied, res.timestep) == (1, s + 1) and abs(res.grad_norm - ref.grad_norm) <= 1e-5 * ref.grad_norm
+            pair.assert_bit_equal()
+        # a plain step afterwards still works, and call-order mistakes are errors, not hangs
+        res, ref = pair.step(cfg)
+        pair.assert_bit_equal()
+        pair.opt.grads_ready(cfg, 0, 1)
+        with pytest.raises(ox.OxzError, match="already handed in"):
+            pair.opt.grads_ready(cfg, 0, 1)
+        with pytest.raises(ox.OxzError, match="differs from the one"):
+            pair.opt.step(ox.StepConfig(max_grad_norm=1e9, eps=1e-8, loss_scale=2.0))
+        res, ref = pair.step(cfg)
+        pair.assert_bit_equal()
+        pair.close()
+        return
+    g = Group(world, [0] * world, "local", seed=62, numel=numel, no_decay=no_decay, bucket_bytes=16384 * world)
+    nb = g.opts[0].info.n_buckets
+    assert nb >= 4
+    cfg = ox.StepConfig(max_grad_norm=1e9, eps=1e-8)
+    for s in range(2):
+        list(g.pool.map(lambda r: g.opts[r].grads_ready(cfg, nb - 1, 1), range(world)))
+        list(g.pool.map(lambda r: g.opts[r].grads_ready(cfg, 1, nb - 3), range(world)))
+        out, ref = g.step(cfg, extras=[1.0] * world)
+        for res, extras in out:
+            assert (res.applied, res.timestep) == (1, s + 1) and abs(res.grad_norm - ref.grad_norm) <= 1e-5 * ref.grad_norm
+            assert extras == [float(world)]
+        g.assert_state(exact=True)
+    g.close()
