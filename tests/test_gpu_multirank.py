@@ -270,3 +270,38 @@ def test_buckets_reduced_during_backward_give_the_same_step(world):
             assert extras == [float(world)]
         g.assert_state(exact=True)
     g.close()
+
+
+def test_two_ranks_equal_one_rank_fed_the_summed_gradients():
+    """tests/data_parallel.rs:226-269 (2 ranks x batch 2 == 1 rank x batch 4): the gradients are summed, never averaged,
+    so two ranks must end bit-identical to a single rank that is handed the f32 sum of their gradients."""
+    numel = [4096, 300, 70001, 513]
+    no_decay = [False, True, False, True]
+    g = Group(2, [0, 0], "local", gd=ox.F32, pd=ox.BF16, seed=71, numel=numel, no_decay=no_decay, grad_std=1.0)
+    summed = [orc.sum_ranks([g.grads[0][i], g.grads[1][i]], orc.F32) for i in range(len(numel))]
+    single = ox.DpOptimizer(numel, no_decay, ox.F32, ox.BF16, bucket_bytes=16384)
+    from tests.helpers import seeded_state
+    master, m, v, _ = seeded_state(numel, 71, 1.0, 2, ox.F32)
+    for i in range(len(numel)):
+        single.import_tensor(ffi.STATE_MASTER, i, master[i])
+        single.import_tensor(ffi.STATE_EXP_AVG, i, m[i])
+        single.import_tensor(ffi.STATE_EXP_AVG_SQ, i, v[i])
+        single.import_tensor(ffi.STATE_WORK, i, orc.narrow(master[i], ox.BF16))
+        single.import_tensor(ffi.STATE_GRADS, i, summed[i])
+    cfg = ox.StepConfig(max_grad_norm=1.0)
+    for _ in range(2):
+        out, ref = g.step(cfg)
+        one = single.step(cfg)
+        assert {res.grad_norm for res, _ in out} == {out[0][0].grad_norm}
+        assert abs(one.grad_norm - out[0][0].grad_norm) <= 1e-9 * one.grad_norm and one.clip_coef < 1.0
+    same_coef = one.clip_coef == out[0][0].clip_coef
+    for kind in (ffi.STATE_MASTER, ffi.STATE_EXP_AVG, ffi.STATE_EXP_AVG_SQ):
+        for i, merged in enumerate(g.merged(kind)):
+            alone = single.export_tensor(kind, i)
+            if same_coef:
+                assert np.array_equal(bits(merged), bits(alone)), (kind, i)
+            else:  # the norm's partial sums are grouped differently; the coefficient may differ in its last bit
+                ref64 = alone.astype(np.float64)
+                assert np.all(np.abs(merged - ref64) <= 1e-6 * (np.abs(ref64) + math.sqrt(float(np.mean(ref64 ** 2))))), (kind, i)
+    single.destroy()
+    g.close()
