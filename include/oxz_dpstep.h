@@ -337,7 +337,8 @@ int32_t oxz_loader_position(const oxz_loader* loader, oxz_data_position* pos);
 int32_t oxz_loader_seek(oxz_loader* loader, oxz_data_position pos);
 /* Draws this rank's rows of the next global batch and advances past the whole global batch. *inputs and *targets
  * are device pointers to [rank_batch_size, seq_len] i64 owned by the loader, valid until the second-next call;
- * rows (may be NULL) receives the global row indices. Asynchronous on `stream`. */
+ * rows (may be NULL) receives the global row indices. Asynchronous on `stream`; use one stream for all calls of a
+ * loader, the buffers are recycled in its order. */
 int32_t oxz_loader_next_batch_async(oxz_loader* loader, void* stream, int64_t** inputs, int64_t** targets, uint64_t* rows);
 
 /* StepWeighting::over_ranks applied to the summed counts (src/dp/weighting.rs:46-61): counts = {scored, masked ranks}

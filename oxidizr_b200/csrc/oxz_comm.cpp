@@ -269,9 +269,13 @@ int32_t oxz_comm_init_all(int32_t n, const int32_t* devices, oxz_comm** out) {
         c->rank = i;
         c->world = n;
         c->device = devices[i];
-        int32_t s = finish_comm(c);
-        if (s != OXZ_OK) return s;
         out[i] = c;
+        int32_t s = finish_comm(c);
+        if (s != OXZ_OK) {
+            for (int j = 0; j <= i; j++) { oxz_comm_destroy(out[j]); out[j] = nullptr; }
+            for (int j = i + 1; j < n; j++) api->CommAbort(comms[j]);
+            return s;
+        }
     }
     return OXZ_OK;
 }

@@ -161,9 +161,9 @@ extern "C" {
 
 int32_t oxz_plan_destroy(oxz_plan* p) {
     if (!p) return OXZ_OK;
-    if (p->allocated) {
+    if (p->allocated || p->own_stream) {  // also after an allocation that failed midway
         cudaSetDevice(p->device);
-        cudaStreamSynchronize(p->stream);
+        if (p->stream) cudaStreamSynchronize(p->stream);
         for (void* q : p->ipc_opened) cudaIpcCloseMemHandle(q);
         if (p->work && p->work != (void*)p->master) cudaFree(p->work);
         for (void* q : {(void*)p->grads, (void*)p->master, (void*)p->exp_avg, (void*)p->exp_avg_sq, p->reduced,
@@ -200,6 +200,7 @@ int32_t oxz_plan_set_stream(oxz_plan* p, void* stream) {
 int32_t oxz_state_alloc(oxz_plan* p, oxz_comm* comm) {
     if (!p) return fail(OXZ_ERR_INVALID, "oxz_state_alloc: null plan");
     if (p->allocated) return fail(OXZ_ERR_STATE, "oxz_state_alloc: the plan already has device state");
+    if (p->own_stream) return fail(OXZ_ERR_STATE, "oxz_state_alloc: an earlier allocation of this plan failed midway. Destroy the plan and create it again");
     if (p->world > 1) {
         OXZ_TRY(comm_check(comm, "oxz_state_alloc"));
         if (comm->world != p->world || comm->rank != p->rank)
