@@ -301,7 +301,8 @@ def run_gpu(args):
                      "traffic": ADAMW_TRAFFIC_RATIO * BYTES_UPDATE * local_params,
                      "traffic_source": "ncu capture of nano_dense scaled by parameters per launch",
                      "algorithmic_bytes_per_launch": BYTES_UPDATE * local_params, "kernel_ms": upd,
-                     "norm_kernel": {"kernel": "k_pull_sumsq" if mode in (ox.SYNC_P2P, ox.SYNC_COPY) else "k_sumsq", "kernel_ms": nrm}},
+                     "norm_kernel": {"kernel": "k_pull_sumsq" if mode in (ox.SYNC_P2P, ox.SYNC_COPY) else "k_sumsq_stream16",
+                                     "kernel_ms": nrm, "achieved_gbs": BYTES_NORM * local_params / (nrm * 1e-3) / 1e9 if world == 1 else None}},
         "phases_ms": {k: statistics.mean(getattr(p, k) for p in profs) for k in
                       ("collect_ms", "norm_ms", "decide_ms", "update_ms", "publish_ms", "total_ms")},
         "step_roofline": step_roofline(P, world, ms_per_step, peak),

@@ -243,6 +243,55 @@ __global__ void __cluster_dims__(CLUSTER, 1, 1) __launch_bounds__(THREADS)
     cluster_reduce_store(a, partials);
 }
 
+// Every tensor present, 16-bit gradients: the shard is one contiguous stream, read 256 bits per lane (16 elements),
+// VEC such loads in flight per thread. Library-owned memory, so 32-byte alignment holds.
+template <int DT, int VEC>
+__global__ void __cluster_dims__(CLUSTER, 1, 1) __launch_bounds__(THREADS)
+    k_sumsq_stream16(const uint16_t* __restrict__ grads, uint64_t first, uint64_t end, float inv_scale, float clamp_hi,
+                     int clamp_on, double* __restrict__ partials) {
+    static_assert(DT == OXZ_BF16 || DT == OXZ_F16, "16-bit gradients only");
+    NormAcc a;
+    const uint64_t nvec = (end - first) / 16;  // the range is a whole number of 256-element tiles
+    const uint64_t stride = static_cast<uint64_t>(gridDim.x) * THREADS;
+    const uint16_t* base = grads + first;
+    for (uint64_t i = static_cast<uint64_t>(blockIdx.x) * THREADS + threadIdx.x; i < nvec; i += stride * VEC) {
+        uint32_t w[VEC][8];
+        bool on[VEC];
+#pragma unroll
+        for (int j = 0; j < VEC; j++) {
+            const uint64_t v = i + static_cast<uint64_t>(j) * stride;
+            on[j] = v < nvec;
+            if (on[j])
+                asm volatile("ld.global.cs.v8.u32 {%0,%1,%2,%3,%4,%5,%6,%7}, [%8];"
+                             : "=r"(w[j][0]), "=r"(w[j][1]), "=r"(w[j][2]), "=r"(w[j][3]), "=r"(w[j][4]), "=r"(w[j][5]),
+                               "=r"(w[j][6]), "=r"(w[j][7])
+                             : "l"(base + v * 16));
+        }
+#pragma unroll
+        for (int j = 0; j < VEC; j++) {
+            if (!on[j]) continue;
+#pragma unroll
+            for (int h = 0; h < 2; h++) {
+                float x[8];
+#pragma unroll
+                for (int q = 0; q < 4; q++) {
+                    const uint32_t u = w[j][4 * h + q];
+                    if constexpr (DT == OXZ_BF16) {
+                        x[2 * q] = __uint_as_float(u << 16);
+                        x[2 * q + 1] = __uint_as_float(u & 0xffff0000u);
+                    } else {
+                        const float2 f = __half22float2(*reinterpret_cast<const __half2*>(&u));
+                        x[2 * q] = f.x;
+                        x[2 * q + 1] = f.y;
+                    }
+                }
+                acc8(x, inv_scale, clamp_hi, clamp_on != 0, a);
+            }
+        }
+    }
+    cluster_reduce_store(a, partials);
+}
+
 // The standalone measurement over a plain array: n elements, any n; the tail is read element by element.
 template <int DT>
 __global__ void __cluster_dims__(CLUSTER, 1, 1) __launch_bounds__(THREADS)
@@ -604,7 +653,8 @@ int32_t query_geom(int device, LaunchGeom* g) {
     const void* funcs[] = {
         (const void*)k_sumsq<OXZ_F32, 4, false>,  (const void*)k_sumsq<OXZ_BF16, 4, false>, (const void*)k_sumsq<OXZ_F16, 4, false>,
         (const void*)k_sumsq<OXZ_F32, 4, true>,   (const void*)k_sumsq<OXZ_BF16, 4, true>,  (const void*)k_sumsq<OXZ_F16, 4, true>,
-        (const void*)k_sumsq_plain<OXZ_F32>, (const void*)k_sumsq_plain<OXZ_BF16>, (const void*)k_sumsq_plain<OXZ_F16>};
+        (const void*)k_sumsq_plain<OXZ_F32>, (const void*)k_sumsq_plain<OXZ_BF16>, (const void*)k_sumsq_plain<OXZ_F16>,
+        (const void*)k_sumsq_stream16<OXZ_BF16, 2>, (const void*)k_sumsq_stream16<OXZ_F16, 2>};
     for (const void* f : funcs) {
         const int m = max_cluster_blocks(f, nb);
         if (m < nb) nb = m;
@@ -651,6 +701,17 @@ static int32_t launch_sumsq_c(cudaStream_t s, const LaunchGeom& g, const void* g
                               int32_t clamp_on, double* partials) {
     constexpr int ILP = 4;
     dim3 grid(g.norm_blocks), block(THREADS);
+    if constexpr (!CHECK) {
+        // measured on B200 (2.47 GB of bf16): 0.383 ms with two 256-bit loads in flight per thread, 0.397 ms with
+        // four, 0.420 ms for the tile-wise 128-bit form
+        if (dt != OXZ_F32) {
+            const uint64_t first = static_cast<uint64_t>(map.first_tile) * TILE, end = static_cast<uint64_t>(map.n_local_tiles) * TILE;
+            const uint16_t* g16 = static_cast<const uint16_t*>(grads);
+            if (dt == OXZ_BF16) k_sumsq_stream16<OXZ_BF16, 2><<<grid, block, 0, s>>>(g16, first, end, inv_scale, clamp_hi, clamp_on, partials);
+            else k_sumsq_stream16<OXZ_F16, 2><<<grid, block, 0, s>>>(g16, first, end, inv_scale, clamp_hi, clamp_on, partials);
+            return check_launch("k_sumsq_stream16");
+        }
+    }
     switch (dt) {
         case OXZ_F32: k_sumsq<OXZ_F32, ILP, CHECK><<<grid, block, 0, s>>>(grads, map, tile_meta, present, inv_scale, clamp_hi, clamp_on, partials); break;
         case OXZ_BF16: k_sumsq<OXZ_BF16, ILP, CHECK><<<grid, block, 0, s>>>(grads, map, tile_meta, present, inv_scale, clamp_hi, clamp_on, partials); break;
