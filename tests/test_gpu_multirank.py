@@ -305,3 +305,31 @@ def test_two_ranks_equal_one_rank_fed_the_summed_gradients():
                 assert np.all(np.abs(merged - ref64) <= 1e-6 * (np.abs(ref64) + math.sqrt(float(np.mean(ref64 ** 2))))), (kind, i)
     single.destroy()
     g.close()
+
+
+def test_spike_guard_vetoes_the_same_step_on_every_rank():
+    """tests/spike_guard.rs with two ranks: the guard judges the loss summed over ranks, so every rank skips the same
+    step (skip list [F,F,F,T,F]); a spike skip with finite gradients leaves the optimizer and the loss scale untouched."""
+    world = 2
+    numel = [3000, 64]
+    g = Group(world, [0, 0], "local", gd=ox.F16, pd=ox.F16, seed=81, numel=numel, no_decay=[False, True])
+    cfg = ox.TrainerConfig(max_grad_norm=1e9, loss_scale=ox.LossScaleConfig(initial=1024.0, growth_interval=100),
+                           spike_guard=ox.SpikeGuardConfig(window=4, z_threshold=6.0, min_steps=2))
+    trainers = [ox.LitTrainerStep(cfg, g.opts[r]) for r in range(world)]
+    for t in trainers:
+        t.loss_probe = lambda index, loss: 1e3 if index == 3 else loss  # the scripted spike of src/metrics/state.rs:122-152
+    history = [[] for _ in range(world)]
+    for step in range(5):
+        before = g.merged(ffi.STATE_MASTER)
+        out = list(g.pool.map(lambda r: trainers[r].training_step(0.5 + 0.05 * (step % 2)), range(world)))
+        for r, (loss, norm) in enumerate(out):
+            history[r].append((loss, math.isfinite(norm), trainers[r].optimizer_timestep(), trainers[r].loss_scale_state().consecutive_ok))
+        after = g.merged(ffi.STATE_MASTER)
+        changed = any(not np.array_equal(bits(a), bits(b)) for a, b in zip(before, after))
+        assert changed == (step != 3)
+    assert history[0] == history[1]
+    assert [h[2] for h in history[0]] == [1, 2, 3, 3, 4]          # the vetoed step does not count
+    assert [h[3] for h in history[0]] == [1, 2, 3, 3, 4]          # and leaves the scaler's clean-step count alone
+    assert history[0][3][0] == 1e3 and abs(history[0][0][0] - 1.0) < 1e-12  # the loss is the sum over the ranks
+    assert all(t.spike_guard.state["skipped"] == 1 and t.spike_guard.state["observed"] == 4 for t in trainers)
+    g.close()
