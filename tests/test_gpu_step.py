@@ -261,6 +261,32 @@ def test_flatten_packs_per_tensor_gradients():
     opt.destroy()
 
 
+def test_param_groups_with_their_own_lr_scale_and_decay():
+    # boostr ParamGroup{ids, lr_scale, weight_decay} (src/weight_decay/plan.rs:113-122): five distinct groups at once
+    numel = [1000, 300, 777, 64, 2048]
+    lr_scale = [1.0, 0.5, 0.5, 1.0, 0.25]
+    no_decay = [False, False, True, True, False]
+    master, m, v, grads = seeded_state(numel, 16, 1e-3, 1, ox.BF16)
+    opt = ox.DpOptimizer(numel, no_decay, ox.BF16, ox.BF16, lr_scale=lr_scale)
+    assert opt.info.n_groups == 5
+    ref = orc.StepState([p.copy() for p in master], [x.copy() for x in m], [x.copy() for x in v],
+                        [orc.to_bf16(p) for p in master], orc.BF16, lr_scale=lr_scale,
+                        group_wd=[0.0 if nd else NAN for nd in no_decay])
+    for i in range(len(numel)):
+        opt.import_tensor(ffi.STATE_MASTER, i, master[i])
+        opt.import_tensor(ffi.STATE_EXP_AVG, i, m[i])
+        opt.import_tensor(ffi.STATE_EXP_AVG_SQ, i, v[i])
+        opt.import_tensor(ffi.STATE_GRADS, i, grads[0][i])
+    cfg = dict(lr=1e-3, max_grad_norm=1e9, eps=1e-8)
+    for _ in range(2):
+        opt.step(ox.StepConfig(**cfg))
+        orc.step(ref, [grads[0]], orc.BF16, orc.StepConfig(**cfg))
+    for kind, arrs in ((ffi.STATE_MASTER, ref.master), (ffi.STATE_EXP_AVG, ref.exp_avg), (ffi.STATE_EXP_AVG_SQ, ref.exp_avg_sq), (ffi.STATE_WORK, ref.work)):
+        for i in range(len(numel)):
+            assert np.array_equal(bits(opt.export_tensor(kind, i)), bits(arrs[i])), (kind, i)
+    opt.destroy()
+
+
 def test_f32_gradients_need_only_16_byte_alignment():
     # caller-owned f32 memory is promised 16-byte aligned, not 32: the norm and the flatten must accept it
     import torch
