@@ -147,11 +147,11 @@ int32_t oxz_plan_set_stream(oxz_plan* plan, void* stream);
  * Replaces the state boostr's AdamW owns: exp_avg, exp_avg_sq, the f32 master and the applied-step
  * count (src/checkpoint_set/optimizer_io.rs:1-5), plus the flat gradient and working-weight buffers. */
 
-/* Allocates the device buffers (zero-filled). `comm` may be NULL at world 1. With OXZ_SYNC_P2P this is
- * collective: ranks exchange peer mappings of their gradient and weight buffers. */
+/* Allocates the device buffers (zero-filled). `comm` may be NULL at world 1. With OXZ_SYNC_P2P and OXZ_SYNC_COPY
+ * this is collective: ranks exchange peer mappings of their gradient and weight buffers. */
 int32_t oxz_state_alloc(oxz_plan* plan, oxz_comm* comm);
 /* Device pointers of the flat buffers. grads: padded_total x grad_dtype. work: padded_total x param_dtype
- * (for param_dtype F32 it is the master itself and only valid at world 1). master/exp_avg/exp_avg_sq:
+ * (at world 1 with param_dtype F32 it is the master itself: no separate copy is kept). master/exp_avg/exp_avg_sq:
  * local_elems x f32. A backward pass may write its gradients straight into grads + offsets[i]. */
 int32_t oxz_state_pointers(const oxz_plan* plan, void** grads, void** work, void** master, void** exp_avg,
                            void** exp_avg_sq);
