@@ -248,6 +248,14 @@ typedef struct oxz_step_profile {
 } oxz_step_profile;
 /* Grid sizes the plan launches with (blocks of 256 threads) and the device's SM count. */
 int32_t oxz_plan_launch_geometry(const oxz_plan* plan, int32_t* sm_count, int32_t* norm_blocks, int32_t* update_blocks);
+/* Which kernel did the most recent pull of the peers' gradients (OXZ_SYNC_P2P): per-lane loads, or bulk
+ * asynchronous copies into shared memory (16-bit gradients, 2, 4 or 8 ranks, every tensor present, a bucket's
+ * shard a multiple of 8 tiles; OXZ_PULL_BULK=0 in the environment turns it off). Both give the same bits. No
+ * reference counterpart: a tuning and test aid. */
+#define OXZ_PULL_KERNEL_NONE 0
+#define OXZ_PULL_KERNEL_LOADS 1
+#define OXZ_PULL_KERNEL_BULK 2
+int32_t oxz_plan_last_pull_kernel(const oxz_plan* plan, int32_t* kind);
 /* on != 0: record the events every step (a few microseconds); off by default. */
 int32_t oxz_plan_set_profile(oxz_plan* plan, int32_t on);
 int32_t oxz_step_profile_read(oxz_plan* plan, oxz_step_profile* out);

@@ -125,6 +125,7 @@ SIGNATURES = {
     "oxz_step_wait": (C.c_int32, [vp, C.POINTER(StepResult)]),
     "oxz_step": (C.c_int32, [vp, vp, C.POINTER(Hyper), u8p, f64p, C.c_uint32, C.POINTER(StepResult)]),
     "oxz_plan_launch_geometry": (C.c_int32, [vp] + [C.POINTER(C.c_int32)] * 3),
+    "oxz_plan_last_pull_kernel": (C.c_int32, [vp, C.POINTER(C.c_int32)]),
     "oxz_plan_set_profile": (C.c_int32, [vp, C.c_int32]),
     "oxz_step_profile_read": (C.c_int32, [vp, C.POINTER(StepProfile)]),
     "oxz_grad_norm": (C.c_int32, [vp, C.c_int32, C.c_uint64, C.c_double, C.c_double, vp, f64p]),

@@ -71,6 +71,8 @@ struct DevScalars {
     float c1, c2;       // clip coefficients applied in this order
     int32_t overflow;
     int32_t skip;       // overflow or spike veto: the update kernel returns at once
+    int32_t wait_expired;  // a bounded wait inside a kernel ran out (bulk-copy pull): the step is reported failed
+    int32_t reserved;
 };
 
 struct PeerTable {
@@ -88,6 +90,7 @@ struct LaunchGeom {
     int sm_count;
     int norm_blocks;   // multiple of the cluster size
     int pull_blocks[3];  // per gradient dtype (f32, bf16, f16), never more than norm_blocks
+    int bulk_blocks[3];  // bulk-copy pull, per rank count 2 / 4 / 8
     int adam_blocks;
 };
 int32_t query_geom(int device, LaunchGeom* g);
@@ -106,6 +109,12 @@ int32_t launch_sumsq_plain(cudaStream_t s, int blocks, const void* grads, int32_
 int32_t launch_pull_sumsq(cudaStream_t s, const LaunchGeom& g, const PeerTable& peers, int32_t world, int staged, int32_t dt,
                           const TileMap& map, const uint32_t* tile_meta, const uint8_t* present, bool check_present,
                           float inv_scale, float clamp_hi, int32_t clamp_on, float* reduced, double* partials);
+// The pull-reduce with 1-D bulk asynchronous copies into shared memory (16-bit gradients, 2/4/8 ranks, every tensor
+// present, shard and range boundaries on multiples of 8 tiles). Returns OXZ_ERR_UNSUPPORTED when the shape does not fit.
+bool pull_bulk_fits(const TileMap& map, int32_t world, int32_t dt, bool check_present);
+int32_t launch_pull_bulk(cudaStream_t s, const LaunchGeom& g, const PeerTable& peers, int32_t world, int32_t dt,
+                         const TileMap& map, float inv_scale, float clamp_hi, int32_t clamp_on, float* reduced,
+                         double* partials, uint32_t slots, DevScalars* scalars);
 // partials[slots][3] -> acc[3] = {sum, inf count, nan count}
 int32_t launch_reduce_partials(cudaStream_t s, const double* partials, uint32_t slots, double* acc);
 // acc[3] -> scalars (norm, clip coefficients, decisions)
@@ -190,6 +199,7 @@ struct oxz_plan {
     cudaEvent_t ev_produced = nullptr, ev_early = nullptr;
     std::vector<uint8_t> early_done;   // per bucket
     uint32_t early_groups = 0;         // partial-sum groups already written this step
+    int32_t last_pull_kernel = 0;      // OXZ_PULL_KERNEL_* of the most recent peer pull
     double early_scale = 0.0, early_clamp = 0.0;
 
     // step bookkeeping

@@ -448,6 +448,124 @@ __global__ void __cluster_dims__(CLUSTER, 1, 1) __launch_bounds__(THREADS)
     cluster_reduce_store(a, partials);
 }
 
+// ---------------------------------------------------------------- pull-reduce with bulk asynchronous copies
+//
+// The same work as k_pull_sumsq for the common shape (16-bit gradients, 2, 4 or 8 ranks, every tensor present), with
+// the peers' tiles brought into shared memory by 1-D bulk asynchronous copies (cp.async.bulk + mbarrier) instead of
+// per-lane loads: one elected thread issues WORLD copies of 4 KiB (8 tiles) per stage, STAGES stages deep, so the
+// NVLink requests are large and independent of the warps' progress. Measured on two B200 with both directions
+// loaded: 669 GB/s per direction for bulk reads against 635 GB/s for 128-bit loads. No cluster multicast is used:
+// every block fetches what it needs itself. Every wait on an mbarrier is bounded; when a bound runs out the block
+// records it in scalars->wait_expired, waits once more (bounded) for its copies in flight, and returns.
+constexpr int BULK_TILES = 8;                       // tiles per chunk: one per warp
+constexpr uint32_t BULK_BYTES = BULK_TILES * TILE * 2;  // 4 KiB per source and chunk
+constexpr uint32_t BULK_SPIN_LIMIT = 1u << 22;
+
+__device__ __forceinline__ uint32_t smem_addr(const void* p) { return static_cast<uint32_t>(__cvta_generic_to_shared(p)); }
+
+__device__ __forceinline__ bool mbar_wait_bounded(uint32_t bar, uint32_t parity, uint32_t limit) {
+    for (uint32_t spins = 0; spins < limit; spins++) {
+        uint32_t done;
+        asm volatile("{ .reg .pred p; mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2; selp.u32 %0, 1, 0, p; }"
+                     : "=r"(done) : "r"(bar), "r"(parity) : "memory");
+        if (done) return true;
+    }
+    return false;
+}
+
+template <int DT, int WORLD, int STAGES>
+__global__ void __cluster_dims__(CLUSTER, 1, 1) __launch_bounds__(THREADS)
+    k_pull_bulk(PeerTable peers, TileMap map, float inv_scale, float clamp_hi, int clamp_on, float* __restrict__ reduced,
+                double* __restrict__ partials, DevScalars* __restrict__ scalars) {
+    static_assert(DT == OXZ_BF16 || DT == OXZ_F16, "16-bit gradients only");
+    extern __shared__ __align__(128) unsigned char bulk_smem[];
+    __shared__ __align__(8) uint64_t bar[STAGES];
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    constexpr uint32_t STAGE_BYTES = BULK_BYTES * WORLD;
+    const uint32_t n_chunks = (map.n_local_tiles - map.first_tile) / BULK_TILES;
+    NormAcc a;
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < STAGES; s++) asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" ::"r"(smem_addr(&bar[s])));
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    __syncthreads();
+    auto issue = [&](uint32_t chunk, int stage) {  // one thread: expect the bytes, then one copy per rank
+        const uint32_t lt0 = map.first_tile + chunk * BULK_TILES;
+        const uint64_t byte0 = static_cast<uint64_t>(flat_tile(map, lt0)) * TILE * 2;
+        const uint32_t b = smem_addr(&bar[stage]);
+        asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(b), "r"(STAGE_BYTES) : "memory");
+#pragma unroll
+        for (int r = 0; r < WORLD; r++)
+            asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+                         ::"r"(smem_addr(bulk_smem + stage * STAGE_BYTES + r * BULK_BYTES)),
+                           "l"(static_cast<const unsigned char*>(peers.grads[r]) + byte0), "r"(BULK_BYTES), "r"(b) : "memory");
+    };
+    uint32_t issued = 0;  // chunks this block has issued so far (thread 0's count is the one used)
+    if (threadIdx.x == 0)
+        for (int s = 0; s < STAGES; s++) {
+            const uint32_t c = blockIdx.x + static_cast<uint32_t>(s) * gridDim.x;
+            if (c < n_chunks) { issue(c, s); issued++; }
+        }
+    int stage = 0;
+    uint32_t parity = 0;
+    bool ok = true;
+    for (uint32_t c = blockIdx.x; c < n_chunks; c += gridDim.x) {
+        if (!mbar_wait_bounded(smem_addr(&bar[stage]), parity, BULK_SPIN_LIMIT)) {
+            ok = false;
+            break;
+        }
+        const unsigned char* st = bulk_smem + stage * STAGE_BYTES + warp * (TILE * 2) + lane * 16;
+        float s8[8];
+        {
+            RawVec<DT> v;
+            v.v = *reinterpret_cast<const uint4*>(st);
+            widen_raw<DT>(v, s8);
+        }
+#pragma unroll
+        for (int r = 1; r < WORLD; r++) {
+            RawVec<DT> v;
+            v.v = *reinterpret_cast<const uint4*>(st + r * BULK_BYTES);
+            float p8[8];
+            widen_raw<DT>(v, p8);
+#pragma unroll
+            for (int i = 0; i < 8; i++) s8[i] = __fadd_rn(s8[i], p8[i]);
+        }
+        const uint32_t lt = map.first_tile + c * BULK_TILES + warp;
+        store8<OXZ_F32>(reduced, static_cast<uint64_t>(lt) * TILE + lane * 8, s8);
+        acc8(s8, inv_scale, clamp_hi, clamp_on != 0, a);
+        __syncthreads();  // every warp has read this stage: it may be refilled
+        const uint32_t nc = c + static_cast<uint32_t>(STAGES) * gridDim.x;
+        if (threadIdx.x == 0 && nc < n_chunks) { issue(nc, stage); issued++; }
+        if (++stage == STAGES) { stage = 0; parity ^= 1; }
+    }
+    if (!ok) {
+        // A wait ran out: say so, then give the copies still in flight into this block's shared memory one more
+        // bounded chance to land before the block ends. The partial sums of this block are incomplete; the host
+        // reports the step as failed.
+        if (threadIdx.x == 0) atomicExch(&scalars->wait_expired, 1);
+        for (int s = 0; s < STAGES; s++) mbar_wait_bounded(smem_addr(&bar[s]), (s < stage) ? (parity ^ 1) : parity, BULK_SPIN_LIMIT);
+    }
+    (void)issued;
+    // the tiles past the last whole chunk (fewer than BULK_TILES, at the end of the last bucket's shard): plain loads
+    const uint32_t tail0 = map.first_tile + n_chunks * BULK_TILES;
+    if (blockIdx.x == gridDim.x - 1 && tail0 + warp < map.n_local_tiles) {
+        const uint32_t lt = tail0 + warp;
+        const uint64_t fe = static_cast<uint64_t>(flat_tile(map, lt)) * TILE + lane * 8;
+        float s8[8];
+        load8<DT>(peers.grads[0], fe, s8);
+#pragma unroll
+        for (int r = 1; r < WORLD; r++) {
+            float p8[8];
+            load8<DT>(peers.grads[r], fe, p8);
+#pragma unroll
+            for (int i = 0; i < 8; i++) s8[i] = __fadd_rn(s8[i], p8[i]);
+        }
+        store8<OXZ_F32>(reduced, static_cast<uint64_t>(lt) * TILE + lane * 8, s8);
+        acc8(s8, inv_scale, clamp_hi, clamp_on != 0, a);
+    }
+    cluster_reduce_store(a, partials);
+}
+
 // One block: adds the per-cluster partials in index order.
 __global__ void __launch_bounds__(THREADS) k_reduce_partials(const double* __restrict__ partials, uint32_t slots,
                                                              double* __restrict__ acc) {
@@ -680,6 +798,11 @@ int32_t query_geom(int device, LaunchGeom* g) {
         }
     }
     g->norm_blocks = nb > 0 ? nb : CLUSTER;
+    for (int i = 0; i < 3; i++) {
+        int bb = g->sm_count * 2;
+        bb -= bb % CLUSTER;
+        g->bulk_blocks[i] = bb < g->norm_blocks ? bb : g->norm_blocks;
+    }
     g->adam_blocks = g->sm_count * adam_blocks_per_sm(adam_variant());
     return OXZ_OK;
 }
@@ -771,6 +894,66 @@ int32_t launch_pull_sumsq(cudaStream_t s, const LaunchGeom& g, const PeerTable& 
                           float inv_scale, float clamp_hi, int32_t clamp_on, float* reduced, double* partials) {
     return check_present ? launch_pull_c<true>(s, g, peers, world, staged, dt, map, tile_meta, present, inv_scale, clamp_hi, clamp_on, reduced, partials)
                          : launch_pull_c<false>(s, g, peers, world, staged, dt, map, tile_meta, present, inv_scale, clamp_hi, clamp_on, reduced, partials);
+}
+
+template <int DT, int WORLD, int STAGES>
+static int32_t launch_pull_bulk_t(cudaStream_t s, int blocks, const PeerTable& peers, const TileMap& map, float inv_scale,
+                                  float clamp_hi, int32_t clamp_on, float* reduced, double* partials, DevScalars* scalars) {
+    const size_t smem = static_cast<size_t>(BULK_BYTES) * WORLD * STAGES;
+    // Per instantiation and device: allow the dynamic shared memory, then size the grid to the clusters that are
+    // resident at once with it (a persistent grid must be one wave). Idempotent: a race only repeats the calls.
+    static int resident[64] = {};
+    int dev = 0;
+    cudaGetDevice(&dev);
+    if (dev < 0 || dev >= 64) return fail(OXZ_ERR_UNSUPPORTED, "device ordinal %d is past 64", dev);
+    if (resident[dev] == 0) {
+        cudaError_t e = cudaFuncSetAttribute(k_pull_bulk<DT, WORLD, STAGES>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        if (e != cudaSuccess) return fail(OXZ_ERR_CUDA, "cudaFuncSetAttribute(k_pull_bulk): %s", cudaGetErrorString(e));
+        cudaLaunchConfig_t cfg = {};
+        cfg.gridDim = dim3(CLUSTER * 1024);
+        cfg.blockDim = dim3(THREADS);
+        cfg.dynamicSmemBytes = smem;
+        cudaLaunchAttribute attr;
+        attr.id = cudaLaunchAttributeClusterDimension;
+        attr.val.clusterDim.x = CLUSTER;
+        attr.val.clusterDim.y = 1;
+        attr.val.clusterDim.z = 1;
+        cfg.attrs = &attr;
+        cfg.numAttrs = 1;
+        int n = 0;
+        if (cudaOccupancyMaxActiveClusters(&n, k_pull_bulk<DT, WORLD, STAGES>, &cfg) != cudaSuccess || n <= 0) {
+            cudaGetLastError();
+            n = blocks / CLUSTER / 2;
+        }
+        resident[dev] = n * CLUSTER > 0 ? n * CLUSTER : CLUSTER;
+    }
+    if (blocks > resident[dev]) blocks = resident[dev];
+    k_pull_bulk<DT, WORLD, STAGES><<<dim3(blocks), dim3(THREADS), smem, s>>>(peers, map, inv_scale, clamp_hi, clamp_on, reduced, partials, scalars);
+    return check_launch("k_pull_bulk");
+}
+
+bool pull_bulk_fits(const TileMap& map, int32_t world, int32_t dt, bool check_present) {
+    if (check_present || dt == OXZ_F32 || (world != 2 && world != 4 && world != 8)) return false;
+    // a chunk must not straddle two buckets' shards; a ragged end of the last shard is handled by plain loads
+    if (map.tiles_per_shard % BULK_TILES || map.first_tile % BULK_TILES) return false;
+    return true;
+}
+
+int32_t launch_pull_bulk(cudaStream_t s, const LaunchGeom& g, const PeerTable& peers, int32_t world, int32_t dt,
+                         const TileMap& map, float inv_scale, float clamp_hi, int32_t clamp_on, float* reduced,
+                         double* partials, uint32_t slots, DevScalars* scalars) {
+    int blocks = g.bulk_blocks[world == 2 ? 0 : world == 4 ? 1 : 2];
+    if (static_cast<uint32_t>(blocks / CLUSTER) > slots) blocks = static_cast<int>(slots) * CLUSTER;  // one partial slot per cluster
+    if (blocks < CLUSTER) return fail(OXZ_ERR_INVALID, "launch_pull_bulk: no partial slot to write to");
+#define OXZ_BULK(DT) \
+    switch (world) { \
+        case 2: return launch_pull_bulk_t<DT, 2, 4>(s, blocks, peers, map, inv_scale, clamp_hi, clamp_on, reduced, partials, scalars); \
+        case 4: return launch_pull_bulk_t<DT, 4, 4>(s, blocks, peers, map, inv_scale, clamp_hi, clamp_on, reduced, partials, scalars); \
+        default: return launch_pull_bulk_t<DT, 8, 3>(s, blocks, peers, map, inv_scale, clamp_hi, clamp_on, reduced, partials, scalars); \
+    }
+    if (dt == OXZ_BF16) { OXZ_BULK(OXZ_BF16) }
+    OXZ_BULK(OXZ_F16)
+#undef OXZ_BULK
 }
 
 int32_t launch_reduce_partials(cudaStream_t s, const double* partials, uint32_t slots, double* acc) {

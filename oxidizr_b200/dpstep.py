@@ -570,6 +570,12 @@ class DpOptimizer:
         check(lib().oxz_plan_launch_geometry(self._h, *[C.byref(x) for x in v]))
         return dict(sm_count=v[0].value, norm_blocks=v[1].value, update_blocks=v[2].value)
 
+    def last_pull_kernel(self) -> int:
+        """0 none yet, 1 per-lane loads, 2 bulk asynchronous copies: the kernel of the most recent peer pull."""
+        v = C.c_int32()
+        check(lib().oxz_plan_last_pull_kernel(self._h, C.byref(v)))
+        return v.value
+
     def set_profile(self, on: bool) -> None:
         """Per-phase CUDA-event timing of each step (the PROFILE_TRAIN switch, src/trainer.rs:262-263)."""
         check(lib().oxz_plan_set_profile(self._h, int(on)))

@@ -139,6 +139,31 @@ def test_sharded_p2p_step_is_bit_identical_to_the_replicated_step(kind, world, d
     g.close()
 
 
+@pytest.mark.parametrize("bulk", [True, False])
+@pytest.mark.parametrize("world,bucket_bytes", [(2, 16384), (4, 16384), (8, 32768), (2, 8192 + 4096)])
+@pytest.mark.parametrize("gd", [ox.BF16, ox.F16])
+def test_bulk_copy_pull_gives_the_same_bits_as_the_per_lane_pull(world, bucket_bytes, gd, bulk, monkeypatch):
+    """The pull has two kernels: bulk asynchronous copies into shared memory where a bucket's shard is a multiple of
+    8 tiles, per-lane loads otherwise. Both must reproduce the replicated step bit for bit, ragged last shard included."""
+    monkeypatch.setenv("OXZ_PULL_BULK", "1" if bulk else "0")
+    g = Group(world, [0] * world, "local", gd=gd, pd=gd, seed=31, bucket_bytes=bucket_bytes)
+    shard_tiles = bucket_bytes // 2 // 256 // world
+    expect = 2 if (bulk and shard_tiles % 8 == 0) else 1
+    for _ in range(2):
+        out, ref = g.step(ox.StepConfig(max_grad_norm=1e9, loss_scale=8.0 if gd == ox.F16 else float("nan")))
+        assert {opt.last_pull_kernel() for opt in g.opts} == {expect}
+        for res, _ in out:
+            assert (res.overflow, res.applied, res.timestep) == (ref.overflow, ref.applied, ref.timestep)
+            assert abs(res.grad_norm - ref.grad_norm) <= 1e-5 * ref.grad_norm
+        g.assert_state(exact=True)
+    # an absent tensor sends the step to the per-lane kernel, which knows how to leave tiles out
+    present = [True, True, False, True, True, True, True]
+    g.step(ox.StepConfig(max_grad_norm=1e9, loss_scale=8.0 if gd == ox.F16 else float("nan")), present=present)
+    assert {opt.last_pull_kernel() for opt in g.opts} == {1}
+    g.assert_state(exact=True)
+    g.close()
+
+
 @pytest.mark.parametrize("mode", [ox.SYNC_P2P, ox.SYNC_COPY])
 @pytest.mark.parametrize("kind,world,devices", layouts())
 def test_sharded_step_with_clipping_and_absent_tensors(kind, world, devices, mode):
