@@ -110,6 +110,7 @@ def cpu_arm(steps: int, warmup: int, threads: int | None = None):
     pick = list(range(1, 1 + 9 * 4))  # 4 layers x (2 norms + 4 attention + 3 MLP tensors); the embedding is skipped
     numel = [tensors[i].elements for i in pick]
     P = sum(numel)
+    all_threads = orc.lib().orc_num_threads()
     if threads:
         orc.lib().orc_set_num_threads(threads)
     cores = orc.lib().orc_num_threads()
@@ -126,6 +127,7 @@ def cpu_arm(steps: int, warmup: int, threads: int | None = None):
     for _ in range(steps):
         orc.step(state, [grads], orc.BF16, cfg)
     dt = (time.perf_counter() - t0) / max(steps, 1)
+    orc.lib().orc_set_num_threads(all_threads)
     sample = f"{len(pick)} tensors = 4 of 16 decoder layers, {P} of 1235814400 params, {steps} steps"
     return P / dt, dt * 1e3, cores, sample
 
@@ -178,7 +180,7 @@ def run_gpu(args):
     plan = ox.DecayPlan(ox.WeightDecaySpec("skip_1d"), tensors)
     numel = [t.elements for t in tensors]
     P = sum(numel)
-    mode = {"p2p": ox.SYNC_P2P, "nccl": ox.SYNC_NCCL, "copy": ox.SYNC_COPY}[args.sync] if world > 1 else ox.SYNC_SINGLE
+    mode = {"p2p": ox.SYNC_P2P, "nccl": ox.SYNC_NCCL, "copy": ox.SYNC_COPY, "replicated": ox.SYNC_REPLICATED}[args.sync] if world > 1 else ox.SYNC_SINGLE
     opt = ox.DpOptimizer(numel, plan.no_decay, ox.BF16, ox.BF16, world=world, rank=rank, sync_mode=mode,
                          device=local_rank, comm=comm)
     ptr, info = opt.pointers(), opt.info
@@ -203,7 +205,7 @@ def run_gpu(args):
     gen.manual_seed(SEED + 1 + rank)
     for off, n in zip(opt.offsets, numel):
         grads[off:off + n] = torch.empty(n, device="cuda", dtype=torch.float32).normal_(0.0, 1e-3, generator=gen).to(torch.bfloat16)
-    if world == 1:
+    if world == 1 or mode == ox.SYNC_REPLICATED:
         work.copy_(master.to(torch.bfloat16))
     opt.timestep = 1
     torch.cuda.synchronize()
@@ -284,9 +286,12 @@ def run_gpu(args):
         overlap = {"buckets": nb, "buckets_reduced_during_backward": early, "exposed_ms_per_step": statistics.median(exposed)}
 
     peak, peak_kind = measured_peaks()
+    totals = sorted(p.total_ms for p in profs)
+    pct = lambda q: totals[min(len(totals) - 1, int(q * len(totals)))]  # noqa: E731
+    pull_kernel = {0: None, 1: "k_pull_sumsq", 2: "k_pull_bulk"}[opt.last_pull_kernel()]
     upd = statistics.mean(p.update_ms for p in profs)
     nrm = statistics.mean(p.norm_ms for p in profs)
-    local_params = P / world
+    local_params = P if mode == ox.SYNC_REPLICATED else P / world  # parameters one rank's update kernel covers
     achieved = BYTES_UPDATE * local_params / (upd * 1e-3) / 1e9
     line = {
         "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps, "warmup": max(args.warmup, 3),
@@ -301,10 +306,12 @@ def run_gpu(args):
                      "traffic": ADAMW_TRAFFIC_RATIO * BYTES_UPDATE * local_params,
                      "traffic_source": "ncu capture of nano_dense scaled by parameters per launch",
                      "algorithmic_bytes_per_launch": BYTES_UPDATE * local_params, "kernel_ms": upd,
-                     "norm_kernel": {"kernel": "k_pull_sumsq" if mode in (ox.SYNC_P2P, ox.SYNC_COPY) else "k_sumsq_stream16",
+                     "norm_kernel": {"kernel": pull_kernel if mode in (ox.SYNC_P2P, ox.SYNC_REPLICATED) else "k_sumsq_stream16" if mode == ox.SYNC_SINGLE else "k_sumsq",
                                      "kernel_ms": nrm, "achieved_gbs": BYTES_NORM * local_params / (nrm * 1e-3) / 1e9 if world == 1 else None}},
         "phases_ms": {k: statistics.mean(getattr(p, k) for p in profs) for k in
                       ("collect_ms", "norm_ms", "decide_ms", "update_ms", "publish_ms", "total_ms")},
+        # device time of each timed step on this rank (CUDA events inside the library), for the spread
+        "step_ms_device": {"median": statistics.median(totals), "p10": pct(0.10), "p90": pct(0.90)},
         "step_roofline": step_roofline(P, world, ms_per_step, peak),
         "e2e": {"value": e2e_value, "unit": UNIT, "h2d_bytes_per_step": P * 2 * world, "d2h_bytes_per_step": 32 * world,
                 "ms_per_step": e2e_sec * 1e3 / e2e_steps, "steps": e2e_steps},
@@ -319,7 +326,9 @@ def run_gpu(args):
     if rank == 0:
         if not args.no_cpu_baseline and world == 1:
             v, ms, cores, sample = cpu_arm(3, 1)
-            line["cpu_baseline"] = {"value": v, "unit": UNIT, "cores": cores, "kind": "port", "sample": sample}
+            v1, _, _, _ = cpu_arm(1, 1, threads=1)
+            line["cpu_baseline"] = {"value": v, "unit": UNIT, "cores": cores, "kind": "port", "sample": sample,
+                                    "single_thread_value": v1}
         else:
             line["cpu_baseline"] = None
         print(json.dumps(line), flush=True)
@@ -351,7 +360,7 @@ def main():
     ap.add_argument("--steps", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", choices=["ours", "reference"], default="ours")
-    ap.add_argument("--sync", choices=["p2p", "copy", "nccl"], default="p2p", help="how ranks meet at --gpus > 1")
+    ap.add_argument("--sync", choices=["p2p", "copy", "nccl", "replicated"], default="p2p", help="how ranks meet at --gpus > 1")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--skip-e2e", action="store_true", help="profiling runs: leave the host-fed leg out")
     ap.add_argument("--workload", default=WORKLOAD, help="parameter set; the headline is llama-3.2-1b, smaller sets serve profiler captures")

@@ -49,9 +49,13 @@ typedef enum oxz_sync_mode {
     OXZ_SYNC_P2P = 1,    /* fused kernels over NVLink peer memory: pull-reduce in f32 in rank order,
                             push of the narrow weights; NCCL only for the 3-double norm all-reduce */
     OXZ_SYNC_NCCL = 2,   /* ncclReduceScatter / ncclAllGather in the gradient's own dtype */
-    OXZ_SYNC_COPY = 3    /* copy engines move the bytes over NVLink (peers' gradient slices into local staging,
+    OXZ_SYNC_COPY = 3,   /* copy engines move the bytes over NVLink (peers' gradient slices into local staging,
                             the updated weights out to every peer), pipelined by groups of buckets with the
                             kernels that sum in f32 in rank order, measure the norm and update */
+    OXZ_SYNC_REPLICATED = 4 /* the reference's own layout (full replicas, README.md:284; src/dp/reduce.rs:30-60):
+                            every rank sums every rank's gradients in f32 in rank order and runs the whole
+                            update on its own full copy of the state; nothing is sharded, no weights travel.
+                            Kept as the parity mode for the sharded ones: W times their memory and update work */
 } oxz_sync_mode;
 
 typedef struct oxz_comm oxz_comm;

@@ -3,7 +3,7 @@
 The product is ``liboxz_dpstep.so`` (hand-written sm_100a CUDA + NCCL, declared in ``include/oxz_dpstep.h``).
 This package binds it with ctypes and mirrors the reference's host-side interface for the path.
 """
-from ._ffi import BF16, F16, F32, SYNC_COPY, SYNC_NCCL, SYNC_P2P, SYNC_SINGLE, OxzError, lib  # noqa: F401
+from ._ffi import BF16, F16, F32, SYNC_COPY, SYNC_NCCL, SYNC_P2P, SYNC_REPLICATED, SYNC_SINGLE, OxzError, lib  # noqa: F401
 from . import _ffi as ffi  # noqa: F401
 from .dpstep import (Communicator, DataPosition, DecayPlan, DpOptimizer, GradScalerState, LitDataLoader, LitTrainerStep,  # noqa: F401
                      LossScaleConfig, LossScaler, LrPlan, RowLayout, SpikeGuard, SpikeGuardConfig, StepConfig,

@@ -13,7 +13,7 @@ LIB_PATH = os.path.join(_HERE, "liboxz_dpstep.so")
 
 OK, ERR_INVALID, ERR_CUDA, ERR_NCCL, ERR_STATE, ERR_ABORTED, ERR_UNSUPPORTED, ERR_DATA, ERR_TIMEOUT = range(9)
 F32, BF16, F16 = 0, 1, 2
-SYNC_SINGLE, SYNC_P2P, SYNC_NCCL, SYNC_COPY = 0, 1, 2, 3
+SYNC_SINGLE, SYNC_P2P, SYNC_NCCL, SYNC_COPY, SYNC_REPLICATED = 0, 1, 2, 3, 4
 STATE_MASTER, STATE_EXP_AVG, STATE_EXP_AVG_SQ, STATE_WORK, STATE_GRADS = range(5)
 DECAY_ALL, SKIP_1D, SKIP_ALL = 0, 1, 2
 LR_CONSTANT, LR_COSINE, LR_LINEAR, LR_WSD = range(4)

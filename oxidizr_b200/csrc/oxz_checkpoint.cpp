@@ -195,7 +195,7 @@ int32_t oxz_optimizer_save(oxz_plan* p, oxz_comm* comm, const char* path, const 
     OXZ_TRY(check_call(p, comm, path, names, ndim, dims, "oxz_optimizer_save"));
     OXZ_CUDA(cudaSetDevice(p->device));
     const bool has_master = p->pdt != OXZ_F32;
-    const bool writer = p->rank == 0;
+    const bool writer = p->cr == 0;  // with full replicas every rank holds everything and rank 0 alone writes
     const char* next = "Check that the checkpoint directory is writable and has free space.";
 
     // header: entries in the order the data is written

@@ -155,7 +155,9 @@ struct oxz_plan {
     std::vector<uint8_t> group_of;
     std::vector<float> group_lr_scale;
     std::vector<uint8_t> group_no_decay;
-    int32_t gdt = 0, pdt = 0, world = 1, rank = 0, mode = 0, device = 0;
+    // world / rank: how the state is sharded (1 / 0 for OXZ_SYNC_REPLICATED); cw / cr: the communicator's size and
+    // this rank's place in it, which is what the gradient sum runs over
+    int32_t gdt = 0, pdt = 0, world = 1, rank = 0, cw = 1, cr = 0, mode = 0, device = 0;
     uint64_t numel_total = 0, total_tiles = 0;
     uint64_t bucket_tiles = 0, n_buckets = 0, last_bucket_tiles = 0, local_tiles = 0;
     std::vector<uint32_t> tile_meta;  // per flat tile: tensor | group << 24
@@ -185,6 +187,7 @@ struct oxz_plan {
     bool profile = false;
     cudaEvent_t ev[6] = {nullptr, nullptr, nullptr, nullptr, nullptr, nullptr};
     oxz::PeerTable peers{};
+    oxz::PeerTable own_work{};  // work[0] = this rank's weights, nothing else
     std::vector<void*> ipc_opened;
     // OXZ_SYNC_COPY: staging for the peers' gradient slices, one copy stream per peer, pipeline events
     void* stage = nullptr;

@@ -63,20 +63,23 @@ int32_t oxz_plan_create(const oxz_plan_desc* d, oxz_plan** out) {
     if (d->rank < 0 || d->rank >= d->world)
         return fail(OXZ_ERR_INVALID, "rank %d is not below world size %d. Pass a rank in [0, %d).", d->rank,
                     d->world, d->world);
-    if (d->sync_mode < OXZ_SYNC_SINGLE || d->sync_mode > OXZ_SYNC_COPY)
+    if (d->sync_mode < OXZ_SYNC_SINGLE || d->sync_mode > OXZ_SYNC_REPLICATED)
         return fail(OXZ_ERR_INVALID, "oxz_plan_create: unknown sync mode %d", d->sync_mode);
     if ((d->sync_mode == OXZ_SYNC_SINGLE) != (d->world == 1))
         return fail(OXZ_ERR_INVALID,
                     "oxz_plan_create: sync mode %d with world size %d. World 1 runs no collective and takes "
-                    "OXZ_SYNC_SINGLE; more ranks need OXZ_SYNC_P2P, OXZ_SYNC_COPY or OXZ_SYNC_NCCL",
+                    "OXZ_SYNC_SINGLE; more ranks need OXZ_SYNC_P2P, OXZ_SYNC_COPY, OXZ_SYNC_NCCL or OXZ_SYNC_REPLICATED",
                     d->sync_mode, d->world);
 
     oxz_plan* p = new oxz_plan();
     p->T = d->n_tensors;
     p->gdt = d->grad_dtype;
     p->pdt = d->param_dtype;
-    p->world = d->world;
-    p->rank = d->rank;
+    p->cw = d->world;
+    p->cr = d->rank;
+    // full replicas: the layout of a single rank, the communicator's size only for the gradient sum
+    p->world = d->sync_mode == OXZ_SYNC_REPLICATED ? 1 : d->world;
+    p->rank = d->sync_mode == OXZ_SYNC_REPLICATED ? 0 : d->rank;
     p->mode = d->sync_mode;
     p->device = d->device;
     p->numel.assign(d->numel, d->numel + d->n_tensors);
@@ -172,9 +175,10 @@ int32_t oxz_plan_bucket(const oxz_plan* p, uint64_t b, int32_t rank, uint64_t* s
     if (b >= p->n_buckets)
         return fail(OXZ_ERR_INVALID, "oxz_plan_bucket: bucket %llu of %llu", (unsigned long long)b,
                     (unsigned long long)p->n_buckets);
-    if (rank < 0 || rank >= p->world)
-        return fail(OXZ_ERR_INVALID, "rank %d is not below world size %d. Pass a rank in [0, %d).", rank, p->world,
-                    p->world);
+    if (rank < 0 || rank >= p->cw)
+        return fail(OXZ_ERR_INVALID, "rank %d is not below world size %d. Pass a rank in [0, %d).", rank, p->cw,
+                    p->cw);
+    if (p->mode == OXZ_SYNC_REPLICATED) rank = 0;  // every rank owns everything
     const uint64_t tiles = (b == p->n_buckets - 1) ? p->last_bucket_tiles : p->bucket_tiles;
     const uint64_t shard = tiles / (uint64_t)p->world;
     const uint64_t s = b * p->bucket_tiles;
@@ -187,9 +191,10 @@ int32_t oxz_plan_bucket(const oxz_plan* p, uint64_t b, int32_t rank, uint64_t* s
 
 int32_t oxz_plan_local_index(const oxz_plan* p, int32_t rank, uint64_t flat_index, uint64_t* local_index) {
     if (!p || !local_index) return fail(OXZ_ERR_INVALID, "oxz_plan_local_index: null argument");
-    if (rank < 0 || rank >= p->world)
-        return fail(OXZ_ERR_INVALID, "rank %d is not below world size %d. Pass a rank in [0, %d).", rank, p->world,
-                    p->world);
+    if (rank < 0 || rank >= p->cw)
+        return fail(OXZ_ERR_INVALID, "rank %d is not below world size %d. Pass a rank in [0, %d).", rank, p->cw,
+                    p->cw);
+    if (p->mode == OXZ_SYNC_REPLICATED) rank = 0;  // every rank owns everything
     if (flat_index >= p->total_tiles * TILE)
         return fail(OXZ_ERR_INVALID, "oxz_plan_local_index: element %llu is past the flat space of %llu",
                     (unsigned long long)flat_index, (unsigned long long)(p->total_tiles * TILE));

@@ -48,11 +48,11 @@ int32_t exchange_peers(oxz_plan* p, oxz_comm* c) {
     mine.device = p->device;
     OXZ_CUDA(cudaIpcGetMemHandle(&mine.grads_handle, p->grads));
     OXZ_CUDA(cudaIpcGetMemHandle(&mine.work_handle, p->work));
-    const int W = p->world;
+    const int W = p->cw;
     std::vector<PeerBlob> all(W);
     OXZ_TRY(comm_allgather_host(c, &mine, all.data(), sizeof(PeerBlob), p->stream));
     for (int r = 0; r < W; r++) {
-        if (r == p->rank) {
+        if (r == p->cr) {
             p->peers.grads[r] = p->grads;
             p->peers.work[r] = p->work;
             continue;
@@ -201,11 +201,11 @@ int32_t oxz_state_alloc(oxz_plan* p, oxz_comm* comm) {
     if (!p) return fail(OXZ_ERR_INVALID, "oxz_state_alloc: null plan");
     if (p->allocated) return fail(OXZ_ERR_STATE, "oxz_state_alloc: the plan already has device state");
     if (p->own_stream) return fail(OXZ_ERR_STATE, "oxz_state_alloc: an earlier allocation of this plan failed midway. Destroy the plan and create it again");
-    if (p->world > 1) {
+    if (p->cw > 1) {
         OXZ_TRY(comm_check(comm, "oxz_state_alloc"));
-        if (comm->world != p->world || comm->rank != p->rank)
+        if (comm->world != p->cw || comm->rank != p->cr)
             return fail(OXZ_ERR_INVALID, "oxz_state_alloc: the plan is rank %d of %d but the communicator is rank %d of %d",
-                        p->rank, p->world, comm->rank, comm->world);
+                        p->cr, p->cw, comm->rank, comm->world);
     }
     OXZ_CUDA(cudaSetDevice(p->device));
     OXZ_TRY(query_geom(p->device, &p->geom));
@@ -226,8 +226,8 @@ int32_t oxz_state_alloc(oxz_plan* p, oxz_comm* comm) {
     const bool separate_work = !(p->pdt == OXZ_F32 && p->world == 1);
     if (separate_work) OXZ_CUDA(zalloc(&p->work, padded * ps));
     else p->work = p->master;
-    const bool peer_mode = p->mode == OXZ_SYNC_P2P || p->mode == OXZ_SYNC_COPY;
-    if (p->world > 1) OXZ_CUDA(zalloc(&p->reduced, local * (peer_mode ? 4 : gs)));
+    const bool peer_mode = p->mode == OXZ_SYNC_P2P || p->mode == OXZ_SYNC_COPY || p->mode == OXZ_SYNC_REPLICATED;
+    if (p->cw > 1) OXZ_CUDA(zalloc(&p->reduced, local * (peer_mode ? 4 : gs)));
     OXZ_CUDA(zalloc((void**)&p->d_tile_meta, p->total_tiles * 4));
     OXZ_CUDA(cudaMemcpy(p->d_tile_meta, p->tile_meta.data(), p->total_tiles * 4, cudaMemcpyHostToDevice));
     OXZ_CUDA(zalloc((void**)&p->d_present, p->T));
@@ -253,6 +253,7 @@ int32_t oxz_state_alloc(oxz_plan* p, oxz_comm* comm) {
     p->peers.grads[0] = p->grads;
     p->peers.work[0] = p->work;
     if (peer_mode) OXZ_TRY(exchange_peers(p, comm));
+    p->own_work.work[0] = p->work;
     if (p->mode == OXZ_SYNC_COPY) {
         // one staging slot per peer, laid out like this rank's local state; the own slot is the gradient buffer itself
         OXZ_CUDA(zalloc(&p->stage, (size_t)(p->world - 1) * local * gs));
@@ -416,15 +417,15 @@ int32_t reduce_buckets(oxz_plan* p, cudaStream_t s, const LaunchGeom& geom, uint
     // 1.24 G bf16 gradients); OXZ_PULL_BULK=0 keeps the per-lane loads.
     const char* bulk_env = getenv("OXZ_PULL_BULK");
     const bool want_bulk = !bulk_env || atoi(bulk_env) != 0;
-    if (want_bulk && pull_bulk_fits(gm, p->world, p->gdt, some_absent)) {
+    if (want_bulk && pull_bulk_fits(gm, p->cw, p->gdt, some_absent)) {
         // its grid is smaller than the group's slot count: the slots it does not write must read as zero
         OXZ_CUDA(cudaMemsetAsync(partials, 0, (size_t)slots * 3 * 8, s));
         p->last_pull_kernel = OXZ_PULL_KERNEL_BULK;
-        return launch_pull_bulk(s, geom, p->peers, p->world, p->gdt, gm, inv_scale, clamp_hi, clamp_on,
+        return launch_pull_bulk(s, geom, p->peers, p->cw, p->gdt, gm, inv_scale, clamp_hi, clamp_on,
                                 static_cast<float*>(p->reduced), partials, slots, p->d_scalars);
     }
     p->last_pull_kernel = OXZ_PULL_KERNEL_LOADS;
-    return launch_pull_sumsq(s, geom, p->peers, p->world, 0, p->gdt, gm, p->d_tile_meta, p->d_present, some_absent,
+    return launch_pull_sumsq(s, geom, p->peers, p->cw, 0, p->gdt, gm, p->d_tile_meta, p->d_present, some_absent,
                              inv_scale, clamp_hi, clamp_on, static_cast<float*>(p->reduced), partials);
 }
 
@@ -456,7 +457,7 @@ int32_t oxz_step_async(oxz_plan* p, oxz_comm* comm, const oxz_hyper* h, const ui
     if (p->inflight) return fail(OXZ_ERR_STATE, "oxz_step_async: the previous step is still in flight. Call oxz_step_wait first");
     if (n_extras > MAX_EXTRAS || (n_extras && !extras)) return fail(OXZ_ERR_INVALID, "oxz_step_async: at most %u extras", MAX_EXTRAS);
     OXZ_TRY(check_hyper(h));
-    if (p->world > 1) {
+    if (p->cw > 1) {
         OXZ_TRY(comm_check(comm, "oxz_step_async"));
         if (comm != p->comm) return fail(OXZ_ERR_INVALID, "oxz_step_async: this is not the communicator the state was allocated with");
     }
@@ -512,23 +513,25 @@ int32_t oxz_step_async(oxz_plan* p, oxz_comm* comm, const oxz_hyper* h, const ui
     fp.spike_skip = h->spike_skip ? 1 : 0;
 
     const TileMap map = tile_map(p);
-    const bool peer_mode = p->mode == OXZ_SYNC_P2P || p->mode == OXZ_SYNC_COPY;
+    const bool replicated = p->mode == OXZ_SYNC_REPLICATED;
+    const bool pulls = p->mode == OXZ_SYNC_P2P || replicated;  // the gradient sum is the fused pull kernel
+    const bool peer_mode = pulls || p->mode == OXZ_SYNC_COPY;
     uint32_t slots = peer_mode ? pull_partial_slots(p->geom, p->gdt) : norm_partial_slots(p->geom);
     const void* gsrc = p->grads;
     int32_t gsrc_dt = p->gdt;
-    int32_t* bar = p->world > 1 ? reinterpret_cast<int32_t*>(static_cast<char*>(comm->d_small) + 384) : nullptr;
+    int32_t* bar = p->cw > 1 ? reinterpret_cast<int32_t*>(static_cast<char*>(comm->d_small) + 384) : nullptr;
 
     auto mark = [&](int i) -> cudaError_t { return p->profile ? cudaEventRecord(p->ev[i], s) : cudaSuccess; };
     OXZ_CUDA(mark(0));
     OXZ_CUDA(cudaMemsetAsync(&p->d_scalars->wait_expired, 0, sizeof(int32_t), s));
-    if (p->mode == OXZ_SYNC_SINGLE || p->mode == OXZ_SYNC_P2P) {
+    if (p->mode == OXZ_SYNC_SINGLE || pulls) {
         // buckets already reduced during backward are skipped; the rest goes now, one launch per run of buckets
         uint32_t groups = p->early_groups;
         if (groups) OXZ_CUDA(cudaStreamWaitEvent(s, p->ev_early, 0));
         bool any_left = false;
         for (uint64_t b = 0; b < p->n_buckets; b++) any_left |= !(groups && p->early_done[b]);
         // every rank's remaining gradients must be complete before anyone pulls them
-        if (p->mode == OXZ_SYNC_P2P && any_left) OXZ_TRY(comm_stream_barrier(comm, bar, s));
+        if (pulls && any_left) OXZ_TRY(comm_stream_barrier(comm, bar, s));
         OXZ_CUDA(mark(1));
         for (uint64_t b = 0; b < p->n_buckets;) {
             if (groups && p->early_done[b]) { b++; continue; }
@@ -541,7 +544,7 @@ int32_t oxz_step_async(oxz_plan* p, oxz_comm* comm, const oxz_hyper* h, const ui
         }
         slots *= groups;
         p->early_groups = 0;
-        if (p->mode == OXZ_SYNC_P2P) {
+        if (pulls) {
             gsrc = p->reduced;
             gsrc_dt = OXZ_F32;
         }
@@ -596,16 +599,19 @@ int32_t oxz_step_async(oxz_plan* p, oxz_comm* comm, const oxz_hyper* h, const ui
     }
     OXZ_CUDA(mark(2));
     OXZ_TRY(launch_reduce_partials(s, p->d_partials, slots, p->d_acc));
-    if (p->world > 1) {
+    if (p->cw > 1) {
         for (uint32_t i = 0; i < n_extras; i++) p->h_extras[i] = extras[i];
         if (n_extras) OXZ_CUDA(cudaMemcpyAsync(p->d_acc + 3, p->h_extras, n_extras * 8, cudaMemcpyHostToDevice, s));
         // The one all-reduce of the step: {sum of squares, inf count, NaN count, extras...}. In P2P mode its end
-        // also tells every rank that all peers have finished reading its gradient buffer.
-        OXZ_TRY(comm_stream_allreduce_f64(comm, p->d_acc, 3 + n_extras, p->h_acc, s));
+        // also tells every rank that all peers have finished reading its gradient buffer. A full replica has
+        // measured every element itself: only the extras are summed, and a barrier stands in when there are none.
+        if (!replicated) OXZ_TRY(comm_stream_allreduce_f64(comm, p->d_acc, 3 + n_extras, p->h_acc, s));
+        else if (n_extras) OXZ_TRY(comm_stream_allreduce_f64(comm, p->d_acc + 3, n_extras, p->h_acc + 3, s));
+        else OXZ_TRY(comm_stream_barrier(comm, bar, s));
     }
     OXZ_TRY(launch_finalize(s, p->d_acc, fp, p->d_scalars));
     OXZ_CUDA(cudaMemcpyAsync(p->h_scalars, p->d_scalars, sizeof(DevScalars), cudaMemcpyDeviceToHost, s));
-    if (p->world > 1 && n_extras)
+    if (p->cw > 1 && n_extras)
         OXZ_CUDA(cudaMemcpyAsync(p->h_acc, p->d_acc, (3 + n_extras) * 8, cudaMemcpyDeviceToHost, s));
 
     OXZ_CUDA(mark(3));
@@ -641,8 +647,9 @@ int32_t oxz_step_async(oxz_plan* p, oxz_comm* comm, const oxz_hyper* h, const ui
         // every rank's copies into this rank's weight buffer must have landed before the step is reported done
         OXZ_TRY(comm_stream_barrier(comm, bar, s));
     } else {
-    OXZ_TRY(launch_adamw(s, p->geom, gsrc, gsrc_dt, p->master, p->exp_avg, p->exp_avg_sq, p->peers, n_work, p->pdt, map,
-                         p->d_tile_meta, p->d_present, some_absent, p->d_scalars, ap));
+    // p->peers lists the communicator's ranks; a full replica writes only its own weights
+    OXZ_TRY(launch_adamw(s, p->geom, gsrc, gsrc_dt, p->master, p->exp_avg, p->exp_avg_sq, replicated ? p->own_work : p->peers,
+                         n_work, p->pdt, map, p->d_tile_meta, p->d_present, some_absent, p->d_scalars, ap));
     OXZ_CUDA(mark(4));
     }
     if (p->mode == OXZ_SYNC_NCCL) {
@@ -683,7 +690,7 @@ int32_t oxz_grads_ready_async(oxz_plan* p, oxz_comm* comm, const oxz_hyper* h, c
         return fail(OXZ_ERR_INVALID, "oxz_grads_ready_async: buckets [%llu, %llu) of %llu", (unsigned long long)first_bucket,
                     (unsigned long long)(first_bucket + n_buckets), (unsigned long long)p->n_buckets);
     if (p->early_groups >= MAX_PIPE - 2) return fail(OXZ_ERR_STATE, "oxz_grads_ready_async: at most %u calls per step", MAX_PIPE - 2);
-    if (p->world > 1) {
+    if (p->cw > 1) {
         OXZ_TRY(comm_check(comm, "oxz_grads_ready_async"));
         if (comm != p->comm) return fail(OXZ_ERR_INVALID, "oxz_grads_ready_async: this is not the communicator the state was allocated with");
     }
@@ -754,7 +761,7 @@ int32_t oxz_step_wait(oxz_plan* p, oxz_step_result* res) {
     const oxz_hyper& h = p->inflight_hyper;
     const bool applied = !d.skip;
     if (applied) p->timestep += 1;
-    if (p->world > 1)
+    if (p->cw > 1)
         for (uint32_t i = 0; i < p->inflight_n_extras; i++) p->inflight_extras[i] = p->h_acc[3 + i];
     if (res) {
         res->grad_norm = d.norm;

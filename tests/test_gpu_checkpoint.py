@@ -36,14 +36,14 @@ def read_safetensors(path):
     return meta, out
 
 
-def make(world, pd=ox.BF16, seed=41, steps=2):
+def make(world, pd=ox.BF16, seed=41, steps=2, mode=None):
     plan = ox.DecayPlan(ox.WeightDecaySpec("skip_1d"), TENSORS)
     master, m, v, grads = seeded_state(NUMEL, seed, 1e-3, world, ox.BF16)
     comms = ox.Communicator.local_group(world, [0] * world, timeout=60.0) if world > 1 else [None]
     pool = ThreadPoolExecutor(world)
 
     def build(r):
-        opt = ox.DpOptimizer(NUMEL, plan.no_decay, ox.BF16, pd, world=world, rank=r, comm=comms[r], bucket_bytes=1024)
+        opt = ox.DpOptimizer(NUMEL, plan.no_decay, ox.BF16, pd, world=world, rank=r, comm=comms[r], bucket_bytes=1024, sync_mode=mode)
         for i in range(len(NUMEL)):
             opt.import_tensor(ffi.STATE_MASTER, i, master[i])
             opt.import_tensor(ffi.STATE_EXP_AVG, i, m[i])
@@ -89,6 +89,28 @@ def test_file_has_the_reference_layout_and_every_bit(world, tmp_path):
         for t, arr in zip(TENSORS, merged(opts, kind)):
             got = tensors[f"{t.name}.{suffix}"]
             assert got.shape == t.shape and np.array_equal(bits(got.reshape(-1)), bits(arr))
+    close(opts, comms)
+
+
+def test_full_replicas_write_the_file_the_shards_write(tmp_path):
+    """With OXZ_SYNC_REPLICATED every rank holds the whole state and rank 0 alone writes it; the bytes must be the
+    ones the sharded run gathers, and loading them back must reach every replica."""
+    files = []
+    for mode in (ox.SYNC_REPLICATED, ox.SYNC_P2P):
+        opts, comms, pool, _ = make(2, mode=mode)
+        path = str(tmp_path / f"mode{mode}.optimizer.safetensors")
+        list(pool.map(lambda r: opts[r].save_optimizer(path, TENSORS), range(2)))
+        files.append(open(path, "rb").read())
+        close(opts, comms)
+    assert files[0] == files[1]
+    opts, comms, pool, _ = make(2, mode=ox.SYNC_REPLICATED, seed=7, steps=0)
+    path = str(tmp_path / f"mode{ox.SYNC_REPLICATED}.optimizer.safetensors")
+    list(pool.map(lambda r: opts[r].load_optimizer(path, TENSORS), range(2)))
+    _, tensors = read_safetensors(path)
+    for o in opts:
+        assert o.timestep == 2
+        for i, t in enumerate(TENSORS):
+            assert np.array_equal(bits(o.export_tensor(ffi.STATE_EXP_AVG_SQ, i)), bits(tensors[f"{t.name}.exp_avg_sq"].reshape(-1)))
     close(opts, comms)
 
 

@@ -164,6 +164,42 @@ def test_bulk_copy_pull_gives_the_same_bits_as_the_per_lane_pull(world, bucket_b
     g.close()
 
 
+@pytest.mark.parametrize("kind,world,devices", layouts())
+@pytest.mark.parametrize("gd,pd", [(ox.BF16, ox.BF16), (ox.F32, ox.F32)])
+def test_full_replicas_step_like_the_reference_and_agree_with_the_sharded_step(kind, world, devices, gd, pd):
+    """OXZ_SYNC_REPLICATED is the reference's own arrangement (every rank sums all gradients and updates a full copy,
+    src/dp/reduce.rs:30-60): each rank alone must hold the oracle's state, bit for bit, and so must the sharded run."""
+    rep = Group(world, devices, kind, mode=ox.SYNC_REPLICATED, gd=gd, pd=pd, seed=41)
+    shd = Group(world, devices, kind, mode=ox.SYNC_P2P, gd=gd, pd=pd, seed=41)
+    cfg = ox.StepConfig(max_grad_norm=1e9)
+    for s in range(2):
+        out, ref = rep.step(cfg, extras=[1.0 + r for r in range(world)])
+        out2, _ = shd.step(cfg, extras=[1.0 + r for r in range(world)])
+        for (res, extras), (res2, extras2) in zip(out, out2):
+            assert (res.overflow, res.applied, res.timestep) == (ref.overflow, ref.applied, ref.timestep)
+            assert abs(res.grad_norm - ref.grad_norm) <= 1e-5 * ref.grad_norm
+            assert extras == extras2 == [sum(1.0 + r for r in range(world))]
+        assert len({res.grad_norm for res, _ in out}) == 1
+    for opt in rep.opts:  # every rank by itself, not a merge over ranks
+        assert opt.info.local_elems == opt.info.padded_total
+        for kind_, refs in ((ffi.STATE_MASTER, rep.ref.master), (ffi.STATE_EXP_AVG, rep.ref.exp_avg),
+                            (ffi.STATE_EXP_AVG_SQ, rep.ref.exp_avg_sq)):
+            for i, b in enumerate(refs):
+                assert np.array_equal(bits(opt.export_tensor(kind_, i)), bits(b)), (kind_, i)
+        for i in range(len(rep.numel)):
+            assert np.array_equal(bits(opt.export_tensor(ffi.STATE_WORK, i)), bits(rep.ref.work[i]))
+    shd.assert_state(exact=True)
+    # an overflow on one rank is seen by every replica
+    grads = [[x.copy() for x in rg] for rg in rep.grads]
+    grads[world - 1][1][7] = np.inf if gd == ox.F32 else 0x7F80  # +inf in f32, and its bf16 pattern
+    rep.set_grads(grads)
+    out, ref = rep.step(cfg)
+    for res, _ in out:
+        assert (res.overflow, res.applied) == (1, 0) == (ref.overflow, ref.applied)
+    rep.close()
+    shd.close()
+
+
 @pytest.mark.parametrize("mode", [ox.SYNC_P2P, ox.SYNC_COPY])
 @pytest.mark.parametrize("kind,world,devices", layouts())
 def test_sharded_step_with_clipping_and_absent_tensors(kind, world, devices, mode):
