@@ -335,6 +335,40 @@ int32_t oxz_rows_advance(const oxz_row_layout* layout, oxz_data_position pos, ui
 int32_t oxz_rows_next_window(const oxz_row_layout* layout, oxz_data_position pos, uint64_t rank, uint64_t seq_len,
                              uint64_t first_row, const uint32_t* tokens, uint64_t n_tokens, uint64_t* rows,
                              int64_t* inputs, int64_t* targets, oxz_data_position* next);
+/* ------------------------------------------------------------------ the checkpoint meta's keys on this path
+ *
+ * `checkpoint_step_N.meta.json` is CheckpointMeta (src/config.rs:1223-1302) as serde_json writes it. These are the keys
+ * the optimizer path records and reads back on resume (src/checkpoint_set/snapshot.rs:245-262); every other key is
+ * skipped on load and written empty by oxz_meta_save. A has_* flag of 0 is serde's Option::None (key absent or null). */
+typedef struct oxz_resume_meta {
+    uint64_t step;
+    int32_t has_world_size, has_global_batch_rows, has_loss_scale, has_data_position, has_spike_guard;
+    int32_t has_weight_decay_rule;
+    int32_t weight_decay_rule;      /* oxz_decay_rule; a meta without the key reads as OXZ_DECAY_ALL, the rule of runs
+                                       from before parameter groups (WeightDecaySpec::of_meta, src/weight_decay/rule.rs:68-74) */
+    uint32_t n_no_decay_patterns;   /* fetch each with oxz_meta_no_decay_pattern */
+    uint64_t world_size, global_batch_rows;
+    oxz_scaler_state loss_scale;     /* GradScalerState {scale, consecutive_ok}; f64 at full precision */
+    oxz_data_position data_position; /* DataPosition {epoch, row} (src/data/rows.rs:28-34) */
+    oxz_spike_state spike_guard;     /* SpikeGuardState (src/metrics/spike.rs:14-26) */
+    char checkpoint_file[512];
+    char optimizer_file[512];        /* empty: none */
+} oxz_resume_meta;
+/* CheckpointMeta::load restricted to the keys above. */
+int32_t oxz_meta_load(const char* path, oxz_resume_meta* out);
+int32_t oxz_meta_no_decay_pattern(const char* path, uint32_t index, char* buf, uint64_t cap);
+/* CheckpointMeta::save_to (src/config.rs:1386-1394): pretty JSON, written beside the target and renamed over it.
+ * Floats are printed so that they read back to the same bits. */
+int32_t oxz_meta_save(const char* path, const oxz_resume_meta* meta, const char* const* no_decay_patterns);
+/* check_resume_world (src/dp/resume.rs:19-55): a meta that records another world size is an error naming both (a
+ * meta without the key counts as one rank); another global batch only fills `warning` (empty otherwise). A run at
+ * step 0 and a null meta_path check nothing. */
+int32_t oxz_check_resume_world(const char* meta_path, uint64_t start_step, uint64_t world, uint64_t global_batch_rows,
+                               char* warning, uint64_t cap);
+/* read_loss_scale_state (src/loss_scale/resume.rs:14-29): the scaler state a run at start_step resumes with;
+ * *has_state = 0 at step 0, without a meta, or when the meta has no loss_scale key. */
+int32_t oxz_read_loss_scale_state(const char* meta_path, uint64_t start_step, int32_t* has_state, oxz_scaler_state* state);
+
 /* The rank-sliced row loader in stream order (LitDataLoader::with_rank + next_batch, src/data/ranks.rs:25-41,
  * src/data/positioning.rs:44-68, src/data/batch.rs:51-71) over one little-endian u32 token file mapped read-only
  * (src/data/source.rs:7-12, 204-230). Rows are seq_len + 1 tokens; rows [first_row, end_row) form the loader's range

@@ -82,6 +82,15 @@ class DataPositionC(C.Structure):
     _fields_ = [("epoch", C.c_uint64), ("row", C.c_uint64)]
 
 
+class ResumeMeta(C.Structure):
+    _fields_ = [("step", C.c_uint64), ("has_world_size", C.c_int32), ("has_global_batch_rows", C.c_int32),
+                ("has_loss_scale", C.c_int32), ("has_data_position", C.c_int32), ("has_spike_guard", C.c_int32),
+                ("has_weight_decay_rule", C.c_int32), ("weight_decay_rule", C.c_int32), ("n_no_decay_patterns", C.c_uint32),
+                ("world_size", C.c_uint64), ("global_batch_rows", C.c_uint64), ("loss_scale", ScalerState),
+                ("data_position", DataPositionC), ("spike_guard", SpikeState), ("checkpoint_file", C.c_char * 512),
+                ("optimizer_file", C.c_char * 512)]
+
+
 RankBody = C.CFUNCTYPE(C.c_int32, C.c_int32, C.c_int32, C.c_void_p)
 
 # name -> (restype, argtypes): one row per declaration of include/oxz_dpstep.h
@@ -140,6 +149,11 @@ SIGNATURES = {
     "oxz_spike_judge": (C.c_int32, [C.POINTER(SpikeConfig), C.POINTER(SpikeState), C.c_uint64, C.c_double,
                                     C.POINTER(C.c_int32), C.POINTER(C.c_int32)]),
     "oxz_lr_at": (C.c_int32, [C.POINTER(LrPlanC), C.c_uint64, f64p]),
+    "oxz_meta_load": (C.c_int32, [C.c_char_p, C.POINTER(ResumeMeta)]),
+    "oxz_meta_no_decay_pattern": (C.c_int32, [C.c_char_p, C.c_uint32, C.c_char_p, C.c_uint64]),
+    "oxz_meta_save": (C.c_int32, [C.c_char_p, C.POINTER(ResumeMeta), C.POINTER(C.c_char_p)]),
+    "oxz_check_resume_world": (C.c_int32, [C.c_char_p, C.c_uint64, C.c_uint64, C.c_uint64, C.c_char_p, C.c_uint64]),
+    "oxz_read_loss_scale_state": (C.c_int32, [C.c_char_p, C.c_uint64, C.POINTER(C.c_int32), C.POINTER(ScalerState)]),
     "oxz_rows_check": (C.c_int32, [C.POINTER(RowLayoutC)]),
     "oxz_rows_advance": (C.c_int32, [C.POINTER(RowLayoutC), DataPositionC, C.c_uint64, C.POINTER(DataPositionC)]),
     "oxz_rows_next_window": (C.c_int32, [C.POINTER(RowLayoutC), DataPositionC, C.c_uint64, C.c_uint64, C.c_uint64,

@@ -9,7 +9,7 @@ import sys
 HERE = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(HERE, "csrc")
 LIB = os.path.join(HERE, "liboxz_dpstep.so")
-SOURCES = ["oxz_kernels.cu", "oxz_noalloc.cu", "oxz_loader.cu", "oxz_plan.cpp", "oxz_step.cpp", "oxz_comm.cpp", "oxz_host.cpp", "oxz_checkpoint.cpp", "oxz_launch.cpp"]
+SOURCES = ["oxz_kernels.cu", "oxz_noalloc.cu", "oxz_loader.cu", "oxz_plan.cpp", "oxz_step.cpp", "oxz_comm.cpp", "oxz_host.cpp", "oxz_checkpoint.cpp", "oxz_meta.cpp", "oxz_launch.cpp"]
 ARCH = ["-gencode", "arch=compute_100a,code=sm_100a"]
 
 

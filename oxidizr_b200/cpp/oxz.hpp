@@ -184,6 +184,41 @@ class RowLayout {
     oxz_row_layout l_{};
 };
 
+// ---- the checkpoint meta's data-parallel and loss-scale keys on resume (src/dp/resume.rs:19-55, src/loss_scale/resume.rs:14-29)
+struct CheckpointMeta {
+    oxz_resume_meta raw{};
+    std::vector<std::string> no_decay_patterns;
+    static CheckpointMeta load(const std::string& path) {
+        CheckpointMeta m;
+        check(oxz_meta_load(path.c_str(), &m.raw));
+        for (uint32_t i = 0; i < m.raw.n_no_decay_patterns; i++) {
+            char buf[4096];
+            check(oxz_meta_no_decay_pattern(path.c_str(), i, buf, sizeof buf));
+            m.no_decay_patterns.emplace_back(buf);
+        }
+        return m;
+    }
+    void save_to(const std::string& path) {
+        std::vector<const char*> p;
+        for (const auto& s : no_decay_patterns) p.push_back(s.c_str());
+        raw.n_no_decay_patterns = (uint32_t)p.size();
+        check(oxz_meta_save(path.c_str(), &raw, p.empty() ? nullptr : p.data()));
+    }
+};
+// Returns the warning (empty: none); throws when the meta records another world size.
+inline std::string check_resume_world(const char* meta_path, uint64_t start_step, uint64_t world, uint64_t global_batch_rows) {
+    char warning[1024];
+    check(oxz_check_resume_world(meta_path, start_step, world, global_batch_rows, warning, sizeof warning));
+    return warning;
+}
+inline bool read_loss_scale_state(const char* meta_path, uint64_t start_step, GradScalerState* out) {
+    int32_t has = 0;
+    oxz_scaler_state st{};
+    check(oxz_read_loss_scale_state(meta_path, start_step, &has, &st));
+    if (has) *out = GradScalerState{st.scale, st.consecutive_ok};
+    return has != 0;
+}
+
 // ---- communicator (src/dp/launch.rs:19-109)
 class Communicator {
   public:

@@ -1,0 +1,378 @@
+// The keys of a checkpoint meta (`checkpoint_step_N.meta.json`, CheckpointMeta of src/config.rs:1223-1302) that the
+// optimizer path writes and reads around a resume: world_size and global_batch_rows (src/dp/resume.rs:19-55),
+// loss_scale (src/loss_scale/resume.rs:14-29), weight_decay_rule and no_decay_patterns
+// (src/weight_decay/rule.rs:68-74), data_position, spike_guard and optimizer_file (src/checkpoint_set/snapshot.rs:245-262).
+// Host only. The file is JSON as serde_json writes it; keys this module does not know are skipped on load.
+#include <cerrno>
+#include <cmath>
+#include <cstdio>
+#include <cstring>
+#include <string>
+#include <vector>
+
+#include "oxz_internal.h"
+
+using namespace oxz;
+
+namespace {
+
+// ---- a small JSON reader over one document ----
+struct Reader {
+    const char* p;
+    const char* e;
+    bool ok = true;
+    void ws() { while (p < e && (*p == ' ' || *p == '\n' || *p == '\t' || *p == '\r')) p++; }
+    bool eat(char c) { ws(); if (p < e && *p == c) { p++; return true; } return false; }
+    bool peek(char c) { ws(); return p < e && *p == c; }
+    bool word(const char* w) {
+        ws();
+        const size_t n = strlen(w);
+        if ((size_t)(e - p) >= n && memcmp(p, w, n) == 0) { p += n; return true; }
+        return false;
+    }
+    static void utf8(std::string& out, uint32_t cp) {
+        if (cp < 0x80) out += (char)cp;
+        else if (cp < 0x800) { out += (char)(0xC0 | (cp >> 6)); out += (char)(0x80 | (cp & 0x3F)); }
+        else if (cp < 0x10000) { out += (char)(0xE0 | (cp >> 12)); out += (char)(0x80 | ((cp >> 6) & 0x3F)); out += (char)(0x80 | (cp & 0x3F)); }
+        else { out += (char)(0xF0 | (cp >> 18)); out += (char)(0x80 | ((cp >> 12) & 0x3F)); out += (char)(0x80 | ((cp >> 6) & 0x3F)); out += (char)(0x80 | (cp & 0x3F)); }
+    }
+    bool hex4(uint32_t* v) {
+        if (e - p < 4) return false;
+        uint32_t x = 0;
+        for (int i = 0; i < 4; i++) {
+            const char c = p[i];
+            x <<= 4;
+            if (c >= '0' && c <= '9') x |= (uint32_t)(c - '0');
+            else if (c >= 'a' && c <= 'f') x |= (uint32_t)(c - 'a' + 10);
+            else if (c >= 'A' && c <= 'F') x |= (uint32_t)(c - 'A' + 10);
+            else return false;
+        }
+        p += 4;
+        *v = x;
+        return true;
+    }
+    std::string str() {
+        std::string out;
+        ws();
+        if (p >= e || *p != '"') { ok = false; return out; }
+        p++;
+        while (p < e && *p != '"') {
+            if (*p != '\\') { out += *p++; continue; }
+            if (++p >= e) break;
+            const char c = *p++;
+            switch (c) {
+                case 'n': out += '\n'; break;
+                case 't': out += '\t'; break;
+                case 'r': out += '\r'; break;
+                case 'b': out += '\b'; break;
+                case 'f': out += '\f'; break;
+                case 'u': {
+                    uint32_t cp = 0, lo = 0;
+                    if (!hex4(&cp)) { ok = false; return out; }
+                    if (cp >= 0xD800 && cp < 0xDC00 && e - p >= 6 && p[0] == '\\' && p[1] == 'u') {
+                        p += 2;
+                        if (!hex4(&lo)) { ok = false; return out; }
+                        cp = 0x10000 + ((cp - 0xD800) << 10) + (lo - 0xDC00);
+                    }
+                    utf8(out, cp);
+                    break;
+                }
+                default: out += c;  // \" \\ \/
+            }
+        }
+        if (p >= e) { ok = false; return out; }
+        p++;
+        return out;
+    }
+    // a JSON number as text; serde_json prints f64 so that it reads back to the same bits
+    std::string number() {
+        ws();
+        const char* s = p;
+        while (p < e && (strchr("+-.eE", *p) || (*p >= '0' && *p <= '9'))) p++;
+        if (p == s) ok = false;
+        return std::string(s, p);
+    }
+    bool u64(uint64_t* v) {
+        const std::string t = number();
+        if (!ok || t.empty() || t.find_first_not_of("0123456789") != std::string::npos || t.size() > 20) { ok = false; return false; }
+        errno = 0;
+        *v = strtoull(t.c_str(), nullptr, 10);
+        if (errno) ok = false;
+        return ok;
+    }
+    bool f64(double* v) {
+        const std::string t = number();
+        if (!ok) return false;
+        char* end = nullptr;
+        *v = strtod(t.c_str(), &end);
+        if (!end || *end) ok = false;
+        return ok;
+    }
+    void skip() {
+        ws();
+        if (p >= e) { ok = false; return; }
+        if (*p == '"') { str(); return; }
+        if (*p == '{' || *p == '[') {
+            const char open = *p, close = open == '{' ? '}' : ']';
+            p++;
+            if (eat(close)) return;
+            do {
+                if (open == '{') { str(); if (!ok || !eat(':')) { ok = false; return; } }
+                skip();
+                if (!ok) return;
+            } while (eat(','));
+            if (!eat(close)) ok = false;
+            return;
+        }
+        if (word("null") || word("true") || word("false")) return;
+        number();
+    }
+    // calls fn(key) for every member of the object at the cursor; fn must consume the value
+    template <class F>
+    bool object(F fn) {
+        if (!eat('{')) { ok = false; return false; }
+        if (eat('}')) return true;
+        do {
+            const std::string key = str();
+            if (!ok || !eat(':')) { ok = false; return false; }
+            fn(key);
+            if (!ok) return false;
+        } while (eat(','));
+        if (!eat('}')) ok = false;
+        return ok;
+    }
+};
+
+struct Parsed {
+    oxz_resume_meta m{};
+    std::vector<std::string> patterns;
+};
+
+int32_t rule_of(const std::string& s) {
+    if (s == "decay_all") return OXZ_DECAY_ALL;
+    if (s == "skip_1d") return OXZ_SKIP_1D;
+    if (s == "skip_all") return OXZ_SKIP_ALL;
+    return -1;
+}
+const char* rule_name(int32_t r) { return r == OXZ_DECAY_ALL ? "decay_all" : r == OXZ_SKIP_1D ? "skip_1d" : "skip_all"; }
+
+// Reads the file; on failure `why` says what went wrong (the caller words the error the way its reference does).
+bool parse_file(const char* path, Parsed* out, std::string* why) {
+    FILE* f = fopen(path, "rb");
+    if (!f) { *why = strerror(errno); return false; }
+    std::string text;
+    char buf[4096];
+    size_t n;
+    while ((n = fread(buf, 1, sizeof buf, f)) > 0) text.append(buf, n);
+    fclose(f);
+    Reader r{text.data(), text.data() + text.size()};
+    oxz_resume_meta& m = out->m;
+    m = oxz_resume_meta{};
+    m.weight_decay_rule = OXZ_DECAY_ALL;  // WeightDecayRule::LEGACY for a meta without the key
+    bool has_step = false;
+    auto copy = [&](char* dst, size_t cap, const std::string& s) {
+        if (s.size() >= cap) { r.ok = false; *why = "a file name in the meta is longer than " + std::to_string(cap - 1) + " bytes"; return; }
+        memcpy(dst, s.c_str(), s.size() + 1);
+    };
+    r.object([&](const std::string& key) {
+        if (r.word("null")) return;  // Option::None written explicitly
+        if (key == "step") { has_step = r.u64(&m.step); }
+        else if (key == "world_size") { m.has_world_size = r.u64(&m.world_size) ? 1 : 0; }
+        else if (key == "global_batch_rows") { m.has_global_batch_rows = r.u64(&m.global_batch_rows) ? 1 : 0; }
+        else if (key == "weight_decay_rule") {
+            const int32_t rule = rule_of(r.str());
+            if (rule < 0) { r.ok = false; *why = "unknown weight_decay_rule"; }
+            else { m.weight_decay_rule = rule; m.has_weight_decay_rule = 1; }
+        } else if (key == "no_decay_patterns") {
+            if (!r.eat('[')) { r.ok = false; return; }
+            if (!r.eat(']')) {
+                do { out->patterns.push_back(r.str()); } while (r.ok && r.eat(','));
+                if (!r.eat(']')) r.ok = false;
+            }
+        } else if (key == "loss_scale") {
+            bool a = false, b = false;
+            r.object([&](const std::string& k) {
+                if (k == "scale") a = r.f64(&m.loss_scale.scale);
+                else if (k == "consecutive_ok") b = r.u64(&m.loss_scale.consecutive_ok);
+                else r.skip();
+            });
+            if (r.ok && !(a && b)) { r.ok = false; *why = "loss_scale needs `scale` and `consecutive_ok`"; }
+            m.has_loss_scale = 1;
+        } else if (key == "data_position") {
+            bool a = false, b = false;
+            r.object([&](const std::string& k) {
+                if (k == "epoch") a = r.u64(&m.data_position.epoch);
+                else if (k == "row") b = r.u64(&m.data_position.row);
+                else r.skip();
+            });
+            if (r.ok && !(a && b)) { r.ok = false; *why = "data_position needs `epoch` and `row`"; }
+            m.has_data_position = 1;
+        } else if (key == "spike_guard") {
+            r.object([&](const std::string& k) {
+                if (k == "mean") r.f64(&m.spike_guard.mean);
+                else if (k == "variance") r.f64(&m.spike_guard.variance);
+                else if (k == "observed") r.u64(&m.spike_guard.observed);
+                else if (k == "detected") r.u64(&m.spike_guard.detected);
+                else if (k == "skipped") r.u64(&m.spike_guard.skipped);
+                else r.skip();
+            });
+            m.has_spike_guard = 1;
+        } else if (key == "optimizer_file") { copy(m.optimizer_file, sizeof m.optimizer_file, r.str()); }
+        else if (key == "checkpoint_file") { copy(m.checkpoint_file, sizeof m.checkpoint_file, r.str()); }
+        else r.skip();
+    });
+    r.ws();
+    if (r.ok && r.p != r.e) r.ok = false;
+    if (r.ok && !has_step) { r.ok = false; *why = "missing field `step`"; }
+    if (!r.ok) {
+        if (why->empty()) *why = "the file is not valid JSON near byte " + std::to_string((size_t)(r.p - text.data()));
+        return false;
+    }
+    m.n_no_decay_patterns = (uint32_t)out->patterns.size();
+    return true;
+}
+
+std::string esc(const std::string& s) {
+    std::string out;
+    for (unsigned char c : s) {
+        if (c == '"' || c == '\\') { out += '\\'; out += (char)c; }
+        else if (c == '\n') out += "\\n";
+        else if (c == '\t') out += "\\t";
+        else if (c == '\r') out += "\\r";
+        else if (c < 0x20) { char b[8]; snprintf(b, sizeof b, "\\u%04x", c); out += b; }
+        else out += (char)c;
+    }
+    return out;
+}
+
+// The shortest decimal text that reads back to the same f64 bits.
+std::string f64_text(double v) {
+    char b[40];
+    for (int prec = 1; prec <= 17; prec++) {
+        snprintf(b, sizeof b, "%.*g", prec, v);
+        if (strtod(b, nullptr) == v) break;
+    }
+    std::string s = b;
+    if (s.find_first_of(".eEn") == std::string::npos) s += ".0";  // serde_json keeps a float a float
+    return s;
+}
+
+}  // namespace
+
+extern "C" {
+
+int32_t oxz_meta_load(const char* path, oxz_resume_meta* out) {
+    if (!path || !out) return fail(OXZ_ERR_INVALID, "oxz_meta_load: null argument");
+    Parsed p;
+    std::string why;
+    if (!parse_file(path, &p, &why))
+        return fail(OXZ_ERR_INVALID, "checkpoint meta '%s' was not read: %s. Restore the file to resume from it.", path, why.c_str());
+    *out = p.m;
+    return OXZ_OK;
+}
+
+int32_t oxz_meta_no_decay_pattern(const char* path, uint32_t index, char* buf, uint64_t cap) {
+    if (!path || !buf || cap == 0) return fail(OXZ_ERR_INVALID, "oxz_meta_no_decay_pattern: null argument");
+    Parsed p;
+    std::string why;
+    if (!parse_file(path, &p, &why))
+        return fail(OXZ_ERR_INVALID, "checkpoint meta '%s' was not read: %s. Restore the file to resume from it.", path, why.c_str());
+    if (index >= p.patterns.size())
+        return fail(OXZ_ERR_INVALID, "oxz_meta_no_decay_pattern: pattern %u of %zu", index, p.patterns.size());
+    if (p.patterns[index].size() >= cap)
+        return fail(OXZ_ERR_INVALID, "oxz_meta_no_decay_pattern: the pattern needs %zu bytes, the buffer has %llu",
+                    p.patterns[index].size() + 1, (unsigned long long)cap);
+    memcpy(buf, p.patterns[index].c_str(), p.patterns[index].size() + 1);
+    return OXZ_OK;
+}
+
+int32_t oxz_meta_save(const char* path, const oxz_resume_meta* m, const char* const* no_decay_patterns) {
+    if (!path || !m || (m->n_no_decay_patterns && !no_decay_patterns)) return fail(OXZ_ERR_INVALID, "oxz_meta_save: null argument");
+    if (m->has_weight_decay_rule && (m->weight_decay_rule < OXZ_DECAY_ALL || m->weight_decay_rule > OXZ_SKIP_ALL))
+        return fail(OXZ_ERR_INVALID, "oxz_meta_save: unknown weight decay rule %d", m->weight_decay_rule);
+    if (m->has_loss_scale && !(std::isfinite(m->loss_scale.scale) && m->loss_scale.scale > 0.0))
+        return fail(OXZ_ERR_INVALID, "oxz_meta_save: loss scale %g must be finite and positive", m->loss_scale.scale);
+    // Field order and Option handling follow CheckpointMeta's serde derive: required keys first, None left out.
+    // The keys outside the optimizer path (timestamp, hashes, data sources) are written empty.
+    std::string j = "{\n";
+    j += "  \"step\": " + std::to_string(m->step) + ",\n";
+    j += "  \"timestamp\": \"\",\n  \"model_config_hash\": \"\",\n  \"data_file_path\": \"\",\n  \"data_file_hash\": \"\",\n";
+    j += "  \"checkpoint_file\": \"" + esc(m->checkpoint_file) + "\"";
+    if (m->has_data_position)
+        j += ",\n  \"data_position\": {\n    \"epoch\": " + std::to_string(m->data_position.epoch) + ",\n    \"row\": " +
+             std::to_string(m->data_position.row) + "\n  }";
+    if (m->optimizer_file[0]) j += ",\n  \"optimizer_file\": \"" + esc(m->optimizer_file) + "\"";
+    if (m->has_weight_decay_rule) j += std::string(",\n  \"weight_decay_rule\": \"") + rule_name(m->weight_decay_rule) + "\"";
+    if (m->n_no_decay_patterns) {
+        j += ",\n  \"no_decay_patterns\": [";
+        for (uint32_t i = 0; i < m->n_no_decay_patterns; i++) {
+            if (!no_decay_patterns[i]) return fail(OXZ_ERR_INVALID, "oxz_meta_save: pattern %u is null", i);
+            j += std::string(i ? "," : "") + "\n    \"" + esc(no_decay_patterns[i]) + "\"";
+        }
+        j += "\n  ]";
+    }
+    if (m->has_loss_scale)
+        j += ",\n  \"loss_scale\": {\n    \"scale\": " + f64_text(m->loss_scale.scale) + ",\n    \"consecutive_ok\": " +
+             std::to_string(m->loss_scale.consecutive_ok) + "\n  }";
+    if (m->has_world_size) j += ",\n  \"world_size\": " + std::to_string(m->world_size);
+    if (m->has_global_batch_rows) j += ",\n  \"global_batch_rows\": " + std::to_string(m->global_batch_rows);
+    if (m->has_spike_guard)
+        j += ",\n  \"spike_guard\": {\n    \"mean\": " + f64_text(m->spike_guard.mean) + ",\n    \"variance\": " +
+             f64_text(m->spike_guard.variance) + ",\n    \"observed\": " + std::to_string(m->spike_guard.observed) +
+             ",\n    \"detected\": " + std::to_string(m->spike_guard.detected) + ",\n    \"skipped\": " +
+             std::to_string(m->spike_guard.skipped) + "\n  }";
+    j += "\n}";
+    // atomic like CheckpointMeta::save_to (src/config.rs:1386-1394): write beside, then rename
+    const std::string tmp = std::string(path) + ".tmp";
+    FILE* f = fopen(tmp.c_str(), "wb");
+    const char* next = "Check that the directory is writable.";
+    if (!f) return fail(OXZ_ERR_INVALID, "failed to write checkpoint meta '%s': %s. %s", path, strerror(errno), next);
+    const bool wrote = fwrite(j.data(), 1, j.size(), f) == j.size();
+    if (fclose(f) != 0 || !wrote || rename(tmp.c_str(), path) != 0) {
+        const int32_t st = fail(OXZ_ERR_INVALID, "failed to write checkpoint meta '%s': %s. %s", path, strerror(errno), next);
+        remove(tmp.c_str());
+        return st;
+    }
+    return OXZ_OK;
+}
+
+int32_t oxz_check_resume_world(const char* meta_path, uint64_t start_step, uint64_t world, uint64_t global_batch_rows,
+                               char* warning, uint64_t cap) {
+    if (warning && cap) warning[0] = '\0';
+    if (!meta_path || start_step == 0) return OXZ_OK;  // a fresh run and a resume without a meta check nothing
+    Parsed p;
+    std::string why;
+    if (!parse_file(meta_path, &p, &why))
+        return fail(OXZ_ERR_INVALID, "checkpoint meta '%s' was not read: %s. Restore the file to resume with its world size.",
+                    meta_path, why.c_str());
+    const uint64_t saved = p.m.has_world_size ? p.m.world_size : 1;  // an old meta reads as one rank
+    if (saved != world)
+        return fail(OXZ_ERR_INVALID,
+                    "checkpoint meta '%s' records world size %llu, and this run has world size %llu. Resume with %llu "
+                    "GPU id(s) in `--gpus`, or start a fresh run.",
+                    meta_path, (unsigned long long)saved, (unsigned long long)world, (unsigned long long)saved);
+    if (p.m.has_global_batch_rows && p.m.global_batch_rows != global_batch_rows && warning && cap)
+        snprintf(warning, cap,
+                 "Warning: checkpoint meta '%s' records global batches of %llu rows, and this run's global batch is %llu "
+                 "rows. The data stream resumes at the saved row, but the resume does not match an uninterrupted run.",
+                 meta_path, (unsigned long long)p.m.global_batch_rows, (unsigned long long)global_batch_rows);
+    return OXZ_OK;
+}
+
+int32_t oxz_read_loss_scale_state(const char* meta_path, uint64_t start_step, int32_t* has_state, oxz_scaler_state* state) {
+    if (!has_state || !state) return fail(OXZ_ERR_INVALID, "oxz_read_loss_scale_state: null argument");
+    *has_state = 0;
+    if (!meta_path || start_step == 0) return OXZ_OK;
+    Parsed p;
+    std::string why;
+    if (!parse_file(meta_path, &p, &why))
+        return fail(OXZ_ERR_INVALID, "checkpoint meta '%s' was not read: %s. Restore the file to resume with its loss scale.",
+                    meta_path, why.c_str());
+    if (p.m.has_loss_scale) {
+        *has_state = 1;
+        *state = p.m.loss_scale;
+    }
+    return OXZ_OK;
+}
+
+}  // extern "C"

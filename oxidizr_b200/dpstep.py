@@ -389,6 +389,96 @@ class LitDataLoader:
             self._h = C.c_void_p()
 
 
+# ------------------------------------------------------------------ the checkpoint meta's keys on this path
+@dataclass
+class SpikeGuardState:
+    """src/metrics/spike.rs:14-26."""
+    mean: float = 0.0
+    variance: float = 0.0
+    observed: int = 0
+    detected: int = 0
+    skipped: int = 0
+
+
+@dataclass
+class CheckpointMeta:
+    """The keys of ``checkpoint_step_N.meta.json`` (CheckpointMeta, src/config.rs:1223-1302) that the optimizer path
+    records and reads on resume (src/checkpoint_set/snapshot.rs:245-262). ``None`` is a key the file does not hold."""
+    step: int
+    checkpoint_file: str = ""
+    optimizer_file: str | None = None
+    data_position: DataPosition | None = None
+    weight_decay_rule: str | None = None
+    no_decay_patterns: list[str] = field(default_factory=list)
+    loss_scale: GradScalerState | None = None
+    world_size: int | None = None
+    global_batch_rows: int | None = None
+    spike_guard: SpikeGuardState | None = None
+
+    def weight_decay_spec(self) -> WeightDecaySpec:
+        """WeightDecaySpec::of_meta (src/weight_decay/rule.rs:68-74): a meta without the rule is a legacy run."""
+        return WeightDecaySpec(self.weight_decay_rule or "decay_all", list(self.no_decay_patterns))
+
+    def save_to(self, path: str) -> None:
+        m = ffi.ResumeMeta()
+        m.step = self.step
+        m.checkpoint_file = self.checkpoint_file.encode()
+        m.optimizer_file = (self.optimizer_file or "").encode()
+        if self.data_position is not None:
+            m.has_data_position, m.data_position = 1, ffi.DataPositionC(self.data_position.epoch, self.data_position.row)
+        if self.weight_decay_rule is not None:
+            m.has_weight_decay_rule, m.weight_decay_rule = 1, _RULES[self.weight_decay_rule]
+        if self.loss_scale is not None:
+            m.has_loss_scale, m.loss_scale = 1, ffi.ScalerState(self.loss_scale.scale, self.loss_scale.consecutive_ok)
+        if self.world_size is not None:
+            m.has_world_size, m.world_size = 1, self.world_size
+        if self.global_batch_rows is not None:
+            m.has_global_batch_rows, m.global_batch_rows = 1, self.global_batch_rows
+        if self.spike_guard is not None:
+            g = self.spike_guard
+            m.has_spike_guard, m.spike_guard = 1, ffi.SpikeState(g.mean, g.variance, g.observed, g.detected, g.skipped)
+        n = len(self.no_decay_patterns)
+        m.n_no_decay_patterns = n
+        arr = (C.c_char_p * max(n, 1))(*[p.encode() for p in self.no_decay_patterns])
+        check(lib().oxz_meta_save(path.encode(), C.byref(m), arr))
+
+    @classmethod
+    def load(cls, path: str) -> "CheckpointMeta":
+        m = ffi.ResumeMeta()
+        check(lib().oxz_meta_load(path.encode(), C.byref(m)))
+        patterns = []
+        for i in range(m.n_no_decay_patterns):
+            buf = C.create_string_buffer(4096)
+            check(lib().oxz_meta_no_decay_pattern(path.encode(), i, buf, len(buf)))
+            patterns.append(buf.value.decode())
+        rules = {v: k for k, v in _RULES.items()}
+        g = m.spike_guard
+        return cls(
+            step=m.step, checkpoint_file=m.checkpoint_file.decode(), optimizer_file=m.optimizer_file.decode() or None,
+            data_position=DataPosition(m.data_position.epoch, m.data_position.row) if m.has_data_position else None,
+            weight_decay_rule=rules[m.weight_decay_rule] if m.has_weight_decay_rule else None, no_decay_patterns=patterns,
+            loss_scale=GradScalerState(m.loss_scale.scale, m.loss_scale.consecutive_ok) if m.has_loss_scale else None,
+            world_size=m.world_size if m.has_world_size else None,
+            global_batch_rows=m.global_batch_rows if m.has_global_batch_rows else None,
+            spike_guard=SpikeGuardState(g.mean, g.variance, g.observed, g.detected, g.skipped) if m.has_spike_guard else None)
+
+
+def check_resume_world(meta_path: str | None, start_step: int, world: int, global_batch_rows: int) -> str | None:
+    """src/dp/resume.rs:19-55: raises when the meta records another world size; returns a warning for another global
+    batch, else None."""
+    buf = C.create_string_buffer(1024)
+    check(lib().oxz_check_resume_world(meta_path.encode() if meta_path else None, start_step, world, global_batch_rows,
+                                       buf, len(buf)))
+    return buf.value.decode() or None
+
+
+def read_loss_scale_state(meta_path: str | None, start_step: int) -> GradScalerState | None:
+    """src/loss_scale/resume.rs:14-29."""
+    has, st = C.c_int32(), ffi.ScalerState()
+    check(lib().oxz_read_loss_scale_state(meta_path.encode() if meta_path else None, start_step, C.byref(has), C.byref(st)))
+    return GradScalerState(st.scale, st.consecutive_ok) if has.value else None
+
+
 def step_weighting(local_micro_batches: int, world: int, scored: int, masked_ranks: int):
     """StepWeighting::over_ranks on the summed counts (src/dp/weighting.rs:46-61): (micro_batches, scored or None)."""
     mb, gs = C.c_uint64(), C.c_int64()

@@ -5,6 +5,9 @@
 #include <cstring>
 #include <thread>
 
+#include <sys/stat.h>
+#include <unistd.h>
+
 #include "../../oxidizr_b200/cpp/oxz.hpp"
 
 using namespace oxidizr;
@@ -113,6 +116,35 @@ static void advance_matches_one_batch_at_a_time() {
     EXPECT(throws([] { RowLayout::create(3, 4); }, "fewer than batch_size 4"));
 }
 
+// src/dp/resume.rs:76-125
+static void the_meta_world_size_gates_a_resume() {
+    const std::string dir = std::string("/tmp/oxz-mirror-meta-") + std::to_string((long)getpid());
+    mkdir(dir.c_str(), 0700);
+    auto meta_file = [&](const char* tag, int world, int rows) {
+        CheckpointMeta m;
+        m.raw.step = 3;
+        snprintf(m.raw.checkpoint_file, sizeof m.raw.checkpoint_file, "w.safetensors");
+        if (world) { m.raw.has_world_size = 1; m.raw.world_size = (uint64_t)world; }
+        if (rows) { m.raw.has_global_batch_rows = 1; m.raw.global_batch_rows = (uint64_t)rows; }
+        const std::string path = dir + "/" + tag + ".meta.json";
+        m.save_to(path);
+        return path;
+    };
+    const std::string match = meta_file("match", 2, 8), old = meta_file("old", 0, 0), batch = meta_file("batch", 1, 4);
+    EXPECT(check_resume_world(match.c_str(), 3, 2, 8).empty());
+    EXPECT(throws([&] { check_resume_world(match.c_str(), 3, 1, 4); }, "world size 2"));
+    EXPECT(throws([&] { check_resume_world(match.c_str(), 3, 1, 4); }, "--gpus"));
+    EXPECT(check_resume_world(old.c_str(), 3, 1, 4).empty());
+    EXPECT(throws([&] { check_resume_world(old.c_str(), 3, 2, 8); }, "world size 1"));
+    const std::string warning = check_resume_world(batch.c_str(), 3, 1, 6);
+    EXPECT(warning.find("4 rows") != std::string::npos && warning.find("6 rows") != std::string::npos);
+    EXPECT(check_resume_world(match.c_str(), 0, 1, 4).empty() && check_resume_world(nullptr, 5, 3, 12).empty());
+    GradScalerState st{};
+    EXPECT(!read_loss_scale_state(match.c_str(), 3, &st));
+    for (const std::string& p : {match, old, batch}) remove(p.c_str());
+    rmdir(dir.c_str());
+}
+
 // src/dp/reduce.rs:88-121, src/dp/launch.rs:296-366
 static void ranks_sum_and_the_first_error_wins() {
     auto comms = Communicator::local_group(2, nullptr, 10.0);
@@ -171,6 +203,7 @@ int main(int argc, char** argv) {
     lr_plan_matches_the_closed_form();
     advance_matches_one_batch_at_a_time();
     ranks_sum_and_the_first_error_wins();
+    the_meta_world_size_gates_a_resume();
     if (argc > 1 && strcmp(argv[1], "--gpu") == 0) the_step_on_the_gpu();
     printf(failures ? "%d FAILED\n" : "all passed (%d failures)\n", failures);
     return failures ? 1 : 0;
