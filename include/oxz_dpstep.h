@@ -377,6 +377,27 @@ typedef struct oxz_loader oxz_loader;
 int32_t oxz_loader_open(const char* path, uint64_t seq_len, uint64_t rank_batch_size, uint64_t rank, uint64_t world,
                         uint64_t first_row, uint64_t end_row, int32_t device, oxz_loader** out);
 int32_t oxz_loader_close(oxz_loader* loader);
+/* LitDataLoader::with_target_mask(TargetMask::PrefixLm{target_base, always_score}) (src/data/mask.rs:21-47): a position
+ * scores iff its TARGET id is at least target_base or is listed in always_score. on = 0 turns the mask off.
+ * TargetMask::SpeechAudio depends on boostr's SpeechLayout and is not offered. */
+#define OXZ_MAX_ALWAYS_SCORE 16u
+int32_t oxz_loader_set_target_mask(oxz_loader* loader, int32_t on, uint32_t target_base, const uint32_t* always_score,
+                                   uint32_t n_always);
+/* LitDataLoader::with_document_mask (src/data/host_masks.rs:28-35): every position whose INPUT is the separator is
+ * unscored (ANDed with the target mask), and each batch carries its document segments (src/data/segments.rs:62-101). */
+int32_t oxz_loader_set_document_mask(oxz_loader* loader, int32_t on, uint32_t separator_id);
+/* The masks of the batch oxz_loader_next_batch_async enqueued last (Batch::loss_mask / scored / segments,
+ * src/data/batch.rs:11-26), built on the device in the same stream. Device pointers are null for what is off.
+ * scored and n_segments point into pinned host memory that the stream fills: read them once the stream has passed
+ * the batch (an unmasked batch scores rows * seq_len, written at once). Valid until the batch after the next. */
+typedef struct oxz_batch_masks {
+    const float* loss_mask;      /* device [rows, seq_len] f32: 1.0 scored, 0.0 not */
+    const int32_t* segment_ids;  /* device [rows, seq_len] i32: segment of each input token, counted over the batch */
+    const int32_t* cu_seqlens;   /* device: *n_segments + 1 cumulative offsets over the flattened inputs, from 0 */
+    const uint64_t* scored;      /* pinned host */
+    const uint64_t* n_segments;  /* pinned host; 0 when the document mask is off */
+} oxz_batch_masks;
+int32_t oxz_loader_batch_masks(const oxz_loader* loader, oxz_batch_masks* out);
 int32_t oxz_loader_num_rows(const oxz_loader* loader, uint64_t* rows);
 /* LitDataLoader::position / seek (src/data/positioning.rs:14-42): the position is global, every rank seeks the same one. */
 int32_t oxz_loader_position(const oxz_loader* loader, oxz_data_position* pos);

@@ -317,6 +317,53 @@ def rank_window(layout: RowLayout, pos: DataPosition, rank: int, seq_len: int, f
     return rows, inputs, targets, DataPosition(start.epoch, start.row + layout.batch_size())
 
 
+# ---------------------------------------------------------------- loss mask and document segments of one window
+def build_target_mask(window, batch_size: int, seq_len: int, target_base: int, always_score=()):
+    """TargetMask::PrefixLm over a raw [batch_size, seq_len + 1] window (src/data/mask.rs:36-47, 72-88): position
+    (b, s) scores iff its TARGET window[b*(S+1) + s + 1] is at least target_base or is listed in always_score."""
+    out = []
+    for b in range(batch_size):
+        row = b * (seq_len + 1)
+        for s in range(seq_len):
+            t = window[row + s + 1]
+            out.append(1.0 if (t >= target_base or t in always_score) else 0.0)
+    return out
+
+
+def host_segments(window, batch_size: int, seq_len: int, separator: int):
+    """HostSegments::build (src/data/segments.rs:62-101): (offsets, ids) over the flattened inputs. A separator ends
+    its segment and belongs to it; every row start begins a segment; a row ending on a separator adds no empty one."""
+    if batch_size * seq_len > 2**31 - 1:
+        raise ValueError(f"a batch of {batch_size} x {seq_len} tokens overflows the i32 segment offsets. "
+                         "Lower trainer.batch_size or model.max_seq_len.")
+    offsets, ids = [0], []
+    for b in range(batch_size):
+        row = window[b * (seq_len + 1): b * (seq_len + 1) + seq_len]
+        for s, token in enumerate(row):
+            ids.append(len(offsets) - 1)
+            if token == separator:
+                offsets.append(b * seq_len + s + 1)
+        if offsets[-1] != (b + 1) * seq_len:
+            offsets.append((b + 1) * seq_len)
+    return offsets, ids
+
+
+def host_masks(window, batch_size: int, seq_len: int, target_mask=None, separator=None):
+    """LitDataLoader::host_masks (src/data/host_masks.rs:49-77). target_mask = (target_base, always_score) or None;
+    separator = the document mask's separator id or None. Returns (loss_mask or None, scored, (offsets, ids) or None):
+    the target mask scores by target id, the document mask clears every position whose INPUT is the separator."""
+    target = build_target_mask(window, batch_size, seq_len, *target_mask) if target_mask is not None else None
+    if separator is None:
+        scored = batch_size * seq_len if target is None else sum(1 for m in target if m != 0.0)
+        return target, scored, None
+    mask = target if target is not None else [1.0] * (batch_size * seq_len)
+    for b in range(batch_size):
+        for s in range(seq_len):
+            if window[b * (seq_len + 1) + s] == separator:
+                mask[b * seq_len + s] = 0.0
+    return mask, sum(1 for m in mask if m != 0.0), host_segments(window, batch_size, seq_len, separator)
+
+
 # ---------------------------------------------------------------- step weighting
 def reduce_step_weighting(local: list[tuple[int, int | None]]):
     """src/dp/weighting.rs:32-61 over src/step_loss.rs:79-112.

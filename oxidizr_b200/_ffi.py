@@ -91,6 +91,11 @@ class ResumeMeta(C.Structure):
                 ("optimizer_file", C.c_char * 512)]
 
 
+class BatchMasks(C.Structure):
+    _fields_ = [("loss_mask", C.c_void_p), ("segment_ids", C.c_void_p), ("cu_seqlens", C.c_void_p),
+                ("scored", C.POINTER(C.c_uint64)), ("n_segments", C.POINTER(C.c_uint64))]
+
+
 RankBody = C.CFUNCTYPE(C.c_int32, C.c_int32, C.c_int32, C.c_void_p)
 
 # name -> (restype, argtypes): one row per declaration of include/oxz_dpstep.h
@@ -149,6 +154,9 @@ SIGNATURES = {
     "oxz_spike_judge": (C.c_int32, [C.POINTER(SpikeConfig), C.POINTER(SpikeState), C.c_uint64, C.c_double,
                                     C.POINTER(C.c_int32), C.POINTER(C.c_int32)]),
     "oxz_lr_at": (C.c_int32, [C.POINTER(LrPlanC), C.c_uint64, f64p]),
+    "oxz_loader_set_target_mask": (C.c_int32, [vp, C.c_int32, C.c_uint32, C.POINTER(C.c_uint32), C.c_uint32]),
+    "oxz_loader_set_document_mask": (C.c_int32, [vp, C.c_int32, C.c_uint32]),
+    "oxz_loader_batch_masks": (C.c_int32, [vp, C.POINTER(BatchMasks)]),
     "oxz_meta_load": (C.c_int32, [C.c_char_p, C.POINTER(ResumeMeta)]),
     "oxz_meta_no_decay_pattern": (C.c_int32, [C.c_char_p, C.c_uint32, C.c_char_p, C.c_uint64]),
     "oxz_meta_save": (C.c_int32, [C.c_char_p, C.POINTER(ResumeMeta), C.POINTER(C.c_char_p)]),

@@ -4,6 +4,10 @@
 // are consecutive in the file, so one step is one pinned staging copy, one host-to-device copy and one kernel that
 // widens the ids to i64 and writes inputs [B,S] and targets [B,S] (src/data/batch.rs:51-71).
 // The shuffled order depends on rand 0.10.3's StdRng and is not offered.
+// With a target mask (TargetMask::PrefixLm, src/data/mask.rs:36-47) or the document mask (src/data/host_masks.rs:49-77,
+// src/data/segments.rs:62-101) on, the same stream also yields the [B,S] f32 loss mask, the count of scored positions,
+// the [B,S] i32 segment ids and the cumulative segment offsets, built on the device from the staged window.
+// TargetMask::SpeechAudio needs boostr's SpeechLayout, which is not vendored, and is not offered.
 #include <fcntl.h>
 #include <sys/mman.h>
 #include <sys/stat.h>
@@ -30,6 +34,17 @@ struct oxz_loader {
     int64_t* d_targets[2] = {nullptr, nullptr};
     cudaEvent_t staged[2] = {nullptr, nullptr};
     int slot = 0;
+    // masks
+    bool target_mask = false, document_mask = false;
+    uint32_t target_base = 0, n_always = 0, separator = 0;
+    uint32_t always[OXZ_MAX_ALWAYS_SCORE] = {};
+    float* d_loss_mask[2] = {nullptr, nullptr};
+    int32_t* d_seg_ids[2] = {nullptr, nullptr};
+    int32_t* d_cu[2] = {nullptr, nullptr};        // B*S + 1 offsets at most
+    uint32_t* d_row_base[2] = {nullptr, nullptr};  // B + 1
+    unsigned long long* d_counts[2] = {nullptr, nullptr};  // {scored, segments}
+    unsigned long long* h_counts[2] = {nullptr, nullptr};  // pinned
+    int last = -1;  // slot of the batch handed out last
 };
 
 namespace {
@@ -47,6 +62,131 @@ __global__ void __launch_bounds__(256) k_split_rows(const uint32_t* __restrict__
     }
 }
 
+struct MaskRule {
+    uint32_t target_base, n_always, separator;
+    int32_t has_target, has_document;
+    uint32_t always[OXZ_MAX_ALWAYS_SCORE];
+};
+
+// k_split_rows plus the loss mask: a position scores iff its TARGET id passes the rule and its INPUT is not the
+// document separator. The scored positions are counted with integer atomics (one per block), so the count is exact.
+__global__ void __launch_bounds__(256) k_split_rows_masked(const uint32_t* __restrict__ window, uint64_t rows, uint64_t seq_len,
+                                                           MaskRule rule, int64_t* __restrict__ inputs,
+                                                           int64_t* __restrict__ targets, float* __restrict__ loss_mask,
+                                                           unsigned long long* __restrict__ counts) {
+    const uint64_t n = rows * seq_len;
+    const uint64_t stride = static_cast<uint64_t>(gridDim.x) * blockDim.x;
+    uint32_t mine = 0;
+    for (uint64_t i = static_cast<uint64_t>(blockIdx.x) * blockDim.x + threadIdx.x; i < n; i += stride) {
+        const uint64_t r = i / seq_len, s = i - r * seq_len;
+        const uint32_t* row = window + r * (seq_len + 1);
+        const uint32_t in = row[s], tg = row[s + 1];
+        inputs[i] = static_cast<int64_t>(in);
+        targets[i] = static_cast<int64_t>(tg);
+        bool scored = true;
+        if (rule.has_target) {
+            scored = tg >= rule.target_base;
+            for (uint32_t k = 0; k < rule.n_always; k++) scored |= tg == rule.always[k];
+        }
+        if (rule.has_document && in == rule.separator) scored = false;
+        loss_mask[i] = scored ? 1.0f : 0.0f;
+        mine += scored ? 1u : 0u;
+    }
+    __shared__ uint32_t sh[8];
+    for (int o = 16; o > 0; o >>= 1) mine += __shfl_down_sync(0xffffffffu, mine, o);
+    if ((threadIdx.x & 31) == 0) sh[threadIdx.x >> 5] = mine;
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        uint32_t t = 0;
+        for (int w = 0; w < 8; w++) t += sh[w];
+        if (t) atomicAdd(&counts[0], static_cast<unsigned long long>(t));
+    }
+}
+
+// Segments, step 1: one warp per row counts the segments the row closes: one per separator among its inputs, and
+// one more for the row end unless the last input is itself a separator (src/data/segments.rs:84-99).
+__global__ void __launch_bounds__(256) k_row_closings(const uint32_t* __restrict__ window, uint32_t rows, uint32_t seq_len,
+                                                      uint32_t separator, uint32_t* __restrict__ row_base) {
+    const uint32_t warp = (blockIdx.x * blockDim.x + threadIdx.x) >> 5, lane = threadIdx.x & 31;
+    if (warp >= rows) return;
+    const uint32_t* row = window + static_cast<uint64_t>(warp) * (seq_len + 1);
+    uint32_t c = 0;
+    for (uint32_t s = lane; s < seq_len; s += 32) c += row[s] == separator ? 1u : 0u;
+    for (int o = 16; o > 0; o >>= 1) c += __shfl_down_sync(0xffffffffu, c, o);
+    if (lane == 0) row_base[warp] = c + (row[seq_len - 1] != separator ? 1u : 0u);
+}
+
+// Step 2: one block turns the per-row counts into exclusive prefix sums in place; row_base[rows] and counts[1]
+// receive the number of segments, and the first offset is 0.
+__global__ void __launch_bounds__(256) k_scan_rows(uint32_t* __restrict__ row_base, uint32_t rows, int32_t* __restrict__ cu,
+                                                   unsigned long long* __restrict__ counts) {
+    __shared__ uint32_t sh[256];
+    __shared__ uint32_t carry;
+    if (threadIdx.x == 0) carry = 0;
+    __syncthreads();
+    for (uint32_t base = 0; base < rows; base += 256) {
+        const uint32_t i = base + threadIdx.x;
+        const uint32_t v = i < rows ? row_base[i] : 0u;
+        sh[threadIdx.x] = v;
+        __syncthreads();
+        for (int o = 1; o < 256; o <<= 1) {  // inclusive scan
+            const uint32_t add = threadIdx.x >= static_cast<uint32_t>(o) ? sh[threadIdx.x - o] : 0u;
+            __syncthreads();
+            sh[threadIdx.x] += add;
+            __syncthreads();
+        }
+        if (i < rows) row_base[i] = carry + sh[threadIdx.x] - v;
+        __syncthreads();
+        if (threadIdx.x == 255) carry += sh[255];
+        __syncthreads();
+    }
+    if (threadIdx.x == 0) {
+        row_base[rows] = carry;
+        counts[1] = carry;
+        cu[0] = 0;
+    }
+}
+
+// Step 3: one block per row walks the row in chunks of 256 positions with a running count of the separators seen:
+// a token's segment is the row's first segment plus the separators before it; a separator at s closes its segment
+// at flat offset b*S + s + 1, the row end closes the last one unless a separator already did.
+__global__ void __launch_bounds__(256) k_fill_segments(const uint32_t* __restrict__ window, uint32_t seq_len, uint32_t separator,
+                                                       const uint32_t* __restrict__ row_base, int32_t* __restrict__ seg_ids,
+                                                       int32_t* __restrict__ cu) {
+    const uint32_t b = blockIdx.x, lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const uint32_t* row = window + static_cast<uint64_t>(b) * (seq_len + 1);
+    const uint32_t first = row_base[b];
+    __shared__ uint32_t warp_sum[8];
+    __shared__ uint32_t seen;  // separators in the chunks before this one
+    if (threadIdx.x == 0) seen = 0;
+    __syncthreads();
+    for (uint32_t base = 0; base < seq_len; base += 256) {
+        const uint32_t s = base + threadIdx.x;
+        const bool live = s < seq_len;
+        const uint32_t flag = live && row[s] == separator ? 1u : 0u;
+        const uint32_t ballot = __ballot_sync(0xffffffffu, flag);
+        const uint32_t before_in_warp = __popc(ballot & ((1u << lane) - 1u));
+        if (lane == 0) warp_sum[warp] = __popc(ballot);
+        __syncthreads();
+        uint32_t before = seen + before_in_warp;
+        for (uint32_t w = 0; w < warp; w++) before += warp_sum[w];
+        if (live) {
+            const uint64_t flat = static_cast<uint64_t>(b) * seq_len + s;
+            seg_ids[flat] = static_cast<int32_t>(first + before);
+            if (flag) cu[first + before + 1] = static_cast<int32_t>(flat + 1);
+        }
+        __syncthreads();
+        if (threadIdx.x == 0) {
+            uint32_t t = 0;
+            for (int w = 0; w < 8; w++) t += warp_sum[w];
+            seen += t;
+        }
+        __syncthreads();
+    }
+    if (threadIdx.x == 0 && row[seq_len - 1] != separator)
+        cu[first + seen + 1] = static_cast<int32_t>((static_cast<uint64_t>(b) + 1) * seq_len);
+}
+
 void release(oxz_loader* l) {
     if (!l) return;
     if (l->d_stage[0] || l->h_stage[0]) cudaSetDevice(l->device);
@@ -56,6 +196,12 @@ void release(oxz_loader* l) {
         if (l->d_inputs[i]) cudaFree(l->d_inputs[i]);
         if (l->d_targets[i]) cudaFree(l->d_targets[i]);
         if (l->staged[i]) cudaEventDestroy(l->staged[i]);
+        if (l->d_loss_mask[i]) cudaFree(l->d_loss_mask[i]);
+        if (l->d_seg_ids[i]) cudaFree(l->d_seg_ids[i]);
+        if (l->d_cu[i]) cudaFree(l->d_cu[i]);
+        if (l->d_row_base[i]) cudaFree(l->d_row_base[i]);
+        if (l->d_counts[i]) cudaFree(l->d_counts[i]);
+        if (l->h_counts[i]) cudaFreeHost(l->h_counts[i]);
     }
     if (l->tokens) munmap(const_cast<uint32_t*>(l->tokens), l->map_bytes);
     if (l->fd >= 0) close(l->fd);
@@ -182,17 +328,92 @@ int32_t oxz_loader_next_batch_async(oxz_loader* l, void* stream, int64_t** input
     memcpy(l->h_stage[k], l->tokens + row_ids[0] * width, B * width * 4);
     cudaStream_t s = (cudaStream_t)stream;
     OXZ_CUDA(cudaMemcpyAsync(l->d_stage[k], l->h_stage[k], B * width * 4, cudaMemcpyHostToDevice, s));
-    OXZ_CUDA(cudaEventRecord(l->staged[k], s));
     const uint64_t n = B * S;
     const int blocks = (int)((n + 255) / 256 < 148 * 8 ? (n + 255) / 256 : 148 * 8);
-    k_split_rows<<<blocks ? blocks : 1, 256, 0, s>>>(l->d_stage[k], B, S, l->d_inputs[k], l->d_targets[k]);
+    const bool masked = l->target_mask || l->document_mask;
+    if (!l->h_counts[0])
+        for (int i = 0; i < 2; i++) OXZ_CUDA(cudaMallocHost((void**)&l->h_counts[i], 16));
+    if (masked && !l->d_loss_mask[0]) {
+        for (int i = 0; i < 2; i++) {
+            OXZ_CUDA(cudaMalloc((void**)&l->d_loss_mask[i], n * 4));
+            OXZ_CUDA(cudaMalloc((void**)&l->d_counts[i], 16));
+        }
+    }
+    if (l->document_mask && !l->d_seg_ids[0]) {
+        for (int i = 0; i < 2; i++) {
+            OXZ_CUDA(cudaMalloc((void**)&l->d_seg_ids[i], n * 4));
+            OXZ_CUDA(cudaMalloc((void**)&l->d_cu[i], (n + 1) * 4));
+            OXZ_CUDA(cudaMalloc((void**)&l->d_row_base[i], (B + 1) * 4));
+        }
+    }
+    if (!masked) {
+        k_split_rows<<<blocks ? blocks : 1, 256, 0, s>>>(l->d_stage[k], B, S, l->d_inputs[k], l->d_targets[k]);
+        l->h_counts[k][0] = n;  // an unmasked batch scores every position (src/data/host_masks.rs:56-57)
+        l->h_counts[k][1] = 0;
+    } else {
+        MaskRule rule{};
+        rule.has_target = l->target_mask ? 1 : 0;
+        rule.has_document = l->document_mask ? 1 : 0;
+        rule.target_base = l->target_base;
+        rule.n_always = l->n_always;
+        rule.separator = l->separator;
+        for (uint32_t i = 0; i < l->n_always; i++) rule.always[i] = l->always[i];
+        OXZ_CUDA(cudaMemsetAsync(l->d_counts[k], 0, 16, s));
+        k_split_rows_masked<<<blocks ? blocks : 1, 256, 0, s>>>(l->d_stage[k], B, S, rule, l->d_inputs[k], l->d_targets[k],
+                                                               l->d_loss_mask[k], l->d_counts[k]);
+        if (l->document_mask) {
+            k_row_closings<<<(unsigned)((B * 32 + 255) / 256), 256, 0, s>>>(l->d_stage[k], (uint32_t)B, (uint32_t)S, l->separator, l->d_row_base[k]);
+            k_scan_rows<<<1, 256, 0, s>>>(l->d_row_base[k], (uint32_t)B, l->d_cu[k], l->d_counts[k]);
+            k_fill_segments<<<(unsigned)B, 256, 0, s>>>(l->d_stage[k], (uint32_t)S, l->separator, l->d_row_base[k], l->d_seg_ids[k], l->d_cu[k]);
+        }
+        OXZ_CUDA(cudaMemcpyAsync(l->h_counts[k], l->d_counts[k], 16, cudaMemcpyDeviceToHost, s));
+    }
     cudaError_t e = cudaGetLastError();
-    if (e != cudaSuccess) return fail(OXZ_ERR_CUDA, "launch of k_split_rows failed: %s", cudaGetErrorString(e));
+    if (e != cudaSuccess) return fail(OXZ_ERR_CUDA, "launch of the batch kernels failed: %s", cudaGetErrorString(e));
+    // marks the point after which this slot's pinned buffers (tokens in, counts out) may be touched again
+    OXZ_CUDA(cudaEventRecord(l->staged[k], s));
+    l->last = k;
     *inputs = l->d_inputs[k];
     *targets = l->d_targets[k];
     if (rows) memcpy(rows, row_ids.data(), B * 8);
     l->pos = next;
     l->slot ^= 1;
+    return OXZ_OK;
+}
+
+int32_t oxz_loader_set_target_mask(oxz_loader* l, int32_t on, uint32_t target_base, const uint32_t* always_score, uint32_t n_always) {
+    if (!l || (on && n_always && !always_score)) return fail(OXZ_ERR_INVALID, "oxz_loader_set_target_mask: null argument");
+    if (on && n_always > OXZ_MAX_ALWAYS_SCORE)
+        return fail(OXZ_ERR_INVALID, "oxz_loader_set_target_mask: %u always-scored ids, at most %u", n_always, OXZ_MAX_ALWAYS_SCORE);
+    l->target_mask = on != 0;
+    l->target_base = target_base;
+    l->n_always = on ? n_always : 0;
+    for (uint32_t i = 0; i < l->n_always; i++) l->always[i] = always_score[i];
+    return OXZ_OK;
+}
+
+int32_t oxz_loader_set_document_mask(oxz_loader* l, int32_t on, uint32_t separator_id) {
+    if (!l) return fail(OXZ_ERR_INVALID, "oxz_loader_set_document_mask: null loader");
+    if (on && l->layout.rank_batch_size * l->seq_len > 0x7fffffffull)
+        return fail(OXZ_ERR_DATA,
+                    "a batch of %llu x %llu tokens overflows the i32 segment offsets. Lower trainer.batch_size or "
+                    "model.max_seq_len.", (unsigned long long)l->layout.rank_batch_size, (unsigned long long)l->seq_len);
+    l->document_mask = on != 0;
+    l->separator = separator_id;
+    return OXZ_OK;
+}
+
+int32_t oxz_loader_batch_masks(const oxz_loader* l, oxz_batch_masks* out) {
+    if (!l || !out) return fail(OXZ_ERR_INVALID, "oxz_loader_batch_masks: null argument");
+    if (l->last < 0) return fail(OXZ_ERR_STATE, "oxz_loader_batch_masks: no batch has been drawn yet");
+    const int k = l->last;
+    const bool masked = l->d_loss_mask[k] && (l->target_mask || l->document_mask);
+    const bool segs = l->d_seg_ids[k] && l->document_mask;
+    out->loss_mask = masked ? l->d_loss_mask[k] : nullptr;
+    out->segment_ids = segs ? l->d_seg_ids[k] : nullptr;
+    out->cu_seqlens = segs ? l->d_cu[k] : nullptr;
+    out->scored = reinterpret_cast<const uint64_t*>(&l->h_counts[k][0]);
+    out->n_segments = reinterpret_cast<const uint64_t*>(&l->h_counts[k][1]);
     return OXZ_OK;
 }
 

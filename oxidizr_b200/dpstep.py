@@ -383,6 +383,27 @@ class LitDataLoader:
         check(lib().oxz_loader_next_batch_async(self._h, C.c_void_p(stream) if stream else None, C.byref(i), C.byref(t), rows))
         return i.value, t.value, list(rows)
 
+    def with_target_mask(self, target_base: int, always_score: list[int] = ()) -> "LitDataLoader":
+        """TargetMask::PrefixLm (src/data/mask.rs:21-47): a position scores iff its target id is at least target_base
+        or is one of always_score."""
+        ids = list(always_score)
+        check(lib().oxz_loader_set_target_mask(self._h, 1, target_base, (C.c_uint32 * max(len(ids), 1))(*ids), len(ids)))
+        return self
+
+    def with_document_mask(self, separator_id: int) -> "LitDataLoader":
+        """src/data/host_masks.rs:28-35: separator inputs are unscored and each batch carries its document segments."""
+        check(lib().oxz_loader_set_document_mask(self._h, 1, separator_id))
+        return self
+
+    def batch_masks(self) -> dict:
+        """Of the batch drawn last: device addresses of loss_mask [B,S] f32, segment_ids [B,S] i32 and cu_seqlens
+        (None for what is off), and two callables that read scored / n_segments from pinned host memory: call them
+        once the stream has passed the batch."""
+        m = ffi.BatchMasks()
+        check(lib().oxz_loader_batch_masks(self._h, C.byref(m)))
+        return dict(loss_mask=m.loss_mask, segment_ids=m.segment_ids, cu_seqlens=m.cu_seqlens,
+                    scored=lambda: int(m.scored[0]), n_segments=lambda: int(m.n_segments[0]))
+
     def close(self) -> None:
         if self._h:
             lib().oxz_loader_close(self._h)

@@ -77,3 +77,115 @@ def test_rank_batches_hold_exactly_the_checkers_token_indices(tmp_path, rows, ba
     assert fresh.next_batch()[2] == a
     for l in loaders + [fresh]:
         l.close()
+
+
+def write_tokens(tmp_path, tokens, name):
+    path = tmp_path / name
+    np.asarray(tokens, dtype="<u4").tofile(path)
+    return str(path)
+
+
+def draw(loader, batch, seq):
+    """One batch with its masks, read back: (inputs, targets, loss_mask|None, scored, offsets|None, ids|None)."""
+    import torch
+    from oxidizr_b200.interop import device_view
+    i, t, _ = loader.next_batch()
+    m = loader.batch_masks()
+    torch.cuda.synchronize()
+    n = batch * seq
+    view = lambda addr, dt, count: device_view(addr, count * torch.empty(0, dtype=dt).element_size(), dt, 0).cpu().tolist()  # noqa: E731
+    mask = view(m["loss_mask"], torch.float32, n) if m["loss_mask"] else None
+    ids = view(m["segment_ids"], torch.int32, n) if m["segment_ids"] else None
+    offsets = view(m["cu_seqlens"], torch.int32, m["n_segments"]() + 1) if m["cu_seqlens"] else None
+    return view(i, torch.int64, n), view(t, torch.int64, n), mask, m["scored"](), offsets, ids
+
+
+@pytest.mark.gpu
+def test_masks_and_segments_give_the_reference_tests_answers(tmp_path):
+    SEP, EOS, BASE = 0, 3, 12
+    # src/data/host_masks.rs:115-124
+    l = ox.LitDataLoader(write_tokens(tmp_path, [5, 6, SEP, 7, 8, 9], "a.bin"), 1, 5).with_document_mask(SEP)
+    _, _, mask, scored, offsets, ids = draw(l, 1, 5)
+    assert (mask, scored, offsets, ids) == ([1.0, 1.0, 0.0, 1.0, 1.0], 4, [0, 3, 5], [0, 0, 0, 1, 1])
+    l.close()
+    # src/data/host_masks.rs:126-137: the document mask ANDs with the target mask
+    l = ox.LitDataLoader(write_tokens(tmp_path, [4, BASE, SEP, BASE + 1, 4], "b.bin"), 1, 4)
+    _, _, mask, scored, _, _ = draw(l.with_target_mask(BASE, [EOS]).with_document_mask(SEP), 1, 4)
+    assert (mask, scored) == ([1.0, 0.0, 0.0, 0.0], 1)
+    l.close()
+    # src/data/host_masks.rs:139-146: off leaves no mask and no segments, every position scores
+    l = ox.LitDataLoader(write_tokens(tmp_path, [5, SEP, 6], "c.bin"), 1, 2)
+    assert draw(l, 1, 2)[2:] == (None, 2, None, None)
+    l.close()
+    # src/data/segments.rs:144-169
+    for tokens, b, s, want_off, want_ids in [
+            ([5, 6, 7, 1, 8, SEP, 9, 2], 2, 3, [0, 3, 5, 6], [0, 0, 0, 1, 1, 2]),
+            ([SEP, SEP, 5, 6], 1, 3, [0, 1, 2, 3], [0, 1, 2]),
+            ([5, SEP, 3, 6, SEP, 4], 2, 2, [0, 2, 4], [0, 0, 1, 1]),
+            ([5, 6, 7, 8, 9, 10], 2, 2, [0, 2, 4], [0, 0, 1, 1])]:
+        l = ox.LitDataLoader(write_tokens(tmp_path, tokens, "d.bin"), b, s).with_document_mask(SEP)
+        _, _, _, _, offsets, ids = draw(l, b, s)
+        assert (offsets, ids) == (want_off, want_ids), tokens
+        l.close()
+    # src/data/mask.rs:222-274: prefix-LM scoring, the boundary, a row that starts mid-sequence
+    l = ox.LitDataLoader(write_tokens(tmp_path, [0, 1, 4, 5, 6, 7, 2, 12, 13, 14, 15, 16, 17, 18, EOS], "e.bin"), 1, 14)
+    assert draw(l.with_target_mask(BASE, [EOS]), 1, 14)[2] == [0.0] * 6 + [1.0] * 8
+    l.close()
+    l = ox.LitDataLoader(write_tokens(tmp_path, [0, BASE - 1, BASE, BASE + 1], "f.bin"), 1, 3).with_target_mask(BASE, [EOS])
+    assert draw(l, 1, 3)[2] == [0.0, 1.0, 1.0]
+    l.close()
+    l = ox.LitDataLoader(write_tokens(tmp_path, [0, 1, 4, 2, 12, 13, EOS, 0, 1, 5, 6, 2, 13, 14, EOS], "g.bin"), 1, 4)
+    l.with_target_mask(BASE, [EOS])
+    assert draw(l, 1, 4)[2] == [0.0, 0.0, 0.0, 1.0] and draw(l, 1, 4)[2] == [1.0, 0.0, 0.0, 0.0]
+    l.close()
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("batch,seq,world,sep_every", [(2, 3, 2, 5), (3, 700, 1, 37), (5, 257, 2, 2), (4, 1024, 1, 100000), (300, 9, 1, 4)])
+def test_masks_equal_the_checkers_on_every_rank_and_batch(tmp_path, batch, seq, world, sep_every):
+    """Long rows (several 256-position chunks), many rows (several scan chunks), dense and absent separators: the loss
+    mask, the scored count, the segment ids and offsets equal the checker's for every rank, and the ranks' offsets
+    concatenate to the global batch's (src/data/host_masks.rs:170-198)."""
+    SEP, BASE, ALWAYS = 7, 40, [3, 11]
+    width = seq + 1
+    rows = batch * world * 3 + 1
+    rng = np.random.default_rng(batch * 1000 + seq)
+    toks = rng.integers(8, 64, size=rows * width + 2, dtype=np.uint32)
+    toks[rng.integers(0, toks.size, size=toks.size // sep_every)] = SEP
+    toks[rng.integers(0, toks.size, size=toks.size // 9)] = 3
+    path = write_tokens(tmp_path, toks, "t.bin")
+    loaders = [ox.LitDataLoader(path, batch, seq, rank=r, world_size=world).with_target_mask(BASE, ALWAYS).with_document_mask(SEP)
+               for r in range(world)]
+    whole = hl.RowLayout(rows, batch * world)
+    ranked = hl.RowLayout(rows, batch, world)
+    pos = hl.DataPosition()
+    for _ in range(4):  # crosses an epoch boundary
+        g_rows, _, _, nxt = hl.rank_window(whole, pos, 0, seq)
+        g_window = [int(t) for r in g_rows for t in toks[r * width:(r + 1) * width]]
+        _, g_scored, (g_off, _) = hl.host_masks(g_window, batch * world, seq, (BASE, ALWAYS), SEP)
+        joined, scored = [0], 0
+        for r, l in enumerate(loaders):
+            rr, _, _, _ = hl.rank_window(ranked, pos, r, seq)
+            window = [int(t) for row in rr for t in toks[row * width:(row + 1) * width]]
+            want_mask, want_scored, (want_off, want_ids) = hl.host_masks(window, batch, seq, (BASE, ALWAYS), SEP)
+            inputs, targets, mask, got_scored, offsets, ids = draw(l, batch, seq)
+            assert inputs == [window[b * width + s] for b in range(batch) for s in range(seq)]
+            assert targets == [window[b * width + s + 1] for b in range(batch) for s in range(seq)]
+            assert mask == want_mask and got_scored == want_scored
+            assert offsets == want_off and ids == want_ids
+            joined += [o + r * batch * seq for o in offsets[1:]]
+            scored += got_scored
+        assert joined == g_off and scored == g_scored
+        pos = nxt
+    for l in loaders:
+        l.close()
+
+
+def test_mask_settings_are_checked_on_the_host(tmp_path):
+    path = write_tokens(tmp_path, list(range(40)), "h.bin")
+    l = ox.LitDataLoader(path, 2, 3)
+    with pytest.raises(ox.OxzError, match="at most 16"):
+        l.with_target_mask(5, list(range(17)))
+    with pytest.raises(ox.OxzError, match="no batch has been drawn"):
+        l.batch_masks()
+    l.close()

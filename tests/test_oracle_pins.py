@@ -343,3 +343,60 @@ def test_step_weighting():
     with pytest.raises(ValueError, match="1 of 2"):
         hl.reduce_step_weighting([(1, 5), (1, None)])
     assert hl.reduce_step_weighting([(3, None)]) == [(3, None)]
+
+
+# ---- loss mask and document segments: the reference's own cases
+SEP, EOS, BASE = 0, 3, 12
+
+
+def test_prefix_lm_mask_known_answers():
+    # src/data/mask.rs:222-274
+    pm = (BASE, [EOS])
+    tokens = [0, 1, 4, 5, 6, 7, 2, 12, 13, 14, 15, 16, 17, 18, EOS]
+    assert hl.build_target_mask(tokens, 1, 14, *pm) == [0.0] * 6 + [1.0] * 8
+    assert hl.build_target_mask([0, BASE - 1, BASE, BASE + 1], 1, 3, *pm) == [0.0, 1.0, 1.0]
+    stream = [0, 1, 4, 2, 12, 13, EOS, 0, 1, 5, 6, 2, 13, 14, EOS]
+    assert hl.build_target_mask(stream[0:5], 1, 4, *pm) == [0.0, 0.0, 0.0, 1.0]
+    assert hl.build_target_mask(stream[5:10], 1, 4, *pm) == [1.0, 0.0, 0.0, 0.0]
+    # no mask: every position scores (src/data/mask.rs:276-282, host_masks.rs:139-146)
+    assert hl.host_masks([5, SEP, 6], 1, 2) == (None, 2, None)
+
+
+def test_document_segments_known_answers():
+    # src/data/segments.rs:135-169
+    assert hl.host_segments([5, 6, SEP, 7, 8, 9], 1, 5, SEP) == ([0, 3, 5], [0, 0, 0, 1, 1])
+    assert hl.host_segments([5, 6, 7, 1, 8, SEP, 9, 2], 2, 3, SEP) == ([0, 3, 5, 6], [0, 0, 0, 1, 1, 2])
+    assert hl.host_segments([SEP, SEP, 5, 6], 1, 3, SEP) == ([0, 1, 2, 3], [0, 1, 2])
+    assert hl.host_segments([5, SEP, 3, 6, SEP, 4], 2, 2, SEP)[0] == [0, 2, 4]
+    assert hl.host_segments([5, 6, 7, 8, 9, 10], 2, 2, SEP) == ([0, 2, 4], [0, 0, 1, 1])
+
+
+def test_document_mask_ands_with_the_target_mask():
+    # src/data/host_masks.rs:115-137
+    mask, scored, (offsets, ids) = hl.host_masks([5, 6, SEP, 7, 8, 9], 1, 5, separator=SEP)
+    assert (mask, scored, offsets, ids) == ([1.0, 1.0, 0.0, 1.0, 1.0], 4, [0, 3, 5], [0, 0, 0, 1, 1])
+    mask, scored, _ = hl.host_masks([4, BASE, SEP, BASE + 1, 4], 1, 4, target_mask=(BASE, [EOS]), separator=SEP)
+    assert (mask, scored) == ([1.0, 0.0, 0.0, 0.0], 1)
+
+
+def test_rank_segments_concatenate_to_the_global_segments():
+    # src/data/host_masks.rs:170-198, in stream order
+    tokens = [SEP if i % 5 == 2 else 1 + i % 11 for i in range(96)]
+    batch, world, seq = 2, 2, 3
+    width = seq + 1
+    whole_layout = hl.RowLayout(len(tokens) // width, batch * world)
+    rank_layout = hl.RowLayout(len(tokens) // width, batch, world)
+    pos = hl.DataPosition()
+    for _ in range(6):
+        rows, _, _, nxt = hl.rank_window(whole_layout, pos, 0, seq)
+        window = [t for r in rows for t in tokens[r * width:(r + 1) * width]]
+        _, whole_scored, (whole_offsets, _) = hl.host_masks(window, batch * world, seq, separator=SEP)
+        joined, scored = [0], 0
+        for rank in range(world):
+            rr, _, _, _ = hl.rank_window(rank_layout, pos, rank, seq)
+            part = [t for r in rr for t in tokens[r * width:(r + 1) * width]]
+            _, s, (off, _) = hl.host_masks(part, batch, seq, separator=SEP)
+            joined += [o + rank * batch * seq for o in off[1:]]
+            scored += s
+        assert joined == whole_offsets and scored == whole_scored
+        pos = nxt
