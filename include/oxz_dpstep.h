@@ -376,6 +376,15 @@ int32_t oxz_read_loss_scale_state(const char* meta_path, uint64_t start_step, in
 typedef struct oxz_loader oxz_loader;
 int32_t oxz_loader_open(const char* path, uint64_t seq_len, uint64_t rank_batch_size, uint64_t rank, uint64_t world,
                         uint64_t first_row, uint64_t end_row, int32_t device, oxz_loader** out);
+/* LitDataLoader::from_files + with_row_ranges + with_rank (src/data/multi_source.rs:17-52, src/data/row_ranges.rs:40-106):
+ * the stream is file 0's whole rows, then file 1's, ...; each file drops its own tail. spans holds n_spans pairs
+ * (start, end) of GLOBAL rows, end exclusive, ascending without overlap; loader rows count across them in order
+ * (n_spans 0: every row). The `.tokens.json` sidecars are the tokenizer's and are not read here. */
+int32_t oxz_loader_open_files(const char* const* paths, uint32_t n_paths, uint64_t seq_len, uint64_t rank_batch_size,
+                              uint64_t rank, uint64_t world, const uint64_t* spans, uint32_t n_spans, int32_t device,
+                              oxz_loader** out);
+/* LitDataLoader::source_rows: whole rows of each source in order; *n_sources receives the count, rows up to cap of them. */
+int32_t oxz_loader_source_rows(const oxz_loader* loader, uint64_t* rows, uint32_t cap, uint32_t* n_sources);
 int32_t oxz_loader_close(oxz_loader* loader);
 /* LitDataLoader::with_target_mask(TargetMask::PrefixLm{target_base, always_score}) (src/data/mask.rs:21-47): a position
  * scores iff its TARGET id is at least target_base or is listed in always_score. on = 0 turns the mask off.

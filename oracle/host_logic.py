@@ -317,6 +317,44 @@ def rank_window(layout: RowLayout, pos: DataPosition, rank: int, seq_len: int, f
     return rows, inputs, targets, DataPosition(start.epoch, start.row + layout.batch_size())
 
 
+class RowRanges:
+    """Ascending, disjoint, non-empty global row ranges (src/data/row_ranges.rs:9-106): loader row r is the r-th row
+    across the ranges in order."""
+
+    def __init__(self, spans, total: int):
+        if not spans:
+            raise ValueError("an empty list of row ranges reads no rows. Pass at least one range.")
+        self.spans, self.before, self.len = list(spans), [], 0
+        prev_end = 0
+        for i, (start, end) in enumerate(spans):
+            if start >= end or end > total:
+                raise ValueError(f"row range [{start}, {end}) is not a non-empty range inside the {total} whole rows of "
+                                 f"this data. Pick a range inside [0, {total}).")
+            if i > 0 and start < prev_end:
+                raise ValueError(f"row range [{start}, {end}) starts before row {prev_end}, the end of the range before "
+                                 "it. Pass ranges in ascending order without overlap.")
+            self.before.append(self.len)
+            self.len += end - start
+            prev_end = end
+
+    def global_row(self, row: int) -> int:
+        index = max(sum(1 for b in self.before if b <= row) - 1, 0)
+        return self.spans[index][0] + (row - self.before[index])
+
+
+def store_row(sources, width: int, global_row: int):
+    """RowStore::row over in-memory sources (src/data/source.rs:96-158): each source keeps its own whole rows of
+    `width` tokens and drops its own tail; global rows count from the start of source 0."""
+    first = 0
+    for tokens in sources:
+        rows = len(tokens) // width
+        if global_row < first + rows:
+            at = (global_row - first) * width
+            return list(tokens[at:at + width])
+        first += rows
+    raise IndexError(f"row {global_row} is past the {first} whole rows of this data")
+
+
 # ---------------------------------------------------------------- loss mask and document segments of one window
 def build_target_mask(window, batch_size: int, seq_len: int, target_base: int, always_score=()):
     """TargetMask::PrefixLm over a raw [batch_size, seq_len + 1] window (src/data/mask.rs:36-47, 72-88): position

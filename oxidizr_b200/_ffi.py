@@ -154,6 +154,9 @@ SIGNATURES = {
     "oxz_spike_judge": (C.c_int32, [C.POINTER(SpikeConfig), C.POINTER(SpikeState), C.c_uint64, C.c_double,
                                     C.POINTER(C.c_int32), C.POINTER(C.c_int32)]),
     "oxz_lr_at": (C.c_int32, [C.POINTER(LrPlanC), C.c_uint64, f64p]),
+    "oxz_loader_open_files": (C.c_int32, [C.POINTER(C.c_char_p), C.c_uint32, C.c_uint64, C.c_uint64, C.c_uint64, C.c_uint64,
+                                          C.POINTER(C.c_uint64), C.c_uint32, C.c_int32, C.POINTER(vp)]),
+    "oxz_loader_source_rows": (C.c_int32, [vp, C.POINTER(C.c_uint64), C.c_uint32, C.POINTER(C.c_uint32)]),
     "oxz_loader_set_target_mask": (C.c_int32, [vp, C.c_int32, C.c_uint32, C.POINTER(C.c_uint32), C.c_uint32]),
     "oxz_loader_set_document_mask": (C.c_int32, [vp, C.c_int32, C.c_uint32]),
     "oxz_loader_batch_masks": (C.c_int32, [vp, C.POINTER(BatchMasks)]),

@@ -18,11 +18,20 @@
 
 #include "oxz_internal.h"
 
-struct oxz_loader {
+// One source: a token file mapped read-only. It keeps its own whole rows and drops its own tail, so no row spans two
+// sources; global row r counts rows from the start of source 0 (src/data/source.rs:1-6, 96-118).
+struct Part {
     int fd = -1;
     const uint32_t* tokens = nullptr;
     size_t map_bytes = 0;
-    uint64_t n_tokens = 0, seq_len = 0, first_row = 0;
+    uint64_t n_tokens = 0, rows = 0, first_row = 0;
+};
+
+struct oxz_loader {
+    std::vector<Part> parts;
+    uint64_t total_rows = 0, seq_len = 0;
+    // ascending, disjoint, non-empty global row ranges; loader row r is the r-th row across them (src/data/row_ranges.rs)
+    std::vector<uint64_t> span_start, span_end, span_before;
     oxz_row_layout layout{};
     uint64_t rank = 0;
     oxz_data_position pos{0, 0};
@@ -203,9 +212,25 @@ void release(oxz_loader* l) {
         if (l->d_counts[i]) cudaFree(l->d_counts[i]);
         if (l->h_counts[i]) cudaFreeHost(l->h_counts[i]);
     }
-    if (l->tokens) munmap(const_cast<uint32_t*>(l->tokens), l->map_bytes);
-    if (l->fd >= 0) close(l->fd);
+    for (Part& p : l->parts) {
+        if (p.tokens) munmap(const_cast<uint32_t*>(p.tokens), p.map_bytes);
+        if (p.fd >= 0) close(p.fd);
+    }
     delete l;
+}
+
+// RowRanges::global_row (src/data/row_ranges.rs:100-106)
+uint64_t global_row(const oxz_loader* l, uint64_t row) {
+    size_t i = l->span_before.size();
+    while (i > 1 && l->span_before[i - 1] > row) i--;
+    return i ? l->span_start[i - 1] + (row - l->span_before[i - 1]) : row;
+}
+
+// RowStore::row (src/data/source.rs:140-158): where global row r starts, or null past the last whole row.
+const uint32_t* row_tokens(const oxz_loader* l, uint64_t r) {
+    for (const Part& p : l->parts)
+        if (r < p.first_row + p.rows) return r >= p.first_row ? p.tokens + (r - p.first_row) * (l->seq_len + 1) : nullptr;
+    return nullptr;
 }
 
 }  // namespace
@@ -214,62 +239,124 @@ using namespace oxz;
 
 extern "C" {
 
+// Maps the files in order. `what` words the errors of an unusable range for the one-file entry point.
+static int32_t open_parts(oxz_loader* l, const char* const* paths, uint32_t n_paths, uint64_t seq_len) {
+    using namespace oxz;
+    if (n_paths == 0) return fail(OXZ_ERR_DATA, "no data files given. Pass -d <file.bin>, or set trainer.data.sources.");
+    for (uint32_t i = 0; i < n_paths; i++) {
+        const char* path = paths[i];
+        if (!path) return fail(OXZ_ERR_INVALID, "oxz_loader_open: path %u is null", i);
+        l->parts.emplace_back();
+        Part& p = l->parts.back();
+        p.fd = open(path, O_RDONLY);
+        if (p.fd < 0) return fail(OXZ_ERR_DATA, "failed to open data file %s: %s", path, strerror(errno));
+        struct stat st;
+        if (fstat(p.fd, &st) != 0) return fail(OXZ_ERR_DATA, "failed to stat data file %s: %s", path, strerror(errno));
+        if (st.st_size % 4 != 0)
+            return fail(OXZ_ERR_DATA, "data file %s is %lld bytes, not a multiple of 4: it is not a u32 token array. Rebuild it as raw u32 tokens.",
+                        path, (long long)st.st_size);
+        p.n_tokens = (uint64_t)st.st_size / 4;
+        if (st.st_size > 0) {
+            void* m = mmap(nullptr, (size_t)st.st_size, PROT_READ, MAP_PRIVATE, p.fd, 0);
+            if (m == MAP_FAILED) return fail(OXZ_ERR_DATA, "failed to mmap data file %s: %s", path, strerror(errno));
+            p.tokens = static_cast<const uint32_t*>(m);
+            p.map_bytes = (size_t)st.st_size;
+        }
+        p.rows = p.n_tokens / (seq_len + 1);  // the tail shorter than a row is never read
+        p.first_row = l->total_rows;
+        l->total_rows += p.rows;
+    }
+    return OXZ_OK;
+}
+
+static int32_t finish_open(oxz_loader* l, uint64_t seq_len, uint64_t rank_batch_size, uint64_t rank, uint64_t world, int32_t device) {
+    using namespace oxz;
+    uint64_t len = 0;
+    for (size_t i = 0; i < l->span_start.size(); i++) {
+        l->span_before.push_back(len);
+        len += l->span_end[i] - l->span_start[i];
+    }
+    l->seq_len = seq_len;
+    l->layout = oxz_row_layout{len, rank_batch_size, world};
+    l->rank = rank;
+    l->device = device;
+    OXZ_TRY(oxz_rows_check(&l->layout));
+    if (rank >= world)
+        return fail(OXZ_ERR_DATA, "rank %llu is not below world size %llu. Pass a rank in [0, %llu).", (unsigned long long)rank,
+                    (unsigned long long)world, (unsigned long long)world);
+    return OXZ_OK;
+}
+
 int32_t oxz_loader_open(const char* path, uint64_t seq_len, uint64_t rank_batch_size, uint64_t rank, uint64_t world,
                         uint64_t first_row, uint64_t end_row, int32_t device, oxz_loader** out) {
     if (!path || !out) return fail(OXZ_ERR_INVALID, "oxz_loader_open: null argument");
     *out = nullptr;
     if (seq_len == 0) return fail(OXZ_ERR_DATA, "model.max_seq_len is 0: a row needs at least one input and one target token");
     oxz_loader* l = new oxz_loader();
-    l->fd = open(path, O_RDONLY);
-    if (l->fd < 0) {
-        int32_t s = fail(OXZ_ERR_DATA, "failed to open data file %s: %s", path, strerror(errno));
-        release(l);
-        return s;
+    int32_t s = open_parts(l, &path, 1, seq_len);
+    if (s == OXZ_OK) {
+        if (end_row == 0) end_row = l->total_rows;
+        if (first_row >= end_row || end_row > l->total_rows)
+            s = fail(OXZ_ERR_DATA, "row range [%llu, %llu) does not fit the data's %llu whole rows", (unsigned long long)first_row,
+                     (unsigned long long)end_row, (unsigned long long)l->total_rows);
     }
-    struct stat st;
-    if (fstat(l->fd, &st) != 0) {
-        int32_t s = fail(OXZ_ERR_DATA, "failed to stat data file %s: %s", path, strerror(errno));
-        release(l);
-        return s;
+    if (s == OXZ_OK) {
+        l->span_start.push_back(first_row);
+        l->span_end.push_back(end_row);
+        s = finish_open(l, seq_len, rank_batch_size, rank, world, device);
     }
-    if (st.st_size % 4 != 0) {
-        int32_t s = fail(OXZ_ERR_DATA, "data file %s is %lld bytes, not a multiple of 4: it is not a u32 token file", path, (long long)st.st_size);
-        release(l);
-        return s;
-    }
-    l->n_tokens = (uint64_t)st.st_size / 4;
-    if (st.st_size > 0) {
-        void* m = mmap(nullptr, (size_t)st.st_size, PROT_READ, MAP_PRIVATE, l->fd, 0);
-        if (m == MAP_FAILED) {
-            int32_t s = fail(OXZ_ERR_DATA, "failed to mmap data file %s: %s", path, strerror(errno));
-            release(l);
-            return s;
-        }
-        l->tokens = static_cast<const uint32_t*>(m);
-        l->map_bytes = (size_t)st.st_size;
-    }
-    const uint64_t total_rows = l->n_tokens / (seq_len + 1);  // the tail shorter than a row is never read
-    if (end_row == 0) end_row = total_rows;
-    if (first_row >= end_row || end_row > total_rows) {
-        int32_t s = fail(OXZ_ERR_DATA, "row range [%llu, %llu) does not fit the data's %llu whole rows", (unsigned long long)first_row,
-                         (unsigned long long)end_row, (unsigned long long)total_rows);
-        release(l);
-        return s;
-    }
-    l->seq_len = seq_len;
-    l->first_row = first_row;
-    l->layout = oxz_row_layout{end_row - first_row, rank_batch_size, world};
-    l->rank = rank;
-    l->device = device;
-    int32_t s = oxz_rows_check(&l->layout);
-    if (s == OXZ_OK && rank >= world)
-        s = fail(OXZ_ERR_DATA, "rank %llu is not below world size %llu. Pass a rank in [0, %llu).", (unsigned long long)rank,
-                 (unsigned long long)world, (unsigned long long)world);
     if (s != OXZ_OK) {
         release(l);
         return s;
     }
     *out = l;
+    return OXZ_OK;
+}
+
+int32_t oxz_loader_open_files(const char* const* paths, uint32_t n_paths, uint64_t seq_len, uint64_t rank_batch_size,
+                              uint64_t rank, uint64_t world, const uint64_t* spans, uint32_t n_spans, int32_t device,
+                              oxz_loader** out) {
+    if (!out || (n_paths && !paths) || (n_spans && !spans)) return fail(OXZ_ERR_INVALID, "oxz_loader_open_files: null argument");
+    *out = nullptr;
+    if (seq_len == 0) return fail(OXZ_ERR_DATA, "model.max_seq_len is 0: a row needs at least one input and one target token");
+    oxz_loader* l = new oxz_loader();
+    int32_t s = open_parts(l, paths, n_paths, seq_len);
+    const uint64_t total = l->total_rows;
+    if (s == OXZ_OK && n_spans == 0) {  // RowRanges::whole
+        if (total) {
+            l->span_start.push_back(0);
+            l->span_end.push_back(total);
+        }
+    }
+    // RowRanges::new (src/data/row_ranges.rs:40-76)
+    uint64_t prev_end = 0;
+    for (uint32_t i = 0; s == OXZ_OK && i < n_spans; i++) {
+        const uint64_t a = spans[2 * i], b = spans[2 * i + 1];
+        if (a >= b || b > total)
+            s = fail(OXZ_ERR_DATA, "row range [%llu, %llu) is not a non-empty range inside the %llu whole rows of this data. Pick a range inside [0, %llu).",
+                     (unsigned long long)a, (unsigned long long)b, (unsigned long long)total, (unsigned long long)total);
+        else if (i > 0 && a < prev_end)
+            s = fail(OXZ_ERR_DATA, "row range [%llu, %llu) starts before row %llu, the end of the range before it. Pass ranges in ascending order without overlap.",
+                     (unsigned long long)a, (unsigned long long)b, (unsigned long long)prev_end);
+        else {
+            l->span_start.push_back(a);
+            l->span_end.push_back(b);
+            prev_end = b;
+        }
+    }
+    if (s == OXZ_OK) s = finish_open(l, seq_len, rank_batch_size, rank, world, device);
+    if (s != OXZ_OK) {
+        release(l);
+        return s;
+    }
+    *out = l;
+    return OXZ_OK;
+}
+
+int32_t oxz_loader_source_rows(const oxz_loader* l, uint64_t* rows, uint32_t cap, uint32_t* n_sources) {
+    if (!l || !n_sources) return fail(OXZ_ERR_INVALID, "oxz_loader_source_rows: null argument");
+    *n_sources = (uint32_t)l->parts.size();
+    for (uint32_t i = 0; rows && i < cap && i < l->parts.size(); i++) rows[i] = l->parts[i].rows;
     return OXZ_OK;
 }
 
@@ -317,15 +404,25 @@ int32_t oxz_loader_next_batch_async(oxz_loader* l, void* stream, int64_t** input
     }
     oxz_data_position next;
     std::vector<uint64_t> row_ids(B);
-    OXZ_TRY(oxz_rows_next_window(&l->layout, l->pos, l->rank, S, l->first_row, nullptr, 0, row_ids.data(), nullptr, nullptr, &next));
-    if ((row_ids[B - 1] + 1) * width > l->n_tokens)
-        return fail(OXZ_ERR_DATA, "row %llu is past the %llu whole rows of this data. This is a loader bug: report it with the data and config.",
-                    (unsigned long long)row_ids[B - 1], (unsigned long long)(l->n_tokens / width));
+    OXZ_TRY(oxz_rows_next_window(&l->layout, l->pos, l->rank, S, 0, nullptr, 0, row_ids.data(), nullptr, nullptr, &next));
+    std::vector<const uint32_t*> src(B);
+    for (uint64_t b = 0; b < B; b++) {
+        row_ids[b] = global_row(l, row_ids[b]);  // loader row -> global row across the ranges
+        src[b] = row_tokens(l, row_ids[b]);
+        if (!src[b])
+            return fail(OXZ_ERR_DATA, "row %llu is past the %llu whole rows of this data. This is a loader bug: report it with the data and config.",
+                        (unsigned long long)row_ids[b], (unsigned long long)l->total_rows);
+    }
     const int k = l->slot;
     // the pinned buffer of this slot may still feed the copy issued two batches ago
     OXZ_CUDA(cudaEventSynchronize(l->staged[k]));
-    // a rank's slots are consecutive rows in stream order: one contiguous span of the file
-    memcpy(l->h_stage[k], l->tokens + row_ids[0] * width, B * width * 4);
+    // a rank's slots are consecutive loader rows: runs that are also consecutive in one file move as one copy
+    for (uint64_t b = 0; b < B;) {
+        uint64_t e = b + 1;
+        while (e < B && src[e] == src[e - 1] + width) e++;
+        memcpy(l->h_stage[k] + b * width, src[b], (e - b) * width * 4);
+        b = e;
+    }
     cudaStream_t s = (cudaStream_t)stream;
     OXZ_CUDA(cudaMemcpyAsync(l->d_stage[k], l->h_stage[k], B * width * 4, cudaMemcpyHostToDevice, s));
     const uint64_t n = B * S;

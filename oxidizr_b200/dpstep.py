@@ -363,6 +363,27 @@ class LitDataLoader:
                                     C.byref(self._h)))
         self.batch_size, self.seq_len, self.rank, self.world_size = batch_size, seq_len, rank, world_size
 
+    @classmethod
+    def from_files(cls, paths: list[str], batch_size: int, seq_len: int, rank: int = 0, world_size: int = 1,
+                   row_ranges: list[tuple[int, int]] | None = None, device: int = 0) -> "LitDataLoader":
+        """from_files + with_row_ranges + with_rank (src/data/multi_source.rs:17-52): the files' whole rows in order,
+        restricted to ascending global row ranges (end exclusive)."""
+        self = cls.__new__(cls)
+        self._h = C.c_void_p()
+        spans = [v for span in (row_ranges or []) for v in span]
+        check(lib().oxz_loader_open_files((C.c_char_p * max(len(paths), 1))(*[p.encode() for p in paths]), len(paths), seq_len,
+                                          batch_size, rank, world_size, (C.c_uint64 * max(len(spans), 1))(*spans),
+                                          len(spans) // 2, device, C.byref(self._h)))
+        self.batch_size, self.seq_len, self.rank, self.world_size = batch_size, seq_len, rank, world_size
+        return self
+
+    def source_rows(self) -> list[int]:
+        n = C.c_uint32()
+        check(lib().oxz_loader_source_rows(self._h, None, 0, C.byref(n)))
+        rows = (C.c_uint64 * max(n.value, 1))()
+        check(lib().oxz_loader_source_rows(self._h, rows, n.value, C.byref(n)))
+        return list(rows)[:n.value]
+
     def num_rows(self) -> int:
         v = C.c_uint64()
         check(lib().oxz_loader_num_rows(self._h, C.byref(v)))

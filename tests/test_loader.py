@@ -189,3 +189,70 @@ def test_mask_settings_are_checked_on_the_host(tmp_path):
     with pytest.raises(ox.OxzError, match="no batch has been drawn"):
         l.batch_masks()
     l.close()
+
+
+def test_several_files_and_row_ranges_are_checked_on_the_host(tmp_path):
+    width = SEQ + 1
+    a = write_tokens(tmp_path, list(range(6 * width + 1)), "s0.bin")
+    b = write_tokens(tmp_path, list(range(4 * width + 3)), "s1.bin")
+    c = write_tokens(tmp_path, [1, 2], "s2.bin")  # shorter than a row: no rows
+    l = ox.LitDataLoader.from_files([a, b, c], 2, SEQ)
+    assert l.source_rows() == [6, 4, 0] and l.num_rows() == 10
+    l.close()
+    l = ox.LitDataLoader.from_files([a, b], 2, SEQ, row_ranges=[(0, 5), (6, 9)])
+    assert l.num_rows() == 8
+    l.close()
+    for ranges, msg in [([(3, 3)], "not a non-empty range"), ([(0, 11)], "inside the 10 whole rows"),
+                        ([(0, 5), (4, 6)], "starts before row 5")]:
+        with pytest.raises(ox.OxzError, match=msg):
+            ox.LitDataLoader.from_files([a, b], 1, SEQ, row_ranges=ranges)
+    with pytest.raises(ox.OxzError, match="no data files given"):
+        ox.LitDataLoader.from_files([], 1, SEQ)
+    with pytest.raises(ox.OxzError, match="failed to open data file"):
+        ox.LitDataLoader.from_files([a, str(tmp_path / "gone.bin")], 1, SEQ)
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("world", [1, 2])
+def test_batches_over_several_files_and_ranges_read_the_checkers_rows(tmp_path, world):
+    """src/data/multi_source.rs:99-161 in stream order: rows follow the sources in order, no row crosses a file seam or
+    touches a tail, train and eval ranges stay disjoint, a batch can carry rows of several sources."""
+    width = SEQ + 1
+    lens = [6 * width + 1, 4 * width + 3, 2, 5 * width]
+    rng = np.random.default_rng(5)
+    sources = [rng.integers(0, 50000, size=n, dtype=np.uint32) for n in lens]
+    paths = [write_tokens(tmp_path, t, f"m{i}.bin") for i, t in enumerate(sources)]
+    total = sum(n // width for n in lens)
+    train_spans, eval_spans = [(0, 5), (6, 9), (10, 15)], [(5, 6), (9, 10)]
+    batch = 2
+    for spans in (train_spans, eval_spans, None):
+        ranges = hl.RowRanges(spans or [(0, total)], total)
+        if ranges.len < batch * world:
+            continue
+        layout = hl.RowLayout(ranges.len, batch, world)
+        loaders = [ox.LitDataLoader.from_files(paths, batch, SEQ, rank=r, world_size=world, row_ranges=spans) for r in range(world)]
+        pos = hl.DataPosition()
+        seen = []
+        for _ in range(2 * layout.batches_per_epoch() + 1):
+            for r, l in enumerate(loaders):
+                loader_rows, _, _, nxt = hl.rank_window(layout, pos, r, SEQ)
+                want_rows = [ranges.global_row(x) for x in loader_rows]
+                window = [t for g in want_rows for t in hl.store_row(sources, width, g)]
+                i, t, rows = l.next_batch()
+                inputs, targets = read_i64(i, batch * SEQ), read_i64(t, batch * SEQ)
+                assert rows == want_rows
+                assert inputs == [int(window[b * width + s]) for b in range(batch) for s in range(SEQ)]
+                assert targets == [int(window[b * width + s + 1]) for b in range(batch) for s in range(SEQ)]
+                seen += rows
+            pos = nxt
+        allowed = {g for a, b in (spans or [(0, total)]) for g in range(a, b)}
+        assert set(seen) <= allowed
+        for l in loaders:
+            l.close()
+
+
+def read_i64(addr, count):
+    import torch
+    from oxidizr_b200.interop import device_view
+    torch.cuda.synchronize()
+    return device_view(addr, count * 8, torch.int64, 0).cpu().tolist()

@@ -400,3 +400,19 @@ def test_rank_segments_concatenate_to_the_global_segments():
             scored += s
         assert joined == whole_offsets and scored == whole_scored
         pos = nxt
+
+
+def test_row_ranges_and_sources_known_answers():
+    # src/data/source.rs:316-328: each source drops its own tail
+    sources = [list(range(7)), list(range(100, 105)), [200, 201]]
+    assert [hl.store_row(sources, 3, r) for r in range(3)] == [[0, 1, 2], [3, 4, 5], [100, 101, 102]]
+    with pytest.raises(IndexError):
+        hl.store_row(sources, 3, 3)
+    # src/data/multi_source.rs:137-154: train [0,5) and [6,9), eval [5,6) and [9,10) of 10 rows
+    train, evalr = hl.RowRanges([(0, 5), (6, 9)], 10), hl.RowRanges([(5, 6), (9, 10)], 10)
+    assert train.len == 8 and [train.global_row(r) for r in range(8)] == [0, 1, 2, 3, 4, 6, 7, 8]
+    assert [evalr.global_row(r) for r in range(2)] == [5, 9]
+    for spans, msg in [([], "empty list"), ([(3, 3)], "not a non-empty range"), ([(0, 11)], "inside the 10 whole rows"),
+                       ([(0, 5), (4, 6)], "starts before row 5")]:
+        with pytest.raises(ValueError, match=msg):
+            hl.RowRanges(spans, 10)
