@@ -285,6 +285,10 @@ def run_gpu(args):
             exposed.append(sec1 * 1e3)
         overlap = {"buckets": nb, "buckets_reduced_during_backward": early, "exposed_ms_per_step": statistics.median(exposed)}
 
+    aux = None
+    if world == 1 and not args.skip_aux:
+        aux = aux_measurements(ox, torch, opt, numel, stream, local_rank)
+
     peak, peak_kind = measured_peaks()
     totals = sorted(p.total_ms for p in profs)
     pct = lambda q: totals[min(len(totals) - 1, int(q * len(totals)))]  # noqa: E731
@@ -320,6 +324,7 @@ def run_gpu(args):
         "gpu_launches": (10 if mode == ox.SYNC_COPY else 4) * args.steps * world,
         "launch_geometry": opt.launch_geometry(),
         "overlap_with_backward": overlap,
+        "aux": aux,
         "clocks": clocks,
         "result": {"grad_norm": res.grad_norm, "applied": res.applied, "timestep": res.timestep},
     }
@@ -338,6 +343,58 @@ def run_gpu(args):
         comm.destroy()
     if dist is not None:
         dist.destroy_process_group()
+
+
+def aux_measurements(ox, torch, opt, numel, stream, local_rank: int) -> dict:
+    """The callers either side of the step, timed apart from `value`: per-tensor gradients into the flat buffer
+    (overwrite and accumulate), and the rank-sliced loader with and without its masks."""
+    import tempfile
+    P = sum(numel)
+    pos, offs = 0, []
+    for n in numel:
+        offs.append(pos)
+        pos += (n + 7) // 8 * 8  # 16-byte aligned starts
+    src = torch.empty(pos, dtype=torch.bfloat16, device="cuda").normal_(0.0, 1e-3)
+    ptrs = [src.data_ptr() + o * 2 for o in offs]
+    out = {"flatten": {}}
+    for name, acc, bytes_per in (("overwrite", False, 4), ("accumulate", True, 6)):
+        opt.flatten_grads(ptrs, acc)
+        torch.cuda.synchronize()
+        t0, t1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        reps = 5
+        with torch.cuda.stream(stream):
+            t0.record(stream)
+            for _ in range(reps):
+                opt.flatten_grads(ptrs, acc)
+            t1.record(stream)
+        torch.cuda.synchronize()
+        ms = t0.elapsed_time(t1) / reps
+        out["flatten"][name] = {"ms": ms, "gbs": bytes_per * P / (ms * 1e-3) / 1e9, "bytes_per_param": bytes_per}
+    del src
+    batch, seq, rows = 8, 2048, 2048
+    with tempfile.TemporaryDirectory() as d:
+        path = os.path.join(d, "tokens.bin")
+        rng = np.random.default_rng(SEED)
+        toks = rng.integers(1, 32000, size=rows * (seq + 1), dtype=np.uint32)
+        toks[rng.integers(0, toks.size, size=toks.size // 400)] = 0  # document separators
+        toks.tofile(path)
+        out["loader"] = {"batch": batch, "seq_len": seq}
+        for name, masked in (("plain", False), ("masked", True)):
+            l = ox.LitDataLoader(path, batch, seq, device=local_rank)
+            if masked:
+                l.with_target_mask(16000, [2]).with_document_mask(0)
+            for _ in range(5):
+                l.next_batch(stream.cuda_stream)
+            torch.cuda.synchronize()
+            n = 200
+            t = time.perf_counter()
+            for _ in range(n):
+                l.next_batch(stream.cuda_stream)
+            torch.cuda.synchronize()
+            dt = (time.perf_counter() - t) / n
+            out["loader"][name] = {"us_per_batch": dt * 1e6, "tokens_per_s": batch * seq / dt}
+            l.close()
+    return out
 
 
 def step_roofline(P: int, world: int, ms: float, hbm_gbs: float) -> dict:
@@ -363,6 +420,7 @@ def main():
     ap.add_argument("--sync", choices=["p2p", "copy", "nccl", "replicated"], default="p2p", help="how ranks meet at --gpus > 1")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--skip-e2e", action="store_true", help="profiling runs: leave the host-fed leg out")
+    ap.add_argument("--skip-aux", action="store_true", help="leave out the flatten and loader timings (1 GPU only)")
     ap.add_argument("--workload", default=WORKLOAD, help="parameter set; the headline is llama-3.2-1b, smaller sets serve profiler captures")
     args = ap.parse_args()
     if args.impl == "reference":

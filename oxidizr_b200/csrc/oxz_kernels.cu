@@ -684,47 +684,88 @@ __global__ void __launch_bounds__(THREADS, MINB)
 
 // ---------------------------------------------------------------- flatten
 
+// Each warp takes several tiles per round and walks them in phases (tile entries, then the per-tensor lookups, then
+// every data load, then the stores), so that the dependent lookups of one tile overlap those of the others and enough
+// bytes are in flight per SM to fill HBM. 16-bit vectors stay packed in registers; only an accumulation widens them.
 template <int DT>
-__global__ void __launch_bounds__(THREADS)
+__global__ void __launch_bounds__(THREADS, 3)
     k_flatten(void* __restrict__ flat, uint32_t n_tiles, const uint32_t* __restrict__ tile_meta,
               const uint64_t* __restrict__ offsets, const uint64_t* __restrict__ numel,
               const void* const* __restrict__ src, int accumulate) {
+    constexpr int ILP = DT == OXZ_F32 ? 2 : 4;
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-    const uint32_t per_iter = gridDim.x * WARPS;
-    for (uint32_t ft = blockIdx.x * WARPS + warp; ft < n_tiles; ft += per_iter) {
-        const uint32_t meta = tile_meta[ft];
-        const uint64_t fe = static_cast<uint64_t>(ft) * TILE + lane * 8;
-        float x[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
-        if (meta != PAD_TILE) {
-            const uint32_t t = meta & 0xffffffu;
-            const void* s = src[t];
-            if (s != nullptr) {
-                const uint64_t te = fe - offsets[t];  // element within the tensor
-                const uint64_t n = numel[t];
-                if (te + 8 <= n) {
-                    load8_user<DT>(s, te, x);
-                } else {
+    const uint32_t per_iter = gridDim.x * WARPS * ILP;
+    for (uint32_t base = (blockIdx.x * WARPS + warp) * ILP; base < n_tiles; base += per_iter) {
+        uint32_t meta[ILP];
 #pragma unroll
-                    for (int i = 0; i < 8; i++) {
-                        if (te + i < n) {
-                            if constexpr (DT == OXZ_F32) x[i] = static_cast<const float*>(s)[te + i];
-                            else if constexpr (DT == OXZ_BF16)
-                                x[i] = __uint_as_float(static_cast<uint32_t>(static_cast<const uint16_t*>(s)[te + i]) << 16);
-                            else x[i] = __half2float(static_cast<const __half*>(s)[te + i]);
-                        }
-                    }
-                }
-                if (accumulate) {
-                    float old[8];
-                    load8<DT>(flat, fe, old);
+        for (int j = 0; j < ILP; j++) meta[j] = base + j < n_tiles ? tile_meta[base + j] : PAD_TILE;
+        const void* s[ILP];
+        uint64_t te[ILP], n[ILP];  // element within the tensor, the tensor's length
 #pragma unroll
-                    for (int i = 0; i < 8; i++) x[i] = __fadd_rn(old[i], x[i]);
-                }
-            } else if (accumulate) {
-                continue;  // nothing to add
+        for (int j = 0; j < ILP; j++) {
+            s[j] = nullptr;
+            te[j] = n[j] = 0;
+            if (meta[j] != PAD_TILE) {
+                const uint32_t t = meta[j] & 0xffffffu;
+                s[j] = src[t];
+                te[j] = static_cast<uint64_t>(base + j) * TILE + lane * 8 - offsets[t];
+                n[j] = numel[t];
             }
         }
-        store8<DT>(flat, fe, x);
+        RawVec<DT> x[ILP], old[ILP];
+#pragma unroll
+        for (int j = 0; j < ILP; j++) {
+            if constexpr (DT == OXZ_F32) {
+#pragma unroll
+                for (int i = 0; i < 8; i++) x[j].x[i] = 0.f;
+            } else {
+                x[j].v = make_uint4(0u, 0u, 0u, 0u);
+            }
+            if (s[j] != nullptr && te[j] + 8 <= n[j]) {
+                // the caller's memory is promised 16-byte aligned only
+                if constexpr (DT == OXZ_F32) load8_user<OXZ_F32>(s[j], te[j], x[j].x);
+                else x[j].v = ld_stream(reinterpret_cast<const uint4*>(static_cast<const uint16_t*>(s[j]) + te[j]));
+            }
+        }
+        if (accumulate) {
+#pragma unroll
+            for (int j = 0; j < ILP; j++)
+                if (s[j] != nullptr) load_raw<DT>(flat, static_cast<uint64_t>(base + j) * TILE + lane * 8, old[j]);
+        }
+#pragma unroll
+        for (int j = 0; j < ILP; j++) {
+            if (base + j >= n_tiles) continue;
+            const uint64_t fe = static_cast<uint64_t>(base + j) * TILE + lane * 8;
+            const bool ragged = s[j] != nullptr && te[j] + 8 > n[j];  // the tensor ends inside this vector
+            if (!ragged && !(accumulate && s[j] != nullptr)) {
+                if (accumulate && s[j] == nullptr && meta[j] != PAD_TILE) continue;  // nothing to add
+                // a plain copy (or zeros for padding and for a tensor without a gradient)
+                if constexpr (DT == OXZ_F32) store8<OXZ_F32>(flat, fe, x[j].x);
+                else st_stream(reinterpret_cast<uint4*>(static_cast<uint16_t*>(flat) + fe), x[j].v);
+                continue;
+            }
+            float f[8];
+            widen_raw<DT>(x[j], f);
+            if (ragged) {
+#pragma unroll
+                for (int i = 0; i < 8; i++) {
+                    f[i] = 0.f;
+                    if (te[j] + i < n[j]) {
+                        if constexpr (DT == OXZ_F32) f[i] = static_cast<const float*>(s[j])[te[j] + i];
+                        else if constexpr (DT == OXZ_BF16)
+                            f[i] = __uint_as_float(static_cast<uint32_t>(static_cast<const uint16_t*>(s[j])[te[j] + i]) << 16);
+                        else f[i] = __half2float(static_cast<const __half*>(s[j])[te[j] + i]);
+                    }
+                }
+            }
+            if (accumulate) {
+                float o[8];
+                widen_raw<DT>(old[j], o);
+#pragma unroll
+                for (int i = 0; i < 8; i++) f[i] = __fadd_rn(o[i], f[i]);
+            }
+            store8<DT>(flat, fe, f);
+        }
     }
 }
 
@@ -1023,7 +1064,7 @@ int32_t launch_adamw(cudaStream_t s, const LaunchGeom& g, const void* gsrc, int3
 int32_t launch_flatten(cudaStream_t s, const LaunchGeom& g, void* flat, int32_t dt, uint32_t n_tiles,
                        const uint32_t* tile_meta, const uint64_t* d_offsets, const uint64_t* d_numel,
                        const void* const* d_src, int32_t accumulate) {
-    dim3 grid(g.sm_count * 4), block(THREADS);
+    dim3 grid(g.sm_count * 3), block(THREADS);
     switch (dt) {
         case OXZ_F32: k_flatten<OXZ_F32><<<grid, block, 0, s>>>(flat, n_tiles, tile_meta, d_offsets, d_numel, d_src, accumulate); break;
         case OXZ_BF16: k_flatten<OXZ_BF16><<<grid, block, 0, s>>>(flat, n_tiles, tile_meta, d_offsets, d_numel, d_src, accumulate); break;
