@@ -222,28 +222,42 @@ int32_t oxz_optimizer_save(oxz_plan* p, oxz_comm* comm, const char* path, const 
 
     std::string tmp = std::string(path) + ".tmp";
     FILE* f = nullptr;
+    // A file error on the writing rank must not leave the other ranks waiting in the gathers below: the writer
+    // remembers it, keeps taking part in every collective, and reports it at the end.
+    int32_t io = OXZ_OK;
+    std::string io_text;
+    auto io_failed = [&]() {
+        if (io == OXZ_OK) {
+            io = io_fail(path, "write failed", next);
+            io_text = oxz_last_error();
+        }
+        if (f) { fclose(f); f = nullptr; }
+    };
     if (writer) {
         f = fopen(tmp.c_str(), "wb");
-        if (!f) return io_fail(path, "write failed", next);
         const uint64_t hl = header.size();
-        if (fwrite(&hl, 8, 1, f) != 1 || fwrite(header.data(), 1, hl, f) != hl) { fclose(f); remove(tmp.c_str()); return io_fail(path, "write failed", next); }
+        if (!f || fwrite(&hl, 8, 1, f) != 1 || fwrite(header.data(), 1, hl, f) != hl) io_failed();
     }
     std::vector<uint32_t> host;
     int32_t st = OXZ_OK;
     for (uint64_t i = 0; i < p->T && st == OXZ_OK; i++) {
         for (int k = 0; k < (has_master ? 3 : 2) && st == OXZ_OK; k++) {
             st = gather_tensor(p, comm, kinds[k], i, host);
-            if (st == OXZ_OK && writer && !host.empty() && fwrite(host.data(), 4, host.size(), f) != host.size())
-                st = io_fail(path, "write failed", next);
+            if (st == OXZ_OK && f && !host.empty() && fwrite(host.data(), 4, host.size(), f) != host.size()) io_failed();
         }
     }
     if (writer) {
         const double step = (double)p->timestep;
-        if (st == OXZ_OK && fwrite(&step, 8, 1, f) != 1) st = io_fail(path, "write failed", next);
-        if (fclose(f) != 0 && st == OXZ_OK) st = io_fail(path, "write failed", next);
+        if (st == OXZ_OK && f && fwrite(&step, 8, 1, f) != 1) io_failed();
+        if (f && fclose(f) != 0) { f = nullptr; io_failed(); }
+        f = nullptr;
         // atomic: an error leaves an existing file unchanged (optimizer_io.rs:62-64)
-        if (st == OXZ_OK && rename(tmp.c_str(), path) != 0) st = io_fail(path, "write failed", next);
-        if (st != OXZ_OK) remove(tmp.c_str());
+        if (st == OXZ_OK && io == OXZ_OK && rename(tmp.c_str(), path) != 0) io_failed();
+        if (st != OXZ_OK || io != OXZ_OK) remove(tmp.c_str());
+        if (st == OXZ_OK && io != OXZ_OK) {
+            oxz_set_last_error(io_text.c_str());
+            st = io;
+        }
     }
     return st;
 }

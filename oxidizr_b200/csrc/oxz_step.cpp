@@ -647,10 +647,10 @@ int32_t oxz_step_async(oxz_plan* p, oxz_comm* comm, const oxz_hyper* h, const ui
         // every rank's copies into this rank's weight buffer must have landed before the step is reported done
         OXZ_TRY(comm_stream_barrier(comm, bar, s));
     } else {
-    // p->peers lists the communicator's ranks; a full replica writes only its own weights
-    OXZ_TRY(launch_adamw(s, p->geom, gsrc, gsrc_dt, p->master, p->exp_avg, p->exp_avg_sq, replicated ? p->own_work : p->peers,
-                         n_work, p->pdt, map, p->d_tile_meta, p->d_present, some_absent, p->d_scalars, ap));
-    OXZ_CUDA(mark(4));
+        // p->peers lists the communicator's ranks; a full replica writes only its own weights
+        OXZ_TRY(launch_adamw(s, p->geom, gsrc, gsrc_dt, p->master, p->exp_avg, p->exp_avg_sq, replicated ? p->own_work : p->peers,
+                             n_work, p->pdt, map, p->d_tile_meta, p->d_present, some_absent, p->d_scalars, ap));
+        OXZ_CUDA(mark(4));
     }
     if (p->mode == OXZ_SYNC_NCCL) {
         const size_t ps = dtype_size(p->pdt);
