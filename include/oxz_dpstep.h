@@ -343,7 +343,9 @@ int32_t oxz_rows_next_window(const oxz_row_layout* layout, oxz_data_position pos
 typedef struct oxz_resume_meta {
     uint64_t step;
     int32_t has_world_size, has_global_batch_rows, has_loss_scale, has_data_position, has_spike_guard;
-    int32_t has_weight_decay_rule;
+    int32_t has_weight_decay_rule, has_mixture;
+    uint32_t n_mixture_weights;      /* MixtureRecord::weights (src/data/mixture/record.rs:13-19): fetch with oxz_meta_mixture_weights */
+    uint64_t mixture_rows_per_epoch;
     int32_t weight_decay_rule;      /* oxz_decay_rule; a meta without the key reads as OXZ_DECAY_ALL, the rule of runs
                                        from before parameter groups (WeightDecaySpec::of_meta, src/weight_decay/rule.rs:68-74) */
     uint32_t n_no_decay_patterns;   /* fetch each with oxz_meta_no_decay_pattern */
@@ -359,7 +361,14 @@ int32_t oxz_meta_load(const char* path, oxz_resume_meta* out);
 int32_t oxz_meta_no_decay_pattern(const char* path, uint32_t index, char* buf, uint64_t cap);
 /* CheckpointMeta::save_to (src/config.rs:1386-1394): pretty JSON, written beside the target and renamed over it.
  * Floats are printed so that they read back to the same bits. */
-int32_t oxz_meta_save(const char* path, const oxz_resume_meta* meta, const char* const* no_decay_patterns);
+int32_t oxz_meta_save(const char* path, const oxz_resume_meta* meta, const char* const* no_decay_patterns,
+                      const double* mixture_weights);
+int32_t oxz_meta_mixture_weights(const char* path, double* weights, uint32_t cap, uint32_t* n_weights);
+/* check_mixture_resume (src/data/mixture/record.rs:40-70): the weights (compared by bits) and rows_per_epoch decide the
+ * row at every slot, so a resume must run the mixture the meta records; a meta without one resumes only a run without
+ * weights. has_current 0: this run sets no weights. Nothing is checked at step 0 or without a meta. */
+int32_t oxz_check_mixture_resume(const char* meta_path, uint64_t start_step, int32_t has_current, const double* weights,
+                                 uint32_t n_weights, uint64_t rows_per_epoch);
 /* check_resume_world (src/dp/resume.rs:19-55): a meta that records another world size is an error naming both (a
  * meta without the key counts as one rank); another global batch only fills `warning` (empty otherwise). A run at
  * step 0 and a null meta_path check nothing. */
@@ -385,6 +394,22 @@ int32_t oxz_loader_open_files(const char* const* paths, uint32_t n_paths, uint64
                               oxz_loader** out);
 /* LitDataLoader::source_rows: whole rows of each source in order; *n_sources receives the count, rows up to cap of them. */
 int32_t oxz_loader_source_rows(const oxz_loader* loader, uint64_t* rows, uint32_t cap, uint32_t* n_sources);
+/* Draws the next batch's rows only: rows[rank_batch_size] receive the global rows this rank reads, and the position
+ * moves on as after a batch. Host only: what a dry run or a test of the row order needs. */
+int32_t oxz_loader_next_rows(oxz_loader* loader, uint64_t* rows);
+/* LitDataLoader::with_mixture (src/data/mixture/loader.rs:16-33) in stream order: one weight per source. An epoch is
+ * rows_per_epoch slots (has_rows_per_epoch 0: the sources' training rows); source i fills its largest-remainder quota of
+ * them (src/data/mixture/quota.rs:22-57), interleaved by smooth weighted round-robin, the same every epoch
+ * (src/data/mixture/schedule.rs:103-122), and its k-th draw of the run reads its training row k % n_i
+ * (src/data/mixture/draw.rs:44-62), so an upsampled source repeats each row once per pass and a seek is exact. The
+ * loader's layout then counts rows_per_epoch rows and the position returns to the start. The shuffled schedule needs
+ * rand 0.10.3's StdRng and is not offered. */
+int32_t oxz_loader_set_mixture(oxz_loader* loader, const double* weights, uint32_t n_weights, int32_t has_rows_per_epoch,
+                               uint64_t rows_per_epoch);
+typedef struct oxz_mixture_source { double weight; uint64_t rows_per_epoch, train_rows; } oxz_mixture_source; /* MixtureSource */
+int32_t oxz_loader_mixture_sources(const oxz_loader* loader, oxz_mixture_source* out, uint32_t cap, uint32_t* n_sources);
+/* quotas(weights, rows) by itself (pure, no loader). */
+int32_t oxz_mixture_quotas(const double* weights, uint32_t n_weights, uint64_t rows, uint64_t* quotas);
 int32_t oxz_loader_close(oxz_loader* loader);
 /* LitDataLoader::with_target_mask(TargetMask::PrefixLm{target_base, always_score}) (src/data/mask.rs:21-47): a position
  * scores iff its TARGET id is at least target_base or is listed in always_score. on = 0 turns the mask off.

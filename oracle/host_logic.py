@@ -355,6 +355,89 @@ def store_row(sources, width: int, global_row: int):
     raise IndexError(f"row {global_row} is past the {first} whole rows of this data")
 
 
+# ---------------------------------------------------------------- weighted mixture of sources, stream order
+def mixture_quotas(weights, rows: int):
+    """Rows of one epoch per source by largest remainder, lower index first on a tie (src/data/mixture/quota.rs:22-57)."""
+    total = sum(weights)
+    shares = [w / total * rows for w in weights]
+    counts = [min(int(math.floor(s)), rows) for s in shares]
+    order = sorted(range(len(weights)), key=lambda i: (-(shares[i] - math.floor(shares[i])), i))
+    assigned = sum(counts)
+    if assigned <= rows:
+        for k in range(rows - assigned):
+            counts[order[k % len(order)]] += 1
+    else:
+        excess, k = assigned - rows, 0
+        back = order[::-1]
+        while excess:
+            i = back[k % len(back)]
+            if counts[i] > 0:
+                counts[i] -= 1
+                excess -= 1
+            k += 1
+    return counts
+
+
+def mixture_round_robin(quotas):
+    """Smooth weighted round-robin over the quotas: the source of each slot of an epoch in stream order, the same
+    every epoch (src/data/mixture/schedule.rs:103-122)."""
+    total = sum(quotas)
+    credit = [0] * len(quotas)
+    out = []
+    for _ in range(total):
+        pick = 0
+        for i, q in enumerate(quotas):
+            credit[i] += q
+            if credit[i] > credit[pick]:
+                pick = i
+        credit[pick] -= total
+        out.append(pick)
+    return out
+
+
+class Mixture:
+    """A weighted mixture as a virtual row order, stream order (src/data/mixture/state.rs:33-178, draw.rs:44-62):
+    slot s of epoch e belongs to source i = schedule[s]; it is that source's draw e * quota_i + (slots of i before s),
+    and draw k of a source of n rows reads its row k % n."""
+
+    def __init__(self, weights, rows_per_epoch, source_rows: list):
+        if len(weights) != len(source_rows):
+            raise ValueError(f"trainer.data.sources sets {len(weights)} weight(s), and the loader reads "
+                             f"{len(source_rows)} source(s).")
+        for i, (w, rows) in enumerate(zip(weights, source_rows)):
+            if not (math.isfinite(w) and w > 0.0):
+                raise ValueError(f"trainer.data.sources[{i}].weight is {w}: a weight must be a finite number above 0.")
+            if rows is None or rows.len == 0:
+                raise ValueError(f"trainer.data.sources[{i}] holds no training rows, and its weight {w} asks for rows.")
+        total = sum(r.len for r in source_rows)
+        rows = rows_per_epoch if rows_per_epoch is not None else total
+        if rows == 0 or rows > (1 << 28):
+            raise ValueError(f"trainer.data.rows_per_epoch is {rows}: an epoch needs at least 1 row and at most "
+                             f"{1 << 28} rows")
+        self.rows_per_epoch = rows
+        self.quotas = mixture_quotas(weights, rows)
+        self.sources = source_rows
+        self.schedule = mixture_round_robin(self.quotas)
+
+    def global_row(self, epoch: int, slot: int) -> int:
+        source = self.schedule[slot]
+        before = sum(1 for s in self.schedule[:slot] if s == source)
+        draw = epoch * self.quotas[source] + before
+        return self.sources[source].global_row(draw % self.sources[source].len)
+
+
+def source_train_rows(source_rows, spans, total):
+    """The training rows of each source: the loader's ranges cut at the source's bounds (src/data/mixture/loader.rs:60-84).
+    None for a source without training rows."""
+    out, first = [], 0
+    for rows in source_rows:
+        end = first + rows
+        inside = [(max(a, first), min(b, end)) for a, b in spans if max(a, first) < min(b, end)]
+        out.append(RowRanges(inside, total) if inside else None)
+        first = end
+    return out
+
+
 # ---------------------------------------------------------------- loss mask and document segments of one window
 def build_target_mask(window, batch_size: int, seq_len: int, target_base: int, always_score=()):
     """TargetMask::PrefixLm over a raw [batch_size, seq_len + 1] window (src/data/mask.rs:36-47, 72-88): position

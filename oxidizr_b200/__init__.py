@@ -5,7 +5,7 @@ This package binds it with ctypes and mirrors the reference's host-side interfac
 """
 from ._ffi import BF16, F16, F32, SYNC_COPY, SYNC_NCCL, SYNC_P2P, SYNC_REPLICATED, SYNC_SINGLE, OxzError, lib  # noqa: F401
 from . import _ffi as ffi  # noqa: F401
-from .dpstep import (CheckpointMeta, Communicator, DataPosition, DecayPlan, DpOptimizer, GradScalerState, LitDataLoader, LitTrainerStep,  # noqa: F401
+from .dpstep import (CheckpointMeta, MixtureRecord, check_mixture_resume, Communicator, DataPosition, DecayPlan, DpOptimizer, GradScalerState, LitDataLoader, LitTrainerStep,  # noqa: F401
                      LossScaleConfig, LossScaler, LrPlan, RowLayout, SpikeGuard, SpikeGuardConfig, SpikeGuardState, StepConfig,
-                     TensorInfo, TrainerConfig, WeightDecaySpec, check_resume_world, compute_grad_norm,
+                     TensorInfo, TrainerConfig, WeightDecaySpec, check_resume_world, compute_grad_norm, mixture_quotas,
                      compute_grad_norm_static, read_loss_scale_state, run_ranks, step_weighting)

@@ -85,10 +85,15 @@ class DataPositionC(C.Structure):
 class ResumeMeta(C.Structure):
     _fields_ = [("step", C.c_uint64), ("has_world_size", C.c_int32), ("has_global_batch_rows", C.c_int32),
                 ("has_loss_scale", C.c_int32), ("has_data_position", C.c_int32), ("has_spike_guard", C.c_int32),
-                ("has_weight_decay_rule", C.c_int32), ("weight_decay_rule", C.c_int32), ("n_no_decay_patterns", C.c_uint32),
+                ("has_weight_decay_rule", C.c_int32), ("has_mixture", C.c_int32), ("n_mixture_weights", C.c_uint32),
+                ("mixture_rows_per_epoch", C.c_uint64), ("weight_decay_rule", C.c_int32), ("n_no_decay_patterns", C.c_uint32),
                 ("world_size", C.c_uint64), ("global_batch_rows", C.c_uint64), ("loss_scale", ScalerState),
                 ("data_position", DataPositionC), ("spike_guard", SpikeState), ("checkpoint_file", C.c_char * 512),
                 ("optimizer_file", C.c_char * 512)]
+
+
+class MixtureSource(C.Structure):
+    _fields_ = [("weight", C.c_double), ("rows_per_epoch", C.c_uint64), ("train_rows", C.c_uint64)]
 
 
 class BatchMasks(C.Structure):
@@ -157,12 +162,18 @@ SIGNATURES = {
     "oxz_loader_open_files": (C.c_int32, [C.POINTER(C.c_char_p), C.c_uint32, C.c_uint64, C.c_uint64, C.c_uint64, C.c_uint64,
                                           C.POINTER(C.c_uint64), C.c_uint32, C.c_int32, C.POINTER(vp)]),
     "oxz_loader_source_rows": (C.c_int32, [vp, C.POINTER(C.c_uint64), C.c_uint32, C.POINTER(C.c_uint32)]),
+    "oxz_loader_next_rows": (C.c_int32, [vp, C.POINTER(C.c_uint64)]),
+    "oxz_loader_set_mixture": (C.c_int32, [vp, C.POINTER(C.c_double), C.c_uint32, C.c_int32, C.c_uint64]),
+    "oxz_loader_mixture_sources": (C.c_int32, [vp, C.POINTER(MixtureSource), C.c_uint32, C.POINTER(C.c_uint32)]),
+    "oxz_mixture_quotas": (C.c_int32, [C.POINTER(C.c_double), C.c_uint32, C.c_uint64, C.POINTER(C.c_uint64)]),
     "oxz_loader_set_target_mask": (C.c_int32, [vp, C.c_int32, C.c_uint32, C.POINTER(C.c_uint32), C.c_uint32]),
     "oxz_loader_set_document_mask": (C.c_int32, [vp, C.c_int32, C.c_uint32]),
     "oxz_loader_batch_masks": (C.c_int32, [vp, C.POINTER(BatchMasks)]),
     "oxz_meta_load": (C.c_int32, [C.c_char_p, C.POINTER(ResumeMeta)]),
     "oxz_meta_no_decay_pattern": (C.c_int32, [C.c_char_p, C.c_uint32, C.c_char_p, C.c_uint64]),
-    "oxz_meta_save": (C.c_int32, [C.c_char_p, C.POINTER(ResumeMeta), C.POINTER(C.c_char_p)]),
+    "oxz_meta_save": (C.c_int32, [C.c_char_p, C.POINTER(ResumeMeta), C.POINTER(C.c_char_p), C.POINTER(C.c_double)]),
+    "oxz_meta_mixture_weights": (C.c_int32, [C.c_char_p, C.POINTER(C.c_double), C.c_uint32, C.POINTER(C.c_uint32)]),
+    "oxz_check_mixture_resume": (C.c_int32, [C.c_char_p, C.c_uint64, C.c_int32, C.POINTER(C.c_double), C.c_uint32, C.c_uint64]),
     "oxz_check_resume_world": (C.c_int32, [C.c_char_p, C.c_uint64, C.c_uint64, C.c_uint64, C.c_char_p, C.c_uint64]),
     "oxz_read_loss_scale_state": (C.c_int32, [C.c_char_p, C.c_uint64, C.POINTER(C.c_int32), C.POINTER(ScalerState)]),
     "oxz_rows_check": (C.c_int32, [C.POINTER(RowLayoutC)]),

@@ -188,6 +188,7 @@ class RowLayout {
 struct CheckpointMeta {
     oxz_resume_meta raw{};
     std::vector<std::string> no_decay_patterns;
+    std::vector<double> mixture_weights;  // with raw.mixture_rows_per_epoch: MixtureRecord
     static CheckpointMeta load(const std::string& path) {
         CheckpointMeta m;
         check(oxz_meta_load(path.c_str(), &m.raw));
@@ -196,13 +197,18 @@ struct CheckpointMeta {
             check(oxz_meta_no_decay_pattern(path.c_str(), i, buf, sizeof buf));
             m.no_decay_patterns.emplace_back(buf);
         }
+        m.mixture_weights.resize(m.raw.n_mixture_weights);
+        uint32_t n = 0;
+        check(oxz_meta_mixture_weights(path.c_str(), m.mixture_weights.data(), m.raw.n_mixture_weights, &n));
         return m;
     }
     void save_to(const std::string& path) {
         std::vector<const char*> p;
         for (const auto& s : no_decay_patterns) p.push_back(s.c_str());
         raw.n_no_decay_patterns = (uint32_t)p.size();
-        check(oxz_meta_save(path.c_str(), &raw, p.empty() ? nullptr : p.data()));
+        raw.has_mixture = mixture_weights.empty() ? raw.has_mixture : 1;
+        raw.n_mixture_weights = (uint32_t)mixture_weights.size();
+        check(oxz_meta_save(path.c_str(), &raw, p.empty() ? nullptr : p.data(), mixture_weights.empty() ? nullptr : mixture_weights.data()));
     }
 };
 // Returns the warning (empty: none); throws when the meta records another world size.

@@ -13,7 +13,9 @@
 #include <sys/stat.h>
 #include <unistd.h>
 
+#include <algorithm>
 #include <cerrno>
+#include <cmath>
 #include <cstring>
 
 #include "oxz_internal.h"
@@ -27,11 +29,61 @@ struct Part {
     uint64_t n_tokens = 0, rows = 0, first_row = 0;
 };
 
+// Ascending, disjoint global row ranges; row r of the set is the r-th row across them (src/data/row_ranges.rs).
+struct Ranges {
+    std::vector<uint64_t> start, end, before;
+    uint64_t len = 0;
+    void push(uint64_t a, uint64_t b) {
+        start.push_back(a);
+        end.push_back(b);
+        before.push_back(len);
+        len += b - a;
+    }
+    uint64_t global_row(uint64_t row) const {
+        size_t i = before.size();
+        while (i > 1 && before[i - 1] > row) i--;
+        return i ? start[i - 1] + (row - before[i - 1]) : row;
+    }
+};
+
+// A weighted mixture of the sources as a virtual row order, stream order (src/data/mixture/state.rs:1-8): an epoch is
+// rows_per_epoch slots; source i fills quota[i] of them in smooth weighted round-robin order, the same every epoch;
+// the p-th slot of source i in epoch e is its draw e * quota[i] + p, and draw k reads the source's row k % n_i.
+struct Mixture {
+    static constexpr uint64_t BLOCK = 4096;
+    std::vector<double> weights;
+    bool requested = false;  // rows_per_epoch was given rather than derived
+    uint64_t rows_per_epoch = 0;
+    std::vector<uint64_t> quotas;
+    std::vector<Ranges> sources;     // each source's training rows
+    std::vector<uint16_t> schedule;  // source of every slot
+    std::vector<uint32_t> prefix;    // per BLOCK slots: how many slots of each source came before
+    uint64_t cur_slot = 0;
+    std::vector<uint32_t> cur_counts;
+
+    // EpochSchedule::locate (src/data/mixture/schedule.rs:74-99): the slot's source and how many of its slots came before
+    bool locate(uint64_t slot, uint32_t* source, uint64_t* before_out) {
+        if (slot >= schedule.size()) return false;
+        const size_t width = quotas.size();
+        if (cur_counts.size() != width || cur_slot > slot || slot - cur_slot >= BLOCK) {
+            const uint64_t block = slot / BLOCK;
+            cur_slot = block * BLOCK;
+            cur_counts.assign(prefix.begin() + block * width, prefix.begin() + (block + 1) * width);
+        }
+        for (uint64_t i = cur_slot; i < slot; i++) cur_counts[schedule[i]]++;
+        *source = schedule[slot];
+        *before_out = cur_counts[*source];
+        cur_counts[*source]++;
+        cur_slot = slot + 1;
+        return true;
+    }
+};
+
 struct oxz_loader {
     std::vector<Part> parts;
+    std::unique_ptr<Mixture> mix;
     uint64_t total_rows = 0, seq_len = 0;
-    // ascending, disjoint, non-empty global row ranges; loader row r is the r-th row across them (src/data/row_ranges.rs)
-    std::vector<uint64_t> span_start, span_end, span_before;
+    Ranges ranges;  // the global rows this loader reads
     oxz_row_layout layout{};
     uint64_t rank = 0;
     oxz_data_position pos{0, 0};
@@ -220,11 +272,7 @@ void release(oxz_loader* l) {
 }
 
 // RowRanges::global_row (src/data/row_ranges.rs:100-106)
-uint64_t global_row(const oxz_loader* l, uint64_t row) {
-    size_t i = l->span_before.size();
-    while (i > 1 && l->span_before[i - 1] > row) i--;
-    return i ? l->span_start[i - 1] + (row - l->span_before[i - 1]) : row;
-}
+uint64_t global_row(const oxz_loader* l, uint64_t row) { return l->ranges.global_row(row); }
 
 // RowStore::row (src/data/source.rs:140-158): where global row r starts, or null past the last whole row.
 const uint32_t* row_tokens(const oxz_loader* l, uint64_t r) {
@@ -271,13 +319,8 @@ static int32_t open_parts(oxz_loader* l, const char* const* paths, uint32_t n_pa
 
 static int32_t finish_open(oxz_loader* l, uint64_t seq_len, uint64_t rank_batch_size, uint64_t rank, uint64_t world, int32_t device) {
     using namespace oxz;
-    uint64_t len = 0;
-    for (size_t i = 0; i < l->span_start.size(); i++) {
-        l->span_before.push_back(len);
-        len += l->span_end[i] - l->span_start[i];
-    }
     l->seq_len = seq_len;
-    l->layout = oxz_row_layout{len, rank_batch_size, world};
+    l->layout = oxz_row_layout{l->ranges.len, rank_batch_size, world};
     l->rank = rank;
     l->device = device;
     OXZ_TRY(oxz_rows_check(&l->layout));
@@ -301,8 +344,7 @@ int32_t oxz_loader_open(const char* path, uint64_t seq_len, uint64_t rank_batch_
                      (unsigned long long)end_row, (unsigned long long)l->total_rows);
     }
     if (s == OXZ_OK) {
-        l->span_start.push_back(first_row);
-        l->span_end.push_back(end_row);
+        l->ranges.push(first_row, end_row);
         s = finish_open(l, seq_len, rank_batch_size, rank, world, device);
     }
     if (s != OXZ_OK) {
@@ -323,10 +365,7 @@ int32_t oxz_loader_open_files(const char* const* paths, uint32_t n_paths, uint64
     int32_t s = open_parts(l, paths, n_paths, seq_len);
     const uint64_t total = l->total_rows;
     if (s == OXZ_OK && n_spans == 0) {  // RowRanges::whole
-        if (total) {
-            l->span_start.push_back(0);
-            l->span_end.push_back(total);
-        }
+        if (total) l->ranges.push(0, total);
     }
     // RowRanges::new (src/data/row_ranges.rs:40-76)
     uint64_t prev_end = 0;
@@ -339,8 +378,7 @@ int32_t oxz_loader_open_files(const char* const* paths, uint32_t n_paths, uint64
             s = fail(OXZ_ERR_DATA, "row range [%llu, %llu) starts before row %llu, the end of the range before it. Pass ranges in ascending order without overlap.",
                      (unsigned long long)a, (unsigned long long)b, (unsigned long long)prev_end);
         else {
-            l->span_start.push_back(a);
-            l->span_end.push_back(b);
+            l->ranges.push(a, b);
             prev_end = b;
         }
     }
@@ -350,6 +388,122 @@ int32_t oxz_loader_open_files(const char* const* paths, uint32_t n_paths, uint64
         return s;
     }
     *out = l;
+    return OXZ_OK;
+}
+
+// quotas (src/data/mixture/quota.rs:22-57): floor of each share, the rows left over one each by largest remainder,
+// lower index first on a tie; rounding error the other way takes rows back from the smallest remainders.
+static void mixture_quotas(const double* weights, uint32_t n, uint64_t rows, std::vector<uint64_t>& counts) {
+    double total = 0.0;
+    for (uint32_t i = 0; i < n; i++) total += weights[i];
+    std::vector<double> shares(n), rem(n);
+    counts.assign(n, 0);
+    uint64_t assigned = 0;
+    for (uint32_t i = 0; i < n; i++) {
+        shares[i] = weights[i] / total * (double)rows;
+        const double fl = std::floor(shares[i]);
+        rem[i] = shares[i] - fl;
+        counts[i] = fl >= (double)rows ? rows : (uint64_t)fl;
+        assigned += counts[i];
+    }
+    std::vector<uint32_t> order(n);
+    for (uint32_t i = 0; i < n; i++) order[i] = i;
+    std::stable_sort(order.begin(), order.end(), [&](uint32_t a, uint32_t b) { return rem[a] > rem[b]; });
+    if (assigned <= rows) {
+        for (uint64_t k = 0; k < rows - assigned; k++) counts[order[k % n]]++;
+    } else {
+        uint64_t excess = assigned - rows;
+        for (uint64_t k = 0; excess; k++) {
+            const uint32_t i = order[n - 1 - (k % n)];
+            if (counts[i] > 0) {
+                counts[i]--;
+                excess--;
+            }
+        }
+    }
+}
+
+int32_t oxz_mixture_quotas(const double* weights, uint32_t n_weights, uint64_t rows, uint64_t* quotas) {
+    if (!weights || !quotas || n_weights == 0) return fail(OXZ_ERR_INVALID, "oxz_mixture_quotas: null argument");
+    for (uint32_t i = 0; i < n_weights; i++)
+        if (!(std::isfinite(weights[i]) && weights[i] > 0.0))
+            return fail(OXZ_ERR_DATA, "trainer.data.sources[%u].weight is %g: a weight must be a finite number above 0. Set it to the source's share, for example 1.0.", i, weights[i]);
+    std::vector<uint64_t> q;
+    mixture_quotas(weights, n_weights, rows, q);
+    for (uint32_t i = 0; i < n_weights; i++) quotas[i] = q[i];
+    return OXZ_OK;
+}
+
+int32_t oxz_loader_set_mixture(oxz_loader* l, const double* weights, uint32_t n_weights, int32_t has_rows_per_epoch,
+                               uint64_t rows_per_epoch) {
+    if (!l || (n_weights && !weights)) return fail(OXZ_ERR_INVALID, "oxz_loader_set_mixture: null argument");
+    const uint64_t MAX_ROWS = 1ull << 28;
+    if (n_weights != l->parts.size())
+        return fail(OXZ_ERR_DATA, "trainer.data.sources sets %u weight(s), and the loader reads %zu source(s). Set one weight per source in trainer.data.sources, and remove the -d flags.",
+                    n_weights, l->parts.size());
+    if (n_weights > 65536)
+        return fail(OXZ_ERR_DATA, "trainer.data.sources lists %u weighted sources, more than the 65536 a mixture can index. Merge some sources into one file.", n_weights);
+    std::unique_ptr<Mixture> m(new Mixture());
+    // the training rows of each source: the loader's ranges cut at the source's bounds (src/data/mixture/loader.rs:60-84)
+    for (uint32_t i = 0; i < n_weights; i++) {
+        const Part& part = l->parts[i];
+        Ranges r;
+        for (size_t k = 0; k < l->ranges.start.size(); k++) {
+            const uint64_t a = std::max(l->ranges.start[k], part.first_row), b = std::min(l->ranges.end[k], part.first_row + part.rows);
+            if (a < b) r.push(a, b);
+        }
+        if (!(std::isfinite(weights[i]) && weights[i] > 0.0))
+            return fail(OXZ_ERR_DATA, "trainer.data.sources[%u].weight is %g: a weight must be a finite number above 0. Set it to the source's share, for example 1.0.", i, weights[i]);
+        if (r.len == 0)
+            return fail(OXZ_ERR_DATA, "trainer.data.sources[%u] holds no training rows, and its weight %g asks for rows. Remove the source, or use a file of at least one row of model.max_seq_len + 1 tokens outside the holdout.", i, weights[i]);
+        if (r.len > 0xffffffffull)
+            return fail(OXZ_ERR_DATA, "trainer.data.sources[%u] holds %llu training rows, more than the 4294967295 a row order can index. Split the file.", i, (unsigned long long)r.len);
+        m->sources.push_back(std::move(r));
+    }
+    uint64_t total = 0;
+    for (const Ranges& r : m->sources) total += r.len;
+    const uint64_t rows = has_rows_per_epoch ? rows_per_epoch : total;
+    if (rows == 0 || rows > MAX_ROWS)
+        return fail(OXZ_ERR_DATA, "trainer.data.rows_per_epoch is %llu: an epoch needs at least 1 row and at most %llu rows, because the schedule keeps 2 bytes per row. Set trainer.data.rows_per_epoch inside that range.",
+                    (unsigned long long)rows, (unsigned long long)MAX_ROWS);
+    m->weights.assign(weights, weights + n_weights);
+    m->requested = has_rows_per_epoch != 0;
+    m->rows_per_epoch = rows;
+    mixture_quotas(weights, n_weights, rows, m->quotas);
+    // smooth weighted round-robin over the quotas (src/data/mixture/schedule.rs:103-122)
+    {
+        std::vector<int64_t> credit(n_weights, 0);
+        m->schedule.reserve(rows);
+        for (uint64_t k = 0; k < rows; k++) {
+            uint32_t pick = 0;
+            for (uint32_t i = 0; i < n_weights; i++) {
+                credit[i] += (int64_t)m->quotas[i];
+                if (credit[i] > credit[pick]) pick = i;
+            }
+            credit[pick] -= (int64_t)rows;
+            m->schedule.push_back((uint16_t)pick);
+        }
+        std::vector<uint32_t> counts(n_weights, 0);
+        for (uint64_t k = 0; k < rows; k++) {
+            if (k % Mixture::BLOCK == 0) m->prefix.insert(m->prefix.end(), counts.begin(), counts.end());
+            counts[m->schedule[k]]++;
+        }
+    }
+    // the layout counts rows per epoch; the position resets to the start (src/data/mixture/loader.rs:28-33)
+    oxz_row_layout layout = l->layout;
+    layout.num_rows = rows;
+    OXZ_TRY(oxz_rows_check(&layout));
+    l->layout = layout;
+    l->pos = oxz_data_position{0, 0};
+    l->mix = std::move(m);
+    return OXZ_OK;
+}
+
+int32_t oxz_loader_mixture_sources(const oxz_loader* l, oxz_mixture_source* out, uint32_t cap, uint32_t* n_sources) {
+    if (!l || !n_sources) return fail(OXZ_ERR_INVALID, "oxz_loader_mixture_sources: null argument");
+    *n_sources = l->mix ? (uint32_t)l->mix->weights.size() : 0;
+    for (uint32_t i = 0; out && i < cap && i < *n_sources; i++)
+        out[i] = oxz_mixture_source{l->mix->weights[i], l->mix->quotas[i], l->mix->sources[i].len};
     return OXZ_OK;
 }
 
@@ -389,6 +543,49 @@ int32_t oxz_loader_seek(oxz_loader* l, oxz_data_position pos) {
     return OXZ_OK;
 }
 
+// The global rows of this rank's part of the next global batch, where each starts in its file, and the position after
+// the batch. Does not move the loader.
+static int32_t draw_rows(oxz_loader* l, std::vector<uint64_t>& row_ids, std::vector<const uint32_t*>& src, oxz_data_position* next_out) {
+    using namespace oxz;
+    const uint64_t B = l->layout.rank_batch_size, S = l->seq_len;
+    oxz_data_position next;
+    OXZ_TRY(oxz_rows_next_window(&l->layout, l->pos, l->rank, S, 0, nullptr, 0, row_ids.data(), nullptr, nullptr, &next));
+    for (uint64_t b = 0; b < B; b++) {
+        if (l->mix) {
+            // the slot's source, that source's draw over the whole run, the draw's row (src/data/mixture/state.rs:150-178)
+            uint32_t source = 0;
+            uint64_t before = 0;
+            const uint64_t slot = row_ids[b];
+            if (!l->mix->locate(slot, &source, &before))
+                return fail(OXZ_ERR_DATA, "mixture slot %llu of epoch %llu is past the %llu rows of an epoch. This is a loader bug: report it with the data and config.",
+                            (unsigned long long)slot, (unsigned long long)next.epoch, (unsigned long long)l->mix->rows_per_epoch);
+            const Ranges& src_rows = l->mix->sources[source];
+            const unsigned __int128 draw = (unsigned __int128)next.epoch * l->mix->quotas[source] + before;
+            row_ids[b] = src_rows.global_row((uint64_t)(draw % src_rows.len));
+        } else {
+            row_ids[b] = global_row(l, row_ids[b]);  // loader row -> global row across the ranges
+        }
+        src[b] = row_tokens(l, row_ids[b]);
+        if (!src[b])
+            return fail(OXZ_ERR_DATA, "row %llu is past the %llu whole rows of this data. This is a loader bug: report it with the data and config.",
+                        (unsigned long long)row_ids[b], (unsigned long long)l->total_rows);
+    }
+    *next_out = next;
+    return OXZ_OK;
+}
+
+int32_t oxz_loader_next_rows(oxz_loader* l, uint64_t* rows) {
+    if (!l || !rows) return fail(OXZ_ERR_INVALID, "oxz_loader_next_rows: null argument");
+    const uint64_t B = l->layout.rank_batch_size;
+    std::vector<uint64_t> row_ids(B);
+    std::vector<const uint32_t*> src(B);
+    oxz_data_position next;
+    OXZ_TRY(draw_rows(l, row_ids, src, &next));
+    memcpy(rows, row_ids.data(), B * 8);
+    l->pos = next;
+    return OXZ_OK;
+}
+
 int32_t oxz_loader_next_batch_async(oxz_loader* l, void* stream, int64_t** inputs, int64_t** targets, uint64_t* rows) {
     if (!l || !inputs || !targets) return fail(OXZ_ERR_INVALID, "oxz_loader_next_batch_async: null argument");
     const uint64_t B = l->layout.rank_batch_size, S = l->seq_len, width = S + 1;
@@ -404,15 +601,8 @@ int32_t oxz_loader_next_batch_async(oxz_loader* l, void* stream, int64_t** input
     }
     oxz_data_position next;
     std::vector<uint64_t> row_ids(B);
-    OXZ_TRY(oxz_rows_next_window(&l->layout, l->pos, l->rank, S, 0, nullptr, 0, row_ids.data(), nullptr, nullptr, &next));
     std::vector<const uint32_t*> src(B);
-    for (uint64_t b = 0; b < B; b++) {
-        row_ids[b] = global_row(l, row_ids[b]);  // loader row -> global row across the ranges
-        src[b] = row_tokens(l, row_ids[b]);
-        if (!src[b])
-            return fail(OXZ_ERR_DATA, "row %llu is past the %llu whole rows of this data. This is a loader bug: report it with the data and config.",
-                        (unsigned long long)row_ids[b], (unsigned long long)l->total_rows);
-    }
+    OXZ_TRY(draw_rows(l, row_ids, src, &next));
     const int k = l->slot;
     // the pinned buffer of this slot may still feed the copy issued two batches ago
     OXZ_CUDA(cudaEventSynchronize(l->staged[k]));

@@ -146,6 +146,7 @@ struct Reader {
 struct Parsed {
     oxz_resume_meta m{};
     std::vector<std::string> patterns;
+    std::vector<double> mixture_weights;  // MixtureRecord::weights
 };
 
 int32_t rule_of(const std::string& s) {
@@ -217,6 +218,21 @@ bool parse_file(const char* path, Parsed* out, std::string* why) {
                 else r.skip();
             });
             m.has_spike_guard = 1;
+        } else if (key == "mixture") {
+            bool a = false, b = false;
+            r.object([&](const std::string& k) {
+                if (k == "weights") {
+                    if (!r.eat('[')) { r.ok = false; return; }
+                    if (!r.eat(']')) {
+                        do { double w = 0.0; r.f64(&w); out->mixture_weights.push_back(w); } while (r.ok && r.eat(','));
+                        if (!r.eat(']')) r.ok = false;
+                    }
+                    a = r.ok;
+                } else if (k == "rows_per_epoch") b = r.u64(&m.mixture_rows_per_epoch);
+                else r.skip();
+            });
+            if (r.ok && !(a && b)) { r.ok = false; *why = "mixture needs `weights` and `rows_per_epoch`"; }
+            m.has_mixture = 1;
         } else if (key == "optimizer_file") { copy(m.optimizer_file, sizeof m.optimizer_file, r.str()); }
         else if (key == "checkpoint_file") { copy(m.checkpoint_file, sizeof m.checkpoint_file, r.str()); }
         else r.skip();
@@ -229,6 +245,7 @@ bool parse_file(const char* path, Parsed* out, std::string* why) {
         return false;
     }
     m.n_no_decay_patterns = (uint32_t)out->patterns.size();
+    m.n_mixture_weights = (uint32_t)out->mixture_weights.size();
     return true;
 }
 
@@ -286,8 +303,21 @@ int32_t oxz_meta_no_decay_pattern(const char* path, uint32_t index, char* buf, u
     return OXZ_OK;
 }
 
-int32_t oxz_meta_save(const char* path, const oxz_resume_meta* m, const char* const* no_decay_patterns) {
-    if (!path || !m || (m->n_no_decay_patterns && !no_decay_patterns)) return fail(OXZ_ERR_INVALID, "oxz_meta_save: null argument");
+int32_t oxz_meta_mixture_weights(const char* path, double* weights, uint32_t cap, uint32_t* n_weights) {
+    if (!path || !n_weights) return fail(OXZ_ERR_INVALID, "oxz_meta_mixture_weights: null argument");
+    Parsed p;
+    std::string why;
+    if (!parse_file(path, &p, &why))
+        return fail(OXZ_ERR_INVALID, "checkpoint meta '%s' was not read: %s. Restore the file to resume from it.", path, why.c_str());
+    *n_weights = (uint32_t)p.mixture_weights.size();
+    for (uint32_t i = 0; weights && i < cap && i < *n_weights; i++) weights[i] = p.mixture_weights[i];
+    return OXZ_OK;
+}
+
+int32_t oxz_meta_save(const char* path, const oxz_resume_meta* m, const char* const* no_decay_patterns,
+                      const double* mixture_weights) {
+    if (!path || !m || (m->n_no_decay_patterns && !no_decay_patterns) || (m->has_mixture && m->n_mixture_weights && !mixture_weights))
+        return fail(OXZ_ERR_INVALID, "oxz_meta_save: null argument");
     if (m->has_weight_decay_rule && (m->weight_decay_rule < OXZ_DECAY_ALL || m->weight_decay_rule > OXZ_SKIP_ALL))
         return fail(OXZ_ERR_INVALID, "oxz_meta_save: unknown weight decay rule %d", m->weight_decay_rule);
     if (m->has_loss_scale && !(std::isfinite(m->loss_scale.scale) && m->loss_scale.scale > 0.0))
@@ -321,6 +351,11 @@ int32_t oxz_meta_save(const char* path, const oxz_resume_meta* m, const char* co
              f64_text(m->spike_guard.variance) + ",\n    \"observed\": " + std::to_string(m->spike_guard.observed) +
              ",\n    \"detected\": " + std::to_string(m->spike_guard.detected) + ",\n    \"skipped\": " +
              std::to_string(m->spike_guard.skipped) + "\n  }";
+    if (m->has_mixture) {
+        j += ",\n  \"mixture\": {\n    \"weights\": [";
+        for (uint32_t i = 0; i < m->n_mixture_weights; i++) j += std::string(i ? "," : "") + "\n      " + f64_text(mixture_weights[i]);
+        j += std::string(m->n_mixture_weights ? "\n    " : "") + "],\n    \"rows_per_epoch\": " + std::to_string(m->mixture_rows_per_epoch) + "\n  }";
+    }
     j += "\n}";
     // atomic like CheckpointMeta::save_to (src/config.rs:1386-1394): write beside, then rename
     const std::string tmp = std::string(path) + ".tmp";
@@ -357,6 +392,52 @@ int32_t oxz_check_resume_world(const char* meta_path, uint64_t start_step, uint6
                  "rows. The data stream resumes at the saved row, but the resume does not match an uninterrupted run.",
                  meta_path, (unsigned long long)p.m.global_batch_rows, (unsigned long long)global_batch_rows);
     return OXZ_OK;
+}
+
+// f64 the way Rust's `{}` prints it for the common cases: the shortest text that reads back, no trailing ".0"
+static std::string display_f64(double v) {
+    std::string t = f64_text(v);
+    if (t.size() > 2 && t.compare(t.size() - 2, 2, ".0") == 0) t.resize(t.size() - 2);
+    return t;
+}
+static std::string debug_weights(const std::vector<double>& w) {  // `{:?}` of a Vec<f64>
+    std::string t = "[";
+    for (size_t i = 0; i < w.size(); i++) t += (i ? ", " : "") + f64_text(w[i]);
+    return t + "]";
+}
+
+int32_t oxz_check_mixture_resume(const char* meta_path, uint64_t start_step, int32_t has_current, const double* weights,
+                                 uint32_t n_weights, uint64_t rows_per_epoch) {
+    if (has_current && n_weights && !weights) return fail(OXZ_ERR_INVALID, "oxz_check_mixture_resume: null argument");
+    if (!meta_path || start_step == 0) return OXZ_OK;
+    Parsed p;
+    std::string why;
+    if (!parse_file(meta_path, &p, &why))
+        return fail(OXZ_ERR_DATA, "checkpoint meta '%s' was not read: %s. Restore the file to resume with its data mixture.",
+                    meta_path, why.c_str());
+    const bool saved = p.m.has_mixture != 0;
+    const std::vector<double> current(weights, weights + (has_current ? n_weights : 0));
+    std::string reason;
+    if (!saved && !has_current) return OXZ_OK;
+    if (saved && !has_current)
+        reason = "the checkpoint trained on trainer.data.sources weights " + debug_weights(p.mixture_weights) + ", and this run sets no weights.";
+    else if (!saved && has_current)
+        reason = "the checkpoint trained without trainer.data.sources weights, and this run sets weights " + debug_weights(current) + ".";
+    else if (p.mixture_weights.size() != current.size())
+        reason = "the checkpoint trained on " + std::to_string(p.mixture_weights.size()) + " weighted trainer.data.sources, and this run sets " +
+                 std::to_string(current.size()) + ".";
+    else {
+        for (size_t i = 0; i < current.size() && reason.empty(); i++)
+            if (memcmp(&p.mixture_weights[i], &current[i], 8) != 0)  // compared by bits
+                reason = "trainer.data.sources[" + std::to_string(i) + "].weight was " + display_f64(p.mixture_weights[i]) +
+                         ", and this run sets " + display_f64(current[i]) + ".";
+        if (reason.empty() && p.m.mixture_rows_per_epoch != rows_per_epoch)
+            reason = "trainer.data.rows_per_epoch was " + std::to_string(p.m.mixture_rows_per_epoch) + ", and this run reads " +
+                     std::to_string(rows_per_epoch) + " rows per epoch.";
+    }
+    if (reason.empty()) return OXZ_OK;
+    return fail(OXZ_ERR_DATA, "checkpoint meta '%s': %s The mixture decides which rows the saved data position counts. Resume with the original config, or start a fresh run.",
+                meta_path, reason.c_str());
 }
 
 int32_t oxz_read_loss_scale_state(const char* meta_path, uint64_t start_step, int32_t* has_state, oxz_scaler_state* state) {

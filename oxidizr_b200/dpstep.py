@@ -404,6 +404,29 @@ class LitDataLoader:
         check(lib().oxz_loader_next_batch_async(self._h, C.c_void_p(stream) if stream else None, C.byref(i), C.byref(t), rows))
         return i.value, t.value, list(rows)
 
+    def next_rows(self) -> list[int]:
+        """The global rows of the next batch, without touching the device; the position moves on as after a batch."""
+        rows = (C.c_uint64 * self.batch_size)()
+        check(lib().oxz_loader_next_rows(self._h, rows))
+        return list(rows)
+
+    def with_mixture(self, weights: list[float], rows_per_epoch: int | None = None) -> "LitDataLoader":
+        """src/data/mixture/loader.rs:16-33, stream order: one weight per source; the layout then counts rows_per_epoch
+        rows (default: the sources' training rows) and the position returns to the start."""
+        check(lib().oxz_loader_set_mixture(self._h, (C.c_double * max(len(weights), 1))(*weights), len(weights),
+                                           int(rows_per_epoch is not None), rows_per_epoch or 0))
+        return self
+
+    def mixture_sources(self) -> list[dict] | None:
+        n = C.c_uint32()
+        check(lib().oxz_loader_mixture_sources(self._h, None, 0, C.byref(n)))
+        if n.value == 0:
+            return None
+        out = (ffi.MixtureSource * n.value)()
+        check(lib().oxz_loader_mixture_sources(self._h, out, n.value, C.byref(n)))
+        return [dict(weight=s.weight, rows_per_epoch=s.rows_per_epoch, train_rows=s.train_rows,
+                     repeats=s.rows_per_epoch / max(s.train_rows, 1)) for s in out]
+
     def with_target_mask(self, target_base: int, always_score: list[int] = ()) -> "LitDataLoader":
         """TargetMask::PrefixLm (src/data/mask.rs:21-47): a position scores iff its target id is at least target_base
         or is one of always_score."""
@@ -443,6 +466,13 @@ class SpikeGuardState:
 
 
 @dataclass
+class MixtureRecord:
+    """What a checkpoint meta records of a weighted mixture (src/data/mixture/record.rs:13-19)."""
+    weights: list[float]
+    rows_per_epoch: int
+
+
+@dataclass
 class CheckpointMeta:
     """The keys of ``checkpoint_step_N.meta.json`` (CheckpointMeta, src/config.rs:1223-1302) that the optimizer path
     records and reads on resume (src/checkpoint_set/snapshot.rs:245-262). ``None`` is a key the file does not hold."""
@@ -456,6 +486,7 @@ class CheckpointMeta:
     world_size: int | None = None
     global_batch_rows: int | None = None
     spike_guard: SpikeGuardState | None = None
+    mixture: "MixtureRecord | None" = None
 
     def weight_decay_spec(self) -> WeightDecaySpec:
         """WeightDecaySpec::of_meta (src/weight_decay/rule.rs:68-74): a meta without the rule is a legacy run."""
@@ -482,7 +513,10 @@ class CheckpointMeta:
         n = len(self.no_decay_patterns)
         m.n_no_decay_patterns = n
         arr = (C.c_char_p * max(n, 1))(*[p.encode() for p in self.no_decay_patterns])
-        check(lib().oxz_meta_save(path.encode(), C.byref(m), arr))
+        weights = list(self.mixture.weights) if self.mixture is not None else []
+        if self.mixture is not None:
+            m.has_mixture, m.n_mixture_weights, m.mixture_rows_per_epoch = 1, len(weights), self.mixture.rows_per_epoch
+        check(lib().oxz_meta_save(path.encode(), C.byref(m), arr, (C.c_double * max(len(weights), 1))(*weights)))
 
     @classmethod
     def load(cls, path: str) -> "CheckpointMeta":
@@ -495,7 +529,13 @@ class CheckpointMeta:
             patterns.append(buf.value.decode())
         rules = {v: k for k, v in _RULES.items()}
         g = m.spike_guard
+        mixture = None
+        if m.has_mixture:
+            w, nw = (C.c_double * max(m.n_mixture_weights, 1))(), C.c_uint32()
+            check(lib().oxz_meta_mixture_weights(path.encode(), w, m.n_mixture_weights, C.byref(nw)))
+            mixture = MixtureRecord(list(w)[:nw.value], m.mixture_rows_per_epoch)
         return cls(
+            mixture=mixture,
             step=m.step, checkpoint_file=m.checkpoint_file.decode(), optimizer_file=m.optimizer_file.decode() or None,
             data_position=DataPosition(m.data_position.epoch, m.data_position.row) if m.has_data_position else None,
             weight_decay_rule=rules[m.weight_decay_rule] if m.has_weight_decay_rule else None, no_decay_patterns=patterns,
@@ -514,11 +554,25 @@ def check_resume_world(meta_path: str | None, start_step: int, world: int, globa
     return buf.value.decode() or None
 
 
+def check_mixture_resume(meta_path: str | None, start_step: int, current: MixtureRecord | None) -> None:
+    """src/data/mixture/record.rs:40-70: a resume must run the mixture the meta records."""
+    w = list(current.weights) if current is not None else []
+    check(lib().oxz_check_mixture_resume(meta_path.encode() if meta_path else None, start_step, int(current is not None),
+                                         (C.c_double * max(len(w), 1))(*w), len(w), current.rows_per_epoch if current else 0))
+
+
 def read_loss_scale_state(meta_path: str | None, start_step: int) -> GradScalerState | None:
     """src/loss_scale/resume.rs:14-29."""
     has, st = C.c_int32(), ffi.ScalerState()
     check(lib().oxz_read_loss_scale_state(meta_path.encode() if meta_path else None, start_step, C.byref(has), C.byref(st)))
     return GradScalerState(st.scale, st.consecutive_ok) if has.value else None
+
+
+def mixture_quotas(weights: list[float], rows: int) -> list[int]:
+    """src/data/mixture/quota.rs:22-57."""
+    out = (C.c_uint64 * len(weights))()
+    check(lib().oxz_mixture_quotas((C.c_double * len(weights))(*weights), len(weights), rows, out))
+    return list(out)
 
 
 def step_weighting(local_micro_batches: int, world: int, scored: int, masked_ranks: int):

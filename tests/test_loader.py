@@ -256,3 +256,131 @@ def read_i64(addr, count):
     from oxidizr_b200.interop import device_view
     torch.cuda.synchronize()
     return device_view(addr, count * 8, torch.int64, 0).cpu().tolist()
+
+
+# ---- weighted mixtures in stream order (host only: the row order needs no GPU)
+def mixed(tmp_path, rows, batch, **kw):
+    """Sources of rows[i] rows whose tokens are their own offsets in the concatenation (src/data/mixture/loader.rs:94-106)."""
+    width = SEQ + 1
+    first, paths = 0, []
+    for i, n in enumerate(rows):
+        paths.append(write_tokens(tmp_path, list(range(first, first + n * width)), f"mix{i}.bin"))
+        first += n * width
+    return ox.LitDataLoader.from_files(paths, batch, SEQ, **kw)
+
+
+def epoch_rows(loader, batches):
+    return [r for _ in range(batches) for r in loader.next_rows()]
+
+
+def test_mixture_quotas_follow_the_reference_cases():
+    # src/data/mixture/quota.rs:63-90
+    assert ox.mixture_quotas([3.0, 1.0], 100) == [75, 25] and ox.mixture_quotas([1.0, 1.0, 2.0], 8) == [2, 2, 4]
+    assert ox.mixture_quotas([1.0, 1.0, 1.0], 10) == [4, 3, 3] and ox.mixture_quotas([1.0, 1.0, 1.0], 11) == [4, 4, 3]
+    assert ox.mixture_quotas([1.0, 2.0, 3.0, 4.0], 12) == [1, 2, 4, 5] and ox.mixture_quotas([2.0, 2.0], 1) == [1, 0]
+    assert ox.mixture_quotas([0.25], 37) == [37]
+    rng = np.random.default_rng(3)
+    for _ in range(200):
+        w = [float(x) for x in rng.uniform(1e-3, 5.0, size=int(rng.integers(1, 7)))]
+        rows = int(rng.integers(1, 20000))
+        assert ox.mixture_quotas(w, rows) == hl.mixture_quotas(w, rows)
+    for bad in (0.0, -1.0, float("nan"), float("inf")):
+        with pytest.raises(ox.OxzError, match=r"trainer.data.sources\[2\].weight"):
+            ox.mixture_quotas([1.0, 1.0, bad], 10)
+
+
+def test_the_layout_counts_rows_per_epoch(tmp_path):
+    # src/data/mixture/loader.rs:108-122
+    l = mixed(tmp_path, [10, 4], 2).with_mixture([1.0, 1.0], 20)
+    assert l.num_rows() == 20
+    sources = l.mixture_sources()
+    assert sources[1]["rows_per_epoch"] == 10 and sources[1]["repeats"] == 2.5 and sources[1]["train_rows"] == 4
+    l.close()
+    plain = mixed(tmp_path, [3], 1)
+    assert plain.mixture_sources() is None
+    plain.close()
+
+
+def test_a_mixture_reads_only_the_row_ranges_and_fills_its_quotas(tmp_path):
+    # src/data/mixture/loader.rs:124-141: sources [0,8) and [8,14); train [0,6) and [8,12); quotas 3 and 7 of 10
+    l = mixed(tmp_path, [8, 6], 2, row_ranges=[(0, 6), (8, 12)]).with_mixture([1.0, 2.0])
+    assert l.num_rows() == 10
+    rows = epoch_rows(l, 15)
+    assert all(r < 6 or 8 <= r < 12 for r in rows)
+    assert sum(r < 6 for r in rows) == 9
+    l.close()
+
+
+def test_one_weighted_source_reads_what_the_plain_loader_reads(tmp_path):
+    # src/data/mixture/loader.rs:143-152, src/data/mixture/state.rs:268-283
+    plain, weighted = mixed(tmp_path, [12], 3), mixed(tmp_path, [12], 3).with_mixture([5.0])
+    assert epoch_rows(weighted, 16) == epoch_rows(plain, 16)
+    for l in (plain, weighted):
+        l.close()
+
+
+def test_an_upsampled_source_repeats_every_row_once_per_pass(tmp_path):
+    # src/data/mixture/state.rs:231-246 and draw.rs:130-137 in stream order
+    l = mixed(tmp_path, [3, 8], 1, row_ranges=[(0, 3), (3, 11)]).with_mixture([1.0, 1.0], 16)
+    rows = epoch_rows(l, 48)
+    small = [r for r in rows if r < 3]
+    assert len(small) == 24 and all(sorted(small[i:i + 3]) == [0, 1, 2] for i in range(0, 24, 3))
+    assert small[:7] == [0, 1, 2, 0, 1, 2, 0]
+    l.close()
+
+
+def test_a_seek_mid_epoch_continues_the_uninterrupted_rows(tmp_path):
+    # src/data/mixture/loader.rs:154-171
+    make = lambda: mixed(tmp_path, [9, 2], 3).with_mixture([1.0, 1.0], 12)  # noqa: E731
+    full = make()
+    epoch_rows(full, 5)
+    resumed = make()
+    resumed.seek(hl_advance(12, 3, 5))
+    assert epoch_rows(resumed, 9) == epoch_rows(full, 9)
+    for l in (full, resumed):
+        l.close()
+
+
+def hl_advance(num_rows, batch, batches):
+    p = hl.RowLayout(num_rows, batch).advance(hl.DataPosition(), batches)
+    return ox.DataPosition(p.epoch, p.row)
+
+
+@pytest.mark.parametrize("world", [1, 2])
+def test_mixture_rows_equal_the_checkers_for_every_rank(tmp_path, world):
+    rows, spans, weights, per_epoch, batch = [700, 3, 190, 40], [(0, 650), (700, 703), (710, 880)], [2.0, 1.0, 1.0], 9000, 5
+    loaders = [mixed(tmp_path, rows[:3], batch, rank=r, world_size=world, row_ranges=spans).with_mixture(weights, per_epoch)
+               for r in range(world)]
+    total = sum(rows[:3])
+    mix = hl.Mixture(weights, per_epoch, hl.source_train_rows(rows[:3], spans, total))
+    layout = hl.RowLayout(per_epoch, batch, world)
+    pos = hl.DataPosition()
+    # jump to the end of the first epoch, then cross into the second
+    skip = layout.batches_per_epoch() - 3
+    pos = layout.advance(pos, skip)
+    for l in loaders:
+        l.seek(ox.DataPosition(pos.epoch, pos.row))
+    for _ in range(8):
+        start = layout.batch_start(pos)
+        for r, l in enumerate(loaders):
+            slots = [start.row + r * batch + k for k in range(batch)]
+            assert l.next_rows() == [mix.global_row(start.epoch, s) for s in slots]
+        pos = hl.DataPosition(start.epoch, start.row + layout.batch_size())
+    for l in loaders:
+        l.close()
+
+
+def test_bad_mixtures_are_refused_naming_the_key(tmp_path):
+    # src/data/mixture/state.rs:285-316, 217-229
+    for weights, per_epoch, msg in [([1.0], None, r"1 weight\(s\), and the loader reads 2 source\(s\)"),
+                                    ([1.0, -2.0], None, r"trainer.data.sources\[1\].weight is -2"),
+                                    ([1.0, 1.0], 0, "trainer.data.rows_per_epoch is 0"),
+                                    ([1.0, 1.0], (1 << 28) + 1, str(1 << 28))]:
+        l = mixed(tmp_path, [4, 4], 1)
+        with pytest.raises(ox.OxzError, match=msg):
+            l.with_mixture(weights, per_epoch)
+        l.close()
+    l = mixed(tmp_path, [4, 4], 1, row_ranges=[(0, 4)])
+    with pytest.raises(ox.OxzError, match=r"trainer.data.sources\[1\] holds no training rows"):
+        l.with_mixture([1.0, 1.0])
+    l.close()

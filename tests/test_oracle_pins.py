@@ -416,3 +416,43 @@ def test_row_ranges_and_sources_known_answers():
                        ([(0, 5), (4, 6)], "starts before row 5")]:
         with pytest.raises(ValueError, match=msg):
             hl.RowRanges(spans, 10)
+
+
+def test_mixture_quotas_and_schedule_known_answers():
+    # src/data/mixture/quota.rs:63-90
+    assert hl.mixture_quotas([3.0, 1.0], 100) == [75, 25] and hl.mixture_quotas([1.0, 1.0, 2.0], 8) == [2, 2, 4]
+    for rows in (1, 7, 10, 99, 1000, 12345):
+        assert sum(hl.mixture_quotas([0.7, 0.2, 0.1, 1e-3], rows)) == rows
+    assert hl.mixture_quotas([1.0, 1.0, 1.0], 10) == [4, 3, 3] and hl.mixture_quotas([1.0, 1.0, 1.0], 11) == [4, 4, 3]
+    assert hl.mixture_quotas([1.0, 2.0, 3.0, 4.0], 12) == [1, 2, 4, 5] and hl.mixture_quotas([2.0, 2.0], 1) == [1, 0]
+    assert hl.mixture_quotas([0.25], 37) == [37]
+    # src/data/mixture/schedule.rs:160-180
+    assert hl.mixture_round_robin([2, 1]) == [0, 1, 0] and hl.mixture_round_robin([3, 1, 0]) == [0, 0, 1, 0]
+    sched = hl.mixture_round_robin([5000, 3, 4100, 1])
+    assert len(sched) == 9104 and [sched.count(i) for i in range(4)] == [5000, 3, 4100, 1]
+
+
+def test_mixture_rows_known_answers():
+    # src/data/mixture/state.rs:196-215: source 0 is rows [0, 10), source 1 rows [100, 104); quotas 3 and 7 of 10
+    m = hl.Mixture([1.0, 3.0], 10, [hl.RowRanges([(0, 10)], 1000), hl.RowRanges([(100, 104)], 1000)])
+    assert m.quotas == [3, 7]
+    for e in range(4):
+        rows = [m.global_row(e, s) for s in range(10)]
+        assert sum(r < 10 for r in rows) == 3 and sum(r >= 100 for r in rows) == 7
+    # src/data/mixture/draw.rs:130-137: stream order cycles through a source's rows
+    one = hl.Mixture([1.0], 7, [hl.RowRanges([(10, 13)], 100)])
+    assert [one.global_row(0, s) for s in range(7)] == [10, 11, 12, 10, 11, 12, 10]
+    assert [one.global_row(1, s) for s in range(3)] == [11, 12, 10]  # draws 7, 8, 9 continue the pass
+    # src/data/mixture/state.rs:268-283: one source of one pass per epoch reads the plain order
+    plain = hl.Mixture([0.3], None, [hl.RowRanges([(4, 24)], 1000)])
+    assert [plain.global_row(1, s) for s in range(20)] == list(range(4, 24))
+    # src/data/mixture/state.rs:285-316
+    two = [hl.RowRanges([(0, 4)], 1000), hl.RowRanges([(4, 8)], 1000)]
+    for args, msg in [(([1.0], None, two), "1 weight"), (([1.0, -2.0], None, two), r"sources\[1\].weight is -2"),
+                      (([1.0, 1.0], 0, two), "rows_per_epoch is 0"), (([1.0, 1.0], None, [two[0], None]), "holds no training rows")]:
+        with pytest.raises(ValueError, match=msg):
+            hl.Mixture(*args)
+    # src/data/mixture/loader.rs:60-84: ranges cut at the sources' bounds
+    parts = hl.source_train_rows([8, 6], [(0, 6), (8, 12)], 14)
+    assert [p.spans for p in parts] == [[(0, 6)], [(8, 12)]]
+    assert hl.source_train_rows([3, 2], [(0, 3)], 5)[1] is None

@@ -90,7 +90,7 @@ def test_every_key_survives_a_round_trip_with_floats_bit_for_bit(tmp_path):
     # and a document with keys in another order, nulls, and keys this path does not know still loads
     other = tmp_path / "other.meta.json"
     doc["holdout_rows"] = None
-    doc["mixture"] = {"weights": [0.5, 0.5], "names": ["a", "b"], "nested": {"x": [1, {"y": "\u00e9"}]}}
+    doc["data_sources"] = [{"weights": [0.5, 0.5], "names": ["a", "b"], "nested": {"x": [1, {"y": "\u00e9"}]}}]
     doc["loss_scale"] = None
     other.write_text(json.dumps(dict(reversed(list(doc.items())))))
     again = ox.CheckpointMeta.load(str(other))
@@ -113,3 +113,35 @@ def test_the_loss_scale_a_resume_reads(tmp_path):
         s.restore(ox.GradScalerState(math.nan, 0))
     with pytest.raises(ox.OxzError, match="finite and positive"):
         ox.CheckpointMeta(step=1, loss_scale=ox.GradScalerState(math.nan, 0)).save_to(str(tmp_path / "x.json"))
+
+
+def test_a_resume_must_run_the_mixture_the_meta_records(tmp_path):
+    # src/data/mixture/record.rs:132-187
+    saved = ox.MixtureRecord([2.0, 1.0], 12)
+    path = str(tmp_path / "checkpoint_step_3.meta.json")
+    ox.CheckpointMeta(step=3, checkpoint_file="w.safetensors", mixture=saved).save_to(path)
+    assert ox.CheckpointMeta.load(path).mixture == saved
+    ox.check_mixture_resume(path, 3, saved)
+    with pytest.raises(ox.OxzError) as e:
+        ox.check_mixture_resume(path, 3, None)
+    assert "checkpoint_step_3.meta.json" in str(e.value) and "sets no weights" in str(e.value)
+    assert "Resume with the original config, or start a fresh run." in str(e.value)
+    ox.check_mixture_resume(path, 0, None)       # step 0 starts fresh
+    ox.check_mixture_resume(None, 3, saved)      # no meta
+    a = ox.MixtureRecord([0.7, 0.3], 100)
+    pa = str(tmp_path / "a.meta.json")
+    ox.CheckpointMeta(step=3, mixture=a).save_to(pa)
+    plain = str(tmp_path / "plain.meta.json")
+    ox.CheckpointMeta(step=3).save_to(plain)
+    ox.check_mixture_resume(plain, 3, None)      # two plain runs match
+    for meta, current, msg in [(pa, ox.MixtureRecord([0.7, 0.4], 100), r"trainer.data.sources\[1\].weight was 0.3, and this run sets 0.4"),
+                               (pa, ox.MixtureRecord([0.7, 0.3], 90), "trainer.data.rows_per_epoch was 100, and this run reads 90"),
+                               (plain, a, r"trained without trainer.data.sources weights, and this run sets weights \[0.7, 0.3\]"),
+                               (pa, ox.MixtureRecord([1.0], 100), "2 weighted trainer.data.sources, and this run sets 1")]:
+        with pytest.raises(ox.OxzError, match=msg):
+            ox.check_mixture_resume(meta, 3, current)
+    # the weights are compared by bits: the nearest other double is another mixture
+    import math
+    ox.check_mixture_resume(pa, 3, ox.MixtureRecord([0.7, 0.3], 100))
+    with pytest.raises(ox.OxzError, match="weight was 0.3"):
+        ox.check_mixture_resume(pa, 3, ox.MixtureRecord([0.7, math.nextafter(0.3, 1.0)], 100))
