@@ -384,3 +384,19 @@ def test_bad_mixtures_are_refused_naming_the_key(tmp_path):
     with pytest.raises(ox.OxzError, match=r"trainer.data.sources\[1\] holds no training rows"):
         l.with_mixture([1.0, 1.0])
     l.close()
+
+
+@pytest.mark.gpu
+def test_mixture_batches_carry_the_tokens_of_the_rows_they_name(tmp_path):
+    """Every token of the mixed sources is its own offset in the concatenation, so a batch's inputs must be
+    row * width + s for the rows the loader names (src/data/positioning.rs tests' rows_of)."""
+    width = SEQ + 1
+    l = mixed(tmp_path, [9, 2, 5], 3, row_ranges=[(0, 8), (9, 16)]).with_mixture([1.0, 1.0, 2.0], 24)
+    twin = mixed(tmp_path, [9, 2, 5], 3, row_ranges=[(0, 8), (9, 16)]).with_mixture([1.0, 1.0, 2.0], 24)
+    for _ in range(20):
+        i, t, rows = l.next_batch()
+        assert rows == twin.next_rows()
+        assert read_i64(i, 3 * SEQ) == [r * width + s for r in rows for s in range(SEQ)]
+        assert read_i64(t, 3 * SEQ) == [r * width + s + 1 for r in rows for s in range(SEQ)]
+    l.close()
+    twin.close()
