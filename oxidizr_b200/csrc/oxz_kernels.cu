@@ -476,7 +476,7 @@ __device__ __forceinline__ bool mbar_wait_bounded(uint32_t bar, uint32_t parity,
 template <int DT, int WORLD, int STAGES>
 __global__ void __cluster_dims__(CLUSTER, 1, 1) __launch_bounds__(THREADS)
     k_pull_bulk(PeerTable peers, TileMap map, float inv_scale, float clamp_hi, int clamp_on, float* __restrict__ reduced,
-                double* __restrict__ partials, DevScalars* __restrict__ scalars) {
+                double* __restrict__ partials, DevScalars* __restrict__ scalars, uint32_t wait_limit) {
     static_assert(DT == OXZ_BF16 || DT == OXZ_F16, "16-bit gradients only");
     extern __shared__ __align__(128) unsigned char bulk_smem[];
     __shared__ __align__(8) uint64_t bar[STAGES];
@@ -500,20 +500,28 @@ __global__ void __cluster_dims__(CLUSTER, 1, 1) __launch_bounds__(THREADS)
                          ::"r"(smem_addr(bulk_smem + stage * STAGE_BYTES + r * BULK_BYTES)),
                            "l"(static_cast<const unsigned char*>(peers.grads[r]) + byte0), "r"(BULK_BYTES), "r"(b) : "memory");
     };
-    uint32_t issued = 0;  // chunks this block has issued so far (thread 0's count is the one used)
-    if (threadIdx.x == 0)
-        for (int s = 0; s < STAGES; s++) {
-            const uint32_t c = blockIdx.x + static_cast<uint32_t>(s) * gridDim.x;
-            if (c < n_chunks) { issue(c, s); issued++; }
+    // Every thread keeps the same books: which stages have copies in flight, and the phase each stage completes next.
+    uint32_t pending = 0, phase = 0;
+    for (int s = 0; s < STAGES; s++) {
+        const uint32_t c = blockIdx.x + static_cast<uint32_t>(s) * gridDim.x;
+        if (c < n_chunks) {
+            if (threadIdx.x == 0) issue(c, s);
+            pending |= 1u << s;
         }
+    }
     int stage = 0;
-    uint32_t parity = 0;
     bool ok = true;
     for (uint32_t c = blockIdx.x; c < n_chunks; c += gridDim.x) {
-        if (!mbar_wait_bounded(smem_addr(&bar[stage]), parity, BULK_SPIN_LIMIT)) {
+        // wait_limit is BULK_SPIN_LIMIT in production; a test lowers it to see the run-out path without any fault
+        // the verdict must be the block's, not the thread's: a thread that saw the copies land on its last poll must
+        // not go on to a barrier its neighbours never reach
+        const int landed = mbar_wait_bounded(smem_addr(&bar[stage]), (phase >> stage) & 1u, wait_limit) ? 1 : 0;
+        if (!__syncthreads_and(landed)) {
             ok = false;
             break;
         }
+        pending &= ~(1u << stage);
+        phase ^= 1u << stage;
         const unsigned char* st = bulk_smem + stage * STAGE_BYTES + warp * (TILE * 2) + lane * 16;
         float s8[8];
         {
@@ -535,17 +543,23 @@ __global__ void __cluster_dims__(CLUSTER, 1, 1) __launch_bounds__(THREADS)
         acc8(s8, inv_scale, clamp_hi, clamp_on != 0, a);
         __syncthreads();  // every warp has read this stage: it may be refilled
         const uint32_t nc = c + static_cast<uint32_t>(STAGES) * gridDim.x;
-        if (threadIdx.x == 0 && nc < n_chunks) { issue(nc, stage); issued++; }
-        if (++stage == STAGES) { stage = 0; parity ^= 1; }
+        if (nc < n_chunks) {
+            if (threadIdx.x == 0) issue(nc, stage);
+            pending |= 1u << stage;
+        }
+        if (++stage == STAGES) stage = 0;
     }
     if (!ok) {
         // A wait ran out: say so, then give the copies still in flight into this block's shared memory one more
-        // bounded chance to land before the block ends. The partial sums of this block are incomplete; the host
-        // reports the step as failed.
+        // bounded chance (the full limit) to land before the block ends, stage by stage. The partial sums of this
+        // block are incomplete; the host reports the step as failed.
         if (threadIdx.x == 0) atomicExch(&scalars->wait_expired, 1);
-        for (int s = 0; s < STAGES; s++) mbar_wait_bounded(smem_addr(&bar[s]), (s < stage) ? (parity ^ 1) : parity, BULK_SPIN_LIMIT);
+        for (int s = 0; s < STAGES; s++)
+            if (pending & (1u << s)) mbar_wait_bounded(smem_addr(&bar[s]), (phase >> s) & 1u, BULK_SPIN_LIMIT);
+        // This block's tiles were not summed. Poison the norm (a NaN seen), so that after the all-reduce every rank
+        // takes the step for an overflow and leaves its state untouched; this rank also reports the time-out.
+        a.flags |= FLAG_NAN;
     }
-    (void)issued;
     // the tiles past the last whole chunk (fewer than BULK_TILES, at the end of the last bucket's shard): plain loads
     const uint32_t tail0 = map.first_tile + n_chunks * BULK_TILES;
     if (blockIdx.x == gridDim.x - 1 && tail0 + warp < map.n_local_tiles) {
@@ -969,7 +983,11 @@ static int32_t launch_pull_bulk_t(cudaStream_t s, int blocks, const PeerTable& p
         resident[dev] = n * CLUSTER > 0 ? n * CLUSTER : CLUSTER;
     }
     if (blocks > resident[dev]) blocks = resident[dev];
-    k_pull_bulk<DT, WORLD, STAGES><<<dim3(blocks), dim3(THREADS), smem, s>>>(peers, map, inv_scale, clamp_hi, clamp_on, reduced, partials, scalars);
+    // OXZ_PULL_WAIT_LIMIT lowers the bound of the main-loop waits (0: the first wait gives up at once) so that a test can
+    // see the run-out path: the kernel records it, still collects its copies in flight and ends normally.
+    const char* lim = getenv("OXZ_PULL_WAIT_LIMIT");
+    const uint32_t wait_limit = lim ? static_cast<uint32_t>(strtoul(lim, nullptr, 10)) : BULK_SPIN_LIMIT;
+    k_pull_bulk<DT, WORLD, STAGES><<<dim3(blocks), dim3(THREADS), smem, s>>>(peers, map, inv_scale, clamp_hi, clamp_on, reduced, partials, scalars, wait_limit);
     return check_launch("k_pull_bulk");
 }
 

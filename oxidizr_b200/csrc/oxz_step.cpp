@@ -523,7 +523,6 @@ int32_t oxz_step_async(oxz_plan* p, oxz_comm* comm, const oxz_hyper* h, const ui
 
     auto mark = [&](int i) -> cudaError_t { return p->profile ? cudaEventRecord(p->ev[i], s) : cudaSuccess; };
     OXZ_CUDA(mark(0));
-    OXZ_CUDA(cudaMemsetAsync(&p->d_scalars->wait_expired, 0, sizeof(int32_t), s));
     if (p->mode == OXZ_SYNC_SINGLE || pulls) {
         // buckets already reduced during backward are skipped; the rest goes now, one launch per run of buckets
         uint32_t groups = p->early_groups;
@@ -611,6 +610,9 @@ int32_t oxz_step_async(oxz_plan* p, oxz_comm* comm, const oxz_hyper* h, const ui
     }
     OXZ_TRY(launch_finalize(s, p->d_acc, fp, p->d_scalars));
     OXZ_CUDA(cudaMemcpyAsync(p->h_scalars, p->d_scalars, sizeof(DevScalars), cudaMemcpyDeviceToHost, s));
+    // the pull kernels (also those of buckets reduced ahead of the next step) raise this flag; it was just copied out
+    // with the rest and starts the next step cleared
+    OXZ_CUDA(cudaMemsetAsync(&p->d_scalars->wait_expired, 0, sizeof(int32_t), s));
     if (p->cw > 1 && n_extras)
         OXZ_CUDA(cudaMemcpyAsync(p->h_acc, p->d_acc, (3 + n_extras) * 8, cudaMemcpyDeviceToHost, s));
 

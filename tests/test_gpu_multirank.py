@@ -200,6 +200,42 @@ def test_full_replicas_step_like_the_reference_and_agree_with_the_sharded_step(k
     shd.close()
 
 
+def test_a_pull_wait_that_runs_out_is_reported_and_changes_nothing(monkeypatch):
+    """The bulk-copy pull bounds every wait on its own copies. Here the bound of the main-loop waits is lowered to zero,
+    so the first wait gives up at once while the copies are in fact on their way: the kernel records the run-out,
+    collects its copies in flight and ends normally; every rank's step comes back as OXZ_ERR_TIMEOUT with optimizer
+    state and weights untouched (the norm is poisoned, so the update is skipped everywhere); the context stays usable
+    and the next step, with the bound restored, is the checker's step. No fault, trap or hang is involved."""
+    world = 2
+    g = Group(world, [0] * world, "local", seed=51)
+    before = [g.merged(k) for k in (ffi.STATE_MASTER, ffi.STATE_EXP_AVG, ffi.STATE_EXP_AVG_SQ)]
+    work_before = [g.opts[1].export_tensor(ffi.STATE_WORK, i) for i in range(len(g.numel))]
+    monkeypatch.setenv("OXZ_PULL_WAIT_LIMIT", "0")
+
+    def failing(r):
+        try:
+            g.opts[r].step(ox.StepConfig(max_grad_norm=1e9))
+            return None
+        except ox.OxzError as e:
+            return e
+    errors = list(g.pool.map(failing, range(world)))
+    assert all(e is not None and e.status == ffi.ERR_TIMEOUT and "bounded wait" in str(e) for e in errors), errors
+    assert {opt.last_pull_kernel() for opt in g.opts} == {2}
+    assert all(opt.timestep == 0 for opt in g.opts)
+    after = [g.merged(k) for k in (ffi.STATE_MASTER, ffi.STATE_EXP_AVG, ffi.STATE_EXP_AVG_SQ)]
+    for b, a in zip(before, after):
+        for x, y in zip(b, a):
+            assert np.array_equal(bits(x), bits(y))
+    for i, w in enumerate(work_before):
+        assert np.array_equal(bits(w), bits(g.opts[1].export_tensor(ffi.STATE_WORK, i)))
+    monkeypatch.delenv("OXZ_PULL_WAIT_LIMIT")
+    out, ref = g.step(ox.StepConfig(max_grad_norm=1e9))
+    for res, _ in out:
+        assert (res.overflow, res.applied, res.timestep) == (0, 1, 1) == (ref.overflow, ref.applied, ref.timestep)
+    g.assert_state(exact=True)
+    g.close()
+
+
 @pytest.mark.parametrize("mode", [ox.SYNC_P2P, ox.SYNC_COPY])
 @pytest.mark.parametrize("kind,world,devices", layouts())
 def test_sharded_step_with_clipping_and_absent_tensors(kind, world, devices, mode):
