@@ -394,6 +394,13 @@ int32_t oxz_loader_open_files(const char* const* paths, uint32_t n_paths, uint64
                               oxz_loader** out);
 /* LitDataLoader::source_rows: whole rows of each source in order; *n_sources receives the count, rows up to cap of them. */
 int32_t oxz_loader_source_rows(const oxz_loader* loader, uint64_t* rows, uint32_t cap, uint32_t* n_sources);
+/* PrefetchDataLoader::new(loader, depth) (src/data/prefetch.rs:37-115): a host thread draws the coming batches in order
+ * from the loader's position and copies their rows into pinned buffers (depth + 2 of them) while the device works on
+ * the current batch, so that oxz_loader_next_batch_async only has to enqueue the copy and the kernels. The batch
+ * sequence is the unprefetched loader's; a seek or a new mixture restarts the thread at the new position; an error
+ * the thread meets is returned by the call that reaches that batch. depth 0 turns it off. Needs the device (pinned
+ * memory). */
+int32_t oxz_loader_set_prefetch(oxz_loader* loader, uint32_t depth);
 /* Draws the next batch's rows only: rows[rank_batch_size] receive the global rows this rank reads, and the position
  * moves on as after a batch. Host only: what a dry run or a test of the row order needs. */
 int32_t oxz_loader_next_rows(oxz_loader* loader, uint64_t* rows);

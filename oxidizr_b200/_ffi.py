@@ -162,6 +162,7 @@ SIGNATURES = {
     "oxz_loader_open_files": (C.c_int32, [C.POINTER(C.c_char_p), C.c_uint32, C.c_uint64, C.c_uint64, C.c_uint64, C.c_uint64,
                                           C.POINTER(C.c_uint64), C.c_uint32, C.c_int32, C.POINTER(vp)]),
     "oxz_loader_source_rows": (C.c_int32, [vp, C.POINTER(C.c_uint64), C.c_uint32, C.POINTER(C.c_uint32)]),
+    "oxz_loader_set_prefetch": (C.c_int32, [vp, C.c_uint32]),
     "oxz_loader_next_rows": (C.c_int32, [vp, C.POINTER(C.c_uint64)]),
     "oxz_loader_set_mixture": (C.c_int32, [vp, C.POINTER(C.c_double), C.c_uint32, C.c_int32, C.c_uint64]),
     "oxz_loader_mixture_sources": (C.c_int32, [vp, C.POINTER(MixtureSource), C.c_uint32, C.POINTER(C.c_uint32)]),

@@ -16,7 +16,11 @@
 #include <algorithm>
 #include <cerrno>
 #include <cmath>
+#include <condition_variable>
 #include <cstring>
+#include <deque>
+#include <mutex>
+#include <thread>
 
 #include "oxz_internal.h"
 
@@ -79,9 +83,31 @@ struct Mixture {
     }
 };
 
+// A host thread that keeps the next batches' rows copied into pinned buffers while the device works on the current one
+// (PrefetchDataLoader, src/data/prefetch.rs:37-61): it draws batches in order from the loader's position, so the batch
+// sequence is the unprefetched loader's.
+struct Prefetch {
+    struct Slot {
+        uint32_t* host = nullptr;       // pinned, one batch of rows
+        cudaEvent_t copied = nullptr;   // the host-to-device copy that last read `host`
+        std::vector<uint64_t> rows;
+        oxz_data_position next{0, 0};
+        int32_t status = 0;
+        std::string error;
+    };
+    std::vector<Slot> slots;
+    std::deque<int> ready, idle;
+    std::mutex mu;
+    std::condition_variable cv;
+    bool stop = false;
+    std::thread worker;
+};
+
 struct oxz_loader {
     std::vector<Part> parts;
     std::unique_ptr<Mixture> mix;
+    std::unique_ptr<Prefetch> pre;
+    uint32_t prefetch_depth = 0;
     uint64_t total_rows = 0, seq_len = 0;
     Ranges ranges;  // the global rows this loader reads
     oxz_row_layout layout{};
@@ -248,8 +274,28 @@ __global__ void __launch_bounds__(256) k_fill_segments(const uint32_t* __restric
         cu[first + seen + 1] = static_cast<int32_t>((static_cast<uint64_t>(b) + 1) * seq_len);
 }
 
+void stop_prefetch(oxz_loader* l) {
+    if (!l->pre) return;
+    {
+        std::lock_guard<std::mutex> g(l->pre->mu);
+        l->pre->stop = true;
+    }
+    l->pre->cv.notify_all();
+    if (l->pre->worker.joinable()) l->pre->worker.join();
+    cudaSetDevice(l->device);
+    for (auto& slot : l->pre->slots) {
+        if (slot.copied) {
+            cudaEventSynchronize(slot.copied);
+            cudaEventDestroy(slot.copied);
+        }
+        if (slot.host) cudaFreeHost(slot.host);
+    }
+    l->pre.reset();
+}
+
 void release(oxz_loader* l) {
     if (!l) return;
+    stop_prefetch(l);
     if (l->d_stage[0] || l->h_stage[0]) cudaSetDevice(l->device);
     for (int i = 0; i < 2; i++) {
         if (l->h_stage[i]) cudaFreeHost(l->h_stage[i]);
@@ -288,6 +334,8 @@ using namespace oxz;
 extern "C" {
 
 // Maps the files in order. `what` words the errors of an unusable range for the one-file entry point.
+static int32_t start_prefetch(oxz_loader* l, uint32_t depth);
+
 static int32_t open_parts(oxz_loader* l, const char* const* paths, uint32_t n_paths, uint64_t seq_len) {
     using namespace oxz;
     if (n_paths == 0) return fail(OXZ_ERR_DATA, "no data files given. Pass -d <file.bin>, or set trainer.data.sources.");
@@ -493,10 +541,12 @@ int32_t oxz_loader_set_mixture(oxz_loader* l, const double* weights, uint32_t n_
     oxz_row_layout layout = l->layout;
     layout.num_rows = rows;
     OXZ_TRY(oxz_rows_check(&layout));
+    const uint32_t depth = l->pre ? l->prefetch_depth : 0;
+    stop_prefetch(l);
     l->layout = layout;
     l->pos = oxz_data_position{0, 0};
     l->mix = std::move(m);
-    return OXZ_OK;
+    return depth ? start_prefetch(l, depth) : (int32_t)OXZ_OK;
 }
 
 int32_t oxz_loader_mixture_sources(const oxz_loader* l, oxz_mixture_source* out, uint32_t cap, uint32_t* n_sources) {
@@ -539,17 +589,21 @@ int32_t oxz_loader_seek(oxz_loader* l, oxz_data_position pos) {
                     "different data or a different model.max_seq_len. Resume with the original data and config, or "
                     "start a fresh run.",
                     (unsigned long long)pos.epoch, (unsigned long long)pos.row, (unsigned long long)l->layout.num_rows);
+    // a prefetch thread has drawn ahead from the old position: it starts over from the new one
+    const uint32_t depth = l->pre ? l->prefetch_depth : 0;
+    stop_prefetch(l);
     l->pos = pos;
-    return OXZ_OK;
+    return depth ? start_prefetch(l, depth) : (int32_t)OXZ_OK;
 }
 
 // The global rows of this rank's part of the next global batch, where each starts in its file, and the position after
 // the batch. Does not move the loader.
-static int32_t draw_rows(oxz_loader* l, std::vector<uint64_t>& row_ids, std::vector<const uint32_t*>& src, oxz_data_position* next_out) {
+static int32_t draw_rows(oxz_loader* l, oxz_data_position from, std::vector<uint64_t>& row_ids, std::vector<const uint32_t*>& src,
+                         oxz_data_position* next_out) {
     using namespace oxz;
     const uint64_t B = l->layout.rank_batch_size, S = l->seq_len;
     oxz_data_position next;
-    OXZ_TRY(oxz_rows_next_window(&l->layout, l->pos, l->rank, S, 0, nullptr, 0, row_ids.data(), nullptr, nullptr, &next));
+    OXZ_TRY(oxz_rows_next_window(&l->layout, from, l->rank, S, 0, nullptr, 0, row_ids.data(), nullptr, nullptr, &next));
     for (uint64_t b = 0; b < B; b++) {
         if (l->mix) {
             // the slot's source, that source's draw over the whole run, the draw's row (src/data/mixture/state.rs:150-178)
@@ -574,13 +628,87 @@ static int32_t draw_rows(oxz_loader* l, std::vector<uint64_t>& row_ids, std::vec
     return OXZ_OK;
 }
 
+// a rank's slots are consecutive loader rows: runs that are also consecutive in one file move as one copy
+static void copy_rows(const oxz_loader* l, const std::vector<const uint32_t*>& src, uint32_t* dst) {
+    const uint64_t B = l->layout.rank_batch_size, width = l->seq_len + 1;
+    for (uint64_t b = 0; b < B;) {
+        uint64_t e = b + 1;
+        while (e < B && src[e] == src[e - 1] + width) e++;
+        memcpy(dst + b * width, src[b], (e - b) * width * 4);
+        b = e;
+    }
+}
+
+static void prefetch_loop(oxz_loader* l, oxz_data_position pos) {
+    Prefetch& q = *l->pre;
+    cudaSetDevice(l->device);
+    const uint64_t B = l->layout.rank_batch_size;
+    std::vector<const uint32_t*> src(B);
+    for (;;) {
+        int i;
+        {
+            std::unique_lock<std::mutex> g(q.mu);
+            q.cv.wait(g, [&] { return q.stop || !q.idle.empty(); });
+            if (q.stop) return;
+            i = q.idle.front();
+            q.idle.pop_front();
+        }
+        Prefetch::Slot& slot = q.slots[i];
+        cudaEventSynchronize(slot.copied);  // the copy that last read this buffer must be over
+        slot.rows.assign(B, 0);
+        slot.status = draw_rows(l, pos, slot.rows, src, &slot.next);
+        if (slot.status == OXZ_OK) {
+            copy_rows(l, src, slot.host);
+            pos = slot.next;
+        } else {
+            slot.error = oxz_last_error();  // the text crosses the thread boundary with the slot
+        }
+        const bool failed = slot.status != OXZ_OK;
+        {
+            std::lock_guard<std::mutex> g(q.mu);
+            q.ready.push_back(i);
+        }
+        q.cv.notify_all();
+        if (failed) return;
+    }
+}
+
+static int32_t start_prefetch(oxz_loader* l, uint32_t depth) {
+    using namespace oxz;
+    const uint64_t B = l->layout.rank_batch_size, width = l->seq_len + 1;
+    OXZ_CUDA(cudaSetDevice(l->device));
+    l->pre.reset(new Prefetch());
+    // `depth` batches kept ready, plus one being filled and one being copied to the device
+    l->pre->slots.resize(depth + 2);
+    for (size_t i = 0; i < l->pre->slots.size(); i++) {
+        cudaError_t e = cudaMallocHost((void**)&l->pre->slots[i].host, B * width * 4);
+        if (e == cudaSuccess) e = cudaEventCreateWithFlags(&l->pre->slots[i].copied, cudaEventDisableTiming);
+        if (e != cudaSuccess) {
+            stop_prefetch(l);
+            return fail(OXZ_ERR_CUDA, "oxz_loader_set_prefetch: %s", cudaGetErrorString(e));
+        }
+        l->pre->idle.push_back((int)i);
+    }
+    l->pre->worker = std::thread(prefetch_loop, l, l->pos);
+    return OXZ_OK;
+}
+
+int32_t oxz_loader_set_prefetch(oxz_loader* l, uint32_t depth) {
+    if (!l) return fail(OXZ_ERR_INVALID, "oxz_loader_set_prefetch: null loader");
+    if (depth > 64) return fail(OXZ_ERR_INVALID, "oxz_loader_set_prefetch: %u batches ahead, at most 64", depth);
+    stop_prefetch(l);
+    l->prefetch_depth = depth;
+    return depth ? start_prefetch(l, depth) : (int32_t)OXZ_OK;
+}
+
 int32_t oxz_loader_next_rows(oxz_loader* l, uint64_t* rows) {
     if (!l || !rows) return fail(OXZ_ERR_INVALID, "oxz_loader_next_rows: null argument");
+    if (l->pre) return fail(OXZ_ERR_STATE, "oxz_loader_next_rows: the prefetch thread draws this loader's rows. Turn prefetching off first");
     const uint64_t B = l->layout.rank_batch_size;
     std::vector<uint64_t> row_ids(B);
     std::vector<const uint32_t*> src(B);
     oxz_data_position next;
-    OXZ_TRY(draw_rows(l, row_ids, src, &next));
+    OXZ_TRY(draw_rows(l, l->pos, row_ids, src, &next));
     memcpy(rows, row_ids.data(), B * 8);
     l->pos = next;
     return OXZ_OK;
@@ -601,20 +729,43 @@ int32_t oxz_loader_next_batch_async(oxz_loader* l, void* stream, int64_t** input
     }
     oxz_data_position next;
     std::vector<uint64_t> row_ids(B);
-    std::vector<const uint32_t*> src(B);
-    OXZ_TRY(draw_rows(l, row_ids, src, &next));
     const int k = l->slot;
-    // the pinned buffer of this slot may still feed the copy issued two batches ago
-    OXZ_CUDA(cudaEventSynchronize(l->staged[k]));
-    // a rank's slots are consecutive loader rows: runs that are also consecutive in one file move as one copy
-    for (uint64_t b = 0; b < B;) {
-        uint64_t e = b + 1;
-        while (e < B && src[e] == src[e - 1] + width) e++;
-        memcpy(l->h_stage[k] + b * width, src[b], (e - b) * width * 4);
-        b = e;
-    }
     cudaStream_t s = (cudaStream_t)stream;
-    OXZ_CUDA(cudaMemcpyAsync(l->d_stage[k], l->h_stage[k], B * width * 4, cudaMemcpyHostToDevice, s));
+    // the pinned buffers of this slot (tokens in, counts out) may still be in use by the batch issued two batches ago
+    OXZ_CUDA(cudaEventSynchronize(l->staged[k]));
+    if (l->pre) {
+        // the worker has the rows in a pinned buffer already, or is about to
+        Prefetch& q = *l->pre;
+        int i;
+        {
+            std::unique_lock<std::mutex> g(q.mu);
+            q.cv.wait(g, [&] { return !q.ready.empty(); });
+            i = q.ready.front();
+            q.ready.pop_front();
+        }
+        Prefetch::Slot& slot = q.slots[i];
+        if (slot.status != OXZ_OK) {
+            const int32_t st = slot.status;
+            const std::string text = slot.error;
+            stop_prefetch(l);  // the worker has left; a seek or a new set_prefetch starts another
+            oxz_set_last_error(text.c_str());
+            return st;
+        }
+        row_ids = slot.rows;
+        next = slot.next;
+        OXZ_CUDA(cudaMemcpyAsync(l->d_stage[k], slot.host, B * width * 4, cudaMemcpyHostToDevice, s));
+        OXZ_CUDA(cudaEventRecord(slot.copied, s));
+        {
+            std::lock_guard<std::mutex> g(q.mu);
+            q.idle.push_back(i);
+        }
+        q.cv.notify_all();
+    } else {
+        std::vector<const uint32_t*> src(B);
+        OXZ_TRY(draw_rows(l, l->pos, row_ids, src, &next));
+        copy_rows(l, src, l->h_stage[k]);
+        OXZ_CUDA(cudaMemcpyAsync(l->d_stage[k], l->h_stage[k], B * width * 4, cudaMemcpyHostToDevice, s));
+    }
     const uint64_t n = B * S;
     const int blocks = (int)((n + 255) / 256 < 148 * 8 ? (n + 255) / 256 : 148 * 8);
     const bool masked = l->target_mask || l->document_mask;

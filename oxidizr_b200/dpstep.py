@@ -404,6 +404,12 @@ class LitDataLoader:
         check(lib().oxz_loader_next_batch_async(self._h, C.c_void_p(stream) if stream else None, C.byref(i), C.byref(t), rows))
         return i.value, t.value, list(rows)
 
+    def with_prefetch(self, depth: int = 2) -> "LitDataLoader":
+        """PrefetchDataLoader::new (src/data/prefetch.rs:86-115): a host thread keeps the coming batches' rows ready in
+        pinned memory; the batches are the unprefetched loader's."""
+        check(lib().oxz_loader_set_prefetch(self._h, depth))
+        return self
+
     def next_rows(self) -> list[int]:
         """The global rows of the next batch, without touching the device; the position moves on as after a batch."""
         rows = (C.c_uint64 * self.batch_size)()

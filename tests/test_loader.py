@@ -400,3 +400,53 @@ def test_mixture_batches_carry_the_tokens_of_the_rows_they_name(tmp_path):
         assert read_i64(t, 3 * SEQ) == [r * width + s + 1 for r in rows for s in range(SEQ)]
     l.close()
     twin.close()
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("depth", [1, 3])
+def test_the_prefetch_loader_yields_the_sync_loaders_batches(tmp_path, depth):
+    """src/data/prefetch.rs:350-390 and src/data/host_masks.rs:148-168: over several epochs, after a seek, with the
+    masks on and under a mixture, a loader with a prefetch thread hands out exactly the batches of one without."""
+    SEP = 0
+    width = SEQ + 1
+    rng = np.random.default_rng(11)
+    lens = [40 * width + 2, 23 * width]
+    paths = []
+    for i, n in enumerate(lens):
+        toks = rng.integers(1, 9, size=n, dtype=np.uint32)
+        toks[rng.integers(0, n, size=n // 7)] = SEP
+        paths.append(write_tokens(tmp_path, toks, f"p{i}.bin"))
+    make = lambda: (ox.LitDataLoader.from_files(paths, 2, SEQ, rank=1, world_size=2, row_ranges=[(0, 35), (40, 60)])  # noqa: E731
+                    .with_mixture([1.0, 2.0], 30).with_target_mask(4, [2]).with_document_mask(SEP))
+    sync, pre = make(), make().with_prefetch(depth)
+    start = hl_advance(30, 4, 3)
+    for l in (sync, pre):
+        l.seek(start)
+    with pytest.raises(ox.OxzError, match="prefetch thread draws"):
+        pre.next_rows()
+    for n in range(25):  # more than three epochs of 7 batches
+        a, b = draw_with_rows(sync, 2, SEQ), draw_with_rows(pre, 2, SEQ)
+        assert a == b, f"batch {n}"
+        assert sync.position() == pre.position()
+    # a seek in the middle restarts the thread at the new position
+    back = hl_advance(30, 4, 9)
+    for l in (sync, pre):
+        l.seek(back)
+    for n in range(5):
+        assert draw_with_rows(sync, 2, SEQ) == draw_with_rows(pre, 2, SEQ)
+    pre.with_prefetch(0)  # off again: the loader goes on from where it stands
+    assert draw_with_rows(sync, 2, SEQ) == draw_with_rows(pre, 2, SEQ)
+    for l in (sync, pre):
+        l.close()
+
+
+def draw_with_rows(loader, batch, seq):
+    import torch
+    from oxidizr_b200.interop import device_view
+    i, t, rows = loader.next_batch()
+    m = loader.batch_masks()
+    torch.cuda.synchronize()
+    n = batch * seq
+    view = lambda addr, dt, count: device_view(addr, count * torch.empty(0, dtype=dt).element_size(), dt, 0).cpu().tolist()  # noqa: E731
+    return (rows, view(i, torch.int64, n), view(t, torch.int64, n), view(m["loss_mask"], torch.float32, n), m["scored"](),
+            view(m["segment_ids"], torch.int32, n), view(m["cu_seqlens"], torch.int32, m["n_segments"]() + 1))
