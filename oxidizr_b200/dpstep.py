@@ -857,6 +857,73 @@ class LitTrainerStep:
     def loss_scale_state(self) -> GradScalerState | None:
         return self.loss_scaler.state() if self.loss_scaler else None
 
+    # -- the data-parallel hooks of src/dp/trainer_hooks.rs:36-107
+    def with_communicator(self, comm: "Communicator", row_layout: "RowLayout") -> "LitTrainerStep":
+        """Checks of LitTrainer::with_communicator: the rank is below the world size, and the world size is the row
+        layout's (the layout of a loader built with this rank and world, so that steps count global batches)."""
+        rank, world = comm.rank(), comm.world_size()
+        if rank >= world:
+            raise ValueError(f"communicator rank {rank} is not below its world size {world}. Pass a communicator of a valid group")
+        if world != row_layout.world_size:
+            raise ValueError(f"communicator world size {world} differs from the row layout's {row_layout.world_size}. Build "
+                             f"the loader with LitDataLoader::with_rank(rank, {world}) and take its row layout")
+        self.comm, self.row_layout = comm, row_layout
+        return self
+
+    def with_abort_hook(self, hook) -> "LitTrainerStep":
+        self.abort_hook = hook
+        return self
+
+    def world_size(self) -> int:
+        return self.optimizer.world
+
+    def rank(self) -> int:
+        return self.optimizer.rank
+
+    def quiet(self) -> bool:
+        """True on ranks other than 0: a quiet rank prints no diagnostic and writes no file."""
+        return self.rank() != 0
+
+    def abort_collectives(self) -> None:
+        """Does nothing in a world of 1 or without a hook; after an abort every later collective of the group fails."""
+        if self.world_size() > 1 and getattr(self, "abort_hook", None) is not None:
+            self.abort_hook()
+
+    def barrier(self) -> None:
+        if self.world_size() <= 1:
+            return
+        try:
+            self.optimizer.comm.barrier()
+        except OxzError as e:
+            raise OxzError(e.status, f"rank {self.rank()} barrier failed: {e.message}") from None
+
+    # -- resume (src/trainer.rs:883-897, src/loss_scale/scaler.rs:123-153)
+    def restore_loss_scale(self, saved: GradScalerState | None, start_step: int) -> str | None:
+        """Both present: the run continues from ``saved``. A scaler without a saved state past step 0, or a saved state
+        without a scaler: the returned warning says what was lost. A saved scale that is not finite and positive
+        raises."""
+        if self.loss_scaler is not None and saved is not None:
+            self.loss_scaler.restore(saved)
+            return None
+        if self.loss_scaler is not None and start_step > 0:
+            return (f"WARNING: the checkpoint records no loss scale state. The scale restarts at {self.loss_scaler.scale()}. "
+                    "Training continues, but it does not match an uninterrupted run.")
+        if saved is not None:
+            return (f"WARNING: the checkpoint records loss scale {saved.scale}, but this run does not train in f16. "
+                    "The loss scale state is dropped.")
+        return None
+
+    def checkpoint_meta(self, step: int, checkpoint_file: str, optimizer_file: str | None, decay: WeightDecaySpec,
+                        position: DataPosition | None = None, mixture: "MixtureRecord | None" = None) -> "CheckpointMeta":
+        """The keys this path contributes to a checkpoint's meta (src/checkpoint_set/snapshot.rs:245-262)."""
+        layout = getattr(self, "row_layout", None)
+        guard = SpikeGuardState(**self.spike_guard.state) if self.spike_guard is not None else None
+        return CheckpointMeta(step=step, checkpoint_file=checkpoint_file, optimizer_file=optimizer_file, data_position=position,
+                              weight_decay_rule=decay.rule, no_decay_patterns=list(decay.no_decay_patterns),
+                              loss_scale=self.loss_scale_state(), world_size=self.world_size(),
+                              global_batch_rows=layout.batch_size() if layout is not None else None, spike_guard=guard,
+                              mixture=mixture)
+
     def training_step(self, local_loss: float, present: list[bool] | None = None) -> tuple[float, float]:
         opt = self.optimizer
         judged = self.spike_guard is not None or self.loss_probe is not None

@@ -145,3 +145,38 @@ def test_a_resume_must_run_the_mixture_the_meta_records(tmp_path):
     ox.check_mixture_resume(pa, 3, ox.MixtureRecord([0.7, 0.3], 100))
     with pytest.raises(ox.OxzError, match="weight was 0.3"):
         ox.check_mixture_resume(pa, 3, ox.MixtureRecord([0.7, math.nextafter(0.3, 1.0)], 100))
+
+
+def test_trainer_hooks_check_the_group_and_describe_the_resume(tmp_path):
+    """src/dp/trainer_hooks.rs:36-107 and src/loss_scale/scaler.rs:123-153, 291-308 through the trainer-step mirror,
+    on a plan without device state (host only)."""
+    class Plan:  # what LitTrainerStep needs of an optimizer on the host
+        world, rank, timestep, comm = 2, 1, 0, None
+    comms = ox.Communicator.local_group(2, None, timeout=5.0)
+    cfg = ox.TrainerConfig(loss_scale=ox.LossScaleConfig(initial=65536.0), spike_guard=ox.SpikeGuardConfig())
+    step = ox.LitTrainerStep(cfg, Plan())
+    step.with_communicator(comms[1], ox.RowLayout(64, 4, 2))
+    assert (step.world_size(), step.rank(), step.quiet()) == (2, 1, True)
+    with pytest.raises(ValueError, match="communicator world size 2 differs from the row layout's 1"):
+        step.with_communicator(comms[1], ox.RowLayout(64, 4, 1))
+    hits = []
+    step.with_abort_hook(lambda: hits.append(1)).abort_collectives()
+    assert hits == [1]
+    # restore: both present continue; a scaler without a state past step 0 and a state without a scaler only warn
+    assert step.restore_loss_scale(ox.GradScalerState(512.0, 7), 3) is None
+    assert step.loss_scale_state() == ox.GradScalerState(512.0, 7)
+    with pytest.raises(ox.OxzError):
+        step.restore_loss_scale(ox.GradScalerState(float("nan"), 0), 3)
+    assert "restarts at 512" in step.restore_loss_scale(None, 3) and step.restore_loss_scale(None, 0) is None
+    plain = ox.LitTrainerStep(ox.TrainerConfig(), Plan())
+    assert "does not train in f16" in plain.restore_loss_scale(ox.GradScalerState(512.0, 7), 3)
+    # the keys the path contributes to a checkpoint's meta, and back
+    meta = step.checkpoint_meta(3, "checkpoint_step_3.safetensors", "checkpoint_step_3.optimizer.safetensors",
+                                ox.WeightDecaySpec("skip_1d", ["embed"]), ox.DataPosition(0, 24))
+    path = str(tmp_path / "checkpoint_step_3.meta.json")
+    meta.save_to(path)
+    back = ox.CheckpointMeta.load(path)
+    assert back == meta and back.world_size == 2 and back.global_batch_rows == 8 and back.loss_scale.scale == 512.0
+    assert ox.check_resume_world(path, 3, 2, 8) is None and ox.read_loss_scale_state(path, 3) == ox.GradScalerState(512.0, 7)
+    for c in comms:
+        c.destroy()
