@@ -192,6 +192,16 @@ int32_t oxz_optimizer_load(oxz_plan* plan, const char* path, const char* const* 
 int32_t oxz_grads_flatten_async(oxz_plan* plan, const void* const* grad_ptrs, int32_t accumulate);
 /* Host gradients of one tensor (grad_dtype; pinned memory copies asynchronously) into the flat buffer. */
 int32_t oxz_grads_upload_async(oxz_plan* plan, uint64_t tensor, const void* host);
+/* A second gradient buffer, so that a step's gradients can arrive from the host while the step before still reads its
+ * own: allocates it (and, with peers, maps it into every rank: collective for OXZ_SYNC_P2P / OXZ_SYNC_REPLICATED).
+ * oxz_grads_upload_next_async copies one tensor into the buffer that is NOT current, on the plan's own upload stream,
+ * also while a step is in flight; it starts after the step that last read that buffer. oxz_grads_swap makes that
+ * buffer the current one (oxz_state_pointers then reports it): the next oxz_step_async or oxz_grads_ready_async waits
+ * for the uploads. With several ranks every rank swaps between the same two steps. No reference counterpart: the
+ * reference's gradients are produced on the device. */
+int32_t oxz_grads_double_buffer(oxz_plan* plan, oxz_comm* comm);
+int32_t oxz_grads_upload_next_async(oxz_plan* plan, uint64_t tensor, const void* host);
+int32_t oxz_grads_swap(oxz_plan* plan);
 
 /* ------------------------------------------------------------------ the step */
 

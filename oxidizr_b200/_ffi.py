@@ -139,6 +139,9 @@ SIGNATURES = {
     "oxz_optimizer_load": (C.c_int32, [vp, C.c_char_p, C.POINTER(C.c_char_p), C.POINTER(C.c_uint32), u64p]),
     "oxz_grads_flatten_async": (C.c_int32, [vp, C.POINTER(vp), C.c_int32]),
     "oxz_grads_upload_async": (C.c_int32, [vp, C.c_uint64, vp]),
+    "oxz_grads_double_buffer": (C.c_int32, [vp, vp]),
+    "oxz_grads_upload_next_async": (C.c_int32, [vp, C.c_uint64, C.c_void_p]),
+    "oxz_grads_swap": (C.c_int32, [vp]),
     "oxz_step_async": (C.c_int32, [vp, vp, C.POINTER(Hyper), u8p, f64p, C.c_uint32]),
     "oxz_grads_ready_async": (C.c_int32, [vp, vp, C.POINTER(Hyper), u8p, C.c_uint64, C.c_uint64, vp]),
     "oxz_step_wait": (C.c_int32, [vp, C.POINTER(StepResult)]),

@@ -188,6 +188,14 @@ struct oxz_plan {
     cudaEvent_t ev[6] = {nullptr, nullptr, nullptr, nullptr, nullptr, nullptr};
     oxz::PeerTable peers{};
     oxz::PeerTable own_work{};  // work[0] = this rank's weights, nothing else
+    // a second gradient buffer (oxz_grads_double_buffer): `grads` is the one the next step reads, `grads_alt` the one
+    // the host may fill meanwhile; oxz_grads_swap exchanges them (and the peers' addresses of them)
+    void* grads_alt = nullptr;
+    const void* peer_grads_alt[oxz::MAX_PEERS] = {};
+    cudaStream_t upload_stream = nullptr;
+    cudaEvent_t ev_uploaded = nullptr, ev_last_read[2] = {nullptr, nullptr};
+    int cur_grads = 0;          // which of the two buffers `grads` is
+    bool upload_pending = false;  // uploads into the current buffer that the next step must wait for
     std::vector<void*> ipc_opened;
     // OXZ_SYNC_COPY: staging for the peers' gradient slices, one copy stream per peer, pipeline events
     void* stage = nullptr;

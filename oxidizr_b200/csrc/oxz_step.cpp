@@ -6,6 +6,7 @@
 #include <cstdlib>
 #include <cstring>
 #include <map>
+#include <utility>
 #include <mutex>
 
 #include "oxz_internal.h"
@@ -77,6 +78,35 @@ int32_t exchange_peers(oxz_plan* p, oxz_comm* c) {
             p->ipc_opened.push_back(w);
             p->peers.grads[r] = g;
             p->peers.work[r] = w;
+        }
+    }
+    return OXZ_OK;
+}
+
+// The same rendezvous for the second gradient buffer alone.
+int32_t exchange_alt_grads(oxz_plan* p, oxz_comm* c) {
+    struct Blob {
+        uint64_t pid, ptr;
+        int32_t device, pad;
+        cudaIpcMemHandle_t handle;
+    };
+    Blob mine{};
+    mine.pid = (uint64_t)getpid();
+    mine.ptr = (uint64_t)p->grads_alt;
+    mine.device = p->device;
+    OXZ_CUDA(cudaIpcGetMemHandle(&mine.handle, p->grads_alt));
+    std::vector<Blob> all(p->cw);
+    OXZ_TRY(comm_allgather_host(c, &mine, all.data(), sizeof(Blob), p->stream));
+    for (int r = 0; r < p->cw; r++) {
+        if (r == p->cr) {
+            p->peer_grads_alt[r] = p->grads_alt;
+        } else if (all[r].pid == mine.pid) {
+            p->peer_grads_alt[r] = (const void*)all[r].ptr;  // peer access was enabled for the first buffer
+        } else {
+            void* g = nullptr;
+            OXZ_CUDA(cudaIpcOpenMemHandle(&g, all[r].handle, cudaIpcMemLazyEnablePeerAccess));
+            p->ipc_opened.push_back(g);
+            p->peer_grads_alt[r] = g;
         }
     }
     return OXZ_OK;
@@ -172,6 +202,10 @@ int32_t oxz_plan_destroy(oxz_plan* p) {
             if (q) cudaFree(q);
         for (void* q : {(void*)p->h_scalars, (void*)p->h_acc, (void*)p->h_extras, (void*)p->h_present, (void*)p->h_src})
             if (q) cudaFreeHost(q);
+        if (p->grads_alt) cudaFree(p->grads_alt);
+        if (p->upload_stream) cudaStreamDestroy(p->upload_stream);
+        if (p->ev_uploaded) cudaEventDestroy(p->ev_uploaded);
+        for (auto e : p->ev_last_read) if (e) cudaEventDestroy(e);
         if (p->early_stream) cudaStreamDestroy(p->early_stream);
         if (p->ev_produced) cudaEventDestroy(p->ev_produced);
         if (p->ev_early) cudaEventDestroy(p->ev_early);
@@ -384,6 +418,56 @@ int32_t oxz_grads_upload_async(oxz_plan* p, uint64_t tensor, const void* host) {
     return OXZ_OK;
 }
 
+int32_t oxz_grads_double_buffer(oxz_plan* p, oxz_comm* comm) {
+    if (!p) return fail(OXZ_ERR_INVALID, "oxz_grads_double_buffer: null plan");
+    if (!p->allocated) return fail(OXZ_ERR_STATE, "oxz_grads_double_buffer: call oxz_state_alloc first");
+    if (p->inflight) return fail(OXZ_ERR_STATE, "oxz_grads_double_buffer: a step is in flight. Call oxz_step_wait first");
+    if (p->grads_alt) return OXZ_OK;
+    if (p->mode == OXZ_SYNC_COPY) return fail(OXZ_ERR_UNSUPPORTED, "oxz_grads_double_buffer does not serve OXZ_SYNC_COPY plans");
+    const bool peer_mode = p->mode == OXZ_SYNC_P2P || p->mode == OXZ_SYNC_REPLICATED;
+    if (peer_mode) {
+        OXZ_TRY(comm_check(comm, "oxz_grads_double_buffer"));
+        if (comm != p->comm) return fail(OXZ_ERR_INVALID, "oxz_grads_double_buffer: this is not the communicator the state was allocated with");
+    }
+    OXZ_CUDA(cudaSetDevice(p->device));
+    const size_t bytes = p->total_tiles * TILE * dtype_size(p->gdt);
+    OXZ_CUDA(cudaMalloc(&p->grads_alt, bytes ? bytes : 16));
+    OXZ_CUDA(cudaMemset(p->grads_alt, 0, bytes ? bytes : 16));
+    OXZ_CUDA(cudaStreamCreateWithFlags(&p->upload_stream, cudaStreamNonBlocking));
+    OXZ_CUDA(cudaEventCreateWithFlags(&p->ev_uploaded, cudaEventDisableTiming));
+    for (auto& e : p->ev_last_read) OXZ_CUDA(cudaEventCreateWithFlags(&e, cudaEventDisableTiming));
+    OXZ_CUDA(cudaDeviceSynchronize());
+    if (peer_mode) OXZ_TRY(exchange_alt_grads(p, comm));
+    return OXZ_OK;
+}
+
+int32_t oxz_grads_upload_next_async(oxz_plan* p, uint64_t tensor, const void* host) {
+    if (!p || !host) return fail(OXZ_ERR_INVALID, "oxz_grads_upload_next_async: null argument");
+    if (!p->grads_alt) return fail(OXZ_ERR_STATE, "oxz_grads_upload_next_async: call oxz_grads_double_buffer first");
+    if (tensor >= p->T) return fail(OXZ_ERR_INVALID, "oxz_grads_upload_next_async: tensor %llu of %llu", (unsigned long long)tensor, (unsigned long long)p->T);
+    OXZ_CUDA(cudaSetDevice(p->device));
+    // the step that last read the other buffer (and, with peers, whose end says that every rank has read it) must be over
+    OXZ_CUDA(cudaStreamWaitEvent(p->upload_stream, p->ev_last_read[1 - p->cur_grads], 0));
+    const size_t es = dtype_size(p->gdt);
+    OXZ_CUDA(cudaMemcpyAsync(static_cast<char*>(p->grads_alt) + p->offset[tensor] * es, host, p->numel[tensor] * es,
+                             cudaMemcpyHostToDevice, p->upload_stream));
+    return OXZ_OK;
+}
+
+int32_t oxz_grads_swap(oxz_plan* p) {
+    if (!p) return fail(OXZ_ERR_INVALID, "oxz_grads_swap: null plan");
+    if (!p->grads_alt) return fail(OXZ_ERR_STATE, "oxz_grads_swap: call oxz_grads_double_buffer first");
+    if (p->inflight) return fail(OXZ_ERR_STATE, "oxz_grads_swap: a step is in flight. Call oxz_step_wait first");
+    if (p->early_groups) return fail(OXZ_ERR_STATE, "oxz_grads_swap: buckets of the current buffer were already handed in for this step");
+    OXZ_CUDA(cudaSetDevice(p->device));
+    OXZ_CUDA(cudaEventRecord(p->ev_uploaded, p->upload_stream));
+    std::swap(p->grads, p->grads_alt);
+    for (int r = 0; r < p->cw; r++) std::swap(p->peers.grads[r], p->peer_grads_alt[r]);
+    p->cur_grads ^= 1;
+    p->upload_pending = true;
+    return OXZ_OK;
+}
+
 namespace {
 
 bool same_or_both_nan(double a, double b) { return a == b || (std::isnan(a) && std::isnan(b)); }
@@ -522,6 +606,11 @@ int32_t oxz_step_async(oxz_plan* p, oxz_comm* comm, const oxz_hyper* h, const ui
     int32_t* bar = p->cw > 1 ? reinterpret_cast<int32_t*>(static_cast<char*>(comm->d_small) + 384) : nullptr;
 
     auto mark = [&](int i) -> cudaError_t { return p->profile ? cudaEventRecord(p->ev[i], s) : cudaSuccess; };
+    if (p->upload_pending) {
+        // gradients copied into this buffer while the step before was still running
+        OXZ_CUDA(cudaStreamWaitEvent(s, p->ev_uploaded, 0));
+        p->upload_pending = false;
+    }
     OXZ_CUDA(mark(0));
     if (p->mode == OXZ_SYNC_SINGLE || pulls) {
         // buckets already reduced during backward are skipped; the rest goes now, one launch per run of buckets
@@ -672,6 +761,7 @@ int32_t oxz_step_async(oxz_plan* p, oxz_comm* comm, const oxz_hyper* h, const ui
         OXZ_TRY(comm_stream_barrier(comm, bar, s));
     }
     OXZ_CUDA(mark(5));
+    if (p->grads_alt) OXZ_CUDA(cudaEventRecord(p->ev_last_read[p->cur_grads], s));
     OXZ_CUDA(cudaEventRecord(p->done, s));
     p->inflight = true;
     p->inflight_hyper = *h;
@@ -703,6 +793,7 @@ int32_t oxz_grads_ready_async(oxz_plan* p, oxz_comm* comm, const oxz_hyper* h, c
         OXZ_CUDA(cudaEventCreateWithFlags(&p->ev_early, cudaEventDisableTiming));
     }
     cudaStream_t es = p->early_stream;
+    if (p->upload_pending) OXZ_CUDA(cudaStreamWaitEvent(es, p->ev_uploaded, 0));  // the buckets may have come from the host
     bool some_absent = false;
     if (p->early_groups == 0) {
         p->early_done.assign(p->n_buckets, 0);

@@ -729,6 +729,18 @@ class DpOptimizer:
     def upload_grads(self, tensor: int, host_ptr: int) -> None:
         check(lib().oxz_grads_upload_async(self._h, tensor, C.c_void_p(host_ptr)))
 
+    def double_buffer_grads(self) -> None:
+        """A second gradient buffer: the next step's gradients can arrive while this step still reads its own."""
+        check(lib().oxz_grads_double_buffer(self._h, self.comm.handle if self.comm else None))
+
+    def upload_next_grads(self, tensor: int, host_ptr: int) -> None:
+        """Into the buffer that is not current, on the plan's upload stream; allowed while a step is in flight."""
+        check(lib().oxz_grads_upload_next_async(self._h, tensor, C.c_void_p(host_ptr)))
+
+    def swap_grads(self) -> None:
+        """The other buffer becomes the current one; the next step waits for the uploads into it."""
+        check(lib().oxz_grads_swap(self._h))
+
     # -- the step
     def step_async(self, cfg: StepConfig, present: list[bool] | None = None, extras: list[float] | None = None) -> None:
         h = cfg.hyper()

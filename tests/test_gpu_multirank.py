@@ -200,6 +200,78 @@ def test_full_replicas_step_like_the_reference_and_agree_with_the_sharded_step(k
     shd.close()
 
 
+@pytest.mark.parametrize("world,mode", [(1, ox.SYNC_SINGLE), (2, ox.SYNC_P2P), (4, ox.SYNC_P2P), (2, ox.SYNC_REPLICATED)])
+def test_gradients_uploaded_into_the_second_buffer_while_a_step_runs_give_the_same_steps(world, mode):
+    """Host-fed steps over the two gradient buffers: the copy of step i+1 is issued while step i is in flight, every
+    rank swaps between the same two steps, and the state after four such steps with four different gradients is, bit
+    for bit, that of four plain steps (import, then step) and of the checker."""
+    steps = 4
+    if world == 1:
+        comms = [None]
+    else:
+        comms = ox.Communicator.local_group(world, [0] * world, timeout=60.0)
+    pool = ThreadPoolExecutor(world)
+    master, m, v, _ = seeded_state(NUMEL, 61, 1e-3, world, ox.BF16)
+    per_step = [seeded_state(NUMEL, 70 + k, 1e-3, world, ox.BF16)[3] for k in range(steps)]
+    work = [orc.narrow(p, ox.BF16) for p in master]
+    ref = orc.StepState([p.copy() for p in master], [x.copy() for x in m], [x.copy() for x in v], [w.copy() for w in work],
+                        ox.BF16, lr_scale=[1.0] * len(NUMEL), group_wd=[0.0 if nd else NAN for nd in NO_DECAY])
+
+    def make(r):
+        opt = ox.DpOptimizer(NUMEL, NO_DECAY, ox.BF16, ox.BF16, world=world, rank=r, sync_mode=mode, device=0,
+                             bucket_bytes=16384, comm=comms[r])
+        for i in range(len(NUMEL)):
+            opt.import_tensor(ffi.STATE_MASTER, i, master[i])
+            opt.import_tensor(ffi.STATE_EXP_AVG, i, m[i])
+            opt.import_tensor(ffi.STATE_EXP_AVG_SQ, i, v[i])
+            opt.import_tensor(ffi.STATE_WORK, i, work[i])
+        return opt
+    cfg = ox.StepConfig(max_grad_norm=1e9)
+
+    def pipelined(r):
+        opt = opts[r]
+        opt.double_buffer_grads()
+        keep = [[np.ascontiguousarray(g) for g in per_step[k][r]] for k in range(steps)]  # stay alive during the copies
+        def upload(k):
+            for i, g in enumerate(keep[k]):
+                if g.size:
+                    opt.upload_next_grads(i, g.ctypes.data)
+        out = []
+        upload(0)
+        for k in range(steps):
+            opt.swap_grads()
+            opt.step_async(cfg)
+            if k + 1 < steps:
+                upload(k + 1)
+            out.append(opt.step_wait())
+        return out
+    opts = list(pool.map(make, range(world)))
+    results = list(pool.map(pipelined, range(world)))
+    for k in range(steps):
+        want = orc.step(ref, [per_step[k][r] for r in range(world)], ox.BF16, orc.StepConfig(max_grad_norm=1e9))
+        for r in range(world):
+            res = results[r][k]
+            assert (res.overflow, res.applied, res.timestep) == (want.overflow, want.applied, want.timestep)
+            assert abs(res.grad_norm - want.grad_norm) <= 1e-5 * want.grad_norm
+    for kind, refs in ((ffi.STATE_MASTER, ref.master), (ffi.STATE_EXP_AVG, ref.exp_avg), (ffi.STATE_EXP_AVG_SQ, ref.exp_avg_sq)):
+        for i, b in enumerate(refs):
+            acc = np.full(NUMEL[i], np.nan, np.float32)
+            for opt in opts:
+                opt.export_tensor(kind, i, acc)
+            assert np.array_equal(bits(acc), bits(b)), (kind, i)
+    for opt in opts:
+        for i in range(len(NUMEL)):
+            assert np.array_equal(bits(opt.export_tensor(ffi.STATE_WORK, i)), bits(ref.work[i]))
+    # the current buffer is what the state calls see: the last step's gradients
+    for r, opt in enumerate(opts):
+        assert np.array_equal(bits(opt.export_tensor(ffi.STATE_GRADS, 3)), bits(per_step[steps - 1][r][3]))
+    list(pool.map(lambda r: opts[r].destroy(), range(world)))
+    for c in comms:
+        if c is not None:
+            c.destroy()
+    pool.shutdown()
+
+
 def test_a_pull_wait_that_runs_out_is_reported_and_changes_nothing(monkeypatch):
     """The bulk-copy pull bounds every wait on its own copies. Here the bound of the main-loop waits is lowered to zero,
     so the first wait gives up at once while the copies are in fact on their way: the kernel records the run-out,
