@@ -78,7 +78,8 @@ int32_t oxz_comm_init_all(int32_t n, const int32_t* devices, oxz_comm** out);
 /* An in-process group of n rank threads that meet on the host, with a collective timeout and abort: the counterpart
  * of boostr's LocalCommunicator::with_timeout (src/dp/launch.rs:52-71, tests/data_parallel.rs:158-185). Ranks may
  * share one GPU (devices[i] equal) or use none (devices NULL or -1: host collectives only). Device collectives
- * drain the stream and go through host memory; it serves OXZ_SYNC_P2P plans, not OXZ_SYNC_NCCL ones. */
+ * drain the stream and go through host memory; it serves OXZ_SYNC_P2P, OXZ_SYNC_COPY and OXZ_SYNC_REPLICATED plans,
+ * not OXZ_SYNC_NCCL ones. */
 int32_t oxz_comm_init_local(int32_t n, const int32_t* devices, double timeout_seconds, oxz_comm** out);
 int32_t oxz_comm_world_size(const oxz_comm* comm, int32_t* world);
 int32_t oxz_comm_rank(const oxz_comm* comm, int32_t* rank);
