@@ -264,7 +264,7 @@ typedef struct oxz_step_profile {
 /* Grid sizes the plan launches with (blocks of 256 threads) and the device's SM count. */
 int32_t oxz_plan_launch_geometry(const oxz_plan* plan, int32_t* sm_count, int32_t* norm_blocks, int32_t* update_blocks);
 /* Which kernel did the most recent pull of the peers' gradients (OXZ_SYNC_P2P): per-lane loads, or bulk
- * asynchronous copies into shared memory (16-bit gradients, 2, 4 or 8 ranks, every tensor present, a bucket's
+ * asynchronous copies into shared memory (16-bit gradients, 2, 4 or 8 ranks, a bucket's
  * shard a multiple of 8 tiles; OXZ_PULL_BULK=0 in the environment turns it off). Both give the same bits. No
  * reference counterpart: a tuning and test aid. */
 #define OXZ_PULL_KERNEL_NONE 0

@@ -111,10 +111,11 @@ int32_t launch_pull_sumsq(cudaStream_t s, const LaunchGeom& g, const PeerTable& 
                           float inv_scale, float clamp_hi, int32_t clamp_on, float* reduced, double* partials);
 // The pull-reduce with 1-D bulk asynchronous copies into shared memory (16-bit gradients, 2/4/8 ranks, every tensor
 // present, shard and range boundaries on multiples of 8 tiles). Returns OXZ_ERR_UNSUPPORTED when the shape does not fit.
-bool pull_bulk_fits(const TileMap& map, int32_t world, int32_t dt, bool check_present);
+bool pull_bulk_fits(const TileMap& map, int32_t world, int32_t dt);
 int32_t launch_pull_bulk(cudaStream_t s, const LaunchGeom& g, const PeerTable& peers, int32_t world, int32_t dt,
-                         const TileMap& map, float inv_scale, float clamp_hi, int32_t clamp_on, float* reduced,
-                         double* partials, uint32_t slots, DevScalars* scalars);
+                         const TileMap& map, const uint32_t* tile_meta, const uint8_t* present, bool check_present,
+                         float inv_scale, float clamp_hi, int32_t clamp_on, float* reduced, double* partials,
+                         uint32_t slots, DevScalars* scalars);
 // partials[slots][3] -> acc[3] = {sum, inf count, nan count}
 int32_t launch_reduce_partials(cudaStream_t s, const double* partials, uint32_t slots, double* acc);
 // acc[3] -> scalars (norm, clip coefficients, decisions)

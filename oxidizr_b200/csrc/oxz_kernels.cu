@@ -450,7 +450,7 @@ __global__ void __cluster_dims__(CLUSTER, 1, 1) __launch_bounds__(THREADS)
 
 // ---------------------------------------------------------------- pull-reduce with bulk asynchronous copies
 //
-// The same work as k_pull_sumsq for the common shape (16-bit gradients, 2, 4 or 8 ranks, every tensor present), with
+// The same work as k_pull_sumsq for the common shape (16-bit gradients, 2, 4 or 8 ranks), with
 // the peers' tiles brought into shared memory by 1-D bulk asynchronous copies (cp.async.bulk + mbarrier) instead of
 // per-lane loads: one elected thread issues WORLD copies of 4 KiB (8 tiles) per stage, STAGES stages deep, so the
 // NVLink requests are large and independent of the warps' progress. Measured on two B200 with both directions
@@ -475,7 +475,8 @@ __device__ __forceinline__ bool mbar_wait_bounded(uint32_t bar, uint32_t parity,
 
 template <int DT, int WORLD, int STAGES>
 __global__ void __cluster_dims__(CLUSTER, 1, 1) __launch_bounds__(THREADS)
-    k_pull_bulk(PeerTable peers, TileMap map, float inv_scale, float clamp_hi, int clamp_on, float* __restrict__ reduced,
+    k_pull_bulk(PeerTable peers, TileMap map, const uint32_t* __restrict__ tile_meta, const uint8_t* __restrict__ present,
+                int check, float inv_scale, float clamp_hi, int clamp_on, float* __restrict__ reduced,
                 double* __restrict__ partials, DevScalars* __restrict__ scalars, uint32_t wait_limit) {
     static_assert(DT == OXZ_BF16 || DT == OXZ_F16, "16-bit gradients only");
     extern __shared__ __align__(128) unsigned char bulk_smem[];
@@ -539,8 +540,15 @@ __global__ void __cluster_dims__(CLUSTER, 1, 1) __launch_bounds__(THREADS)
             for (int i = 0; i < 8; i++) s8[i] = __fadd_rn(s8[i], p8[i]);
         }
         const uint32_t lt = map.first_tile + c * BULK_TILES + warp;
-        store8<OXZ_F32>(reduced, static_cast<uint64_t>(lt) * TILE + lane * 8, s8);
-        acc8(s8, inv_scale, clamp_hi, clamp_on != 0, a);
+        bool keep = true;
+        if (check) {  // some tensor has no gradient this step: its tiles, and padding, stay out of the sum and the norm
+            const uint32_t meta = tile_meta[flat_tile(map, lt)];
+            keep = meta != PAD_TILE && present[meta & 0xffffffu];
+        }
+        if (keep) {
+            store8<OXZ_F32>(reduced, static_cast<uint64_t>(lt) * TILE + lane * 8, s8);
+            acc8(s8, inv_scale, clamp_hi, clamp_on != 0, a);
+        }
         __syncthreads();  // every warp has read this stage: it may be refilled
         const uint32_t nc = c + static_cast<uint32_t>(STAGES) * gridDim.x;
         if (nc < n_chunks) {
@@ -564,7 +572,13 @@ __global__ void __cluster_dims__(CLUSTER, 1, 1) __launch_bounds__(THREADS)
     const uint32_t tail0 = map.first_tile + n_chunks * BULK_TILES;
     if (blockIdx.x == gridDim.x - 1 && tail0 + warp < map.n_local_tiles) {
         const uint32_t lt = tail0 + warp;
-        const uint64_t fe = static_cast<uint64_t>(flat_tile(map, lt)) * TILE + lane * 8;
+        const uint32_t ft = flat_tile(map, lt);
+        const uint64_t fe = static_cast<uint64_t>(ft) * TILE + lane * 8;
+        bool keep = true;
+        if (check) {
+            const uint32_t meta = tile_meta[ft];
+            keep = meta != PAD_TILE && present[meta & 0xffffffu];
+        }
         float s8[8];
         load8<DT>(peers.grads[0], fe, s8);
 #pragma unroll
@@ -574,8 +588,10 @@ __global__ void __cluster_dims__(CLUSTER, 1, 1) __launch_bounds__(THREADS)
 #pragma unroll
             for (int i = 0; i < 8; i++) s8[i] = __fadd_rn(s8[i], p8[i]);
         }
-        store8<OXZ_F32>(reduced, static_cast<uint64_t>(lt) * TILE + lane * 8, s8);
-        acc8(s8, inv_scale, clamp_hi, clamp_on != 0, a);
+        if (keep) {
+            store8<OXZ_F32>(reduced, static_cast<uint64_t>(lt) * TILE + lane * 8, s8);
+            acc8(s8, inv_scale, clamp_hi, clamp_on != 0, a);
+        }
     }
     cluster_reduce_store(a, partials);
 }
@@ -952,7 +968,8 @@ int32_t launch_pull_sumsq(cudaStream_t s, const LaunchGeom& g, const PeerTable& 
 }
 
 template <int DT, int WORLD, int STAGES>
-static int32_t launch_pull_bulk_t(cudaStream_t s, int blocks, const PeerTable& peers, const TileMap& map, float inv_scale,
+static int32_t launch_pull_bulk_t(cudaStream_t s, int blocks, const PeerTable& peers, const TileMap& map,
+                                  const uint32_t* tile_meta, const uint8_t* present, bool check_present, float inv_scale,
                                   float clamp_hi, int32_t clamp_on, float* reduced, double* partials, DevScalars* scalars) {
     const size_t smem = static_cast<size_t>(BULK_BYTES) * WORLD * STAGES;
     // Per instantiation and device: allow the dynamic shared memory, then size the grid to the clusters that are
@@ -987,28 +1004,29 @@ static int32_t launch_pull_bulk_t(cudaStream_t s, int blocks, const PeerTable& p
     // see the run-out path: the kernel records it, still collects its copies in flight and ends normally.
     const char* lim = getenv("OXZ_PULL_WAIT_LIMIT");
     const uint32_t wait_limit = lim ? static_cast<uint32_t>(strtoul(lim, nullptr, 10)) : BULK_SPIN_LIMIT;
-    k_pull_bulk<DT, WORLD, STAGES><<<dim3(blocks), dim3(THREADS), smem, s>>>(peers, map, inv_scale, clamp_hi, clamp_on, reduced, partials, scalars, wait_limit);
+    k_pull_bulk<DT, WORLD, STAGES><<<dim3(blocks), dim3(THREADS), smem, s>>>(peers, map, tile_meta, present, check_present ? 1 : 0, inv_scale, clamp_hi, clamp_on, reduced, partials, scalars, wait_limit);
     return check_launch("k_pull_bulk");
 }
 
-bool pull_bulk_fits(const TileMap& map, int32_t world, int32_t dt, bool check_present) {
-    if (check_present || dt == OXZ_F32 || (world != 2 && world != 4 && world != 8)) return false;
+bool pull_bulk_fits(const TileMap& map, int32_t world, int32_t dt) {
+    if (dt == OXZ_F32 || (world != 2 && world != 4 && world != 8)) return false;
     // a chunk must not straddle two buckets' shards; a ragged end of the last shard is handled by plain loads
     if (map.tiles_per_shard % BULK_TILES || map.first_tile % BULK_TILES) return false;
     return true;
 }
 
 int32_t launch_pull_bulk(cudaStream_t s, const LaunchGeom& g, const PeerTable& peers, int32_t world, int32_t dt,
-                         const TileMap& map, float inv_scale, float clamp_hi, int32_t clamp_on, float* reduced,
-                         double* partials, uint32_t slots, DevScalars* scalars) {
+                         const TileMap& map, const uint32_t* tile_meta, const uint8_t* present, bool check_present,
+                         float inv_scale, float clamp_hi, int32_t clamp_on, float* reduced, double* partials,
+                         uint32_t slots, DevScalars* scalars) {
     int blocks = g.bulk_blocks[world == 2 ? 0 : world == 4 ? 1 : 2];
     if (static_cast<uint32_t>(blocks / CLUSTER) > slots) blocks = static_cast<int>(slots) * CLUSTER;  // one partial slot per cluster
     if (blocks < CLUSTER) return fail(OXZ_ERR_INVALID, "launch_pull_bulk: no partial slot to write to");
 #define OXZ_BULK(DT) \
     switch (world) { \
-        case 2: return launch_pull_bulk_t<DT, 2, 4>(s, blocks, peers, map, inv_scale, clamp_hi, clamp_on, reduced, partials, scalars); \
-        case 4: return launch_pull_bulk_t<DT, 4, 4>(s, blocks, peers, map, inv_scale, clamp_hi, clamp_on, reduced, partials, scalars); \
-        default: return launch_pull_bulk_t<DT, 8, 3>(s, blocks, peers, map, inv_scale, clamp_hi, clamp_on, reduced, partials, scalars); \
+        case 2: return launch_pull_bulk_t<DT, 2, 4>(s, blocks, peers, map, tile_meta, present, check_present, inv_scale, clamp_hi, clamp_on, reduced, partials, scalars); \
+        case 4: return launch_pull_bulk_t<DT, 4, 4>(s, blocks, peers, map, tile_meta, present, check_present, inv_scale, clamp_hi, clamp_on, reduced, partials, scalars); \
+        default: return launch_pull_bulk_t<DT, 8, 3>(s, blocks, peers, map, tile_meta, present, check_present, inv_scale, clamp_hi, clamp_on, reduced, partials, scalars); \
     }
     if (dt == OXZ_BF16) { OXZ_BULK(OXZ_BF16) }
     OXZ_BULK(OXZ_F16)

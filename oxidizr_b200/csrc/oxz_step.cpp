@@ -501,12 +501,12 @@ int32_t reduce_buckets(oxz_plan* p, cudaStream_t s, const LaunchGeom& geom, uint
     // 1.24 G bf16 gradients); OXZ_PULL_BULK=0 keeps the per-lane loads.
     const char* bulk_env = getenv("OXZ_PULL_BULK");
     const bool want_bulk = !bulk_env || atoi(bulk_env) != 0;
-    if (want_bulk && pull_bulk_fits(gm, p->cw, p->gdt, some_absent)) {
+    if (want_bulk && pull_bulk_fits(gm, p->cw, p->gdt)) {
         // its grid is smaller than the group's slot count: the slots it does not write must read as zero
         OXZ_CUDA(cudaMemsetAsync(partials, 0, (size_t)slots * 3 * 8, s));
         p->last_pull_kernel = OXZ_PULL_KERNEL_BULK;
-        return launch_pull_bulk(s, geom, p->peers, p->cw, p->gdt, gm, inv_scale, clamp_hi, clamp_on,
-                                static_cast<float*>(p->reduced), partials, slots, p->d_scalars);
+        return launch_pull_bulk(s, geom, p->peers, p->cw, p->gdt, gm, p->d_tile_meta, p->d_present, some_absent, inv_scale,
+                                clamp_hi, clamp_on, static_cast<float*>(p->reduced), partials, slots, p->d_scalars);
     }
     p->last_pull_kernel = OXZ_PULL_KERNEL_LOADS;
     return launch_pull_sumsq(s, geom, p->peers, p->cw, 0, p->gdt, gm, p->d_tile_meta, p->d_present, some_absent,
