@@ -181,7 +181,11 @@ def run_gpu(args):
     numel = [t.elements for t in tensors]
     P = sum(numel)
     mode = {"p2p": ox.SYNC_P2P, "nccl": ox.SYNC_NCCL, "copy": ox.SYNC_COPY, "replicated": ox.SYNC_REPLICATED}[args.sync] if world > 1 else ox.SYNC_SINGLE
-    opt = ox.DpOptimizer(numel, plan.no_decay, ox.BF16, ox.BF16, world=world, rank=rank, sync_mode=mode,
+    es = 4 if args.dtype == "f32" else 2  # bytes per gradient and per working weight
+    ox_dt = ox.F32 if args.dtype == "f32" else ox.BF16
+    t_dt = torch.float32 if args.dtype == "f32" else torch.bfloat16
+    bytes_norm = es  # the norm pass reads every gradient once; the update moves 28 B/param in either dtype
+    opt = ox.DpOptimizer(numel, plan.no_decay, ox_dt, ox_dt, world=world, rank=rank, sync_mode=mode,
                          device=local_rank, comm=comm)
     ptr, info = opt.pointers(), opt.info
     stream = torch.cuda.Stream()
@@ -190,8 +194,9 @@ def run_gpu(args):
 
     # seeded synthetic state, generated on the device straight into the library's buffers
     gen = torch.Generator(device="cuda")
-    grads = device_view(ptr["grads"], info.padded_total * 2, torch.bfloat16, local_rank)
-    work = device_view(ptr["work"], info.padded_total * 2, torch.bfloat16, local_rank)
+    grads = device_view(ptr["grads"], info.padded_total * es, t_dt, local_rank)
+    separate_work = ptr["work"] != ptr["master"]  # f32 parameters at one rank keep no narrow copy
+    work = device_view(ptr["work"], info.padded_total * es, t_dt, local_rank) if separate_work else None
     master = device_view(ptr["master"], info.local_elems * 4, torch.float32, local_rank)
     m = device_view(ptr["exp_avg"], info.local_elems * 4, torch.float32, local_rank)
     v = device_view(ptr["exp_avg_sq"], info.local_elems * 4, torch.float32, local_rank)
@@ -204,9 +209,9 @@ def run_gpu(args):
         v[lo:hi].normal_(0.0, 1e-6, generator=gen).abs_()
     gen.manual_seed(SEED + 1 + rank)
     for off, n in zip(opt.offsets, numel):
-        grads[off:off + n] = torch.empty(n, device="cuda", dtype=torch.float32).normal_(0.0, 1e-3, generator=gen).to(torch.bfloat16)
-    if world == 1 or mode == ox.SYNC_REPLICATED:
-        work.copy_(master.to(torch.bfloat16))
+        grads[off:off + n] = torch.empty(n, device="cuda", dtype=torch.float32).normal_(0.0, 1e-3, generator=gen).to(t_dt)
+    if separate_work and (world == 1 or mode == ox.SYNC_REPLICATED):
+        work.copy_(master.to(t_dt))
     opt.timestep = 1
     torch.cuda.synchronize()
 
@@ -251,7 +256,7 @@ def run_gpu(args):
     # end to end: every step copies that step's gradients from pinned host memory, then reads the result back
     host_off, base = [], 0
     if not args.skip_e2e:
-        host = torch.empty(P, dtype=torch.bfloat16).pin_memory()
+        host = torch.empty(P, dtype=t_dt).pin_memory()
         pos = 0
         for off, n in zip(opt.offsets, numel):
             host[pos:pos + n].copy_(grads[off:off + n])
@@ -262,11 +267,11 @@ def run_gpu(args):
 
     def upload():
         for i, n in enumerate(numel):
-            opt.upload_grads(i, base + host_off[i] * 2)
+            opt.upload_grads(i, base + host_off[i] * es)
 
     def upload_next():
         for i, n in enumerate(numel):
-            opt.upload_next_grads(i, base + host_off[i] * 2)
+            opt.upload_next_grads(i, base + host_off[i] * es)
 
     def timed_host_fed(n_steps: int):
         """Every step's gradients come from pinned host memory and its result is read back. The library's second
@@ -321,7 +326,7 @@ def run_gpu(args):
 
     aux = None
     if world == 1 and not args.skip_aux:
-        aux = aux_measurements(ox, torch, opt, numel, stream, local_rank)
+        aux = aux_measurements(ox, torch, opt, numel, stream, local_rank, t_dt, es)
 
     peak, peak_kind = measured_peaks()
     totals = sorted(p.total_ms for p in profs)
@@ -335,23 +340,23 @@ def run_gpu(args):
         "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps, "warmup": max(args.warmup, 3),
         "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
         "dtype": "f32", "data": "synthetic",
-        "config": {"workload": args.workload, "params": P, "tensors": len(numel), "grad_dtype": "bf16", "param_dtype": "bf16",
+        "config": {"workload": args.workload, "params": P, "tensors": len(numel), "grad_dtype": args.dtype, "param_dtype": args.dtype,
                    "world": world, "sync": args.sync if world > 1 else "single",
-                   "l2": "inputs larger than L2: 30 B/param x %d params per rank per step" % int(local_params),
+                   "l2": "inputs larger than L2: %d B/param x %d params per rank per step" % (bytes_norm + BYTES_UPDATE, int(local_params)),
                    "hyper": HYPER},
         "roofline": {"bound": "hbm", "kernel": "k_adamw", "achieved": achieved, "peak": peak, "unit": "GB/s",
                      "frac": achieved / peak, "peak_kind": peak_kind,
-                     "traffic": ADAMW_TRAFFIC_RATIO * BYTES_UPDATE * local_params,
-                     "traffic_source": "ncu capture of nano_dense scaled by parameters per launch",
+                     "traffic": ADAMW_TRAFFIC_RATIO * BYTES_UPDATE * local_params if args.dtype == "bf16" else None,
+                     "traffic_source": "ncu capture of nano_dense scaled by parameters per launch" if args.dtype == "bf16" else "not captured for f32",
                      "algorithmic_bytes_per_launch": BYTES_UPDATE * local_params, "kernel_ms": upd,
-                     "norm_kernel": {"kernel": pull_kernel if mode in (ox.SYNC_P2P, ox.SYNC_REPLICATED) else "k_sumsq_stream16" if mode == ox.SYNC_SINGLE else "k_sumsq",
-                                     "kernel_ms": nrm, "achieved_gbs": BYTES_NORM * local_params / (nrm * 1e-3) / 1e9 if world == 1 else None}},
+                     "norm_kernel": {"kernel": pull_kernel if mode in (ox.SYNC_P2P, ox.SYNC_REPLICATED) else ("k_sumsq_stream16" if es == 2 else "k_sumsq") if mode == ox.SYNC_SINGLE else "k_sumsq",
+                                     "kernel_ms": nrm, "achieved_gbs": bytes_norm * local_params / (nrm * 1e-3) / 1e9 if world == 1 else None}},
         "phases_ms": {k: statistics.mean(getattr(p, k) for p in profs) for k in
                       ("collect_ms", "norm_ms", "decide_ms", "update_ms", "publish_ms", "total_ms")},
         # device time of each timed step on this rank (CUDA events inside the library), for the spread
         "step_ms_device": {"median": statistics.median(totals), "p10": pct(0.10), "p90": pct(0.90)},
-        "step_roofline": step_roofline(P, world, ms_per_step, peak),
-        "e2e": {"value": e2e_value, "unit": UNIT, "h2d_bytes_per_step": P * 2 * world, "d2h_bytes_per_step": 32 * world,
+        "step_roofline": step_roofline(P, world, ms_per_step, peak, es),
+        "e2e": {"value": e2e_value, "unit": UNIT, "h2d_bytes_per_step": P * es * world, "d2h_bytes_per_step": 32 * world,
                 "ms_per_step": e2e_sec * 1e3 / e2e_steps, "steps": e2e_steps,
                 "copy_overlaps_previous_step": bool(pipelined and not args.skip_e2e)},
         # kernels of this library per step: norm (or pull) + reduce_partials + finalize + update; the copy mode runs
@@ -380,7 +385,7 @@ def run_gpu(args):
         dist.destroy_process_group()
 
 
-def aux_measurements(ox, torch, opt, numel, stream, local_rank: int) -> dict:
+def aux_measurements(ox, torch, opt, numel, stream, local_rank: int, t_dt, es: int) -> dict:
     """The callers either side of the step, timed apart from `value`: per-tensor gradients into the flat buffer
     (overwrite and accumulate), and the rank-sliced loader with and without its masks."""
     import tempfile
@@ -389,10 +394,10 @@ def aux_measurements(ox, torch, opt, numel, stream, local_rank: int) -> dict:
     for n in numel:
         offs.append(pos)
         pos += (n + 7) // 8 * 8  # 16-byte aligned starts
-    src = torch.empty(pos, dtype=torch.bfloat16, device="cuda").normal_(0.0, 1e-3)
-    ptrs = [src.data_ptr() + o * 2 for o in offs]
+    src = torch.empty(pos, dtype=t_dt, device="cuda").normal_(0.0, 1e-3)
+    ptrs = [src.data_ptr() + o * es for o in offs]
     out = {"flatten": {}}
-    for name, acc, bytes_per in (("overwrite", False, 4), ("accumulate", True, 6)):
+    for name, acc, bytes_per in (("overwrite", False, 2 * es), ("accumulate", True, 3 * es)):
         opt.flatten_grads(ptrs, acc)
         torch.cuda.synchronize()
         t0, t1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
@@ -432,12 +437,13 @@ def aux_measurements(ox, torch, opt, numel, stream, local_rank: int) -> dict:
     return out
 
 
-def step_roofline(P: int, world: int, ms: float, hbm_gbs: float) -> dict:
-    """Whole-step roofline: the slower of the HBM term (30 B/param on each rank's 1/world) and, with more ranks,
-    the NVLink term (bf16 reduce-scatter in + bf16 all-gather out, (world-1)/world * 2 B/param each)."""
-    hbm_ms_nominal = (BYTES_NORM + BYTES_UPDATE) * P / world / 8.0e12 * 1e3
-    hbm_ms_measured = (BYTES_NORM + BYTES_UPDATE) * P / world / (hbm_gbs * 1e9) * 1e3
-    wire = 2 * (world - 1) / world * 2 * P
+def step_roofline(P: int, world: int, ms: float, hbm_gbs: float, es: int = 2) -> dict:
+    """Whole-step roofline: the slower of the HBM term (es + 28 B/param on each rank's 1/world: 30 for 16-bit, 32 for
+    f32) and, with more ranks, the NVLink term (reduce-scatter in + all-gather out in the gradients' and weights' own
+    width, (world-1)/world * es B/param each)."""
+    hbm_ms_nominal = (es + BYTES_UPDATE) * P / world / 8.0e12 * 1e3
+    hbm_ms_measured = (es + BYTES_UPDATE) * P / world / (hbm_gbs * 1e9) * 1e3
+    wire = 2 * (world - 1) / world * es * P
     wire_ms_nominal = wire / 900e9 * 1e3
     wire_ms_measured = wire / 770e9 * 1e3
     nominal = max(hbm_ms_nominal, wire_ms_nominal)
@@ -456,6 +462,8 @@ def main():
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--skip-e2e", action="store_true", help="profiling runs: leave the host-fed leg out")
     ap.add_argument("--skip-aux", action="store_true", help="leave out the flatten and loader timings (1 GPU only)")
+    ap.add_argument("--dtype", choices=["bf16", "f32"], default="bf16",
+                    help="width of gradients and working weights: bf16 is the headline; f32 is the all-f32 configuration")
     ap.add_argument("--workload", default=WORKLOAD, help="parameter set; the headline is llama-3.2-1b, smaller sets serve profiler captures")
     args = ap.parse_args()
     if args.impl == "reference":
