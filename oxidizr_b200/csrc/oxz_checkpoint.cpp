@@ -11,6 +11,7 @@
 #include <string>
 
 #include "oxz_internal.h"
+#include "oxz_json.h"
 #include "oxz_nccl.h"
 
 using namespace oxz;
@@ -23,93 +24,29 @@ struct Entry {
     uint64_t begin = 0, end = 0;
 };
 
-// ---- a small JSON reader, enough for a SafeTensors header ----
-struct Json {
-    const char* p;
-    const char* e;
-    bool ok = true;
-    void ws() { while (p < e && (*p == ' ' || *p == '\n' || *p == '\t' || *p == '\r')) p++; }
-    bool eat(char c) { ws(); if (p < e && *p == c) { p++; return true; } return false; }
-    std::string str() {
-        std::string out;
-        ws();
-        if (p >= e || *p != '"') { ok = false; return out; }
-        p++;
-        while (p < e && *p != '"') {
-            if (*p == '\\' && p + 1 < e) {
-                p++;
-                switch (*p) {
-                    case 'n': out += '\n'; break;
-                    case 't': out += '\t'; break;
-                    case 'u': out += '?'; p += 4; break;
-                    default: out += *p;
-                }
-                p++;
-            } else {
-                out += *p++;
-            }
-        }
-        if (p >= e) { ok = false; return out; }
-        p++;
-        return out;
-    }
-    uint64_t num() {
-        ws();
-        uint64_t v = 0;
-        if (p >= e || *p < '0' || *p > '9') { ok = false; return 0; }
-        while (p < e && *p >= '0' && *p <= '9') v = v * 10 + (uint64_t)(*p++ - '0');
-        return v;
-    }
-    void skip() {  // any value
-        ws();
-        if (p >= e) { ok = false; return; }
-        if (*p == '"') { str(); return; }
-        if (*p == '{' || *p == '[') {
-            const char open = *p, close = open == '{' ? '}' : ']';
-            p++;
-            if (eat(close)) return;
-            do {
-                if (open == '{') { str(); if (!eat(':')) { ok = false; return; } }
-                skip();
-                if (!ok) return;
-            } while (eat(','));
-            if (!eat(close)) ok = false;
-            return;
-        }
-        while (p < e && *p != ',' && *p != '}' && *p != ']') p++;
-    }
-};
-
 bool parse_header(const std::string& text, std::map<std::string, Entry>& out) {
-    Json j{text.data(), text.data() + text.size()};
-    if (!j.eat('{')) return false;
-    if (j.eat('}')) return true;
-    do {
-        std::string name = j.str();
-        if (!j.ok || !j.eat(':')) return false;
-        if (name == "__metadata__") { j.skip(); if (!j.ok) return false; continue; }
+    JsonReader j{text.data(), text.data() + text.size()};
+    j.object([&](const std::string& name) {
+        if (name == "__metadata__") { j.skip(); return; }
         Entry en;
-        if (!j.eat('{')) return false;
-        do {
-            std::string key = j.str();
-            if (!j.ok || !j.eat(':')) return false;
+        j.object([&](const std::string& key) {
             if (key == "dtype") en.dtype = j.str();
-            else if (key == "shape") {
-                if (!j.eat('[')) return false;
-                if (!j.eat(']')) { do { en.shape.push_back(j.num()); } while (j.eat(',')); if (!j.eat(']')) return false; }
-            } else if (key == "data_offsets") {
-                if (!j.eat('[')) return false;
-                en.begin = j.num();
-                if (!j.eat(',')) return false;
-                en.end = j.num();
-                if (!j.eat(']')) return false;
+            else if (key == "shape" || key == "data_offsets") {
+                std::vector<uint64_t> v;
+                if (!j.eat('[')) { j.ok = false; return; }
+                if (!j.eat(']')) {
+                    do { uint64_t x = 0; j.u64(&x); v.push_back(x); } while (j.ok && j.eat(','));
+                    if (!j.eat(']')) j.ok = false;
+                }
+                if (key == "shape") en.shape = v;
+                else if (v.size() == 2) { en.begin = v[0]; en.end = v[1]; }
+                else j.ok = false;
             } else j.skip();
-            if (!j.ok) return false;
-        } while (j.eat(','));
-        if (!j.eat('}')) return false;
-        out[name] = en;
-    } while (j.eat(','));
-    return j.eat('}') && j.ok;
+        });
+        if (j.ok) out[name] = en;
+    });
+    j.ws();
+    return j.ok && j.p == j.e;
 }
 
 std::string json_escape(const char* s) {
