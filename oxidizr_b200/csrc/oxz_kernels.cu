@@ -454,7 +454,7 @@ __global__ void __cluster_dims__(CLUSTER, 1, 1) __launch_bounds__(THREADS)
 // the peers' tiles brought into shared memory by 1-D bulk asynchronous copies (cp.async.bulk + mbarrier) instead of
 // per-lane loads: one elected thread issues WORLD copies of 4 KiB (8 tiles) per stage, STAGES stages deep, so the
 // NVLink requests are large and independent of the warps' progress. Measured on two B200 with both directions
-// loaded: 669 GB/s per direction for bulk reads against 635 GB/s for 128-bit loads. No cluster multicast is used:
+// loaded: 669 GB/s per direction for bulk reads against 635 GB/s for 128-bit loads. No load is shared across the cluster:
 // every block fetches what it needs itself. Every wait on an mbarrier is bounded; when a bound runs out the block
 // records it in scalars->wait_expired, waits once more (bounded) for its copies in flight, and returns.
 constexpr int BULK_TILES = 8;                       // tiles per chunk: one per warp
