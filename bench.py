@@ -99,9 +99,10 @@ def tiled_normal(n: int, std: float, seed: int, absolute: bool = False) -> np.nd
 
 
 # ------------------------------------------------------------------ the CPU arm
-def cpu_arm(steps: int, warmup: int, threads: int | None = None):
+def cpu_arm(steps: int, warmup: int, threads: int | None = None, world: int = 1):
     """The reference's CPU optimizer path, restated (the reference is Rust over un-vendored crates and cannot be
-    built here), on a bounded sample of the workload: the first 4 of 16 decoder layers."""
+    built here), on a bounded sample of the workload: the first 4 of 16 decoder layers. With world > 1 the step first
+    sums that many gradient buffers in f32, as the reference's in-process communicator does (src/dp/reduce.rs:30-60)."""
     from oracle import dpstep as orc
     from oxidizr_b200 import DecayPlan, WeightDecaySpec, inventory
 
@@ -121,14 +122,15 @@ def cpu_arm(steps: int, warmup: int, threads: int | None = None):
                           group_wd=[0.0 if plan.no_decay[i] else float("nan") for i in pick], timestep=1)
     grads = [orc.to_bf16(tiled_normal(n, 1e-3, SEED + 300 + i)) for i, n in enumerate(numel)]
     cfg = orc.StepConfig(**HYPER)
+    ranks = [grads] * max(world, 1)  # every rank's buffer holds the same values: only the work of the sum matters here
     for _ in range(warmup):
-        orc.step(state, [grads], orc.BF16, cfg)
+        orc.step(state, ranks, orc.BF16, cfg)
     t0 = time.perf_counter()
     for _ in range(steps):
-        orc.step(state, [grads], orc.BF16, cfg)
+        orc.step(state, ranks, orc.BF16, cfg)
     dt = (time.perf_counter() - t0) / max(steps, 1)
     orc.lib().orc_set_num_threads(all_threads)
-    sample = f"{len(pick)} tensors = 4 of 16 decoder layers, {P} of 1235814400 params, {steps} steps"
+    sample = f"{len(pick)} tensors = 4 of 16 decoder layers, {P} of 1235814400 params, {steps} steps, {max(world, 1)} rank buffer(s) summed"
     return P / dt, dt * 1e3, cores, sample
 
 
@@ -136,7 +138,7 @@ def run_reference(args):
     rank = int(os.environ.get("RANK", "0"))
     if rank != 0:
         return
-    value, ms, cores, sample = cpu_arm(args.steps, args.warmup)
+    value, ms, cores, sample = cpu_arm(args.steps, args.warmup, world=args.gpus)
     line = {
         "impl": "reference", "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": args.gpus, "steps": args.steps,
         "warmup": args.warmup, "ms_per_step": ms, "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
