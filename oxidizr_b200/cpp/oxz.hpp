@@ -284,6 +284,78 @@ inline void run_ranks(const std::vector<Communicator>& comms, const std::functio
     check(oxz_run_ranks((int32_t)comms.size(), raw.data(), tramp, &ctx, &failed));
 }
 
+// ---- the rank-sliced loader (src/data/construction.rs, ranks.rs:25-41, multi_source.rs:17-52, mixture/loader.rs:16-33,
+// host_masks.rs:28-77, prefetch.rs:86-115), stream order
+struct Batch {  // src/data/batch.rs:11-26; device pointers, valid until the batch after the next
+    const int64_t* inputs = nullptr;
+    const int64_t* targets = nullptr;
+    const float* loss_mask = nullptr;       // null when masking is off
+    const int32_t* segment_ids = nullptr;   // null unless the document mask is on
+    const int32_t* cu_seqlens = nullptr;
+    const uint64_t* scored = nullptr;       // pinned host: read once the stream has passed the batch
+    const uint64_t* n_segments = nullptr;
+    std::vector<uint64_t> rows;             // the global rows of the batch
+};
+class LitDataLoader {
+  public:
+    static LitDataLoader from_files(const std::vector<std::string>& paths, uint64_t batch_size, uint64_t seq_len, int32_t device = 0) {
+        return LitDataLoader(paths, batch_size, seq_len, 0, 1, {}, device);
+    }
+    LitDataLoader(const std::vector<std::string>& paths, uint64_t batch_size, uint64_t seq_len, uint64_t rank, uint64_t world,
+                  const std::vector<std::pair<uint64_t, uint64_t>>& row_ranges, int32_t device = 0)
+        : batch_(batch_size) {
+        std::vector<const char*> p;
+        for (const auto& s : paths) p.push_back(s.c_str());
+        std::vector<uint64_t> spans;
+        for (const auto& r : row_ranges) { spans.push_back(r.first); spans.push_back(r.second); }
+        check(oxz_loader_open_files(p.data(), (uint32_t)p.size(), seq_len, batch_size, rank, world, spans.empty() ? nullptr : spans.data(),
+                                    (uint32_t)row_ranges.size(), device, &h_));
+    }
+    LitDataLoader(LitDataLoader&& o) noexcept : h_(o.h_), batch_(o.batch_) { o.h_ = nullptr; }
+    LitDataLoader(const LitDataLoader&) = delete;
+    ~LitDataLoader() { if (h_) oxz_loader_close(h_); }
+    LitDataLoader& with_mixture(const std::vector<double>& weights, std::optional<uint64_t> rows_per_epoch = std::nullopt) {
+        check(oxz_loader_set_mixture(h_, weights.data(), (uint32_t)weights.size(), rows_per_epoch ? 1 : 0, rows_per_epoch.value_or(0)));
+        return *this;
+    }
+    LitDataLoader& with_target_mask(uint32_t target_base, const std::vector<uint32_t>& always_score) {  // TargetMask::PrefixLm
+        check(oxz_loader_set_target_mask(h_, 1, target_base, always_score.empty() ? nullptr : always_score.data(), (uint32_t)always_score.size()));
+        return *this;
+    }
+    LitDataLoader& with_document_mask(uint32_t separator_id) { check(oxz_loader_set_document_mask(h_, 1, separator_id)); return *this; }
+    LitDataLoader& with_prefetch(uint32_t depth) { check(oxz_loader_set_prefetch(h_, depth)); return *this; }
+    uint64_t num_rows() const { uint64_t n = 0; check(oxz_loader_num_rows(h_, &n)); return n; }
+    std::vector<uint64_t> source_rows() const {
+        uint32_t n = 0;
+        check(oxz_loader_source_rows(h_, nullptr, 0, &n));
+        std::vector<uint64_t> rows(n);
+        check(oxz_loader_source_rows(h_, rows.data(), n, &n));
+        return rows;
+    }
+    DataPosition position() const { oxz_data_position p{}; check(oxz_loader_position(h_, &p)); return {p.epoch, p.row}; }
+    void seek(DataPosition pos) { check(oxz_loader_seek(h_, {pos.epoch, pos.row})); }
+    std::vector<uint64_t> next_rows() { std::vector<uint64_t> rows(batch_); check(oxz_loader_next_rows(h_, rows.data())); return rows; }
+    Batch next_batch(void* stream = nullptr) {
+        Batch b;
+        b.rows.resize(batch_);
+        int64_t *in = nullptr, *tg = nullptr;
+        check(oxz_loader_next_batch_async(h_, stream, &in, &tg, b.rows.data()));
+        oxz_batch_masks m{};
+        check(oxz_loader_batch_masks(h_, &m));
+        b.inputs = in;
+        b.targets = tg;
+        b.loss_mask = m.loss_mask;
+        b.segment_ids = m.segment_ids;
+        b.cu_seqlens = m.cu_seqlens;
+        b.scored = m.scored;
+        b.n_segments = m.n_segments;
+        return b;
+    }
+  private:
+    oxz_loader* h_ = nullptr;
+    uint64_t batch_;
+};
+
 // ---- the optimizer state and step
 struct StepConfig {  // trainer keys with the reference's defaults (src/config.rs:40-62)
     double lr = 3e-4, beta1 = 0.9, beta2 = 0.95, eps = 1e-6, weight_decay = 0.1, max_grad_norm = 1.0;

@@ -145,6 +145,50 @@ static void the_meta_world_size_gates_a_resume() {
     rmdir(dir.c_str());
 }
 
+// src/data/multi_source.rs:99-161, src/data/mixture/loader.rs:108-171 in stream order, on the host alone
+static void the_loader_reads_sources_ranges_and_mixtures_in_order() {
+    const std::string dir = std::string("/tmp/oxz-mirror-data-") + std::to_string((long)getpid());
+    mkdir(dir.c_str(), 0700);
+    const uint64_t seq = 3, width = seq + 1;
+    std::vector<std::string> paths;
+    uint32_t first = 0;
+    const uint64_t rows[3] = {3, 2, 4};
+    for (int i = 0; i < 3; i++) {  // every token is its own offset in the concatenation; each file has a 2-token tail
+        paths.push_back(dir + "/s" + std::to_string(i) + ".bin");
+        FILE* f = fopen(paths.back().c_str(), "wb");
+        for (uint32_t t = 0; t < rows[i] * width; t++) { const uint32_t v = first + t; fwrite(&v, 4, 1, f); }
+        const uint32_t tail = 0xffffffffu;
+        fwrite(&tail, 4, 1, f);
+        fwrite(&tail, 4, 1, f);
+        fclose(f);
+        first += (uint32_t)(rows[i] * width);
+    }
+    {
+        LitDataLoader l = LitDataLoader::from_files(paths, 3, seq, -1);
+        EXPECT((l.source_rows() == std::vector<uint64_t>{3, 2, 4}) && l.num_rows() == 9);
+        std::vector<uint64_t> seen;
+        for (int b = 0; b < 3; b++) for (uint64_t r : l.next_rows()) seen.push_back(r);
+        EXPECT((seen == std::vector<uint64_t>{0, 1, 2, 3, 4, 5, 6, 7, 8}));
+    }
+    {
+        LitDataLoader eval(paths, 1, seq, 0, 1, {{2, 3}, {8, 9}}, -1);
+        EXPECT((eval.next_rows() == std::vector<uint64_t>{2}) && (eval.next_rows() == std::vector<uint64_t>{8}));
+        EXPECT(throws([&] { LitDataLoader(paths, 1, seq, 0, 1, {{0, 5}, {4, 6}}, -1); }, "starts before row 5"));
+    }
+    {
+        LitDataLoader full(paths, 3, seq, 0, 1, {}, -1), resumed(paths, 3, seq, 0, 1, {}, -1);
+        full.with_mixture({1.0, 1.0, 2.0}, 12);
+        resumed.with_mixture({1.0, 1.0, 2.0}, 12);
+        EXPECT(full.num_rows() == 12);
+        for (int b = 0; b < 5; b++) full.next_rows();
+        resumed.seek(RowLayout::create(12, 3).advance({}, 5));
+        for (int b = 0; b < 9; b++) EXPECT(full.next_rows() == resumed.next_rows());
+        EXPECT(throws([&] { LitDataLoader(paths, 1, seq, 0, 1, {}, -1).with_mixture({1.0}); }, "1 weight(s)"));
+    }
+    for (const auto& p : paths) remove(p.c_str());
+    rmdir(dir.c_str());
+}
+
 // src/dp/reduce.rs:88-121, src/dp/launch.rs:296-366
 static void ranks_sum_and_the_first_error_wins() {
     auto comms = Communicator::local_group(2, nullptr, 10.0);
@@ -204,6 +248,7 @@ int main(int argc, char** argv) {
     advance_matches_one_batch_at_a_time();
     ranks_sum_and_the_first_error_wins();
     the_meta_world_size_gates_a_resume();
+    the_loader_reads_sources_ranges_and_mixtures_in_order();
     if (argc > 1 && strcmp(argv[1], "--gpu") == 0) the_step_on_the_gpu();
     printf(failures ? "%d FAILED\n" : "all passed (%d failures)\n", failures);
     return failures ? 1 : 0;
