@@ -129,147 +129,151 @@ extern "C" {
 
 int32_t oxz_optimizer_save(oxz_plan* p, oxz_comm* comm, const char* path, const char* const* names,
                            const uint32_t* ndim, const uint64_t* dims) {
-    OXZ_TRY(check_call(p, comm, path, names, ndim, dims, "oxz_optimizer_save"));
-    OXZ_CUDA(cudaSetDevice(p->device));
-    const bool has_master = p->pdt != OXZ_F32;
-    const bool writer = p->cr == 0;  // with full replicas every rank holds everything and rank 0 alone writes
-    const char* next = "Check that the checkpoint directory is writable and has free space.";
+    return oxz::guarded("oxz_optimizer_save", [&]() -> int32_t {
+        OXZ_TRY(check_call(p, comm, path, names, ndim, dims, "oxz_optimizer_save"));
+        OXZ_CUDA(cudaSetDevice(p->device));
+        const bool has_master = p->pdt != OXZ_F32;
+        const bool writer = p->cr == 0;  // with full replicas every rank holds everything and rank 0 alone writes
+        const char* next = "Check that the checkpoint directory is writable and has free space.";
 
-    // header: entries in the order the data is written
-    std::string header = "{\"__metadata__\":{\"format\":\"oxidizr-optimizer\",\"optimizer\":\"adamw\"}";
-    uint64_t off = 0;
-    const int kinds[3] = {OXZ_STATE_EXP_AVG, OXZ_STATE_EXP_AVG_SQ, OXZ_STATE_MASTER};
-    const char* suffix[3] = {".exp_avg", ".exp_avg_sq", ".master"};
-    {
-        const uint64_t* d = dims;
-        for (uint64_t i = 0; i < p->T; i++) {
-            std::string shape = "[";
-            for (uint32_t k = 0; k < ndim[i]; k++) shape += (k ? "," : "") + std::to_string(d[k]);
-            shape += "]";
-            for (int k = 0; k < (has_master ? 3 : 2); k++) {
-                header += ",\"" + json_escape(names[i]) + suffix[k] + "\":{\"dtype\":\"F32\",\"shape\":" + shape +
-                          ",\"data_offsets\":[" + std::to_string(off) + "," + std::to_string(off + p->numel[i] * 4) + "]}";
-                off += p->numel[i] * 4;
+        // header: entries in the order the data is written
+        std::string header = "{\"__metadata__\":{\"format\":\"oxidizr-optimizer\",\"optimizer\":\"adamw\"}";
+        uint64_t off = 0;
+        const int kinds[3] = {OXZ_STATE_EXP_AVG, OXZ_STATE_EXP_AVG_SQ, OXZ_STATE_MASTER};
+        const char* suffix[3] = {".exp_avg", ".exp_avg_sq", ".master"};
+        {
+            const uint64_t* d = dims;
+            for (uint64_t i = 0; i < p->T; i++) {
+                std::string shape = "[";
+                for (uint32_t k = 0; k < ndim[i]; k++) shape += (k ? "," : "") + std::to_string(d[k]);
+                shape += "]";
+                for (int k = 0; k < (has_master ? 3 : 2); k++) {
+                    header += ",\"" + json_escape(names[i]) + suffix[k] + "\":{\"dtype\":\"F32\",\"shape\":" + shape +
+                              ",\"data_offsets\":[" + std::to_string(off) + "," + std::to_string(off + p->numel[i] * 4) + "]}";
+                    off += p->numel[i] * 4;
+                }
+                d += ndim[i];
             }
-            d += ndim[i];
+            header += ",\"__step\":{\"dtype\":\"F64\",\"shape\":[1],\"data_offsets\":[" + std::to_string(off) + "," + std::to_string(off + 8) + "]}}";
+            while (header.size() % 8) header += ' ';
         }
-        header += ",\"__step\":{\"dtype\":\"F64\",\"shape\":[1],\"data_offsets\":[" + std::to_string(off) + "," + std::to_string(off + 8) + "]}}";
-        while (header.size() % 8) header += ' ';
-    }
 
-    std::string tmp = std::string(path) + ".tmp";
-    FILE* f = nullptr;
-    // A file error on the writing rank must not leave the other ranks waiting in the gathers below: the writer
-    // remembers it, keeps taking part in every collective, and reports it at the end.
-    int32_t io = OXZ_OK;
-    std::string io_text;
-    auto io_failed = [&]() {
-        if (io == OXZ_OK) {
-            io = io_fail(path, "write failed", next);
-            io_text = oxz_last_error();
+        std::string tmp = std::string(path) + ".tmp";
+        FILE* f = nullptr;
+        // A file error on the writing rank must not leave the other ranks waiting in the gathers below: the writer
+        // remembers it, keeps taking part in every collective, and reports it at the end.
+        int32_t io = OXZ_OK;
+        std::string io_text;
+        auto io_failed = [&]() {
+            if (io == OXZ_OK) {
+                io = io_fail(path, "write failed", next);
+                io_text = oxz_last_error();
+            }
+            if (f) { fclose(f); f = nullptr; }
+        };
+        if (writer) {
+            f = fopen(tmp.c_str(), "wb");
+            const uint64_t hl = header.size();
+            if (!f || fwrite(&hl, 8, 1, f) != 1 || fwrite(header.data(), 1, hl, f) != hl) io_failed();
         }
-        if (f) { fclose(f); f = nullptr; }
-    };
-    if (writer) {
-        f = fopen(tmp.c_str(), "wb");
-        const uint64_t hl = header.size();
-        if (!f || fwrite(&hl, 8, 1, f) != 1 || fwrite(header.data(), 1, hl, f) != hl) io_failed();
-    }
-    std::vector<uint32_t> host;
-    int32_t st = OXZ_OK;
-    for (uint64_t i = 0; i < p->T && st == OXZ_OK; i++) {
-        for (int k = 0; k < (has_master ? 3 : 2) && st == OXZ_OK; k++) {
-            st = gather_tensor(p, comm, kinds[k], i, host);
-            if (st == OXZ_OK && f && !host.empty() && fwrite(host.data(), 4, host.size(), f) != host.size()) io_failed();
+        std::vector<uint32_t> host;
+        int32_t st = OXZ_OK;
+        for (uint64_t i = 0; i < p->T && st == OXZ_OK; i++) {
+            for (int k = 0; k < (has_master ? 3 : 2) && st == OXZ_OK; k++) {
+                st = gather_tensor(p, comm, kinds[k], i, host);
+                if (st == OXZ_OK && f && !host.empty() && fwrite(host.data(), 4, host.size(), f) != host.size()) io_failed();
+            }
         }
-    }
-    if (writer) {
-        const double step = (double)p->timestep;
-        if (st == OXZ_OK && f && fwrite(&step, 8, 1, f) != 1) io_failed();
-        if (f && fclose(f) != 0) { f = nullptr; io_failed(); }
-        f = nullptr;
-        // atomic: an error leaves an existing file unchanged (optimizer_io.rs:62-64)
-        if (st == OXZ_OK && io == OXZ_OK && rename(tmp.c_str(), path) != 0) io_failed();
-        if (st != OXZ_OK || io != OXZ_OK) remove(tmp.c_str());
-        if (st == OXZ_OK && io != OXZ_OK) {
-            oxz_set_last_error(io_text.c_str());
-            st = io;
+        if (writer) {
+            const double step = (double)p->timestep;
+            if (st == OXZ_OK && f && fwrite(&step, 8, 1, f) != 1) io_failed();
+            if (f && fclose(f) != 0) { f = nullptr; io_failed(); }
+            f = nullptr;
+            // atomic: an error leaves an existing file unchanged (optimizer_io.rs:62-64)
+            if (st == OXZ_OK && io == OXZ_OK && rename(tmp.c_str(), path) != 0) io_failed();
+            if (st != OXZ_OK || io != OXZ_OK) remove(tmp.c_str());
+            if (st == OXZ_OK && io != OXZ_OK) {
+                oxz_set_last_error(io_text.c_str());
+                st = io;
+            }
         }
-    }
-    return st;
+        return st;
+    });
 }
 
 int32_t oxz_optimizer_load(oxz_plan* p, const char* path, const char* const* names, const uint32_t* ndim,
                            const uint64_t* dims) {
-    OXZ_TRY(check_call(p, p ? p->comm : nullptr, path, names, ndim, dims, "oxz_optimizer_load"));
-    OXZ_CUDA(cudaSetDevice(p->device));
-    const char* next = "Restore the file from the run that wrote it.";
-    const char* mismatch = "The file does not match this model's trainable parameters. Resume with the config that wrote this checkpoint.";
-    FILE* f = fopen(path, "rb");
-    if (!f) return io_fail(path, "open failed", next);
-    uint64_t hl = 0;
-    if (fread(&hl, 8, 1, f) != 1 || hl == 0 || hl > (1ull << 30)) { fclose(f); return fail(OXZ_ERR_INVALID, "optimizer state file '%s': open failed: not a SafeTensors file. %s", path, next); }
-    std::string text(hl, '\0');
-    if (fread(&text[0], 1, hl, f) != hl) { fclose(f); return fail(OXZ_ERR_INVALID, "optimizer state file '%s': open failed: truncated header. %s", path, next); }
-    std::map<std::string, Entry> entries;
-    if (!parse_header(text, entries)) { fclose(f); return fail(OXZ_ERR_INVALID, "optimizer state file '%s': open failed: the header is not valid JSON. %s", path, next); }
-    const uint64_t data0 = 8 + hl;
+    return oxz::guarded("oxz_optimizer_load", [&]() -> int32_t {
+        OXZ_TRY(check_call(p, p ? p->comm : nullptr, path, names, ndim, dims, "oxz_optimizer_load"));
+        OXZ_CUDA(cudaSetDevice(p->device));
+        const char* next = "Restore the file from the run that wrote it.";
+        const char* mismatch = "The file does not match this model's trainable parameters. Resume with the config that wrote this checkpoint.";
+        FILE* f = fopen(path, "rb");
+        if (!f) return io_fail(path, "open failed", next);
+        uint64_t hl = 0;
+        if (fread(&hl, 8, 1, f) != 1 || hl == 0 || hl > (1ull << 30)) { fclose(f); return fail(OXZ_ERR_INVALID, "optimizer state file '%s': open failed: not a SafeTensors file. %s", path, next); }
+        std::string text(hl, '\0');
+        if (fread(&text[0], 1, hl, f) != hl) { fclose(f); return fail(OXZ_ERR_INVALID, "optimizer state file '%s': open failed: truncated header. %s", path, next); }
+        std::map<std::string, Entry> entries;
+        if (!parse_header(text, entries)) { fclose(f); return fail(OXZ_ERR_INVALID, "optimizer state file '%s': open failed: the header is not valid JSON. %s", path, next); }
+        const uint64_t data0 = 8 + hl;
 
-    // strict and atomic (optimizer_io.rs:113-116): every check runs before anything is loaded
-    const bool has_master = p->pdt != OXZ_F32;
-    const char* suffix[3] = {".exp_avg", ".exp_avg_sq", ".master"};
-    const int kinds[3] = {OXZ_STATE_EXP_AVG, OXZ_STATE_EXP_AVG_SQ, OXZ_STATE_MASTER};
-    size_t expected = 1;
-    {
-        const uint64_t* d = dims;
-        for (uint64_t i = 0; i < p->T; i++) {
-            for (int k = 0; k < (has_master ? 3 : 2); k++) {
-                const std::string key = std::string(names[i]) + suffix[k];
-                auto it = entries.find(key);
-                if (it == entries.end()) { fclose(f); return fail(OXZ_ERR_INVALID, "optimizer state file '%s': load failed: missing key '%s'. %s", path, key.c_str(), mismatch); }
-                const Entry& en = it->second;
-                bool same = en.shape.size() == ndim[i];
-                for (uint32_t q = 0; same && q < ndim[i]; q++) same = en.shape[q] == d[q];
-                if (!same) { fclose(f); return fail(OXZ_ERR_INVALID, "optimizer state file '%s': load failed: shape mismatch for '%s'. %s", path, key.c_str(), mismatch); }
-                if (en.dtype != "F32" || en.end - en.begin != p->numel[i] * 4) { fclose(f); return fail(OXZ_ERR_INVALID, "optimizer state file '%s': load failed: dtype mismatch for '%s' (%s). %s", path, key.c_str(), en.dtype.c_str(), mismatch); }
-                expected++;
+        // strict and atomic (optimizer_io.rs:113-116): every check runs before anything is loaded
+        const bool has_master = p->pdt != OXZ_F32;
+        const char* suffix[3] = {".exp_avg", ".exp_avg_sq", ".master"};
+        const int kinds[3] = {OXZ_STATE_EXP_AVG, OXZ_STATE_EXP_AVG_SQ, OXZ_STATE_MASTER};
+        size_t expected = 1;
+        {
+            const uint64_t* d = dims;
+            for (uint64_t i = 0; i < p->T; i++) {
+                for (int k = 0; k < (has_master ? 3 : 2); k++) {
+                    const std::string key = std::string(names[i]) + suffix[k];
+                    auto it = entries.find(key);
+                    if (it == entries.end()) { fclose(f); return fail(OXZ_ERR_INVALID, "optimizer state file '%s': load failed: missing key '%s'. %s", path, key.c_str(), mismatch); }
+                    const Entry& en = it->second;
+                    bool same = en.shape.size() == ndim[i];
+                    for (uint32_t q = 0; same && q < ndim[i]; q++) same = en.shape[q] == d[q];
+                    if (!same) { fclose(f); return fail(OXZ_ERR_INVALID, "optimizer state file '%s': load failed: shape mismatch for '%s'. %s", path, key.c_str(), mismatch); }
+                    if (en.dtype != "F32" || en.end - en.begin != p->numel[i] * 4) { fclose(f); return fail(OXZ_ERR_INVALID, "optimizer state file '%s': load failed: dtype mismatch for '%s' (%s). %s", path, key.c_str(), en.dtype.c_str(), mismatch); }
+                    expected++;
+                }
+                d += ndim[i];
             }
-            d += ndim[i];
         }
-    }
-    auto st_it = entries.find("__step");
-    if (st_it == entries.end() || st_it->second.dtype != "F64" || st_it->second.end - st_it->second.begin != 8) { fclose(f); return fail(OXZ_ERR_INVALID, "optimizer state file '%s': load failed: missing key '__step' (F64). %s", path, mismatch); }
-    if (entries.size() != expected) {
-        for (const auto& kv : entries) {
-            bool known = kv.first == "__step";
-            for (uint64_t i = 0; !known && i < p->T; i++)
-                for (int k = 0; !known && k < (has_master ? 3 : 2); k++) known = kv.first == std::string(names[i]) + suffix[k];
-            if (!known) { fclose(f); return fail(OXZ_ERR_INVALID, "optimizer state file '%s': load failed: unknown name '%s'. %s", path, kv.first.c_str(), mismatch); }
+        auto st_it = entries.find("__step");
+        if (st_it == entries.end() || st_it->second.dtype != "F64" || st_it->second.end - st_it->second.begin != 8) { fclose(f); return fail(OXZ_ERR_INVALID, "optimizer state file '%s': load failed: missing key '__step' (F64). %s", path, mismatch); }
+        if (entries.size() != expected) {
+            for (const auto& kv : entries) {
+                bool known = kv.first == "__step";
+                for (uint64_t i = 0; !known && i < p->T; i++)
+                    for (int k = 0; !known && k < (has_master ? 3 : 2); k++) known = kv.first == std::string(names[i]) + suffix[k];
+                if (!known) { fclose(f); return fail(OXZ_ERR_INVALID, "optimizer state file '%s': load failed: unknown name '%s'. %s", path, kv.first.c_str(), mismatch); }
+            }
         }
-    }
-    {
-        uint64_t need = 0;
-        for (const auto& kv : entries) need = kv.second.end > need ? kv.second.end : need;
-        if (fseek(f, 0, SEEK_END) != 0 || (uint64_t)ftell(f) < data0 + need) { fclose(f); return fail(OXZ_ERR_INVALID, "optimizer state file '%s': open failed: the data is shorter than the header says. %s", path, next); }
-    }
-    double step = 0.0;
-    if (fseek(f, (long)(data0 + st_it->second.begin), SEEK_SET) != 0 || fread(&step, 8, 1, f) != 1 || !(step >= 0.0) || step != std::floor(step)) { fclose(f); return fail(OXZ_ERR_INVALID, "optimizer state file '%s': read of '__step' failed. %s", path, next); }
+        {
+            uint64_t need = 0;
+            for (const auto& kv : entries) need = kv.second.end > need ? kv.second.end : need;
+            if (fseek(f, 0, SEEK_END) != 0 || (uint64_t)ftell(f) < data0 + need) { fclose(f); return fail(OXZ_ERR_INVALID, "optimizer state file '%s': open failed: the data is shorter than the header says. %s", path, next); }
+        }
+        double step = 0.0;
+        if (fseek(f, (long)(data0 + st_it->second.begin), SEEK_SET) != 0 || fread(&step, 8, 1, f) != 1 || !(step >= 0.0) || step != std::floor(step)) { fclose(f); return fail(OXZ_ERR_INVALID, "optimizer state file '%s': read of '__step' failed. %s", path, next); }
 
-    std::vector<float> host;
-    int32_t st = OXZ_OK;
-    for (uint64_t i = 0; i < p->T && st == OXZ_OK; i++) {
-        if (p->numel[i] == 0) continue;
-        for (int k = 0; k < (has_master ? 3 : 2) && st == OXZ_OK; k++) {
-            const Entry& en = entries[std::string(names[i]) + suffix[k]];
-            host.resize(p->numel[i]);
-            if (fseek(f, (long)(data0 + en.begin), SEEK_SET) != 0 || fread(host.data(), 4, host.size(), f) != host.size())
-                st = fail(OXZ_ERR_INVALID, "optimizer state file '%s': read of '%s%s' failed: truncated data. %s", path, names[i], suffix[k], next);
-            else st = oxz_state_import(p, kinds[k], i, host.data());
+        std::vector<float> host;
+        int32_t st = OXZ_OK;
+        for (uint64_t i = 0; i < p->T && st == OXZ_OK; i++) {
+            if (p->numel[i] == 0) continue;
+            for (int k = 0; k < (has_master ? 3 : 2) && st == OXZ_OK; k++) {
+                const Entry& en = entries[std::string(names[i]) + suffix[k]];
+                host.resize(p->numel[i]);
+                if (fseek(f, (long)(data0 + en.begin), SEEK_SET) != 0 || fread(host.data(), 4, host.size(), f) != host.size())
+                    st = fail(OXZ_ERR_INVALID, "optimizer state file '%s': read of '%s%s' failed: truncated data. %s", path, names[i], suffix[k], next);
+                else st = oxz_state_import(p, kinds[k], i, host.data());
+            }
         }
-    }
-    fclose(f);
-    if (st == OXZ_OK) p->timestep = (uint64_t)step;
-    return st;
+        fclose(f);
+        if (st == OXZ_OK) p->timestep = (uint64_t)step;
+        return st;
+    });
 }
 
 }  // extern "C"

@@ -216,209 +216,233 @@ using namespace oxz;
 extern "C" {
 
 int32_t oxz_comm_unique_id(uint8_t id[128]) {
-    const NcclApi* api;
-    OXZ_TRY(need_api(&api));
-    static_assert(sizeof(ncclUniqueId) == 128, "ncclUniqueId is 128 bytes");
-    ncclUniqueId u;
-    ncclResult_t rc = api->GetUniqueId(&u);
-    if (rc != ncclSuccess) return nccl_fail("ncclGetUniqueId", rc);
-    memcpy(id, &u, 128);
-    return OXZ_OK;
+    return oxz::guarded("oxz_comm_unique_id", [&]() -> int32_t {
+        const NcclApi* api;
+        OXZ_TRY(need_api(&api));
+        static_assert(sizeof(ncclUniqueId) == 128, "ncclUniqueId is 128 bytes");
+        ncclUniqueId u;
+        ncclResult_t rc = api->GetUniqueId(&u);
+        if (rc != ncclSuccess) return nccl_fail("ncclGetUniqueId", rc);
+        memcpy(id, &u, 128);
+        return OXZ_OK;
+    });
 }
 
 int32_t oxz_comm_init_rank(int32_t device, int32_t rank, int32_t world, const uint8_t id[128], oxz_comm** out) {
-    if (!out || !id) return fail(OXZ_ERR_INVALID, "oxz_comm_init_rank: null argument");
-    *out = nullptr;
-    if (world < 1) return fail(OXZ_ERR_INVALID, "world size is 0: a run needs at least one rank.");
-    if (rank < 0 || rank >= world)
-        return fail(OXZ_ERR_INVALID, "rank %d is not below world size %d. Pass a rank in [0, %d).", rank, world, world);
-    const NcclApi* api;
-    OXZ_TRY(need_api(&api));
-    OXZ_CUDA(cudaSetDevice(device));
-    ncclUniqueId u;
-    memcpy(&u, id, 128);
-    ncclComm_t comm;
-    ncclResult_t rc = api->CommInitRank(&comm, world, u, rank);
-    if (rc != ncclSuccess) return nccl_fail("ncclCommInitRank", rc);
-    oxz_comm* c = new oxz_comm();
-    c->nccl = comm;
-    c->rank = rank;
-    c->world = world;
-    c->device = device;
-    int32_t s = finish_comm(c);
-    if (s != OXZ_OK) {
-        api->CommAbort(comm);
-        delete c;
-        return s;
-    }
-    *out = c;
-    return OXZ_OK;
+    return oxz::guarded("oxz_comm_init_rank", [&]() -> int32_t {
+        if (!out || !id) return fail(OXZ_ERR_INVALID, "oxz_comm_init_rank: null argument");
+        *out = nullptr;
+        if (world < 1) return fail(OXZ_ERR_INVALID, "world size is 0: a run needs at least one rank.");
+        if (rank < 0 || rank >= world)
+            return fail(OXZ_ERR_INVALID, "rank %d is not below world size %d. Pass a rank in [0, %d).", rank, world, world);
+        const NcclApi* api;
+        OXZ_TRY(need_api(&api));
+        OXZ_CUDA(cudaSetDevice(device));
+        ncclUniqueId u;
+        memcpy(&u, id, 128);
+        ncclComm_t comm;
+        ncclResult_t rc = api->CommInitRank(&comm, world, u, rank);
+        if (rc != ncclSuccess) return nccl_fail("ncclCommInitRank", rc);
+        oxz_comm* c = new oxz_comm();
+        c->nccl = comm;
+        c->rank = rank;
+        c->world = world;
+        c->device = device;
+        int32_t s = finish_comm(c);
+        if (s != OXZ_OK) {
+            api->CommAbort(comm);
+            delete c;
+            return s;
+        }
+        *out = c;
+        return OXZ_OK;
+    });
 }
 
 int32_t oxz_comm_init_all(int32_t n, const int32_t* devices, oxz_comm** out) {
-    if (!out || !devices) return fail(OXZ_ERR_INVALID, "oxz_comm_init_all: null argument");
-    if (n < 1 || n > (int32_t)MAX_PEERS) return fail(OXZ_ERR_INVALID, "oxz_comm_init_all: %d ranks is outside [1, %u]", n, MAX_PEERS);
-    const NcclApi* api;
-    OXZ_TRY(need_api(&api));
-    std::vector<ncclComm_t> comms(n);
-    ncclResult_t rc = api->CommInitAll(comms.data(), n, devices);
-    if (rc != ncclSuccess) return nccl_fail("ncclCommInitAll", rc);
-    for (int i = 0; i < n; i++) {
-        oxz_comm* c = new oxz_comm();
-        c->nccl = comms[i];
-        c->rank = i;
-        c->world = n;
-        c->device = devices[i];
-        out[i] = c;
-        int32_t s = finish_comm(c);
-        if (s != OXZ_OK) {
-            for (int j = 0; j <= i; j++) { oxz_comm_destroy(out[j]); out[j] = nullptr; }
-            for (int j = i + 1; j < n; j++) api->CommAbort(comms[j]);
-            return s;
+    return oxz::guarded("oxz_comm_init_all", [&]() -> int32_t {
+        if (!out || !devices) return fail(OXZ_ERR_INVALID, "oxz_comm_init_all: null argument");
+        if (n < 1 || n > (int32_t)MAX_PEERS) return fail(OXZ_ERR_INVALID, "oxz_comm_init_all: %d ranks is outside [1, %u]", n, MAX_PEERS);
+        const NcclApi* api;
+        OXZ_TRY(need_api(&api));
+        std::vector<ncclComm_t> comms(n);
+        ncclResult_t rc = api->CommInitAll(comms.data(), n, devices);
+        if (rc != ncclSuccess) return nccl_fail("ncclCommInitAll", rc);
+        for (int i = 0; i < n; i++) {
+            oxz_comm* c = new oxz_comm();
+            c->nccl = comms[i];
+            c->rank = i;
+            c->world = n;
+            c->device = devices[i];
+            out[i] = c;
+            int32_t s = finish_comm(c);
+            if (s != OXZ_OK) {
+                for (int j = 0; j <= i; j++) { oxz_comm_destroy(out[j]); out[j] = nullptr; }
+                for (int j = i + 1; j < n; j++) api->CommAbort(comms[j]);
+                return s;
+            }
         }
-    }
-    return OXZ_OK;
+        return OXZ_OK;
+    });
 }
 
 int32_t oxz_comm_init_local(int32_t n, const int32_t* devices, double timeout_seconds, oxz_comm** out) {
-    if (!out) return fail(OXZ_ERR_INVALID, "oxz_comm_init_local: null argument");
-    if (n < 1 || n > (int32_t)MAX_PEERS) return fail(OXZ_ERR_INVALID, "oxz_comm_init_local: %d ranks is outside [1, %u]", n, MAX_PEERS);
-    if (!(timeout_seconds > 0.0)) return fail(OXZ_ERR_INVALID, "oxz_comm_init_local: the timeout %g s must be positive", timeout_seconds);
-    auto group = std::make_shared<LocalGroup>();
-    group->world = n;
-    group->timeout_s = timeout_seconds;
-    group->slots.resize(n);
-    for (int i = 0; i < n; i++) {
-        oxz_comm* c = new oxz_comm();
-        c->kind = 1;
-        c->local = group;
-        c->rank = i;
-        c->world = n;
-        c->device = devices ? devices[i] : -1;
-        if (c->device >= 0) {
-            int32_t s = finish_comm(c);
-            if (s != OXZ_OK) return s;
+    return oxz::guarded("oxz_comm_init_local", [&]() -> int32_t {
+        if (!out) return fail(OXZ_ERR_INVALID, "oxz_comm_init_local: null argument");
+        if (n < 1 || n > (int32_t)MAX_PEERS) return fail(OXZ_ERR_INVALID, "oxz_comm_init_local: %d ranks is outside [1, %u]", n, MAX_PEERS);
+        if (!(timeout_seconds > 0.0)) return fail(OXZ_ERR_INVALID, "oxz_comm_init_local: the timeout %g s must be positive", timeout_seconds);
+        auto group = std::make_shared<LocalGroup>();
+        group->world = n;
+        group->timeout_s = timeout_seconds;
+        group->slots.resize(n);
+        for (int i = 0; i < n; i++) {
+            oxz_comm* c = new oxz_comm();
+            c->kind = 1;
+            c->local = group;
+            c->rank = i;
+            c->world = n;
+            c->device = devices ? devices[i] : -1;
+            if (c->device >= 0) {
+                int32_t s = finish_comm(c);
+                if (s != OXZ_OK) return s;
+            }
+            out[i] = c;
         }
-        out[i] = c;
-    }
-    return OXZ_OK;
+        return OXZ_OK;
+    });
 }
 
 int32_t oxz_comm_world_size(const oxz_comm* c, int32_t* world) {
-    if (!c || !world) return fail(OXZ_ERR_INVALID, "oxz_comm_world_size: null argument");
-    *world = c->world;
-    return OXZ_OK;
+    return oxz::guarded("oxz_comm_world_size", [&]() -> int32_t {
+        if (!c || !world) return fail(OXZ_ERR_INVALID, "oxz_comm_world_size: null argument");
+        *world = c->world;
+        return OXZ_OK;
+    });
 }
 
 int32_t oxz_comm_rank(const oxz_comm* c, int32_t* rank) {
-    if (!c || !rank) return fail(OXZ_ERR_INVALID, "oxz_comm_rank: null argument");
-    *rank = c->rank;
-    return OXZ_OK;
+    return oxz::guarded("oxz_comm_rank", [&]() -> int32_t {
+        if (!c || !rank) return fail(OXZ_ERR_INVALID, "oxz_comm_rank: null argument");
+        *rank = c->rank;
+        return OXZ_OK;
+    });
 }
 
 int32_t oxz_comm_abort(oxz_comm* c) {
-    if (!c) return fail(OXZ_ERR_INVALID, "oxz_comm_abort: null communicator");
-    int expected = 0;
-    if (!c->aborted.compare_exchange_strong(expected, 1)) return OXZ_OK;  // the first abort wins
-    if (c->kind == 1) {
-        std::lock_guard<std::mutex> lock(c->local->mu);
-        c->local->aborted = true;
-        c->local->cv.notify_all();
+    return oxz::guarded("oxz_comm_abort", [&]() -> int32_t {
+        if (!c) return fail(OXZ_ERR_INVALID, "oxz_comm_abort: null communicator");
+        int expected = 0;
+        if (!c->aborted.compare_exchange_strong(expected, 1)) return OXZ_OK;  // the first abort wins
+        if (c->kind == 1) {
+            std::lock_guard<std::mutex> lock(c->local->mu);
+            c->local->aborted = true;
+            c->local->cv.notify_all();
+            return OXZ_OK;
+        }
+        const NcclApi* api = nccl_api();
+        if (api && c->nccl) {
+            ncclResult_t rc = api->CommAbort((ncclComm_t)c->nccl);
+            c->nccl = nullptr;
+            if (rc != ncclSuccess) return nccl_fail("ncclCommAbort", rc);
+        }
         return OXZ_OK;
-    }
-    const NcclApi* api = nccl_api();
-    if (api && c->nccl) {
-        ncclResult_t rc = api->CommAbort((ncclComm_t)c->nccl);
-        c->nccl = nullptr;
-        if (rc != ncclSuccess) return nccl_fail("ncclCommAbort", rc);
-    }
-    return OXZ_OK;
+    });
 }
 
 int32_t oxz_comm_destroy(oxz_comm* c) {
-    if (!c) return OXZ_OK;
-    const NcclApi* api = c->kind == 0 ? nccl_api() : nullptr;
-    if (c->device >= 0) cudaSetDevice(c->device);
-    if (api && c->nccl && !c->aborted.load()) api->CommDestroy((ncclComm_t)c->nccl);
-    if (c->d_small) cudaFree(c->d_small);
-    if (c->stream) cudaStreamDestroy(c->stream);
-    delete c;
-    return OXZ_OK;
+    return oxz::guarded("oxz_comm_destroy", [&]() -> int32_t {
+        if (!c) return OXZ_OK;
+        const NcclApi* api = c->kind == 0 ? nccl_api() : nullptr;
+        if (c->device >= 0) cudaSetDevice(c->device);
+        if (api && c->nccl && !c->aborted.load()) api->CommDestroy((ncclComm_t)c->nccl);
+        if (c->d_small) cudaFree(c->d_small);
+        if (c->stream) cudaStreamDestroy(c->stream);
+        delete c;
+        return OXZ_OK;
+    });
 }
 
 int32_t oxz_allreduce_i64x2(oxz_comm* c, int64_t inout[2]) {
-    OXZ_TRY(comm_check(c, "oxz_allreduce_i64x2"));
-    if (!inout) return fail(OXZ_ERR_INVALID, "oxz_allreduce_i64x2: null argument");
-    if (c->world <= 1) return OXZ_OK;
-    for (int i = 0; i < 2; i++)
-        if (inout[i] < 0) return fail(OXZ_ERR_INVALID, "step count %lld is negative. Every rank must pass counts of 0 or more", (long long)inout[i]);
-    if (c->kind == 1) return local_sum<int64_t>(c, inout, 2, "the step-count sum");
-    const NcclApi* api = nccl_api();
-    OXZ_CUDA(cudaSetDevice(c->device));
-    OXZ_CUDA(cudaMemcpyAsync(c->d_small, inout, 16, cudaMemcpyHostToDevice, c->stream));
-    ncclResult_t rc = api->AllReduce(c->d_small, c->d_small, 2, ncclInt64, ncclSum, (ncclComm_t)c->nccl, c->stream);
-    if (rc != ncclSuccess) return nccl_fail("the step-count sum", rc);
-    OXZ_CUDA(cudaMemcpyAsync(inout, c->d_small, 16, cudaMemcpyDeviceToHost, c->stream));
-    OXZ_CUDA(cudaStreamSynchronize(c->stream));
-    if (c->aborted.load()) return fail(OXZ_ERR_ABORTED, "oxz_allreduce_i64x2: the communicator was aborted");
-    return OXZ_OK;
+    return oxz::guarded("oxz_allreduce_i64x2", [&]() -> int32_t {
+        OXZ_TRY(comm_check(c, "oxz_allreduce_i64x2"));
+        if (!inout) return fail(OXZ_ERR_INVALID, "oxz_allreduce_i64x2: null argument");
+        if (c->world <= 1) return OXZ_OK;
+        for (int i = 0; i < 2; i++)
+            if (inout[i] < 0) return fail(OXZ_ERR_INVALID, "step count %lld is negative. Every rank must pass counts of 0 or more", (long long)inout[i]);
+        if (c->kind == 1) return local_sum<int64_t>(c, inout, 2, "the step-count sum");
+        const NcclApi* api = nccl_api();
+        OXZ_CUDA(cudaSetDevice(c->device));
+        OXZ_CUDA(cudaMemcpyAsync(c->d_small, inout, 16, cudaMemcpyHostToDevice, c->stream));
+        ncclResult_t rc = api->AllReduce(c->d_small, c->d_small, 2, ncclInt64, ncclSum, (ncclComm_t)c->nccl, c->stream);
+        if (rc != ncclSuccess) return nccl_fail("the step-count sum", rc);
+        OXZ_CUDA(cudaMemcpyAsync(inout, c->d_small, 16, cudaMemcpyDeviceToHost, c->stream));
+        OXZ_CUDA(cudaStreamSynchronize(c->stream));
+        if (c->aborted.load()) return fail(OXZ_ERR_ABORTED, "oxz_allreduce_i64x2: the communicator was aborted");
+        return OXZ_OK;
+    });
 }
 
 int32_t oxz_allreduce_f64(oxz_comm* c, double* inout, uint32_t n) {
-    OXZ_TRY(comm_check(c, "oxz_allreduce_f64"));
-    if (!inout && n) return fail(OXZ_ERR_INVALID, "oxz_allreduce_f64: null argument");
-    if (n > 16) return fail(OXZ_ERR_INVALID, "oxz_allreduce_f64: %u values, at most 16", n);
-    if (c->world <= 1 || n == 0) return OXZ_OK;
-    if (c->kind == 1) return local_sum<double>(c, inout, n, "the loss sum");
-    const NcclApi* api = nccl_api();
-    OXZ_CUDA(cudaSetDevice(c->device));
-    OXZ_CUDA(cudaMemcpyAsync(c->d_small, inout, n * 8, cudaMemcpyHostToDevice, c->stream));
-    ncclResult_t rc = api->AllReduce(c->d_small, c->d_small, n, ncclFloat64, ncclSum, (ncclComm_t)c->nccl, c->stream);
-    if (rc != ncclSuccess) return nccl_fail("the loss sum", rc);
-    OXZ_CUDA(cudaMemcpyAsync(inout, c->d_small, n * 8, cudaMemcpyDeviceToHost, c->stream));
-    OXZ_CUDA(cudaStreamSynchronize(c->stream));
-    if (c->aborted.load()) return fail(OXZ_ERR_ABORTED, "oxz_allreduce_f64: the communicator was aborted");
-    return OXZ_OK;
+    return oxz::guarded("oxz_allreduce_f64", [&]() -> int32_t {
+        OXZ_TRY(comm_check(c, "oxz_allreduce_f64"));
+        if (!inout && n) return fail(OXZ_ERR_INVALID, "oxz_allreduce_f64: null argument");
+        if (n > 16) return fail(OXZ_ERR_INVALID, "oxz_allreduce_f64: %u values, at most 16", n);
+        if (c->world <= 1 || n == 0) return OXZ_OK;
+        if (c->kind == 1) return local_sum<double>(c, inout, n, "the loss sum");
+        const NcclApi* api = nccl_api();
+        OXZ_CUDA(cudaSetDevice(c->device));
+        OXZ_CUDA(cudaMemcpyAsync(c->d_small, inout, n * 8, cudaMemcpyHostToDevice, c->stream));
+        ncclResult_t rc = api->AllReduce(c->d_small, c->d_small, n, ncclFloat64, ncclSum, (ncclComm_t)c->nccl, c->stream);
+        if (rc != ncclSuccess) return nccl_fail("the loss sum", rc);
+        OXZ_CUDA(cudaMemcpyAsync(inout, c->d_small, n * 8, cudaMemcpyDeviceToHost, c->stream));
+        OXZ_CUDA(cudaStreamSynchronize(c->stream));
+        if (c->aborted.load()) return fail(OXZ_ERR_ABORTED, "oxz_allreduce_f64: the communicator was aborted");
+        return OXZ_OK;
+    });
 }
 
 int32_t oxz_broadcast(oxz_comm* c, void* device_ptr, uint64_t bytes, int32_t root) {
-    OXZ_TRY(comm_check(c, "oxz_broadcast"));
-    if (root < 0 || root >= c->world) return fail(OXZ_ERR_INVALID, "oxz_broadcast: root %d of world %d", root, c->world);
-    if (c->world <= 1 || bytes == 0) return OXZ_OK;
-    if (!device_ptr) return fail(OXZ_ERR_INVALID, "oxz_broadcast: null buffer");
-    if (c->kind == 1) {
-        // through host memory: the root's bytes are what every rank leaves with
+    return oxz::guarded("oxz_broadcast", [&]() -> int32_t {
+        OXZ_TRY(comm_check(c, "oxz_broadcast"));
+        if (root < 0 || root >= c->world) return fail(OXZ_ERR_INVALID, "oxz_broadcast: root %d of world %d", root, c->world);
+        if (c->world <= 1 || bytes == 0) return OXZ_OK;
+        if (!device_ptr) return fail(OXZ_ERR_INVALID, "oxz_broadcast: null buffer");
+        if (c->kind == 1) {
+            // through host memory: the root's bytes are what every rank leaves with
+            OXZ_CUDA(cudaSetDevice(c->device));
+            std::vector<uint8_t> host(c->rank == root ? bytes : 0);
+            if (c->rank == root) OXZ_CUDA(cudaMemcpy(host.data(), device_ptr, bytes, cudaMemcpyDeviceToHost));
+            std::vector<uint8_t> got(bytes);
+            OXZ_TRY(local_exchange(c, host.data(), host.size(), got.data(), bytes,
+                                   [root](const auto& slots, auto& result) { result = slots[root]; }, "oxz_broadcast"));
+            if (c->rank != root) OXZ_CUDA(cudaMemcpy(device_ptr, got.data(), bytes, cudaMemcpyHostToDevice));
+            return OXZ_OK;
+        }
+        const NcclApi* api = nccl_api();
         OXZ_CUDA(cudaSetDevice(c->device));
-        std::vector<uint8_t> host(c->rank == root ? bytes : 0);
-        if (c->rank == root) OXZ_CUDA(cudaMemcpy(host.data(), device_ptr, bytes, cudaMemcpyDeviceToHost));
-        std::vector<uint8_t> got(bytes);
-        OXZ_TRY(local_exchange(c, host.data(), host.size(), got.data(), bytes,
-                               [root](const auto& slots, auto& result) { result = slots[root]; }, "oxz_broadcast"));
-        if (c->rank != root) OXZ_CUDA(cudaMemcpy(device_ptr, got.data(), bytes, cudaMemcpyHostToDevice));
+        ncclResult_t rc = api->Broadcast(device_ptr, device_ptr, bytes, ncclInt8, root, (ncclComm_t)c->nccl, c->stream);
+        if (rc != ncclSuccess) return nccl_fail("ncclBroadcast", rc);
+        OXZ_CUDA(cudaStreamSynchronize(c->stream));
         return OXZ_OK;
-    }
-    const NcclApi* api = nccl_api();
-    OXZ_CUDA(cudaSetDevice(c->device));
-    ncclResult_t rc = api->Broadcast(device_ptr, device_ptr, bytes, ncclInt8, root, (ncclComm_t)c->nccl, c->stream);
-    if (rc != ncclSuccess) return nccl_fail("ncclBroadcast", rc);
-    OXZ_CUDA(cudaStreamSynchronize(c->stream));
-    return OXZ_OK;
+    });
 }
 
 int32_t oxz_barrier(oxz_comm* c) {
-    OXZ_TRY(comm_check(c, "oxz_barrier"));
-    if (c->world <= 1) return OXZ_OK;
-    if (c->kind == 1) {
-        uint8_t z = 0;
-        return local_exchange(c, &z, 0, nullptr, 0, [](const auto&, auto&) {}, "oxz_barrier");
-    }
-    const NcclApi* api = nccl_api();
-    OXZ_CUDA(cudaSetDevice(c->device));
-    int32_t* flag = reinterpret_cast<int32_t*>(static_cast<char*>(c->d_small) + 256);
-    ncclResult_t rc = api->AllReduce(flag, flag, 1, ncclInt32, ncclSum, (ncclComm_t)c->nccl, c->stream);
-    if (rc != ncclSuccess) return nccl_fail("barrier", rc);
-    OXZ_CUDA(cudaStreamSynchronize(c->stream));
-    return OXZ_OK;
+    return oxz::guarded("oxz_barrier", [&]() -> int32_t {
+        OXZ_TRY(comm_check(c, "oxz_barrier"));
+        if (c->world <= 1) return OXZ_OK;
+        if (c->kind == 1) {
+            uint8_t z = 0;
+            return local_exchange(c, &z, 0, nullptr, 0, [](const auto&, auto&) {}, "oxz_barrier");
+        }
+        const NcclApi* api = nccl_api();
+        OXZ_CUDA(cudaSetDevice(c->device));
+        int32_t* flag = reinterpret_cast<int32_t*>(static_cast<char*>(c->d_small) + 256);
+        ncclResult_t rc = api->AllReduce(flag, flag, 1, ncclInt32, ncclSum, (ncclComm_t)c->nccl, c->stream);
+        if (rc != ncclSuccess) return nccl_fail("barrier", rc);
+        OXZ_CUDA(cudaStreamSynchronize(c->stream));
+        return OXZ_OK;
+    });
 }
 
 }  // extern "C"

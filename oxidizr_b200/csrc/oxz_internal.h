@@ -6,6 +6,8 @@
 
 #include <atomic>
 #include <memory>
+#include <new>
+#include <stdexcept>
 #include <string>
 #include <vector>
 
@@ -16,6 +18,21 @@ namespace oxz {
 // ---- errors: thread-local text behind oxz_last_error() ----
 int32_t fail(int32_t status, const char* fmt, ...) __attribute__((format(printf, 2, 3)));
 void clear_error();
+
+// Runs the body of a C entry point: whatever C++ throws inside (an allocation that fails, say) becomes a status and a
+// message; no exception leaves the library, as a caller across a C boundary cannot catch one.
+template <class F>
+inline int32_t guarded(const char* who, F&& body) noexcept {
+    try {
+        return body();
+    } catch (const std::bad_alloc&) {
+        return fail(OXZ_ERR_STATE, "%s: out of host memory", who);
+    } catch (const std::exception& e) {
+        return fail(OXZ_ERR_STATE, "%s: %s", who, e.what());
+    } catch (...) {
+        return fail(OXZ_ERR_STATE, "%s: an unknown C++ exception", who);
+    }
+}
 
 #define OXZ_CUDA(expr)                                                                              \
     do {                                                                                            \

@@ -380,63 +380,67 @@ static int32_t finish_open(oxz_loader* l, uint64_t seq_len, uint64_t rank_batch_
 
 int32_t oxz_loader_open(const char* path, uint64_t seq_len, uint64_t rank_batch_size, uint64_t rank, uint64_t world,
                         uint64_t first_row, uint64_t end_row, int32_t device, oxz_loader** out) {
-    if (!path || !out) return fail(OXZ_ERR_INVALID, "oxz_loader_open: null argument");
-    *out = nullptr;
-    if (seq_len == 0) return fail(OXZ_ERR_DATA, "model.max_seq_len is 0: a row needs at least one input and one target token");
-    oxz_loader* l = new oxz_loader();
-    int32_t s = open_parts(l, &path, 1, seq_len);
-    if (s == OXZ_OK) {
-        if (end_row == 0) end_row = l->total_rows;
-        if (first_row >= end_row || end_row > l->total_rows)
-            s = fail(OXZ_ERR_DATA, "row range [%llu, %llu) does not fit the data's %llu whole rows", (unsigned long long)first_row,
-                     (unsigned long long)end_row, (unsigned long long)l->total_rows);
-    }
-    if (s == OXZ_OK) {
-        l->ranges.push(first_row, end_row);
-        s = finish_open(l, seq_len, rank_batch_size, rank, world, device);
-    }
-    if (s != OXZ_OK) {
-        release(l);
-        return s;
-    }
-    *out = l;
-    return OXZ_OK;
+    return oxz::guarded("oxz_loader_open", [&]() -> int32_t {
+        if (!path || !out) return fail(OXZ_ERR_INVALID, "oxz_loader_open: null argument");
+        *out = nullptr;
+        if (seq_len == 0) return fail(OXZ_ERR_DATA, "model.max_seq_len is 0: a row needs at least one input and one target token");
+        oxz_loader* l = new oxz_loader();
+        int32_t s = open_parts(l, &path, 1, seq_len);
+        if (s == OXZ_OK) {
+            if (end_row == 0) end_row = l->total_rows;
+            if (first_row >= end_row || end_row > l->total_rows)
+                s = fail(OXZ_ERR_DATA, "row range [%llu, %llu) does not fit the data's %llu whole rows", (unsigned long long)first_row,
+                         (unsigned long long)end_row, (unsigned long long)l->total_rows);
+        }
+        if (s == OXZ_OK) {
+            l->ranges.push(first_row, end_row);
+            s = finish_open(l, seq_len, rank_batch_size, rank, world, device);
+        }
+        if (s != OXZ_OK) {
+            release(l);
+            return s;
+        }
+        *out = l;
+        return OXZ_OK;
+    });
 }
 
 int32_t oxz_loader_open_files(const char* const* paths, uint32_t n_paths, uint64_t seq_len, uint64_t rank_batch_size,
                               uint64_t rank, uint64_t world, const uint64_t* spans, uint32_t n_spans, int32_t device,
                               oxz_loader** out) {
-    if (!out || (n_paths && !paths) || (n_spans && !spans)) return fail(OXZ_ERR_INVALID, "oxz_loader_open_files: null argument");
-    *out = nullptr;
-    if (seq_len == 0) return fail(OXZ_ERR_DATA, "model.max_seq_len is 0: a row needs at least one input and one target token");
-    oxz_loader* l = new oxz_loader();
-    int32_t s = open_parts(l, paths, n_paths, seq_len);
-    const uint64_t total = l->total_rows;
-    if (s == OXZ_OK && n_spans == 0) {  // RowRanges::whole
-        if (total) l->ranges.push(0, total);
-    }
-    // RowRanges::new (src/data/row_ranges.rs:40-76)
-    uint64_t prev_end = 0;
-    for (uint32_t i = 0; s == OXZ_OK && i < n_spans; i++) {
-        const uint64_t a = spans[2 * i], b = spans[2 * i + 1];
-        if (a >= b || b > total)
-            s = fail(OXZ_ERR_DATA, "row range [%llu, %llu) is not a non-empty range inside the %llu whole rows of this data. Pick a range inside [0, %llu).",
-                     (unsigned long long)a, (unsigned long long)b, (unsigned long long)total, (unsigned long long)total);
-        else if (i > 0 && a < prev_end)
-            s = fail(OXZ_ERR_DATA, "row range [%llu, %llu) starts before row %llu, the end of the range before it. Pass ranges in ascending order without overlap.",
-                     (unsigned long long)a, (unsigned long long)b, (unsigned long long)prev_end);
-        else {
-            l->ranges.push(a, b);
-            prev_end = b;
+    return oxz::guarded("oxz_loader_open_files", [&]() -> int32_t {
+        if (!out || (n_paths && !paths) || (n_spans && !spans)) return fail(OXZ_ERR_INVALID, "oxz_loader_open_files: null argument");
+        *out = nullptr;
+        if (seq_len == 0) return fail(OXZ_ERR_DATA, "model.max_seq_len is 0: a row needs at least one input and one target token");
+        oxz_loader* l = new oxz_loader();
+        int32_t s = open_parts(l, paths, n_paths, seq_len);
+        const uint64_t total = l->total_rows;
+        if (s == OXZ_OK && n_spans == 0) {  // RowRanges::whole
+            if (total) l->ranges.push(0, total);
         }
-    }
-    if (s == OXZ_OK) s = finish_open(l, seq_len, rank_batch_size, rank, world, device);
-    if (s != OXZ_OK) {
-        release(l);
-        return s;
-    }
-    *out = l;
-    return OXZ_OK;
+        // RowRanges::new (src/data/row_ranges.rs:40-76)
+        uint64_t prev_end = 0;
+        for (uint32_t i = 0; s == OXZ_OK && i < n_spans; i++) {
+            const uint64_t a = spans[2 * i], b = spans[2 * i + 1];
+            if (a >= b || b > total)
+                s = fail(OXZ_ERR_DATA, "row range [%llu, %llu) is not a non-empty range inside the %llu whole rows of this data. Pick a range inside [0, %llu).",
+                         (unsigned long long)a, (unsigned long long)b, (unsigned long long)total, (unsigned long long)total);
+            else if (i > 0 && a < prev_end)
+                s = fail(OXZ_ERR_DATA, "row range [%llu, %llu) starts before row %llu, the end of the range before it. Pass ranges in ascending order without overlap.",
+                         (unsigned long long)a, (unsigned long long)b, (unsigned long long)prev_end);
+            else {
+                l->ranges.push(a, b);
+                prev_end = b;
+            }
+        }
+        if (s == OXZ_OK) s = finish_open(l, seq_len, rank_batch_size, rank, world, device);
+        if (s != OXZ_OK) {
+            release(l);
+            return s;
+        }
+        *out = l;
+        return OXZ_OK;
+    });
 }
 
 // quotas (src/data/mixture/quota.rs:22-57): floor of each share, the rows left over one each by largest remainder,
@@ -472,128 +476,144 @@ static void mixture_quotas(const double* weights, uint32_t n, uint64_t rows, std
 }
 
 int32_t oxz_mixture_quotas(const double* weights, uint32_t n_weights, uint64_t rows, uint64_t* quotas) {
-    if (!weights || !quotas || n_weights == 0) return fail(OXZ_ERR_INVALID, "oxz_mixture_quotas: null argument");
-    for (uint32_t i = 0; i < n_weights; i++)
-        if (!(std::isfinite(weights[i]) && weights[i] > 0.0))
-            return fail(OXZ_ERR_DATA, "trainer.data.sources[%u].weight is %g: a weight must be a finite number above 0. Set it to the source's share, for example 1.0.", i, weights[i]);
-    std::vector<uint64_t> q;
-    mixture_quotas(weights, n_weights, rows, q);
-    for (uint32_t i = 0; i < n_weights; i++) quotas[i] = q[i];
-    return OXZ_OK;
+    return oxz::guarded("oxz_mixture_quotas", [&]() -> int32_t {
+        if (!weights || !quotas || n_weights == 0) return fail(OXZ_ERR_INVALID, "oxz_mixture_quotas: null argument");
+        for (uint32_t i = 0; i < n_weights; i++)
+            if (!(std::isfinite(weights[i]) && weights[i] > 0.0))
+                return fail(OXZ_ERR_DATA, "trainer.data.sources[%u].weight is %g: a weight must be a finite number above 0. Set it to the source's share, for example 1.0.", i, weights[i]);
+        std::vector<uint64_t> q;
+        mixture_quotas(weights, n_weights, rows, q);
+        for (uint32_t i = 0; i < n_weights; i++) quotas[i] = q[i];
+        return OXZ_OK;
+    });
 }
 
 int32_t oxz_loader_set_mixture(oxz_loader* l, const double* weights, uint32_t n_weights, int32_t has_rows_per_epoch,
                                uint64_t rows_per_epoch) {
-    if (!l || (n_weights && !weights)) return fail(OXZ_ERR_INVALID, "oxz_loader_set_mixture: null argument");
-    const uint64_t MAX_ROWS = 1ull << 28;
-    if (n_weights != l->parts.size())
-        return fail(OXZ_ERR_DATA, "trainer.data.sources sets %u weight(s), and the loader reads %zu source(s). Set one weight per source in trainer.data.sources, and remove the -d flags.",
-                    n_weights, l->parts.size());
-    if (n_weights > 65536)
-        return fail(OXZ_ERR_DATA, "trainer.data.sources lists %u weighted sources, more than the 65536 a mixture can index. Merge some sources into one file.", n_weights);
-    std::unique_ptr<Mixture> m(new Mixture());
-    // the training rows of each source: the loader's ranges cut at the source's bounds (src/data/mixture/loader.rs:60-84)
-    for (uint32_t i = 0; i < n_weights; i++) {
-        const Part& part = l->parts[i];
-        Ranges r;
-        for (size_t k = 0; k < l->ranges.start.size(); k++) {
-            const uint64_t a = std::max(l->ranges.start[k], part.first_row), b = std::min(l->ranges.end[k], part.first_row + part.rows);
-            if (a < b) r.push(a, b);
-        }
-        if (!(std::isfinite(weights[i]) && weights[i] > 0.0))
-            return fail(OXZ_ERR_DATA, "trainer.data.sources[%u].weight is %g: a weight must be a finite number above 0. Set it to the source's share, for example 1.0.", i, weights[i]);
-        if (r.len == 0)
-            return fail(OXZ_ERR_DATA, "trainer.data.sources[%u] holds no training rows, and its weight %g asks for rows. Remove the source, or use a file of at least one row of model.max_seq_len + 1 tokens outside the holdout.", i, weights[i]);
-        if (r.len > 0xffffffffull)
-            return fail(OXZ_ERR_DATA, "trainer.data.sources[%u] holds %llu training rows, more than the 4294967295 a row order can index. Split the file.", i, (unsigned long long)r.len);
-        m->sources.push_back(std::move(r));
-    }
-    uint64_t total = 0;
-    for (const Ranges& r : m->sources) total += r.len;
-    const uint64_t rows = has_rows_per_epoch ? rows_per_epoch : total;
-    if (rows == 0 || rows > MAX_ROWS)
-        return fail(OXZ_ERR_DATA, "trainer.data.rows_per_epoch is %llu: an epoch needs at least 1 row and at most %llu rows, because the schedule keeps 2 bytes per row. Set trainer.data.rows_per_epoch inside that range.",
-                    (unsigned long long)rows, (unsigned long long)MAX_ROWS);
-    m->weights.assign(weights, weights + n_weights);
-    m->requested = has_rows_per_epoch != 0;
-    m->rows_per_epoch = rows;
-    mixture_quotas(weights, n_weights, rows, m->quotas);
-    // smooth weighted round-robin over the quotas (src/data/mixture/schedule.rs:103-122)
-    {
-        std::vector<int64_t> credit(n_weights, 0);
-        m->schedule.reserve(rows);
-        for (uint64_t k = 0; k < rows; k++) {
-            uint32_t pick = 0;
-            for (uint32_t i = 0; i < n_weights; i++) {
-                credit[i] += (int64_t)m->quotas[i];
-                if (credit[i] > credit[pick]) pick = i;
+    return oxz::guarded("oxz_loader_set_mixture", [&]() -> int32_t {
+        if (!l || (n_weights && !weights)) return fail(OXZ_ERR_INVALID, "oxz_loader_set_mixture: null argument");
+        const uint64_t MAX_ROWS = 1ull << 28;
+        if (n_weights != l->parts.size())
+            return fail(OXZ_ERR_DATA, "trainer.data.sources sets %u weight(s), and the loader reads %zu source(s). Set one weight per source in trainer.data.sources, and remove the -d flags.",
+                        n_weights, l->parts.size());
+        if (n_weights > 65536)
+            return fail(OXZ_ERR_DATA, "trainer.data.sources lists %u weighted sources, more than the 65536 a mixture can index. Merge some sources into one file.", n_weights);
+        std::unique_ptr<Mixture> m(new Mixture());
+        // the training rows of each source: the loader's ranges cut at the source's bounds (src/data/mixture/loader.rs:60-84)
+        for (uint32_t i = 0; i < n_weights; i++) {
+            const Part& part = l->parts[i];
+            Ranges r;
+            for (size_t k = 0; k < l->ranges.start.size(); k++) {
+                const uint64_t a = std::max(l->ranges.start[k], part.first_row), b = std::min(l->ranges.end[k], part.first_row + part.rows);
+                if (a < b) r.push(a, b);
             }
-            credit[pick] -= (int64_t)rows;
-            m->schedule.push_back((uint16_t)pick);
+            if (!(std::isfinite(weights[i]) && weights[i] > 0.0))
+                return fail(OXZ_ERR_DATA, "trainer.data.sources[%u].weight is %g: a weight must be a finite number above 0. Set it to the source's share, for example 1.0.", i, weights[i]);
+            if (r.len == 0)
+                return fail(OXZ_ERR_DATA, "trainer.data.sources[%u] holds no training rows, and its weight %g asks for rows. Remove the source, or use a file of at least one row of model.max_seq_len + 1 tokens outside the holdout.", i, weights[i]);
+            if (r.len > 0xffffffffull)
+                return fail(OXZ_ERR_DATA, "trainer.data.sources[%u] holds %llu training rows, more than the 4294967295 a row order can index. Split the file.", i, (unsigned long long)r.len);
+            m->sources.push_back(std::move(r));
         }
-        std::vector<uint32_t> counts(n_weights, 0);
-        for (uint64_t k = 0; k < rows; k++) {
-            if (k % Mixture::BLOCK == 0) m->prefix.insert(m->prefix.end(), counts.begin(), counts.end());
-            counts[m->schedule[k]]++;
+        uint64_t total = 0;
+        for (const Ranges& r : m->sources) total += r.len;
+        const uint64_t rows = has_rows_per_epoch ? rows_per_epoch : total;
+        if (rows == 0 || rows > MAX_ROWS)
+            return fail(OXZ_ERR_DATA, "trainer.data.rows_per_epoch is %llu: an epoch needs at least 1 row and at most %llu rows, because the schedule keeps 2 bytes per row. Set trainer.data.rows_per_epoch inside that range.",
+                        (unsigned long long)rows, (unsigned long long)MAX_ROWS);
+        m->weights.assign(weights, weights + n_weights);
+        m->requested = has_rows_per_epoch != 0;
+        m->rows_per_epoch = rows;
+        mixture_quotas(weights, n_weights, rows, m->quotas);
+        // smooth weighted round-robin over the quotas (src/data/mixture/schedule.rs:103-122)
+        {
+            std::vector<int64_t> credit(n_weights, 0);
+            m->schedule.reserve(rows);
+            for (uint64_t k = 0; k < rows; k++) {
+                uint32_t pick = 0;
+                for (uint32_t i = 0; i < n_weights; i++) {
+                    credit[i] += (int64_t)m->quotas[i];
+                    if (credit[i] > credit[pick]) pick = i;
+                }
+                credit[pick] -= (int64_t)rows;
+                m->schedule.push_back((uint16_t)pick);
+            }
+            std::vector<uint32_t> counts(n_weights, 0);
+            for (uint64_t k = 0; k < rows; k++) {
+                if (k % Mixture::BLOCK == 0) m->prefix.insert(m->prefix.end(), counts.begin(), counts.end());
+                counts[m->schedule[k]]++;
+            }
         }
-    }
-    // the layout counts rows per epoch; the position resets to the start (src/data/mixture/loader.rs:28-33)
-    oxz_row_layout layout = l->layout;
-    layout.num_rows = rows;
-    OXZ_TRY(oxz_rows_check(&layout));
-    const uint32_t depth = l->pre ? l->prefetch_depth : 0;
-    stop_prefetch(l);
-    l->layout = layout;
-    l->pos = oxz_data_position{0, 0};
-    l->mix = std::move(m);
-    return depth ? start_prefetch(l, depth) : (int32_t)OXZ_OK;
+        // the layout counts rows per epoch; the position resets to the start (src/data/mixture/loader.rs:28-33)
+        oxz_row_layout layout = l->layout;
+        layout.num_rows = rows;
+        OXZ_TRY(oxz_rows_check(&layout));
+        const uint32_t depth = l->pre ? l->prefetch_depth : 0;
+        stop_prefetch(l);
+        l->layout = layout;
+        l->pos = oxz_data_position{0, 0};
+        l->mix = std::move(m);
+        return depth ? start_prefetch(l, depth) : (int32_t)OXZ_OK;
+    });
 }
 
 int32_t oxz_loader_mixture_sources(const oxz_loader* l, oxz_mixture_source* out, uint32_t cap, uint32_t* n_sources) {
-    if (!l || !n_sources) return fail(OXZ_ERR_INVALID, "oxz_loader_mixture_sources: null argument");
-    *n_sources = l->mix ? (uint32_t)l->mix->weights.size() : 0;
-    for (uint32_t i = 0; out && i < cap && i < *n_sources; i++)
-        out[i] = oxz_mixture_source{l->mix->weights[i], l->mix->quotas[i], l->mix->sources[i].len};
-    return OXZ_OK;
+    return oxz::guarded("oxz_loader_mixture_sources", [&]() -> int32_t {
+        if (!l || !n_sources) return fail(OXZ_ERR_INVALID, "oxz_loader_mixture_sources: null argument");
+        *n_sources = l->mix ? (uint32_t)l->mix->weights.size() : 0;
+        for (uint32_t i = 0; out && i < cap && i < *n_sources; i++)
+            out[i] = oxz_mixture_source{l->mix->weights[i], l->mix->quotas[i], l->mix->sources[i].len};
+        return OXZ_OK;
+    });
 }
 
 int32_t oxz_loader_source_rows(const oxz_loader* l, uint64_t* rows, uint32_t cap, uint32_t* n_sources) {
-    if (!l || !n_sources) return fail(OXZ_ERR_INVALID, "oxz_loader_source_rows: null argument");
-    *n_sources = (uint32_t)l->parts.size();
-    for (uint32_t i = 0; rows && i < cap && i < l->parts.size(); i++) rows[i] = l->parts[i].rows;
-    return OXZ_OK;
+    return oxz::guarded("oxz_loader_source_rows", [&]() -> int32_t {
+        if (!l || !n_sources) return fail(OXZ_ERR_INVALID, "oxz_loader_source_rows: null argument");
+        *n_sources = (uint32_t)l->parts.size();
+        for (uint32_t i = 0; rows && i < cap && i < l->parts.size(); i++) rows[i] = l->parts[i].rows;
+        return OXZ_OK;
+    });
 }
 
 int32_t oxz_loader_close(oxz_loader* l) {
-    release(l);
-    return OXZ_OK;
+    return oxz::guarded("oxz_loader_close", [&]() -> int32_t {
+        release(l);
+        return OXZ_OK;
+    });
 }
 
 int32_t oxz_loader_num_rows(const oxz_loader* l, uint64_t* rows) {
-    if (!l || !rows) return fail(OXZ_ERR_INVALID, "oxz_loader_num_rows: null argument");
-    *rows = l->layout.num_rows;
-    return OXZ_OK;
+    return oxz::guarded("oxz_loader_num_rows", [&]() -> int32_t {
+        if (!l || !rows) return fail(OXZ_ERR_INVALID, "oxz_loader_num_rows: null argument");
+        *rows = l->layout.num_rows;
+        return OXZ_OK;
+    });
 }
 
 int32_t oxz_loader_position(const oxz_loader* l, oxz_data_position* pos) {
-    if (!l || !pos) return fail(OXZ_ERR_INVALID, "oxz_loader_position: null argument");
-    *pos = l->pos;
-    return OXZ_OK;
+    return oxz::guarded("oxz_loader_position", [&]() -> int32_t {
+        if (!l || !pos) return fail(OXZ_ERR_INVALID, "oxz_loader_position: null argument");
+        *pos = l->pos;
+        return OXZ_OK;
+    });
 }
 
 int32_t oxz_loader_seek(oxz_loader* l, oxz_data_position pos) {
-    if (!l) return fail(OXZ_ERR_INVALID, "oxz_loader_seek: null loader");
-    if (pos.row > l->layout.num_rows)
-        return fail(OXZ_ERR_DATA,
-                    "data position epoch %llu row %llu is past this shard's %llu rows: the checkpoint was saved over "
-                    "different data or a different model.max_seq_len. Resume with the original data and config, or "
-                    "start a fresh run.",
-                    (unsigned long long)pos.epoch, (unsigned long long)pos.row, (unsigned long long)l->layout.num_rows);
-    // a prefetch thread has drawn ahead from the old position: it starts over from the new one
-    const uint32_t depth = l->pre ? l->prefetch_depth : 0;
-    stop_prefetch(l);
-    l->pos = pos;
-    return depth ? start_prefetch(l, depth) : (int32_t)OXZ_OK;
+    return oxz::guarded("oxz_loader_seek", [&]() -> int32_t {
+        if (!l) return fail(OXZ_ERR_INVALID, "oxz_loader_seek: null loader");
+        if (pos.row > l->layout.num_rows)
+            return fail(OXZ_ERR_DATA,
+                        "data position epoch %llu row %llu is past this shard's %llu rows: the checkpoint was saved over "
+                        "different data or a different model.max_seq_len. Resume with the original data and config, or "
+                        "start a fresh run.",
+                        (unsigned long long)pos.epoch, (unsigned long long)pos.row, (unsigned long long)l->layout.num_rows);
+        // a prefetch thread has drawn ahead from the old position: it starts over from the new one
+        const uint32_t depth = l->pre ? l->prefetch_depth : 0;
+        stop_prefetch(l);
+        l->pos = pos;
+        return depth ? start_prefetch(l, depth) : (int32_t)OXZ_OK;
+    });
 }
 
 // The global rows of this rank's part of the next global batch, where each starts in its file, and the position after
@@ -694,165 +714,177 @@ static int32_t start_prefetch(oxz_loader* l, uint32_t depth) {
 }
 
 int32_t oxz_loader_set_prefetch(oxz_loader* l, uint32_t depth) {
-    if (!l) return fail(OXZ_ERR_INVALID, "oxz_loader_set_prefetch: null loader");
-    if (depth > 64) return fail(OXZ_ERR_INVALID, "oxz_loader_set_prefetch: %u batches ahead, at most 64", depth);
-    stop_prefetch(l);
-    l->prefetch_depth = depth;
-    return depth ? start_prefetch(l, depth) : (int32_t)OXZ_OK;
+    return oxz::guarded("oxz_loader_set_prefetch", [&]() -> int32_t {
+        if (!l) return fail(OXZ_ERR_INVALID, "oxz_loader_set_prefetch: null loader");
+        if (depth > 64) return fail(OXZ_ERR_INVALID, "oxz_loader_set_prefetch: %u batches ahead, at most 64", depth);
+        stop_prefetch(l);
+        l->prefetch_depth = depth;
+        return depth ? start_prefetch(l, depth) : (int32_t)OXZ_OK;
+    });
 }
 
 int32_t oxz_loader_next_rows(oxz_loader* l, uint64_t* rows) {
-    if (!l || !rows) return fail(OXZ_ERR_INVALID, "oxz_loader_next_rows: null argument");
-    if (l->pre) return fail(OXZ_ERR_STATE, "oxz_loader_next_rows: the prefetch thread draws this loader's rows. Turn prefetching off first");
-    const uint64_t B = l->layout.rank_batch_size;
-    std::vector<uint64_t> row_ids(B);
-    std::vector<const uint32_t*> src(B);
-    oxz_data_position next;
-    OXZ_TRY(draw_rows(l, l->pos, row_ids, src, &next));
-    memcpy(rows, row_ids.data(), B * 8);
-    l->pos = next;
-    return OXZ_OK;
+    return oxz::guarded("oxz_loader_next_rows", [&]() -> int32_t {
+        if (!l || !rows) return fail(OXZ_ERR_INVALID, "oxz_loader_next_rows: null argument");
+        if (l->pre) return fail(OXZ_ERR_STATE, "oxz_loader_next_rows: the prefetch thread draws this loader's rows. Turn prefetching off first");
+        const uint64_t B = l->layout.rank_batch_size;
+        std::vector<uint64_t> row_ids(B);
+        std::vector<const uint32_t*> src(B);
+        oxz_data_position next;
+        OXZ_TRY(draw_rows(l, l->pos, row_ids, src, &next));
+        memcpy(rows, row_ids.data(), B * 8);
+        l->pos = next;
+        return OXZ_OK;
+    });
 }
 
 int32_t oxz_loader_next_batch_async(oxz_loader* l, void* stream, int64_t** inputs, int64_t** targets, uint64_t* rows) {
-    if (!l || !inputs || !targets) return fail(OXZ_ERR_INVALID, "oxz_loader_next_batch_async: null argument");
-    const uint64_t B = l->layout.rank_batch_size, S = l->seq_len, width = S + 1;
-    OXZ_CUDA(cudaSetDevice(l->device));
-    if (!l->d_stage[0]) {
-        for (int i = 0; i < 2; i++) {
-            OXZ_CUDA(cudaMallocHost((void**)&l->h_stage[i], B * width * 4));
-            OXZ_CUDA(cudaMalloc((void**)&l->d_stage[i], B * width * 4));
-            OXZ_CUDA(cudaMalloc((void**)&l->d_inputs[i], B * S * 8));
-            OXZ_CUDA(cudaMalloc((void**)&l->d_targets[i], B * S * 8));
-            OXZ_CUDA(cudaEventCreateWithFlags(&l->staged[i], cudaEventDisableTiming));
+    return oxz::guarded("oxz_loader_next_batch_async", [&]() -> int32_t {
+        if (!l || !inputs || !targets) return fail(OXZ_ERR_INVALID, "oxz_loader_next_batch_async: null argument");
+        const uint64_t B = l->layout.rank_batch_size, S = l->seq_len, width = S + 1;
+        OXZ_CUDA(cudaSetDevice(l->device));
+        if (!l->d_stage[0]) {
+            for (int i = 0; i < 2; i++) {
+                OXZ_CUDA(cudaMallocHost((void**)&l->h_stage[i], B * width * 4));
+                OXZ_CUDA(cudaMalloc((void**)&l->d_stage[i], B * width * 4));
+                OXZ_CUDA(cudaMalloc((void**)&l->d_inputs[i], B * S * 8));
+                OXZ_CUDA(cudaMalloc((void**)&l->d_targets[i], B * S * 8));
+                OXZ_CUDA(cudaEventCreateWithFlags(&l->staged[i], cudaEventDisableTiming));
+            }
         }
-    }
-    oxz_data_position next;
-    std::vector<uint64_t> row_ids(B);
-    const int k = l->slot;
-    cudaStream_t s = (cudaStream_t)stream;
-    // the pinned buffers of this slot (tokens in, counts out) may still be in use by the batch issued two batches ago
-    OXZ_CUDA(cudaEventSynchronize(l->staged[k]));
-    if (l->pre) {
-        // the worker has the rows in a pinned buffer already, or is about to
-        Prefetch& q = *l->pre;
-        int i;
-        {
-            std::unique_lock<std::mutex> g(q.mu);
-            q.cv.wait(g, [&] { return !q.ready.empty(); });
-            i = q.ready.front();
-            q.ready.pop_front();
+        oxz_data_position next;
+        std::vector<uint64_t> row_ids(B);
+        const int k = l->slot;
+        cudaStream_t s = (cudaStream_t)stream;
+        // the pinned buffers of this slot (tokens in, counts out) may still be in use by the batch issued two batches ago
+        OXZ_CUDA(cudaEventSynchronize(l->staged[k]));
+        if (l->pre) {
+            // the worker has the rows in a pinned buffer already, or is about to
+            Prefetch& q = *l->pre;
+            int i;
+            {
+                std::unique_lock<std::mutex> g(q.mu);
+                q.cv.wait(g, [&] { return !q.ready.empty(); });
+                i = q.ready.front();
+                q.ready.pop_front();
+            }
+            Prefetch::Slot& slot = q.slots[i];
+            if (slot.status != OXZ_OK) {
+                const int32_t st = slot.status;
+                const std::string text = slot.error;
+                stop_prefetch(l);  // the worker has left; a seek or a new set_prefetch starts another
+                oxz_set_last_error(text.c_str());
+                return st;
+            }
+            row_ids = slot.rows;
+            next = slot.next;
+            OXZ_CUDA(cudaMemcpyAsync(l->d_stage[k], slot.host, B * width * 4, cudaMemcpyHostToDevice, s));
+            OXZ_CUDA(cudaEventRecord(slot.copied, s));
+            {
+                std::lock_guard<std::mutex> g(q.mu);
+                q.idle.push_back(i);
+            }
+            q.cv.notify_all();
+        } else {
+            std::vector<const uint32_t*> src(B);
+            OXZ_TRY(draw_rows(l, l->pos, row_ids, src, &next));
+            copy_rows(l, src, l->h_stage[k]);
+            OXZ_CUDA(cudaMemcpyAsync(l->d_stage[k], l->h_stage[k], B * width * 4, cudaMemcpyHostToDevice, s));
         }
-        Prefetch::Slot& slot = q.slots[i];
-        if (slot.status != OXZ_OK) {
-            const int32_t st = slot.status;
-            const std::string text = slot.error;
-            stop_prefetch(l);  // the worker has left; a seek or a new set_prefetch starts another
-            oxz_set_last_error(text.c_str());
-            return st;
+        const uint64_t n = B * S;
+        const int blocks = (int)((n + 255) / 256 < 148 * 8 ? (n + 255) / 256 : 148 * 8);
+        const bool masked = l->target_mask || l->document_mask;
+        if (!l->h_counts[0])
+            for (int i = 0; i < 2; i++) OXZ_CUDA(cudaMallocHost((void**)&l->h_counts[i], 16));
+        if (masked && !l->d_loss_mask[0]) {
+            for (int i = 0; i < 2; i++) {
+                OXZ_CUDA(cudaMalloc((void**)&l->d_loss_mask[i], n * 4));
+                OXZ_CUDA(cudaMalloc((void**)&l->d_counts[i], 16));
+            }
         }
-        row_ids = slot.rows;
-        next = slot.next;
-        OXZ_CUDA(cudaMemcpyAsync(l->d_stage[k], slot.host, B * width * 4, cudaMemcpyHostToDevice, s));
-        OXZ_CUDA(cudaEventRecord(slot.copied, s));
-        {
-            std::lock_guard<std::mutex> g(q.mu);
-            q.idle.push_back(i);
+        if (l->document_mask && !l->d_seg_ids[0]) {
+            for (int i = 0; i < 2; i++) {
+                OXZ_CUDA(cudaMalloc((void**)&l->d_seg_ids[i], n * 4));
+                OXZ_CUDA(cudaMalloc((void**)&l->d_cu[i], (n + 1) * 4));
+                OXZ_CUDA(cudaMalloc((void**)&l->d_row_base[i], (B + 1) * 4));
+            }
         }
-        q.cv.notify_all();
-    } else {
-        std::vector<const uint32_t*> src(B);
-        OXZ_TRY(draw_rows(l, l->pos, row_ids, src, &next));
-        copy_rows(l, src, l->h_stage[k]);
-        OXZ_CUDA(cudaMemcpyAsync(l->d_stage[k], l->h_stage[k], B * width * 4, cudaMemcpyHostToDevice, s));
-    }
-    const uint64_t n = B * S;
-    const int blocks = (int)((n + 255) / 256 < 148 * 8 ? (n + 255) / 256 : 148 * 8);
-    const bool masked = l->target_mask || l->document_mask;
-    if (!l->h_counts[0])
-        for (int i = 0; i < 2; i++) OXZ_CUDA(cudaMallocHost((void**)&l->h_counts[i], 16));
-    if (masked && !l->d_loss_mask[0]) {
-        for (int i = 0; i < 2; i++) {
-            OXZ_CUDA(cudaMalloc((void**)&l->d_loss_mask[i], n * 4));
-            OXZ_CUDA(cudaMalloc((void**)&l->d_counts[i], 16));
+        if (!masked) {
+            k_split_rows<<<blocks ? blocks : 1, 256, 0, s>>>(l->d_stage[k], B, S, l->d_inputs[k], l->d_targets[k]);
+            l->h_counts[k][0] = n;  // an unmasked batch scores every position (src/data/host_masks.rs:56-57)
+            l->h_counts[k][1] = 0;
+        } else {
+            MaskRule rule{};
+            rule.has_target = l->target_mask ? 1 : 0;
+            rule.has_document = l->document_mask ? 1 : 0;
+            rule.target_base = l->target_base;
+            rule.n_always = l->n_always;
+            rule.separator = l->separator;
+            for (uint32_t i = 0; i < l->n_always; i++) rule.always[i] = l->always[i];
+            OXZ_CUDA(cudaMemsetAsync(l->d_counts[k], 0, 16, s));
+            k_split_rows_masked<<<blocks ? blocks : 1, 256, 0, s>>>(l->d_stage[k], B, S, rule, l->d_inputs[k], l->d_targets[k],
+                                                                   l->d_loss_mask[k], l->d_counts[k]);
+            if (l->document_mask) {
+                k_row_closings<<<(unsigned)((B * 32 + 255) / 256), 256, 0, s>>>(l->d_stage[k], (uint32_t)B, (uint32_t)S, l->separator, l->d_row_base[k]);
+                k_scan_rows<<<1, 256, 0, s>>>(l->d_row_base[k], (uint32_t)B, l->d_cu[k], l->d_counts[k]);
+                k_fill_segments<<<(unsigned)B, 256, 0, s>>>(l->d_stage[k], (uint32_t)S, l->separator, l->d_row_base[k], l->d_seg_ids[k], l->d_cu[k]);
+            }
+            OXZ_CUDA(cudaMemcpyAsync(l->h_counts[k], l->d_counts[k], 16, cudaMemcpyDeviceToHost, s));
         }
-    }
-    if (l->document_mask && !l->d_seg_ids[0]) {
-        for (int i = 0; i < 2; i++) {
-            OXZ_CUDA(cudaMalloc((void**)&l->d_seg_ids[i], n * 4));
-            OXZ_CUDA(cudaMalloc((void**)&l->d_cu[i], (n + 1) * 4));
-            OXZ_CUDA(cudaMalloc((void**)&l->d_row_base[i], (B + 1) * 4));
-        }
-    }
-    if (!masked) {
-        k_split_rows<<<blocks ? blocks : 1, 256, 0, s>>>(l->d_stage[k], B, S, l->d_inputs[k], l->d_targets[k]);
-        l->h_counts[k][0] = n;  // an unmasked batch scores every position (src/data/host_masks.rs:56-57)
-        l->h_counts[k][1] = 0;
-    } else {
-        MaskRule rule{};
-        rule.has_target = l->target_mask ? 1 : 0;
-        rule.has_document = l->document_mask ? 1 : 0;
-        rule.target_base = l->target_base;
-        rule.n_always = l->n_always;
-        rule.separator = l->separator;
-        for (uint32_t i = 0; i < l->n_always; i++) rule.always[i] = l->always[i];
-        OXZ_CUDA(cudaMemsetAsync(l->d_counts[k], 0, 16, s));
-        k_split_rows_masked<<<blocks ? blocks : 1, 256, 0, s>>>(l->d_stage[k], B, S, rule, l->d_inputs[k], l->d_targets[k],
-                                                               l->d_loss_mask[k], l->d_counts[k]);
-        if (l->document_mask) {
-            k_row_closings<<<(unsigned)((B * 32 + 255) / 256), 256, 0, s>>>(l->d_stage[k], (uint32_t)B, (uint32_t)S, l->separator, l->d_row_base[k]);
-            k_scan_rows<<<1, 256, 0, s>>>(l->d_row_base[k], (uint32_t)B, l->d_cu[k], l->d_counts[k]);
-            k_fill_segments<<<(unsigned)B, 256, 0, s>>>(l->d_stage[k], (uint32_t)S, l->separator, l->d_row_base[k], l->d_seg_ids[k], l->d_cu[k]);
-        }
-        OXZ_CUDA(cudaMemcpyAsync(l->h_counts[k], l->d_counts[k], 16, cudaMemcpyDeviceToHost, s));
-    }
-    cudaError_t e = cudaGetLastError();
-    if (e != cudaSuccess) return fail(OXZ_ERR_CUDA, "launch of the batch kernels failed: %s", cudaGetErrorString(e));
-    // marks the point after which this slot's pinned buffers (tokens in, counts out) may be touched again
-    OXZ_CUDA(cudaEventRecord(l->staged[k], s));
-    l->last = k;
-    *inputs = l->d_inputs[k];
-    *targets = l->d_targets[k];
-    if (rows) memcpy(rows, row_ids.data(), B * 8);
-    l->pos = next;
-    l->slot ^= 1;
-    return OXZ_OK;
+        cudaError_t e = cudaGetLastError();
+        if (e != cudaSuccess) return fail(OXZ_ERR_CUDA, "launch of the batch kernels failed: %s", cudaGetErrorString(e));
+        // marks the point after which this slot's pinned buffers (tokens in, counts out) may be touched again
+        OXZ_CUDA(cudaEventRecord(l->staged[k], s));
+        l->last = k;
+        *inputs = l->d_inputs[k];
+        *targets = l->d_targets[k];
+        if (rows) memcpy(rows, row_ids.data(), B * 8);
+        l->pos = next;
+        l->slot ^= 1;
+        return OXZ_OK;
+    });
 }
 
 int32_t oxz_loader_set_target_mask(oxz_loader* l, int32_t on, uint32_t target_base, const uint32_t* always_score, uint32_t n_always) {
-    if (!l || (on && n_always && !always_score)) return fail(OXZ_ERR_INVALID, "oxz_loader_set_target_mask: null argument");
-    if (on && n_always > OXZ_MAX_ALWAYS_SCORE)
-        return fail(OXZ_ERR_INVALID, "oxz_loader_set_target_mask: %u always-scored ids, at most %u", n_always, OXZ_MAX_ALWAYS_SCORE);
-    l->target_mask = on != 0;
-    l->target_base = target_base;
-    l->n_always = on ? n_always : 0;
-    for (uint32_t i = 0; i < l->n_always; i++) l->always[i] = always_score[i];
-    return OXZ_OK;
+    return oxz::guarded("oxz_loader_set_target_mask", [&]() -> int32_t {
+        if (!l || (on && n_always && !always_score)) return fail(OXZ_ERR_INVALID, "oxz_loader_set_target_mask: null argument");
+        if (on && n_always > OXZ_MAX_ALWAYS_SCORE)
+            return fail(OXZ_ERR_INVALID, "oxz_loader_set_target_mask: %u always-scored ids, at most %u", n_always, OXZ_MAX_ALWAYS_SCORE);
+        l->target_mask = on != 0;
+        l->target_base = target_base;
+        l->n_always = on ? n_always : 0;
+        for (uint32_t i = 0; i < l->n_always; i++) l->always[i] = always_score[i];
+        return OXZ_OK;
+    });
 }
 
 int32_t oxz_loader_set_document_mask(oxz_loader* l, int32_t on, uint32_t separator_id) {
-    if (!l) return fail(OXZ_ERR_INVALID, "oxz_loader_set_document_mask: null loader");
-    if (on && l->layout.rank_batch_size * l->seq_len > 0x7fffffffull)
-        return fail(OXZ_ERR_DATA,
-                    "a batch of %llu x %llu tokens overflows the i32 segment offsets. Lower trainer.batch_size or "
-                    "model.max_seq_len.", (unsigned long long)l->layout.rank_batch_size, (unsigned long long)l->seq_len);
-    l->document_mask = on != 0;
-    l->separator = separator_id;
-    return OXZ_OK;
+    return oxz::guarded("oxz_loader_set_document_mask", [&]() -> int32_t {
+        if (!l) return fail(OXZ_ERR_INVALID, "oxz_loader_set_document_mask: null loader");
+        if (on && l->layout.rank_batch_size * l->seq_len > 0x7fffffffull)
+            return fail(OXZ_ERR_DATA,
+                        "a batch of %llu x %llu tokens overflows the i32 segment offsets. Lower trainer.batch_size or "
+                        "model.max_seq_len.", (unsigned long long)l->layout.rank_batch_size, (unsigned long long)l->seq_len);
+        l->document_mask = on != 0;
+        l->separator = separator_id;
+        return OXZ_OK;
+    });
 }
 
 int32_t oxz_loader_batch_masks(const oxz_loader* l, oxz_batch_masks* out) {
-    if (!l || !out) return fail(OXZ_ERR_INVALID, "oxz_loader_batch_masks: null argument");
-    if (l->last < 0) return fail(OXZ_ERR_STATE, "oxz_loader_batch_masks: no batch has been drawn yet");
-    const int k = l->last;
-    const bool masked = l->d_loss_mask[k] && (l->target_mask || l->document_mask);
-    const bool segs = l->d_seg_ids[k] && l->document_mask;
-    out->loss_mask = masked ? l->d_loss_mask[k] : nullptr;
-    out->segment_ids = segs ? l->d_seg_ids[k] : nullptr;
-    out->cu_seqlens = segs ? l->d_cu[k] : nullptr;
-    out->scored = reinterpret_cast<const uint64_t*>(&l->h_counts[k][0]);
-    out->n_segments = reinterpret_cast<const uint64_t*>(&l->h_counts[k][1]);
-    return OXZ_OK;
+    return oxz::guarded("oxz_loader_batch_masks", [&]() -> int32_t {
+        if (!l || !out) return fail(OXZ_ERR_INVALID, "oxz_loader_batch_masks: null argument");
+        if (l->last < 0) return fail(OXZ_ERR_STATE, "oxz_loader_batch_masks: no batch has been drawn yet");
+        const int k = l->last;
+        const bool masked = l->d_loss_mask[k] && (l->target_mask || l->document_mask);
+        const bool segs = l->d_seg_ids[k] && l->document_mask;
+        out->loss_mask = masked ? l->d_loss_mask[k] : nullptr;
+        out->segment_ids = segs ? l->d_seg_ids[k] : nullptr;
+        out->cu_seqlens = segs ? l->d_cu[k] : nullptr;
+        out->scored = reinterpret_cast<const uint64_t*>(&l->h_counts[k][0]);
+        out->n_segments = reinterpret_cast<const uint64_t*>(&l->h_counts[k][1]);
+        return OXZ_OK;
+    });
 }
 
 }  // extern "C"

@@ -153,119 +153,129 @@ std::string f64_text(double v) {
 extern "C" {
 
 int32_t oxz_meta_load(const char* path, oxz_resume_meta* out) {
-    if (!path || !out) return fail(OXZ_ERR_INVALID, "oxz_meta_load: null argument");
-    Parsed p;
-    std::string why;
-    if (!parse_file(path, &p, &why))
-        return fail(OXZ_ERR_INVALID, "checkpoint meta '%s' was not read: %s. Restore the file to resume from it.", path, why.c_str());
-    *out = p.m;
-    return OXZ_OK;
+    return oxz::guarded("oxz_meta_load", [&]() -> int32_t {
+        if (!path || !out) return fail(OXZ_ERR_INVALID, "oxz_meta_load: null argument");
+        Parsed p;
+        std::string why;
+        if (!parse_file(path, &p, &why))
+            return fail(OXZ_ERR_INVALID, "checkpoint meta '%s' was not read: %s. Restore the file to resume from it.", path, why.c_str());
+        *out = p.m;
+        return OXZ_OK;
+    });
 }
 
 int32_t oxz_meta_no_decay_pattern(const char* path, uint32_t index, char* buf, uint64_t cap) {
-    if (!path || !buf || cap == 0) return fail(OXZ_ERR_INVALID, "oxz_meta_no_decay_pattern: null argument");
-    Parsed p;
-    std::string why;
-    if (!parse_file(path, &p, &why))
-        return fail(OXZ_ERR_INVALID, "checkpoint meta '%s' was not read: %s. Restore the file to resume from it.", path, why.c_str());
-    if (index >= p.patterns.size())
-        return fail(OXZ_ERR_INVALID, "oxz_meta_no_decay_pattern: pattern %u of %zu", index, p.patterns.size());
-    if (p.patterns[index].size() >= cap)
-        return fail(OXZ_ERR_INVALID, "oxz_meta_no_decay_pattern: the pattern needs %zu bytes, the buffer has %llu",
-                    p.patterns[index].size() + 1, (unsigned long long)cap);
-    memcpy(buf, p.patterns[index].c_str(), p.patterns[index].size() + 1);
-    return OXZ_OK;
+    return oxz::guarded("oxz_meta_no_decay_pattern", [&]() -> int32_t {
+        if (!path || !buf || cap == 0) return fail(OXZ_ERR_INVALID, "oxz_meta_no_decay_pattern: null argument");
+        Parsed p;
+        std::string why;
+        if (!parse_file(path, &p, &why))
+            return fail(OXZ_ERR_INVALID, "checkpoint meta '%s' was not read: %s. Restore the file to resume from it.", path, why.c_str());
+        if (index >= p.patterns.size())
+            return fail(OXZ_ERR_INVALID, "oxz_meta_no_decay_pattern: pattern %u of %zu", index, p.patterns.size());
+        if (p.patterns[index].size() >= cap)
+            return fail(OXZ_ERR_INVALID, "oxz_meta_no_decay_pattern: the pattern needs %zu bytes, the buffer has %llu",
+                        p.patterns[index].size() + 1, (unsigned long long)cap);
+        memcpy(buf, p.patterns[index].c_str(), p.patterns[index].size() + 1);
+        return OXZ_OK;
+    });
 }
 
 int32_t oxz_meta_mixture_weights(const char* path, double* weights, uint32_t cap, uint32_t* n_weights) {
-    if (!path || !n_weights) return fail(OXZ_ERR_INVALID, "oxz_meta_mixture_weights: null argument");
-    Parsed p;
-    std::string why;
-    if (!parse_file(path, &p, &why))
-        return fail(OXZ_ERR_INVALID, "checkpoint meta '%s' was not read: %s. Restore the file to resume from it.", path, why.c_str());
-    *n_weights = (uint32_t)p.mixture_weights.size();
-    for (uint32_t i = 0; weights && i < cap && i < *n_weights; i++) weights[i] = p.mixture_weights[i];
-    return OXZ_OK;
+    return oxz::guarded("oxz_meta_mixture_weights", [&]() -> int32_t {
+        if (!path || !n_weights) return fail(OXZ_ERR_INVALID, "oxz_meta_mixture_weights: null argument");
+        Parsed p;
+        std::string why;
+        if (!parse_file(path, &p, &why))
+            return fail(OXZ_ERR_INVALID, "checkpoint meta '%s' was not read: %s. Restore the file to resume from it.", path, why.c_str());
+        *n_weights = (uint32_t)p.mixture_weights.size();
+        for (uint32_t i = 0; weights && i < cap && i < *n_weights; i++) weights[i] = p.mixture_weights[i];
+        return OXZ_OK;
+    });
 }
 
 int32_t oxz_meta_save(const char* path, const oxz_resume_meta* m, const char* const* no_decay_patterns,
                       const double* mixture_weights) {
-    if (!path || !m || (m->n_no_decay_patterns && !no_decay_patterns) || (m->has_mixture && m->n_mixture_weights && !mixture_weights))
-        return fail(OXZ_ERR_INVALID, "oxz_meta_save: null argument");
-    if (m->has_weight_decay_rule && (m->weight_decay_rule < OXZ_DECAY_ALL || m->weight_decay_rule > OXZ_SKIP_ALL))
-        return fail(OXZ_ERR_INVALID, "oxz_meta_save: unknown weight decay rule %d", m->weight_decay_rule);
-    if (m->has_loss_scale && !(std::isfinite(m->loss_scale.scale) && m->loss_scale.scale > 0.0))
-        return fail(OXZ_ERR_INVALID, "oxz_meta_save: loss scale %g must be finite and positive", m->loss_scale.scale);
-    // Field order and Option handling follow CheckpointMeta's serde derive: required keys first, None left out.
-    // The keys outside the optimizer path (timestamp, hashes, data sources) are written empty.
-    std::string j = "{\n";
-    j += "  \"step\": " + std::to_string(m->step) + ",\n";
-    j += "  \"timestamp\": \"\",\n  \"model_config_hash\": \"\",\n  \"data_file_path\": \"\",\n  \"data_file_hash\": \"\",\n";
-    j += "  \"checkpoint_file\": \"" + esc(m->checkpoint_file) + "\"";
-    if (m->has_data_position)
-        j += ",\n  \"data_position\": {\n    \"epoch\": " + std::to_string(m->data_position.epoch) + ",\n    \"row\": " +
-             std::to_string(m->data_position.row) + "\n  }";
-    if (m->optimizer_file[0]) j += ",\n  \"optimizer_file\": \"" + esc(m->optimizer_file) + "\"";
-    if (m->has_weight_decay_rule) j += std::string(",\n  \"weight_decay_rule\": \"") + rule_name(m->weight_decay_rule) + "\"";
-    if (m->n_no_decay_patterns) {
-        j += ",\n  \"no_decay_patterns\": [";
-        for (uint32_t i = 0; i < m->n_no_decay_patterns; i++) {
-            if (!no_decay_patterns[i]) return fail(OXZ_ERR_INVALID, "oxz_meta_save: pattern %u is null", i);
-            j += std::string(i ? "," : "") + "\n    \"" + esc(no_decay_patterns[i]) + "\"";
+    return oxz::guarded("oxz_meta_save", [&]() -> int32_t {
+        if (!path || !m || (m->n_no_decay_patterns && !no_decay_patterns) || (m->has_mixture && m->n_mixture_weights && !mixture_weights))
+            return fail(OXZ_ERR_INVALID, "oxz_meta_save: null argument");
+        if (m->has_weight_decay_rule && (m->weight_decay_rule < OXZ_DECAY_ALL || m->weight_decay_rule > OXZ_SKIP_ALL))
+            return fail(OXZ_ERR_INVALID, "oxz_meta_save: unknown weight decay rule %d", m->weight_decay_rule);
+        if (m->has_loss_scale && !(std::isfinite(m->loss_scale.scale) && m->loss_scale.scale > 0.0))
+            return fail(OXZ_ERR_INVALID, "oxz_meta_save: loss scale %g must be finite and positive", m->loss_scale.scale);
+        // Field order and Option handling follow CheckpointMeta's serde derive: required keys first, None left out.
+        // The keys outside the optimizer path (timestamp, hashes, data sources) are written empty.
+        std::string j = "{\n";
+        j += "  \"step\": " + std::to_string(m->step) + ",\n";
+        j += "  \"timestamp\": \"\",\n  \"model_config_hash\": \"\",\n  \"data_file_path\": \"\",\n  \"data_file_hash\": \"\",\n";
+        j += "  \"checkpoint_file\": \"" + esc(m->checkpoint_file) + "\"";
+        if (m->has_data_position)
+            j += ",\n  \"data_position\": {\n    \"epoch\": " + std::to_string(m->data_position.epoch) + ",\n    \"row\": " +
+                 std::to_string(m->data_position.row) + "\n  }";
+        if (m->optimizer_file[0]) j += ",\n  \"optimizer_file\": \"" + esc(m->optimizer_file) + "\"";
+        if (m->has_weight_decay_rule) j += std::string(",\n  \"weight_decay_rule\": \"") + rule_name(m->weight_decay_rule) + "\"";
+        if (m->n_no_decay_patterns) {
+            j += ",\n  \"no_decay_patterns\": [";
+            for (uint32_t i = 0; i < m->n_no_decay_patterns; i++) {
+                if (!no_decay_patterns[i]) return fail(OXZ_ERR_INVALID, "oxz_meta_save: pattern %u is null", i);
+                j += std::string(i ? "," : "") + "\n    \"" + esc(no_decay_patterns[i]) + "\"";
+            }
+            j += "\n  ]";
         }
-        j += "\n  ]";
-    }
-    if (m->has_loss_scale)
-        j += ",\n  \"loss_scale\": {\n    \"scale\": " + f64_text(m->loss_scale.scale) + ",\n    \"consecutive_ok\": " +
-             std::to_string(m->loss_scale.consecutive_ok) + "\n  }";
-    if (m->has_world_size) j += ",\n  \"world_size\": " + std::to_string(m->world_size);
-    if (m->has_global_batch_rows) j += ",\n  \"global_batch_rows\": " + std::to_string(m->global_batch_rows);
-    if (m->has_spike_guard)
-        j += ",\n  \"spike_guard\": {\n    \"mean\": " + f64_text(m->spike_guard.mean) + ",\n    \"variance\": " +
-             f64_text(m->spike_guard.variance) + ",\n    \"observed\": " + std::to_string(m->spike_guard.observed) +
-             ",\n    \"detected\": " + std::to_string(m->spike_guard.detected) + ",\n    \"skipped\": " +
-             std::to_string(m->spike_guard.skipped) + "\n  }";
-    if (m->has_mixture) {
-        j += ",\n  \"mixture\": {\n    \"weights\": [";
-        for (uint32_t i = 0; i < m->n_mixture_weights; i++) j += std::string(i ? "," : "") + "\n      " + f64_text(mixture_weights[i]);
-        j += std::string(m->n_mixture_weights ? "\n    " : "") + "],\n    \"rows_per_epoch\": " + std::to_string(m->mixture_rows_per_epoch) + "\n  }";
-    }
-    j += "\n}";
-    // atomic like CheckpointMeta::save_to (src/config.rs:1386-1394): write beside, then rename
-    const std::string tmp = std::string(path) + ".tmp";
-    FILE* f = fopen(tmp.c_str(), "wb");
-    const char* next = "Check that the directory is writable.";
-    if (!f) return fail(OXZ_ERR_INVALID, "failed to write checkpoint meta '%s': %s. %s", path, strerror(errno), next);
-    const bool wrote = fwrite(j.data(), 1, j.size(), f) == j.size();
-    if (fclose(f) != 0 || !wrote || rename(tmp.c_str(), path) != 0) {
-        const int32_t st = fail(OXZ_ERR_INVALID, "failed to write checkpoint meta '%s': %s. %s", path, strerror(errno), next);
-        remove(tmp.c_str());
-        return st;
-    }
-    return OXZ_OK;
+        if (m->has_loss_scale)
+            j += ",\n  \"loss_scale\": {\n    \"scale\": " + f64_text(m->loss_scale.scale) + ",\n    \"consecutive_ok\": " +
+                 std::to_string(m->loss_scale.consecutive_ok) + "\n  }";
+        if (m->has_world_size) j += ",\n  \"world_size\": " + std::to_string(m->world_size);
+        if (m->has_global_batch_rows) j += ",\n  \"global_batch_rows\": " + std::to_string(m->global_batch_rows);
+        if (m->has_spike_guard)
+            j += ",\n  \"spike_guard\": {\n    \"mean\": " + f64_text(m->spike_guard.mean) + ",\n    \"variance\": " +
+                 f64_text(m->spike_guard.variance) + ",\n    \"observed\": " + std::to_string(m->spike_guard.observed) +
+                 ",\n    \"detected\": " + std::to_string(m->spike_guard.detected) + ",\n    \"skipped\": " +
+                 std::to_string(m->spike_guard.skipped) + "\n  }";
+        if (m->has_mixture) {
+            j += ",\n  \"mixture\": {\n    \"weights\": [";
+            for (uint32_t i = 0; i < m->n_mixture_weights; i++) j += std::string(i ? "," : "") + "\n      " + f64_text(mixture_weights[i]);
+            j += std::string(m->n_mixture_weights ? "\n    " : "") + "],\n    \"rows_per_epoch\": " + std::to_string(m->mixture_rows_per_epoch) + "\n  }";
+        }
+        j += "\n}";
+        // atomic like CheckpointMeta::save_to (src/config.rs:1386-1394): write beside, then rename
+        const std::string tmp = std::string(path) + ".tmp";
+        FILE* f = fopen(tmp.c_str(), "wb");
+        const char* next = "Check that the directory is writable.";
+        if (!f) return fail(OXZ_ERR_INVALID, "failed to write checkpoint meta '%s': %s. %s", path, strerror(errno), next);
+        const bool wrote = fwrite(j.data(), 1, j.size(), f) == j.size();
+        if (fclose(f) != 0 || !wrote || rename(tmp.c_str(), path) != 0) {
+            const int32_t st = fail(OXZ_ERR_INVALID, "failed to write checkpoint meta '%s': %s. %s", path, strerror(errno), next);
+            remove(tmp.c_str());
+            return st;
+        }
+        return OXZ_OK;
+    });
 }
 
 int32_t oxz_check_resume_world(const char* meta_path, uint64_t start_step, uint64_t world, uint64_t global_batch_rows,
                                char* warning, uint64_t cap) {
-    if (warning && cap) warning[0] = '\0';
-    if (!meta_path || start_step == 0) return OXZ_OK;  // a fresh run and a resume without a meta check nothing
-    Parsed p;
-    std::string why;
-    if (!parse_file(meta_path, &p, &why))
-        return fail(OXZ_ERR_INVALID, "checkpoint meta '%s' was not read: %s. Restore the file to resume with its world size.",
-                    meta_path, why.c_str());
-    const uint64_t saved = p.m.has_world_size ? p.m.world_size : 1;  // an old meta reads as one rank
-    if (saved != world)
-        return fail(OXZ_ERR_INVALID,
-                    "checkpoint meta '%s' records world size %llu, and this run has world size %llu. Resume with %llu "
-                    "GPU id(s) in `--gpus`, or start a fresh run.",
-                    meta_path, (unsigned long long)saved, (unsigned long long)world, (unsigned long long)saved);
-    if (p.m.has_global_batch_rows && p.m.global_batch_rows != global_batch_rows && warning && cap)
-        snprintf(warning, cap,
-                 "Warning: checkpoint meta '%s' records global batches of %llu rows, and this run's global batch is %llu "
-                 "rows. The data stream resumes at the saved row, but the resume does not match an uninterrupted run.",
-                 meta_path, (unsigned long long)p.m.global_batch_rows, (unsigned long long)global_batch_rows);
-    return OXZ_OK;
+    return oxz::guarded("oxz_check_resume_world", [&]() -> int32_t {
+        if (warning && cap) warning[0] = '\0';
+        if (!meta_path || start_step == 0) return OXZ_OK;  // a fresh run and a resume without a meta check nothing
+        Parsed p;
+        std::string why;
+        if (!parse_file(meta_path, &p, &why))
+            return fail(OXZ_ERR_INVALID, "checkpoint meta '%s' was not read: %s. Restore the file to resume with its world size.",
+                        meta_path, why.c_str());
+        const uint64_t saved = p.m.has_world_size ? p.m.world_size : 1;  // an old meta reads as one rank
+        if (saved != world)
+            return fail(OXZ_ERR_INVALID,
+                        "checkpoint meta '%s' records world size %llu, and this run has world size %llu. Resume with %llu "
+                        "GPU id(s) in `--gpus`, or start a fresh run.",
+                        meta_path, (unsigned long long)saved, (unsigned long long)world, (unsigned long long)saved);
+        if (p.m.has_global_batch_rows && p.m.global_batch_rows != global_batch_rows && warning && cap)
+            snprintf(warning, cap,
+                     "Warning: checkpoint meta '%s' records global batches of %llu rows, and this run's global batch is %llu "
+                     "rows. The data stream resumes at the saved row, but the resume does not match an uninterrupted run.",
+                     meta_path, (unsigned long long)p.m.global_batch_rows, (unsigned long long)global_batch_rows);
+        return OXZ_OK;
+    });
 }
 
 // f64 the way Rust's `{}` prints it for the common cases: the shortest text that reads back, no trailing ".0"
@@ -282,52 +292,56 @@ static std::string debug_weights(const std::vector<double>& w) {  // `{:?}` of a
 
 int32_t oxz_check_mixture_resume(const char* meta_path, uint64_t start_step, int32_t has_current, const double* weights,
                                  uint32_t n_weights, uint64_t rows_per_epoch) {
-    if (has_current && n_weights && !weights) return fail(OXZ_ERR_INVALID, "oxz_check_mixture_resume: null argument");
-    if (!meta_path || start_step == 0) return OXZ_OK;
-    Parsed p;
-    std::string why;
-    if (!parse_file(meta_path, &p, &why))
-        return fail(OXZ_ERR_DATA, "checkpoint meta '%s' was not read: %s. Restore the file to resume with its data mixture.",
-                    meta_path, why.c_str());
-    const bool saved = p.m.has_mixture != 0;
-    const std::vector<double> current(weights, weights + (has_current ? n_weights : 0));
-    std::string reason;
-    if (!saved && !has_current) return OXZ_OK;
-    if (saved && !has_current)
-        reason = "the checkpoint trained on trainer.data.sources weights " + debug_weights(p.mixture_weights) + ", and this run sets no weights.";
-    else if (!saved && has_current)
-        reason = "the checkpoint trained without trainer.data.sources weights, and this run sets weights " + debug_weights(current) + ".";
-    else if (p.mixture_weights.size() != current.size())
-        reason = "the checkpoint trained on " + std::to_string(p.mixture_weights.size()) + " weighted trainer.data.sources, and this run sets " +
-                 std::to_string(current.size()) + ".";
-    else {
-        for (size_t i = 0; i < current.size() && reason.empty(); i++)
-            if (memcmp(&p.mixture_weights[i], &current[i], 8) != 0)  // compared by bits
-                reason = "trainer.data.sources[" + std::to_string(i) + "].weight was " + display_f64(p.mixture_weights[i]) +
-                         ", and this run sets " + display_f64(current[i]) + ".";
-        if (reason.empty() && p.m.mixture_rows_per_epoch != rows_per_epoch)
-            reason = "trainer.data.rows_per_epoch was " + std::to_string(p.m.mixture_rows_per_epoch) + ", and this run reads " +
-                     std::to_string(rows_per_epoch) + " rows per epoch.";
-    }
-    if (reason.empty()) return OXZ_OK;
-    return fail(OXZ_ERR_DATA, "checkpoint meta '%s': %s The mixture decides which rows the saved data position counts. Resume with the original config, or start a fresh run.",
-                meta_path, reason.c_str());
+    return oxz::guarded("oxz_check_mixture_resume", [&]() -> int32_t {
+        if (has_current && n_weights && !weights) return fail(OXZ_ERR_INVALID, "oxz_check_mixture_resume: null argument");
+        if (!meta_path || start_step == 0) return OXZ_OK;
+        Parsed p;
+        std::string why;
+        if (!parse_file(meta_path, &p, &why))
+            return fail(OXZ_ERR_DATA, "checkpoint meta '%s' was not read: %s. Restore the file to resume with its data mixture.",
+                        meta_path, why.c_str());
+        const bool saved = p.m.has_mixture != 0;
+        const std::vector<double> current(weights, weights + (has_current ? n_weights : 0));
+        std::string reason;
+        if (!saved && !has_current) return OXZ_OK;
+        if (saved && !has_current)
+            reason = "the checkpoint trained on trainer.data.sources weights " + debug_weights(p.mixture_weights) + ", and this run sets no weights.";
+        else if (!saved && has_current)
+            reason = "the checkpoint trained without trainer.data.sources weights, and this run sets weights " + debug_weights(current) + ".";
+        else if (p.mixture_weights.size() != current.size())
+            reason = "the checkpoint trained on " + std::to_string(p.mixture_weights.size()) + " weighted trainer.data.sources, and this run sets " +
+                     std::to_string(current.size()) + ".";
+        else {
+            for (size_t i = 0; i < current.size() && reason.empty(); i++)
+                if (memcmp(&p.mixture_weights[i], &current[i], 8) != 0)  // compared by bits
+                    reason = "trainer.data.sources[" + std::to_string(i) + "].weight was " + display_f64(p.mixture_weights[i]) +
+                             ", and this run sets " + display_f64(current[i]) + ".";
+            if (reason.empty() && p.m.mixture_rows_per_epoch != rows_per_epoch)
+                reason = "trainer.data.rows_per_epoch was " + std::to_string(p.m.mixture_rows_per_epoch) + ", and this run reads " +
+                         std::to_string(rows_per_epoch) + " rows per epoch.";
+        }
+        if (reason.empty()) return OXZ_OK;
+        return fail(OXZ_ERR_DATA, "checkpoint meta '%s': %s The mixture decides which rows the saved data position counts. Resume with the original config, or start a fresh run.",
+                    meta_path, reason.c_str());
+    });
 }
 
 int32_t oxz_read_loss_scale_state(const char* meta_path, uint64_t start_step, int32_t* has_state, oxz_scaler_state* state) {
-    if (!has_state || !state) return fail(OXZ_ERR_INVALID, "oxz_read_loss_scale_state: null argument");
-    *has_state = 0;
-    if (!meta_path || start_step == 0) return OXZ_OK;
-    Parsed p;
-    std::string why;
-    if (!parse_file(meta_path, &p, &why))
-        return fail(OXZ_ERR_INVALID, "checkpoint meta '%s' was not read: %s. Restore the file to resume with its loss scale.",
-                    meta_path, why.c_str());
-    if (p.m.has_loss_scale) {
-        *has_state = 1;
-        *state = p.m.loss_scale;
-    }
-    return OXZ_OK;
+    return oxz::guarded("oxz_read_loss_scale_state", [&]() -> int32_t {
+        if (!has_state || !state) return fail(OXZ_ERR_INVALID, "oxz_read_loss_scale_state: null argument");
+        *has_state = 0;
+        if (!meta_path || start_step == 0) return OXZ_OK;
+        Parsed p;
+        std::string why;
+        if (!parse_file(meta_path, &p, &why))
+            return fail(OXZ_ERR_INVALID, "checkpoint meta '%s' was not read: %s. Restore the file to resume with its loss scale.",
+                        meta_path, why.c_str());
+        if (p.m.has_loss_scale) {
+            *has_state = 1;
+            *state = p.m.loss_scale;
+        }
+        return OXZ_OK;
+    });
 }
 
 }  // extern "C"

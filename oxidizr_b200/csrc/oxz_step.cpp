@@ -190,282 +190,308 @@ int32_t check_state_call(oxz_plan* p, int32_t kind, uint64_t tensor, const void*
 extern "C" {
 
 int32_t oxz_plan_destroy(oxz_plan* p) {
-    if (!p) return OXZ_OK;
-    if (p->allocated || p->own_stream) {  // also after an allocation that failed midway
-        cudaSetDevice(p->device);
-        if (p->stream) cudaStreamSynchronize(p->stream);
-        for (void* q : p->ipc_opened) cudaIpcCloseMemHandle(q);
-        if (p->work && p->work != (void*)p->master) cudaFree(p->work);
-        for (void* q : {(void*)p->grads, (void*)p->master, (void*)p->exp_avg, (void*)p->exp_avg_sq, p->reduced,
-                        (void*)p->d_tile_meta, (void*)p->d_present, (void*)p->d_offsets, (void*)p->d_numel,
-                        (void*)p->d_src, (void*)p->d_partials, (void*)p->d_acc, (void*)p->d_scalars})
-            if (q) cudaFree(q);
-        for (void* q : {(void*)p->h_scalars, (void*)p->h_acc, (void*)p->h_extras, (void*)p->h_present, (void*)p->h_src})
-            if (q) cudaFreeHost(q);
-        if (p->grads_alt) cudaFree(p->grads_alt);
-        if (p->upload_stream) cudaStreamDestroy(p->upload_stream);
-        if (p->ev_uploaded) cudaEventDestroy(p->ev_uploaded);
-        for (auto e : p->ev_last_read) if (e) cudaEventDestroy(e);
-        if (p->early_stream) cudaStreamDestroy(p->early_stream);
-        if (p->ev_produced) cudaEventDestroy(p->ev_produced);
-        if (p->ev_early) cudaEventDestroy(p->ev_early);
-        if (p->stage) cudaFree(p->stage);
-        for (auto st : p->copy_stream) if (st) cudaStreamDestroy(st);
-        if (p->ev_go) cudaEventDestroy(p->ev_go);
-        for (auto& row : p->ev_copied) for (auto e : row) if (e) cudaEventDestroy(e);
-        for (auto e : p->ev_updated) if (e) cudaEventDestroy(e);
-        for (auto e : p->ev_pushed) if (e) cudaEventDestroy(e);
-        if (p->done) cudaEventDestroy(p->done);
-        for (auto e : p->ev) if (e) cudaEventDestroy(e);
-        if (p->own_stream) cudaStreamDestroy(p->own_stream);
-    }
-    delete p;
-    return OXZ_OK;
+    return oxz::guarded("oxz_plan_destroy", [&]() -> int32_t {
+        if (!p) return OXZ_OK;
+        if (p->allocated || p->own_stream) {  // also after an allocation that failed midway
+            cudaSetDevice(p->device);
+            if (p->stream) cudaStreamSynchronize(p->stream);
+            for (void* q : p->ipc_opened) cudaIpcCloseMemHandle(q);
+            if (p->work && p->work != (void*)p->master) cudaFree(p->work);
+            for (void* q : {(void*)p->grads, (void*)p->master, (void*)p->exp_avg, (void*)p->exp_avg_sq, p->reduced,
+                            (void*)p->d_tile_meta, (void*)p->d_present, (void*)p->d_offsets, (void*)p->d_numel,
+                            (void*)p->d_src, (void*)p->d_partials, (void*)p->d_acc, (void*)p->d_scalars})
+                if (q) cudaFree(q);
+            for (void* q : {(void*)p->h_scalars, (void*)p->h_acc, (void*)p->h_extras, (void*)p->h_present, (void*)p->h_src})
+                if (q) cudaFreeHost(q);
+            if (p->grads_alt) cudaFree(p->grads_alt);
+            if (p->upload_stream) cudaStreamDestroy(p->upload_stream);
+            if (p->ev_uploaded) cudaEventDestroy(p->ev_uploaded);
+            for (auto e : p->ev_last_read) if (e) cudaEventDestroy(e);
+            if (p->early_stream) cudaStreamDestroy(p->early_stream);
+            if (p->ev_produced) cudaEventDestroy(p->ev_produced);
+            if (p->ev_early) cudaEventDestroy(p->ev_early);
+            if (p->stage) cudaFree(p->stage);
+            for (auto st : p->copy_stream) if (st) cudaStreamDestroy(st);
+            if (p->ev_go) cudaEventDestroy(p->ev_go);
+            for (auto& row : p->ev_copied) for (auto e : row) if (e) cudaEventDestroy(e);
+            for (auto e : p->ev_updated) if (e) cudaEventDestroy(e);
+            for (auto e : p->ev_pushed) if (e) cudaEventDestroy(e);
+            if (p->done) cudaEventDestroy(p->done);
+            for (auto e : p->ev) if (e) cudaEventDestroy(e);
+            if (p->own_stream) cudaStreamDestroy(p->own_stream);
+        }
+        delete p;
+        return OXZ_OK;
+    });
 }
 
 int32_t oxz_plan_set_stream(oxz_plan* p, void* stream) {
-    if (!p) return fail(OXZ_ERR_INVALID, "oxz_plan_set_stream: null plan");
-    if (!p->allocated) return fail(OXZ_ERR_STATE, "oxz_plan_set_stream: call oxz_state_alloc first");
-    if (p->inflight) return fail(OXZ_ERR_STATE, "oxz_plan_set_stream: a step is in flight");
-    p->stream = stream ? (cudaStream_t)stream : p->own_stream;
-    return OXZ_OK;
+    return oxz::guarded("oxz_plan_set_stream", [&]() -> int32_t {
+        if (!p) return fail(OXZ_ERR_INVALID, "oxz_plan_set_stream: null plan");
+        if (!p->allocated) return fail(OXZ_ERR_STATE, "oxz_plan_set_stream: call oxz_state_alloc first");
+        if (p->inflight) return fail(OXZ_ERR_STATE, "oxz_plan_set_stream: a step is in flight");
+        p->stream = stream ? (cudaStream_t)stream : p->own_stream;
+        return OXZ_OK;
+    });
 }
 
 int32_t oxz_state_alloc(oxz_plan* p, oxz_comm* comm) {
-    if (!p) return fail(OXZ_ERR_INVALID, "oxz_state_alloc: null plan");
-    if (p->allocated) return fail(OXZ_ERR_STATE, "oxz_state_alloc: the plan already has device state");
-    if (p->own_stream) return fail(OXZ_ERR_STATE, "oxz_state_alloc: an earlier allocation of this plan failed midway. Destroy the plan and create it again");
-    if (p->cw > 1) {
-        OXZ_TRY(comm_check(comm, "oxz_state_alloc"));
-        if (comm->world != p->cw || comm->rank != p->cr)
-            return fail(OXZ_ERR_INVALID, "oxz_state_alloc: the plan is rank %d of %d but the communicator is rank %d of %d",
-                        p->cr, p->cw, comm->rank, comm->world);
-    }
-    OXZ_CUDA(cudaSetDevice(p->device));
-    OXZ_TRY(query_geom(p->device, &p->geom));
-    OXZ_CUDA(cudaStreamCreateWithFlags(&p->own_stream, cudaStreamNonBlocking));
-    p->stream = p->own_stream;
-    p->comm = comm;
-    const uint64_t padded = p->total_tiles * TILE, local = p->local_tiles * TILE;
-    const size_t gs = dtype_size(p->gdt), ps = dtype_size(p->pdt);
-    auto zalloc = [](void** q, size_t bytes) -> cudaError_t {
-        cudaError_t e = cudaMalloc(q, bytes ? bytes : 16);
-        if (e != cudaSuccess) return e;
-        return cudaMemset(*q, 0, bytes ? bytes : 16);
-    };
-    OXZ_CUDA(zalloc(&p->grads, padded * gs));
-    OXZ_CUDA(zalloc((void**)&p->master, local * 4));
-    OXZ_CUDA(zalloc((void**)&p->exp_avg, local * 4));
-    OXZ_CUDA(zalloc((void**)&p->exp_avg_sq, local * 4));
-    const bool separate_work = !(p->pdt == OXZ_F32 && p->world == 1);
-    if (separate_work) OXZ_CUDA(zalloc(&p->work, padded * ps));
-    else p->work = p->master;
-    const bool peer_mode = p->mode == OXZ_SYNC_P2P || p->mode == OXZ_SYNC_COPY || p->mode == OXZ_SYNC_REPLICATED;
-    if (p->cw > 1) OXZ_CUDA(zalloc(&p->reduced, local * (peer_mode ? 4 : gs)));
-    OXZ_CUDA(zalloc((void**)&p->d_tile_meta, p->total_tiles * 4));
-    OXZ_CUDA(cudaMemcpy(p->d_tile_meta, p->tile_meta.data(), p->total_tiles * 4, cudaMemcpyHostToDevice));
-    OXZ_CUDA(zalloc((void**)&p->d_present, p->T));
-    if (p->T) OXZ_CUDA(cudaMemset(p->d_present, 1, p->T));
-    OXZ_CUDA(zalloc((void**)&p->d_offsets, p->T * 8));
-    OXZ_CUDA(zalloc((void**)&p->d_numel, p->T * 8));
-    if (p->T) {
-        OXZ_CUDA(cudaMemcpy(p->d_offsets, p->offset.data(), p->T * 8, cudaMemcpyHostToDevice));
-        OXZ_CUDA(cudaMemcpy(p->d_numel, p->numel.data(), p->T * 8, cudaMemcpyHostToDevice));
-    }
-    OXZ_CUDA(zalloc((void**)&p->d_src, p->T * 8));
-    OXZ_CUDA(zalloc((void**)&p->d_partials, (size_t)norm_partial_slots(p->geom) * 3 * 8 * MAX_PIPE));
-    OXZ_CUDA(zalloc((void**)&p->d_acc, (3 + MAX_EXTRAS) * 8));
-    OXZ_CUDA(zalloc((void**)&p->d_scalars, sizeof(DevScalars)));
-    OXZ_CUDA(cudaMallocHost((void**)&p->h_scalars, sizeof(DevScalars)));
-    OXZ_CUDA(cudaMallocHost((void**)&p->h_acc, (3 + MAX_EXTRAS) * 8));
-    OXZ_CUDA(cudaMallocHost((void**)&p->h_extras, MAX_EXTRAS * 8));
-    OXZ_CUDA(cudaMallocHost((void**)&p->h_present, p->T ? p->T : 1));
-    OXZ_CUDA(cudaMallocHost((void**)&p->h_src, (p->T ? p->T : 1) * 8));
-    memset(p->h_present, 1, p->T ? p->T : 1);
-    OXZ_CUDA(cudaEventCreateWithFlags(&p->done, cudaEventDisableTiming));
-    OXZ_CUDA(cudaDeviceSynchronize());
-    p->peers.grads[0] = p->grads;
-    p->peers.work[0] = p->work;
-    if (peer_mode) OXZ_TRY(exchange_peers(p, comm));
-    p->own_work.work[0] = p->work;
-    if (p->mode == OXZ_SYNC_COPY) {
-        // one staging slot per peer, laid out like this rank's local state; the own slot is the gradient buffer itself
-        OXZ_CUDA(zalloc(&p->stage, (size_t)(p->world - 1) * local * gs));
-        int slot = 0;
-        for (int r = 0; r < p->world; r++) {
-            if (r == p->rank) {
-                p->staged_src.grads[r] = p->grads;
-            } else {
-                p->staged_src.grads[r] = static_cast<char*>(p->stage) + (size_t)slot * local * gs;
-                slot++;
-            }
-            OXZ_CUDA(cudaStreamCreateWithFlags(&p->copy_stream[r], cudaStreamNonBlocking));
-            OXZ_CUDA(cudaEventCreateWithFlags(&p->ev_pushed[r], cudaEventDisableTiming));
-            for (uint32_t g = 0; g < MAX_PIPE; g++) OXZ_CUDA(cudaEventCreateWithFlags(&p->ev_copied[r][g], cudaEventDisableTiming));
+    return oxz::guarded("oxz_state_alloc", [&]() -> int32_t {
+        if (!p) return fail(OXZ_ERR_INVALID, "oxz_state_alloc: null plan");
+        if (p->allocated) return fail(OXZ_ERR_STATE, "oxz_state_alloc: the plan already has device state");
+        if (p->own_stream) return fail(OXZ_ERR_STATE, "oxz_state_alloc: an earlier allocation of this plan failed midway. Destroy the plan and create it again");
+        if (p->cw > 1) {
+            OXZ_TRY(comm_check(comm, "oxz_state_alloc"));
+            if (comm->world != p->cw || comm->rank != p->cr)
+                return fail(OXZ_ERR_INVALID, "oxz_state_alloc: the plan is rank %d of %d but the communicator is rank %d of %d",
+                            p->cr, p->cw, comm->rank, comm->world);
         }
-        OXZ_CUDA(cudaEventCreateWithFlags(&p->ev_go, cudaEventDisableTiming));
-        for (uint32_t g = 0; g < MAX_PIPE; g++) OXZ_CUDA(cudaEventCreateWithFlags(&p->ev_updated[g], cudaEventDisableTiming));
-        const char* e = getenv("OXZ_PIPE_GROUPS");
-        uint32_t want = e ? (uint32_t)atoi(e) : 4;
-        if (want < 1) want = 1;
-        if (want > MAX_PIPE) want = MAX_PIPE;
-        if (want > p->n_buckets) want = (uint32_t)p->n_buckets;
-        p->pipe_groups = want;
-    }
-    p->allocated = true;
-    return OXZ_OK;
+        OXZ_CUDA(cudaSetDevice(p->device));
+        OXZ_TRY(query_geom(p->device, &p->geom));
+        OXZ_CUDA(cudaStreamCreateWithFlags(&p->own_stream, cudaStreamNonBlocking));
+        p->stream = p->own_stream;
+        p->comm = comm;
+        const uint64_t padded = p->total_tiles * TILE, local = p->local_tiles * TILE;
+        const size_t gs = dtype_size(p->gdt), ps = dtype_size(p->pdt);
+        auto zalloc = [](void** q, size_t bytes) -> cudaError_t {
+            cudaError_t e = cudaMalloc(q, bytes ? bytes : 16);
+            if (e != cudaSuccess) return e;
+            return cudaMemset(*q, 0, bytes ? bytes : 16);
+        };
+        OXZ_CUDA(zalloc(&p->grads, padded * gs));
+        OXZ_CUDA(zalloc((void**)&p->master, local * 4));
+        OXZ_CUDA(zalloc((void**)&p->exp_avg, local * 4));
+        OXZ_CUDA(zalloc((void**)&p->exp_avg_sq, local * 4));
+        const bool separate_work = !(p->pdt == OXZ_F32 && p->world == 1);
+        if (separate_work) OXZ_CUDA(zalloc(&p->work, padded * ps));
+        else p->work = p->master;
+        const bool peer_mode = p->mode == OXZ_SYNC_P2P || p->mode == OXZ_SYNC_COPY || p->mode == OXZ_SYNC_REPLICATED;
+        if (p->cw > 1) OXZ_CUDA(zalloc(&p->reduced, local * (peer_mode ? 4 : gs)));
+        OXZ_CUDA(zalloc((void**)&p->d_tile_meta, p->total_tiles * 4));
+        OXZ_CUDA(cudaMemcpy(p->d_tile_meta, p->tile_meta.data(), p->total_tiles * 4, cudaMemcpyHostToDevice));
+        OXZ_CUDA(zalloc((void**)&p->d_present, p->T));
+        if (p->T) OXZ_CUDA(cudaMemset(p->d_present, 1, p->T));
+        OXZ_CUDA(zalloc((void**)&p->d_offsets, p->T * 8));
+        OXZ_CUDA(zalloc((void**)&p->d_numel, p->T * 8));
+        if (p->T) {
+            OXZ_CUDA(cudaMemcpy(p->d_offsets, p->offset.data(), p->T * 8, cudaMemcpyHostToDevice));
+            OXZ_CUDA(cudaMemcpy(p->d_numel, p->numel.data(), p->T * 8, cudaMemcpyHostToDevice));
+        }
+        OXZ_CUDA(zalloc((void**)&p->d_src, p->T * 8));
+        OXZ_CUDA(zalloc((void**)&p->d_partials, (size_t)norm_partial_slots(p->geom) * 3 * 8 * MAX_PIPE));
+        OXZ_CUDA(zalloc((void**)&p->d_acc, (3 + MAX_EXTRAS) * 8));
+        OXZ_CUDA(zalloc((void**)&p->d_scalars, sizeof(DevScalars)));
+        OXZ_CUDA(cudaMallocHost((void**)&p->h_scalars, sizeof(DevScalars)));
+        OXZ_CUDA(cudaMallocHost((void**)&p->h_acc, (3 + MAX_EXTRAS) * 8));
+        OXZ_CUDA(cudaMallocHost((void**)&p->h_extras, MAX_EXTRAS * 8));
+        OXZ_CUDA(cudaMallocHost((void**)&p->h_present, p->T ? p->T : 1));
+        OXZ_CUDA(cudaMallocHost((void**)&p->h_src, (p->T ? p->T : 1) * 8));
+        memset(p->h_present, 1, p->T ? p->T : 1);
+        OXZ_CUDA(cudaEventCreateWithFlags(&p->done, cudaEventDisableTiming));
+        OXZ_CUDA(cudaDeviceSynchronize());
+        p->peers.grads[0] = p->grads;
+        p->peers.work[0] = p->work;
+        if (peer_mode) OXZ_TRY(exchange_peers(p, comm));
+        p->own_work.work[0] = p->work;
+        if (p->mode == OXZ_SYNC_COPY) {
+            // one staging slot per peer, laid out like this rank's local state; the own slot is the gradient buffer itself
+            OXZ_CUDA(zalloc(&p->stage, (size_t)(p->world - 1) * local * gs));
+            int slot = 0;
+            for (int r = 0; r < p->world; r++) {
+                if (r == p->rank) {
+                    p->staged_src.grads[r] = p->grads;
+                } else {
+                    p->staged_src.grads[r] = static_cast<char*>(p->stage) + (size_t)slot * local * gs;
+                    slot++;
+                }
+                OXZ_CUDA(cudaStreamCreateWithFlags(&p->copy_stream[r], cudaStreamNonBlocking));
+                OXZ_CUDA(cudaEventCreateWithFlags(&p->ev_pushed[r], cudaEventDisableTiming));
+                for (uint32_t g = 0; g < MAX_PIPE; g++) OXZ_CUDA(cudaEventCreateWithFlags(&p->ev_copied[r][g], cudaEventDisableTiming));
+            }
+            OXZ_CUDA(cudaEventCreateWithFlags(&p->ev_go, cudaEventDisableTiming));
+            for (uint32_t g = 0; g < MAX_PIPE; g++) OXZ_CUDA(cudaEventCreateWithFlags(&p->ev_updated[g], cudaEventDisableTiming));
+            const char* e = getenv("OXZ_PIPE_GROUPS");
+            uint32_t want = e ? (uint32_t)atoi(e) : 4;
+            if (want < 1) want = 1;
+            if (want > MAX_PIPE) want = MAX_PIPE;
+            if (want > p->n_buckets) want = (uint32_t)p->n_buckets;
+            p->pipe_groups = want;
+        }
+        p->allocated = true;
+        return OXZ_OK;
+    });
 }
 
 int32_t oxz_state_pointers(const oxz_plan* p, void** grads, void** work, void** master, void** exp_avg,
                            void** exp_avg_sq) {
-    if (!p) return fail(OXZ_ERR_INVALID, "oxz_state_pointers: null plan");
-    if (!p->allocated) return fail(OXZ_ERR_STATE, "oxz_state_pointers: call oxz_state_alloc first");
-    if (grads) *grads = p->grads;
-    if (work) *work = p->work;
-    if (master) *master = p->master;
-    if (exp_avg) *exp_avg = p->exp_avg;
-    if (exp_avg_sq) *exp_avg_sq = p->exp_avg_sq;
-    return OXZ_OK;
+    return oxz::guarded("oxz_state_pointers", [&]() -> int32_t {
+        if (!p) return fail(OXZ_ERR_INVALID, "oxz_state_pointers: null plan");
+        if (!p->allocated) return fail(OXZ_ERR_STATE, "oxz_state_pointers: call oxz_state_alloc first");
+        if (grads) *grads = p->grads;
+        if (work) *work = p->work;
+        if (master) *master = p->master;
+        if (exp_avg) *exp_avg = p->exp_avg;
+        if (exp_avg_sq) *exp_avg_sq = p->exp_avg_sq;
+        return OXZ_OK;
+    });
 }
 
 int32_t oxz_state_import(oxz_plan* p, int32_t kind, uint64_t tensor, const void* host) {
-    OXZ_TRY(check_state_call(p, kind, tensor, host, "oxz_state_import"));
-    OXZ_CUDA(cudaSetDevice(p->device));
-    OXZ_CUDA(cudaStreamSynchronize(p->stream));
-    const uint64_t n = p->numel[tensor];
-    if (kind == OXZ_STATE_GRADS || kind == OXZ_STATE_WORK) {
-        const size_t es = dtype_size(kind == OXZ_STATE_GRADS ? p->gdt : p->pdt);
-        char* base = static_cast<char*>(kind == OXZ_STATE_GRADS ? p->grads : p->work);
-        if (kind == OXZ_STATE_WORK && p->work == (void*)p->master) kind = OXZ_STATE_MASTER;
-        else {
-            OXZ_CUDA(cudaMemcpy(base + p->offset[tensor] * es, host, n * es, cudaMemcpyHostToDevice));
-            return OXZ_OK;
+    return oxz::guarded("oxz_state_import", [&]() -> int32_t {
+        OXZ_TRY(check_state_call(p, kind, tensor, host, "oxz_state_import"));
+        OXZ_CUDA(cudaSetDevice(p->device));
+        OXZ_CUDA(cudaStreamSynchronize(p->stream));
+        const uint64_t n = p->numel[tensor];
+        if (kind == OXZ_STATE_GRADS || kind == OXZ_STATE_WORK) {
+            const size_t es = dtype_size(kind == OXZ_STATE_GRADS ? p->gdt : p->pdt);
+            char* base = static_cast<char*>(kind == OXZ_STATE_GRADS ? p->grads : p->work);
+            if (kind == OXZ_STATE_WORK && p->work == (void*)p->master) kind = OXZ_STATE_MASTER;
+            else {
+                OXZ_CUDA(cudaMemcpy(base + p->offset[tensor] * es, host, n * es, cudaMemcpyHostToDevice));
+                return OXZ_OK;
+            }
         }
-    }
-    float* arr = state_array(p, kind);
-    cudaError_t err = cudaSuccess;
-    for_owned_runs(p, tensor, [&](uint64_t flat, uint64_t local, uint64_t len) {
-        if (err != cudaSuccess) return;
-        err = cudaMemcpy(arr + local, static_cast<const float*>(host) + (flat - p->offset[tensor]), len * 4, cudaMemcpyHostToDevice);
+        float* arr = state_array(p, kind);
+        cudaError_t err = cudaSuccess;
+        for_owned_runs(p, tensor, [&](uint64_t flat, uint64_t local, uint64_t len) {
+            if (err != cudaSuccess) return;
+            err = cudaMemcpy(arr + local, static_cast<const float*>(host) + (flat - p->offset[tensor]), len * 4, cudaMemcpyHostToDevice);
+        });
+        if (err != cudaSuccess) return fail(OXZ_ERR_CUDA, "oxz_state_import: %s", cudaGetErrorString(err));
+        return OXZ_OK;
     });
-    if (err != cudaSuccess) return fail(OXZ_ERR_CUDA, "oxz_state_import: %s", cudaGetErrorString(err));
-    return OXZ_OK;
 }
 
 int32_t oxz_state_export(oxz_plan* p, int32_t kind, uint64_t tensor, void* host) {
-    OXZ_TRY(check_state_call(p, kind, tensor, host, "oxz_state_export"));
-    OXZ_CUDA(cudaSetDevice(p->device));
-    OXZ_CUDA(cudaStreamSynchronize(p->stream));
-    const uint64_t n = p->numel[tensor];
-    if (kind == OXZ_STATE_GRADS || kind == OXZ_STATE_WORK) {
-        const size_t es = dtype_size(kind == OXZ_STATE_GRADS ? p->gdt : p->pdt);
-        const char* base = static_cast<const char*>(kind == OXZ_STATE_GRADS ? p->grads : p->work);
-        if (kind == OXZ_STATE_WORK && p->work == (void*)p->master) kind = OXZ_STATE_MASTER;
-        else {
-            OXZ_CUDA(cudaMemcpy(host, base + p->offset[tensor] * es, n * es, cudaMemcpyDeviceToHost));
-            return OXZ_OK;
+    return oxz::guarded("oxz_state_export", [&]() -> int32_t {
+        OXZ_TRY(check_state_call(p, kind, tensor, host, "oxz_state_export"));
+        OXZ_CUDA(cudaSetDevice(p->device));
+        OXZ_CUDA(cudaStreamSynchronize(p->stream));
+        const uint64_t n = p->numel[tensor];
+        if (kind == OXZ_STATE_GRADS || kind == OXZ_STATE_WORK) {
+            const size_t es = dtype_size(kind == OXZ_STATE_GRADS ? p->gdt : p->pdt);
+            const char* base = static_cast<const char*>(kind == OXZ_STATE_GRADS ? p->grads : p->work);
+            if (kind == OXZ_STATE_WORK && p->work == (void*)p->master) kind = OXZ_STATE_MASTER;
+            else {
+                OXZ_CUDA(cudaMemcpy(host, base + p->offset[tensor] * es, n * es, cudaMemcpyDeviceToHost));
+                return OXZ_OK;
+            }
         }
-    }
-    const float* arr = state_array(p, kind);
-    cudaError_t err = cudaSuccess;
-    for_owned_runs(p, tensor, [&](uint64_t flat, uint64_t local, uint64_t len) {
-        if (err != cudaSuccess) return;
-        err = cudaMemcpy(static_cast<float*>(host) + (flat - p->offset[tensor]), arr + local, len * 4, cudaMemcpyDeviceToHost);
+        const float* arr = state_array(p, kind);
+        cudaError_t err = cudaSuccess;
+        for_owned_runs(p, tensor, [&](uint64_t flat, uint64_t local, uint64_t len) {
+            if (err != cudaSuccess) return;
+            err = cudaMemcpy(static_cast<float*>(host) + (flat - p->offset[tensor]), arr + local, len * 4, cudaMemcpyDeviceToHost);
+        });
+        if (err != cudaSuccess) return fail(OXZ_ERR_CUDA, "oxz_state_export: %s", cudaGetErrorString(err));
+        return OXZ_OK;
     });
-    if (err != cudaSuccess) return fail(OXZ_ERR_CUDA, "oxz_state_export: %s", cudaGetErrorString(err));
-    return OXZ_OK;
 }
 
 int32_t oxz_state_set_timestep(oxz_plan* p, uint64_t t) {
-    if (!p) return fail(OXZ_ERR_INVALID, "oxz_state_set_timestep: null plan");
-    if (p->inflight) return fail(OXZ_ERR_STATE, "oxz_state_set_timestep: a step is in flight");
-    p->timestep = t;
-    return OXZ_OK;
+    return oxz::guarded("oxz_state_set_timestep", [&]() -> int32_t {
+        if (!p) return fail(OXZ_ERR_INVALID, "oxz_state_set_timestep: null plan");
+        if (p->inflight) return fail(OXZ_ERR_STATE, "oxz_state_set_timestep: a step is in flight");
+        p->timestep = t;
+        return OXZ_OK;
+    });
 }
 
 int32_t oxz_state_timestep(const oxz_plan* p, uint64_t* t) {
-    if (!p || !t) return fail(OXZ_ERR_INVALID, "oxz_state_timestep: null argument");
-    *t = p->timestep;
-    return OXZ_OK;
+    return oxz::guarded("oxz_state_timestep", [&]() -> int32_t {
+        if (!p || !t) return fail(OXZ_ERR_INVALID, "oxz_state_timestep: null argument");
+        *t = p->timestep;
+        return OXZ_OK;
+    });
 }
 
 int32_t oxz_grads_flatten_async(oxz_plan* p, const void* const* grad_ptrs, int32_t accumulate) {
-    if (!p || !grad_ptrs) return fail(OXZ_ERR_INVALID, "oxz_grads_flatten_async: null argument");
-    if (!p->allocated) return fail(OXZ_ERR_STATE, "oxz_grads_flatten_async: call oxz_state_alloc first");
-    if (p->inflight) return fail(OXZ_ERR_STATE, "oxz_grads_flatten_async: a step is in flight. Call oxz_step_wait first");
-    OXZ_CUDA(cudaSetDevice(p->device));
-    for (uint64_t i = 0; i < p->T; i++) {
-        if (grad_ptrs[i] && ((uintptr_t)grad_ptrs[i] & 15))
-            return fail(OXZ_ERR_INVALID, "oxz_grads_flatten_async: the gradient of tensor %llu is not 16-byte aligned", (unsigned long long)i);
-    }
-    // The pointer table is staged in pinned memory; the previous use must have left the stream.
-    OXZ_CUDA(cudaStreamSynchronize(p->stream));
-    for (uint64_t i = 0; i < p->T; i++) p->h_src[i] = grad_ptrs[i];
-    if (p->T) OXZ_CUDA(cudaMemcpyAsync(p->d_src, p->h_src, p->T * 8, cudaMemcpyHostToDevice, p->stream));
-    return launch_flatten(p->stream, p->geom, p->grads, p->gdt, (uint32_t)p->total_tiles, p->d_tile_meta, p->d_offsets,
-                          p->d_numel, p->d_src, accumulate);
+    return oxz::guarded("oxz_grads_flatten_async", [&]() -> int32_t {
+        if (!p || !grad_ptrs) return fail(OXZ_ERR_INVALID, "oxz_grads_flatten_async: null argument");
+        if (!p->allocated) return fail(OXZ_ERR_STATE, "oxz_grads_flatten_async: call oxz_state_alloc first");
+        if (p->inflight) return fail(OXZ_ERR_STATE, "oxz_grads_flatten_async: a step is in flight. Call oxz_step_wait first");
+        OXZ_CUDA(cudaSetDevice(p->device));
+        for (uint64_t i = 0; i < p->T; i++) {
+            if (grad_ptrs[i] && ((uintptr_t)grad_ptrs[i] & 15))
+                return fail(OXZ_ERR_INVALID, "oxz_grads_flatten_async: the gradient of tensor %llu is not 16-byte aligned", (unsigned long long)i);
+        }
+        // The pointer table is staged in pinned memory; the previous use must have left the stream.
+        OXZ_CUDA(cudaStreamSynchronize(p->stream));
+        for (uint64_t i = 0; i < p->T; i++) p->h_src[i] = grad_ptrs[i];
+        if (p->T) OXZ_CUDA(cudaMemcpyAsync(p->d_src, p->h_src, p->T * 8, cudaMemcpyHostToDevice, p->stream));
+        return launch_flatten(p->stream, p->geom, p->grads, p->gdt, (uint32_t)p->total_tiles, p->d_tile_meta, p->d_offsets,
+                              p->d_numel, p->d_src, accumulate);
+    });
 }
 
 int32_t oxz_grads_upload_async(oxz_plan* p, uint64_t tensor, const void* host) {
-    if (!p || !host) return fail(OXZ_ERR_INVALID, "oxz_grads_upload_async: null argument");
-    if (!p->allocated) return fail(OXZ_ERR_STATE, "oxz_grads_upload_async: call oxz_state_alloc first");
-    if (p->inflight) return fail(OXZ_ERR_STATE, "oxz_grads_upload_async: a step is in flight. Call oxz_step_wait first");
-    if (tensor >= p->T) return fail(OXZ_ERR_INVALID, "oxz_grads_upload_async: tensor %llu of %llu", (unsigned long long)tensor, (unsigned long long)p->T);
-    OXZ_CUDA(cudaSetDevice(p->device));
-    const size_t es = dtype_size(p->gdt);
-    OXZ_CUDA(cudaMemcpyAsync(static_cast<char*>(p->grads) + p->offset[tensor] * es, host, p->numel[tensor] * es,
-                             cudaMemcpyHostToDevice, p->stream));
-    return OXZ_OK;
+    return oxz::guarded("oxz_grads_upload_async", [&]() -> int32_t {
+        if (!p || !host) return fail(OXZ_ERR_INVALID, "oxz_grads_upload_async: null argument");
+        if (!p->allocated) return fail(OXZ_ERR_STATE, "oxz_grads_upload_async: call oxz_state_alloc first");
+        if (p->inflight) return fail(OXZ_ERR_STATE, "oxz_grads_upload_async: a step is in flight. Call oxz_step_wait first");
+        if (tensor >= p->T) return fail(OXZ_ERR_INVALID, "oxz_grads_upload_async: tensor %llu of %llu", (unsigned long long)tensor, (unsigned long long)p->T);
+        OXZ_CUDA(cudaSetDevice(p->device));
+        const size_t es = dtype_size(p->gdt);
+        OXZ_CUDA(cudaMemcpyAsync(static_cast<char*>(p->grads) + p->offset[tensor] * es, host, p->numel[tensor] * es,
+                                 cudaMemcpyHostToDevice, p->stream));
+        return OXZ_OK;
+    });
 }
 
 int32_t oxz_grads_double_buffer(oxz_plan* p, oxz_comm* comm) {
-    if (!p) return fail(OXZ_ERR_INVALID, "oxz_grads_double_buffer: null plan");
-    if (!p->allocated) return fail(OXZ_ERR_STATE, "oxz_grads_double_buffer: call oxz_state_alloc first");
-    if (p->inflight) return fail(OXZ_ERR_STATE, "oxz_grads_double_buffer: a step is in flight. Call oxz_step_wait first");
-    if (p->grads_alt) return OXZ_OK;
-    if (p->mode == OXZ_SYNC_COPY) return fail(OXZ_ERR_UNSUPPORTED, "oxz_grads_double_buffer does not serve OXZ_SYNC_COPY plans");
-    const bool peer_mode = p->mode == OXZ_SYNC_P2P || p->mode == OXZ_SYNC_REPLICATED;
-    if (peer_mode) {
-        OXZ_TRY(comm_check(comm, "oxz_grads_double_buffer"));
-        if (comm != p->comm) return fail(OXZ_ERR_INVALID, "oxz_grads_double_buffer: this is not the communicator the state was allocated with");
-    }
-    OXZ_CUDA(cudaSetDevice(p->device));
-    const size_t bytes = p->total_tiles * TILE * dtype_size(p->gdt);
-    OXZ_CUDA(cudaMalloc(&p->grads_alt, bytes ? bytes : 16));
-    OXZ_CUDA(cudaMemset(p->grads_alt, 0, bytes ? bytes : 16));
-    OXZ_CUDA(cudaStreamCreateWithFlags(&p->upload_stream, cudaStreamNonBlocking));
-    OXZ_CUDA(cudaEventCreateWithFlags(&p->ev_uploaded, cudaEventDisableTiming));
-    for (auto& e : p->ev_last_read) OXZ_CUDA(cudaEventCreateWithFlags(&e, cudaEventDisableTiming));
-    OXZ_CUDA(cudaDeviceSynchronize());
-    if (peer_mode) OXZ_TRY(exchange_alt_grads(p, comm));
-    return OXZ_OK;
+    return oxz::guarded("oxz_grads_double_buffer", [&]() -> int32_t {
+        if (!p) return fail(OXZ_ERR_INVALID, "oxz_grads_double_buffer: null plan");
+        if (!p->allocated) return fail(OXZ_ERR_STATE, "oxz_grads_double_buffer: call oxz_state_alloc first");
+        if (p->inflight) return fail(OXZ_ERR_STATE, "oxz_grads_double_buffer: a step is in flight. Call oxz_step_wait first");
+        if (p->grads_alt) return OXZ_OK;
+        if (p->mode == OXZ_SYNC_COPY) return fail(OXZ_ERR_UNSUPPORTED, "oxz_grads_double_buffer does not serve OXZ_SYNC_COPY plans");
+        const bool peer_mode = p->mode == OXZ_SYNC_P2P || p->mode == OXZ_SYNC_REPLICATED;
+        if (peer_mode) {
+            OXZ_TRY(comm_check(comm, "oxz_grads_double_buffer"));
+            if (comm != p->comm) return fail(OXZ_ERR_INVALID, "oxz_grads_double_buffer: this is not the communicator the state was allocated with");
+        }
+        OXZ_CUDA(cudaSetDevice(p->device));
+        const size_t bytes = p->total_tiles * TILE * dtype_size(p->gdt);
+        OXZ_CUDA(cudaMalloc(&p->grads_alt, bytes ? bytes : 16));
+        OXZ_CUDA(cudaMemset(p->grads_alt, 0, bytes ? bytes : 16));
+        OXZ_CUDA(cudaStreamCreateWithFlags(&p->upload_stream, cudaStreamNonBlocking));
+        OXZ_CUDA(cudaEventCreateWithFlags(&p->ev_uploaded, cudaEventDisableTiming));
+        for (auto& e : p->ev_last_read) OXZ_CUDA(cudaEventCreateWithFlags(&e, cudaEventDisableTiming));
+        OXZ_CUDA(cudaDeviceSynchronize());
+        if (peer_mode) OXZ_TRY(exchange_alt_grads(p, comm));
+        return OXZ_OK;
+    });
 }
 
 int32_t oxz_grads_upload_next_async(oxz_plan* p, uint64_t tensor, const void* host) {
-    if (!p || !host) return fail(OXZ_ERR_INVALID, "oxz_grads_upload_next_async: null argument");
-    if (!p->grads_alt) return fail(OXZ_ERR_STATE, "oxz_grads_upload_next_async: call oxz_grads_double_buffer first");
-    if (tensor >= p->T) return fail(OXZ_ERR_INVALID, "oxz_grads_upload_next_async: tensor %llu of %llu", (unsigned long long)tensor, (unsigned long long)p->T);
-    OXZ_CUDA(cudaSetDevice(p->device));
-    // the step that last read the other buffer (and, with peers, whose end says that every rank has read it) must be over
-    OXZ_CUDA(cudaStreamWaitEvent(p->upload_stream, p->ev_last_read[1 - p->cur_grads], 0));
-    const size_t es = dtype_size(p->gdt);
-    OXZ_CUDA(cudaMemcpyAsync(static_cast<char*>(p->grads_alt) + p->offset[tensor] * es, host, p->numel[tensor] * es,
-                             cudaMemcpyHostToDevice, p->upload_stream));
-    return OXZ_OK;
+    return oxz::guarded("oxz_grads_upload_next_async", [&]() -> int32_t {
+        if (!p || !host) return fail(OXZ_ERR_INVALID, "oxz_grads_upload_next_async: null argument");
+        if (!p->grads_alt) return fail(OXZ_ERR_STATE, "oxz_grads_upload_next_async: call oxz_grads_double_buffer first");
+        if (tensor >= p->T) return fail(OXZ_ERR_INVALID, "oxz_grads_upload_next_async: tensor %llu of %llu", (unsigned long long)tensor, (unsigned long long)p->T);
+        OXZ_CUDA(cudaSetDevice(p->device));
+        // the step that last read the other buffer (and, with peers, whose end says that every rank has read it) must be over
+        OXZ_CUDA(cudaStreamWaitEvent(p->upload_stream, p->ev_last_read[1 - p->cur_grads], 0));
+        const size_t es = dtype_size(p->gdt);
+        OXZ_CUDA(cudaMemcpyAsync(static_cast<char*>(p->grads_alt) + p->offset[tensor] * es, host, p->numel[tensor] * es,
+                                 cudaMemcpyHostToDevice, p->upload_stream));
+        return OXZ_OK;
+    });
 }
 
 int32_t oxz_grads_swap(oxz_plan* p) {
-    if (!p) return fail(OXZ_ERR_INVALID, "oxz_grads_swap: null plan");
-    if (!p->grads_alt) return fail(OXZ_ERR_STATE, "oxz_grads_swap: call oxz_grads_double_buffer first");
-    if (p->inflight) return fail(OXZ_ERR_STATE, "oxz_grads_swap: a step is in flight. Call oxz_step_wait first");
-    if (p->early_groups) return fail(OXZ_ERR_STATE, "oxz_grads_swap: buckets of the current buffer were already handed in for this step");
-    OXZ_CUDA(cudaSetDevice(p->device));
-    OXZ_CUDA(cudaEventRecord(p->ev_uploaded, p->upload_stream));
-    std::swap(p->grads, p->grads_alt);
-    for (int r = 0; r < p->cw; r++) std::swap(p->peers.grads[r], p->peer_grads_alt[r]);
-    p->cur_grads ^= 1;
-    p->upload_pending = true;
-    return OXZ_OK;
+    return oxz::guarded("oxz_grads_swap", [&]() -> int32_t {
+        if (!p) return fail(OXZ_ERR_INVALID, "oxz_grads_swap: null plan");
+        if (!p->grads_alt) return fail(OXZ_ERR_STATE, "oxz_grads_swap: call oxz_grads_double_buffer first");
+        if (p->inflight) return fail(OXZ_ERR_STATE, "oxz_grads_swap: a step is in flight. Call oxz_step_wait first");
+        if (p->early_groups) return fail(OXZ_ERR_STATE, "oxz_grads_swap: buckets of the current buffer were already handed in for this step");
+        OXZ_CUDA(cudaSetDevice(p->device));
+        OXZ_CUDA(cudaEventRecord(p->ev_uploaded, p->upload_stream));
+        std::swap(p->grads, p->grads_alt);
+        for (int r = 0; r < p->cw; r++) std::swap(p->peers.grads[r], p->peer_grads_alt[r]);
+        p->cur_grads ^= 1;
+        p->upload_pending = true;
+        return OXZ_OK;
+    });
 }
 
 namespace {
@@ -536,388 +562,404 @@ static int32_t check_hyper(const oxz_hyper* h) {
 
 int32_t oxz_step_async(oxz_plan* p, oxz_comm* comm, const oxz_hyper* h, const uint8_t* present, double* extras,
                        uint32_t n_extras) {
-    if (!p || !h) return fail(OXZ_ERR_INVALID, "oxz_step_async: null argument");
-    if (!p->allocated) return fail(OXZ_ERR_STATE, "oxz_step_async: the plan has no device state. Call oxz_state_alloc first");
-    if (p->inflight) return fail(OXZ_ERR_STATE, "oxz_step_async: the previous step is still in flight. Call oxz_step_wait first");
-    if (n_extras > MAX_EXTRAS || (n_extras && !extras)) return fail(OXZ_ERR_INVALID, "oxz_step_async: at most %u extras", MAX_EXTRAS);
-    OXZ_TRY(check_hyper(h));
-    if (p->cw > 1) {
-        OXZ_TRY(comm_check(comm, "oxz_step_async"));
-        if (comm != p->comm) return fail(OXZ_ERR_INVALID, "oxz_step_async: this is not the communicator the state was allocated with");
-    }
-    OXZ_CUDA(cudaSetDevice(p->device));
-    cudaStream_t s = p->stream;
-    const bool nccl_mode = p->mode == OXZ_SYNC_NCCL;
-    if (nccl_mode && comm->kind != 0)
-        return fail(OXZ_ERR_UNSUPPORTED, "OXZ_SYNC_NCCL needs an NCCL communicator; a local group serves OXZ_SYNC_P2P");
-    const NcclApi* api = nccl_mode ? nccl_api() : nullptr;
-    ncclComm_t nc = nccl_mode ? (ncclComm_t)comm->nccl : nullptr;
-
-    // which tensors have a gradient this step
-    bool some_absent = false;
-    if (p->early_groups == 0) {
-        OXZ_TRY(update_present(p, present, s, &some_absent));
-    } else {
-        for (uint64_t i = 0; i < p->T; i++) {
-            const uint8_t v = present ? (present[i] ? 1 : 0) : 1;
-            if (p->h_present[i] != v) return fail(OXZ_ERR_INVALID, "oxz_step_async: `present` differs from the one oxz_grads_ready_async was given for this step");
-            some_absent |= v == 0;
+    return oxz::guarded("oxz_step_async", [&]() -> int32_t {
+        if (!p || !h) return fail(OXZ_ERR_INVALID, "oxz_step_async: null argument");
+        if (!p->allocated) return fail(OXZ_ERR_STATE, "oxz_step_async: the plan has no device state. Call oxz_state_alloc first");
+        if (p->inflight) return fail(OXZ_ERR_STATE, "oxz_step_async: the previous step is still in flight. Call oxz_step_wait first");
+        if (n_extras > MAX_EXTRAS || (n_extras && !extras)) return fail(OXZ_ERR_INVALID, "oxz_step_async: at most %u extras", MAX_EXTRAS);
+        OXZ_TRY(check_hyper(h));
+        if (p->cw > 1) {
+            OXZ_TRY(comm_check(comm, "oxz_step_async"));
+            if (comm != p->comm) return fail(OXZ_ERR_INVALID, "oxz_step_async: this is not the communicator the state was allocated with");
         }
-        if (!same_or_both_nan(h->loss_scale, p->early_scale) || !same_or_both_nan(h->max_grad_value, p->early_clamp))
-            return fail(OXZ_ERR_INVALID, "oxz_step_async: loss_scale or max_grad_value differs from the one oxz_grads_ready_async was given for this step");
-    }
+        OXZ_CUDA(cudaSetDevice(p->device));
+        cudaStream_t s = p->stream;
+        const bool nccl_mode = p->mode == OXZ_SYNC_NCCL;
+        if (nccl_mode && comm->kind != 0)
+            return fail(OXZ_ERR_UNSUPPORTED, "OXZ_SYNC_NCCL needs an NCCL communicator; a local group serves OXZ_SYNC_P2P");
+        const NcclApi* api = nccl_mode ? nccl_api() : nullptr;
+        ncclComm_t nc = nccl_mode ? (ncclComm_t)comm->nccl : nullptr;
 
-    // per-step scalars, f64 on the host, rounded to f32 once
-    const uint64_t t = p->timestep + 1;
-    const bool scaled = !std::isnan(h->loss_scale) && h->loss_scale != 0.0;
-    AdamParams ap{};
-    const double bc1 = 1.0 - std::pow(h->beta1, (double)t), bc2 = 1.0 - std::pow(h->beta2, (double)t);
-    ap.beta1 = (float)h->beta1;
-    ap.one_minus_beta1 = (float)(1.0 - h->beta1);
-    ap.beta2 = (float)h->beta2;
-    ap.one_minus_beta2 = (float)(1.0 - h->beta2);
-    ap.eps = (float)h->eps;
-    ap.bias2_sqrt = (float)std::sqrt(bc2);
-    ap.inv_scale = scaled ? (float)(1.0 / h->loss_scale) : 1.0f;
-    ap.clamp_on = std::isnan(h->max_grad_value) ? 0 : 1;
-    ap.clamp_hi = ap.clamp_on ? (float)h->max_grad_value : 0.f;
-    ap.decay_after = h->decay_after ? 1 : 0;
-    ap.eps_mode = h->eps_mode ? 1 : 0;
-    for (size_t g = 0; g < p->group_lr_scale.size(); g++) {
-        const double lr_t = h->lr * (double)p->group_lr_scale[g];
-        const double wd = p->group_no_decay[g] ? 0.0 : h->weight_decay;
-        ap.step_size[g] = ap.eps_mode == 0 ? (float)(lr_t / bc1) : (float)(lr_t * std::sqrt(bc2) / bc1);
-        ap.decay_mul[g] = (float)(1.0 - lr_t * wd);
-    }
-    FinalizeParams fp{};
-    fp.max_grad_norm = h->max_grad_norm;
-    fp.has_target = std::isnan(h->target_grad_norm) ? 0 : 1;
-    fp.target_grad_norm = fp.has_target ? h->target_grad_norm : 0.0;
-    fp.clip_eps = h->clip_eps;
-    fp.spike_skip = h->spike_skip ? 1 : 0;
-
-    const TileMap map = tile_map(p);
-    const bool replicated = p->mode == OXZ_SYNC_REPLICATED;
-    const bool pulls = p->mode == OXZ_SYNC_P2P || replicated;  // the gradient sum is the fused pull kernel
-    const bool peer_mode = pulls || p->mode == OXZ_SYNC_COPY;
-    uint32_t slots = peer_mode ? pull_partial_slots(p->geom, p->gdt) : norm_partial_slots(p->geom);
-    const void* gsrc = p->grads;
-    int32_t gsrc_dt = p->gdt;
-    int32_t* bar = p->cw > 1 ? reinterpret_cast<int32_t*>(static_cast<char*>(comm->d_small) + 384) : nullptr;
-
-    auto mark = [&](int i) -> cudaError_t { return p->profile ? cudaEventRecord(p->ev[i], s) : cudaSuccess; };
-    if (p->upload_pending) {
-        // gradients copied into this buffer while the step before was still running
-        OXZ_CUDA(cudaStreamWaitEvent(s, p->ev_uploaded, 0));
-        p->upload_pending = false;
-    }
-    OXZ_CUDA(mark(0));
-    if (p->mode == OXZ_SYNC_SINGLE || pulls) {
-        // buckets already reduced during backward are skipped; the rest goes now, one launch per run of buckets
-        uint32_t groups = p->early_groups;
-        if (groups) OXZ_CUDA(cudaStreamWaitEvent(s, p->ev_early, 0));
-        bool any_left = false;
-        for (uint64_t b = 0; b < p->n_buckets; b++) any_left |= !(groups && p->early_done[b]);
-        // every rank's remaining gradients must be complete before anyone pulls them
-        if (pulls && any_left) OXZ_TRY(comm_stream_barrier(comm, bar, s));
-        OXZ_CUDA(mark(1));
-        for (uint64_t b = 0; b < p->n_buckets;) {
-            if (groups && p->early_done[b]) { b++; continue; }
-            uint64_t e = b;
-            while (e < p->n_buckets && !(p->early_groups && p->early_done[e])) e++;
-            if (groups >= MAX_PIPE) return fail(OXZ_ERR_STATE, "oxz_step_async: the buckets left after oxz_grads_ready_async form too many separate runs");
-            OXZ_TRY(reduce_buckets(p, s, p->geom, b, e, groups, slots, some_absent, ap.inv_scale, ap.clamp_hi, ap.clamp_on));
-            groups++;
-            b = e;
+        // which tensors have a gradient this step
+        bool some_absent = false;
+        if (p->early_groups == 0) {
+            OXZ_TRY(update_present(p, present, s, &some_absent));
+        } else {
+            for (uint64_t i = 0; i < p->T; i++) {
+                const uint8_t v = present ? (present[i] ? 1 : 0) : 1;
+                if (p->h_present[i] != v) return fail(OXZ_ERR_INVALID, "oxz_step_async: `present` differs from the one oxz_grads_ready_async was given for this step");
+                some_absent |= v == 0;
+            }
+            if (!same_or_both_nan(h->loss_scale, p->early_scale) || !same_or_both_nan(h->max_grad_value, p->early_clamp))
+                return fail(OXZ_ERR_INVALID, "oxz_step_async: loss_scale or max_grad_value differs from the one oxz_grads_ready_async was given for this step");
         }
-        slots *= groups;
-        p->early_groups = 0;
-        if (pulls) {
+
+        // per-step scalars, f64 on the host, rounded to f32 once
+        const uint64_t t = p->timestep + 1;
+        const bool scaled = !std::isnan(h->loss_scale) && h->loss_scale != 0.0;
+        AdamParams ap{};
+        const double bc1 = 1.0 - std::pow(h->beta1, (double)t), bc2 = 1.0 - std::pow(h->beta2, (double)t);
+        ap.beta1 = (float)h->beta1;
+        ap.one_minus_beta1 = (float)(1.0 - h->beta1);
+        ap.beta2 = (float)h->beta2;
+        ap.one_minus_beta2 = (float)(1.0 - h->beta2);
+        ap.eps = (float)h->eps;
+        ap.bias2_sqrt = (float)std::sqrt(bc2);
+        ap.inv_scale = scaled ? (float)(1.0 / h->loss_scale) : 1.0f;
+        ap.clamp_on = std::isnan(h->max_grad_value) ? 0 : 1;
+        ap.clamp_hi = ap.clamp_on ? (float)h->max_grad_value : 0.f;
+        ap.decay_after = h->decay_after ? 1 : 0;
+        ap.eps_mode = h->eps_mode ? 1 : 0;
+        for (size_t g = 0; g < p->group_lr_scale.size(); g++) {
+            const double lr_t = h->lr * (double)p->group_lr_scale[g];
+            const double wd = p->group_no_decay[g] ? 0.0 : h->weight_decay;
+            ap.step_size[g] = ap.eps_mode == 0 ? (float)(lr_t / bc1) : (float)(lr_t * std::sqrt(bc2) / bc1);
+            ap.decay_mul[g] = (float)(1.0 - lr_t * wd);
+        }
+        FinalizeParams fp{};
+        fp.max_grad_norm = h->max_grad_norm;
+        fp.has_target = std::isnan(h->target_grad_norm) ? 0 : 1;
+        fp.target_grad_norm = fp.has_target ? h->target_grad_norm : 0.0;
+        fp.clip_eps = h->clip_eps;
+        fp.spike_skip = h->spike_skip ? 1 : 0;
+
+        const TileMap map = tile_map(p);
+        const bool replicated = p->mode == OXZ_SYNC_REPLICATED;
+        const bool pulls = p->mode == OXZ_SYNC_P2P || replicated;  // the gradient sum is the fused pull kernel
+        const bool peer_mode = pulls || p->mode == OXZ_SYNC_COPY;
+        uint32_t slots = peer_mode ? pull_partial_slots(p->geom, p->gdt) : norm_partial_slots(p->geom);
+        const void* gsrc = p->grads;
+        int32_t gsrc_dt = p->gdt;
+        int32_t* bar = p->cw > 1 ? reinterpret_cast<int32_t*>(static_cast<char*>(comm->d_small) + 384) : nullptr;
+
+        auto mark = [&](int i) -> cudaError_t { return p->profile ? cudaEventRecord(p->ev[i], s) : cudaSuccess; };
+        if (p->upload_pending) {
+            // gradients copied into this buffer while the step before was still running
+            OXZ_CUDA(cudaStreamWaitEvent(s, p->ev_uploaded, 0));
+            p->upload_pending = false;
+        }
+        OXZ_CUDA(mark(0));
+        if (p->mode == OXZ_SYNC_SINGLE || pulls) {
+            // buckets already reduced during backward are skipped; the rest goes now, one launch per run of buckets
+            uint32_t groups = p->early_groups;
+            if (groups) OXZ_CUDA(cudaStreamWaitEvent(s, p->ev_early, 0));
+            bool any_left = false;
+            for (uint64_t b = 0; b < p->n_buckets; b++) any_left |= !(groups && p->early_done[b]);
+            // every rank's remaining gradients must be complete before anyone pulls them
+            if (pulls && any_left) OXZ_TRY(comm_stream_barrier(comm, bar, s));
+            OXZ_CUDA(mark(1));
+            for (uint64_t b = 0; b < p->n_buckets;) {
+                if (groups && p->early_done[b]) { b++; continue; }
+                uint64_t e = b;
+                while (e < p->n_buckets && !(p->early_groups && p->early_done[e])) e++;
+                if (groups >= MAX_PIPE) return fail(OXZ_ERR_STATE, "oxz_step_async: the buckets left after oxz_grads_ready_async form too many separate runs");
+                OXZ_TRY(reduce_buckets(p, s, p->geom, b, e, groups, slots, some_absent, ap.inv_scale, ap.clamp_hi, ap.clamp_on));
+                groups++;
+                b = e;
+            }
+            slots *= groups;
+            p->early_groups = 0;
+            if (pulls) {
+                gsrc = p->reduced;
+                gsrc_dt = OXZ_F32;
+            }
+        } else if (p->mode == OXZ_SYNC_COPY) {
+            // every rank's gradients must be complete before anyone copies them
+            OXZ_TRY(comm_stream_barrier(comm, bar, s));
+            OXZ_CUDA(mark(1));
+            OXZ_CUDA(cudaEventRecord(p->ev_go, s));
+            const size_t gs = dtype_size(p->gdt);
+            const uint32_t G = p->pipe_groups;
+            for (int r = 0; r < p->world; r++)
+                if (r != p->rank) OXZ_CUDA(cudaStreamWaitEvent(p->copy_stream[r], p->ev_go, 0));
+            for (uint32_t g = 0; g < G; g++) {
+                uint64_t b0, b1;
+                group_buckets(p, g, &b0, &b1);
+                for (int r = 0; r < p->world; r++) {
+                    if (r == p->rank) continue;
+                    // the peer's slices of this rank's shard, buckets [b0, b1): a strided read, packed into the slot
+                    OXZ_TRY(copy_shard_rows(p, static_cast<char*>(const_cast<void*>(p->staged_src.grads[r])), true,
+                                            static_cast<const char*>(p->peers.grads[r]), false, gs, b0, b1, p->copy_stream[r]));
+                    OXZ_CUDA(cudaEventRecord(p->ev_copied[r][g], p->copy_stream[r]));
+                }
+                for (int r = 0; r < p->world; r++)
+                    if (r != p->rank) OXZ_CUDA(cudaStreamWaitEvent(s, p->ev_copied[r][g], 0));
+                TileMap gm = map;
+                group_tiles(p, b0, b1, &gm.first_tile, &gm.n_local_tiles);
+                OXZ_TRY(launch_pull_sumsq(s, p->geom, p->staged_src, p->world, 1, p->gdt, gm, p->d_tile_meta, p->d_present, some_absent,
+                                          ap.inv_scale, ap.clamp_hi, ap.clamp_on, static_cast<float*>(p->reduced),
+                                          p->d_partials + (size_t)g * slots * 3));
+            }
+            slots *= G;
             gsrc = p->reduced;
             gsrc_dt = OXZ_F32;
-        }
-    } else if (p->mode == OXZ_SYNC_COPY) {
-        // every rank's gradients must be complete before anyone copies them
-        OXZ_TRY(comm_stream_barrier(comm, bar, s));
-        OXZ_CUDA(mark(1));
-        OXZ_CUDA(cudaEventRecord(p->ev_go, s));
-        const size_t gs = dtype_size(p->gdt);
-        const uint32_t G = p->pipe_groups;
-        for (int r = 0; r < p->world; r++)
-            if (r != p->rank) OXZ_CUDA(cudaStreamWaitEvent(p->copy_stream[r], p->ev_go, 0));
-        for (uint32_t g = 0; g < G; g++) {
-            uint64_t b0, b1;
-            group_buckets(p, g, &b0, &b1);
-            for (int r = 0; r < p->world; r++) {
-                if (r == p->rank) continue;
-                // the peer's slices of this rank's shard, buckets [b0, b1): a strided read, packed into the slot
-                OXZ_TRY(copy_shard_rows(p, static_cast<char*>(const_cast<void*>(p->staged_src.grads[r])), true,
-                                        static_cast<const char*>(p->peers.grads[r]), false, gs, b0, b1, p->copy_stream[r]));
-                OXZ_CUDA(cudaEventRecord(p->ev_copied[r][g], p->copy_stream[r]));
+        } else {
+            const size_t gs = dtype_size(p->gdt);
+            ncclResult_t rc = api->GroupStart();
+            if (rc != ncclSuccess) return nccl_fail("ncclGroupStart", rc);
+            for (uint64_t b = 0; b < p->n_buckets; b++) {
+                uint64_t start, len, ss, sl;
+                oxz_plan_bucket(p, b, p->rank, &start, &len, &ss, &sl);
+                const uint64_t local = b * (p->bucket_tiles / (uint64_t)p->world) * TILE;
+                rc = api->ReduceScatter(static_cast<const char*>(p->grads) + start * gs, static_cast<char*>(p->reduced) + local * gs,
+                                        sl, nccl_dtype(p->gdt), ncclSum, nc, s);
+                if (rc != ncclSuccess) return nccl_fail("the gradient reduce-scatter", rc);
             }
-            for (int r = 0; r < p->world; r++)
-                if (r != p->rank) OXZ_CUDA(cudaStreamWaitEvent(s, p->ev_copied[r][g], 0));
-            TileMap gm = map;
-            group_tiles(p, b0, b1, &gm.first_tile, &gm.n_local_tiles);
-            OXZ_TRY(launch_pull_sumsq(s, p->geom, p->staged_src, p->world, 1, p->gdt, gm, p->d_tile_meta, p->d_present, some_absent,
-                                      ap.inv_scale, ap.clamp_hi, ap.clamp_on, static_cast<float*>(p->reduced),
-                                      p->d_partials + (size_t)g * slots * 3));
-        }
-        slots *= G;
-        gsrc = p->reduced;
-        gsrc_dt = OXZ_F32;
-    } else {
-        const size_t gs = dtype_size(p->gdt);
-        ncclResult_t rc = api->GroupStart();
-        if (rc != ncclSuccess) return nccl_fail("ncclGroupStart", rc);
-        for (uint64_t b = 0; b < p->n_buckets; b++) {
-            uint64_t start, len, ss, sl;
-            oxz_plan_bucket(p, b, p->rank, &start, &len, &ss, &sl);
-            const uint64_t local = b * (p->bucket_tiles / (uint64_t)p->world) * TILE;
-            rc = api->ReduceScatter(static_cast<const char*>(p->grads) + start * gs, static_cast<char*>(p->reduced) + local * gs,
-                                    sl, nccl_dtype(p->gdt), ncclSum, nc, s);
+            rc = api->GroupEnd();
             if (rc != ncclSuccess) return nccl_fail("the gradient reduce-scatter", rc);
+            OXZ_CUDA(mark(1));
+            OXZ_TRY(launch_sumsq(s, p->geom, p->reduced, p->gdt, map, p->d_tile_meta, p->d_present, some_absent, ap.inv_scale,
+                                 ap.clamp_hi, ap.clamp_on, p->d_partials));
+            gsrc = p->reduced;
         }
-        rc = api->GroupEnd();
-        if (rc != ncclSuccess) return nccl_fail("the gradient reduce-scatter", rc);
-        OXZ_CUDA(mark(1));
-        OXZ_TRY(launch_sumsq(s, p->geom, p->reduced, p->gdt, map, p->d_tile_meta, p->d_present, some_absent, ap.inv_scale,
-                             ap.clamp_hi, ap.clamp_on, p->d_partials));
-        gsrc = p->reduced;
-    }
-    OXZ_CUDA(mark(2));
-    OXZ_TRY(launch_reduce_partials(s, p->d_partials, slots, p->d_acc));
-    if (p->cw > 1) {
-        for (uint32_t i = 0; i < n_extras; i++) p->h_extras[i] = extras[i];
-        if (n_extras) OXZ_CUDA(cudaMemcpyAsync(p->d_acc + 3, p->h_extras, n_extras * 8, cudaMemcpyHostToDevice, s));
-        // The one all-reduce of the step: {sum of squares, inf count, NaN count, extras...}. In P2P mode its end
-        // also tells every rank that all peers have finished reading its gradient buffer. A full replica has
-        // measured every element itself: only the extras are summed, and a barrier stands in when there are none.
-        if (!replicated) OXZ_TRY(comm_stream_allreduce_f64(comm, p->d_acc, 3 + n_extras, p->h_acc, s));
-        else if (n_extras) OXZ_TRY(comm_stream_allreduce_f64(comm, p->d_acc + 3, n_extras, p->h_acc + 3, s));
-        else OXZ_TRY(comm_stream_barrier(comm, bar, s));
-    }
-    OXZ_TRY(launch_finalize(s, p->d_acc, fp, p->d_scalars));
-    OXZ_CUDA(cudaMemcpyAsync(p->h_scalars, p->d_scalars, sizeof(DevScalars), cudaMemcpyDeviceToHost, s));
-    // the pull kernels (also those of buckets reduced ahead of the next step) raise this flag; it was just copied out
-    // with the rest and starts the next step cleared
-    OXZ_CUDA(cudaMemsetAsync(&p->d_scalars->wait_expired, 0, sizeof(int32_t), s));
-    if (p->cw > 1 && n_extras)
-        OXZ_CUDA(cudaMemcpyAsync(p->h_acc, p->d_acc, (3 + n_extras) * 8, cudaMemcpyDeviceToHost, s));
+        OXZ_CUDA(mark(2));
+        OXZ_TRY(launch_reduce_partials(s, p->d_partials, slots, p->d_acc));
+        if (p->cw > 1) {
+            for (uint32_t i = 0; i < n_extras; i++) p->h_extras[i] = extras[i];
+            if (n_extras) OXZ_CUDA(cudaMemcpyAsync(p->d_acc + 3, p->h_extras, n_extras * 8, cudaMemcpyHostToDevice, s));
+            // The one all-reduce of the step: {sum of squares, inf count, NaN count, extras...}. In P2P mode its end
+            // also tells every rank that all peers have finished reading its gradient buffer. A full replica has
+            // measured every element itself: only the extras are summed, and a barrier stands in when there are none.
+            if (!replicated) OXZ_TRY(comm_stream_allreduce_f64(comm, p->d_acc, 3 + n_extras, p->h_acc, s));
+            else if (n_extras) OXZ_TRY(comm_stream_allreduce_f64(comm, p->d_acc + 3, n_extras, p->h_acc + 3, s));
+            else OXZ_TRY(comm_stream_barrier(comm, bar, s));
+        }
+        OXZ_TRY(launch_finalize(s, p->d_acc, fp, p->d_scalars));
+        OXZ_CUDA(cudaMemcpyAsync(p->h_scalars, p->d_scalars, sizeof(DevScalars), cudaMemcpyDeviceToHost, s));
+        // the pull kernels (also those of buckets reduced ahead of the next step) raise this flag; it was just copied out
+        // with the rest and starts the next step cleared
+        OXZ_CUDA(cudaMemsetAsync(&p->d_scalars->wait_expired, 0, sizeof(int32_t), s));
+        if (p->cw > 1 && n_extras)
+            OXZ_CUDA(cudaMemcpyAsync(p->h_acc, p->d_acc, (3 + n_extras) * 8, cudaMemcpyDeviceToHost, s));
 
-    OXZ_CUDA(mark(3));
-    const bool separate_work = p->work != (void*)p->master;
-    const int32_t n_work = !separate_work ? 0 : (p->mode == OXZ_SYNC_P2P ? p->world : 1);
-    if (p->mode == OXZ_SYNC_COPY) {
-        // the update runs group by group; as soon as a group's weights are written the copy engines push them to
-        // every peer while the next group updates
-        const size_t ps = dtype_size(p->pdt);
-        PeerTable own{};
-        own.work[0] = p->work;
-        for (uint32_t g = 0; g < p->pipe_groups; g++) {
-            uint64_t b0, b1;
-            group_buckets(p, g, &b0, &b1);
-            TileMap gm = map;
-            group_tiles(p, b0, b1, &gm.first_tile, &gm.n_local_tiles);
-            OXZ_TRY(launch_adamw(s, p->geom, gsrc, gsrc_dt, p->master, p->exp_avg, p->exp_avg_sq, own, 1, p->pdt, gm,
-                                 p->d_tile_meta, p->d_present, some_absent, p->d_scalars, ap));
-            OXZ_CUDA(cudaEventRecord(p->ev_updated[g], s));
+        OXZ_CUDA(mark(3));
+        const bool separate_work = p->work != (void*)p->master;
+        const int32_t n_work = !separate_work ? 0 : (p->mode == OXZ_SYNC_P2P ? p->world : 1);
+        if (p->mode == OXZ_SYNC_COPY) {
+            // the update runs group by group; as soon as a group's weights are written the copy engines push them to
+            // every peer while the next group updates
+            const size_t ps = dtype_size(p->pdt);
+            PeerTable own{};
+            own.work[0] = p->work;
+            for (uint32_t g = 0; g < p->pipe_groups; g++) {
+                uint64_t b0, b1;
+                group_buckets(p, g, &b0, &b1);
+                TileMap gm = map;
+                group_tiles(p, b0, b1, &gm.first_tile, &gm.n_local_tiles);
+                OXZ_TRY(launch_adamw(s, p->geom, gsrc, gsrc_dt, p->master, p->exp_avg, p->exp_avg_sq, own, 1, p->pdt, gm,
+                                     p->d_tile_meta, p->d_present, some_absent, p->d_scalars, ap));
+                OXZ_CUDA(cudaEventRecord(p->ev_updated[g], s));
+                for (int r = 0; r < p->world; r++) {
+                    if (r == p->rank) continue;
+                    OXZ_CUDA(cudaStreamWaitEvent(p->copy_stream[r], p->ev_updated[g], 0));
+                    OXZ_TRY(copy_shard_rows(p, static_cast<char*>(p->peers.work[r]), false, static_cast<const char*>(p->work), false,
+                                            ps, b0, b1, p->copy_stream[r]));
+                }
+            }
+            OXZ_CUDA(mark(4));
             for (int r = 0; r < p->world; r++) {
                 if (r == p->rank) continue;
-                OXZ_CUDA(cudaStreamWaitEvent(p->copy_stream[r], p->ev_updated[g], 0));
-                OXZ_TRY(copy_shard_rows(p, static_cast<char*>(p->peers.work[r]), false, static_cast<const char*>(p->work), false,
-                                        ps, b0, b1, p->copy_stream[r]));
+                OXZ_CUDA(cudaEventRecord(p->ev_pushed[r], p->copy_stream[r]));
+                OXZ_CUDA(cudaStreamWaitEvent(s, p->ev_pushed[r], 0));
             }
+            // every rank's copies into this rank's weight buffer must have landed before the step is reported done
+            OXZ_TRY(comm_stream_barrier(comm, bar, s));
+        } else {
+            // p->peers lists the communicator's ranks; a full replica writes only its own weights
+            OXZ_TRY(launch_adamw(s, p->geom, gsrc, gsrc_dt, p->master, p->exp_avg, p->exp_avg_sq, replicated ? p->own_work : p->peers,
+                                 n_work, p->pdt, map, p->d_tile_meta, p->d_present, some_absent, p->d_scalars, ap));
+            OXZ_CUDA(mark(4));
         }
-        OXZ_CUDA(mark(4));
-        for (int r = 0; r < p->world; r++) {
-            if (r == p->rank) continue;
-            OXZ_CUDA(cudaEventRecord(p->ev_pushed[r], p->copy_stream[r]));
-            OXZ_CUDA(cudaStreamWaitEvent(s, p->ev_pushed[r], 0));
-        }
-        // every rank's copies into this rank's weight buffer must have landed before the step is reported done
-        OXZ_TRY(comm_stream_barrier(comm, bar, s));
-    } else {
-        // p->peers lists the communicator's ranks; a full replica writes only its own weights
-        OXZ_TRY(launch_adamw(s, p->geom, gsrc, gsrc_dt, p->master, p->exp_avg, p->exp_avg_sq, replicated ? p->own_work : p->peers,
-                             n_work, p->pdt, map, p->d_tile_meta, p->d_present, some_absent, p->d_scalars, ap));
-        OXZ_CUDA(mark(4));
-    }
-    if (p->mode == OXZ_SYNC_NCCL) {
-        const size_t ps = dtype_size(p->pdt);
-        ncclResult_t rc = api->GroupStart();
-        if (rc != ncclSuccess) return nccl_fail("ncclGroupStart", rc);
-        for (uint64_t b = 0; b < p->n_buckets; b++) {
-            uint64_t start, len, ss, sl;
-            oxz_plan_bucket(p, b, p->rank, &start, &len, &ss, &sl);
-            rc = api->AllGather(static_cast<const char*>(p->work) + ss * ps, static_cast<char*>(p->work) + start * ps, sl * ps,
-                                ncclInt8, nc, s);
+        if (p->mode == OXZ_SYNC_NCCL) {
+            const size_t ps = dtype_size(p->pdt);
+            ncclResult_t rc = api->GroupStart();
+            if (rc != ncclSuccess) return nccl_fail("ncclGroupStart", rc);
+            for (uint64_t b = 0; b < p->n_buckets; b++) {
+                uint64_t start, len, ss, sl;
+                oxz_plan_bucket(p, b, p->rank, &start, &len, &ss, &sl);
+                rc = api->AllGather(static_cast<const char*>(p->work) + ss * ps, static_cast<char*>(p->work) + start * ps, sl * ps,
+                                    ncclInt8, nc, s);
+                if (rc != ncclSuccess) return nccl_fail("the weight all-gather", rc);
+            }
+            rc = api->GroupEnd();
             if (rc != ncclSuccess) return nccl_fail("the weight all-gather", rc);
+        } else if (p->mode == OXZ_SYNC_P2P) {
+            // every rank's stores into this rank's weight buffer must have landed before the step is reported done
+            OXZ_TRY(comm_stream_barrier(comm, bar, s));
         }
-        rc = api->GroupEnd();
-        if (rc != ncclSuccess) return nccl_fail("the weight all-gather", rc);
-    } else if (p->mode == OXZ_SYNC_P2P) {
-        // every rank's stores into this rank's weight buffer must have landed before the step is reported done
-        OXZ_TRY(comm_stream_barrier(comm, bar, s));
-    }
-    OXZ_CUDA(mark(5));
-    if (p->grads_alt) OXZ_CUDA(cudaEventRecord(p->ev_last_read[p->cur_grads], s));
-    OXZ_CUDA(cudaEventRecord(p->done, s));
-    p->inflight = true;
-    p->inflight_hyper = *h;
-    p->inflight_extras = extras;
-    p->inflight_n_extras = n_extras;
-    return OXZ_OK;
+        OXZ_CUDA(mark(5));
+        if (p->grads_alt) OXZ_CUDA(cudaEventRecord(p->ev_last_read[p->cur_grads], s));
+        OXZ_CUDA(cudaEventRecord(p->done, s));
+        p->inflight = true;
+        p->inflight_hyper = *h;
+        p->inflight_extras = extras;
+        p->inflight_n_extras = n_extras;
+        return OXZ_OK;
+    });
 }
 
 int32_t oxz_grads_ready_async(oxz_plan* p, oxz_comm* comm, const oxz_hyper* h, const uint8_t* present, uint64_t first_bucket,
                               uint64_t n_buckets, void* producer_stream) {
-    if (!p || !h) return fail(OXZ_ERR_INVALID, "oxz_grads_ready_async: null argument");
-    if (!p->allocated) return fail(OXZ_ERR_STATE, "oxz_grads_ready_async: the plan has no device state. Call oxz_state_alloc first");
-    if (p->inflight) return fail(OXZ_ERR_STATE, "oxz_grads_ready_async: the previous step is still in flight. Call oxz_step_wait first");
-    if (p->mode != OXZ_SYNC_SINGLE && p->mode != OXZ_SYNC_P2P)
-        return fail(OXZ_ERR_UNSUPPORTED, "oxz_grads_ready_async serves OXZ_SYNC_SINGLE and OXZ_SYNC_P2P plans");
-    OXZ_TRY(check_hyper(h));
-    if (n_buckets == 0 || first_bucket + n_buckets > p->n_buckets)
-        return fail(OXZ_ERR_INVALID, "oxz_grads_ready_async: buckets [%llu, %llu) of %llu", (unsigned long long)first_bucket,
-                    (unsigned long long)(first_bucket + n_buckets), (unsigned long long)p->n_buckets);
-    if (p->early_groups >= MAX_PIPE - 2) return fail(OXZ_ERR_STATE, "oxz_grads_ready_async: at most %u calls per step", MAX_PIPE - 2);
-    if (p->cw > 1) {
-        OXZ_TRY(comm_check(comm, "oxz_grads_ready_async"));
-        if (comm != p->comm) return fail(OXZ_ERR_INVALID, "oxz_grads_ready_async: this is not the communicator the state was allocated with");
-    }
-    OXZ_CUDA(cudaSetDevice(p->device));
-    if (!p->early_stream) {
-        OXZ_CUDA(cudaStreamCreateWithFlags(&p->early_stream, cudaStreamNonBlocking));
-        OXZ_CUDA(cudaEventCreateWithFlags(&p->ev_produced, cudaEventDisableTiming));
-        OXZ_CUDA(cudaEventCreateWithFlags(&p->ev_early, cudaEventDisableTiming));
-    }
-    cudaStream_t es = p->early_stream;
-    if (p->upload_pending) OXZ_CUDA(cudaStreamWaitEvent(es, p->ev_uploaded, 0));  // the buckets may have come from the host
-    bool some_absent = false;
-    if (p->early_groups == 0) {
-        p->early_done.assign(p->n_buckets, 0);
-        p->early_scale = h->loss_scale;
-        p->early_clamp = h->max_grad_value;
-        // the side stream must not run ahead of the previous step's update, which read the same buffers
-        OXZ_CUDA(cudaEventRecord(p->ev_early, p->stream));
-        OXZ_CUDA(cudaStreamWaitEvent(es, p->ev_early, 0));
-        OXZ_TRY(update_present(p, present, es, &some_absent));
-    } else {
-        if (!same_or_both_nan(h->loss_scale, p->early_scale) || !same_or_both_nan(h->max_grad_value, p->early_clamp))
-            return fail(OXZ_ERR_INVALID, "oxz_grads_ready_async: loss_scale or max_grad_value changed within one step");
-        for (uint64_t i = 0; i < p->T; i++) {
-            const uint8_t v = present ? (present[i] ? 1 : 0) : 1;
-            if (p->h_present[i] != v) return fail(OXZ_ERR_INVALID, "oxz_grads_ready_async: `present` changed within one step");
-            some_absent |= v == 0;
+    return oxz::guarded("oxz_grads_ready_async", [&]() -> int32_t {
+        if (!p || !h) return fail(OXZ_ERR_INVALID, "oxz_grads_ready_async: null argument");
+        if (!p->allocated) return fail(OXZ_ERR_STATE, "oxz_grads_ready_async: the plan has no device state. Call oxz_state_alloc first");
+        if (p->inflight) return fail(OXZ_ERR_STATE, "oxz_grads_ready_async: the previous step is still in flight. Call oxz_step_wait first");
+        if (p->mode != OXZ_SYNC_SINGLE && p->mode != OXZ_SYNC_P2P)
+            return fail(OXZ_ERR_UNSUPPORTED, "oxz_grads_ready_async serves OXZ_SYNC_SINGLE and OXZ_SYNC_P2P plans");
+        OXZ_TRY(check_hyper(h));
+        if (n_buckets == 0 || first_bucket + n_buckets > p->n_buckets)
+            return fail(OXZ_ERR_INVALID, "oxz_grads_ready_async: buckets [%llu, %llu) of %llu", (unsigned long long)first_bucket,
+                        (unsigned long long)(first_bucket + n_buckets), (unsigned long long)p->n_buckets);
+        if (p->early_groups >= MAX_PIPE - 2) return fail(OXZ_ERR_STATE, "oxz_grads_ready_async: at most %u calls per step", MAX_PIPE - 2);
+        if (p->cw > 1) {
+            OXZ_TRY(comm_check(comm, "oxz_grads_ready_async"));
+            if (comm != p->comm) return fail(OXZ_ERR_INVALID, "oxz_grads_ready_async: this is not the communicator the state was allocated with");
         }
-    }
-    for (uint64_t b = first_bucket; b < first_bucket + n_buckets; b++)
-        if (p->early_done[b]) return fail(OXZ_ERR_INVALID, "oxz_grads_ready_async: bucket %llu was already handed in this step", (unsigned long long)b);
-    // the producer's work so far must have finished before the buckets are read
-    OXZ_CUDA(cudaEventRecord(p->ev_produced, (cudaStream_t)producer_stream));
-    OXZ_CUDA(cudaStreamWaitEvent(es, p->ev_produced, 0));
-    if (p->mode == OXZ_SYNC_P2P) {
-        int32_t* bar = reinterpret_cast<int32_t*>(static_cast<char*>(comm->d_small) + 448);
-        OXZ_TRY(comm_stream_barrier(comm, bar, es));
-    }
-    const bool scaled = !std::isnan(h->loss_scale) && h->loss_scale != 0.0;
-    const int32_t clamp_on = std::isnan(h->max_grad_value) ? 0 : 1;
-    // a quarter of the usual grid: the pull is NVLink-bound and backward still needs the SMs
-    LaunchGeom geom = p->geom;
-    const int cap = (geom.sm_count / 4) * 4;
-    geom.norm_blocks = geom.norm_blocks < cap ? geom.norm_blocks : cap;
-    for (int& b : geom.pull_blocks) b = b < cap ? b : cap;
-    for (int& b : geom.bulk_blocks) b = b < cap ? b : cap;
-    const uint32_t slots = p->mode == OXZ_SYNC_P2P ? pull_partial_slots(p->geom, p->gdt) : norm_partial_slots(p->geom);
-    // the smaller grid fills only the first slots of its group; the rest must read as zero
-    OXZ_CUDA(cudaMemsetAsync(p->d_partials + (size_t)p->early_groups * slots * 3, 0, (size_t)slots * 3 * 8, es));
-    OXZ_TRY(reduce_buckets(p, es, geom, first_bucket, first_bucket + n_buckets, p->early_groups, slots, some_absent,
-                           scaled ? (float)(1.0 / h->loss_scale) : 1.0f, clamp_on ? (float)h->max_grad_value : 0.f, clamp_on));
-    OXZ_CUDA(cudaEventRecord(p->ev_early, es));
-    for (uint64_t b = first_bucket; b < first_bucket + n_buckets; b++) p->early_done[b] = 1;
-    p->early_groups++;
-    return OXZ_OK;
+        OXZ_CUDA(cudaSetDevice(p->device));
+        if (!p->early_stream) {
+            OXZ_CUDA(cudaStreamCreateWithFlags(&p->early_stream, cudaStreamNonBlocking));
+            OXZ_CUDA(cudaEventCreateWithFlags(&p->ev_produced, cudaEventDisableTiming));
+            OXZ_CUDA(cudaEventCreateWithFlags(&p->ev_early, cudaEventDisableTiming));
+        }
+        cudaStream_t es = p->early_stream;
+        if (p->upload_pending) OXZ_CUDA(cudaStreamWaitEvent(es, p->ev_uploaded, 0));  // the buckets may have come from the host
+        bool some_absent = false;
+        if (p->early_groups == 0) {
+            p->early_done.assign(p->n_buckets, 0);
+            p->early_scale = h->loss_scale;
+            p->early_clamp = h->max_grad_value;
+            // the side stream must not run ahead of the previous step's update, which read the same buffers
+            OXZ_CUDA(cudaEventRecord(p->ev_early, p->stream));
+            OXZ_CUDA(cudaStreamWaitEvent(es, p->ev_early, 0));
+            OXZ_TRY(update_present(p, present, es, &some_absent));
+        } else {
+            if (!same_or_both_nan(h->loss_scale, p->early_scale) || !same_or_both_nan(h->max_grad_value, p->early_clamp))
+                return fail(OXZ_ERR_INVALID, "oxz_grads_ready_async: loss_scale or max_grad_value changed within one step");
+            for (uint64_t i = 0; i < p->T; i++) {
+                const uint8_t v = present ? (present[i] ? 1 : 0) : 1;
+                if (p->h_present[i] != v) return fail(OXZ_ERR_INVALID, "oxz_grads_ready_async: `present` changed within one step");
+                some_absent |= v == 0;
+            }
+        }
+        for (uint64_t b = first_bucket; b < first_bucket + n_buckets; b++)
+            if (p->early_done[b]) return fail(OXZ_ERR_INVALID, "oxz_grads_ready_async: bucket %llu was already handed in this step", (unsigned long long)b);
+        // the producer's work so far must have finished before the buckets are read
+        OXZ_CUDA(cudaEventRecord(p->ev_produced, (cudaStream_t)producer_stream));
+        OXZ_CUDA(cudaStreamWaitEvent(es, p->ev_produced, 0));
+        if (p->mode == OXZ_SYNC_P2P) {
+            int32_t* bar = reinterpret_cast<int32_t*>(static_cast<char*>(comm->d_small) + 448);
+            OXZ_TRY(comm_stream_barrier(comm, bar, es));
+        }
+        const bool scaled = !std::isnan(h->loss_scale) && h->loss_scale != 0.0;
+        const int32_t clamp_on = std::isnan(h->max_grad_value) ? 0 : 1;
+        // a quarter of the usual grid: the pull is NVLink-bound and backward still needs the SMs
+        LaunchGeom geom = p->geom;
+        const int cap = (geom.sm_count / 4) * 4;
+        geom.norm_blocks = geom.norm_blocks < cap ? geom.norm_blocks : cap;
+        for (int& b : geom.pull_blocks) b = b < cap ? b : cap;
+        for (int& b : geom.bulk_blocks) b = b < cap ? b : cap;
+        const uint32_t slots = p->mode == OXZ_SYNC_P2P ? pull_partial_slots(p->geom, p->gdt) : norm_partial_slots(p->geom);
+        // the smaller grid fills only the first slots of its group; the rest must read as zero
+        OXZ_CUDA(cudaMemsetAsync(p->d_partials + (size_t)p->early_groups * slots * 3, 0, (size_t)slots * 3 * 8, es));
+        OXZ_TRY(reduce_buckets(p, es, geom, first_bucket, first_bucket + n_buckets, p->early_groups, slots, some_absent,
+                               scaled ? (float)(1.0 / h->loss_scale) : 1.0f, clamp_on ? (float)h->max_grad_value : 0.f, clamp_on));
+        OXZ_CUDA(cudaEventRecord(p->ev_early, es));
+        for (uint64_t b = first_bucket; b < first_bucket + n_buckets; b++) p->early_done[b] = 1;
+        p->early_groups++;
+        return OXZ_OK;
+    });
 }
 
 int32_t oxz_step_wait(oxz_plan* p, oxz_step_result* res) {
-    if (!p) return fail(OXZ_ERR_INVALID, "oxz_step_wait: null plan");
-    if (!p->inflight) return fail(OXZ_ERR_STATE, "oxz_step_wait: no step is in flight");
-    OXZ_CUDA(cudaSetDevice(p->device));
-    cudaError_t e = cudaEventSynchronize(p->done);
-    p->inflight = false;
-    if (p->comm && p->comm->aborted.load()) return fail(OXZ_ERR_ABORTED, "oxz_step_wait: the communicator was aborted during the step");
-    if (e != cudaSuccess) return fail(OXZ_ERR_CUDA, "oxz_step_wait: %s", cudaGetErrorString(e));
-    const DevScalars& d = *p->h_scalars;
-    if (d.wait_expired)
-        return fail(OXZ_ERR_TIMEOUT, "oxz_step_wait: a bounded wait inside the pull kernel ran out before a peer's data arrived; the step's result is not valid");
-    const oxz_hyper& h = p->inflight_hyper;
-    const bool applied = !d.skip;
-    if (applied) p->timestep += 1;
-    if (p->cw > 1)
-        for (uint32_t i = 0; i < p->inflight_n_extras; i++) p->inflight_extras[i] = p->h_acc[3 + i];
-    if (res) {
-        res->grad_norm = d.norm;
-        res->overflow = d.overflow;
-        res->applied = applied ? 1 : 0;
-        res->timestep = p->timestep;
-        res->clip_coef = (double)d.c1 * (double)d.c2;
-        double rep = d.norm;
-        if (applied) {
-            rep = d.norm < h.max_grad_norm ? d.norm : h.max_grad_norm;
-            if (!std::isnan(h.target_grad_norm) && h.target_grad_norm < rep) rep = h.target_grad_norm;
+    return oxz::guarded("oxz_step_wait", [&]() -> int32_t {
+        if (!p) return fail(OXZ_ERR_INVALID, "oxz_step_wait: null plan");
+        if (!p->inflight) return fail(OXZ_ERR_STATE, "oxz_step_wait: no step is in flight");
+        OXZ_CUDA(cudaSetDevice(p->device));
+        cudaError_t e = cudaEventSynchronize(p->done);
+        p->inflight = false;
+        if (p->comm && p->comm->aborted.load()) return fail(OXZ_ERR_ABORTED, "oxz_step_wait: the communicator was aborted during the step");
+        if (e != cudaSuccess) return fail(OXZ_ERR_CUDA, "oxz_step_wait: %s", cudaGetErrorString(e));
+        const DevScalars& d = *p->h_scalars;
+        if (d.wait_expired)
+            return fail(OXZ_ERR_TIMEOUT, "oxz_step_wait: a bounded wait inside the pull kernel ran out before a peer's data arrived; the step's result is not valid");
+        const oxz_hyper& h = p->inflight_hyper;
+        const bool applied = !d.skip;
+        if (applied) p->timestep += 1;
+        if (p->cw > 1)
+            for (uint32_t i = 0; i < p->inflight_n_extras; i++) p->inflight_extras[i] = p->h_acc[3 + i];
+        if (res) {
+            res->grad_norm = d.norm;
+            res->overflow = d.overflow;
+            res->applied = applied ? 1 : 0;
+            res->timestep = p->timestep;
+            res->clip_coef = (double)d.c1 * (double)d.c2;
+            double rep = d.norm;
+            if (applied) {
+                rep = d.norm < h.max_grad_norm ? d.norm : h.max_grad_norm;
+                if (!std::isnan(h.target_grad_norm) && h.target_grad_norm < rep) rep = h.target_grad_norm;
+            }
+            res->reported_norm = rep;
         }
-        res->reported_norm = rep;
-    }
-    return OXZ_OK;
+        return OXZ_OK;
+    });
 }
 
 int32_t oxz_plan_launch_geometry(const oxz_plan* p, int32_t* sm_count, int32_t* norm_blocks, int32_t* update_blocks) {
-    if (!p) return fail(OXZ_ERR_INVALID, "oxz_plan_launch_geometry: null plan");
-    if (!p->allocated) return fail(OXZ_ERR_STATE, "oxz_plan_launch_geometry: call oxz_state_alloc first");
-    if (sm_count) *sm_count = p->geom.sm_count;
-    if (norm_blocks) *norm_blocks = p->geom.norm_blocks;
-    if (update_blocks) *update_blocks = p->geom.adam_blocks;
-    return OXZ_OK;
+    return oxz::guarded("oxz_plan_launch_geometry", [&]() -> int32_t {
+        if (!p) return fail(OXZ_ERR_INVALID, "oxz_plan_launch_geometry: null plan");
+        if (!p->allocated) return fail(OXZ_ERR_STATE, "oxz_plan_launch_geometry: call oxz_state_alloc first");
+        if (sm_count) *sm_count = p->geom.sm_count;
+        if (norm_blocks) *norm_blocks = p->geom.norm_blocks;
+        if (update_blocks) *update_blocks = p->geom.adam_blocks;
+        return OXZ_OK;
+    });
 }
 
 int32_t oxz_plan_last_pull_kernel(const oxz_plan* p, int32_t* kind) {
-    if (!p || !kind) return fail(OXZ_ERR_INVALID, "oxz_plan_last_pull_kernel: null argument");
-    *kind = p->last_pull_kernel;
-    return OXZ_OK;
+    return oxz::guarded("oxz_plan_last_pull_kernel", [&]() -> int32_t {
+        if (!p || !kind) return fail(OXZ_ERR_INVALID, "oxz_plan_last_pull_kernel: null argument");
+        *kind = p->last_pull_kernel;
+        return OXZ_OK;
+    });
 }
 
 int32_t oxz_plan_set_profile(oxz_plan* p, int32_t on) {
-    if (!p) return fail(OXZ_ERR_INVALID, "oxz_plan_set_profile: null plan");
-    if (!p->allocated) return fail(OXZ_ERR_STATE, "oxz_plan_set_profile: call oxz_state_alloc first");
-    if (p->inflight) return fail(OXZ_ERR_STATE, "oxz_plan_set_profile: a step is in flight");
-    OXZ_CUDA(cudaSetDevice(p->device));
-    if (on && !p->ev[0])
-        for (auto& e : p->ev) OXZ_CUDA(cudaEventCreate(&e));
-    p->profile = on != 0;
-    return OXZ_OK;
+    return oxz::guarded("oxz_plan_set_profile", [&]() -> int32_t {
+        if (!p) return fail(OXZ_ERR_INVALID, "oxz_plan_set_profile: null plan");
+        if (!p->allocated) return fail(OXZ_ERR_STATE, "oxz_plan_set_profile: call oxz_state_alloc first");
+        if (p->inflight) return fail(OXZ_ERR_STATE, "oxz_plan_set_profile: a step is in flight");
+        OXZ_CUDA(cudaSetDevice(p->device));
+        if (on && !p->ev[0])
+            for (auto& e : p->ev) OXZ_CUDA(cudaEventCreate(&e));
+        p->profile = on != 0;
+        return OXZ_OK;
+    });
 }
 
 int32_t oxz_step_profile_read(oxz_plan* p, oxz_step_profile* out) {
-    if (!p || !out) return fail(OXZ_ERR_INVALID, "oxz_step_profile_read: null argument");
-    if (!p->profile) return fail(OXZ_ERR_STATE, "oxz_step_profile_read: profiling is off. Call oxz_plan_set_profile first");
-    if (p->inflight) return fail(OXZ_ERR_STATE, "oxz_step_profile_read: a step is in flight. Call oxz_step_wait first");
-    OXZ_CUDA(cudaSetDevice(p->device));
-    float d[5];
-    for (int i = 0; i < 5; i++) OXZ_CUDA(cudaEventElapsedTime(&d[i], p->ev[i], p->ev[i + 1]));
-    out->collect_ms = d[0];
-    out->norm_ms = d[1];
-    out->decide_ms = d[2];
-    out->update_ms = d[3];
-    out->publish_ms = d[4];
-    OXZ_CUDA(cudaEventElapsedTime(&out->total_ms, p->ev[0], p->ev[5]));
-    return OXZ_OK;
+    return oxz::guarded("oxz_step_profile_read", [&]() -> int32_t {
+        if (!p || !out) return fail(OXZ_ERR_INVALID, "oxz_step_profile_read: null argument");
+        if (!p->profile) return fail(OXZ_ERR_STATE, "oxz_step_profile_read: profiling is off. Call oxz_plan_set_profile first");
+        if (p->inflight) return fail(OXZ_ERR_STATE, "oxz_step_profile_read: a step is in flight. Call oxz_step_wait first");
+        OXZ_CUDA(cudaSetDevice(p->device));
+        float d[5];
+        for (int i = 0; i < 5; i++) OXZ_CUDA(cudaEventElapsedTime(&d[i], p->ev[i], p->ev[i + 1]));
+        out->collect_ms = d[0];
+        out->norm_ms = d[1];
+        out->decide_ms = d[2];
+        out->update_ms = d[3];
+        out->publish_ms = d[4];
+        OXZ_CUDA(cudaEventElapsedTime(&out->total_ms, p->ev[0], p->ev[5]));
+        return OXZ_OK;
+    });
 }
 
 int32_t oxz_step(oxz_plan* p, oxz_comm* comm, const oxz_hyper* h, const uint8_t* present, double* extras,
                  uint32_t n_extras, oxz_step_result* res) {
-    OXZ_TRY(oxz_step_async(p, comm, h, present, extras, n_extras));
-    return oxz_step_wait(p, res);
+    return oxz::guarded("oxz_step", [&]() -> int32_t {
+        OXZ_TRY(oxz_step_async(p, comm, h, present, extras, n_extras));
+        return oxz_step_wait(p, res);
+    });
 }
 
 // ---- standalone norm ----
@@ -936,38 +978,40 @@ std::map<int, NormScratch> g_norm_scratch;
 
 int32_t oxz_grad_norm(const void* device_grads, int32_t dtype, uint64_t n, double loss_scale, double max_grad_value,
                       void* stream, double* norm) {
-    if (!norm || (!device_grads && n)) return fail(OXZ_ERR_INVALID, "oxz_grad_norm: null argument");
-    if (dtype != OXZ_F32 && dtype != OXZ_BF16 && dtype != OXZ_F16) return fail(OXZ_ERR_INVALID, "oxz_grad_norm: dtype %d is none of f32, bf16, f16", dtype);
-    if ((uintptr_t)device_grads & 15) return fail(OXZ_ERR_INVALID, "oxz_grad_norm: the gradients are not 16-byte aligned");
-    if (!std::isnan(max_grad_value) && !(std::isfinite(max_grad_value) && max_grad_value > 0.0))
-        return fail(OXZ_ERR_INVALID, "trainer.max_grad_value is %g: it must be a finite positive number. Set a positive value, or remove the key to disable per-element clipping.", max_grad_value);
-    int dev = 0;
-    OXZ_CUDA(cudaGetDevice(&dev));
-    std::lock_guard<std::mutex> lock(g_norm_mu);
-    NormScratch& sc = g_norm_scratch[dev];
-    if (!sc.d_partials) {
-        LaunchGeom g;
-        OXZ_TRY(query_geom(dev, &g));
-        sc.blocks = g.norm_blocks;
-        sc.slots = norm_partial_slots(g);
-        OXZ_CUDA(cudaMalloc((void**)&sc.d_partials, (size_t)norm_partial_slots(g) * 3 * 8));
-        OXZ_CUDA(cudaMalloc((void**)&sc.d_acc, 3 * 8));
-        OXZ_CUDA(cudaMalloc((void**)&sc.d_scalars, sizeof(DevScalars)));
-        OXZ_CUDA(cudaMallocHost((void**)&sc.h_scalars, sizeof(DevScalars)));
-    }
-    cudaStream_t s = (cudaStream_t)stream;
-    const bool scaled = !std::isnan(loss_scale) && loss_scale != 0.0;
-    const int clamp_on = std::isnan(max_grad_value) ? 0 : 1;
-    OXZ_TRY(launch_sumsq_plain(s, sc.blocks, device_grads, dtype, n, scaled ? (float)(1.0 / loss_scale) : 1.0f,
-                               clamp_on ? (float)max_grad_value : 0.f, clamp_on, sc.d_partials));
-    OXZ_TRY(launch_reduce_partials(s, sc.d_partials, sc.slots, sc.d_acc));
-    FinalizeParams fp{};
-    fp.max_grad_norm = 1.7976931348623157e308;  // a pure measurement: nothing is rescaled
-    OXZ_TRY(launch_finalize(s, sc.d_acc, fp, sc.d_scalars));
-    OXZ_CUDA(cudaMemcpyAsync(sc.h_scalars, sc.d_scalars, sizeof(DevScalars), cudaMemcpyDeviceToHost, s));
-    OXZ_CUDA(cudaStreamSynchronize(s));
-    *norm = sc.h_scalars->norm;
-    return OXZ_OK;
+    return oxz::guarded("oxz_grad_norm", [&]() -> int32_t {
+        if (!norm || (!device_grads && n)) return fail(OXZ_ERR_INVALID, "oxz_grad_norm: null argument");
+        if (dtype != OXZ_F32 && dtype != OXZ_BF16 && dtype != OXZ_F16) return fail(OXZ_ERR_INVALID, "oxz_grad_norm: dtype %d is none of f32, bf16, f16", dtype);
+        if ((uintptr_t)device_grads & 15) return fail(OXZ_ERR_INVALID, "oxz_grad_norm: the gradients are not 16-byte aligned");
+        if (!std::isnan(max_grad_value) && !(std::isfinite(max_grad_value) && max_grad_value > 0.0))
+            return fail(OXZ_ERR_INVALID, "trainer.max_grad_value is %g: it must be a finite positive number. Set a positive value, or remove the key to disable per-element clipping.", max_grad_value);
+        int dev = 0;
+        OXZ_CUDA(cudaGetDevice(&dev));
+        std::lock_guard<std::mutex> lock(g_norm_mu);
+        NormScratch& sc = g_norm_scratch[dev];
+        if (!sc.d_partials) {
+            LaunchGeom g;
+            OXZ_TRY(query_geom(dev, &g));
+            sc.blocks = g.norm_blocks;
+            sc.slots = norm_partial_slots(g);
+            OXZ_CUDA(cudaMalloc((void**)&sc.d_partials, (size_t)norm_partial_slots(g) * 3 * 8));
+            OXZ_CUDA(cudaMalloc((void**)&sc.d_acc, 3 * 8));
+            OXZ_CUDA(cudaMalloc((void**)&sc.d_scalars, sizeof(DevScalars)));
+            OXZ_CUDA(cudaMallocHost((void**)&sc.h_scalars, sizeof(DevScalars)));
+        }
+        cudaStream_t s = (cudaStream_t)stream;
+        const bool scaled = !std::isnan(loss_scale) && loss_scale != 0.0;
+        const int clamp_on = std::isnan(max_grad_value) ? 0 : 1;
+        OXZ_TRY(launch_sumsq_plain(s, sc.blocks, device_grads, dtype, n, scaled ? (float)(1.0 / loss_scale) : 1.0f,
+                                   clamp_on ? (float)max_grad_value : 0.f, clamp_on, sc.d_partials));
+        OXZ_TRY(launch_reduce_partials(s, sc.d_partials, sc.slots, sc.d_acc));
+        FinalizeParams fp{};
+        fp.max_grad_norm = 1.7976931348623157e308;  // a pure measurement: nothing is rescaled
+        OXZ_TRY(launch_finalize(s, sc.d_acc, fp, sc.d_scalars));
+        OXZ_CUDA(cudaMemcpyAsync(sc.h_scalars, sc.d_scalars, sizeof(DevScalars), cudaMemcpyDeviceToHost, s));
+        OXZ_CUDA(cudaStreamSynchronize(s));
+        *norm = sc.h_scalars->norm;
+        return OXZ_OK;
+    });
 }
 
 }  // extern "C"
