@@ -209,6 +209,7 @@ struct oxz_plan {
     // a second gradient buffer (oxz_grads_double_buffer): `grads` is the one the next step reads, `grads_alt` the one
     // the host may fill meanwhile; oxz_grads_swap exchanges them (and the peers' addresses of them)
     void* grads_alt = nullptr;
+    bool double_buffered = false;  // the second buffer is complete: allocated, events made, mapped by the peers
     const void* peer_grads_alt[oxz::MAX_PEERS] = {};
     cudaStream_t upload_stream = nullptr;
     cudaEvent_t ev_uploaded = nullptr, ev_last_read[2] = {nullptr, nullptr};

@@ -443,7 +443,8 @@ int32_t oxz_grads_double_buffer(oxz_plan* p, oxz_comm* comm) {
         if (!p) return fail(OXZ_ERR_INVALID, "oxz_grads_double_buffer: null plan");
         if (!p->allocated) return fail(OXZ_ERR_STATE, "oxz_grads_double_buffer: call oxz_state_alloc first");
         if (p->inflight) return fail(OXZ_ERR_STATE, "oxz_grads_double_buffer: a step is in flight. Call oxz_step_wait first");
-        if (p->grads_alt) return OXZ_OK;
+        if (p->double_buffered) return OXZ_OK;
+        if (p->grads_alt) return fail(OXZ_ERR_STATE, "oxz_grads_double_buffer: an earlier call failed midway. Destroy the plan and create it again");
         if (p->mode == OXZ_SYNC_COPY) return fail(OXZ_ERR_UNSUPPORTED, "oxz_grads_double_buffer does not serve OXZ_SYNC_COPY plans");
         const bool peer_mode = p->mode == OXZ_SYNC_P2P || p->mode == OXZ_SYNC_REPLICATED;
         if (peer_mode) {
@@ -459,6 +460,7 @@ int32_t oxz_grads_double_buffer(oxz_plan* p, oxz_comm* comm) {
         for (auto& e : p->ev_last_read) OXZ_CUDA(cudaEventCreateWithFlags(&e, cudaEventDisableTiming));
         OXZ_CUDA(cudaDeviceSynchronize());
         if (peer_mode) OXZ_TRY(exchange_alt_grads(p, comm));
+        p->double_buffered = true;
         return OXZ_OK;
     });
 }
@@ -466,7 +468,7 @@ int32_t oxz_grads_double_buffer(oxz_plan* p, oxz_comm* comm) {
 int32_t oxz_grads_upload_next_async(oxz_plan* p, uint64_t tensor, const void* host) {
     return oxz::guarded("oxz_grads_upload_next_async", [&]() -> int32_t {
         if (!p || !host) return fail(OXZ_ERR_INVALID, "oxz_grads_upload_next_async: null argument");
-        if (!p->grads_alt) return fail(OXZ_ERR_STATE, "oxz_grads_upload_next_async: call oxz_grads_double_buffer first");
+        if (!p->double_buffered) return fail(OXZ_ERR_STATE, "oxz_grads_upload_next_async: call oxz_grads_double_buffer first");
         if (tensor >= p->T) return fail(OXZ_ERR_INVALID, "oxz_grads_upload_next_async: tensor %llu of %llu", (unsigned long long)tensor, (unsigned long long)p->T);
         OXZ_CUDA(cudaSetDevice(p->device));
         // the step that last read the other buffer (and, with peers, whose end says that every rank has read it) must be over
@@ -481,7 +483,7 @@ int32_t oxz_grads_upload_next_async(oxz_plan* p, uint64_t tensor, const void* ho
 int32_t oxz_grads_swap(oxz_plan* p) {
     return oxz::guarded("oxz_grads_swap", [&]() -> int32_t {
         if (!p) return fail(OXZ_ERR_INVALID, "oxz_grads_swap: null plan");
-        if (!p->grads_alt) return fail(OXZ_ERR_STATE, "oxz_grads_swap: call oxz_grads_double_buffer first");
+        if (!p->double_buffered) return fail(OXZ_ERR_STATE, "oxz_grads_swap: call oxz_grads_double_buffer first");
         if (p->inflight) return fail(OXZ_ERR_STATE, "oxz_grads_swap: a step is in flight. Call oxz_step_wait first");
         if (p->early_groups) return fail(OXZ_ERR_STATE, "oxz_grads_swap: buckets of the current buffer were already handed in for this step");
         OXZ_CUDA(cudaSetDevice(p->device));
@@ -788,7 +790,7 @@ int32_t oxz_step_async(oxz_plan* p, oxz_comm* comm, const oxz_hyper* h, const ui
             OXZ_TRY(comm_stream_barrier(comm, bar, s));
         }
         OXZ_CUDA(mark(5));
-        if (p->grads_alt) OXZ_CUDA(cudaEventRecord(p->ev_last_read[p->cur_grads], s));
+        if (p->double_buffered) OXZ_CUDA(cudaEventRecord(p->ev_last_read[p->cur_grads], s));
         OXZ_CUDA(cudaEventRecord(p->done, s));
         p->inflight = true;
         p->inflight_hyper = *h;
