@@ -301,10 +301,22 @@ def run_gpu(args):
 
     e2e_steps = max(2, min(args.steps, 5))
     pipelined = mode in (ox.SYNC_SINGLE, ox.SYNC_P2P, ox.SYNC_REPLICATED, ox.SYNC_NCCL)
+    if pipelined and not args.skip_e2e:
+        # every rank must take the same leg: if the second buffer cannot be set up on some rank, all fall back
+        ok = 1
+        try:
+            opt.double_buffer_grads()
+        except ox.OxzError as e:
+            print(f"rank {rank}: no second gradient buffer ({e}); the host-fed leg copies, then steps", file=sys.stderr)
+            ok = 0
+        if dist is not None:
+            t = torch.tensor([ok], device="cuda", dtype=torch.int32)
+            dist.all_reduce(t, op=dist.ReduceOp.MIN)
+            ok = int(t.item())
+        pipelined = bool(ok)
     if args.skip_e2e:
         e2e_sec, e2e_value = float("nan"), None
     elif pipelined:
-        opt.double_buffer_grads()
         timed_host_fed(2)
         e2e_sec = timed_host_fed(e2e_steps)
         e2e_value = P * e2e_steps / e2e_sec
