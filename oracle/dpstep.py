@@ -78,6 +78,9 @@ def lib() -> C.CDLL:
         L.orc_sumsq.restype = C.c_double
         L.orc_clamp.argtypes = [vp, sz, C.c_double]
         L.orc_scale.argtypes = [vp, sz, C.c_float]
+        L.orc_clip_gradients.argtypes = [sz, C.POINTER(sz), C.POINTER(vp), vp, C.c_double, C.c_double, C.c_double,
+                                         C.POINTER(C.c_double)]
+        L.orc_clip_gradients.restype = C.c_double
         L.orc_adam_prepare.argtypes = [C.c_double] * 6 + [C.c_uint64, C.c_int32, C.c_int32, C.POINTER(AdamScalars)]
         L.orc_adamw.argtypes = [vp, vp, vp, vp, sz, C.POINTER(AdamScalars), vp, C.c_int]
         L.orc_step.argtypes = [sz, C.POINTER(sz), C.POINTER(vp), C.c_int, C.c_int, C.POINTER(vp), C.POINTER(vp),
@@ -142,6 +145,21 @@ def unscale(g: np.ndarray, code: int, scale: float) -> np.ndarray:
 def sumsq(g: np.ndarray) -> float:
     g = np.ascontiguousarray(g, dtype=np.float32)
     return float(lib().orc_sumsq(_ptr(g), g.size))
+
+
+def clip_gradients(grads: list[np.ndarray], max_grad_value: float, max_grad_norm: float, clip_eps: float = 1e-6,
+                   present: list[bool] | None = None) -> tuple[float, float]:
+    """clip_gradients (src/grad_clip.rs:36-56) in place on f32 arrays, through the function the checker's step calls.
+    Returns (the norm the norm clip measured, the coefficient applied)."""
+    T = len(grads)
+    for g in grads:
+        assert g.dtype == np.float32 and g.flags["C_CONTIGUOUS"]
+    numel = (C.c_size_t * T)(*[g.size for g in grads])
+    ptrs = (C.c_void_p * T)(*[_ptr(g) for g in grads])
+    pres = np.array([1 if (present is None or present[i]) else 0 for i in range(T)], dtype=np.uint8)
+    coef = C.c_double(1.0)
+    norm = lib().orc_clip_gradients(T, numel, ptrs, _ptr(pres), max_grad_value, max_grad_norm, clip_eps, C.byref(coef))
+    return float(norm), float(coef.value)
 
 
 def adam_prepare(lr, lr_scale, beta1, beta2, eps, weight_decay, t, decay_after=0, eps_mode=0) -> AdamScalars:

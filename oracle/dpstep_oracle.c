@@ -296,6 +296,49 @@ void orc_adamw(float* p, float* m, float* v, const float* g, size_t n, const orc
     }
 }
 
+/*
+ * One call of boostr clip_grad_norm as oxidizr uses it (compute_grad_norm, src/prelude.rs:13): measure the global
+ * L2 norm of the gradients as they are now, and when it is finite and above `max_norm` scale every gradient in place
+ * by the f32 coefficient max_norm / (norm + eps). Returns the measured norm. Called for the max-norm clip
+ * (src/grad_clip.rs:55) and, with the target as the limit, for the optional second clip (src/trainer.rs:635-645).
+ * SWITCH (parity unpinned): eps, 1e-6 by default.
+ */
+static double clip_norm_pass(size_t T, const size_t* numel, float* const* g, const uint8_t* present, double max_norm,
+                             double eps, double* coef) {
+    double ss = 0.0;
+    for (size_t i = 0; i < T; i++)
+        if (present[i]) ss += orc_sumsq(g[i], numel[i]);
+    double norm = sqrt(ss);
+    if (isfinite(norm) && norm > max_norm) {
+        float c = (float)(max_norm / (norm + eps));
+        for (size_t i = 0; i < T; i++)
+            if (present[i]) orc_scale(g[i], numel[i], c);
+        *coef *= (double)c;
+    }
+    return norm;
+}
+
+/*
+ * clip_gradients (src/grad_clip.rs:36-56) over T f32 gradients in place (present[i] == 0: tensor i has none):
+ * with a value clip, the raw norm first; a non-finite raw norm returns as is, before any clamp; else clamp every
+ * element, then the norm clip. Returns the norm the norm clip measured; *coef is multiplied by the coefficient applied.
+ * orc_step calls this function, and the reference's known answers (src/grad_clip.rs:82-143) are checked on it.
+ */
+double orc_clip_gradients(size_t T, const size_t* numel, float* const* g, const uint8_t* present, double max_grad_value,
+                          double max_grad_norm, double clip_eps, double* coef) {
+    int value_clip = max_grad_value == max_grad_value;
+    if (value_clip) {
+        double raw = 0.0;
+        for (size_t i = 0; i < T; i++)
+            if (present[i]) raw += orc_sumsq(g[i], numel[i]);
+        raw = sqrt(raw);
+        if (!isfinite(raw)) return raw;
+        for (size_t i = 0; i < T; i++)
+            if (present[i]) orc_clamp(g[i], numel[i], max_grad_value);
+    }
+    return clip_norm_pass(T, numel, g, present, max_grad_norm, clip_eps, coef);
+}
+
 /* ---- the whole post-accumulation step, src/trainer.rs:515-695 ------------ */
 
 typedef struct {
@@ -363,35 +406,8 @@ void orc_step(size_t T, const size_t* numel, const void* const* rank_grads, int 
     }
 
     /* A4: clip_gradients (src/grad_clip.rs:36-56). */
-    double norm;
     double coef = 1.0;
-    int value_clip = h->max_grad_value == h->max_grad_value;
-    int bailed = 0;
-    if (value_clip) {
-        double raw = 0.0;
-        for (size_t i = 0; i < T; i++)
-            if (present[i]) raw += orc_sumsq(g[i], numel[i]);
-        raw = sqrt(raw);
-        if (!isfinite(raw)) {
-            norm = raw;
-            bailed = 1;
-        } else {
-            for (size_t i = 0; i < T; i++)
-                if (present[i]) orc_clamp(g[i], numel[i], h->max_grad_value);
-        }
-    }
-    if (!bailed) {
-        double ss = 0.0;
-        for (size_t i = 0; i < T; i++)
-            if (present[i]) ss += orc_sumsq(g[i], numel[i]);
-        norm = sqrt(ss);
-        if (isfinite(norm) && norm > h->max_grad_norm) {
-            float c = (float)(h->max_grad_norm / (norm + h->clip_eps));
-            for (size_t i = 0; i < T; i++)
-                if (present[i]) orc_scale(g[i], numel[i], c);
-            coef *= (double)c;
-        }
-    }
+    double norm = orc_clip_gradients(T, numel, g, present, h->max_grad_value, h->max_grad_norm, h->clip_eps, &coef);
 
     /* A5: the skip decision (src/trainer.rs:611-633). */
     int overflow = !isfinite(norm);
@@ -405,10 +421,10 @@ void orc_step(size_t T, const size_t* numel, const void* const* rank_grads, int 
         double eff = norm < h->max_grad_norm ? norm : h->max_grad_norm;
         int has_target = h->target_grad_norm == h->target_grad_norm;
         if (has_target && eff > h->target_grad_norm && eff > 1e-8) {
-            float c = (float)(h->target_grad_norm / (eff + h->clip_eps));
-            for (size_t i = 0; i < T; i++)
-                if (present[i]) orc_scale(g[i], numel[i], c);
-            coef *= (double)c;
+            /* the same utility once more, on the gradients as the first clip left them: it measures them AGAIN
+               and rescales by target / (measured + eps). After a max-norm clip the measured norm is about
+               max * norm / (norm + eps), a little under max, so this is not target / (max + eps). */
+            (void)clip_norm_pass(T, numel, g, present, h->target_grad_norm, h->clip_eps, &coef);
         }
         /* A7: optimizer.step (src/trainer.rs:649). */
         uint64_t t = timestep + 1;

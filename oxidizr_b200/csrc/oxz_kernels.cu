@@ -629,7 +629,14 @@ __global__ void k_finalize(const double* __restrict__ acc, FinalizeParams fp, De
     if (!overflow && norm > fp.max_grad_norm) c1 = static_cast<float>(fp.max_grad_norm / (norm + fp.clip_eps));
     if (!overflow && !fp.spike_skip && fp.has_target) {
         const double eff = norm < fp.max_grad_norm ? norm : fp.max_grad_norm;
-        if (eff > fp.target_grad_norm && eff > 1e-8) c2 = static_cast<float>(fp.target_grad_norm / (eff + fp.clip_eps));
+        if (eff > fp.target_grad_norm && eff > 1e-8) {
+            // The reference calls the norm clip a second time with the target as its limit (src/trainer.rs:635-645):
+            // it measures the gradients again, as the first clip left them. Each of them is then fl(g * c1), so that
+            // second norm is c1 * norm within 2^-24 relative (exactly norm when the first clip did not fire), and no
+            // second pass over the gradients is needed. It is a little under max_grad_norm, not max_grad_norm itself.
+            const double again = static_cast<double>(c1) * norm;
+            if (again > fp.target_grad_norm) c2 = static_cast<float>(fp.target_grad_norm / (again + fp.clip_eps));
+        }
     }
     out->norm = norm;
     out->sumsq = sum;

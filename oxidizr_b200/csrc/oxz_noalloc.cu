@@ -40,6 +40,8 @@ DeviceSetup g_setup[MAX_DEVICES];
 extern "C" int32_t oxz_grad_norm_static(const void* device_grads, int32_t dtype, uint64_t n, double loss_scale,
                                         double max_grad_value, uint32_t clusters, void* stream, double* norm) {
     using namespace oxz;
+    // like every other entry point: whatever C++ throws inside (the mutex, the error text) becomes a status
+    return guarded("oxz_grad_norm_static", [&]() -> int32_t {
     if (!norm || (!device_grads && n)) return fail(OXZ_ERR_INVALID, "oxz_grad_norm_static: null argument");
     if (dtype != OXZ_F32 && dtype != OXZ_BF16 && dtype != OXZ_F16)
         return fail(OXZ_ERR_INVALID, "oxz_grad_norm_static: dtype %d is none of f32, bf16, f16", dtype);
@@ -98,4 +100,5 @@ extern "C" int32_t oxz_grad_norm_static(const void* device_grads, int32_t dtype,
     OXZ_CUDA(cudaMemcpyAsync(norm, &scalars->norm, sizeof(double), cudaMemcpyDeviceToHost, s));
     OXZ_CUDA(cudaStreamSynchronize(s));
     return OXZ_OK;
+    });
 }

@@ -106,6 +106,23 @@ def test_value_clamp_then_norm_clip_then_target():
     pair.close()
 
 
+def test_both_clips_fire_on_small_gradients_the_second_measures_again():
+    # src/trainer.rs:635-645: the second norm clip measures the gradients the first one scaled. With a norm near 1e-3
+    # the epsilon of the first coefficient leaves them 5e-4 under max_grad_norm, which target / (max + eps) would miss
+    # by 500 times the tolerance; the checker measures again, the GPU forms c1 * norm.
+    pair = Pair([5000, 77], [False, True], ox.F32, ox.F32, seed=15, grad_std=2e-5)
+    cfg = ox.StepConfig(max_grad_norm=1e-3, target_grad_norm=5e-4)
+    res, ref = pair.step(cfg)
+    assert 1.2e-3 < ref.grad_norm < 1.7e-3
+    closed_form = float(np.float32(1e-3 / (ref.grad_norm + 1e-6))) * float(np.float32(5e-4 / (1e-3 + 1e-6)))
+    assert abs(closed_form - ref.clip_coef) > 1e-4 * ref.clip_coef  # the case does tell the two forms apart
+    assert abs(res.clip_coef - ref.clip_coef) <= 1e-6 * ref.clip_coef
+    assert abs(res.grad_norm - ref.grad_norm) <= NORM_RTOL * ref.grad_norm
+    assert res.reported_norm == ref.reported_norm == 5e-4
+    pair.assert_close(1e-6)
+    pair.close()
+
+
 @pytest.mark.parametrize("switch", [dict(decay_after=1), dict(eps_mode=1), dict(clip_eps=0.0)])
 def test_unpinned_forms_follow_their_switches(switch):
     pair = Pair([3000, 10], [False, True], ox.BF16, ox.BF16, seed=6)

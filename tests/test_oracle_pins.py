@@ -16,20 +16,21 @@ def one_tensor_state(values, work_dtype=orc.F32):
 
 
 def clip_only(grads, max_value, max_norm):
-    """clip_gradients alone (src/grad_clip.rs:36-56): returns (norm, clipped grads)."""
+    """clip_gradients alone (src/grad_clip.rs:36-56), through the very function the checker's step calls:
+    returns (norm, clipped grads)."""
     flat = [np.array(g, dtype=np.float32) for g in grads]
-    if max_value == max_value:
-        raw = math.sqrt(sum(orc.sumsq(g) for g in flat))
-        if not math.isfinite(raw):
-            return raw, flat
-        for g in flat:
-            orc.lib().orc_clamp(g.ctypes.data, g.size, max_value)
-    norm = math.sqrt(sum(orc.sumsq(g) for g in flat))
-    if math.isfinite(norm) and norm > max_norm:
-        c = np.float32(max_norm / (norm + 1e-6))
-        for g in flat:
-            orc.lib().orc_scale(g.ctypes.data, g.size, c)
+    norm, _ = orc.clip_gradients(flat, max_value, max_norm)
     return norm, flat
+
+
+def clip_through_step(grads, max_value, max_norm):
+    """The same known answers through the whole step: with beta1 = 0 the first moment after one step IS the gradient
+    the optimizer was handed, i.e. the clipped one. Returns (norm, clipped grads, applied)."""
+    flat = [np.array(g, dtype=np.float32) for g in grads]
+    st = orc.StepState([np.zeros_like(g) for g in flat], [np.zeros_like(g) for g in flat],
+                       [np.zeros_like(g) for g in flat], None)
+    res = orc.step(st, [flat], orc.F32, orc.StepConfig(beta1=0.0, max_grad_value=max_value, max_grad_norm=max_norm))
+    return res.grad_norm, st.exp_avg, res.applied
 
 
 F64_MAX = 1.7976931348623157e308
@@ -56,6 +57,46 @@ def test_norm_clip_runs_after_value_clip():
     norm, g = clip_only([[100.0, -100.0, 100.0, -100.0]], 3.0, 1.5)
     assert abs(norm - 6.0) < 1e-5
     assert np.all(np.abs(np.abs(g[0]) - 0.75) < 1e-5)
+
+
+def test_clip_known_answers_through_the_whole_step():
+    # src/grad_clip.rs:82-128 once more, this time through orc.step, the call the GPU path is compared with
+    norm, g, applied = clip_through_step([[3.0, 4.0]], NAN, F64_MAX)
+    assert applied and abs(norm - 5.0) < 1e-6 and g[0].tolist() == [3.0, 4.0]
+    norm, g, applied = clip_through_step([[1e15, -1e15, 0.25], [-7e14, 3.0]], 0.5, F64_MAX)
+    vals = np.concatenate(g)
+    assert applied and np.all(np.abs(vals) <= 0.5) and vals[2] == 0.25
+    assert abs(norm - math.sqrt(4.0 * 0.25 + 0.0625)) < 1e-6
+    norm, g, applied = clip_through_step([[100.0, -100.0, 100.0, -100.0]], 3.0, 1.5)
+    assert applied and abs(norm - 6.0) < 1e-5 and np.all(np.abs(np.abs(g[0]) - 0.75) < 1e-5)
+    for bad in (float("nan"), float("inf"), float("-inf")):
+        norm, g, applied = clip_through_step([[1.0, bad]], 0.5, 1.0)
+        assert not applied and not math.isfinite(norm) and g[0].tolist() == [0.0, 0.0]
+
+
+def test_target_clip_measures_the_clipped_gradients_again():
+    # src/trainer.rs:635-645: when both clips fire, the second call of the norm clip sees the gradients the first one
+    # scaled. Their norm is max * norm / (norm + eps), a little under max, so the second coefficient is
+    # target / (that + eps) and not target / (max + eps).
+    g = [np.array([3.0, 4.0], np.float32)]
+    st = orc.StepState([np.zeros(2, np.float32)], [np.zeros(2, np.float32)], [np.zeros(2, np.float32)], None)
+    res = orc.step(st, [g], orc.F32, orc.StepConfig(beta1=0.0, max_grad_norm=1.0, target_grad_norm=0.5))
+    c1 = np.float32(1.0 / (5.0 + 1e-6))
+    once = g[0] * c1
+    again = math.sqrt(float(np.float32(once[0] * once[0])) + float(np.float32(once[1] * once[1])))
+    c2 = np.float32(0.5 / (again + 1e-6))
+    assert again < 1.0
+    assert np.array_equal(st.exp_avg[0], (once * c2).astype(np.float32))
+    assert res.clip_coef == float(c1) * float(c2) and res.reported_norm == 0.5 and abs(res.grad_norm - 5.0) < 1e-6
+    # the first clip alone: the second call measures unchanged gradients, the very same norm
+    st = orc.StepState([np.zeros(2, np.float32)], [np.zeros(2, np.float32)], [np.zeros(2, np.float32)], None)
+    res = orc.step(st, [g], orc.F32, orc.StepConfig(beta1=0.0, max_grad_norm=10.0, target_grad_norm=2.0))
+    assert res.clip_coef == float(np.float32(2.0 / (5.0 + 1e-6)))
+    # a target within rounding of max: the outer test passes (min(norm, max) > target) but the gradients, already
+    # scaled to just under max, measure below the target, and the second call leaves them alone
+    st = orc.StepState([np.zeros(2, np.float32)], [np.zeros(2, np.float32)], [np.zeros(2, np.float32)], None)
+    res = orc.step(st, [g], orc.F32, orc.StepConfig(beta1=0.0, max_grad_norm=1.0, target_grad_norm=1.0 - 1e-9))
+    assert res.clip_coef == float(c1)
 
 
 @pytest.mark.parametrize("bad", [float("nan"), float("inf"), float("-inf")])

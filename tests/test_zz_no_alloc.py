@@ -32,6 +32,14 @@ def test_static_scratch_norm_matches_the_allocating_entry_point_on_two_calls_in_
         got = ox.compute_grad_norm_static(d.data_ptr(), dtype, n, **kw)
         assert math.isfinite(want) and want > 0.0
         assert abs(got - want) <= NORM_RTOL * want, (got, want)
+        # and against the CPU checker: widen, unscale, clamp, f32 squares summed in f64 (src/grad_clip.rs:47-55)
+        x = orc.widen(g, dtype)
+        if not math.isnan(kw["loss_scale"]):
+            x = orc.unscale(x, orc.F32, kw["loss_scale"])
+        if not math.isnan(kw["max_grad_value"]):
+            x = np.clip(x, np.float32(-kw["max_grad_value"]), np.float32(kw["max_grad_value"]))
+        cpu = math.sqrt(orc.sumsq(x))
+        assert abs(got - cpu) <= NORM_RTOL * cpu, (got, cpu)
         # a caller-chosen, smaller launch uses fewer partial-sum slots of the same array
         got_small = ox.compute_grad_norm_static(d.data_ptr(), dtype, n, clusters=7, **kw)
         assert abs(got_small - want) <= NORM_RTOL * want, (got_small, want)
