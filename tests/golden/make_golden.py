@@ -23,6 +23,8 @@ CASES = {
     "bf16_noclip_w2": (orc.BF16, orc.BF16, 2, 1e-3, dict(max_grad_norm=1e9, eps=1e-8), 2),
     "f16_scaled": (orc.F16, orc.F16, 1, 1e-3 * 1024.0, dict(loss_scale=1024.0, max_grad_norm=1e9), 1),
     "f32_value_target": (orc.F32, orc.F32, 1, 1.0, dict(max_grad_value=0.5, max_grad_norm=2.0, target_grad_norm=0.5), 1),
+    # both norm clips fire on gradients so small that the epsilon of the first coefficient shows in the second
+    "f32_both_clips_small": (orc.F32, orc.F32, 1, 4e-5, dict(max_grad_norm=1e-3, target_grad_norm=5e-4), 1),
 }
 
 
