@@ -38,7 +38,8 @@ typedef enum oxz_status {
     OXZ_ERR_ABORTED = 5,     /* the communicator was aborted (src/dp/launch.rs:97-103) */
     OXZ_ERR_UNSUPPORTED = 6, /* NCCL library or peer access unavailable */
     OXZ_ERR_DATA = 7,        /* mirrors Error::DataError of the row arithmetic */
-    OXZ_ERR_TIMEOUT = 8      /* a rank never joined a collective of a local group within its timeout */
+    OXZ_ERR_TIMEOUT = 8      /* a rank never joined a collective of a local group within its timeout, or a bounded
+                                wait inside a kernel of the step ran out (on any rank: every rank reports it) */
 } oxz_status;
 
 typedef enum oxz_dtype { OXZ_F32 = 0, OXZ_BF16 = 1, OXZ_F16 = 2 } oxz_dtype;
@@ -46,8 +47,10 @@ typedef enum oxz_dtype { OXZ_F32 = 0, OXZ_BF16 = 1, OXZ_F16 = 2 } oxz_dtype;
 /* How the gradients of different ranks meet. */
 typedef enum oxz_sync_mode {
     OXZ_SYNC_SINGLE = 0, /* world 1: no collective (NoOpCommunicator, src/trainer.rs:234) */
-    OXZ_SYNC_P2P = 1,    /* fused kernels over NVLink peer memory: pull-reduce in f32 in rank order,
-                            push of the narrow weights; NCCL only for the 3-double norm all-reduce */
+    OXZ_SYNC_P2P = 1,    /* fused kernels over NVLink peer memory: pull-reduce in f32 in rank order, push of the narrow
+                            weights; the step's barriers and its one small sum (norm terms, loss) also cross through
+                            peer memory, in rank order, when the ranks sit on distinct GPUs behind an NCCL
+                            communicator (OXZ_MAIL=0 in the environment keeps small NCCL all-reduces instead) */
     OXZ_SYNC_NCCL = 2,   /* ncclReduceScatter / ncclAllGather in the gradient's own dtype */
     OXZ_SYNC_COPY = 3,   /* copy engines move the bytes over NVLink (peers' gradient slices into local staging,
                             the updated weights out to every peer), pipelined by groups of buckets with the
@@ -230,8 +233,11 @@ typedef struct oxz_step_result {
 } oxz_step_result;
 
 /* One optimizer step on the gradients now in the flat buffer: src/trainer.rs:520-661 in one call.
- * present: [n_tensors] 0 = no rank produced a gradient for this tensor this step (it is left untouched,
- *          src/dp/reduce.rs:20); NULL = all present. Must be equal on every rank.
+ * present: [n_tensors] 0 = THIS rank produced no gradient for the tensor this step; NULL = it has all of them. The
+ *          ranks' flags may differ (an expert only some ranks routed to): the library forms their union, and a tensor
+ *          is left untouched only when NO rank has a gradient for it (src/dp/reduce.rs:20). Where a rank's flag is 0
+ *          but another's is 1, that rank's span of the gradient buffer must hold zeros (oxz_grads_flatten_async with
+ *          a NULL pointer for the tensor writes them); a span no rank has a gradient for may hold anything.
  * extras:  n_extras host doubles summed over ranks in place (the logged loss, src/dp/reduce.rs:57-59).
  * The decision to skip is taken on the device; nothing is read back between the norm and the update. */
 int32_t oxz_step_async(oxz_plan* plan, oxz_comm* comm, const oxz_hyper* hyper, const uint8_t* present,
@@ -271,6 +277,20 @@ int32_t oxz_plan_launch_geometry(const oxz_plan* plan, int32_t* sm_count, int32_
 #define OXZ_PULL_KERNEL_LOADS 1
 #define OXZ_PULL_KERNEL_BULK 2
 int32_t oxz_plan_last_pull_kernel(const oxz_plan* plan, int32_t* kind);
+/* How the plan's ranks meet for the step's barriers and its small sum: 0 = not at all (one rank), 1 = collectives of
+ * the communicator (NCCL all-reduces, or the host rendezvous of a local group), 2 = through mailboxes in peer memory
+ * (one kernel per exchange, every wait bounded: OXZ_MAIL_TIMEOUT_MS in the environment, 30000 by default, after which
+ * the step changes nothing and oxz_step_wait returns OXZ_ERR_TIMEOUT; oxz_comm_abort ends such a wait at once).
+ * No reference counterpart: a tuning and test aid. */
+#define OXZ_EXCHANGE_NONE 0
+#define OXZ_EXCHANGE_COMM 1
+#define OXZ_EXCHANGE_MAILBOX 2
+int32_t oxz_plan_exchange_kind(const oxz_plan* plan, int32_t* kind);
+/* Shows on one GPU, without any fault, what a rank sees when a peer never arrives: launches the gate kernel as rank 0 of
+ * two ranks whose other rank does not exist, with its wait bounded to limit_ms. *outcome receives what the kernel
+ * recorded (1 = the wait ran out, which is the expected answer); the call then runs the same kernel alone (world 1) to
+ * show the context still works, and returns OXZ_OK only if both went as expected. No reference counterpart: a test aid. */
+int32_t oxz_selftest_bounded_wait(int32_t device, uint32_t limit_ms, int32_t* outcome);
 /* on != 0: record the events every step (a few microseconds); off by default. */
 int32_t oxz_plan_set_profile(oxz_plan* plan, int32_t on);
 int32_t oxz_step_profile_read(oxz_plan* plan, oxz_step_profile* out);
@@ -280,6 +300,16 @@ int32_t oxz_step_profile_read(oxz_plan* plan, oxz_step_profile* out);
  * non-finite norm (src/grad_clip.rs:130-143). Blocking; allocates its partial-sum scratch on first use per device. */
 int32_t oxz_grad_norm(const void* device_grads, int32_t dtype, uint64_t n, double loss_scale, double max_grad_value,
                       void* stream, double* norm);
+
+/* The L2 norm of every tensor's gradient as the last step saw it: summed over ranks, unscaled by loss_scale (NaN or 0:
+ * no scaler), clamped to max_grad_value when that is not NaN. It is grad_norm_for_tensor (src/trainer.rs:933-937), which
+ * the reference calls per parameter to name the offending tensors after a non-finite norm (diagnose_bad_gradients,
+ * src/trainer.rs:990-1020) and for its DEBUG_GRAD breakdown (src/trainer.rs:940-988). norms[n_tensors]: a tensor with a
+ * non-finite element gives inf or NaN as the global norm does; a tensor no rank had a gradient for gives -1. Call it
+ * after oxz_step_wait and before the gradient buffer changes; collective with more than one rank (each rank measures
+ * the part it owns); blocking; off the step's path (it is only needed after a skipped step or for debugging). The
+ * per-tensor sums are accumulated with atomic adds: their last bits may differ from run to run. */
+int32_t oxz_grad_norms_per_tensor(oxz_plan* plan, oxz_comm* comm, double loss_scale, double max_grad_value, double* norms);
 
 /* The same measurement as oxz_grad_norm for hosts that must not allocate. It has no counterpart in the reference:
  * it exists for callers of this library whose device memory is already spoken for (a trainer whose caching
@@ -346,6 +376,23 @@ int32_t oxz_rows_advance(const oxz_row_layout* layout, oxz_data_position pos, ui
 int32_t oxz_rows_next_window(const oxz_row_layout* layout, oxz_data_position pos, uint64_t rank, uint64_t seq_len,
                              uint64_t first_row, const uint32_t* tokens, uint64_t n_tokens, uint64_t* rows,
                              int64_t* inputs, int64_t* targets, oxz_data_position* next);
+/* The row order the reference runs by default, RowOrder::Shuffled (trainer.shuffle_rows = true, src/config.rs:80-82): a
+ * permutation of the shard's rows per epoch, which the Rust side makes with rand's StdRng and SliceRandom::shuffle
+ * (epoch_permutation(num_rows, seed, epoch), src/data/rows.rs:258-272) and hands over; the library maps slot -> perm[slot]
+ * as EpochOrder::row does (src/data/rows.rs:240-256) and so reads the reference's rows bit for bit without restating the
+ * generator.
+ * oxz_rows_batch_epoch: the epoch whose order the batch drawn at `pos` reads - pos.epoch, or the next one when fewer
+ * rows than a global batch are left (RowLayout::batch_start, src/data/rows.rs:153-165).
+ * oxz_rows_check_permutation: OXZ_ERR_DATA unless perm holds every value of 0..n once.
+ * oxz_rows_next_window_ordered: oxz_rows_next_window with the row at each slot taken from perm (n_perm = num_rows
+ * values, the order of epoch perm_epoch); OXZ_ERR_DATA when the batch reads another epoch than perm_epoch. Only the
+ * entries it reads are range-checked here; check the whole permutation once with oxz_rows_check_permutation. */
+int32_t oxz_rows_batch_epoch(const oxz_row_layout* layout, oxz_data_position pos, uint64_t* epoch);
+int32_t oxz_rows_check_permutation(const uint32_t* perm, uint64_t n);
+int32_t oxz_rows_next_window_ordered(const oxz_row_layout* layout, oxz_data_position pos, uint64_t rank, uint64_t seq_len,
+                                     uint64_t first_row, const uint32_t* tokens, uint64_t n_tokens, uint64_t perm_epoch,
+                                     const uint32_t* perm, uint64_t n_perm, uint64_t* rows, int64_t* inputs,
+                                     int64_t* targets, oxz_data_position* next);
 /* ------------------------------------------------------------------ the checkpoint meta's keys on this path
  *
  * `checkpoint_step_N.meta.json` is CheckpointMeta (src/config.rs:1223-1302) as serde_json writes it. These are the keys
@@ -412,6 +459,13 @@ int32_t oxz_loader_source_rows(const oxz_loader* loader, uint64_t* rows, uint32_
  * the thread meets is returned by the call that reaches that batch. depth 0 turns it off. Needs the device (pinned
  * memory). */
 int32_t oxz_loader_set_prefetch(oxz_loader* loader, uint32_t depth);
+/* LitDataLoader::with_row_order(RowOrder::Shuffled{seed}) (src/data/construction.rs:140) with the permutation made by the
+ * caller: perm[slot] is the loader row (0..oxz_loader_num_rows) read at `slot` of `epoch`. The loader copies it, rejects
+ * anything that is not a permutation of its rows, and keeps the orders of two epochs (a third drops the lowest), so the
+ * next epoch's can be handed over before the rollover - a prefetch thread draws across it. A batch whose epoch has no
+ * order fails with OXZ_ERR_DATA naming the epoch. perm NULL: back to stream order. Restarts a prefetch thread at the
+ * loader's position. Not together with a mixture, whose sources are drawn in passes of their own. */
+int32_t oxz_loader_set_row_order(oxz_loader* loader, uint64_t epoch, const uint32_t* perm, uint64_t n);
 /* Draws the next batch's rows only: rows[rank_batch_size] receive the global rows this rank reads, and the position
  * moves on as after a batch. Host only: what a dry run or a test of the row order needs. */
 int32_t oxz_loader_next_rows(oxz_loader* loader, uint64_t* rows);
@@ -420,8 +474,8 @@ int32_t oxz_loader_next_rows(oxz_loader* loader, uint64_t* rows);
  * them (src/data/mixture/quota.rs:22-57), interleaved by smooth weighted round-robin, the same every epoch
  * (src/data/mixture/schedule.rs:103-122), and its k-th draw of the run reads its training row k % n_i
  * (src/data/mixture/draw.rs:44-62), so an upsampled source repeats each row once per pass and a seek is exact. The
- * loader's layout then counts rows_per_epoch rows and the position returns to the start. The shuffled schedule needs
- * rand 0.10.3's StdRng and is not offered. */
+ * loader's layout then counts rows_per_epoch rows and the position returns to the start. The shuffled schedule and the
+ * per-pass permutations of a shuffled mixture need rand 0.10.3's StdRng on this side and are not offered. */
 int32_t oxz_loader_set_mixture(oxz_loader* loader, const double* weights, uint32_t n_weights, int32_t has_rows_per_epoch,
                                uint64_t rows_per_epoch);
 typedef struct oxz_mixture_source { double weight; uint64_t rows_per_epoch, train_rows; } oxz_mixture_source; /* MixtureSource */

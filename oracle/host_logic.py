@@ -298,8 +298,13 @@ class RowLayout:
         return self.advance(DataPosition(), steps * grad_accum)
 
 
-def rank_window(layout: RowLayout, pos: DataPosition, rank: int, seq_len: int, first_row: int = 0):
-    """One rank's draw of the next global batch in stream order.
+def rank_window(layout: RowLayout, pos: DataPosition, rank: int, seq_len: int, first_row: int = 0, order=None):
+    """One rank's draw of the next global batch, in stream order or, with `order`, in the reference's shuffled order.
+
+    order: a callable epoch -> permutation of range(num_rows), standing for epoch_permutation(num_rows, seed, epoch)
+    (src/data/rows.rs:258-263: rand 0.10.3's StdRng + SliceRandom::shuffle, un-vendored, so the VALUES of the
+    reference's permutations are not restated; what is restated is EpochOrder::row, src/data/rows.rs:240-256: the
+    row at `slot` of `epoch` is perm(epoch)[slot], asked for the epoch of layout.batch_start(pos)).
 
     src/data/positioning.rs:44-68 (slots [start.row + rank*B, +B)), src/data/rows.rs:243-246 (stream order:
     row = slot), src/data/row_ranges.rs:100-106 (one range: first_row + row), src/data/rows.rs:4-7
@@ -311,7 +316,12 @@ def rank_window(layout: RowLayout, pos: DataPosition, rank: int, seq_len: int, f
     start = layout.batch_start(pos)
     width = seq_len + 1
     first = start.row + rank * layout.rank_batch_size
-    rows = [first_row + slot for slot in range(first, first + layout.rank_batch_size)]
+    slots = range(first, first + layout.rank_batch_size)
+    if order is None:
+        rows = [first_row + slot for slot in slots]
+    else:
+        perm = order(start.epoch)
+        rows = [first_row + int(perm[slot]) for slot in slots]
     inputs = [[r * width + j for j in range(seq_len)] for r in rows]
     targets = [[r * width + j + 1 for j in range(seq_len)] for r in rows]
     return rows, inputs, targets, DataPosition(start.epoch, start.row + layout.batch_size())

@@ -8,4 +8,5 @@ from . import _ffi as ffi  # noqa: F401
 from .dpstep import (CheckpointMeta, MixtureRecord, check_mixture_resume, Communicator, DataPosition, DecayPlan, DpOptimizer, GradScalerState, LitDataLoader, LitTrainerStep,  # noqa: F401
                      LossScaleConfig, LossScaler, LrPlan, RowLayout, SpikeGuard, SpikeGuardConfig, SpikeGuardState, StepConfig,
                      TensorInfo, TrainerConfig, WeightDecaySpec, check_resume_world, compute_grad_norm, mixture_quotas,
-                     compute_grad_norm_static, read_loss_scale_state, run_ranks, step_weighting)
+                     compute_grad_norm_static, diagnose_bad_gradients, read_loss_scale_state, run_ranks, selftest_bounded_wait,
+                     step_weighting)

@@ -14,6 +14,7 @@ LIB_PATH = os.path.join(_HERE, "liboxz_dpstep.so")
 OK, ERR_INVALID, ERR_CUDA, ERR_NCCL, ERR_STATE, ERR_ABORTED, ERR_UNSUPPORTED, ERR_DATA, ERR_TIMEOUT = range(9)
 F32, BF16, F16 = 0, 1, 2
 SYNC_SINGLE, SYNC_P2P, SYNC_NCCL, SYNC_COPY, SYNC_REPLICATED = 0, 1, 2, 3, 4
+EXCHANGE_NONE, EXCHANGE_COMM, EXCHANGE_MAILBOX = 0, 1, 2
 STATE_MASTER, STATE_EXP_AVG, STATE_EXP_AVG_SQ, STATE_WORK, STATE_GRADS = range(5)
 DECAY_ALL, SKIP_1D, SKIP_ALL = 0, 1, 2
 LR_CONSTANT, LR_COSINE, LR_LINEAR, LR_WSD = range(4)
@@ -148,6 +149,9 @@ SIGNATURES = {
     "oxz_step": (C.c_int32, [vp, vp, C.POINTER(Hyper), u8p, f64p, C.c_uint32, C.POINTER(StepResult)]),
     "oxz_plan_launch_geometry": (C.c_int32, [vp] + [C.POINTER(C.c_int32)] * 3),
     "oxz_plan_last_pull_kernel": (C.c_int32, [vp, C.POINTER(C.c_int32)]),
+    "oxz_plan_exchange_kind": (C.c_int32, [vp, C.POINTER(C.c_int32)]),
+    "oxz_selftest_bounded_wait": (C.c_int32, [C.c_int32, C.c_uint32, C.POINTER(C.c_int32)]),
+    "oxz_grad_norms_per_tensor": (C.c_int32, [vp, vp, C.c_double, C.c_double, f64p]),
     "oxz_plan_set_profile": (C.c_int32, [vp, C.c_int32]),
     "oxz_step_profile_read": (C.c_int32, [vp, C.POINTER(StepProfile)]),
     "oxz_grad_norm": (C.c_int32, [vp, C.c_int32, C.c_uint64, C.c_double, C.c_double, vp, f64p]),
@@ -185,6 +189,12 @@ SIGNATURES = {
     "oxz_rows_next_window": (C.c_int32, [C.POINTER(RowLayoutC), DataPositionC, C.c_uint64, C.c_uint64, C.c_uint64,
                                          C.POINTER(C.c_uint32), C.c_uint64, u64p, i64p, i64p,
                                          C.POINTER(DataPositionC)]),
+    "oxz_rows_batch_epoch": (C.c_int32, [C.POINTER(RowLayoutC), DataPositionC, u64p]),
+    "oxz_rows_check_permutation": (C.c_int32, [C.POINTER(C.c_uint32), C.c_uint64]),
+    "oxz_rows_next_window_ordered": (C.c_int32, [C.POINTER(RowLayoutC), DataPositionC, C.c_uint64, C.c_uint64, C.c_uint64,
+                                                 C.POINTER(C.c_uint32), C.c_uint64, C.c_uint64, C.POINTER(C.c_uint32), C.c_uint64,
+                                                 u64p, i64p, i64p, C.POINTER(DataPositionC)]),
+    "oxz_loader_set_row_order": (C.c_int32, [vp, C.c_uint64, C.POINTER(C.c_uint32), C.c_uint64]),
     "oxz_loader_open": (C.c_int32, [C.c_char_p, C.c_uint64, C.c_uint64, C.c_uint64, C.c_uint64, C.c_uint64, C.c_uint64,
                                     C.c_int32, C.POINTER(vp)]),
     "oxz_loader_close": (C.c_int32, [vp]),

@@ -77,6 +77,9 @@ static int32_t finish_comm(oxz_comm* c) {
     OXZ_CUDA(cudaStreamCreateWithFlags(&c->stream, cudaStreamNonBlocking));
     OXZ_CUDA(cudaMalloc(&c->d_small, 512));
     OXZ_CUDA(cudaMemset(c->d_small, 0, 512));
+    // kernels that wait on other ranks poll this word in host memory: an abort from any thread ends their wait
+    OXZ_CUDA(cudaHostAlloc((void**)&c->h_abort_flag, sizeof(int32_t), cudaHostAllocMapped | cudaHostAllocPortable));
+    *c->h_abort_flag = 0;
     return OXZ_OK;
 }
 
@@ -154,6 +157,27 @@ int32_t comm_stream_barrier(oxz_comm* c, int32_t* d_flag, cudaStream_t s) {
     }
     ncclResult_t rc = nccl_api()->AllReduce(d_flag, d_flag, 1, ncclInt32, ncclSum, (ncclComm_t)c->nccl, s);
     if (rc != ncclSuccess) return nccl_fail("step barrier", rc);
+    return OXZ_OK;
+}
+
+// The union over ranks of per-tensor flags (1 = this rank has a gradient): a local group forms it on the host, in
+// place in h_inout, and *host_known says so; NCCL forms it on the device (maximum of bytes), d_in -> d_out, which also
+// serves as a barrier on `s`.
+int32_t comm_present_union(oxz_comm* c, uint8_t* h_inout, const uint8_t* d_in, uint8_t* d_out, uint64_t n, cudaStream_t s,
+                           bool* host_known) {
+    if (c->kind == 1) {
+        *host_known = true;
+        return local_exchange(c, h_inout, n, h_inout, n,
+                              [n](const std::vector<std::vector<uint8_t>>& slots, std::vector<uint8_t>& result) {
+                                  result.assign(n, 0);
+                                  for (const auto& sl : slots)
+                                      for (size_t i = 0; i < n && i < sl.size(); i++) result[i] |= sl[i] ? 1 : 0;
+                              }, "the union of the ranks' gradient flags");
+    }
+    *host_known = false;
+    if (n == 0) return OXZ_OK;
+    ncclResult_t rc = nccl_api()->AllReduce(d_in, d_out, n, ncclUint8, ncclMax, (ncclComm_t)c->nccl, s);
+    if (rc != ncclSuccess) return nccl_fail("the union of the ranks' gradient flags", rc);
     return OXZ_OK;
 }
 
@@ -333,6 +357,7 @@ int32_t oxz_comm_abort(oxz_comm* c) {
         if (!c) return fail(OXZ_ERR_INVALID, "oxz_comm_abort: null communicator");
         int expected = 0;
         if (!c->aborted.compare_exchange_strong(expected, 1)) return OXZ_OK;  // the first abort wins
+        if (c->h_abort_flag) *reinterpret_cast<volatile int32_t*>(c->h_abort_flag) = 1;  // ends the kernels' own waits
         if (c->kind == 1) {
             std::lock_guard<std::mutex> lock(c->local->mu);
             c->local->aborted = true;
@@ -356,6 +381,7 @@ int32_t oxz_comm_destroy(oxz_comm* c) {
         if (c->device >= 0) cudaSetDevice(c->device);
         if (api && c->nccl && !c->aborted.load()) api->CommDestroy((ncclComm_t)c->nccl);
         if (c->d_small) cudaFree(c->d_small);
+        if (c->h_abort_flag) cudaFreeHost(c->h_abort_flag);
         if (c->stream) cudaStreamDestroy(c->stream);
         delete c;
         return OXZ_OK;

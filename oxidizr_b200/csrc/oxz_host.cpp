@@ -4,6 +4,8 @@
 #include <cstring>
 #include <string>
 
+#include <vector>
+
 #include "oxz_internal.h"
 
 using namespace oxz;
@@ -266,6 +268,73 @@ int32_t oxz_rows_next_window(const oxz_row_layout* l, oxz_data_position pos, uin
             }
         }
         if (next) *next = oxz_data_position{start.epoch, start.row + B * l->world_size};
+        return OXZ_OK;
+    });
+}
+
+int32_t oxz_rows_batch_epoch(const oxz_row_layout* l, oxz_data_position pos, uint64_t* epoch) {
+    return oxz::guarded("oxz_rows_batch_epoch", [&]() -> int32_t {
+        if (!epoch) return fail(OXZ_ERR_INVALID, "oxz_rows_batch_epoch: null argument");
+        OXZ_TRY(oxz_rows_check(l));
+        if (pos.row > l->num_rows)
+            return fail(OXZ_ERR_DATA, "data position epoch %llu row %llu is past this shard's %llu rows", (unsigned long long)pos.epoch,
+                        (unsigned long long)pos.row, (unsigned long long)l->num_rows);
+        *epoch = batch_start(l, pos).epoch;
+        return OXZ_OK;
+    });
+}
+
+int32_t oxz_rows_check_permutation(const uint32_t* perm, uint64_t n) {
+    return oxz::guarded("oxz_rows_check_permutation", [&]() -> int32_t {
+        if (!perm && n) return fail(OXZ_ERR_INVALID, "oxz_rows_check_permutation: null argument");
+        std::vector<uint64_t> seen((n + 63) / 64, 0);
+        for (uint64_t i = 0; i < n; i++) {
+            const uint64_t v = perm[i];
+            if (v >= n) return fail(OXZ_ERR_DATA, "the row order holds row %llu at slot %llu, past its %llu rows: it is not a permutation of 0..%llu", (unsigned long long)v, (unsigned long long)i, (unsigned long long)n, (unsigned long long)n);
+            if (seen[v >> 6] & (1ull << (v & 63)))
+                return fail(OXZ_ERR_DATA, "the row order holds row %llu twice (again at slot %llu): it is not a permutation of 0..%llu", (unsigned long long)v, (unsigned long long)i, (unsigned long long)n);
+            seen[v >> 6] |= 1ull << (v & 63);
+        }
+        return OXZ_OK;
+    });
+}
+
+int32_t oxz_rows_next_window_ordered(const oxz_row_layout* l, oxz_data_position pos, uint64_t rank, uint64_t seq_len,
+                                     uint64_t first_row, const uint32_t* tokens, uint64_t n_tokens, uint64_t perm_epoch,
+                                     const uint32_t* perm, uint64_t n_perm, uint64_t* rows, int64_t* inputs, int64_t* targets,
+                                     oxz_data_position* next) {
+    return oxz::guarded("oxz_rows_next_window_ordered", [&]() -> int32_t {
+        if (!perm) return fail(OXZ_ERR_INVALID, "oxz_rows_next_window_ordered: null row order");
+        OXZ_TRY(oxz_rows_check(l));
+        if (n_perm != l->num_rows)
+            return fail(OXZ_ERR_DATA, "the row order holds %llu rows and the layout %llu: pass the permutation of this layout's rows",
+                        (unsigned long long)n_perm, (unsigned long long)l->num_rows);
+        // the slots, by the stream-order arithmetic; then EpochOrder::row: the row at each slot (src/data/rows.rs:240-256)
+        std::vector<uint64_t> slots(l->rank_batch_size);
+        oxz_data_position after{};
+        OXZ_TRY(oxz_rows_next_window(l, pos, rank, seq_len, 0, nullptr, 0, slots.data(), nullptr, nullptr, &after));
+        if (after.epoch != perm_epoch)
+            return fail(OXZ_ERR_DATA, "the next batch reads epoch %llu and the row order given is epoch %llu's: pass epoch_permutation(num_rows, seed, %llu)",
+                        (unsigned long long)after.epoch, (unsigned long long)perm_epoch, (unsigned long long)after.epoch);
+        const uint64_t width = seq_len + 1;
+        for (uint64_t k = 0; k < l->rank_batch_size; k++) {
+            const uint64_t shard_row = perm[slots[k]];
+            if (shard_row >= l->num_rows)
+                return fail(OXZ_ERR_DATA, "the row order holds row %llu at slot %llu, past its %llu rows: it is not a permutation", (unsigned long long)shard_row,
+                            (unsigned long long)slots[k], (unsigned long long)l->num_rows);
+            const uint64_t row = first_row + shard_row;
+            if (rows) rows[k] = row;
+            if (tokens) {
+                if ((row + 1) * width > n_tokens)
+                    return fail(OXZ_ERR_DATA, "row %llu lies past the %llu tokens of the stream", (unsigned long long)row, (unsigned long long)n_tokens);
+                const uint32_t* src = tokens + row * width;
+                for (uint64_t j = 0; j < seq_len; j++) {
+                    if (inputs) inputs[k * seq_len + j] = (int64_t)src[j];
+                    if (targets) targets[k * seq_len + j] = (int64_t)src[j + 1];
+                }
+            }
+        }
+        if (next) *next = after;
         return OXZ_OK;
     });
 }

@@ -53,7 +53,31 @@ constexpr uint32_t MAX_GROUPS = 8;       // distinct (lr_scale, decay) groups a 
 constexpr uint32_t PAD_TILE = 0xFFFFFFFFu;  // tile_meta of a tile past the last tensor
 constexpr uint32_t MAX_PEERS = 16;
 constexpr uint32_t MAX_EXTRAS = 13;
-constexpr uint32_t MAX_PIPE = 8;         // groups of buckets a copy-engine step is pipelined in      // doubles that ride on the norm all-reduce
+constexpr uint32_t MAX_PIPE = 8;         // groups of buckets a copy-engine step is pipelined in
+// The doubles that cross the ranks once per step: {sum of squares, infinities seen, NaNs seen, a bounded wait ran out
+// on some rank, extras...}.
+constexpr uint32_t ACC_EXPIRED = 3;
+constexpr uint32_t ACC_EXTRAS = 4;
+constexpr uint32_t ACC_DOUBLES = ACC_EXTRAS + MAX_EXTRAS;
+
+// A rank's mailbox: one slot per sending rank and parity of the exchange number, in device memory every peer can
+// write. An exchange is: write the payload into my slot of every rank's mailbox, then the exchange number (release);
+// wait until every slot of my own mailbox carries that number (acquire); read the payloads. Two parities suffice: a
+// rank can enter exchange k+2, which reuses the slots of k, only after every rank has entered k+1 and so has finished
+// reading k. It stands in for a small NCCL all-reduce or barrier (tens of microseconds) at a few microseconds, and
+// the sum over the slots runs in rank order on every rank.
+constexpr uint32_t MAIL_PAYLOAD = 4096;  // bytes: the tensors' present flags, or ACC_DOUBLES doubles
+struct alignas(16) MailSlot {
+    unsigned long long seq;
+    unsigned long long pad;
+    unsigned char payload[MAIL_PAYLOAD];
+};
+struct MailBox {
+    MailSlot slot[2][MAX_PEERS];
+};
+struct MailPeers {
+    MailBox* box[MAX_PEERS];  // box[r]: rank r's mailbox as this rank addresses it; box[rank] is local
+};
 
 inline size_t dtype_size(int32_t dt) { return dt == OXZ_F32 ? 4 : 2; }
 
@@ -88,7 +112,8 @@ struct DevScalars {
     float c1, c2;       // clip coefficients applied in this order
     int32_t overflow;
     int32_t skip;       // overflow or spike veto: the update kernel returns at once
-    int32_t wait_expired;  // a bounded wait inside a kernel ran out (bulk-copy pull): the step is reported failed
+    int32_t wait_expired;  // a bounded wait inside a kernel ran out, on this rank or (after the exchange) on any rank:
+                           // the step changes nothing and is reported failed. 2: the wait was ended by an abort
     int32_t reserved;
 };
 
@@ -118,6 +143,10 @@ uint32_t pull_partial_slots(const LaunchGeom& g, int32_t dt);
 int32_t launch_sumsq(cudaStream_t s, const LaunchGeom& g, const void* grads, int32_t dt, const TileMap& map,
                      const uint32_t* tile_meta, const uint8_t* present, bool check_present, float inv_scale,
                      float clamp_hi, int32_t clamp_on, double* partials);
+// Per-tensor {sum, inf, NaN} of the same quantity, added into out[3 * n_tensors] (zeroed by the caller).
+int32_t launch_sumsq_tensors(cudaStream_t s, const LaunchGeom& g, const void* grads, int32_t dt, const TileMap& map,
+                             const uint32_t* tile_meta, const uint8_t* present, float inv_scale, float clamp_hi,
+                             int32_t clamp_on, double* out);
 // Same over a plain array of n elements (no plan): the standalone norm entry point.
 int32_t launch_sumsq_plain(cudaStream_t s, int blocks, const void* grads, int32_t dt, uint64_t n, float inv_scale,
                            float clamp_hi, int32_t clamp_on, double* partials);
@@ -133,10 +162,21 @@ int32_t launch_pull_bulk(cudaStream_t s, const LaunchGeom& g, const PeerTable& p
                          const TileMap& map, const uint32_t* tile_meta, const uint8_t* present, bool check_present,
                          float inv_scale, float clamp_hi, int32_t clamp_on, float* reduced, double* partials,
                          uint32_t slots, DevScalars* scalars);
-// partials[slots][3] -> acc[3] = {sum, inf count, nan count}
-int32_t launch_reduce_partials(cudaStream_t s, const double* partials, uint32_t slots, double* acc);
-// acc[3] -> scalars (norm, clip coefficients, decisions)
+// partials[slots][3] -> acc[0..3) = {sum, inf count, nan count}; acc[ACC_EXPIRED] = 1 when scalars (may be null) says a
+// bounded wait of this rank ran out
+int32_t launch_reduce_partials(cudaStream_t s, const double* partials, uint32_t slots, double* acc, const DevScalars* scalars);
+// acc -> scalars (norm, clip coefficients, decisions); acc[ACC_EXPIRED] > 0 makes the step a reported failure
 int32_t launch_finalize(cudaStream_t s, const double* acc, const FinalizeParams& fp, DevScalars* scalars);
+// Exchange `seq` as a barrier, optionally carrying the tensors' present flags: present_out[i] = OR over ranks of their
+// present_in[i] (T 0: barrier only). Every wait is bounded by limit_ns and ended early by *abort_flag != 0.
+int32_t launch_gate(cudaStream_t s, const MailPeers& mail, int32_t world, int32_t rank, uint64_t seq, const uint8_t* present_in,
+                    uint8_t* present_out, uint32_t T, DevScalars* scalars, uint64_t limit_ns, const int32_t* abort_flag);
+// The step's one data exchange, fused with the sums either side of it: partials -> this rank's {sum, inf, NaN} ->
+// exchange `seq` with acc[ACC_EXPIRED..ACC_EXTRAS + n_extras) riding along -> sums over ranks in rank order ->
+// acc and the scalars. sum_norm 0 (full replicas): the three norm terms stay this rank's own.
+int32_t launch_decide(cudaStream_t s, const MailPeers& mail, int32_t world, int32_t rank, uint64_t seq, const double* partials,
+                      uint32_t slots, double* acc, uint32_t n_extras, int32_t sum_norm, const FinalizeParams& fp,
+                      DevScalars* scalars, uint64_t limit_ns, const int32_t* abort_flag);
 // The fused update. gsrc is indexed in local space (dtype gdt); master/m/v local f32; work is written in flat space
 // to every pointer of `peers.work[0..n_work)` (n_work 0: no working copy).
 int32_t launch_adamw(cudaStream_t s, const LaunchGeom& g, const void* gsrc, int32_t gdt, float* master, float* m,
@@ -163,6 +203,7 @@ struct oxz_comm {
     int32_t rank = 0, world = 1, device = 0;
     cudaStream_t stream = nullptr;  // for the small blocking collectives
     void* d_small = nullptr;        // 512 bytes of device scratch for them
+    int32_t* h_abort_flag = nullptr;  // pinned, mapped: kernels that wait on other ranks poll it; oxz_comm_abort sets it
     std::atomic<int> aborted{0};
 };
 
@@ -189,7 +230,8 @@ struct oxz_plan {
     float *master = nullptr, *exp_avg = nullptr, *exp_avg_sq = nullptr;
     void* reduced = nullptr;  // W>1: the summed gradients of this rank's tiles (f32 for P2P, grad dtype for NCCL)
     uint32_t* d_tile_meta = nullptr;
-    uint8_t* d_present = nullptr;
+    uint8_t* d_present = nullptr;     // per tensor: some rank has a gradient this step (what the kernels read)
+    uint8_t* d_present_in = nullptr;  // this rank's own flags (more than one rank)
     uint64_t *d_offsets = nullptr, *d_numel = nullptr;
     const void** d_src = nullptr;
     double* d_partials = nullptr;
@@ -199,7 +241,8 @@ struct oxz_plan {
     oxz::DevScalars* h_scalars = nullptr;
     double* h_acc = nullptr;
     double* h_extras = nullptr;
-    uint8_t* h_present = nullptr;
+    uint8_t* h_present = nullptr;     // this rank's own flags as last given
+    uint8_t* h_union = nullptr;       // the union over ranks, where the host learns it (a local group)
     const void** h_src = nullptr;
     cudaEvent_t done = nullptr;
     bool profile = false;
@@ -223,6 +266,12 @@ struct oxz_plan {
     cudaEvent_t ev_go = nullptr, ev_copied[oxz::MAX_PEERS][oxz::MAX_PIPE] = {}, ev_updated[oxz::MAX_PIPE] = {}, ev_pushed[oxz::MAX_PEERS] = {};
     uint32_t pipe_groups = 1;
     oxz_comm* comm = nullptr;
+    // exchanges between ranks through peer memory (ranks on distinct GPUs behind an NCCL communicator)
+    bool use_mail = false;
+    oxz::MailBox* mail = nullptr;
+    oxz::MailPeers mail_peers{};
+    uint64_t mail_seq = 0;        // exchanges made so far; every rank makes the same ones in the same order
+    uint64_t mail_limit_ns = 0;
 
     // buckets reduced ahead of the step (oxz_grads_ready_async)
     cudaStream_t early_stream = nullptr;

@@ -20,6 +20,7 @@
 #include <cuda_fp16.h>
 
 #include <cstdlib>
+#include <cstring>
 
 #include "oxz_internal.h"
 
@@ -323,6 +324,48 @@ __global__ void __cluster_dims__(CLUSTER, 1, 1) __launch_bounds__(THREADS)
     cluster_reduce_store(a, partials);
 }
 
+// Per-tensor sums of squares over this rank's tiles: out[3 * t + {0, 1, 2}] += {sum, infinities seen, NaNs seen} of
+// tensor t. A warp walks its tiles in order and keeps a running sum while the tensor stays the same, so the atomic
+// adds number a few per warp and tensor, not one per tile. Off the step's path: a diagnostic after a skipped step.
+template <int DT>
+__global__ void __launch_bounds__(THREADS)
+    k_sumsq_tensors(const void* __restrict__ grads, TileMap map, const uint32_t* __restrict__ tile_meta,
+                    const uint8_t* __restrict__ present, float inv_scale, float clamp_hi, int clamp_on,
+                    double* __restrict__ out) {
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const uint32_t per_iter = gridDim.x * WARPS;
+    uint32_t cur = PAD_TILE;
+    NormAcc a;
+    auto flush = [&]() {
+        if (cur == PAD_TILE) return;
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) {
+            a.sum += __shfl_down_sync(0xffffffffu, a.sum, o);
+            a.flags |= __shfl_down_sync(0xffffffffu, a.flags, o);
+        }
+        if (lane == 0) {
+            atomicAdd(&out[3 * static_cast<size_t>(cur) + 0], a.sum);
+            if (a.flags & FLAG_INF) atomicAdd(&out[3 * static_cast<size_t>(cur) + 1], 1.0);
+            if (a.flags & FLAG_NAN) atomicAdd(&out[3 * static_cast<size_t>(cur) + 2], 1.0);
+        }
+        a = NormAcc();
+    };
+    for (uint32_t lt = map.first_tile + blockIdx.x * WARPS + warp; lt < map.n_local_tiles; lt += per_iter) {
+        const uint32_t meta = tile_meta[flat_tile(map, lt)];
+        if (meta == PAD_TILE) continue;
+        const uint32_t t = meta & 0xffffffu;
+        if (!present[t]) continue;
+        if (t != cur) {
+            flush();
+            cur = t;
+        }
+        float g[8];
+        load8<DT>(grads, static_cast<uint64_t>(lt) * TILE + lane * 8, g);
+        acc8(g, inv_scale, clamp_hi, clamp_on != 0, a);
+    }
+    flush();
+}
+
 // A vector of 8 elements as it sits in memory: 16-bit types stay packed (4 registers) until they are needed, so a
 // lane can keep eight remote loads in flight without eight times the registers.
 template <int DT>
@@ -596,10 +639,9 @@ __global__ void __cluster_dims__(CLUSTER, 1, 1) __launch_bounds__(THREADS)
     cluster_reduce_store(a, partials);
 }
 
-// One block: adds the per-cluster partials in index order.
-__global__ void __launch_bounds__(THREADS) k_reduce_partials(const double* __restrict__ partials, uint32_t slots,
-                                                             double* __restrict__ acc) {
-    __shared__ double sh[3][THREADS];
+// Adds the per-cluster partials in index order; the block's threads leave {sum, inf, NaN} in t_out[0..3) (shared).
+__device__ __forceinline__ void block_sum_partials(const double* __restrict__ partials, uint32_t slots, double (&sh)[3][THREADS],
+                                                   double (&t_out)[3]) {
     double t[3] = {0.0, 0.0, 0.0};
     // contiguous chunks per thread keep the order fixed
     const uint32_t per = (slots + THREADS - 1) / THREADS;
@@ -611,14 +653,25 @@ __global__ void __launch_bounds__(THREADS) k_reduce_partials(const double* __res
     if (threadIdx.x < 3) {
         double r = 0.0;
         for (int i = 0; i < THREADS; i++) r += sh[threadIdx.x][i];
-        acc[threadIdx.x] = r;
+        t_out[threadIdx.x] = r;
     }
+    __syncthreads();
 }
 
-// acc = {sum of squares, infinities seen, NaNs seen} summed over every rank.
+// One block. acc[ACC_EXPIRED] tells the other ranks (it rides on the same all-reduce) that a bounded wait of this
+// rank's pull ran out, so that every rank reports the step failed and none takes it for an overflow.
+__global__ void __launch_bounds__(THREADS) k_reduce_partials(const double* __restrict__ partials, uint32_t slots,
+                                                             double* __restrict__ acc, const DevScalars* __restrict__ scalars) {
+    __shared__ double sh[3][THREADS];
+    __shared__ double t[3];
+    block_sum_partials(partials, slots, sh, t);
+    if (threadIdx.x < 3) acc[threadIdx.x] = t[threadIdx.x];
+    if (threadIdx.x == 3) acc[ACC_EXPIRED] = (scalars != nullptr && scalars->wait_expired) ? 1.0 : 0.0;
+}
+
+// acc = {sum of squares, infinities seen, NaNs seen, waits run out} summed over every rank.
 // norm, the overflow decision and the clip coefficients follow src/grad_clip.rs:36-56 and src/trainer.rs:619-645.
-__global__ void k_finalize(const double* __restrict__ acc, FinalizeParams fp, DevScalars* __restrict__ out) {
-    if (threadIdx.x != 0 || blockIdx.x != 0) return;
+__device__ __forceinline__ void finalize_scalars(const double* acc, const FinalizeParams& fp, DevScalars* out) {
     const double sum = acc[0];
     double norm;
     if (acc[2] > 0.0) norm = __longlong_as_double(0x7ff8000000000000ll);
@@ -638,12 +691,142 @@ __global__ void k_finalize(const double* __restrict__ acc, FinalizeParams fp, De
             if (again > fp.target_grad_norm) c2 = static_cast<float>(fp.target_grad_norm / (again + fp.clip_eps));
         }
     }
+    // a wait that ran out anywhere: some rank's sum is incomplete, the step must change nothing on any rank
+    // (this rank's own flag is part of that sum: nothing of `out` is read here)
+    const bool expired = acc[ACC_EXPIRED] > 0.0;
     out->norm = norm;
     out->sumsq = sum;
     out->c1 = c1;
     out->c2 = c2;
     out->overflow = overflow ? 1 : 0;
-    out->skip = (overflow || fp.spike_skip) ? 1 : 0;
+    out->skip = (overflow || fp.spike_skip || expired) ? 1 : 0;
+    if (expired) atomicMax(&out->wait_expired, 1);
+}
+
+__global__ void k_finalize(const double* __restrict__ acc, FinalizeParams fp, DevScalars* __restrict__ out) {
+    if (threadIdx.x != 0 || blockIdx.x != 0) return;
+    finalize_scalars(acc, fp, out);
+}
+
+// ---------------------------------------------------------------- exchanges between ranks through peer memory
+//
+// Ranks on distinct GPUs, one kernel per rank and exchange, each in its own stream. Nothing here may run with two
+// ranks on one GPU: their kernels would wait on one another with no promise of running at the same time.
+
+__device__ __forceinline__ unsigned long long ld_acquire_sys(const unsigned long long* p) {
+    unsigned long long v;
+    asm volatile("ld.acquire.sys.global.u64 %0, [%1];" : "=l"(v) : "l"(p) : "memory");
+    return v;
+}
+__device__ __forceinline__ void st_release_sys(unsigned long long* p, unsigned long long v) {
+    asm volatile("st.release.sys.global.u64 [%0], %1;" ::"l"(p), "l"(v) : "memory");
+}
+__device__ __forceinline__ unsigned long long global_ns() {
+    unsigned long long t;
+    asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
+    return t;
+}
+
+// Waits until `slot` carries exchange number `seq` or later. 0: it does; 1: limit_ns went by; 2: the host raised the
+// abort flag (oxz_comm_abort). Never unbounded.
+__device__ __forceinline__ int mail_wait(const MailSlot* slot, unsigned long long seq, unsigned long long limit_ns,
+                                         const int32_t* abort_flag) {
+    const unsigned long long t0 = global_ns();
+    // the clock decides; the poll count is a second bound should the clock ever stand still (a poll with its share of
+    // the sleeps takes well over 10 ns)
+    const unsigned long long max_polls = limit_ns / 10ull + 4096ull;
+    for (unsigned long long polls = 0; polls < max_polls; polls++) {
+        if (ld_acquire_sys(&slot->seq) >= seq) return 0;
+        if ((polls & 63ull) == 63ull) {
+            if (abort_flag != nullptr && *reinterpret_cast<const volatile int32_t*>(abort_flag) != 0) return 2;
+            if (global_ns() - t0 > limit_ns) return 1;
+            __nanosleep(200);
+        }
+    }
+    return 1;
+}
+
+// Posts this rank's arrival at exchange `seq` in every rank's mailbox (its own included) and waits for every rank's.
+// The payload bytes were written by the block before; the fence makes them, and whatever this rank's earlier kernels
+// stored into peer memory, visible before the number that announces them. Returns the block's verdict: 0 = every
+// rank arrived, else the worst wait result. Thread r serves rank r.
+__device__ __forceinline__ int mail_arrive_and_wait(const MailPeers& mail, int world, int rank, unsigned long long seq,
+                                                    unsigned long long limit_ns, const int32_t* abort_flag) {
+    __shared__ int verdict;
+    const int par = static_cast<int>(seq & 1ull);
+    if (threadIdx.x == 0) verdict = 0;
+    __threadfence_system();
+    __syncthreads();
+    if (static_cast<int>(threadIdx.x) < world) {
+        st_release_sys(&mail.box[threadIdx.x]->slot[par][rank].seq, seq);
+        const int w = mail_wait(&mail.box[rank]->slot[par][threadIdx.x], seq, limit_ns, abort_flag);
+        if (w) atomicMax(&verdict, w);
+    }
+    __syncthreads();
+    return verdict;
+}
+
+__global__ void __launch_bounds__(THREADS) k_gate(MailPeers mail, int world, int rank, unsigned long long seq,
+                                                  const uint8_t* __restrict__ present_in, uint8_t* __restrict__ present_out,
+                                                  uint32_t T, DevScalars* __restrict__ scalars, unsigned long long limit_ns,
+                                                  const int32_t* __restrict__ abort_flag) {
+    const int par = static_cast<int>(seq & 1ull);
+    for (int r = 0; r < world; r++) {
+        unsigned char* dst = mail.box[r]->slot[par][rank].payload;
+        for (uint32_t i = threadIdx.x; i < T; i += THREADS) dst[i] = present_in[i];
+    }
+    const int v = mail_arrive_and_wait(mail, world, rank, seq, limit_ns, abort_flag);
+    if (v) {
+        // some rank never arrived: record it; the kernels after this one still run on whatever the peers hold, the
+        // decision kernel turns the step into a reported failure that changes nothing
+        if (threadIdx.x == 0) atomicMax(&scalars->wait_expired, v);
+        return;
+    }
+    const MailBox* mine = mail.box[rank];
+    for (uint32_t i = threadIdx.x; i < T; i += THREADS) {
+        unsigned char any = 0;
+        for (int r = 0; r < world; r++) any |= mine->slot[par][r].payload[i];
+        present_out[i] = any ? 1 : 0;
+    }
+}
+
+__global__ void __launch_bounds__(THREADS) k_decide(MailPeers mail, int world, int rank, unsigned long long seq,
+                                                    const double* __restrict__ partials, uint32_t slots, double* __restrict__ acc,
+                                                    uint32_t n_extras, int sum_norm, FinalizeParams fp, DevScalars* __restrict__ scalars,
+                                                    unsigned long long limit_ns, const int32_t* __restrict__ abort_flag) {
+    __shared__ double sh[3][THREADS];
+    __shared__ double t[3];
+    block_sum_partials(partials, slots, sh, t);
+    const int par = static_cast<int>(seq & 1ull);
+    const uint32_t n = ACC_EXTRAS + n_extras;
+    // this rank's contribution: its three norm terms, whether one of its waits ran out, its extras (already in acc)
+    if (threadIdx.x < n) {
+        double v;
+        if (threadIdx.x < 3) v = t[threadIdx.x];
+        else if (threadIdx.x == ACC_EXPIRED) v = scalars->wait_expired ? 1.0 : 0.0;
+        else v = acc[threadIdx.x];
+        for (int r = 0; r < world; r++) reinterpret_cast<double*>(mail.box[r]->slot[par][rank].payload)[threadIdx.x] = v;
+    }
+    const int verdict = mail_arrive_and_wait(mail, world, rank, seq, limit_ns, abort_flag);
+    if (verdict) {
+        if (threadIdx.x == 0) {
+            atomicMax(&scalars->wait_expired, verdict);
+            scalars->norm = __longlong_as_double(0x7ff8000000000000ll);
+            scalars->c1 = scalars->c2 = 1.f;
+            scalars->overflow = 0;
+            scalars->skip = 1;
+        }
+        return;
+    }
+    // every rank adds the contributions in rank order: the same bits everywhere
+    if (threadIdx.x < n) {
+        const MailBox* mine = mail.box[rank];
+        double total = 0.0;
+        for (int r = 0; r < world; r++) total += reinterpret_cast<const double*>(mine->slot[par][r].payload)[threadIdx.x];
+        acc[threadIdx.x] = (threadIdx.x < 3 && !sum_norm) ? t[threadIdx.x] : total;
+    }
+    __syncthreads();
+    if (threadIdx.x == 0) finalize_scalars(acc, fp, scalars);
 }
 
 // ---------------------------------------------------------------- AdamW
@@ -941,6 +1124,19 @@ int32_t launch_sumsq_plain(cudaStream_t s, int blocks, const void* grads, int32_
     return check_launch("k_sumsq_plain");
 }
 
+int32_t launch_sumsq_tensors(cudaStream_t s, const LaunchGeom& g, const void* grads, int32_t dt, const TileMap& map,
+                             const uint32_t* tile_meta, const uint8_t* present, float inv_scale, float clamp_hi,
+                             int32_t clamp_on, double* out) {
+    dim3 grid(g.sm_count * 4), block(THREADS);
+    switch (dt) {
+        case OXZ_F32: k_sumsq_tensors<OXZ_F32><<<grid, block, 0, s>>>(grads, map, tile_meta, present, inv_scale, clamp_hi, clamp_on, out); break;
+        case OXZ_BF16: k_sumsq_tensors<OXZ_BF16><<<grid, block, 0, s>>>(grads, map, tile_meta, present, inv_scale, clamp_hi, clamp_on, out); break;
+        case OXZ_F16: k_sumsq_tensors<OXZ_F16><<<grid, block, 0, s>>>(grads, map, tile_meta, present, inv_scale, clamp_hi, clamp_on, out); break;
+        default: return fail(OXZ_ERR_INVALID, "unknown gradient dtype %d", dt);
+    }
+    return check_launch("k_sumsq_tensors");
+}
+
 template <bool CHECK, int WORLD>
 static int32_t launch_pull_w(cudaStream_t s, const LaunchGeom& g, const PeerTable& peers, int32_t world, int staged, int32_t dt,
                              const TileMap& map, const uint32_t* tile_meta, const uint8_t* present, float inv_scale,
@@ -1009,8 +1205,13 @@ static int32_t launch_pull_bulk_t(cudaStream_t s, int blocks, const PeerTable& p
     if (blocks > resident[dev]) blocks = resident[dev];
     // OXZ_PULL_WAIT_LIMIT lowers the bound of the main-loop waits (0: the first wait gives up at once) so that a test can
     // see the run-out path: the kernel records it, still collects its copies in flight and ends normally.
+    // "N@R" lowers it on rank R alone: the other ranks then learn of the run-out through the step's exchange.
     const char* lim = getenv("OXZ_PULL_WAIT_LIMIT");
-    const uint32_t wait_limit = lim ? static_cast<uint32_t>(strtoul(lim, nullptr, 10)) : BULK_SPIN_LIMIT;
+    uint32_t wait_limit = BULK_SPIN_LIMIT;
+    if (lim) {
+        const char* at = strchr(lim, '@');
+        if (!at || static_cast<uint32_t>(strtoul(at + 1, nullptr, 10)) == map.rank) wait_limit = static_cast<uint32_t>(strtoul(lim, nullptr, 10));
+    }
     k_pull_bulk<DT, WORLD, STAGES><<<dim3(blocks), dim3(THREADS), smem, s>>>(peers, map, tile_meta, present, check_present ? 1 : 0, inv_scale, clamp_hi, clamp_on, reduced, partials, scalars, wait_limit);
     return check_launch("k_pull_bulk");
 }
@@ -1040,9 +1241,23 @@ int32_t launch_pull_bulk(cudaStream_t s, const LaunchGeom& g, const PeerTable& p
 #undef OXZ_BULK
 }
 
-int32_t launch_reduce_partials(cudaStream_t s, const double* partials, uint32_t slots, double* acc) {
-    k_reduce_partials<<<1, THREADS, 0, s>>>(partials, slots, acc);
+int32_t launch_reduce_partials(cudaStream_t s, const double* partials, uint32_t slots, double* acc, const DevScalars* scalars) {
+    k_reduce_partials<<<1, THREADS, 0, s>>>(partials, slots, acc, scalars);
     return check_launch("k_reduce_partials");
+}
+
+int32_t launch_gate(cudaStream_t s, const MailPeers& mail, int32_t world, int32_t rank, uint64_t seq, const uint8_t* present_in,
+                    uint8_t* present_out, uint32_t T, DevScalars* scalars, uint64_t limit_ns, const int32_t* abort_flag) {
+    if (T > MAIL_PAYLOAD) return fail(OXZ_ERR_INVALID, "launch_gate: %u flags do not fit a mailbox slot", T);
+    k_gate<<<1, THREADS, 0, s>>>(mail, world, rank, seq, present_in, present_out, T, scalars, limit_ns, abort_flag);
+    return check_launch("k_gate");
+}
+
+int32_t launch_decide(cudaStream_t s, const MailPeers& mail, int32_t world, int32_t rank, uint64_t seq, const double* partials,
+                      uint32_t slots, double* acc, uint32_t n_extras, int32_t sum_norm, const FinalizeParams& fp,
+                      DevScalars* scalars, uint64_t limit_ns, const int32_t* abort_flag) {
+    k_decide<<<1, THREADS, 0, s>>>(mail, world, rank, seq, partials, slots, acc, n_extras, sum_norm, fp, scalars, limit_ns, abort_flag);
+    return check_launch("k_decide");
 }
 
 int32_t launch_finalize(cudaStream_t s, const double* acc, const FinalizeParams& fp, DevScalars* scalars) {

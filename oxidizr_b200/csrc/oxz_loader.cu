@@ -106,6 +106,9 @@ struct Prefetch {
 struct oxz_loader {
     std::vector<Part> parts;
     std::unique_ptr<Mixture> mix;
+    // RowOrder::Shuffled with the permutations supplied by the caller: (epoch, permutation of the loader's rows), at
+    // most two epochs at a time so that a prefetch thread can cross into the next one. Empty: stream order.
+    std::vector<std::pair<uint64_t, std::vector<uint32_t>>> orders;
     std::unique_ptr<Prefetch> pre;
     uint32_t prefetch_depth = 0;
     uint64_t total_rows = 0, seq_len = 0;
@@ -492,6 +495,8 @@ int32_t oxz_loader_set_mixture(oxz_loader* l, const double* weights, uint32_t n_
                                uint64_t rows_per_epoch) {
     return oxz::guarded("oxz_loader_set_mixture", [&]() -> int32_t {
         if (!l || (n_weights && !weights)) return fail(OXZ_ERR_INVALID, "oxz_loader_set_mixture: null argument");
+        if (!l->orders.empty())
+            return fail(OXZ_ERR_UNSUPPORTED, "oxz_loader_set_mixture: the loader reads a caller-supplied row order; a mixture draws its sources' rows in passes of their own. Clear the row order first");
         const uint64_t MAX_ROWS = 1ull << 28;
         if (n_weights != l->parts.size())
             return fail(OXZ_ERR_DATA, "trainer.data.sources sets %u weight(s), and the loader reads %zu source(s). Set one weight per source in trainer.data.sources, and remove the -d flags.",
@@ -616,6 +621,41 @@ int32_t oxz_loader_seek(oxz_loader* l, oxz_data_position pos) {
     });
 }
 
+int32_t oxz_loader_set_row_order(oxz_loader* l, uint64_t epoch, const uint32_t* perm, uint64_t n) {
+    return oxz::guarded("oxz_loader_set_row_order", [&]() -> int32_t {
+        if (!l) return fail(OXZ_ERR_INVALID, "oxz_loader_set_row_order: null loader");
+        if (perm && l->mix)
+            return fail(OXZ_ERR_UNSUPPORTED, "oxz_loader_set_row_order: a mixture draws its sources' rows in passes of their own (src/data/mixture/draw.rs:44-62); a caller-supplied row order serves a loader without weights");
+        if (perm) {
+            if (n != l->layout.num_rows)
+                return fail(OXZ_ERR_DATA, "the row order holds %llu rows and the loader %llu: pass the permutation of the loader's rows",
+                            (unsigned long long)n, (unsigned long long)l->layout.num_rows);
+            OXZ_TRY(oxz_rows_check_permutation(perm, n));
+        }
+        // a prefetch thread reads the orders: it stops, and starts over from the loader's position with the new ones
+        const uint32_t depth = l->pre ? l->prefetch_depth : 0;
+        stop_prefetch(l);
+        if (!perm) {
+            l->orders.clear();
+        } else {
+            bool replaced = false;
+            for (auto& o : l->orders)
+                if (o.first == epoch) {
+                    o.second.assign(perm, perm + n);
+                    replaced = true;
+                }
+            if (!replaced) {
+                if (l->orders.size() >= 2) {  // keep the newest two: drop the lowest epoch
+                    size_t drop = l->orders[0].first < l->orders[1].first ? 0 : 1;
+                    l->orders.erase(l->orders.begin() + drop);
+                }
+                l->orders.emplace_back(epoch, std::vector<uint32_t>(perm, perm + n));
+            }
+        }
+        return depth ? start_prefetch(l, depth) : (int32_t)OXZ_OK;
+    });
+}
+
 // The global rows of this rank's part of the next global batch, where each starts in its file, and the position after
 // the batch. Does not move the loader.
 static int32_t draw_rows(oxz_loader* l, oxz_data_position from, std::vector<uint64_t>& row_ids, std::vector<const uint32_t*>& src,
@@ -637,7 +677,18 @@ static int32_t draw_rows(oxz_loader* l, oxz_data_position from, std::vector<uint
             const unsigned __int128 draw = (unsigned __int128)next.epoch * l->mix->quotas[source] + before;
             row_ids[b] = src_rows.global_row((uint64_t)(draw % src_rows.len));
         } else {
-            row_ids[b] = global_row(l, row_ids[b]);  // loader row -> global row across the ranges
+            uint64_t loader_row = row_ids[b];  // stream order: the row at slot i is row i
+            if (!l->orders.empty()) {
+                // EpochOrder::row (src/data/rows.rs:240-256) with the epoch's permutation as the caller made it
+                const std::vector<uint32_t>* perm = nullptr;
+                for (const auto& o : l->orders)
+                    if (o.first == next.epoch) perm = &o.second;
+                if (!perm)
+                    return fail(OXZ_ERR_DATA, "the next batch reads epoch %llu and the loader holds no row order for it: call oxz_loader_set_row_order with epoch_permutation(num_rows, seed, %llu)",
+                                (unsigned long long)next.epoch, (unsigned long long)next.epoch);
+                loader_row = (*perm)[loader_row];
+            }
+            row_ids[b] = global_row(l, loader_row);  // loader row -> global row across the ranges
         }
         src[b] = row_tokens(l, row_ids[b]);
         if (!src[b])

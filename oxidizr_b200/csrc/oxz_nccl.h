@@ -36,6 +36,10 @@ int32_t comm_check(oxz_comm* c, const char* who);
 // group drains `s`, meets the other rank threads on the host and resumes.
 // Barrier: every rank's work enqueued before it on its own stream has finished when it ends.
 int32_t comm_stream_barrier(oxz_comm* c, int32_t* d_flag, cudaStream_t s);
+// Union over ranks of n per-tensor flags: on the host for a local group (h_inout, in place; *host_known = true), on the
+// device for NCCL (d_in -> d_out on `s`, which also serves as a barrier; *host_known = false).
+int32_t comm_present_union(oxz_comm* c, uint8_t* h_inout, const uint8_t* d_in, uint8_t* d_out, uint64_t n, cudaStream_t s,
+                           bool* host_known);
 // Sum of n device doubles over ranks, in place. h_tmp: n pinned doubles of staging for the local kind.
 int32_t comm_stream_allreduce_f64(oxz_comm* c, double* d_buf, uint32_t n, double* h_tmp, cudaStream_t s);
 // Sum of n device 32-bit words over ranks, in place (merging disjoint slices bit for bit). Blocking for a local group.

@@ -17,7 +17,7 @@ namespace {
 
 constexpr uint32_t MAX_CLUSTERS = OXZ_STATIC_NORM_MAX_CLUSTERS;  // partial-sum slots the array holds
 constexpr size_t PARTIALS_BYTES = size_t(MAX_CLUSTERS) * 3 * sizeof(double);
-constexpr size_t ACC_OFFSET = PARTIALS_BYTES;                    // 3 doubles
+constexpr size_t ACC_OFFSET = PARTIALS_BYTES;                    // the reducer's four doubles
 constexpr size_t SCALARS_OFFSET = ACC_OFFSET + 256;              // one oxz::DevScalars
 constexpr size_t SCRATCH_BYTES = SCALARS_OFFSET + 256;
 constexpr int MAX_DEVICES = 64;
@@ -88,11 +88,11 @@ extern "C" int32_t oxz_grad_norm_static(const void* device_grads, int32_t dtype,
     const bool scaled = !std::isnan(loss_scale) && loss_scale != 0.0;
     const int clamp_on = std::isnan(max_grad_value) ? 0 : 1;
     // Nothing in the scratch has to start at zero: each stage overwrites exactly what the next one reads (every
-    // cluster stores its slot, the reducer reads `use` slots and stores all three sums, the last kernel stores the
+    // cluster stores its slot, the reducer reads `use` slots and stores all four of its doubles, the last kernel stores the
     // whole record), so what an earlier call left behind is never read.
     OXZ_TRY(launch_sumsq_plain(s, (int)use * 4, device_grads, dtype, n, scaled ? (float)(1.0 / loss_scale) : 1.0f,
                                clamp_on ? (float)max_grad_value : 0.f, clamp_on, partials));
-    OXZ_TRY(launch_reduce_partials(s, partials, use, acc));
+    OXZ_TRY(launch_reduce_partials(s, partials, use, acc, nullptr));
     FinalizeParams fp{};
     fp.max_grad_norm = 1.7976931348623157e308;  // a pure measurement: nothing is rescaled
     OXZ_TRY(launch_finalize(s, acc, fp, scalars));

@@ -32,9 +32,9 @@ ncclDataType_t nccl_dtype(int32_t dt) { return dt == OXZ_F32 ? ncclFloat32 : dt 
 
 struct PeerBlob {
     uint64_t pid;
-    uint64_t grads_ptr, work_ptr;
-    int32_t device, pad;
-    cudaIpcMemHandle_t grads_handle, work_handle;
+    uint64_t grads_ptr, work_ptr, mail_ptr;
+    int32_t device, has_mail;
+    cudaIpcMemHandle_t grads_handle, work_handle, mail_handle;
 };
 
 // Exchanges the gradient and weight buffers of every rank and maps the peers' copies into this process.
@@ -49,13 +49,21 @@ int32_t exchange_peers(oxz_plan* p, oxz_comm* c) {
     mine.device = p->device;
     OXZ_CUDA(cudaIpcGetMemHandle(&mine.grads_handle, p->grads));
     OXZ_CUDA(cudaIpcGetMemHandle(&mine.work_handle, p->work));
+    mine.has_mail = p->mail ? 1 : 0;
+    mine.mail_ptr = (uint64_t)p->mail;
+    if (p->mail) OXZ_CUDA(cudaIpcGetMemHandle(&mine.mail_handle, p->mail));
     const int W = p->cw;
     std::vector<PeerBlob> all(W);
     OXZ_TRY(comm_allgather_host(c, &mine, all.data(), sizeof(PeerBlob), p->stream));
+    // the mailbox serves only when every rank made one (the same environment and tensor count everywhere)
+    bool all_mail = p->mail != nullptr;
+    for (int r = 0; r < W; r++) all_mail = all_mail && all[r].has_mail != 0;
+    p->use_mail = all_mail;
     for (int r = 0; r < W; r++) {
         if (r == p->cr) {
             p->peers.grads[r] = p->grads;
             p->peers.work[r] = p->work;
+            p->mail_peers.box[r] = p->mail;
             continue;
         }
         const PeerBlob& b = all[r];
@@ -70,6 +78,7 @@ int32_t exchange_peers(oxz_plan* p, oxz_comm* c) {
             }
             p->peers.grads[r] = (const void*)b.grads_ptr;
             p->peers.work[r] = (void*)b.work_ptr;
+            if (all_mail) p->mail_peers.box[r] = (MailBox*)b.mail_ptr;
         } else {
             void *g = nullptr, *w = nullptr;
             OXZ_CUDA(cudaIpcOpenMemHandle(&g, b.grads_handle, cudaIpcMemLazyEnablePeerAccess));
@@ -78,6 +87,12 @@ int32_t exchange_peers(oxz_plan* p, oxz_comm* c) {
             p->ipc_opened.push_back(w);
             p->peers.grads[r] = g;
             p->peers.work[r] = w;
+            if (all_mail) {
+                void* mb = nullptr;
+                OXZ_CUDA(cudaIpcOpenMemHandle(&mb, b.mail_handle, cudaIpcMemLazyEnablePeerAccess));
+                p->ipc_opened.push_back(mb);
+                p->mail_peers.box[r] = (MailBox*)mb;
+            }
         }
     }
     return OXZ_OK;
@@ -199,9 +214,10 @@ int32_t oxz_plan_destroy(oxz_plan* p) {
             if (p->work && p->work != (void*)p->master) cudaFree(p->work);
             for (void* q : {(void*)p->grads, (void*)p->master, (void*)p->exp_avg, (void*)p->exp_avg_sq, p->reduced,
                             (void*)p->d_tile_meta, (void*)p->d_present, (void*)p->d_offsets, (void*)p->d_numel,
-                            (void*)p->d_src, (void*)p->d_partials, (void*)p->d_acc, (void*)p->d_scalars})
+                            (void*)p->d_src, (void*)p->d_partials, (void*)p->d_acc, (void*)p->d_scalars, (void*)p->d_present_in,
+                            (void*)p->mail})
                 if (q) cudaFree(q);
-            for (void* q : {(void*)p->h_scalars, (void*)p->h_acc, (void*)p->h_extras, (void*)p->h_present, (void*)p->h_src})
+            for (void* q : {(void*)p->h_scalars, (void*)p->h_acc, (void*)p->h_extras, (void*)p->h_present, (void*)p->h_union, (void*)p->h_src})
                 if (q) cudaFreeHost(q);
             if (p->grads_alt) cudaFree(p->grads_alt);
             if (p->upload_stream) cudaStreamDestroy(p->upload_stream);
@@ -271,6 +287,10 @@ int32_t oxz_state_alloc(oxz_plan* p, oxz_comm* comm) {
         OXZ_CUDA(cudaMemcpy(p->d_tile_meta, p->tile_meta.data(), p->total_tiles * 4, cudaMemcpyHostToDevice));
         OXZ_CUDA(zalloc((void**)&p->d_present, p->T));
         if (p->T) OXZ_CUDA(cudaMemset(p->d_present, 1, p->T));
+        if (p->cw > 1) {
+            OXZ_CUDA(zalloc((void**)&p->d_present_in, p->T));
+            if (p->T) OXZ_CUDA(cudaMemset(p->d_present_in, 1, p->T));
+        }
         OXZ_CUDA(zalloc((void**)&p->d_offsets, p->T * 8));
         OXZ_CUDA(zalloc((void**)&p->d_numel, p->T * 8));
         if (p->T) {
@@ -279,15 +299,30 @@ int32_t oxz_state_alloc(oxz_plan* p, oxz_comm* comm) {
         }
         OXZ_CUDA(zalloc((void**)&p->d_src, p->T * 8));
         OXZ_CUDA(zalloc((void**)&p->d_partials, (size_t)norm_partial_slots(p->geom) * 3 * 8 * MAX_PIPE));
-        OXZ_CUDA(zalloc((void**)&p->d_acc, (3 + MAX_EXTRAS) * 8));
+        OXZ_CUDA(zalloc((void**)&p->d_acc, ACC_DOUBLES * 8));
         OXZ_CUDA(zalloc((void**)&p->d_scalars, sizeof(DevScalars)));
         OXZ_CUDA(cudaMallocHost((void**)&p->h_scalars, sizeof(DevScalars)));
-        OXZ_CUDA(cudaMallocHost((void**)&p->h_acc, (3 + MAX_EXTRAS) * 8));
+        OXZ_CUDA(cudaMallocHost((void**)&p->h_acc, ACC_DOUBLES * 8));
         OXZ_CUDA(cudaMallocHost((void**)&p->h_extras, MAX_EXTRAS * 8));
         OXZ_CUDA(cudaMallocHost((void**)&p->h_present, p->T ? p->T : 1));
+        OXZ_CUDA(cudaMallocHost((void**)&p->h_union, p->T ? p->T : 1));
+        memset(p->h_union, 1, p->T ? p->T : 1);
         OXZ_CUDA(cudaMallocHost((void**)&p->h_src, (p->T ? p->T : 1) * 8));
         memset(p->h_present, 1, p->T ? p->T : 1);
         OXZ_CUDA(cudaEventCreateWithFlags(&p->done, cudaEventDisableTiming));
+        // Exchanges between ranks through peer memory instead of small NCCL collectives: for the modes whose kernels
+        // already address peer memory, behind an NCCL communicator (its ranks sit on distinct GPUs, so the waiting
+        // kernels of different ranks never share one), when the flags of all tensors fit a slot. OXZ_MAIL=0 keeps NCCL.
+        const char* mail_env = getenv("OXZ_MAIL");
+        const bool want_mail = (p->mode == OXZ_SYNC_P2P || p->mode == OXZ_SYNC_REPLICATED) && p->cw > 1 && comm->kind == 0 &&
+                               p->T <= MAIL_PAYLOAD && !(mail_env && atoi(mail_env) == 0);
+        if (want_mail) {
+            static_assert(sizeof(MailBox) <= (2u << 20), "a mailbox fits its allocation");
+            OXZ_CUDA(zalloc((void**)&p->mail, 2u << 20));  // an allocation of its own page size, shared with the peers
+            const char* lim = getenv("OXZ_MAIL_TIMEOUT_MS");
+            const double ms = lim ? atof(lim) : 30000.0;
+            p->mail_limit_ns = (uint64_t)((ms > 0.0 ? ms : 30000.0) * 1e6);
+        }
         OXZ_CUDA(cudaDeviceSynchronize());
         p->peers.grads[0] = p->grads;
         p->peers.work[0] = p->work;
@@ -500,20 +535,44 @@ namespace {
 
 bool same_or_both_nan(double a, double b) { return a == b || (std::isnan(a) && std::isnan(b)); }
 
-// Records which tensors have a gradient this step; returns whether any is absent.
-int32_t update_present(oxz_plan* p, const uint8_t* present, cudaStream_t s, bool* some_absent) {
-    bool changed = false;
+// Records which tensors have a gradient this step. With several ranks the flags the kernels read are the UNION over
+// ranks: a tensor is left alone only when no rank produced a gradient for it (src/dp/reduce.rs:20); a rank without one
+// contributes the zeros its gradient buffer holds there. A local group forms the union on the host; an NCCL group on
+// the device, either here (a byte-wise maximum, which is also a barrier on `s`) or, when `by_gate`, in the opening
+// gate kernel the caller launches next. *some_absent: whether the kernels must look the flags up. Where the host
+// does not see the union it answers for this rank's own flags, which can only err towards looking them up.
+int32_t sync_present(oxz_plan* p, oxz_comm* comm, const uint8_t* present, cudaStream_t s, bool by_gate, bool* some_absent) {
+    bool changed = false, own_absent = false;
     for (uint64_t i = 0; i < p->T; i++) {
         const uint8_t v = present ? (present[i] ? 1 : 0) : 1;
         if (p->h_present[i] != v) {
             p->h_present[i] = v;
             changed = true;
         }
+        own_absent |= v == 0;
     }
-    if (changed) OXZ_CUDA(cudaMemcpyAsync(p->d_present, p->h_present, p->T, cudaMemcpyHostToDevice, s));
-    *some_absent = false;
-    for (uint64_t i = 0; i < p->T; i++) *some_absent |= p->h_present[i] == 0;
+    *some_absent = own_absent;
+    if (p->cw == 1) {
+        if (changed) OXZ_CUDA(cudaMemcpyAsync(p->d_present, p->h_present, p->T, cudaMemcpyHostToDevice, s));
+        return OXZ_OK;
+    }
+    if (changed) OXZ_CUDA(cudaMemcpyAsync(p->d_present_in, p->h_present, p->T, cudaMemcpyHostToDevice, s));
+    if (comm->kind != 1 && by_gate) return OXZ_OK;
+    memcpy(p->h_union, p->h_present, p->T);
+    bool host_known = false;
+    OXZ_TRY(comm_present_union(comm, p->h_union, p->d_present_in, p->d_present, p->T, s, &host_known));
+    if (host_known) {
+        if (p->T) OXZ_CUDA(cudaMemcpyAsync(p->d_present, p->h_union, p->T, cudaMemcpyHostToDevice, s));
+        *some_absent = false;
+        for (uint64_t i = 0; i < p->T; i++) *some_absent |= p->h_union[i] == 0;
+    }
     return OXZ_OK;
+}
+
+// An exchange through the mailboxes used as a barrier; with `carry_present` it also forms the union of the flags.
+int32_t mail_gate(oxz_plan* p, oxz_comm* comm, cudaStream_t s, bool carry_present) {
+    return launch_gate(s, p->mail_peers, p->cw, p->cr, ++p->mail_seq, p->d_present_in, p->d_present,
+                       carry_present ? (uint32_t)p->T : 0u, p->d_scalars, p->mail_limit_ns, comm->h_abort_flag);
 }
 
 // The norm pass (fused with the pull over ranks in P2P mode) over buckets [b0, b1) into partial-sum group `group`.
@@ -584,13 +643,17 @@ int32_t oxz_step_async(oxz_plan* p, oxz_comm* comm, const oxz_hyper* h, const ui
 
         // which tensors have a gradient this step
         bool some_absent = false;
+        // the opening gate of the pulling modes carries the flags itself when the ranks meet through the mailboxes
+        const bool gate_carries = p->use_mail;
+        // with NCCL the union of the flags, formed on `s` just below, is a barrier over the ranks' streams already
+        const bool flags_were_barrier = p->cw > 1 && comm->kind == 0 && !gate_carries && p->early_groups == 0 && p->T > 0;
         if (p->early_groups == 0) {
-            OXZ_TRY(update_present(p, present, s, &some_absent));
+            OXZ_TRY(sync_present(p, comm, present, s, gate_carries, &some_absent));
         } else {
             for (uint64_t i = 0; i < p->T; i++) {
                 const uint8_t v = present ? (present[i] ? 1 : 0) : 1;
                 if (p->h_present[i] != v) return fail(OXZ_ERR_INVALID, "oxz_step_async: `present` differs from the one oxz_grads_ready_async was given for this step");
-                some_absent |= v == 0;
+                some_absent |= (p->cw > 1 && comm->kind == 1 ? p->h_union[i] : v) == 0;
             }
             if (!same_or_both_nan(h->loss_scale, p->early_scale) || !same_or_both_nan(h->max_grad_value, p->early_clamp))
                 return fail(OXZ_ERR_INVALID, "oxz_step_async: loss_scale or max_grad_value differs from the one oxz_grads_ready_async was given for this step");
@@ -648,7 +711,10 @@ int32_t oxz_step_async(oxz_plan* p, oxz_comm* comm, const oxz_hyper* h, const ui
             bool any_left = false;
             for (uint64_t b = 0; b < p->n_buckets; b++) any_left |= !(groups && p->early_done[b]);
             // every rank's remaining gradients must be complete before anyone pulls them
-            if (pulls && any_left) OXZ_TRY(comm_stream_barrier(comm, bar, s));
+            if (pulls && any_left) {
+                if (p->use_mail) OXZ_TRY(mail_gate(p, comm, s, true));
+                else if (!flags_were_barrier) OXZ_TRY(comm_stream_barrier(comm, bar, s));
+            }
             OXZ_CUDA(mark(1));
             for (uint64_t b = 0; b < p->n_buckets;) {
                 if (groups && p->early_done[b]) { b++; continue; }
@@ -667,7 +733,7 @@ int32_t oxz_step_async(oxz_plan* p, oxz_comm* comm, const oxz_hyper* h, const ui
             }
         } else if (p->mode == OXZ_SYNC_COPY) {
             // every rank's gradients must be complete before anyone copies them
-            OXZ_TRY(comm_stream_barrier(comm, bar, s));
+            if (!flags_were_barrier) OXZ_TRY(comm_stream_barrier(comm, bar, s));
             OXZ_CUDA(mark(1));
             OXZ_CUDA(cudaEventRecord(p->ev_go, s));
             const size_t gs = dtype_size(p->gdt);
@@ -715,24 +781,30 @@ int32_t oxz_step_async(oxz_plan* p, oxz_comm* comm, const oxz_hyper* h, const ui
             gsrc = p->reduced;
         }
         OXZ_CUDA(mark(2));
-        OXZ_TRY(launch_reduce_partials(s, p->d_partials, slots, p->d_acc));
         if (p->cw > 1) {
             for (uint32_t i = 0; i < n_extras; i++) p->h_extras[i] = extras[i];
-            if (n_extras) OXZ_CUDA(cudaMemcpyAsync(p->d_acc + 3, p->h_extras, n_extras * 8, cudaMemcpyHostToDevice, s));
-            // The one all-reduce of the step: {sum of squares, inf count, NaN count, extras...}. In P2P mode its end
-            // also tells every rank that all peers have finished reading its gradient buffer. A full replica has
-            // measured every element itself: only the extras are summed, and a barrier stands in when there are none.
-            if (!replicated) OXZ_TRY(comm_stream_allreduce_f64(comm, p->d_acc, 3 + n_extras, p->h_acc, s));
-            else if (n_extras) OXZ_TRY(comm_stream_allreduce_f64(comm, p->d_acc + 3, n_extras, p->h_acc + 3, s));
-            else OXZ_TRY(comm_stream_barrier(comm, bar, s));
+            if (n_extras) OXZ_CUDA(cudaMemcpyAsync(p->d_acc + ACC_EXTRAS, p->h_extras, n_extras * 8, cudaMemcpyHostToDevice, s));
         }
-        OXZ_TRY(launch_finalize(s, p->d_acc, fp, p->d_scalars));
+        // The one data exchange of the step: {sum of squares, inf count, NaN count, a wait ran out, extras...}. In P2P
+        // mode its end also tells every rank that all peers have finished reading its gradient buffer. A full replica
+        // has measured every element itself: only the run-out flag and the extras are summed.
+        if (p->cw > 1 && p->use_mail) {
+            OXZ_TRY(launch_decide(s, p->mail_peers, p->cw, p->cr, ++p->mail_seq, p->d_partials, slots, p->d_acc, n_extras,
+                                  replicated ? 0 : 1, fp, p->d_scalars, p->mail_limit_ns, comm->h_abort_flag));
+        } else {
+            OXZ_TRY(launch_reduce_partials(s, p->d_partials, slots, p->d_acc, p->d_scalars));
+            if (p->cw > 1) {
+                if (!replicated) OXZ_TRY(comm_stream_allreduce_f64(comm, p->d_acc, ACC_EXTRAS + n_extras, p->h_acc, s));
+                else OXZ_TRY(comm_stream_allreduce_f64(comm, p->d_acc + ACC_EXPIRED, 1 + n_extras, p->h_acc + ACC_EXPIRED, s));
+            }
+            OXZ_TRY(launch_finalize(s, p->d_acc, fp, p->d_scalars));
+        }
         OXZ_CUDA(cudaMemcpyAsync(p->h_scalars, p->d_scalars, sizeof(DevScalars), cudaMemcpyDeviceToHost, s));
         // the pull kernels (also those of buckets reduced ahead of the next step) raise this flag; it was just copied out
         // with the rest and starts the next step cleared
         OXZ_CUDA(cudaMemsetAsync(&p->d_scalars->wait_expired, 0, sizeof(int32_t), s));
         if (p->cw > 1 && n_extras)
-            OXZ_CUDA(cudaMemcpyAsync(p->h_acc, p->d_acc, (3 + n_extras) * 8, cudaMemcpyDeviceToHost, s));
+            OXZ_CUDA(cudaMemcpyAsync(p->h_acc, p->d_acc, (ACC_EXTRAS + n_extras) * 8, cudaMemcpyDeviceToHost, s));
 
         OXZ_CUDA(mark(3));
         const bool separate_work = p->work != (void*)p->master;
@@ -787,7 +859,8 @@ int32_t oxz_step_async(oxz_plan* p, oxz_comm* comm, const oxz_hyper* h, const ui
             if (rc != ncclSuccess) return nccl_fail("the weight all-gather", rc);
         } else if (p->mode == OXZ_SYNC_P2P) {
             // every rank's stores into this rank's weight buffer must have landed before the step is reported done
-            OXZ_TRY(comm_stream_barrier(comm, bar, s));
+            if (p->use_mail) OXZ_TRY(mail_gate(p, comm, s, false));
+            else OXZ_TRY(comm_stream_barrier(comm, bar, s));
         }
         OXZ_CUDA(mark(5));
         if (p->double_buffered) OXZ_CUDA(cudaEventRecord(p->ev_last_read[p->cur_grads], s));
@@ -833,14 +906,14 @@ int32_t oxz_grads_ready_async(oxz_plan* p, oxz_comm* comm, const oxz_hyper* h, c
             // the side stream must not run ahead of the previous step's update, which read the same buffers
             OXZ_CUDA(cudaEventRecord(p->ev_early, p->stream));
             OXZ_CUDA(cudaStreamWaitEvent(es, p->ev_early, 0));
-            OXZ_TRY(update_present(p, present, es, &some_absent));
+            OXZ_TRY(sync_present(p, comm, present, es, false, &some_absent));
         } else {
             if (!same_or_both_nan(h->loss_scale, p->early_scale) || !same_or_both_nan(h->max_grad_value, p->early_clamp))
                 return fail(OXZ_ERR_INVALID, "oxz_grads_ready_async: loss_scale or max_grad_value changed within one step");
             for (uint64_t i = 0; i < p->T; i++) {
                 const uint8_t v = present ? (present[i] ? 1 : 0) : 1;
                 if (p->h_present[i] != v) return fail(OXZ_ERR_INVALID, "oxz_grads_ready_async: `present` changed within one step");
-                some_absent |= v == 0;
+                some_absent |= (p->cw > 1 && comm->kind == 1 ? p->h_union[i] : v) == 0;
             }
         }
         for (uint64_t b = first_bucket; b < first_bucket + n_buckets; b++)
@@ -882,13 +955,16 @@ int32_t oxz_step_wait(oxz_plan* p, oxz_step_result* res) {
         if (p->comm && p->comm->aborted.load()) return fail(OXZ_ERR_ABORTED, "oxz_step_wait: the communicator was aborted during the step");
         if (e != cudaSuccess) return fail(OXZ_ERR_CUDA, "oxz_step_wait: %s", cudaGetErrorString(e));
         const DevScalars& d = *p->h_scalars;
+        if (d.wait_expired == 2)
+            return fail(OXZ_ERR_ABORTED, "oxz_step_wait: the communicator was aborted while a kernel of the step waited for the other ranks; nothing was updated");
         if (d.wait_expired)
-            return fail(OXZ_ERR_TIMEOUT, "oxz_step_wait: a bounded wait inside the pull kernel ran out before a peer's data arrived; the step's result is not valid");
+            return fail(OXZ_ERR_TIMEOUT, "oxz_step_wait: a bounded wait inside a kernel of the step ran out, on this rank or another, before a peer's "
+                                         "data or arrival was seen; nothing was updated on any rank that reports this. Abort the group");
         const oxz_hyper& h = p->inflight_hyper;
         const bool applied = !d.skip;
         if (applied) p->timestep += 1;
         if (p->cw > 1)
-            for (uint32_t i = 0; i < p->inflight_n_extras; i++) p->inflight_extras[i] = p->h_acc[3 + i];
+            for (uint32_t i = 0; i < p->inflight_n_extras; i++) p->inflight_extras[i] = p->h_acc[ACC_EXTRAS + i];
         if (res) {
             res->grad_norm = d.norm;
             res->overflow = d.overflow;
@@ -922,6 +998,118 @@ int32_t oxz_plan_last_pull_kernel(const oxz_plan* p, int32_t* kind) {
         if (!p || !kind) return fail(OXZ_ERR_INVALID, "oxz_plan_last_pull_kernel: null argument");
         *kind = p->last_pull_kernel;
         return OXZ_OK;
+    });
+}
+
+int32_t oxz_plan_exchange_kind(const oxz_plan* p, int32_t* kind) {
+    return oxz::guarded("oxz_plan_exchange_kind", [&]() -> int32_t {
+        if (!p || !kind) return fail(OXZ_ERR_INVALID, "oxz_plan_exchange_kind: null argument");
+        if (!p->allocated) return fail(OXZ_ERR_STATE, "oxz_plan_exchange_kind: call oxz_state_alloc first");
+        *kind = p->cw <= 1 ? OXZ_EXCHANGE_NONE : p->use_mail ? OXZ_EXCHANGE_MAILBOX : OXZ_EXCHANGE_COMM;
+        return OXZ_OK;
+    });
+}
+
+int32_t oxz_selftest_bounded_wait(int32_t device, uint32_t limit_ms, int32_t* outcome) {
+    return oxz::guarded("oxz_selftest_bounded_wait", [&]() -> int32_t {
+        if (!outcome) return fail(OXZ_ERR_INVALID, "oxz_selftest_bounded_wait: null argument");
+        if (limit_ms == 0 || limit_ms > 2000) return fail(OXZ_ERR_INVALID, "oxz_selftest_bounded_wait: limit_ms %u is outside [1, 2000]", limit_ms);
+        OXZ_CUDA(cudaSetDevice(device));
+        // two mailboxes in this device's memory: "mine", and one standing for a second rank that never runs, so nothing
+        // ever posts that rank's arrival in mine and the wait for it runs into its limit
+        MailBox* boxes = nullptr;
+        DevScalars* d_sc = nullptr;
+        DevScalars h_sc{};
+        OXZ_CUDA(cudaMalloc((void**)&boxes, 2 * sizeof(MailBox)));
+        cudaError_t e = cudaMalloc((void**)&d_sc, sizeof(DevScalars));
+        if (e != cudaSuccess) {
+            cudaFree(boxes);
+            return fail(OXZ_ERR_CUDA, "oxz_selftest_bounded_wait: %s", cudaGetErrorString(e));
+        }
+        auto finish = [&](int32_t status) {
+            cudaFree(boxes);
+            cudaFree(d_sc);
+            return status;
+        };
+        if (cudaMemset(boxes, 0, 2 * sizeof(MailBox)) != cudaSuccess || cudaMemset(d_sc, 0, sizeof(DevScalars)) != cudaSuccess)
+            return finish(fail(OXZ_ERR_CUDA, "oxz_selftest_bounded_wait: cudaMemset failed"));
+        MailPeers two{};
+        two.box[0] = boxes;
+        two.box[1] = boxes + 1;
+        int32_t st = launch_gate(nullptr, two, 2, 0, 1, nullptr, nullptr, 0, d_sc, (uint64_t)limit_ms * 1000000ull, nullptr);
+        if (st != OXZ_OK) return finish(st);
+        if (cudaMemcpy(&h_sc, d_sc, sizeof(DevScalars), cudaMemcpyDeviceToHost) != cudaSuccess)
+            return finish(fail(OXZ_ERR_CUDA, "oxz_selftest_bounded_wait: the context did not survive the wait that ran out"));
+        *outcome = h_sc.wait_expired;
+        if (h_sc.wait_expired != 1) return finish(fail(OXZ_ERR_STATE, "oxz_selftest_bounded_wait: the wait recorded %d, not a run-out", h_sc.wait_expired));
+        // the same kernel alone: its own arrival is all it waits for
+        if (cudaMemset(d_sc, 0, sizeof(DevScalars)) != cudaSuccess) return finish(fail(OXZ_ERR_CUDA, "oxz_selftest_bounded_wait: cudaMemset failed"));
+        MailPeers one{};
+        one.box[0] = boxes;
+        st = launch_gate(nullptr, one, 1, 0, 2, nullptr, nullptr, 0, d_sc, (uint64_t)limit_ms * 1000000ull, nullptr);
+        if (st != OXZ_OK) return finish(st);
+        if (cudaMemcpy(&h_sc, d_sc, sizeof(DevScalars), cudaMemcpyDeviceToHost) != cudaSuccess)
+            return finish(fail(OXZ_ERR_CUDA, "oxz_selftest_bounded_wait: the second launch failed"));
+        if (h_sc.wait_expired != 0) return finish(fail(OXZ_ERR_STATE, "oxz_selftest_bounded_wait: a rank alone did not pass its own gate"));
+        return finish(OXZ_OK);
+    });
+}
+
+int32_t oxz_grad_norms_per_tensor(oxz_plan* p, oxz_comm* comm, double loss_scale, double max_grad_value, double* norms) {
+    return oxz::guarded("oxz_grad_norms_per_tensor", [&]() -> int32_t {
+        if (!p || !norms) return fail(OXZ_ERR_INVALID, "oxz_grad_norms_per_tensor: null argument");
+        if (!p->allocated) return fail(OXZ_ERR_STATE, "oxz_grad_norms_per_tensor: the plan has no device state. Call oxz_state_alloc first");
+        if (p->inflight) return fail(OXZ_ERR_STATE, "oxz_grad_norms_per_tensor: a step is in flight. Call oxz_step_wait first");
+        if (p->early_groups) return fail(OXZ_ERR_STATE, "oxz_grad_norms_per_tensor: buckets of the next step were already handed in");
+        if (!std::isnan(max_grad_value) && !(std::isfinite(max_grad_value) && max_grad_value > 0.0))
+            return fail(OXZ_ERR_INVALID, "trainer.max_grad_value is %g: it must be a finite positive number. Set a positive value, or remove the key to disable per-element clipping.", max_grad_value);
+        if (p->cw > 1) {
+            OXZ_TRY(comm_check(comm, "oxz_grad_norms_per_tensor"));
+            if (comm != p->comm) return fail(OXZ_ERR_INVALID, "oxz_grad_norms_per_tensor: this is not the communicator the state was allocated with");
+        }
+        if (p->T == 0) return OXZ_OK;
+        OXZ_CUDA(cudaSetDevice(p->device));
+        cudaStream_t s = p->stream;
+        const size_t n = 3 * (size_t)p->T;
+        double* d_out = nullptr;
+        double* h_out = nullptr;
+        OXZ_CUDA(cudaMalloc((void**)&d_out, n * 8));
+        cudaError_t e = cudaMallocHost((void**)&h_out, n * 8);
+        if (e != cudaSuccess) {
+            cudaFree(d_out);
+            return fail(OXZ_ERR_CUDA, "oxz_grad_norms_per_tensor: %s", cudaGetErrorString(e));
+        }
+        auto run = [&]() -> int32_t {
+            OXZ_CUDA(cudaMemsetAsync(d_out, 0, n * 8, s));
+            const bool scaled = !std::isnan(loss_scale) && loss_scale != 0.0;
+            const int32_t clamp_on = std::isnan(max_grad_value) ? 0 : 1;
+            // with several ranks the summed gradients of the tiles this rank owns are what the step's reduction left
+            // (f32 for the pulling and copying modes, the gradients' own type after an NCCL reduce-scatter)
+            const bool summed = p->cw > 1;
+            const void* src = summed ? p->reduced : p->grads;
+            const int32_t dt = !summed ? p->gdt : (p->mode == OXZ_SYNC_NCCL ? p->gdt : OXZ_F32);
+            OXZ_TRY(launch_sumsq_tensors(s, p->geom, src, dt, tile_map(p), p->d_tile_meta, p->d_present,
+                                         scaled ? (float)(1.0 / loss_scale) : 1.0f, clamp_on ? (float)max_grad_value : 0.f,
+                                         clamp_on, d_out));
+            // ranks own disjoint tiles: the sum over ranks completes every tensor (a full replica already holds all)
+            if (p->cw > 1 && p->mode != OXZ_SYNC_REPLICATED) OXZ_TRY(comm_stream_allreduce_f64(comm, d_out, (uint32_t)n, h_out, s));
+            OXZ_CUDA(cudaMemcpyAsync(h_out, d_out, n * 8, cudaMemcpyDeviceToHost, s));
+            OXZ_CUDA(cudaStreamSynchronize(s));
+            // which tensors some rank had a gradient for: the flags the last step's kernels read
+            std::vector<uint8_t> flags(p->T);
+            OXZ_CUDA(cudaMemcpy(flags.data(), p->d_present, p->T, cudaMemcpyDeviceToHost));
+            for (uint64_t i = 0; i < p->T; i++) {
+                if (!flags[i]) norms[i] = -1.0;
+                else if (h_out[3 * i + 2] > 0.0) norms[i] = std::nan("");
+                else if (h_out[3 * i + 1] > 0.0) norms[i] = INFINITY;
+                else norms[i] = std::sqrt(h_out[3 * i]);
+            }
+            return OXZ_OK;
+        };
+        const int32_t st = run();
+        cudaFreeHost(h_out);
+        cudaFree(d_out);
+        return st;
     });
 }
 
@@ -996,7 +1184,7 @@ int32_t oxz_grad_norm(const void* device_grads, int32_t dtype, uint64_t n, doubl
             sc.blocks = g.norm_blocks;
             sc.slots = norm_partial_slots(g);
             OXZ_CUDA(cudaMalloc((void**)&sc.d_partials, (size_t)norm_partial_slots(g) * 3 * 8));
-            OXZ_CUDA(cudaMalloc((void**)&sc.d_acc, 3 * 8));
+            OXZ_CUDA(cudaMalloc((void**)&sc.d_acc, ACC_DOUBLES * 8));
             OXZ_CUDA(cudaMalloc((void**)&sc.d_scalars, sizeof(DevScalars)));
             OXZ_CUDA(cudaMallocHost((void**)&sc.h_scalars, sizeof(DevScalars)));
         }
@@ -1005,7 +1193,7 @@ int32_t oxz_grad_norm(const void* device_grads, int32_t dtype, uint64_t n, doubl
         const int clamp_on = std::isnan(max_grad_value) ? 0 : 1;
         OXZ_TRY(launch_sumsq_plain(s, sc.blocks, device_grads, dtype, n, scaled ? (float)(1.0 / loss_scale) : 1.0f,
                                    clamp_on ? (float)max_grad_value : 0.f, clamp_on, sc.d_partials));
-        OXZ_TRY(launch_reduce_partials(s, sc.d_partials, sc.slots, sc.d_acc));
+        OXZ_TRY(launch_reduce_partials(s, sc.d_partials, sc.slots, sc.d_acc, nullptr));
         FinalizeParams fp{};
         fp.max_grad_norm = 1.7976931348623157e308;  // a pure measurement: nothing is rescaled
         OXZ_TRY(launch_finalize(s, sc.d_acc, fp, sc.d_scalars));

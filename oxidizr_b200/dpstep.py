@@ -332,9 +332,18 @@ class RowLayout:
     def position_after_steps(self, steps: int, grad_accum: int) -> DataPosition:
         return self.advance(DataPosition(), steps * grad_accum)
 
+    def batch_epoch(self, pos: DataPosition) -> int:
+        """The epoch whose row order the batch drawn at `pos` reads (it rolls over when fewer rows than a global
+        batch are left, src/data/rows.rs:153-165)."""
+        v = C.c_uint64()
+        check(lib().oxz_rows_batch_epoch(C.byref(self._c), ffi.DataPositionC(pos.epoch, pos.row), C.byref(v)))
+        return v.value
+
     def next_window(self, pos: DataPosition, rank: int, seq_len: int, tokens: np.ndarray | None = None,
-                    first_row: int = 0):
-        """One rank's rows of the next global batch in stream order: (rows, inputs, targets, next position)."""
+                    first_row: int = 0, row_order: tuple[int, np.ndarray] | None = None):
+        """One rank's rows of the next global batch: (rows, inputs, targets, next position). Stream order, or with
+        row_order = (epoch, permutation) the reference's shuffled order with the permutation the caller made
+        (EpochOrder::row, src/data/rows.rs:240-256)."""
         B = self.rank_batch_size
         rows = np.empty(B, dtype=np.uint64)
         nxt = ffi.DataPositionC()
@@ -347,6 +356,13 @@ class RowLayout:
             tok_p = tokens.ctypes.data_as(C.POINTER(C.c_uint32))
             n_tok = tokens.size
             in_p, tg_p = inputs.ctypes.data_as(ffi.i64p), targets.ctypes.data_as(ffi.i64p)
+        if row_order is not None:
+            epoch, perm = row_order
+            perm = np.ascontiguousarray(perm, dtype=np.uint32)
+            check(lib().oxz_rows_next_window_ordered(C.byref(self._c), ffi.DataPositionC(pos.epoch, pos.row), rank, seq_len,
+                                                     first_row, tok_p, n_tok, epoch, perm.ctypes.data_as(C.POINTER(C.c_uint32)),
+                                                     perm.size, rows.ctypes.data_as(ffi.u64p), in_p, tg_p, C.byref(nxt)))
+            return rows, inputs, targets, DataPosition(nxt.epoch, nxt.row)
         check(lib().oxz_rows_next_window(C.byref(self._c), ffi.DataPositionC(pos.epoch, pos.row), rank, seq_len,
                                          first_row, tok_p, n_tok, rows.ctypes.data_as(ffi.u64p), in_p, tg_p,
                                          C.byref(nxt)))
@@ -408,6 +424,17 @@ class LitDataLoader:
         """PrefetchDataLoader::new (src/data/prefetch.rs:86-115): a host thread keeps the coming batches' rows ready in
         pinned memory; the batches are the unprefetched loader's."""
         check(lib().oxz_loader_set_prefetch(self._h, depth))
+        return self
+
+    def set_row_order(self, epoch: int, perm: np.ndarray | None) -> "LitDataLoader":
+        """with_row_order(RowOrder::Shuffled) (src/data/construction.rs:140) with the epoch's permutation made by the
+        caller (epoch_permutation, src/data/rows.rs:258-263): perm[slot] is the loader row read at `slot`. The loader
+        keeps two epochs' orders; None returns to stream order."""
+        if perm is None:
+            check(lib().oxz_loader_set_row_order(self._h, epoch, None, 0))
+            return self
+        perm = np.ascontiguousarray(perm, dtype=np.uint32)
+        check(lib().oxz_loader_set_row_order(self._h, epoch, perm.ctypes.data_as(C.POINTER(C.c_uint32)), perm.size))
         return self
 
     def next_rows(self) -> list[int]:
@@ -780,6 +807,22 @@ class DpOptimizer:
         check(lib().oxz_plan_last_pull_kernel(self._h, C.byref(v)))
         return v.value
 
+    def exchange_kind(self) -> int:
+        """How the ranks meet for the step's barriers and small sum: 0 one rank, 1 the communicator's collectives,
+        2 mailboxes in peer memory."""
+        v = C.c_int32()
+        check(lib().oxz_plan_exchange_kind(self._h, C.byref(v)))
+        return v.value
+
+    def grad_norms_per_tensor(self, loss_scale: float = NAN, max_grad_value: float = NAN) -> list[float]:
+        """grad_norm_for_tensor for every tensor (src/trainer.rs:933-937): what diagnose_bad_gradients and the
+        DEBUG_GRAD breakdown read (src/trainer.rs:940-1020). -1 marks a tensor no rank had a gradient for.
+        Collective at world > 1; call after a step, before the gradients change."""
+        T = len(self.numel)
+        out = (C.c_double * max(T, 1))()
+        check(lib().oxz_grad_norms_per_tensor(self._h, self.comm.handle if self.comm else None, loss_scale, max_grad_value, out))
+        return [out[i] for i in range(T)]
+
     def set_profile(self, on: bool) -> None:
         """Per-phase CUDA-event timing of each step (the PROFILE_TRAIN switch, src/trainer.rs:262-263)."""
         check(lib().oxz_plan_set_profile(self._h, int(on)))
@@ -807,6 +850,22 @@ def compute_grad_norm(device_ptr: int, dtype: int, n: int, loss_scale: float = N
     out = C.c_double()
     check(lib().oxz_grad_norm(C.c_void_p(device_ptr), dtype, n, loss_scale, max_grad_value,
                               C.c_void_p(stream) if stream else None, C.byref(out)))
+    return out.value
+
+
+def diagnose_bad_gradients(names: list[str], norms: list[float], top: int = 5) -> list[tuple[str, float]]:
+    """The reference's report after a non-finite norm (diagnose_bad_gradients, src/trainer.rs:990-1020): the tensors
+    whose own norm is inf, NaN or above 1e6, non-finite ones first, then by falling norm; at most `top` of them."""
+    bad = [(n, v) for n, v in zip(names, norms) if math.isinf(v) or math.isnan(v) or v > 1e6]
+    bad.sort(key=lambda nv: (0 if (math.isnan(nv[1]) or math.isinf(nv[1])) else 1, -nv[1] if math.isfinite(nv[1]) else 0.0))
+    return bad[:top]
+
+
+def selftest_bounded_wait(device: int = 0, limit_ms: int = 50) -> int:
+    """What a rank sees when a peer never arrives, shown on one GPU without any fault: returns what the gate kernel
+    recorded (1 = its wait ran out after limit_ms); raises if the context did not stay usable."""
+    out = C.c_int32(-1)
+    check(lib().oxz_selftest_bounded_wait(device, limit_ms, C.byref(out)))
     return out.value
 
 

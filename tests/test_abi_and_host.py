@@ -1,5 +1,6 @@
 """CPU-side checks: the library loads and exports every declared symbol, the planner's layout is consistent,
 and the C++ host logic agrees with the Python checker on the reference's known answers and on random cases."""
+import ctypes as C
 import math
 import os
 import re
@@ -238,6 +239,53 @@ def test_row_arithmetic_matches_checker_bit_for_bit():
             ox.RowLayout(*args)
     with pytest.raises(ox.OxzError, match="rank 2 is not below world size 2"):
         ranks.next_window(ox.DataPosition(), 2, seq)
+
+
+def test_shuffled_row_order_with_the_callers_permutations_matches_the_checker():
+    # EpochOrder::row (src/data/rows.rs:240-256): the row at `slot` of `epoch` is that epoch's permutation at `slot`;
+    # the permutation is the caller's (here any seeded one from NumPy: the library never makes it)
+    seq, rows, bs, world = 3, 23, 3, 2
+    tokens = (np.arange(rows * (seq + 1) + 1, dtype=np.uint64) * 2654435761 % 100003).astype(np.uint32)
+    perm_of = lambda epoch: np.random.default_rng(1000 + epoch).permutation(rows).astype(np.uint32)  # noqa: E731
+    layout, cl = ox.RowLayout(rows, bs, world), hl.RowLayout(rows, bs, world)
+    pos, cpos = [ox.DataPosition(), ox.DataPosition()], hl.DataPosition()
+    seen_epochs = set()
+    for step in range(11):  # crosses three epoch boundaries (3 global batches per epoch)
+        union = []
+        for k in range(world):
+            epoch = layout.batch_epoch(pos[k])
+            assert epoch == cl.batch_start(cpos).epoch
+            seen_epochs.add(epoch)
+            r, i, t, pos[k] = layout.next_window(pos[k], k, seq, tokens, row_order=(epoch, perm_of(epoch)))
+            crow, cin, ctg, cnext = hl.rank_window(cl, cpos, k, seq, order=perm_of)
+            assert r.tolist() == crow
+            assert np.array_equal(i, tokens[np.array(cin)].astype(np.int64))
+            assert np.array_equal(t, tokens[np.array(ctg)].astype(np.int64))
+            union += crow
+        assert len(set(union)) == bs * world  # every row of the global batch once
+        cpos = cnext
+        assert (pos[0].epoch, pos[0].row) == (pos[1].epoch, pos[1].row) == (cpos.epoch, cpos.row)
+    assert seen_epochs == {0, 1, 2, 3}
+    # within an epoch the batches visit distinct rows (src/data/rows.rs:376-411: an epoch reads every row once)
+    p, rows_seen = ox.DataPosition(), []
+    for _ in range(3):
+        for k in range(world):
+            r, _, _, nxt = layout.next_window(p, k, seq, row_order=(0, perm_of(0)))
+            rows_seen += r.tolist()
+        p = nxt
+    assert len(set(rows_seen)) == 18
+    # the wrong epoch's order, a wrong length and a non-permutation are refused
+    with pytest.raises(ox.OxzError, match="reads epoch 0 and the row order given is epoch 1"):
+        layout.next_window(ox.DataPosition(), 0, seq, row_order=(1, perm_of(1)))
+    with pytest.raises(ox.OxzError, match="holds 22 rows and the layout 23"):
+        layout.next_window(ox.DataPosition(), 0, seq, row_order=(0, perm_of(0)[:22]))
+    bad = perm_of(0).copy()
+    bad[1] = bad[0]
+    with pytest.raises(ox.OxzError, match="twice"):
+        ffi.check(ox.lib().oxz_rows_check_permutation(bad.ctypes.data_as(C.POINTER(C.c_uint32)), bad.size))
+    bad[1] = 99
+    with pytest.raises(ox.OxzError, match="past its 23 rows"):
+        ffi.check(ox.lib().oxz_rows_check_permutation(bad.ctypes.data_as(C.POINTER(C.c_uint32)), bad.size))
 
 
 def test_step_weighting_matches_checker():

@@ -64,11 +64,15 @@ class Group:
         list(self.pool.map(put, range(self.world)))
 
     def step(self, cfg, extras=None, present=None):
+        """present: one list of flags for every rank, or one list per rank (the ranks' flags may differ)."""
+        per_rank = present is not None and len(present) > 0 and isinstance(present[0], (list, tuple))
+        flags = [present[r] if per_rank else present for r in range(self.world)]
+
         def run(r):
-            res = self.opts[r].step(cfg, present, [extras[r]] if extras else None)
+            res = self.opts[r].step(cfg, flags[r], [extras[r]] if extras else None)
             return res, (self.opts[r].last_extras if extras else None)
         out = list(self.pool.map(run, range(self.world)))
-        rg = [[g if (present is None or present[i]) else None for i, g in enumerate(self.grads[r])] for r in range(self.world)]
+        rg = [[g if (flags[r] is None or flags[r][i]) else None for i, g in enumerate(self.grads[r])] for r in range(self.world)]
         ocfg = orc.StepConfig(**{k: getattr(cfg, k) for k in orc.StepConfig.__dataclass_fields__})
         ref = orc.step(self.ref, rg, self.gd, ocfg)
         return out, ref
@@ -305,6 +309,91 @@ def test_a_pull_wait_that_runs_out_is_reported_and_changes_nothing(monkeypatch):
     for res, _ in out:
         assert (res.overflow, res.applied, res.timestep) == (0, 1, 1) == (ref.overflow, ref.applied, ref.timestep)
     g.assert_state(exact=True)
+    g.close()
+
+
+def test_a_run_out_on_one_rank_alone_is_reported_by_every_rank(monkeypatch):
+    """Only rank 1's pull gives up (its bound alone is lowered). Its flag rides on the step's exchange, so rank 0 does
+    not take the poisoned norm for an overflow: both ranks return OXZ_ERR_TIMEOUT, nothing changes anywhere, and no
+    rank would back its loss scale off and walk into the next collective alone."""
+    world = 2
+    g = Group(world, [0] * world, "local", seed=52)
+    before = [g.merged(k) for k in (ffi.STATE_MASTER, ffi.STATE_EXP_AVG, ffi.STATE_EXP_AVG_SQ)]
+    monkeypatch.setenv("OXZ_PULL_WAIT_LIMIT", "0@1")
+
+    def failing(r):
+        try:
+            return g.opts[r].step(ox.StepConfig(max_grad_norm=1e9))
+        except ox.OxzError as e:
+            return e
+    got = list(g.pool.map(failing, range(world)))
+    assert all(isinstance(e, ox.OxzError) and e.status == ffi.ERR_TIMEOUT for e in got), got
+    assert all(opt.timestep == 0 for opt in g.opts)
+    after = [g.merged(k) for k in (ffi.STATE_MASTER, ffi.STATE_EXP_AVG, ffi.STATE_EXP_AVG_SQ)]
+    for b, a in zip(before, after):
+        for x, y in zip(b, a):
+            assert np.array_equal(bits(x), bits(y))
+    monkeypatch.delenv("OXZ_PULL_WAIT_LIMIT")
+    out, ref = g.step(ox.StepConfig(max_grad_norm=1e9))
+    for res, _ in out:
+        assert (res.overflow, res.applied, res.timestep) == (0, 1, 1)
+    g.assert_state(exact=True)
+    g.close()
+
+
+def test_a_wait_for_a_rank_that_never_arrives_runs_out_and_leaves_the_context_usable():
+    # the gate kernel of the peer-memory exchanges, as rank 0 of two ranks whose other rank does not exist: its wait is
+    # bounded, the kernel records the run-out and returns; nothing faults, traps or hangs
+    assert ox.selftest_bounded_wait(0, limit_ms=30) == 1
+
+
+@pytest.mark.parametrize("mode", [ox.SYNC_P2P, ox.SYNC_COPY, ox.SYNC_REPLICATED])
+@pytest.mark.parametrize("kind,world,devices", layouts())
+def test_ranks_with_different_gradient_flags_update_the_union(kind, world, devices, mode):
+    """src/dp/reduce.rs:20: a tensor is left alone only when NO rank has a gradient for it. Tensor 2 has one on rank 0
+    only, tensor 5 on the last rank only, tensor 3 on no rank, the others on every rank. The ranks hand in different
+    flags; the library forms their union, the ranks without a gradient contribute the zeros their buffers hold."""
+    g = Group(world, devices, kind, mode=mode, seed=24)
+    T = len(g.numel)
+    flags = [[True] * T for _ in range(world)]
+    grads = [[x.copy() for x in rg] for rg in g.grads]
+    for r in range(world):
+        flags[r][3] = False
+        if r != 0:
+            flags[r][2] = False
+            grads[r][2] = np.zeros_like(grads[r][2])
+        if r != world - 1:
+            flags[r][5] = False
+            grads[r][5] = np.zeros_like(grads[r][5])
+    g.set_grads(grads)
+    before3 = g.merged(ffi.STATE_MASTER)[3].copy()
+    out, ref = g.step(ox.StepConfig(max_grad_norm=1e9), present=flags)
+    for res, _ in out:
+        assert (res.overflow, res.applied) == (0, 1) and abs(res.grad_norm - ref.grad_norm) <= 1e-5 * ref.grad_norm
+    if mode == ox.SYNC_REPLICATED:
+        for opt in g.opts:  # every replica holds everything
+            for kind_, refs in ((ffi.STATE_MASTER, g.ref.master), (ffi.STATE_EXP_AVG, g.ref.exp_avg), (ffi.STATE_EXP_AVG_SQ, g.ref.exp_avg_sq)):
+                for i in range(T):
+                    assert np.array_equal(bits(opt.export_tensor(kind_, i)), bits(refs[i])), (kind_, i)
+    else:
+        g.assert_state(exact=True)
+        assert np.array_equal(bits(g.merged(ffi.STATE_MASTER)[3]), bits(before3))
+    # the per-tensor norms name the tensor no rank had a gradient for
+    per = list(g.pool.map(lambda r: g.opts[r].grad_norms_per_tensor(), range(world)))
+    for norms in per:
+        assert norms[3] == -1.0 and norms[4] == 0.0  # tensor 4 is empty
+        for i in (0, 1, 2, 5, 6):
+            rank_sum = orc.sum_ranks([orc.widen(grads[r][i], g.gd) for r in range(world)], orc.F32)
+            want = math.sqrt(orc.sumsq(rank_sum))
+            assert abs(norms[i] - want) <= 1e-5 * want, (i, norms[i], want)
+    g.close()
+
+
+@pytest.mark.parametrize("kind,world,devices", layouts())
+def test_exchange_kind_follows_the_communicator(kind, world, devices):
+    g = Group(world, devices, kind, seed=25)
+    want = ffi.EXCHANGE_MAILBOX if kind == "nccl" else ffi.EXCHANGE_COMM
+    assert {opt.exchange_kind() for opt in g.opts} == {want}
     g.close()
 
 

@@ -123,6 +123,35 @@ def test_both_clips_fire_on_small_gradients_the_second_measures_again():
     pair.close()
 
 
+@pytest.mark.parametrize("gd", [ox.BF16, ox.F16, ox.F32])
+def test_per_tensor_norms_name_the_offending_tensors(gd):
+    # grad_norm_for_tensor for every parameter (src/trainer.rs:933-937), as diagnose_bad_gradients reads it after a
+    # non-finite norm (src/trainer.rs:990-1020)
+    pair = Pair(RAGGED, None, gd, gd if gd != ox.F32 else ox.F32, seed=16)
+    g = [x.copy() for x in pair.grads]
+    inf_bits = {ox.BF16: 0x7f80, ox.F16: 0x7c00}
+    if gd == ox.F32:
+        g[9][17], g[10][99999] = np.float32(np.inf), np.float32(np.nan)
+    else:
+        g[9][17] = inf_bits[gd]
+        g[10][99999] = inf_bits[gd] | 0x0040 | 1  # a NaN pattern of either 16-bit type
+    pair.set_grads(g)
+    present = [True] * len(RAGGED)
+    present[4] = False
+    res, ref = pair.step(ox.StepConfig(loss_scale=8.0), present)
+    assert res.overflow == 1 and res.applied == 0 and ref.overflow == 1
+    norms = pair.opt.grad_norms_per_tensor(loss_scale=8.0)
+    assert norms[4] == -1.0 and norms[11] == 0.0
+    assert math.isinf(norms[9]) and math.isnan(norms[10])
+    for i in (0, 1, 2, 3, 5, 6, 7, 8, 12):
+        want = math.sqrt(orc.sumsq(orc.unscale(g[i], gd, 8.0)))
+        assert abs(norms[i] - want) <= NORM_RTOL * want, (i, norms[i], want)
+    names = [f"model.t{i}.weight" for i in range(len(RAGGED))]
+    assert [n for n, _ in ox.diagnose_bad_gradients(names, norms)] == ["model.t9.weight", "model.t10.weight"] or \
+        [n for n, _ in ox.diagnose_bad_gradients(names, norms)] == ["model.t10.weight", "model.t9.weight"]
+    pair.close()
+
+
 @pytest.mark.parametrize("switch", [dict(decay_after=1), dict(eps_mode=1), dict(clip_eps=0.0)])
 def test_unpinned_forms_follow_their_switches(switch):
     pair = Pair([3000, 10], [False, True], ox.BF16, ox.BF16, seed=6)

@@ -79,6 +79,85 @@ def test_rank_batches_hold_exactly_the_checkers_token_indices(tmp_path, rows, ba
         l.close()
 
 
+def test_the_loader_reads_the_callers_row_order_on_the_host(tmp_path):
+    """RowOrder::Shuffled with the permutations handed over by the caller: the rows every rank draws equal the
+    checker's across epoch boundaries, over two files and two row ranges; needs no GPU (next_rows)."""
+    width = SEQ + 1
+    paths = [token_file(tmp_path, 13, 2, "a.bin")[0], token_file(tmp_path, 9, 0, "b.bin")[0]]
+    spans = [(1, 8), (10, 21)]
+    world, batch = 2, 2
+    loaders = [ox.LitDataLoader.from_files(paths, batch, SEQ, rank=r, world_size=world, row_ranges=spans) for r in range(world)]
+    n = loaders[0].num_rows()
+    assert n == 18
+    perm_of = lambda epoch: np.random.default_rng(77 + epoch).permutation(n).astype(np.uint32)  # noqa: E731
+    ranges = hl.RowRanges(spans, 22)
+    layout = hl.RowLayout(n, batch, world)
+    for l in loaders:
+        l.set_row_order(0, perm_of(0)).set_row_order(1, perm_of(1))
+    pos = hl.DataPosition()
+    for step in range(9):  # 4 global batches per epoch
+        if step == 5:  # during epoch 1 the caller hands over epoch 2's order; epoch 0's is dropped
+            for l in loaders:
+                l.set_row_order(2, perm_of(2))
+        for r, l in enumerate(loaders):
+            want, _, _, nxt = hl.rank_window(layout, pos, r, SEQ, order=perm_of)
+            assert l.next_rows() == [ranges.global_row(x) for x in want], (step, r)
+        pos = nxt
+    # epoch 3's order was never given: the batch that needs it says so
+    for _ in range(3):
+        loaders[0].next_rows()
+    with pytest.raises(ox.OxzError, match="reads epoch 3 and the loader holds no row order for it"):
+        loaders[0].next_rows()
+    # not a permutation, or of another length: refused; None returns to stream order
+    bad = perm_of(0).copy()
+    bad[3] = bad[4]
+    with pytest.raises(ox.OxzError, match="twice"):
+        loaders[1].set_row_order(5, bad)
+    with pytest.raises(ox.OxzError, match="holds 17 rows and the loader 18"):
+        loaders[1].set_row_order(5, perm_of(0)[:17])
+    loaders[1].set_row_order(0, None)
+    loaders[1].seek(ox.DataPosition(0, 0))
+    assert loaders[1].next_rows() == [ranges.global_row(x) for x in (2, 3)]
+    with pytest.raises(ox.OxzError, match="mixture"):
+        loaders[0].with_mixture([1.0, 1.0])
+    for l in loaders:
+        l.close()
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("depth", [0, 2])
+def test_shuffled_batches_carry_the_tokens_of_the_permuted_rows(tmp_path, depth):
+    """The same on the device, with and without the prefetch thread: inputs and targets are the tokens of the rows the
+    caller's permutation names, bit for bit, across two epoch boundaries."""
+    import torch
+    from oxidizr_b200.interop import device_view
+    rows, batch, world = 14, 2, 2
+    path, toks = token_file(tmp_path, rows, 3)
+    perm_of = lambda epoch: np.random.default_rng(5 + epoch).permutation(rows).astype(np.uint32)  # noqa: E731
+    loaders = [ox.LitDataLoader(path, batch, SEQ, rank=r, world_size=world) for r in range(world)]
+    for l in loaders:
+        l.set_row_order(0, perm_of(0)).set_row_order(1, perm_of(1))
+        if depth:
+            l.with_prefetch(depth)
+    layout, pos = hl.RowLayout(rows, batch, world), hl.DataPosition()
+    for step in range(8):  # 3 global batches per epoch
+        if step == 4:
+            for l in loaders:
+                l.set_row_order(2, perm_of(2))
+        for r, l in enumerate(loaders):
+            i_ptr, t_ptr, got_rows = l.next_batch()
+            torch.cuda.synchronize()
+            inputs = device_view(i_ptr, batch * SEQ * 8, torch.int64).cpu().numpy().reshape(batch, SEQ)
+            targets = device_view(t_ptr, batch * SEQ * 8, torch.int64).cpu().numpy().reshape(batch, SEQ)
+            want_rows, want_in, want_tg, nxt = hl.rank_window(layout, pos, r, SEQ, order=perm_of)
+            assert got_rows == want_rows, (step, r)
+            assert np.array_equal(inputs, toks[np.array(want_in)].astype(np.int64))
+            assert np.array_equal(targets, toks[np.array(want_tg)].astype(np.int64))
+        pos = nxt
+    for l in loaders:
+        l.close()
+
+
 def write_tokens(tmp_path, tokens, name):
     path = tmp_path / name
     np.asarray(tokens, dtype="<u4").tofile(path)
