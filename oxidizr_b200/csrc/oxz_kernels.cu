@@ -902,6 +902,237 @@ __global__ void __launch_bounds__(THREADS, MINB)
     }
 }
 
+// One element's share of the update as k_adamw does it: unscale, clamp, both clip coefficients, AdamW.
+__device__ __forceinline__ void adam_tile8(float (&p)[8], float (&m)[8], float (&v)[8], const float (&g)[8], const AdamParams& k,
+                                           float c1, float c2, float step, float decay) {
+#pragma unroll
+    for (int i = 0; i < 8; i++) {
+        float x = __fmul_rn(g[i], k.inv_scale);
+        if (k.clamp_on) {
+            x = x > k.clamp_hi ? k.clamp_hi : x;
+            x = x < -k.clamp_hi ? -k.clamp_hi : x;
+        }
+        x = __fmul_rn(__fmul_rn(x, c1), c2);
+        adam1(p[i], m[i], v[i], x, k, step, decay);
+    }
+}
+
+template <int PDT>
+__device__ __forceinline__ void pack8(const float (&x)[8], uint32_t (&w)[4]) {
+#pragma unroll
+    for (int i = 0; i < 4; i++) {
+        if constexpr (PDT == OXZ_BF16) {
+            __nv_bfloat162 h = __floats2bfloat162_rn(x[2 * i], x[2 * i + 1]);
+            w[i] = *reinterpret_cast<uint32_t*>(&h);
+        } else {
+            __half2 h = __floats2half2_rn(x[2 * i], x[2 * i + 1]);
+            w[i] = *reinterpret_cast<uint32_t*>(&h);
+        }
+    }
+}
+
+// The update with the push of 16-bit working weights as 256-bit peer stores. A warp takes two neighbouring tiles per
+// round (the f32 state still moves one 256-bit access per lane and array); the two tiles' packed weights, 16 bytes per
+// lane each, are exchanged by shuffles so that lanes 0-15 hold tile A and lanes 16-31 tile B in 32-byte pieces, and
+// every rank's buffer receives ONE 32-byte store per lane for the pair: half the peer-store instructions of k_adamw
+// and 1 KiB per warp and peer. Where the two tiles are not neighbours in the flat space (a shard's odd end) or one of
+// them is left out, each goes the 128-bit way. Same arithmetic, same bits as k_adamw.
+template <int GDT, int PDT, bool CHECK>
+__global__ void __launch_bounds__(THREADS, 2)
+    k_adamw_wide(const void* __restrict__ gsrc, float* __restrict__ master, float* __restrict__ exp_avg,
+                 float* __restrict__ exp_avg_sq, PeerTable peers, int n_work, TileMap map,
+                 const uint32_t* __restrict__ tile_meta, const uint8_t* __restrict__ present,
+                 const DevScalars* __restrict__ scalars, AdamParams k) {
+    static_assert(PDT == OXZ_BF16 || PDT == OXZ_F16, "16-bit working weights only");
+    if (scalars->skip) return;
+    const float c1 = scalars->c1, c2 = scalars->c2;
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const uint32_t per_iter = gridDim.x * WARPS * 2;
+    for (uint32_t base = map.first_tile + (blockIdx.x * WARPS + warp) * 2; base < map.n_local_tiles; base += per_iter) {
+        float g[2][8], p[2][8], m[2][8], v[2][8];
+        bool on[2];
+        uint32_t ftile[2], meta[2];
+#pragma unroll
+        for (int j = 0; j < 2; j++) {
+            const uint32_t lt = base + j;
+            on[j] = lt < map.n_local_tiles;
+            ftile[j] = 0;
+            meta[j] = PAD_TILE;
+            if (on[j]) {
+                const uint64_t le = static_cast<uint64_t>(lt) * TILE + lane * 8;
+                load8<GDT>(gsrc, le, g[j]);
+                load8<OXZ_F32>(master, le, p[j]);
+                load8<OXZ_F32>(exp_avg, le, m[j]);
+                load8<OXZ_F32>(exp_avg_sq, le, v[j]);
+                ftile[j] = flat_tile(map, lt);
+                meta[j] = tile_meta[ftile[j]];
+            }
+        }
+        uint32_t w[2][4];
+#pragma unroll
+        for (int j = 0; j < 2; j++) {
+            on[j] = on[j] && meta[j] != PAD_TILE;
+            if constexpr (CHECK) on[j] = on[j] && present[meta[j] & 0xffffffu];
+            if (!on[j]) continue;
+            const uint32_t grp = meta[j] >> 24;
+            adam_tile8(p[j], m[j], v[j], g[j], k, c1, c2, k.step_size[grp], k.decay_mul[grp]);
+            const uint64_t le = static_cast<uint64_t>(base + j) * TILE + lane * 8;
+            store8<OXZ_F32>(master, le, p[j]);
+            store8<OXZ_F32>(exp_avg, le, m[j]);
+            store8<OXZ_F32>(exp_avg_sq, le, v[j]);
+            pack8<PDT>(p[j], w[j]);
+        }
+        if (on[0] && on[1] && ftile[1] == ftile[0] + 1) {  // warp-uniform: tiles and their flags are
+            const int src = 2 * (lane & 15);
+            uint32_t out[8];
+#pragma unroll
+            for (int q = 0; q < 4; q++) {
+                const uint32_t a_lo = __shfl_sync(0xffffffffu, w[0][q], src), b_lo = __shfl_sync(0xffffffffu, w[1][q], src);
+                const uint32_t a_hi = __shfl_sync(0xffffffffu, w[0][q], src + 1), b_hi = __shfl_sync(0xffffffffu, w[1][q], src + 1);
+                out[q] = lane < 16 ? a_lo : b_lo;
+                out[4 + q] = lane < 16 ? a_hi : b_hi;
+            }
+            const uint64_t fe = static_cast<uint64_t>(ftile[0]) * TILE + (lane < 16 ? 0 : TILE) + (lane & 15) * 16;
+            for (int r = 0; r < n_work; r++) {
+                uint16_t* dst = static_cast<uint16_t*>(peers.work[r]) + fe;
+                asm volatile("st.global.cs.v8.b32 [%0], {%1,%2,%3,%4,%5,%6,%7,%8};" ::"l"(dst), "r"(out[0]), "r"(out[1]), "r"(out[2]),
+                             "r"(out[3]), "r"(out[4]), "r"(out[5]), "r"(out[6]), "r"(out[7])
+                             : "memory");
+            }
+        } else {
+#pragma unroll
+            for (int j = 0; j < 2; j++) {
+                if (!on[j]) continue;
+                const uint64_t fe = static_cast<uint64_t>(ftile[j]) * TILE + lane * 8;
+                for (int r = 0; r < n_work; r++)
+                    st_stream(reinterpret_cast<uint4*>(static_cast<uint16_t*>(peers.work[r]) + fe), make_uint4(w[j][0], w[j][1], w[j][2], w[j][3]));
+            }
+        }
+    }
+}
+
+// The update with its four input streams staged through shared memory by 1-D bulk asynchronous copies (cp.async.bulk
+// + mbarrier, no multicast), for one rank with every tensor present: STAGES stages of 8 tiles, one elected thread
+// issues the four copies of a stage (gradients, master, exp_avg, exp_avg_sq), each warp updates one tile of the stage
+// from shared memory and stores its results straight to global memory. It exists to measure staging against the
+// direct 256-bit loads of k_adamw on the same work; same arithmetic, same bits. Every wait is bounded.
+template <int GDT, int PDT, int STAGES>
+__global__ void __launch_bounds__(THREADS)
+    k_adamw_staged(const void* __restrict__ gsrc, float* __restrict__ master, float* __restrict__ exp_avg,
+                   float* __restrict__ exp_avg_sq, void* __restrict__ work, uint32_t n_tiles,
+                   const uint32_t* __restrict__ tile_meta, DevScalars* __restrict__ scalars, AdamParams k) {
+    extern __shared__ __align__(128) unsigned char stage_smem[];
+    __shared__ __align__(8) uint64_t bar[STAGES];
+    if (scalars->skip) return;
+    constexpr uint32_t GS = GDT == OXZ_F32 ? 4 : 2;
+    constexpr uint32_t G_BYTES = BULK_TILES * TILE * GS, F_BYTES = BULK_TILES * TILE * 4;
+    constexpr uint32_t STAGE_BYTES = G_BYTES + 3 * F_BYTES;
+    const float c1 = scalars->c1, c2 = scalars->c2;
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const uint32_t n_chunks = n_tiles / BULK_TILES;
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < STAGES; s++) asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" ::"r"(smem_addr(&bar[s])));
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    __syncthreads();
+    auto issue = [&](uint32_t chunk, int stage) {
+        const uint64_t e0 = static_cast<uint64_t>(chunk) * BULK_TILES * TILE;
+        const uint32_t b = smem_addr(&bar[stage]);
+        unsigned char* dst = stage_smem + static_cast<size_t>(stage) * STAGE_BYTES;
+        asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(b), "r"(STAGE_BYTES) : "memory");
+        asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+                     ::"r"(smem_addr(dst)), "l"(static_cast<const unsigned char*>(gsrc) + e0 * GS), "r"(G_BYTES), "r"(b) : "memory");
+#pragma unroll
+        for (int a = 0; a < 3; a++) {
+            const float* src = a == 0 ? master : a == 1 ? exp_avg : exp_avg_sq;
+            asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+                         ::"r"(smem_addr(dst + G_BYTES + a * F_BYTES)), "l"(src + e0), "r"(F_BYTES), "r"(b) : "memory");
+        }
+    };
+    uint32_t pending = 0, phase = 0;
+    for (int s = 0; s < STAGES; s++) {
+        const uint32_t c = blockIdx.x + static_cast<uint32_t>(s) * gridDim.x;
+        if (c < n_chunks) {
+            if (threadIdx.x == 0) issue(c, s);
+            pending |= 1u << s;
+        }
+    }
+    int stage = 0;
+    bool ok = true;
+    for (uint32_t c = blockIdx.x; c < n_chunks; c += gridDim.x) {
+        const int landed = mbar_wait_bounded(smem_addr(&bar[stage]), (phase >> stage) & 1u, BULK_SPIN_LIMIT) ? 1 : 0;
+        if (!__syncthreads_and(landed)) {
+            ok = false;
+            break;
+        }
+        pending &= ~(1u << stage);
+        phase ^= 1u << stage;
+        const unsigned char* st = stage_smem + static_cast<size_t>(stage) * STAGE_BYTES;
+        const uint32_t tile = c * BULK_TILES + warp;
+        const uint32_t meta = tile_meta[tile];
+        float g[8], pmv[3][8];  // master, exp_avg, exp_avg_sq
+        if constexpr (GDT == OXZ_F32) {
+            const float4* q = reinterpret_cast<const float4*>(st + warp * (TILE * 4) + lane * 32);
+            const float4 a = q[0], b2 = q[1];
+            g[0] = a.x; g[1] = a.y; g[2] = a.z; g[3] = a.w; g[4] = b2.x; g[5] = b2.y; g[6] = b2.z; g[7] = b2.w;
+        } else {
+            RawVec<GDT> r;
+            r.v = *reinterpret_cast<const uint4*>(st + warp * (TILE * 2) + lane * 16);
+            widen_raw<GDT>(r, g);
+        }
+#pragma unroll
+        for (int a = 0; a < 3; a++) {
+            const float4* q = reinterpret_cast<const float4*>(st + G_BYTES + a * F_BYTES + warp * (TILE * 4) + lane * 32);
+            const float4 lo = q[0], hi = q[1];
+            pmv[a][0] = lo.x; pmv[a][1] = lo.y; pmv[a][2] = lo.z; pmv[a][3] = lo.w;
+            pmv[a][4] = hi.x; pmv[a][5] = hi.y; pmv[a][6] = hi.z; pmv[a][7] = hi.w;
+        }
+        __syncthreads();  // every warp has read this stage: it may be refilled while the arithmetic runs
+        const uint32_t nc = c + static_cast<uint32_t>(STAGES) * gridDim.x;
+        if (nc < n_chunks) {
+            if (threadIdx.x == 0) issue(nc, stage);
+            pending |= 1u << stage;
+        }
+        if (++stage == STAGES) stage = 0;
+        if (meta == PAD_TILE) continue;
+        const uint32_t grp = meta >> 24;
+        adam_tile8(pmv[0], pmv[1], pmv[2], g, k, c1, c2, k.step_size[grp], k.decay_mul[grp]);
+        const uint64_t e = static_cast<uint64_t>(tile) * TILE + lane * 8;
+        store8<OXZ_F32>(master, e, pmv[0]);
+        store8<OXZ_F32>(exp_avg, e, pmv[1]);
+        store8<OXZ_F32>(exp_avg_sq, e, pmv[2]);
+        if (work != nullptr) store8<PDT>(work, e, pmv[0]);
+    }
+    if (!ok) {
+        // a copy of this block never landed: say so, give the copies in flight their bounded chance, and leave; the
+        // tiles this block had not reached keep their old state and the host reports the step failed
+        if (threadIdx.x == 0) atomicMax(&scalars->wait_expired, 1);
+        for (int s = 0; s < STAGES; s++)
+            if (pending & (1u << s)) mbar_wait_bounded(smem_addr(&bar[s]), (phase >> s) & 1u, BULK_SPIN_LIMIT);
+        return;
+    }
+    // the tiles past the last whole chunk: the direct way, by the last block
+    const uint32_t tail0 = n_chunks * BULK_TILES;
+    if (blockIdx.x == gridDim.x - 1 && tail0 + warp < n_tiles) {
+        const uint32_t tile = tail0 + warp;
+        const uint32_t meta = tile_meta[tile];
+        if (meta != PAD_TILE) {
+            const uint64_t e = static_cast<uint64_t>(tile) * TILE + lane * 8;
+            float g[8], p[8], m[8], v[8];
+            load8<GDT>(gsrc, e, g);
+            load8<OXZ_F32>(master, e, p);
+            load8<OXZ_F32>(exp_avg, e, m);
+            load8<OXZ_F32>(exp_avg_sq, e, v);
+            const uint32_t grp = meta >> 24;
+            adam_tile8(p, m, v, g, k, c1, c2, k.step_size[grp], k.decay_mul[grp]);
+            store8<OXZ_F32>(master, e, p);
+            store8<OXZ_F32>(exp_avg, e, m);
+            store8<OXZ_F32>(exp_avg_sq, e, v);
+            if (work != nullptr) store8<PDT>(work, e, p);
+        }
+    }
+}
+
 // ---------------------------------------------------------------- flatten
 
 // Each warp takes several tiles per round and walks them in phases (tile entries, then the per-tensor lookups, then
@@ -991,12 +1222,9 @@ __global__ void __launch_bounds__(THREADS, 3)
 
 // ---------------------------------------------------------------- launchers
 
-static int adam_variant() {
-    static int v = [] {
-        const char* e = getenv("OXZ_ADAM_VARIANT");
-        return e ? atoi(e) : 0;
-    }();
-    return v;
+static int adam_variant() {  // read at every launch, so that a test can compare the forms within one process
+    const char* e = getenv("OXZ_ADAM_VARIANT");
+    return e ? atoi(e) : 0;
 }
 
 static int adam_blocks_per_sm(int variant) { return variant == 1 ? 4 : variant == 2 ? 2 : 3; }
@@ -1228,6 +1456,10 @@ int32_t launch_pull_bulk(cudaStream_t s, const LaunchGeom& g, const PeerTable& p
                          float inv_scale, float clamp_hi, int32_t clamp_on, float* reduced, double* partials,
                          uint32_t slots, DevScalars* scalars) {
     int blocks = g.bulk_blocks[world == 2 ? 0 : world == 4 ? 1 : 2];
+    if (const char* e = getenv("OXZ_BULK_BLOCKS")) {  // tuning aid: another grid size, still a whole number of clusters
+        const int want = atoi(e) / CLUSTER * CLUSTER;
+        if (want >= CLUSTER) blocks = want;
+    }
     if (static_cast<uint32_t>(blocks / CLUSTER) > slots) blocks = static_cast<int>(slots) * CLUSTER;  // one partial slot per cluster
     if (blocks < CLUSTER) return fail(OXZ_ERR_INVALID, "launch_pull_bulk: no partial slot to write to");
 #define OXZ_BULK(DT) \
@@ -1282,12 +1514,54 @@ static void launch_adamw_v(int variant, dim3 grid, cudaStream_t s, const void* g
 #undef OXZ_ADAM
 }
 
+// The staged form: grid = the blocks resident at once with its shared memory (a persistent grid is one wave).
+template <int GDT, int PDT>
+static int32_t launch_adamw_staged(cudaStream_t s, const LaunchGeom& g, const void* gsrc, float* master, float* m, float* v,
+                                   void* work, uint32_t n_tiles, const uint32_t* tile_meta, const DevScalars* scalars,
+                                   const AdamParams& ap) {
+    constexpr int STAGES = 3;
+    constexpr size_t smem = static_cast<size_t>(STAGES) * BULK_TILES * TILE * ((GDT == OXZ_F32 ? 4 : 2) + 12);
+    static int per_sm[64] = {};
+    int dev = 0;
+    cudaGetDevice(&dev);
+    if (dev < 0 || dev >= 64) return fail(OXZ_ERR_UNSUPPORTED, "device ordinal %d is past 64", dev);
+    if (per_sm[dev] == 0) {
+        cudaError_t e = cudaFuncSetAttribute(k_adamw_staged<GDT, PDT, STAGES>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        if (e != cudaSuccess) return fail(OXZ_ERR_CUDA, "cudaFuncSetAttribute(k_adamw_staged): %s", cudaGetErrorString(e));
+        int n = 0;
+        e = cudaOccupancyMaxActiveBlocksPerMultiprocessor(&n, k_adamw_staged<GDT, PDT, STAGES>, THREADS, smem);
+        if (e != cudaSuccess || n <= 0) return fail(OXZ_ERR_CUDA, "k_adamw_staged does not fit an SM with %zu bytes of shared memory", smem);
+        per_sm[dev] = n;
+    }
+    k_adamw_staged<GDT, PDT, STAGES><<<dim3(g.sm_count * per_sm[dev]), dim3(THREADS), smem, s>>>(
+        gsrc, master, m, v, work, n_tiles, tile_meta, const_cast<DevScalars*>(scalars), ap);
+    return check_launch("k_adamw_staged");
+}
+
 template <int GDT, bool CHECK>
 static int32_t launch_adamw_g(cudaStream_t s, const LaunchGeom& g, const void* gsrc, float* master, float* m, float* v,
                               const PeerTable& peers, int32_t n_work, int32_t pdt, const TileMap& map,
                               const uint32_t* tile_meta, const uint8_t* present, const DevScalars* scalars,
                               const AdamParams& ap) {
     const int variant = adam_variant();
+    // OXZ_ADAM_VARIANT=4: the shared-memory-staged form, where it applies (one rank, every tensor present, the whole
+    // range: local and flat tiles coincide). Measured against the direct loads, not the default.
+    if (variant == 4 && !CHECK && n_work <= 1 && map.first_tile == 0 && map.tiles_per_shard == map.tiles_per_bucket && map.rank == 0) {
+        void* work = n_work ? peers.work[0] : nullptr;
+        switch (pdt) {
+            case OXZ_F32: return launch_adamw_staged<GDT, OXZ_F32>(s, g, gsrc, master, m, v, work, map.n_local_tiles, tile_meta, scalars, ap);
+            case OXZ_BF16: return launch_adamw_staged<GDT, OXZ_BF16>(s, g, gsrc, master, m, v, work, map.n_local_tiles, tile_meta, scalars, ap);
+            case OXZ_F16: return launch_adamw_staged<GDT, OXZ_F16>(s, g, gsrc, master, m, v, work, map.n_local_tiles, tile_meta, scalars, ap);
+            default: return fail(OXZ_ERR_INVALID, "unknown parameter dtype %d", pdt);
+        }
+    }
+    // OXZ_ADAM_VARIANT=3: 256-bit stores of the 16-bit working weights (two tiles per warp)
+    if (variant == 3 && pdt != OXZ_F32 && n_work >= 1) {
+        dim3 grid2(g.sm_count * 2), block(THREADS);
+        if (pdt == OXZ_BF16) k_adamw_wide<GDT, OXZ_BF16, CHECK><<<grid2, block, 0, s>>>(gsrc, master, m, v, peers, n_work, map, tile_meta, present, scalars, ap);
+        else k_adamw_wide<GDT, OXZ_F16, CHECK><<<grid2, block, 0, s>>>(gsrc, master, m, v, peers, n_work, map, tile_meta, present, scalars, ap);
+        return check_launch("k_adamw_wide");
+    }
     dim3 grid(g.adam_blocks);
     switch (pdt) {
         case OXZ_F32: launch_adamw_v<GDT, OXZ_F32, CHECK>(variant, grid, s, gsrc, master, m, v, peers, n_work, map, tile_meta, present, scalars, ap); break;

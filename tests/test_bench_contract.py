@@ -8,8 +8,11 @@ ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
 
 
 def test_reference_arm_prints_one_json_line_with_the_contract_keys():
-    out = subprocess.run([sys.executable, os.path.join(ROOT, "bench.py"), "--impl", "reference", "--steps", "1", "--warmup", "0"],
-                         capture_output=True, text=True, timeout=300, env=dict(os.environ, OMP_NUM_THREADS="4"))
+    # on the small dense set, so the CPU suite stays short; the line's shape is the same for every workload. The
+    # launcher-style OMP_NUM_THREADS=1 must not reach the timed loop: the arm sets its own thread count.
+    out = subprocess.run([sys.executable, os.path.join(ROOT, "bench.py"), "--impl", "reference", "--steps", "1", "--warmup", "0",
+                          "--workload", "nano_dense", "--gpus", "2"],
+                         capture_output=True, text=True, timeout=300, env=dict(os.environ, OMP_NUM_THREADS="1"))
     assert out.returncode == 0, out.stderr
     lines = [l for l in out.stdout.splitlines() if l.strip()]
     assert len(lines) == 1
@@ -17,8 +20,11 @@ def test_reference_arm_prints_one_json_line_with_the_contract_keys():
     for key in ("metric", "value", "unit", "n_gpus", "steps", "warmup", "ms_per_step", "higher_is_better", "scaling",
                 "vs_baseline", "dtype", "data", "config", "impl", "cpu_baseline", "e2e"):
         assert key in d, key
-    assert d["impl"] == "reference" and d["vs_baseline"] is None and d["config"]["workload"] == "llama-3.2-1b"
-    assert d["cpu_baseline"]["kind"] == "port" and d["cpu_baseline"]["cores"] >= 1 and d["cpu_baseline"]["value"] == d["value"] > 0
+    assert d["impl"] == "reference" and d["vs_baseline"] is None and d["config"]["workload"] == "nano_dense"
+    assert d["config"]["params"] == 134188544 and "whole set" in d["cpu_baseline"]["sample"]  # nothing is sampled away
+    assert d["cpu_baseline"]["kind"] == "port" and d["cpu_baseline"]["value"] == d["value"] > 0
+    assert d["cpu_baseline"]["cores"] == len(os.sched_getaffinity(0))
+    assert d["product_library_mapped"] is False  # the CPU arm runs the checker alone
     assert d["e2e"] == {"value": d["value"], "unit": d["unit"], "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}
 
 

@@ -390,6 +390,22 @@ def test_ranks_with_different_gradient_flags_update_the_union(kind, world, devic
 
 
 @pytest.mark.parametrize("kind,world,devices", layouts())
+@pytest.mark.parametrize("gd,pd", [(ox.BF16, ox.BF16), (ox.F32, ox.F16)])
+def test_the_wide_push_lands_the_same_weights_on_every_rank(monkeypatch, kind, world, devices, gd, pd):
+    # OXZ_ADAM_VARIANT=3: the 16-bit working weights leave as one 256-bit store per lane and rank for two tiles
+    monkeypatch.setenv("OXZ_ADAM_VARIANT", "3")
+    g = Group(world, devices, kind, gd=gd, pd=pd, seed=26)
+    out, ref = g.step(ox.StepConfig(max_grad_norm=1e9, eps=1e-8))
+    for res, _ in out:
+        assert (res.overflow, res.applied, res.timestep) == (0, 1, 1)
+    g.assert_state(exact=True)
+    present = [True, True, False, True, True, True, False]
+    out, ref = g.step(ox.StepConfig(max_grad_norm=1e9, eps=1e-8), present=present)
+    g.assert_state(exact=True)
+    g.close()
+
+
+@pytest.mark.parametrize("kind,world,devices", layouts())
 def test_exchange_kind_follows_the_communicator(kind, world, devices):
     g = Group(world, devices, kind, seed=25)
     want = ffi.EXCHANGE_MAILBOX if kind == "nccl" else ffi.EXCHANGE_COMM

@@ -123,6 +123,26 @@ def test_both_clips_fire_on_small_gradients_the_second_measures_again():
     pair.close()
 
 
+@pytest.mark.parametrize("gd,pd", DTYPES)
+@pytest.mark.parametrize("variant", ["1", "2", "3", "4"])
+def test_every_form_of_the_update_kernel_gives_the_same_bits(monkeypatch, variant, gd, pd):
+    # OXZ_ADAM_VARIANT: other launch shapes (1, 2), 256-bit stores of the 16-bit weights (3), inputs staged through
+    # shared memory by bulk asynchronous copies (4). Same arithmetic: the state must come out bit for bit the same.
+    sizes = RAGGED + [8 * 256 * 5 + 77]  # more than a few whole 8-tile chunks for the staged form
+    base = Pair(sizes, [n < 300 for n in sizes], gd, pd, seed=17, grad_std=1.0)
+    base.step(ox.StepConfig(max_grad_norm=1.0, loss_scale=4.0, max_grad_value=3.0))
+    want = base.gpu_state()
+    base.close()
+    monkeypatch.setenv("OXZ_ADAM_VARIANT", variant)
+    other = Pair(sizes, [n < 300 for n in sizes], gd, pd, seed=17, grad_std=1.0)
+    other.step(ox.StepConfig(max_grad_norm=1.0, loss_scale=4.0, max_grad_value=3.0))
+    got = other.gpu_state()
+    other.close()
+    for key in want:
+        for i, (a, b) in enumerate(zip(got[key], want[key])):
+            assert np.array_equal(bits(a), bits(b)), (key, i)
+
+
 @pytest.mark.parametrize("gd", [ox.BF16, ox.F16, ox.F32])
 def test_per_tensor_norms_name_the_offending_tensors(gd):
     # grad_norm_for_tensor for every parameter (src/trainer.rs:933-937), as diagnose_bad_gradients reads it after a
