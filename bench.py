@@ -342,7 +342,13 @@ class Checker:
                     eq["work"] = bool(np.array_equal(orc.narrow(p, self.code), w[own]))
                 entry["bit_equal"] = eq
                 if not all(eq.values()):
-                    self.problems.append(f"{self.tensors[i].name}: not bit-equal to the checker: {eq}")
+                    bad = np.flatnonzero(p.view(np.uint32) != after["master"][own].view(np.uint32))
+                    where = {"differing_master_elements": int(bad.size)}
+                    if bad.size:
+                        k = int(bad[0])
+                        where.update(first=k, last=int(bad[-1]), want=float(p[k]), got=float(after["master"][own][k]))
+                    entry["mismatch"] = where
+                    self.problems.append(f"{self.tensors[i].name}: not bit-equal to the checker: {eq} {where}")
             out["sampled"].append(entry)
         return out
 

@@ -124,7 +124,7 @@ def test_both_clips_fire_on_small_gradients_the_second_measures_again():
 
 
 @pytest.mark.parametrize("gd,pd", DTYPES)
-@pytest.mark.parametrize("variant", ["1", "2", "3", "4"])
+@pytest.mark.parametrize("variant", ["1", "2", "3", "4", "5"])
 def test_every_form_of_the_update_kernel_gives_the_same_bits(monkeypatch, variant, gd, pd):
     # OXZ_ADAM_VARIANT: other launch shapes (1, 2), 256-bit stores of the 16-bit weights (3), inputs staged through
     # shared memory by bulk asynchronous copies (4). Same arithmetic: the state must come out bit for bit the same.
