@@ -519,6 +519,7 @@ def run_gpu(args):
     value = P * args.steps / sec
     exchange = {0: "none", 1: "communicator collectives", 2: "peer-memory mailboxes"}[opt.exchange_kind()]
     pull_kernel = {0: None, 1: "k_pull_sumsq", 2: "k_pull_bulk"}[opt.last_pull_kernel()]
+    update_kernel = {0: None, 1: "k_adamw", 2: "k_adamw_wide", 3: "k_adamw_staged"}[opt.last_update_kernel()]
 
     # ---- the check leg (untimed): before anything else touches the gradient buffer
     check = None
@@ -624,7 +625,7 @@ def run_gpu(args):
     replicated = mode == ox.SYNC_REPLICATED
     live = P - (sum(numel[i] for i in gone) if present is not None else 0)  # parameters the kernels touch
     local_params = live if replicated else live / world  # ... of which one rank's update kernel covers these
-    roof = kernel_rooflines(live, world, replicated, es, nrm, upd, peak, pull_kernel, mode == ox.SYNC_SINGLE, args.dtype)
+    roof = kernel_rooflines(live, world, replicated, es, nrm, upd, peak, pull_kernel, update_kernel, mode == ox.SYNC_SINGLE, args.dtype)
     roof["peak_kind"] = peak_kind
     sync_name = args.sync if world > 1 else "single"
     config = workload_config(args, P, T, world, sync_name)
@@ -677,7 +678,7 @@ def run_gpu(args):
 
 
 def kernel_rooflines(live: float, world: int, replicated: bool, es: int, norm_ms: float, update_ms: float, hbm_peak: float,
-                     pull_kernel, single: bool, dtype: str) -> dict:
+                     pull_kernel, update_kernel, single: bool, dtype: str) -> dict:
     """The roofline of the two kernels that carry the step, each against the resource that binds it.
 
     One rank: both are HBM streams (norm es B/param, update 28 B/param). More ranks (sharded): the norm kernel is the
@@ -699,7 +700,7 @@ def kernel_rooflines(live: float, world: int, replicated: bool, es: int, norm_ms
         upd_hbm = (4 + 24 + es) * own + (W - 1) * es * own   # f32 sum in, state, own weights out, the peers' weights landing
         wire_in = wire_out = (W - 1) * es * own
     for name, ms, hbm, wire, what in ((norm_name, norm_ms, norm_hbm, wire_in, "pull (reduce-scatter) + unscale + norm"),
-                                      ("k_adamw", update_ms, upd_hbm, wire_out, "AdamW + push (all-gather)")):
+                                      (update_kernel, update_ms, upd_hbm, wire_out, "AdamW + push (all-gather)")):
         hbm_gbs = hbm / (ms * 1e-3) / 1e9
         wire_gbs = wire / (ms * 1e-3) / 1e9
         f_hbm, f_wire = hbm_gbs / hbm_peak, wire_gbs / NVLINK_MEASURED_GBS
@@ -710,10 +711,11 @@ def kernel_rooflines(live: float, world: int, replicated: bool, es: int, norm_ms
                         "nvlink_frac_of_measured": f_wire, "nvlink_frac_of_nominal": wire_gbs / NVLINK_NOMINAL_GBS})
     top = max(kernels, key=lambda k: k["kernel_ms"])
     if top["bound"] == "hbm":
-        algorithmic = BYTES_UPDATE * own if top["kernel"] == "k_adamw" else es * own
+        is_update = top["work"].startswith("AdamW")
+        algorithmic = BYTES_UPDATE * own if is_update else es * own
         out = {"bound": "hbm", "kernel": top["kernel"], "achieved": top["hbm_gbs"], "peak": hbm_peak, "unit": "GB/s",
                "frac": top["hbm_frac_of_measured_peak"],
-               "traffic": ADAMW_TRAFFIC_RATIO * top["hbm_bytes_per_launch"] if (dtype == "bf16" and top["kernel"] == "k_adamw") else None,
+               "traffic": ADAMW_TRAFFIC_RATIO * top["hbm_bytes_per_launch"] if (dtype == "bf16" and is_update) else None,
                "traffic_source": "ncu capture of nano_dense (one rank) scaled by bytes per launch" if dtype == "bf16" else "not captured",
                "algorithmic_bytes_per_launch": algorithmic if W == 1 else top["hbm_bytes_per_launch"], "kernel_ms": top["kernel_ms"]}
     else:

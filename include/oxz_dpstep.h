@@ -277,6 +277,15 @@ int32_t oxz_plan_launch_geometry(const oxz_plan* plan, int32_t* sm_count, int32_
 #define OXZ_PULL_KERNEL_LOADS 1
 #define OXZ_PULL_KERNEL_BULK 2
 int32_t oxz_plan_last_pull_kernel(const oxz_plan* plan, int32_t* kind);
+/* Which form of the update kernel the most recent step launched: one tile per warp (the default), two tiles per warp
+ * with 256-bit stores of the 16-bit weights (the default with two ranks), or inputs staged through shared memory
+ * (OXZ_ADAM_VARIANT=4|5 in the environment; measured slower, kept for the comparison). All give the same bits. No
+ * reference counterpart: a tuning and test aid. */
+#define OXZ_UPDATE_KERNEL_NONE 0
+#define OXZ_UPDATE_KERNEL_TILE 1
+#define OXZ_UPDATE_KERNEL_WIDE 2
+#define OXZ_UPDATE_KERNEL_STAGED 3
+int32_t oxz_plan_last_update_kernel(const oxz_plan* plan, int32_t* kind);
 /* How the plan's ranks meet for the step's barriers and its small sum: 0 = not at all (one rank), 1 = collectives of
  * the communicator (NCCL all-reduces, or the host rendezvous of a local group), 2 = through mailboxes in peer memory
  * (one kernel per exchange, every wait bounded: OXZ_MAIL_TIMEOUT_MS in the environment, 30000 by default, after which

@@ -150,6 +150,7 @@ SIGNATURES = {
     "oxz_plan_launch_geometry": (C.c_int32, [vp] + [C.POINTER(C.c_int32)] * 3),
     "oxz_plan_last_pull_kernel": (C.c_int32, [vp, C.POINTER(C.c_int32)]),
     "oxz_plan_exchange_kind": (C.c_int32, [vp, C.POINTER(C.c_int32)]),
+    "oxz_plan_last_update_kernel": (C.c_int32, [vp, C.POINTER(C.c_int32)]),
     "oxz_selftest_bounded_wait": (C.c_int32, [C.c_int32, C.c_uint32, C.POINTER(C.c_int32)]),
     "oxz_grad_norms_per_tensor": (C.c_int32, [vp, vp, C.c_double, C.c_double, f64p]),
     "oxz_plan_set_profile": (C.c_int32, [vp, C.c_int32]),

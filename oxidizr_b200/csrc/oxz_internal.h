@@ -183,6 +183,8 @@ int32_t launch_adamw(cudaStream_t s, const LaunchGeom& g, const void* gsrc, int3
                      float* v, const PeerTable& peers, int32_t n_work, int32_t pdt, const TileMap& map,
                      const uint32_t* tile_meta, const uint8_t* present, bool check_present, const DevScalars* scalars,
                      const AdamParams& ap);
+// Which form of the update kernel the calling thread's last launch_adamw took (OXZ_UPDATE_KERNEL_*).
+int32_t last_update_kernel();
 // Packs per-tensor gradients into the flat buffer.
 int32_t launch_flatten(cudaStream_t s, const LaunchGeom& g, void* flat, int32_t dt, uint32_t n_tiles,
                        const uint32_t* tile_meta, const uint64_t* d_offsets, const uint64_t* d_numel,
@@ -279,6 +281,7 @@ struct oxz_plan {
     std::vector<uint8_t> early_done;   // per bucket
     uint32_t early_groups = 0;         // partial-sum groups already written this step
     int32_t last_pull_kernel = 0;      // OXZ_PULL_KERNEL_* of the most recent peer pull
+    int32_t last_update_kernel = 0;    // OXZ_UPDATE_KERNEL_* of the most recent update
     double early_scale = 0.0, early_clamp = 0.0;
 
     // step bookkeeping

@@ -246,10 +246,13 @@ __global__ void __cluster_dims__(CLUSTER, 1, 1) __launch_bounds__(THREADS)
 
 // Every tensor present, 16-bit gradients: the shard is one contiguous stream, read 256 bits per lane (16 elements),
 // VEC such loads in flight per thread. Library-owned memory, so 32-byte alignment holds.
-template <int DT, int VEC>
+// CHECK: some tensor has no gradient this step; every vector (16 lanes share a tile) looks its tile's tensor up and
+// leaves the vector out when that tensor is absent or the tile is padding. The lookups are issued with the loads.
+template <int DT, int VEC, bool CHECK>
 __global__ void __cluster_dims__(CLUSTER, 1, 1) __launch_bounds__(THREADS)
     k_sumsq_stream16(const uint16_t* __restrict__ grads, uint64_t first, uint64_t end, float inv_scale, float clamp_hi,
-                     int clamp_on, double* __restrict__ partials) {
+                     int clamp_on, double* __restrict__ partials, TileMap map, const uint32_t* __restrict__ tile_meta,
+                     const uint8_t* __restrict__ present) {
     static_assert(DT == OXZ_BF16 || DT == OXZ_F16, "16-bit gradients only");
     NormAcc a;
     const uint64_t nvec = (end - first) / 16;  // the range is a whole number of 256-element tiles
@@ -258,15 +261,23 @@ __global__ void __cluster_dims__(CLUSTER, 1, 1) __launch_bounds__(THREADS)
     for (uint64_t i = static_cast<uint64_t>(blockIdx.x) * THREADS + threadIdx.x; i < nvec; i += stride * VEC) {
         uint32_t w[VEC][8];
         bool on[VEC];
+        uint32_t meta[VEC];
 #pragma unroll
         for (int j = 0; j < VEC; j++) {
             const uint64_t v = i + static_cast<uint64_t>(j) * stride;
             on[j] = v < nvec;
-            if (on[j])
+            if (on[j]) {
                 asm volatile("ld.global.cs.v8.u32 {%0,%1,%2,%3,%4,%5,%6,%7}, [%8];"
                              : "=r"(w[j][0]), "=r"(w[j][1]), "=r"(w[j][2]), "=r"(w[j][3]), "=r"(w[j][4]), "=r"(w[j][5]),
                                "=r"(w[j][6]), "=r"(w[j][7])
                              : "l"(base + v * 16));
+                if constexpr (CHECK) meta[j] = __ldg(&tile_meta[flat_tile(map, static_cast<uint32_t>((first + v * 16) / TILE))]);
+            }
+        }
+        if constexpr (CHECK) {
+#pragma unroll
+            for (int j = 0; j < VEC; j++)
+                if (on[j]) on[j] = meta[j] != PAD_TILE && __ldg(&present[meta[j] & 0xffffffu]) != 0;
         }
 #pragma unroll
         for (int j = 0; j < VEC; j++) {
@@ -1230,10 +1241,13 @@ __global__ void __launch_bounds__(THREADS, 3)
 
 // ---------------------------------------------------------------- launchers
 
-static int adam_variant() {  // read at every launch, so that a test can compare the forms within one process
+static int adam_variant() {  // read at every launch, so that a test can compare the forms within one process; -1: not set
     const char* e = getenv("OXZ_ADAM_VARIANT");
-    return e ? atoi(e) : 0;
+    return e ? atoi(e) : -1;
 }
+
+static thread_local int32_t g_last_update_kernel = 0;
+int32_t last_update_kernel() { return g_last_update_kernel; }
 
 static int adam_blocks_per_sm(int variant) { return variant == 1 ? 4 : variant == 2 ? 2 : 3; }
 
@@ -1269,7 +1283,8 @@ int32_t query_geom(int device, LaunchGeom* g) {
         (const void*)k_sumsq<OXZ_F32, 4, false>,  (const void*)k_sumsq<OXZ_BF16, 4, false>, (const void*)k_sumsq<OXZ_F16, 4, false>,
         (const void*)k_sumsq<OXZ_F32, 4, true>,   (const void*)k_sumsq<OXZ_BF16, 4, true>,  (const void*)k_sumsq<OXZ_F16, 4, true>,
         (const void*)k_sumsq_plain<OXZ_F32>, (const void*)k_sumsq_plain<OXZ_BF16>, (const void*)k_sumsq_plain<OXZ_F16>,
-        (const void*)k_sumsq_stream16<OXZ_BF16, 2>, (const void*)k_sumsq_stream16<OXZ_F16, 2>};
+        (const void*)k_sumsq_stream16<OXZ_BF16, 2, false>, (const void*)k_sumsq_stream16<OXZ_F16, 2, false>,
+        (const void*)k_sumsq_stream16<OXZ_BF16, 2, true>, (const void*)k_sumsq_stream16<OXZ_F16, 2, true>};
     for (const void* f : funcs) {
         const int m = max_cluster_blocks(f, nb);
         if (m < nb) nb = m;
@@ -1321,16 +1336,14 @@ static int32_t launch_sumsq_c(cudaStream_t s, const LaunchGeom& g, const void* g
                               int32_t clamp_on, double* partials) {
     constexpr int ILP = 4;
     dim3 grid(g.norm_blocks), block(THREADS);
-    if constexpr (!CHECK) {
-        // measured on B200 (2.47 GB of bf16): 0.383 ms with two 256-bit loads in flight per thread, 0.397 ms with
-        // four, 0.420 ms for the tile-wise 128-bit form
-        if (dt != OXZ_F32) {
-            const uint64_t first = static_cast<uint64_t>(map.first_tile) * TILE, end = static_cast<uint64_t>(map.n_local_tiles) * TILE;
-            const uint16_t* g16 = static_cast<const uint16_t*>(grads);
-            if (dt == OXZ_BF16) k_sumsq_stream16<OXZ_BF16, 2><<<grid, block, 0, s>>>(g16, first, end, inv_scale, clamp_hi, clamp_on, partials);
-            else k_sumsq_stream16<OXZ_F16, 2><<<grid, block, 0, s>>>(g16, first, end, inv_scale, clamp_hi, clamp_on, partials);
-            return check_launch("k_sumsq_stream16");
-        }
+    // measured on B200 (2.47 GB of bf16): 0.383 ms with two 256-bit loads in flight per thread, 0.397 ms with
+    // four, 0.420 ms for the tile-wise 128-bit form (0.63 ms when that form also looks the tensors' flags up)
+    if (dt != OXZ_F32) {
+        const uint64_t first = static_cast<uint64_t>(map.first_tile) * TILE, end = static_cast<uint64_t>(map.n_local_tiles) * TILE;
+        const uint16_t* g16 = static_cast<const uint16_t*>(grads);
+        if (dt == OXZ_BF16) k_sumsq_stream16<OXZ_BF16, 2, CHECK><<<grid, block, 0, s>>>(g16, first, end, inv_scale, clamp_hi, clamp_on, partials, map, tile_meta, present);
+        else k_sumsq_stream16<OXZ_F16, 2, CHECK><<<grid, block, 0, s>>>(g16, first, end, inv_scale, clamp_hi, clamp_on, partials, map, tile_meta, present);
+        return check_launch("k_sumsq_stream16");
     }
     switch (dt) {
         case OXZ_F32: k_sumsq<OXZ_F32, ILP, CHECK><<<grid, block, 0, s>>>(grads, map, tile_meta, present, inv_scale, clamp_hi, clamp_on, partials); break;
@@ -1550,12 +1563,17 @@ static int32_t launch_adamw_g(cudaStream_t s, const LaunchGeom& g, const void* g
                               const PeerTable& peers, int32_t n_work, int32_t pdt, const TileMap& map,
                               const uint32_t* tile_meta, const uint8_t* present, const DevScalars* scalars,
                               const AdamParams& ap) {
-    const int variant = adam_variant();
+    int variant = adam_variant();
+    // Not set: with two ranks and 16-bit weights the wide-store form (its update is HBM-bound with the push riding along,
+    // and two tiles per warp at two blocks per SM stream it 4 % faster: 3.05 against 3.19 ms on the 1.24 B set); the
+    // one-tile form everywhere else (one rank: 5.40 against 6.45 ms; four ranks, wire-bound: 2.93 against 2.97 ms).
+    if (variant < 0) variant = (n_work == 2 && pdt != OXZ_F32) ? 3 : 0;
     // OXZ_ADAM_VARIANT=4: the shared-memory-staged form, where it applies (one rank, every tensor present, the whole
     // range: local and flat tiles coincide). Measured against the direct loads, not the default.
     // (5: the same with four stages instead of three.)
     if ((variant == 4 || variant == 5) && !CHECK && n_work <= 1 && map.first_tile == 0 && map.tiles_per_shard == map.tiles_per_bucket && map.rank == 0) {
         void* work = n_work ? peers.work[0] : nullptr;
+        g_last_update_kernel = OXZ_UPDATE_KERNEL_STAGED;
 #define OXZ_STAGED(PDT) \
         (variant == 4 ? launch_adamw_staged<GDT, PDT, 3>(s, g, gsrc, master, m, v, work, map.n_local_tiles, tile_meta, scalars, ap) \
                       : launch_adamw_staged<GDT, PDT, 4>(s, g, gsrc, master, m, v, work, map.n_local_tiles, tile_meta, scalars, ap))
@@ -1570,11 +1588,13 @@ static int32_t launch_adamw_g(cudaStream_t s, const LaunchGeom& g, const void* g
     // OXZ_ADAM_VARIANT=3: 256-bit stores of the 16-bit working weights (two tiles per warp)
     if (variant == 3 && pdt != OXZ_F32 && n_work >= 1) {
         dim3 grid2(g.sm_count * 2), block(THREADS);
+        g_last_update_kernel = OXZ_UPDATE_KERNEL_WIDE;
         if (pdt == OXZ_BF16) k_adamw_wide<GDT, OXZ_BF16, CHECK><<<grid2, block, 0, s>>>(gsrc, master, m, v, peers, n_work, map, tile_meta, present, scalars, ap);
         else k_adamw_wide<GDT, OXZ_F16, CHECK><<<grid2, block, 0, s>>>(gsrc, master, m, v, peers, n_work, map, tile_meta, present, scalars, ap);
         return check_launch("k_adamw_wide");
     }
     dim3 grid(g.adam_blocks);
+    g_last_update_kernel = OXZ_UPDATE_KERNEL_TILE;
     switch (pdt) {
         case OXZ_F32: launch_adamw_v<GDT, OXZ_F32, CHECK>(variant, grid, s, gsrc, master, m, v, peers, n_work, map, tile_meta, present, scalars, ap); break;
         case OXZ_BF16: launch_adamw_v<GDT, OXZ_BF16, CHECK>(variant, grid, s, gsrc, master, m, v, peers, n_work, map, tile_meta, present, scalars, ap); break;

@@ -844,6 +844,7 @@ int32_t oxz_step_async(oxz_plan* p, oxz_comm* comm, const oxz_hyper* h, const ui
                                  n_work, p->pdt, map, p->d_tile_meta, p->d_present, some_absent, p->d_scalars, ap));
             OXZ_CUDA(mark(4));
         }
+        p->last_update_kernel = last_update_kernel();
         if (p->mode == OXZ_SYNC_NCCL) {
             const size_t ps = dtype_size(p->pdt);
             ncclResult_t rc = api->GroupStart();
@@ -997,6 +998,14 @@ int32_t oxz_plan_last_pull_kernel(const oxz_plan* p, int32_t* kind) {
     return oxz::guarded("oxz_plan_last_pull_kernel", [&]() -> int32_t {
         if (!p || !kind) return fail(OXZ_ERR_INVALID, "oxz_plan_last_pull_kernel: null argument");
         *kind = p->last_pull_kernel;
+        return OXZ_OK;
+    });
+}
+
+int32_t oxz_plan_last_update_kernel(const oxz_plan* p, int32_t* kind) {
+    return oxz::guarded("oxz_plan_last_update_kernel", [&]() -> int32_t {
+        if (!p || !kind) return fail(OXZ_ERR_INVALID, "oxz_plan_last_update_kernel: null argument");
+        *kind = p->last_update_kernel;
         return OXZ_OK;
     });
 }

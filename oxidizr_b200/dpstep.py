@@ -807,6 +807,12 @@ class DpOptimizer:
         check(lib().oxz_plan_last_pull_kernel(self._h, C.byref(v)))
         return v.value
 
+    def last_update_kernel(self) -> int:
+        """0 none yet, 1 k_adamw (one tile per warp), 2 k_adamw_wide (256-bit weight stores), 3 k_adamw_staged."""
+        v = C.c_int32()
+        check(lib().oxz_plan_last_update_kernel(self._h, C.byref(v)))
+        return v.value
+
     def exchange_kind(self) -> int:
         """How the ranks meet for the step's barriers and small sum: 0 one rank, 1 the communicator's collectives,
         2 mailboxes in peer memory."""

@@ -405,6 +405,23 @@ def test_the_wide_push_lands_the_same_weights_on_every_rank(monkeypatch, kind, w
     g.close()
 
 
+@pytest.mark.skipif(gpu_count() < 2, reason="needs two GPUs: real peer memory")
+def test_pull_and_push_over_real_peer_memory_beyond_l2():
+    """Two rank threads of one process, one GPU each, meeting on the host: the bulk-copy pull reads the other GPU's
+    gradients over NVLink and the update stores the weights into the other GPU's buffer, on tensors larger than the
+    L2 cache (100 M parameters: 200 MB of gradients per rank), bit for bit against the checker. One process and no
+    kernel that waits on another: this is the case a profiler capture of the two peer kernels runs on."""
+    numel = [60_000_000, 2048, 40_000_000 + 77]
+    g = Group(2, [0, 1], "local", seed=27, bucket_bytes=0, numel=numel, no_decay=[False, True, False])
+    out, ref = g.step(ox.StepConfig(max_grad_norm=1e9, eps=1e-8))
+    for res, _ in out:
+        assert (res.overflow, res.applied, res.timestep) == (0, 1, 1)
+        assert abs(res.grad_norm - ref.grad_norm) <= 1e-5 * ref.grad_norm
+    assert {opt.last_pull_kernel() for opt in g.opts} == {2} and {opt.last_update_kernel() for opt in g.opts} == {2}
+    g.assert_state(exact=True)
+    g.close()
+
+
 @pytest.mark.parametrize("kind,world,devices", layouts())
 def test_exchange_kind_follows_the_communicator(kind, world, devices):
     g = Group(world, devices, kind, seed=25)
