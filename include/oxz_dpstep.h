@@ -178,12 +178,15 @@ int32_t oxz_state_timestep(const oxz_plan* plan, uint64_t* applied_steps); /* op
  * 62-74): SafeTensors keyed `<name>.exp_avg`, `<name>.exp_avg_sq`, `<name>.master` (F32; master only for parameters
  * narrower than f32) and `__step` (F64), metadata format = "oxidizr-optimizer". names[i] is tensor i's checkpoint name,
  * ndim[i] its rank and dims its shapes back to back. Collective with more than one rank: the slices are merged bit
- * for bit and rank 0 writes. The write is atomic (temporary file, then rename). Blocking. */
+ * for bit and rank 0 writes. The write is atomic (temporary file, then rename), and every rank returns the same answer:
+ * a file error on the writing rank is an error on all of them. Blocking. */
 int32_t oxz_optimizer_save(oxz_plan* plan, oxz_comm* comm, const char* path, const char* const* names,
                            const uint32_t* ndim, const uint64_t* dims);
 /* Reads such a file into the plan's state (src/checkpoint_set/optimizer_io.rs:113-137): strict - an unknown name, a
- * missing key, a shape or dtype mismatch is an error and the state stays unchanged. Every rank reads the file and keeps
- * the elements it owns, so a file written at one world size loads at another. Blocking. */
+ * missing key, a shape or dtype mismatch, or a file shorter than its header says is found before anything is loaded and
+ * leaves the state unchanged. A read or copy error after those checks (the disk or the device failing midway) leaves the
+ * state partly loaded: load again, or create the plan afresh. Every rank reads the file and keeps the elements it owns, so
+ * a file written at one world size loads at another. Blocking. */
 int32_t oxz_optimizer_load(oxz_plan* plan, const char* path, const char* const* names, const uint32_t* ndim,
                            const uint64_t* dims);
 

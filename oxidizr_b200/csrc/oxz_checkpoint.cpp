@@ -75,13 +75,13 @@ float* array_of(oxz_plan* p, int kind) {
 
 // The whole of one tensor's state on the host: this rank's slices, merged with the other ranks' through a sum of the
 // raw 32-bit patterns (exactly one rank contributes non-zero bits per element, so every bit survives, -0.0 included).
-int32_t gather_tensor(oxz_plan* p, oxz_comm* comm, int kind, uint64_t t, std::vector<uint32_t>& host) {
+// `d` is device scratch of at least n words that every rank allocated (and agreed on) before the first gather, so no
+// rank can drop out of a collective here for want of memory.
+int32_t gather_tensor(oxz_plan* p, oxz_comm* comm, int kind, uint64_t t, std::vector<uint32_t>& host, uint32_t* d) {
     const uint64_t n = p->numel[t];
     host.assign(n, 0u);
     if (n == 0) return OXZ_OK;
     if (p->world == 1) return oxz_state_export(p, kind, t, host.data());
-    uint32_t* d = nullptr;
-    OXZ_CUDA(cudaMalloc((void**)&d, n * 4));
     OXZ_CUDA(cudaMemsetAsync(d, 0, n * 4, p->stream));
     const float* arr = array_of(p, kind);
     const uint64_t lo = p->offset[t], hi = lo + n, be = p->bucket_tiles * TILE, full = be / (uint64_t)p->world;
@@ -99,8 +99,22 @@ int32_t gather_tensor(oxz_plan* p, oxz_comm* comm, int kind, uint64_t t, std::ve
         if (e == cudaSuccess) e = cudaStreamSynchronize(p->stream);
         if (e != cudaSuccess) st = fail(OXZ_ERR_CUDA, "oxz_optimizer_save: %s", cudaGetErrorString(e));
     }
-    cudaFree(d);
     return st;
+}
+
+// Every rank hands in whether it failed; all leave knowing whether any did. One word through the communicator.
+int32_t agree_on_failure(oxz_plan* p, oxz_comm* comm, bool failed, bool* any_failed) {
+    *any_failed = failed;
+    if (p->world == 1) return OXZ_OK;
+    uint32_t* d_flag = reinterpret_cast<uint32_t*>(static_cast<char*>(comm->d_small) + 128);
+    const uint32_t mine = failed ? 1u : 0u;
+    uint32_t all = 0;
+    OXZ_CUDA(cudaMemcpyAsync(d_flag, &mine, 4, cudaMemcpyHostToDevice, p->stream));
+    OXZ_TRY(comm_stream_allreduce_u32(comm, d_flag, 1, p->stream));
+    OXZ_CUDA(cudaMemcpyAsync(&all, d_flag, 4, cudaMemcpyDeviceToHost, p->stream));
+    OXZ_CUDA(cudaStreamSynchronize(p->stream));
+    *any_failed = all != 0;
+    return OXZ_OK;
 }
 
 int32_t check_call(oxz_plan* p, oxz_comm* comm, const char* path, const char* const* names, const uint32_t* ndim,
@@ -178,12 +192,26 @@ int32_t oxz_optimizer_save(oxz_plan* p, oxz_comm* comm, const char* path, const 
         }
         std::vector<uint32_t> host;
         int32_t st = OXZ_OK;
+        // the merge scratch, sized for the largest tensor: allocated by every rank, and agreed on, before any gather
+        uint32_t* d_merge = nullptr;
+        if (p->world > 1) {
+            uint64_t widest = 1;
+            for (uint64_t i = 0; i < p->T; i++) widest = p->numel[i] > widest ? p->numel[i] : widest;
+            const cudaError_t e = cudaMalloc((void**)&d_merge, widest * 4);
+            if (e != cudaSuccess) cudaGetLastError();
+            bool any = false;
+            st = agree_on_failure(p, comm, e != cudaSuccess, &any);
+            if (st == OXZ_OK && any)
+                st = e != cudaSuccess ? fail(OXZ_ERR_CUDA, "oxz_optimizer_save: no device memory for the merge of %llu elements: %s", (unsigned long long)widest, cudaGetErrorString(e))
+                                      : fail(OXZ_ERR_STATE, "oxz_optimizer_save: another rank has no device memory for the merge; nothing was written");
+        }
         for (uint64_t i = 0; i < p->T && st == OXZ_OK; i++) {
             for (int k = 0; k < (has_master ? 3 : 2) && st == OXZ_OK; k++) {
-                st = gather_tensor(p, comm, kinds[k], i, host);
+                st = gather_tensor(p, comm, kinds[k], i, host, d_merge);
                 if (st == OXZ_OK && f && !host.empty() && fwrite(host.data(), 4, host.size(), f) != host.size()) io_failed();
             }
         }
+        if (d_merge) cudaFree(d_merge);
         if (writer) {
             const double step = (double)p->timestep;
             if (st == OXZ_OK && f && fwrite(&step, 8, 1, f) != 1) io_failed();
@@ -196,6 +224,17 @@ int32_t oxz_optimizer_save(oxz_plan* p, oxz_comm* comm, const char* path, const 
                 oxz_set_last_error(io_text.c_str());
                 st = io;
             }
+        }
+        // Only the writing rank sees a file error. Every rank must leave with the same answer, or the others would
+        // take a checkpoint that does not exist for written: one more word crosses the ranks (when the collectives
+        // themselves still work).
+        if (p->world > 1 && (st == OXZ_OK || (writer && st == io && io != OXZ_OK))) {
+            const std::string mine = st != OXZ_OK ? std::string(oxz_last_error()) : std::string();
+            bool any = false;
+            const int32_t agreed = agree_on_failure(p, comm, st != OXZ_OK, &any);
+            if (agreed != OXZ_OK) return agreed;
+            if (st != OXZ_OK) oxz_set_last_error(mine.c_str());
+            else if (any) st = fail(OXZ_ERR_INVALID, "optimizer state file '%s': the writing rank could not write it (its own error text says why); nothing was saved", path);
         }
         return st;
     });
