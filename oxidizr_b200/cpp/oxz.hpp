@@ -178,6 +178,19 @@ class RowLayout {
         return {out.epoch, out.row};
     }
     DataPosition batch_start(DataPosition pos) const { return pos.row + batch_size() > l_.num_rows ? DataPosition{pos.epoch + 1, 0} : pos; }
+    // One rank's rows of the next global batch. With `order` = (epoch, that epoch's permutation) the row at each slot is
+    // order.second[slot], as EpochOrder::row does under RowOrder::Shuffled (src/data/rows.rs:240-256); the permutation is
+    // the caller's epoch_permutation(num_rows, seed, epoch) (src/data/rows.rs:258-263). Returns the position after the batch.
+    DataPosition next_window(DataPosition pos, uint64_t rank, std::vector<uint64_t>& rows,
+                             const std::pair<uint64_t, std::vector<uint32_t>>* order = nullptr) const {
+        rows.resize(l_.rank_batch_size);
+        oxz_data_position next{};
+        if (order) check(oxz_rows_next_window_ordered(&l_, {pos.epoch, pos.row}, rank, 1, 0, nullptr, 0, order->first, order->second.data(),
+                                                      order->second.size(), rows.data(), nullptr, nullptr, &next));
+        else check(oxz_rows_next_window(&l_, {pos.epoch, pos.row}, rank, 1, 0, nullptr, 0, rows.data(), nullptr, nullptr, &next));
+        return {next.epoch, next.row};
+    }
+    uint64_t batch_epoch(DataPosition pos) const { uint64_t e = 0; check(oxz_rows_batch_epoch(&l_, {pos.epoch, pos.row}, &e)); return e; }
     DataPosition position_after_steps(uint64_t steps, uint64_t grad_accum) const { return advance({}, steps * grad_accum); }
     const oxz_row_layout& raw() const { return l_; }
   private:
@@ -324,6 +337,12 @@ class LitDataLoader {
     }
     LitDataLoader& with_document_mask(uint32_t separator_id) { check(oxz_loader_set_document_mask(h_, 1, separator_id)); return *this; }
     LitDataLoader& with_prefetch(uint32_t depth) { check(oxz_loader_set_prefetch(h_, depth)); return *this; }
+    // with_row_order(RowOrder::Shuffled{seed}) (src/data/construction.rs:140) with the epoch's permutation made by the
+    // caller; the loader keeps two epochs' orders. An empty permutation returns to stream order.
+    LitDataLoader& set_row_order(uint64_t epoch, const std::vector<uint32_t>& perm) {
+        check(oxz_loader_set_row_order(h_, epoch, perm.empty() ? nullptr : perm.data(), perm.size()));
+        return *this;
+    }
     uint64_t num_rows() const { uint64_t n = 0; check(oxz_loader_num_rows(h_, &n)); return n; }
     std::vector<uint64_t> source_rows() const {
         uint32_t n = 0;
@@ -388,6 +407,15 @@ class DpOptimizer {
         check(oxz_step(h_, comm_ ? comm_->handle() : nullptr, &h, present ? present->data() : nullptr, loss, loss ? 1 : 0, &r));
         return r;
     }
+    // grad_norm_for_tensor for every parameter (src/trainer.rs:933-937), what diagnose_bad_gradients reads after a
+    // non-finite norm (src/trainer.rs:990-1020); -1 marks a tensor no rank had a gradient for. Collective.
+    std::vector<double> grad_norms_per_tensor(double loss_scale = NONE, double max_grad_value = NONE) {
+        std::vector<double> norms(numel_.size());
+        check(oxz_grad_norms_per_tensor(h_, comm_ ? comm_->handle() : nullptr, loss_scale, max_grad_value, norms.data()));
+        return norms;
+    }
+    int32_t exchange_kind() const { int32_t k = 0; check(oxz_plan_exchange_kind(h_, &k)); return k; }
+    int32_t last_update_kernel() const { int32_t k = 0; check(oxz_plan_last_update_kernel(h_, &k)); return k; }
     oxz_plan* handle() const { return h_; }
   private:
     oxz_plan* h_ = nullptr;

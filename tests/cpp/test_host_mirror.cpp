@@ -116,6 +116,42 @@ static void advance_matches_one_batch_at_a_time() {
     EXPECT(throws([] { RowLayout::create(3, 4); }, "fewer than batch_size 4"));
 }
 
+// src/data/rows.rs:240-256 and :376-411: under a shuffled order the row at a slot is the epoch's permutation at that
+// slot; an epoch reads every row once; the ranks' windows are disjoint; the wrong epoch's order is refused.
+static void a_shuffled_epoch_reads_the_callers_permutation() {
+    const uint64_t rows = 12;
+    RowLayout l = RowLayout::for_world(rows, 2, 2);
+    auto perm_of = [&](uint64_t epoch) {
+        std::vector<uint32_t> p(rows);
+        for (uint64_t i = 0; i < rows; i++) p[i] = (uint32_t)((i * 5 + 3 * epoch + 1) % rows);  // 5 is coprime to 12
+        return p;
+    };
+    DataPosition pos[2] = {{}, {}};
+    for (uint64_t epoch = 0; epoch < 2; epoch++) {
+        std::vector<int> seen(rows, 0);
+        for (int batch = 0; batch < 3; batch++)
+            for (uint64_t rank = 0; rank < 2; rank++) {
+                EXPECT(l.batch_epoch(pos[rank]) == epoch);
+                std::pair<uint64_t, std::vector<uint32_t>> order{epoch, perm_of(epoch)};
+                std::vector<uint64_t> got;
+                const DataPosition start = l.batch_start(pos[rank]);
+                pos[rank] = l.next_window(pos[rank], rank, got, &order);
+                for (uint64_t k = 0; k < 2; k++) {
+                    EXPECT(got[k] == order.second[start.row + rank * 2 + k]);
+                    seen[got[k]]++;
+                }
+            }
+        for (uint64_t r = 0; r < rows; r++) EXPECT(seen[r] == 1);
+    }
+    std::pair<uint64_t, std::vector<uint32_t>> wrong{5, perm_of(5)};
+    std::vector<uint64_t> got;
+    EXPECT(throws([&] { l.next_window({}, 0, got, &wrong); }, "reads epoch 0 and the row order given is epoch 5"));
+    std::vector<uint32_t> twice = perm_of(0);
+    twice[1] = twice[0];
+    EXPECT(oxz_rows_check_permutation(twice.data(), twice.size()) == OXZ_ERR_DATA);
+    EXPECT(oxz_rows_check_permutation(perm_of(1).data(), rows) == OXZ_OK);
+}
+
 // src/dp/resume.rs:76-125
 static void the_meta_world_size_gates_a_resume() {
     const std::string dir = std::string("/tmp/oxz-mirror-meta-") + std::to_string((long)getpid());
@@ -232,6 +268,10 @@ static void the_step_on_the_gpu() {
     opt.export_tensor(OXZ_STATE_MASTER, 0, after);
     EXPECT(r.overflow == 1 && r.applied == 0 && !std::isfinite(r.grad_norm) && opt.timestep() == 1);
     EXPECT(memcmp(before, after, sizeof before) == 0);
+    // diagnose_bad_gradients (src/trainer.rs:990-1020): the per-tensor norms name the tensor that overflowed
+    const std::vector<double> per = opt.grad_norms_per_tensor();
+    EXPECT(std::isinf(per[0]) && per[1] == 0.0);
+    EXPECT(opt.exchange_kind() == OXZ_EXCHANGE_NONE && opt.last_update_kernel() == OXZ_UPDATE_KERNEL_TILE);
     // the trainer's half of the step with a scaler: overflow halves the scale, the step does not count
     LossScaleConfig lc; lc.initial = 1048576.0;
     LitTrainerStep trainer(opt, LrPlan(3e-4, OXZ_LR_CONSTANT, 0, 0, 0.0), lc);
@@ -246,6 +286,7 @@ int main(int argc, char** argv) {
     the_guard_skips_the_scripted_spike();
     lr_plan_matches_the_closed_form();
     advance_matches_one_batch_at_a_time();
+    a_shuffled_epoch_reads_the_callers_permutation();
     ranks_sum_and_the_first_error_wins();
     the_meta_world_size_gates_a_resume();
     the_loader_reads_sources_ranges_and_mixtures_in_order();
