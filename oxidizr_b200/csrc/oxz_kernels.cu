@@ -555,11 +555,23 @@ __global__ void __cluster_dims__(CLUSTER, 1, 1) __launch_bounds__(THREADS)
                          ::"r"(smem_addr(bulk_smem + stage * STAGE_BYTES + r * BULK_BYTES)),
                            "l"(static_cast<const unsigned char*>(peers.grads[r]) + byte0), "r"(BULK_BYTES), "r"(b) : "memory");
     };
+    // With absent tensors (check): a chunk none of whose tiles takes part is not fetched at all - an expert no rank
+    // routed to is millions of elements that need not cross NVLink. Its first and last tile decide: both left out and
+    // of one tensor (or both padding) means every tile between them is too; anything else is fetched and sorted out
+    // tile by tile below. Every thread evaluates it alike, so the block agrees without talking.
+    auto chunk_live = [&](uint32_t chunk) -> bool {
+        if (!check) return true;
+        const uint32_t ft0 = flat_tile(map, map.first_tile + chunk * BULK_TILES);
+        const uint32_t m0 = __ldg(&tile_meta[ft0]), m7 = __ldg(&tile_meta[ft0 + BULK_TILES - 1]);
+        const bool out0 = m0 == PAD_TILE || !__ldg(&present[m0 & 0xffffffu]);
+        const bool out7 = m7 == PAD_TILE || !__ldg(&present[m7 & 0xffffffu]);
+        return !(out0 && out7 && m0 == m7);
+    };
     // Every thread keeps the same books: which stages have copies in flight, and the phase each stage completes next.
     uint32_t pending = 0, phase = 0;
     for (int s = 0; s < STAGES; s++) {
         const uint32_t c = blockIdx.x + static_cast<uint32_t>(s) * gridDim.x;
-        if (c < n_chunks) {
+        if (c < n_chunks && chunk_live(c)) {
             if (threadIdx.x == 0) issue(c, s);
             pending |= 1u << s;
         }
@@ -567,6 +579,16 @@ __global__ void __cluster_dims__(CLUSTER, 1, 1) __launch_bounds__(THREADS)
     int stage = 0;
     bool ok = true;
     for (uint32_t c = blockIdx.x; c < n_chunks; c += gridDim.x) {
+        if (!(pending & (1u << stage))) {
+            // nothing was fetched for this chunk: nothing to sum; the stage takes the chunk STAGES rounds ahead
+            const uint32_t ahead = c + static_cast<uint32_t>(STAGES) * gridDim.x;
+            if (ahead < n_chunks && chunk_live(ahead)) {
+                if (threadIdx.x == 0) issue(ahead, stage);
+                pending |= 1u << stage;
+            }
+            if (++stage == STAGES) stage = 0;
+            continue;
+        }
         // wait_limit is BULK_SPIN_LIMIT in production; a test lowers it to see the run-out path without any fault
         // the verdict must be the block's, not the thread's: a thread that saw the copies land on its last poll must
         // not go on to a barrier its neighbours never reach
@@ -605,7 +627,7 @@ __global__ void __cluster_dims__(CLUSTER, 1, 1) __launch_bounds__(THREADS)
         }
         __syncthreads();  // every warp has read this stage: it may be refilled
         const uint32_t nc = c + static_cast<uint32_t>(STAGES) * gridDim.x;
-        if (nc < n_chunks) {
+        if (nc < n_chunks && chunk_live(nc)) {
             if (threadIdx.x == 0) issue(nc, stage);
             pending |= 1u << stage;
         }
