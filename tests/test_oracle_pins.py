@@ -497,3 +497,50 @@ def test_mixture_rows_known_answers():
     parts = hl.source_train_rows([8, 6], [(0, 6), (8, 12)], 14)
     assert [p.spans for p in parts] == [[(0, 6)], [(8, 12)]]
     assert hl.source_train_rows([3, 2], [(0, 3)], 5)[1] is None
+
+
+def test_default_adamw_form_is_the_conventional_one():
+    """The reference's AdamW arithmetic lives in un-vendored boostr, so no reference number pins its form. What can be
+    pinned is that the checker's DEFAULT switches (decay before the Adam term, eps added after the bias-corrected square
+    root) are the conventional decoupled AdamW - here torch.optim.AdamW in fp32 on the CPU, single-tensor path - to a
+    few ulps over three steps, with a learning rate, decay and eps large enough that the other forms would differ by
+    1e-3 and more. torch forms the first moment as a lerp, so the agreement is close, not bit for bit."""
+    import torch
+    rng = np.random.default_rng(5)
+    n, lr, wd, eps, b1, b2 = 4096, 1e-2, 0.5, 1e-3, 0.9, 0.95
+    p0 = (rng.standard_normal(n) * 0.02).astype(np.float32)
+    grads = [(rng.standard_normal(n) * 1e-2).astype(np.float32) for _ in range(3)]
+    tp = torch.nn.Parameter(torch.from_numpy(p0.copy()))
+    opt = torch.optim.AdamW([tp], lr=lr, betas=(b1, b2), eps=eps, weight_decay=wd, foreach=False, fused=False)
+
+    def run(**switch):
+        st = orc.StepState([p0.copy()], [np.zeros(n, np.float32)], [np.zeros(n, np.float32)], None)
+        for g in grads:
+            orc.step(st, [[g]], orc.F32, orc.StepConfig(lr=lr, beta1=b1, beta2=b2, eps=eps, weight_decay=wd, max_grad_norm=1e9, **switch))
+        return st.master[0].astype(np.float64)
+    for g in grads:
+        tp.grad = torch.from_numpy(g.copy())
+        opt.step()
+    want = tp.detach().numpy().astype(np.float64)
+    scale = np.abs(want) + np.sqrt(np.mean(want ** 2))
+    assert np.max(np.abs(run() - want) / scale) < 2e-6
+    # the switches select forms that are visibly something else
+    assert np.max(np.abs(run(decay_after=1) - want) / scale) > 1e-4
+    assert np.max(np.abs(run(eps_mode=1) - want) / scale) > 1e-4
+
+
+def test_default_clip_coefficient_is_the_conventional_one():
+    """Likewise for the norm clip's coefficient, max_norm / (norm + 1e-6) applied when the norm exceeds max_norm:
+    torch.nn.utils.clip_grad_norm_ on the same values."""
+    import torch
+    rng = np.random.default_rng(6)
+    g = [(rng.standard_normal(n)).astype(np.float32) for n in (1000, 37)]
+    ours = [x.copy() for x in g]
+    norm, coef = orc.clip_gradients(ours, NAN, 0.25)
+    params = [torch.nn.Parameter(torch.zeros(x.size)) for x in g]
+    for p, x in zip(params, g):
+        p.grad = torch.from_numpy(x.copy())
+    total = torch.nn.utils.clip_grad_norm_(params, 0.25, foreach=False)
+    assert abs(float(total) - norm) <= 1e-6 * norm and coef < 1.0
+    for p, x in zip(params, ours):
+        assert np.max(np.abs(p.grad.numpy() - x)) <= 2e-7 * np.max(np.abs(x))
