@@ -43,6 +43,10 @@ BYTES_UPDATE = 28
 # DRAM bytes over algorithmic bytes of k_adamw from one ncu capture of a smaller case of the same kernel
 # (nano_dense, 134 M parameters): 3.7015 GB read+write for 3.7573 GB algorithmic.
 ADAMW_TRAFFIC_RATIO = 3.7015 / 3.7573
+# The same for the update kernel with peers (k_adamw_wide reading the f32 sum, 30 B per owned parameter) from a capture
+# on two GPUs with 50 M owned parameters: 800.84 MB read + 641.82 MB written for 1500.03 MB algorithmic (the part of
+# the write-back still in L2 at the kernel's end weighs more on that small case).
+ADAMW_PEER_TRAFFIC_RATIO = (800.84 + 641.82) / 1500.03
 # NVLink 5 per direction and GPU: nominal, and the peer-copy figure measured on this pool's B200s.
 NVLINK_NOMINAL_GBS, NVLINK_MEASURED_GBS = 900.0, 770.0
 NVLINK_MEASURED_SOURCE = "peer copy per direction measured on this pool (770 GB/s; nominal 900)"
@@ -715,9 +719,16 @@ def kernel_rooflines(live: float, world: int, replicated: bool, es: int, norm_ms
         algorithmic = BYTES_UPDATE * own if is_update else es * own
         out = {"bound": "hbm", "kernel": top["kernel"], "achieved": top["hbm_gbs"], "peak": hbm_peak, "unit": "GB/s",
                "frac": top["hbm_frac_of_measured_peak"],
-               "traffic": ADAMW_TRAFFIC_RATIO * top["hbm_bytes_per_launch"] if (dtype == "bf16" and is_update) else None,
-               "traffic_source": "ncu capture of nano_dense (one rank) scaled by bytes per launch" if dtype == "bf16" else "not captured",
+               "traffic": None, "traffic_source": "not captured",
                "algorithmic_bytes_per_launch": algorithmic if W == 1 else top["hbm_bytes_per_launch"], "kernel_ms": top["kernel_ms"]}
+        if dtype == "bf16" and is_update and W == 1:
+            out["traffic"] = ADAMW_TRAFFIC_RATIO * top["hbm_bytes_per_launch"]
+            out["traffic_source"] = "ncu capture of nano_dense (one rank) scaled by bytes per launch"
+        elif dtype == "bf16" and is_update and not replicated:
+            # the kernel's own 30 B per owned parameter by the two-GPU capture, plus the peers' weights landing here
+            out["traffic"] = ADAMW_PEER_TRAFFIC_RATIO * (4 + 24 + es) * own + (W - 1) * es * own
+            out["traffic_source"] = ("ncu capture of the update kernel on two GPUs (50 M owned parameters) scaled by bytes per "
+                                     "launch, plus the algorithmic bytes of the peers' weights landing in this GPU's memory")
     else:
         out = {"bound": "nvlink", "kernel": top["kernel"], "achieved": top["nvlink_gbs"], "peak": NVLINK_MEASURED_GBS,
                "peak_source": NVLINK_MEASURED_SOURCE, "peak_nominal": NVLINK_NOMINAL_GBS, "unit": "GB/s",
