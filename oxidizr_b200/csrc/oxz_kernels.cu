@@ -1045,7 +1045,7 @@ __global__ void __launch_bounds__(THREADS, 2)
 }
 
 // The update with its four input streams staged through shared memory by 1-D bulk asynchronous copies (cp.async.bulk
-// + mbarrier, no multicast), for one rank with every tensor present: STAGES stages of 8 tiles, one elected thread
+// + mbarrier, each block fetching for itself), for one rank with every tensor present: STAGES stages of 8 tiles, one elected thread
 // issues the four copies of a stage (gradients, master, exp_avg, exp_avg_sq), each warp updates one tile of the stage
 // from shared memory and stores its results straight to global memory. It exists to measure staging against the
 // direct 256-bit loads of k_adamw on the same work; same arithmetic, same bits. Every wait is bounded.
