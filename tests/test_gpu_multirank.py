@@ -422,6 +422,51 @@ def test_pull_and_push_over_real_peer_memory_beyond_l2():
     g.close()
 
 
+ABORT_CHILD = r"""
+import threading, time
+import oxidizr_b200 as ox
+from oxidizr_b200 import ffi
+comms = ox.Communicator.init_all([0, 1])
+opts = [None, None]
+def make(r):
+    opts[r] = ox.DpOptimizer([70001, 300], None, ox.BF16, ox.BF16, world=2, rank=r, device=r, comm=comms[r], bucket_bytes=16384)
+threads = [threading.Thread(target=make, args=(r,)) for r in range(2)]
+[t.start() for t in threads]
+[t.join() for t in threads]
+assert opts[0].exchange_kind() == ffi.EXCHANGE_MAILBOX
+opts[0].step_async(ox.StepConfig())   # rank 1 never joins: rank 0's gate kernel waits for its arrival
+time.sleep(0.3)
+t0 = time.time()
+for c in comms:
+    c.abort()
+try:
+    opts[0].step_wait()
+    print("NO ERROR")
+except ox.OxzError as e:
+    print("STATUS", e.status, "AFTER", round(time.time() - t0, 2), "TIMESTEP", opts[0].timestep)
+"""
+
+
+@pytest.mark.skipif(gpu_count() < 2, reason="needs two GPUs: the peer-memory exchanges run one GPU per rank")
+def test_an_abort_ends_the_wait_for_a_rank_that_never_joins():
+    """src/dp/launch.rs:97-103, 142-150: the first failure aborts the group so that peers blocked in a collective
+    return. Here the collective is the step's opening gate, a kernel polling its mailbox: rank 1 never makes the step
+    (a failure made on the host), rank 0 waits, and oxz_comm_abort from another thread ends the wait at once - well
+    inside the 20 s the wait itself would allow - with OXZ_ERR_ABORTED and nothing applied. A child process with NVLS
+    off, as every test that leaves a rank behind should run; no kernel faults, traps or spins without a bound."""
+    import os
+    import subprocess
+    import sys
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    env = dict(os.environ, NCCL_NVLS_ENABLE="0", OXZ_MAIL_TIMEOUT_MS="20000", PYTHONPATH=root)
+    out = subprocess.run([sys.executable, "-c", ABORT_CHILD], capture_output=True, text=True, timeout=180, env=env, cwd=root)
+    line = [l for l in out.stdout.splitlines() if l.startswith(("STATUS", "NO ERROR"))]
+    assert line, out.stdout + out.stderr
+    words = line[-1].split()
+    assert words[0] == "STATUS" and int(words[1]) == ffi.ERR_ABORTED, line
+    assert float(words[3]) < 5.0 and int(words[5]) == 0, line
+
+
 @pytest.mark.parametrize("kind,world,devices", layouts())
 def test_exchange_kind_follows_the_communicator(kind, world, devices):
     g = Group(world, devices, kind, seed=25)
