@@ -43,6 +43,18 @@ def test_no_gpu_call_fails_loudly_instead_of_falling_back():
         ox.DpOptimizer([10])
 
 
+def test_calls_that_need_device_state_say_so_before_it_exists():
+    # a plan is host-only until oxz_state_alloc: the newer entry points refuse it with a status, not a crash
+    opt = ox.DpOptimizer([10, 300], allocate=False)
+    for call in (opt.grad_norms_per_tensor, opt.exchange_kind, opt.launch_geometry):
+        with pytest.raises(ox.OxzError, match="OXZ_ERR_STATE"):
+            call()
+    assert opt.last_update_kernel() == 0 and opt.last_pull_kernel() == 0
+    with pytest.raises(ox.OxzError, match="limit_ms 0 is outside"):
+        ox.selftest_bounded_wait(0, limit_ms=0)
+    opt.destroy()
+
+
 @pytest.mark.parametrize("world", [1, 2, 3, 8])
 @pytest.mark.parametrize("bucket_bytes", [0, 4096, 1 << 20])
 def test_plan_layout_covers_every_element_once(world, bucket_bytes):
