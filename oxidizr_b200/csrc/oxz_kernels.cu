@@ -1,6 +1,6 @@
 // Hand-written sm_100a kernels of the data-parallel optimizer step.
 //
-// All of them are HBM-bound streaming kernels: no tensor cores, 128-bit coalesced accesses, grids sized in
+// All of them are HBM- or NVLink-bound streaming kernels: no tensor cores, 128- and 256-bit coalesced accesses, grids sized in
 // multiples of the SM count, one 8-element vector per lane and one 256-element tile per warp. A tile never
 // straddles two tensors (tensor starts are tile-aligned), so the group scalars are warp-uniform.
 //
@@ -8,9 +8,16 @@
 //                  reduction through distributed shared memory, one partial per cluster.
 //   k_pull_sumsq   the same fused with the gradient sum over ranks: every rank pulls its tiles from all peers'
 //                  buffers over NVLink with plain 128-bit loads and adds them in f32 in rank order.
+//   k_pull_bulk    the same pull with 1-D bulk asynchronous copies into shared memory (16-bit gradients, 2/4/8 ranks);
+//                  chunks of tensors no rank has a gradient for are not fetched.
 //   k_reduce_partials / k_finalize   partials -> norm, overflow, clip coefficients, all on the device.
+//   k_gate / k_decide   the ranks' barriers and their one small sum through mailboxes in peer memory (ranks on
+//                  distinct GPUs): bounded waits, sums in rank order, the decision fused with the exchange.
 //   k_adamw        clip-scale + bias-corrected AdamW + decoupled decay by group + f32 master and narrow working
 //                  weights; with peers it stores the working weights into every rank's buffer (the all-gather).
+//   k_adamw_wide   the same on two tiles per warp with 256-bit stores of the 16-bit weights (two ranks).
+//   k_adamw_staged the same with its inputs staged through shared memory (kept for the measured comparison).
+//   k_sumsq_tensors   per-tensor sums of squares for the report after a skipped step.
 //   k_flatten      per-tensor gradients -> flat buffer.
 //
 // The update uses explicit round-to-nearest intrinsics so that no multiply-add is contracted: every f32
