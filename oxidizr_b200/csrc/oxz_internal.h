@@ -101,6 +101,7 @@ struct AdamParams {
     float clamp_hi;    // max_grad_value
     int32_t clamp_on;
     int32_t decay_after, eps_mode;
+    int32_t push_hint;  // 0: streaming stores of the working weights (default); 1: plain stores (tuning aid)
     float step_size[MAX_GROUPS];
     float decay_mul[MAX_GROUPS];
 };

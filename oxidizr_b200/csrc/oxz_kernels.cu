@@ -884,6 +884,20 @@ __device__ __forceinline__ void adam1(float& p, float& m, float& v, float g, con
     if (k.decay_after) p = __fmul_rn(p, decay);
 }
 
+template <int PDT>
+__device__ __forceinline__ void pack8(const float (&x)[8], uint32_t (&w)[4]) {
+#pragma unroll
+    for (int i = 0; i < 4; i++) {
+        if constexpr (PDT == OXZ_BF16) {
+            __nv_bfloat162 h = __floats2bfloat162_rn(x[2 * i], x[2 * i + 1]);
+            w[i] = *reinterpret_cast<uint32_t*>(&h);
+        } else {
+            __half2 h = __floats2half2_rn(x[2 * i], x[2 * i + 1]);
+            w[i] = *reinterpret_cast<uint32_t*>(&h);
+        }
+    }
+}
+
 template <int GDT, int PDT, int ILP, int MINB, bool CHECK>
 __global__ void __launch_bounds__(THREADS, MINB)
     k_adamw(const void* __restrict__ gsrc, float* __restrict__ master, float* __restrict__ exp_avg,
@@ -937,7 +951,14 @@ __global__ void __launch_bounds__(THREADS, MINB)
             store8<OXZ_F32>(exp_avg, le, m[j]);
             store8<OXZ_F32>(exp_avg_sq, le, v[j]);
             const uint64_t fe = static_cast<uint64_t>(ftile[j]) * TILE + lane * 8;
-            for (int r = 0; r < n_work; r++) store8<PDT>(peers.work[r], fe, p[j]);
+            if (k.push_hint == 0 || PDT == OXZ_F32) {
+                for (int r = 0; r < n_work; r++) store8<PDT>(peers.work[r], fe, p[j]);
+            } else if constexpr (PDT != OXZ_F32) {
+                uint32_t w[4];
+                pack8<PDT>(p[j], w);
+                for (int r = 0; r < n_work; r++)
+                    *reinterpret_cast<uint4*>(static_cast<uint16_t*>(peers.work[r]) + fe) = make_uint4(w[0], w[1], w[2], w[3]);
+            }
         }
     }
 }
@@ -957,19 +978,6 @@ __device__ __forceinline__ void adam_tile8(float (&p)[8], float (&m)[8], float (
     }
 }
 
-template <int PDT>
-__device__ __forceinline__ void pack8(const float (&x)[8], uint32_t (&w)[4]) {
-#pragma unroll
-    for (int i = 0; i < 4; i++) {
-        if constexpr (PDT == OXZ_BF16) {
-            __nv_bfloat162 h = __floats2bfloat162_rn(x[2 * i], x[2 * i + 1]);
-            w[i] = *reinterpret_cast<uint32_t*>(&h);
-        } else {
-            __half2 h = __floats2half2_rn(x[2 * i], x[2 * i + 1]);
-            w[i] = *reinterpret_cast<uint32_t*>(&h);
-        }
-    }
-}
 
 // The update with the push of 16-bit working weights as 256-bit peer stores. A warp takes two neighbouring tiles per
 // round (the f32 state still moves one 256-bit access per lane and array); the two tiles' packed weights, 16 bytes per
@@ -1623,6 +1631,10 @@ static int32_t launch_adamw_g(cudaStream_t s, const LaunchGeom& g, const void* g
         return check_launch("k_adamw_wide");
     }
     dim3 grid(g.adam_blocks);
+    if (const char* e = getenv("OXZ_ADAM_BLOCKS")) {  // tuning aid: another grid size
+        const int want = atoi(e);
+        if (want > 0) grid = dim3(want);
+    }
     g_last_update_kernel = OXZ_UPDATE_KERNEL_TILE;
     switch (pdt) {
         case OXZ_F32: launch_adamw_v<GDT, OXZ_F32, CHECK>(variant, grid, s, gsrc, master, m, v, peers, n_work, map, tile_meta, present, scalars, ap); break;

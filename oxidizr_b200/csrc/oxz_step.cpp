@@ -675,6 +675,7 @@ int32_t oxz_step_async(oxz_plan* p, oxz_comm* comm, const oxz_hyper* h, const ui
         ap.clamp_hi = ap.clamp_on ? (float)h->max_grad_value : 0.f;
         ap.decay_after = h->decay_after ? 1 : 0;
         ap.eps_mode = h->eps_mode ? 1 : 0;
+        if (const char* e = getenv("OXZ_PUSH_HINT")) ap.push_hint = atoi(e);  // tuning aid
         for (size_t g = 0; g < p->group_lr_scale.size(); g++) {
             const double lr_t = h->lr * (double)p->group_lr_scale[g];
             const double wd = p->group_no_decay[g] ? 0.0 : h->weight_decay;
