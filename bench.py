@@ -213,6 +213,9 @@ class Checker:
         self.tensors, self.numel, self.no_decay, self.present, self.gone = tensors, numel, no_decay, present, gone
         self.v, self.world, self.rank, self.dev, self.code, self.scale = views, world, rank, local_rank, code, scale
         self.problems: list[str] = []
+        # The NCCL mode's reduce-scatter sums in the gradients' own 16-bit type and rounds the sum to it: that mode (a
+        # baseline for comparison, not the product) is checked to a tolerance, every other mode bit for bit.
+        self.exact = True
 
     # -- evidence helpers
     def checksum(self, t) -> tuple[int, int]:
@@ -340,11 +343,18 @@ class Checker:
                 wd = 0.0 if self.no_decay[i] else self.cfg.weight_decay
                 s = orc.adam_prepare(self.cfg.lr, 1.0, self.cfg.beta1, self.cfg.beta2, self.cfg.eps, wd, t0 + 1)
                 orc.adamw(p, m, v, np.ascontiguousarray(g.astype(np.float32)), s)
-                eq = {k: bool(np.array_equal(x.view(np.uint32), after[k][own].view(np.uint32))) for (k, _), x in zip(kinds, (p, m, v))}
-                if self.code != orc.F32:
-                    w = opt.export_tensor(ffi.STATE_WORK, i)
-                    eq["work"] = bool(np.array_equal(orc.narrow(p, self.code), w[own]))
-                entry["bit_equal"] = eq
+                if self.exact:
+                    eq = {k: bool(np.array_equal(x.view(np.uint32), after[k][own].view(np.uint32))) for (k, _), x in zip(kinds, (p, m, v))}
+                    if self.code != orc.F32:
+                        w = opt.export_tensor(ffi.STATE_WORK, i)
+                        eq["work"] = bool(np.array_equal(orc.narrow(p, self.code), w[own]))
+                    entry["bit_equal"] = eq
+                else:
+                    def close(x, y):
+                        x64, y64 = x.astype(np.float64), y.astype(np.float64)
+                        return bool(x.size == 0 or np.all(np.abs(x64 - y64) <= 2e-2 * (np.abs(x64) + np.sqrt(np.mean(x64 ** 2)))))
+                    eq = {k: close(x, after[k][own]) for (k, _), x in zip(kinds, (p, m, v))}
+                    entry["within_2e-2_of_the_f32_sum"] = eq
                 if not all(eq.values()):
                     bad = np.flatnonzero(p.view(np.uint32) != after["master"][own].view(np.uint32))
                     where = {"differing_master_elements": int(bad.size)}
@@ -529,7 +539,9 @@ def run_gpu(args):
     check = None
     if not args.skip_check:
         ck = Checker(torch, dist, ox, opt, cfg, tensors, numel, plan.no_decay, present, gone, v, world, rank, local_rank, ox_dt, scale)
+        ck.exact = mode != ox.SYNC_NCCL
         check = {"step": ck.one_step_against_the_checker()}
+        check["exact"] = ck.exact
         check["work_equal_on_every_rank"] = ck.weights_equal_on_every_rank()
         if args.inject_inf:
             check["overflow_scenario"] = ck.overflow_scenario()
