@@ -49,8 +49,9 @@ typedef enum oxz_sync_mode {
     OXZ_SYNC_SINGLE = 0, /* world 1: no collective (NoOpCommunicator, src/trainer.rs:234) */
     OXZ_SYNC_P2P = 1,    /* fused kernels over NVLink peer memory: pull-reduce in f32 in rank order, push of the narrow
                             weights; the step's barriers and its one small sum (norm terms, loss) also cross through
-                            peer memory, in rank order, when the ranks sit on distinct GPUs behind an NCCL
-                            communicator (OXZ_MAIL=0 in the environment keeps small NCCL all-reduces instead) */
+                            peer memory, in rank order, when up to four ranks sit on distinct GPUs behind an NCCL
+                            communicator (OXZ_MAIL=1 in the environment: at any rank count; OXZ_MAIL=0: never; small
+                            NCCL all-reduces serve otherwise, at the same speed) */
     OXZ_SYNC_NCCL = 2,   /* ncclReduceScatter / ncclAllGather in the gradient's own dtype */
     OXZ_SYNC_COPY = 3,   /* copy engines move the bytes over NVLink (peers' gradient slices into local staging,
                             the updated weights out to every peer), pipelined by groups of buckets with the

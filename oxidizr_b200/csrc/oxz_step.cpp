@@ -313,9 +313,12 @@ int32_t oxz_state_alloc(oxz_plan* p, oxz_comm* comm) {
         // Exchanges between ranks through peer memory instead of small NCCL collectives: for the modes whose kernels
         // already address peer memory, behind an NCCL communicator (its ranks sit on distinct GPUs, so the waiting
         // kernels of different ranks never share one), when the flags of all tensors fit a slot. OXZ_MAIL=0 keeps NCCL.
+        // By default up to four ranks, where the mailboxes were verified on real GPUs; OXZ_MAIL=1 asks for them at any
+        // rank count (the kernels do not depend on it), OXZ_MAIL=0 never.
         const char* mail_env = getenv("OXZ_MAIL");
+        const bool mail_on = mail_env ? atoi(mail_env) != 0 : p->cw <= 4;
         const bool want_mail = (p->mode == OXZ_SYNC_P2P || p->mode == OXZ_SYNC_REPLICATED) && p->cw > 1 && comm->kind == 0 &&
-                               p->T <= MAIL_PAYLOAD && !(mail_env && atoi(mail_env) == 0);
+                               p->T <= MAIL_PAYLOAD && mail_on;
         if (want_mail) {
             static_assert(sizeof(MailBox) <= (2u << 20), "a mailbox fits its allocation");
             OXZ_CUDA(zalloc((void**)&p->mail, 2u << 20));  // an allocation of its own page size, shared with the peers
